@@ -1,0 +1,564 @@
+// Memory-bound kernels of the transformer block for sm_100a: RMSNorm fwd/bwd, gain-free QK-norm
+// fused with RoPE fwd/bwd, SwiGLU fwd/bwd, fused cross-entropy + z-loss fwd+bwd, embedding
+// gather and its deterministic backward, canonical sums.
+//
+// Every reduction follows csrc/common/det_reduce.h and every transcendental comes from
+// csrc/common/det_math.h, so csrc/cpu/ref_ops.cpp returns the same bits.
+// Activations are templated on T in {bf16, float}; arithmetic is always fp32 with one
+// rounding to T at the store.
+//
+// Reference roles: repop rms_norm (src/pretrain/model/modules/norm_repop.py:19-22), silu
+// (ffn_repop.py:52-54), apply_rope (rope.py:103-125), fused_ce_z_loss (model/fused_loss.py:40-104),
+// deterministic embedding backward (embedding_repop.py:3-10).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "det_math.h"
+
+namespace {
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_butterfly(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+// Canonical block sum: butterfly inside each warp, then butterfly over the warp sums
+// (number of warps a power of two <= 32). All threads get the result.
+__device__ __forceinline__ float block_tree_sum(float v, float* sh /*>=32 floats*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_butterfly(v);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float w = (lane < nw) ? sh[lane] : 0.0f;
+  for (int off = nw >> 1; off >= 1; off >>= 1) w = __fadd_rn(w, __shfl_xor_sync(0xffffffffu, w, off));
+  return __shfl_sync(0xffffffffu, w, 0);
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float w = (lane < nw) ? sh[lane] : -INFINITY;
+  w = warp_max(w);
+  return w;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// one warp per row; lane_tree with VW = 8
+template <typename T>
+__global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                   float* __restrict__ rstd_out, long rows, int D, float inv_d, float eps) {
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + row * D;
+  float acc = 0.0f;
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8];
+    Vec8<T>::load(xr + c, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = __fmaf_rn(f[e], f[e], acc);
+  }
+  const float ss = warp_butterfly(acc);
+  const float rstd = det_rsqrtf(__fadd_rn(__fmul_rn(ss, inv_d), eps));
+  if (lane == 0) rstd_out[row] = rstd;
+  T* yr = y + row * D;
+  for (int c = lane * 8; c < D; c += 256) {
+    float f[8], o[8];
+    Vec8<T>::load(xr + c, f);
+    if (w) {
+      float g[8];
+      Vec8<T>::load(w + c, g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = __fmul_rn(__fmul_rn(f[e], rstd), g[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = __fmul_rn(f[e], rstd);
+    }
+    Vec8<T>::store(yr + c, o);
+  }
+}
+
+// one warp per slab of SLAB rows; dgamma partial [slab][D] = ascending-row fold inside the slab.
+// MAXC = max number of 8-wide column chunks per lane (D <= 256 * MAXC).
+constexpr int NORM_SLAB = 8;
+template <typename T, int MAXC>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                   const float* __restrict__ rstd_in, T* __restrict__ dx,
+                                   float* __restrict__ dgamma_partial, long rows, int D, float inv_d) {
+  const long slab = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long r0 = slab * NORM_SLAB;
+  if (r0 >= rows) return;
+  float dg[MAXC][8];
+#pragma unroll
+  for (int j = 0; j < MAXC; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dg[j][e] = 0.0f;
+  for (long row = r0; row < r0 + NORM_SLAB && row < rows; ++row) {
+    const float rstd = rstd_in[row];
+    const T* xr = x + row * D;
+    const T* dyr = dy + row * D;
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane * 8 + j * 256;
+      if (c < D) {
+        float xf[8], df[8], g[8];
+        Vec8<T>::load(xr + c, xf);
+        Vec8<T>::load(dyr + c, df);
+        if (w) Vec8<T>::load(w + c, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = __fmul_rn(xf[e], rstd);
+          const float gy = w ? __fmul_rn(df[e], g[e]) : df[e];
+          acc = __fmaf_rn(gy, xh, acc);
+          dg[j][e] = __fadd_rn(dg[j][e], __fmul_rn(df[e], xh));
+        }
+      }
+    }
+    const float cs = __fmul_rn(warp_butterfly(acc), inv_d);
+    T* dxr = dx + row * D;
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane * 8 + j * 256;
+      if (c < D) {
+        float xf[8], df[8], g[8], o[8];
+        Vec8<T>::load(xr + c, xf);
+        Vec8<T>::load(dyr + c, df);
+        if (w) Vec8<T>::load(w + c, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = __fmul_rn(xf[e], rstd);
+          const float gy = w ? __fmul_rn(df[e], g[e]) : df[e];
+          o[e] = __fmul_rn(rstd, __fmaf_rn(-xh, cs, gy));
+        }
+        Vec8<T>::store(dxr + c, o);
+      }
+    }
+  }
+  if (dgamma_partial) {
+    float* out = dgamma_partial + slab * D;
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane * 8 + j * 256;
+      if (c < D) {
+        *reinterpret_cast<float4*>(out + c) = make_float4(dg[j][0], dg[j][1], dg[j][2], dg[j][3]);
+        *reinterpret_cast<float4*>(out + c + 4) = make_float4(dg[j][4], dg[j][5], dg[j][6], dg[j][7]);
+      }
+    }
+  }
+}
+
+// pair_tree over the leading dimension of v[n][D], in place; result in row 0. One thread per column.
+__global__ void pair_tree_cols_kernel(float* __restrict__ v, long n, int D) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= D) return;
+  for (long s = 1; s < n; s *= 2)
+    for (long i = 0; i + s < n; i += 2 * s) v[i * D + col] = __fadd_rn(v[i * D + col], v[(i + s) * D + col]);
+}
+
+// --------------------------------------------------- gain-free QK-norm + RoPE
+// One warp per (token, head) over the first `heads` heads of a [rows, ld_in] buffer with head
+// width D (<= 128, multiple of 4): lane l holds elements 4l..4l+3 (two rotation pairs).
+// out[row, head*D + i]; rstd[row*heads + head]. lane_tree with VW = 4.
+template <typename T>
+__global__ void qknorm_rope_fwd_kernel(const T* __restrict__ in, long ld_in, T* __restrict__ out, long ld_out,
+                                       float* __restrict__ rstd_out, const float* __restrict__ cosb,
+                                       const float* __restrict__ sinb, long rows, int heads, int D, int seq_len,
+                                       int do_norm, float inv_d, float eps) {
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * heads) return;
+  const long row = wid / heads;
+  const int head = (int)(wid - row * heads);
+  const int pos = (int)(row % seq_len);
+  const bool active = lane * 4 < D;
+  float f[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const T* p = in + row * ld_in + (long)head * D + lane * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = to_f<T>(p[e]);
+  }
+  float rstd = 1.0f;
+  if (do_norm) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc = __fmaf_rn(f[e], f[e], acc);
+    const float ss = warp_butterfly(acc);
+    rstd = det_rsqrtf(__fadd_rn(__fmul_rn(ss, inv_d), eps));
+    if (lane == 0) rstd_out[wid] = rstd;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = __fmul_rn(f[e], rstd);
+  }
+  if (active) {
+    const int half = D >> 1;
+    T* o = out + row * ld_out + (long)head * D + lane * 4;
+#pragma unroll
+    for (int pr = 0; pr < 2; ++pr) {
+      const float c = cosb[(long)pos * half + lane * 2 + pr];
+      const float s = sinb[(long)pos * half + lane * 2 + pr];
+      const float xe = f[2 * pr], xo = f[2 * pr + 1];
+      o[2 * pr] = from_f<T>(__fmaf_rn(xe, c, -__fmul_rn(xo, s)));
+      o[2 * pr + 1] = from_f<T>(__fmaf_rn(xe, s, __fmul_rn(xo, c)));
+    }
+  }
+}
+
+template <typename T>
+__global__ void qknorm_rope_bwd_kernel(const T* __restrict__ dout, long ld_dout, const T* __restrict__ in, long ld_in,
+                                       const float* __restrict__ rstd_in, T* __restrict__ din, long ld_din,
+                                       const float* __restrict__ cosb, const float* __restrict__ sinb, long rows,
+                                       int heads, int D, int seq_len, int do_norm, float inv_d) {
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * heads) return;
+  const long row = wid / heads;
+  const int head = (int)(wid - row * heads);
+  const int pos = (int)(row % seq_len);
+  const bool active = lane * 4 < D;
+  float g[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const int half = D >> 1;
+    const T* p = dout + row * ld_dout + (long)head * D + lane * 4;
+#pragma unroll
+    for (int pr = 0; pr < 2; ++pr) {
+      const float c = cosb[(long)pos * half + lane * 2 + pr];
+      const float s = sinb[(long)pos * half + lane * 2 + pr];
+      const float de = to_f<T>(p[2 * pr]), dd = to_f<T>(p[2 * pr + 1]);
+      g[2 * pr] = __fmaf_rn(de, c, __fmul_rn(dd, s));
+      g[2 * pr + 1] = __fmaf_rn(dd, c, -__fmul_rn(de, s));
+    }
+  }
+  if (do_norm) {
+    const float rstd = rstd_in[wid];
+    float xh[4] = {0.f, 0.f, 0.f, 0.f};
+    if (active) {
+      const T* p = in + row * ld_in + (long)head * D + lane * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xh[e] = __fmul_rn(to_f<T>(p[e]), rstd);
+    }
+    float acc = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc = __fmaf_rn(g[e], xh[e], acc);
+    const float cs = __fmul_rn(warp_butterfly(acc), inv_d);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[e] = __fmul_rn(rstd, __fmaf_rn(-xh[e], cs, g[e]));
+  }
+  if (active) {
+    T* o = din + row * ld_din + (long)head * D + lane * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = from_f<T>(g[e]);
+  }
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// gate_up [rows, 2F] (gate = cols [0,F), up = cols [F,2F)) -> h [rows, F] = silu(gate) * up
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ h, long rows, int F) {
+  const long idx = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (idx >= rows * F) return;
+  const long row = idx / F;
+  const int col = (int)(idx - row * F);
+  float g[8], u[8], o[8];
+  Vec8<T>::load(gu + row * 2 * F + col, g);
+  Vec8<T>::load(gu + row * 2 * F + F + col, u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = __fmul_rn(__fmul_rn(g[e], det_sigmoidf(g[e])), u[e]);
+  Vec8<T>::store(h + idx, o);
+}
+// d_gate_up [rows, 2F] from dh [rows, F]
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gu, const T* __restrict__ dh, T* __restrict__ dgu, long rows,
+                                  int F) {
+  const long idx = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (idx >= rows * F) return;
+  const long row = idx / F;
+  const int col = (int)(idx - row * F);
+  float g[8], u[8], d[8], og[8], ou[8];
+  Vec8<T>::load(gu + row * 2 * F + col, g);
+  Vec8<T>::load(gu + row * 2 * F + F + col, u);
+  Vec8<T>::load(dh + idx, d);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float sg = det_sigmoidf(g[e]);
+    const float silu = __fmul_rn(g[e], sg);
+    // d silu / dg = sg * (1 + g (1 - sg))
+    const float dsilu = __fmul_rn(sg, __fmaf_rn(g[e], __fadd_rn(1.0f, -sg), 1.0f));
+    og[e] = __fmul_rn(__fmul_rn(d[e], u[e]), dsilu);
+    ou[e] = __fmul_rn(d[e], silu);
+  }
+  Vec8<T>::store(dgu + row * 2 * F + col, og);
+  Vec8<T>::store(dgu + row * 2 * F + F + col, ou);
+}
+
+// --------------------------------------------------------- fused CE + z-loss
+// One CTA of 256 threads per row of logits [rows, V] (V % 8 == 0). Element i belongs to thread
+// (i / 8) % 256, folded in ascending i; block combine = block_tree_sum. Writes ce[row] = lse - x[label],
+// lse_out[row] = lse, and overwrites the row with d loss / d logits =
+//   (softmax * (1 + 2 z lse) - onehot) * scale      (scale = 1 / (tokens * accum), host reciprocal)
+// Rows with label < 0 are ignored: zero loss, zero gradient.
+template <typename T>
+__global__ void __launch_bounds__(256) ce_zloss_kernel(T* __restrict__ logits, const long* __restrict__ labels,
+                                                       float* __restrict__ ce_out, float* __restrict__ lse_out,
+                                                       long rows, int V, float two_z, float scale, int write_grad) {
+  __shared__ float sh[32];
+  const long row = blockIdx.x;
+  T* xr = logits + row * V;
+  const long label = labels[row];
+  if (label < 0) {
+    if (threadIdx.x == 0) { ce_out[row] = 0.0f; lse_out[row] = 0.0f; }
+    if (write_grad) {
+      float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int c = threadIdx.x * 8; c < V; c += 2048) Vec8<T>::store(xr + c, z);
+    }
+    return;
+  }
+  float mx = -INFINITY;
+  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+    float f[8];
+    Vec8<T>::load(xr + c, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
+  }
+  mx = block_max(mx, sh);
+  float acc = 0.0f;
+  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+    float f[8];
+    Vec8<T>::load(xr + c, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc = __fadd_rn(acc, det_expf(__fadd_rn(f[e], -mx)));
+  }
+  const float s = block_tree_sum(acc, sh);
+  const float lse = __fadd_rn(det_logf(s), mx);
+  if (threadIdx.x == 0) {
+    ce_out[row] = __fadd_rn(lse, -to_f<T>(xr[label]));
+    lse_out[row] = lse;
+  }
+  if (!write_grad) return;
+  __syncthreads();  // the label logit was read before anyone overwrites it
+  const float a = __fmaf_rn(two_z, lse, 1.0f);
+  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+    float f[8], o[8];
+    Vec8<T>::load(xr + c, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float p = __fdiv_rn(det_expf(__fadd_rn(f[e], -mx)), s);
+      float g = __fmul_rn(p, a);
+      if (c + e == label) g = __fadd_rn(g, -1.0f);
+      o[e] = __fmul_rn(g, scale);
+    }
+    Vec8<T>::store(xr + c, o);
+  }
+}
+
+// sum (or sum of squares) of n floats: element i -> thread i % 1024, ascending fold, block_tree_sum.
+// mode 0: sum x, 1: sum x*x (fma chain). out[0] = result * post_scale.
+__global__ void __launch_bounds__(1024) det_sum_kernel(const float* __restrict__ x, long n, int mode, float post_scale,
+                                                        float* __restrict__ out) {
+  __shared__ float sh[32];
+  float acc = 0.0f;
+  for (long i = threadIdx.x; i < n; i += 1024) {
+    const float v = x[i];
+    acc = mode ? __fmaf_rn(v, v, acc) : __fadd_rn(acc, v);
+  }
+  const float s = block_tree_sum(acc, sh);
+  if (threadIdx.x == 0) out[0] = __fmul_rn(s, post_scale);
+}
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_fwd_kernel(const long* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                     long rows, int D) {
+  const long row = blockIdx.x;
+  const long id = ids[row];
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * D);
+  uint4* dst = reinterpret_cast<uint4*>(out + row * D);
+  const int nvec = D * (int)sizeof(T) / 16;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
+}
+// sorted_tok: token positions stably sorted by id; seg_start[u]..seg_start[u+1] is the run of unique id u_ids[u].
+// dW[id, :] (+)= sum over the run in ascending token position, fp32.
+template <typename T>
+__global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long* __restrict__ sorted_tok,
+                                     const long* __restrict__ seg_start, const long* __restrict__ u_ids,
+                                     float* __restrict__ dW, int D, int accumulate) {
+  const long u = blockIdx.x;
+  const long b = seg_start[u], e = seg_start[u + 1];
+  float* out = dW + u_ids[u] * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.0f;
+    for (long i = b; i < e; ++i) acc = __fadd_rn(acc, to_f<T>(dy[sorted_tok[i] * D + c]));
+    out[c] = accumulate ? __fadd_rn(out[c], acc) : acc;
+  }
+}
+
+// elementwise helpers ---------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long n) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_f<TO>(to_f<TI>(in[i]));
+}
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, long n) {
+  const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float x[8], y[8], o[8];
+  Vec8<T>::load(a + i, x);
+  Vec8<T>::load(b + i, y);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = __fadd_rn(x[e], y[e]);
+  Vec8<T>::store(out + i, o);
+}
+
+inline unsigned blocks_for(long n, int per) { return (unsigned)((n + per - 1) / per); }
+
+}  // namespace
+
+#define S(stream) reinterpret_cast<cudaStream_t>(stream)
+#define DISPATCH_T(is_bf16, ...)                       \
+  if (is_bf16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+  else { using T = float; __VA_ARGS__ }
+
+// dtype: 1 = bf16, 0 = fp32 for every activation pointer. All row widths multiples of 8.
+extern "C" int otb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int D, float inv_d,
+                               float eps, int dtype, void* stream) {
+  if (D % 8) return -2;
+  DISPATCH_T(dtype, rmsnorm_fwd_kernel<T><<<blocks_for(rows, 8), 256, 0, S(stream)>>>(
+                        (const T*)x, (const T*)w, (T*)y, rstd, rows, D, inv_d, eps);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                               float* dgamma_partial, long rows, int D, float inv_d, int dtype, void* stream) {
+  if (D % 8 || D > 256 * 16) return -2;
+  const long slabs = (rows + NORM_SLAB - 1) / NORM_SLAB;
+#define RB(MAXC)                                                                                     \
+  DISPATCH_T(dtype, rmsnorm_bwd_kernel<T, MAXC><<<blocks_for(slabs, 4), 128, 0, S(stream)>>>(         \
+                        (const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dgamma_partial, rows, D, inv_d);)
+  if (D <= 256) { RB(1) } else if (D <= 1024) { RB(4) } else if (D <= 2048) { RB(8) } else { RB(16) }
+#undef RB
+  if (dgamma_partial) pair_tree_cols_kernel<<<blocks_for(D, 128), 128, 0, S(stream)>>>(dgamma_partial, slabs, D);
+  return (int)cudaGetLastError();
+}
+extern "C" long otb_rmsnorm_slabs(long rows) { return (rows + NORM_SLAB - 1) / NORM_SLAB; }
+
+extern "C" int otb_pair_tree_cols(float* v, long n, int D, void* stream) {
+  pair_tree_cols_kernel<<<blocks_for(D, 128), 128, 0, S(stream)>>>(v, n, D);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int otb_qknorm_rope_fwd(const void* in, long ld_in, void* out, long ld_out, float* rstd, const float* cosb,
+                                   const float* sinb, long rows, int heads, int D, int seq_len, int do_norm,
+                                   float inv_d, float eps, int dtype, void* stream) {
+  if (D % 4 || D > 128) return -2;
+  DISPATCH_T(dtype, qknorm_rope_fwd_kernel<T><<<blocks_for(rows * heads, 8), 256, 0, S(stream)>>>(
+                        (const T*)in, ld_in, (T*)out, ld_out, rstd, cosb, sinb, rows, heads, D, seq_len, do_norm, inv_d,
+                        eps);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_qknorm_rope_bwd(const void* dout, long ld_dout, const void* in, long ld_in, const float* rstd,
+                                   void* din, long ld_din, const float* cosb, const float* sinb, long rows, int heads,
+                                   int D, int seq_len, int do_norm, float inv_d, int dtype, void* stream) {
+  if (D % 4 || D > 128) return -2;
+  DISPATCH_T(dtype, qknorm_rope_bwd_kernel<T><<<blocks_for(rows * heads, 8), 256, 0, S(stream)>>>(
+                        (const T*)dout, ld_dout, (const T*)in, ld_in, rstd, (T*)din, ld_din, cosb, sinb, rows, heads, D,
+                        seq_len, do_norm, inv_d);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_swiglu_fwd(const void* gu, void* h, long rows, int F, int dtype, void* stream) {
+  if (F % 8) return -2;
+  DISPATCH_T(dtype, swiglu_fwd_kernel<T><<<blocks_for(rows * F / 8, 256), 256, 0, S(stream)>>>((const T*)gu, (T*)h,
+                                                                                                 rows, F);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_swiglu_bwd(const void* gu, const void* dh, void* dgu, long rows, int F, int dtype, void* stream) {
+  if (F % 8) return -2;
+  DISPATCH_T(dtype, swiglu_bwd_kernel<T><<<blocks_for(rows * F / 8, 256), 256, 0, S(stream)>>>(
+                        (const T*)gu, (const T*)dh, (T*)dgu, rows, F);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_ce_zloss(void* logits, const long* labels, float* ce, float* lse, long rows, int V, float two_z,
+                            float scale, int write_grad, int dtype, void* stream) {
+  if (V % 8) return -2;
+  DISPATCH_T(dtype, ce_zloss_kernel<T><<<(unsigned)rows, 256, 0, S(stream)>>>((T*)logits, labels, ce, lse, rows, V,
+                                                                               two_z, scale, write_grad);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_det_sum(const float* x, long n, int mode, float post_scale, float* out, void* stream) {
+  det_sum_kernel<<<1, 1024, 0, S(stream)>>>(x, n, mode, post_scale, out);
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_embedding_fwd(const long* ids, const void* table, void* out, long rows, int D, int dtype,
+                                 void* stream) {
+  if (D % 8) return -2;
+  DISPATCH_T(dtype, embedding_fwd_kernel<T><<<(unsigned)rows, 128, 0, S(stream)>>>(ids, (const T*)table, (T*)out, rows,
+                                                                                    D);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_embedding_bwd(const void* dy, const long* sorted_tok, const long* seg_start, const long* u_ids,
+                                 long n_unique, float* dW, int D, int accumulate, int dtype, void* stream) {
+  if (n_unique <= 0) return 0;
+  DISPATCH_T(dtype, embedding_bwd_kernel<T><<<(unsigned)n_unique, 256, 0, S(stream)>>>(
+                        (const T*)dy, sorted_tok, seg_start, u_ids, dW, D, accumulate);)
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_cast(const void* in, void* out, long n, int in_bf16, int out_bf16, void* stream) {
+  const unsigned g = blocks_for(n, 256);
+  if (in_bf16 && !out_bf16) cast_kernel<__nv_bfloat16, float><<<g, 256, 0, S(stream)>>>((const __nv_bfloat16*)in, (float*)out, n);
+  else if (!in_bf16 && out_bf16) cast_kernel<float, __nv_bfloat16><<<g, 256, 0, S(stream)>>>((const float*)in, (__nv_bfloat16*)out, n);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+extern "C" int otb_add(const void* a, const void* b, void* out, long n, int dtype, void* stream) {
+  if (n % 8) return -2;
+  DISPATCH_T(dtype, add_kernel<T><<<blocks_for(n / 8, 256), 256, 0, S(stream)>>>((const T*)a, (const T*)b, (T*)out, n);)
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,89 @@
+"""ctypes access to the two native libraries (``_ext/libotb_cuda.so``, ``_ext/libotb_cpu.so``).
+
+The CUDA library is mandatory on a GPU machine: ``cuda_lib()`` raises instead of silently
+falling back to PyTorch ops, so a GPU test can never pass on a library path by accident.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_EXT = Path(__file__).resolve().parent.parent / "_ext"
+_lock = threading.Lock()
+_libs: dict[str, ctypes.CDLL] = {}
+
+c_void_p, c_int, c_long, c_float, c_double = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_double
+
+
+def _load(name: str, builder: str) -> ctypes.CDLL:
+    with _lock:
+        if name in _libs:
+            return _libs[name]
+        path = _EXT / ("lib%s.so" % name)
+        if not path.exists() or os.environ.get("OTB_REBUILD") == "1":
+            from .. import build_native
+
+            getattr(build_native, builder)()
+        lib = ctypes.CDLL(str(path))
+        _libs[name] = lib
+        return lib
+
+
+def cpu_lib() -> ctypes.CDLL:
+    return _load("otb_cpu", "build_cpu")
+
+
+def cuda_lib() -> ctypes.CDLL:
+    return _load("otb_cuda", "build_cuda")
+
+
+def loaded_libraries() -> list[str]:
+    return sorted(_libs)
+
+
+def P(t) -> ctypes.c_void_p:
+    """Pointer argument from a tensor (None -> NULL)."""
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def I(x) -> ctypes.c_int:
+    return c_int(int(x))
+
+
+def L(x) -> ctypes.c_long:
+    return c_long(int(x))
+
+
+def F(x) -> ctypes.c_float:
+    return c_float(float(x))
+
+
+def D(x) -> ctypes.c_double:
+    return c_double(float(x))
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError("%s failed with code %d" % (what, rc))
+
+
+def is_bf16(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError("activations must be bf16 or fp32, got %s" % t.dtype)
