@@ -169,6 +169,43 @@ DET_HD float det_logf(float x) {
   return r;
 }
 
+
+// exp(x) for the attention kernels, x <= 0 (or -inf): same reduction and polynomial as det_expf,
+// inputs below -87 return 0 so the 2^k scaling is a single exact-exponent multiply.
+DET_HD float det_exp_attn(float x) {
+  if (!(x >= -87.0f)) return 0.0f;
+  const float kf = det_rintf(det_mulf(x, 1.44269504088896341f));
+  float r = det_fmaf(kf, -0.693359375f, x);
+  r = det_fmaf(kf, 2.12194440e-4f, r);
+  float p = 1.9875691500e-4f;
+  p = det_fmaf(p, r, 1.3981999507e-3f);
+  p = det_fmaf(p, r, 8.3334519073e-3f);
+  p = det_fmaf(p, r, 4.1665795894e-2f);
+  p = det_fmaf(p, r, 1.6666665459e-1f);
+  p = det_fmaf(p, r, 5.0000001201e-1f);
+  const float r2 = det_mulf(r, r);
+  const float y = det_addf(det_fmaf(p, r2, r), 1.0f);
+  return det_mulf(y, det_pow2i((int)kf));
+}
+
+// 2^y for the attention kernels, y in [-125, ~1] (anything below -125, -inf included, gives 0).
+// Round-to-nearest-integer by the 1.5*2^23 trick (two exact adds), r = y - k exact, degree-6
+// polynomial for 2^r on |r| <= 1/2, then k is added to the exponent field.
+DET_HD float det_exp2_attn(float y) {
+  if (!(y >= -125.0f)) return 0.0f;
+  const float t = det_addf(y, 12582912.0f);
+  const float kf = det_addf(t, -12582912.0f);
+  const float r = det_addf(y, -kf);
+  float p = 1.5403530393381606e-4f;
+  p = det_fmaf(p, r, 1.3333558146428443e-3f);
+  p = det_fmaf(p, r, 9.6181291076284772e-3f);
+  p = det_fmaf(p, r, 5.5504108664821580e-2f);
+  p = det_fmaf(p, r, 2.4022650695910071e-1f);
+  p = det_fmaf(p, r, 6.9314718055994531e-1f);
+  p = det_fmaf(p, r, 1.0f);
+  return det_u2f(det_f2u(p) + ((det_f2u(t) - 0x4B400000u) << 23));
+}
+
 // sigmoid(x) = 1 / (1 + exp(-x))
 DET_HD float det_sigmoidf(float x) { return det_divf(1.0f, det_addf(1.0f, det_expf(-x))); }
 

@@ -1,0 +1,213 @@
+// CPU twins of the GEMM and attention kernels.
+//
+// Two arithmetic families exist, on the GPU and here alike:
+//   * exact fp32 family (fp32 activations): every dot product is ONE chain
+//       acc = fma(a_k, b_k, acc), k ascending, acc starting at +0
+//     which csrc/cuda/exact_f32.cu reproduces bit for bit on CUDA cores;
+//   * bf16 tensor-core family (bf16 activations): products of bf16 values are exact in fp32;
+//     this twin accumulates them with the same ascending-k fma chain. The tensor core adds its
+//     16 products per instruction with its own internal alignment, so for bf16 runs this twin is
+//     a MODEL of the GPU (equal for exactly-representable sums, otherwise within a few ulp), not
+//     a bit-exact copy; fp32 runs are bit-exact.
+// The attention twin follows csrc/cuda/attention_tc05.cu step by step: 128-key blocks in
+// ascending order, two 64-key halves per row, log2-domain scores, det_exp2_attn, deferred
+// O = fma(O, alpha, PV).
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <vector>
+
+#include "det_math.h"
+#include "det_reduce.h"
+
+namespace {
+inline float ldx(const void* p, long i, int bf16) {
+  return bf16 ? det_bf2f(((const uint16_t*)p)[i]) : ((const float*)p)[i];
+}
+inline void stx(void* p, long i, float v, int bf16) {
+  if (bf16) ((uint16_t*)p)[i] = det_f2bf(v);
+  else ((float*)p)[i] = v;
+}
+}  // namespace
+
+extern "C" {
+
+// C[M,N] = op(A) op(B)^T. a_mn = 0: A is [M,K] (lda), 1: A is [K,M]. b_mn = 0: B is [N,K], 1: B is [K,N].
+// epi: 0 store in out dtype, 1 store fp32, 2 accumulate into fp32 C, 3 store out dtype of acc + R.
+// in_bf16: operand dtype; out_bf16: dtype of C for epi 0/3 and of R.
+int otb_cpu_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long lda, long ldb, long ldc,
+                 long ldr, int a_mn, int b_mn, int epi, int in_bf16, int out_bf16) {
+  // gather operands once into K-contiguous fp32 panels
+  std::vector<float> a((size_t)M * K), b((size_t)N * K);
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m)
+    for (int k = 0; k < K; ++k) a[(size_t)m * K + k] = a_mn ? ldx(A, (long)k * lda + m, in_bf16) : ldx(A, (long)m * lda + k, in_bf16);
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int k = 0; k < K; ++k) b[(size_t)n * K + k] = b_mn ? ldx(B, (long)k * ldb + n, in_bf16) : ldx(B, (long)n * ldb + k, in_bf16);
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    const float* ar = &a[(size_t)m * K];
+    for (int n = 0; n < N; ++n) {
+      const float* br = &b[(size_t)n * K];
+      float acc = 0.0f;
+      for (int k = 0; k < K; ++k) acc = det_fmaf(ar[k], br[k], acc);
+      const long ci = (long)m * ldc + n;
+      switch (epi) {
+        case 0: stx(C, ci, acc, out_bf16); break;
+        case 1: ((float*)C)[ci] = acc; break;
+        case 2: ((float*)C)[ci] = ((float*)C)[ci] + acc; break;
+        default: stx(C, ci, acc + ldx(R, (long)m * ldr + n, out_bf16), out_bf16); break;
+      }
+    }
+  }
+  return 0;
+}
+
+// qk: [B*T, ldqk] (H query heads then Hkv key heads), qkv: [B*T, ldqkv] with V at column (H+Hkv)*D,
+// O: [B*T, ldo], lse: [B,H,T] (log2 domain). bf16 = activation dtype (P is rounded to bf16 only then).
+int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B, int T,
+                     int H, int Hkv, int D, int window, float scale, int bf16) {
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  const int G = H / Hkv;
+#pragma omp parallel for collapse(2) schedule(dynamic, 8)
+  for (int bh = 0; bh < B * H; ++bh) {
+    for (int qi = 0; qi < T; ++qi) {
+      const int b = bh / H, h = bh % H, g = h / G;
+      const long qrow = (long)b * T + qi;
+      float q[128], o[128], pv[128], p[128];
+      for (int d = 0; d < D; ++d) { q[d] = ldx(qk, qrow * ldqk + (long)h * D + d, bf16); o[d] = 0.0f; }
+      const int q0 = (qi / 128) * 128;
+      const int jmax = qi / 128;
+      const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
+      float m_run = -INFINITY, l_half[2] = {0.0f, 0.0f};
+      for (int j = jmin; j <= jmax; ++j) {
+        float s[128];
+        float mx = -INFINITY;
+        for (int e = 0; e < 128; ++e) {
+          const int kj = j * 128 + e;
+          const bool dead = kj > qi || (window > 0 && kj <= qi - window) || kj >= T;
+          if (dead) { s[e] = -INFINITY; continue; }
+          const long krow = (long)b * T + kj;
+          float acc = 0.0f;
+          for (int d = 0; d < D; ++d) acc = det_fmaf(q[d], ldx(qk, krow * ldqk + (long)(H + g) * D + d, bf16), acc);
+          s[e] = acc;
+          mx = fmaxf(mx, acc);
+        }
+        const float m_new = fmaxf(m_run, mx * c_log2);
+        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float alpha = det_exp2_attn(m_run + (-m_safe));
+        for (int hf = 0; hf < 2; ++hf) {
+          float lsum = 0.0f;
+          for (int e = hf * 64; e < hf * 64 + 64; ++e) {
+            const float y = (s[e] == -INFINITY) ? -INFINITY : det_fmaf(s[e], c_log2, -m_safe);
+            const float pe = det_exp2_attn(y);
+            lsum = lsum + pe;
+            p[e] = bf16 ? det_bf2f(det_f2bf(pe)) : pe;
+          }
+          l_half[hf] = det_fmaf(l_half[hf], alpha, lsum);
+        }
+        for (int d = 0; d < D; ++d) pv[d] = 0.0f;
+        for (int e = 0; e < 128; ++e) {
+          const int kj = j * 128 + e;
+          if (kj >= T) break;
+          if (p[e] == 0.0f) continue;  // fma(0, v, acc) == acc for finite v
+          const long krow = (long)b * T + kj;
+          for (int d = 0; d < D; ++d) pv[d] = det_fmaf(p[e], ldx(qkv, krow * ldqkv + (long)(H + Hkv + g) * D + d, bf16), pv[d]);
+        }
+        for (int d = 0; d < D; ++d) o[d] = det_fmaf(o[d], alpha, pv[d]);
+        m_run = m_new;
+      }
+      const float l_tot = l_half[0] + l_half[1];
+      for (int d = 0; d < D; ++d) stx(O, qrow * ldo + (long)h * D + d, o[d] / l_tot, bf16);
+      lse[((long)b * H + h) * T + qi] = det_fmaf(det_logf(l_tot), 1.44269504088896341f, m_run);
+    }
+  }
+  return 0;
+}
+
+// Backward. dqk: [B*T, lddqk] (dQ heads then dK heads); dV at column (H+Hkv)*D of dqkv; delta: [B,H,T] scratch.
+int otb_cpu_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldqkv, const void* O, long ldo, const void* dO,
+                     long lddo, const float* lse, float* delta, void* dqk, long lddqk, void* dqkv, long lddqkv, int B,
+                     int T, int H, int Hkv, int D, int window, float scale, int bf16) {
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  const int G = H / Hkv;
+  // delta: lane_tree with VW = 4
+#pragma omp parallel for schedule(static)
+  for (long w = 0; w < (long)B * T * H; ++w) {
+    const long row = w / H;
+    const int h = (int)(w % H);
+    float part[32];
+    for (int l = 0; l < 32; ++l) part[l] = 0.0f;
+    for (int d = 0; d < D; ++d)
+      part[d / 4] = det_fmaf(ldx(dO, row * lddo + (long)h * D + d, bf16), ldx(O, row * ldo + (long)h * D + d, bf16), part[d / 4]);
+    const long b = row / T, t = row % T;
+    delta[(b * H + h) * T + t] = det_butterfly_host(part, 32);
+  }
+  auto prob_ds = [&](int b, int h, int g, int qi, int kj, float* p_out, float* ds_out) {
+    // returns false when the pair is masked
+    if (kj > qi || (window > 0 && kj <= qi - window)) return false;
+    const long qrow = (long)b * T + qi, krow = (long)b * T + kj;
+    float s = 0.0f, dp = 0.0f;
+    for (int d = 0; d < D; ++d) s = det_fmaf(ldx(qk, qrow * ldqk + (long)h * D + d, bf16), ldx(qk, krow * ldqk + (long)(H + g) * D + d, bf16), s);
+    for (int d = 0; d < D; ++d) dp = det_fmaf(ldx(dO, qrow * lddo + (long)h * D + d, bf16), ldx(qkv, krow * ldqkv + (long)(H + Hkv + g) * D + d, bf16), dp);
+    const float l2 = lse[((long)b * H + h) * T + qi], dl = delta[((long)b * H + h) * T + qi];
+    const float p = det_exp2_attn(det_fmaf(s, c_log2, -l2));
+    const float ds = (p * (dp + (-dl))) * scale;
+    *p_out = bf16 ? det_bf2f(det_f2bf(p)) : p;
+    *ds_out = bf16 ? det_bf2f(det_f2bf(ds)) : ds;
+    return true;
+  };
+  // dK, dV: owner = (b, kv head, key); heads of the group ascending, then queries ascending
+#pragma omp parallel for collapse(2) schedule(dynamic, 8)
+  for (int bg = 0; bg < B * Hkv; ++bg) {
+    for (int kj = 0; kj < T; ++kj) {
+      const int b = bg / Hkv, g = bg % Hkv;
+      float dk[128], dv[128];
+      for (int d = 0; d < D; ++d) { dk[d] = 0.0f; dv[d] = 0.0f; }
+      const int kb = kj / 128;
+      int qlast = (T + 127) / 128 - 1;
+      if (window > 0) { const int ql = (kb * 128 + 127 + window - 1) / 128; if (ql < qlast) qlast = ql; }
+      for (int hh = 0; hh < G; ++hh) {
+        const int h = g * G + hh;
+        for (int qi = kb * 128; qi < (qlast + 1) * 128 && qi < T; ++qi) {
+          float p, ds;
+          if (!prob_ds(b, h, g, qi, kj, &p, &ds)) continue;
+          const long qrow = (long)b * T + qi;
+          for (int d = 0; d < D; ++d) {
+            dv[d] = det_fmaf(p, ldx(dO, qrow * lddo + (long)h * D + d, bf16), dv[d]);
+            dk[d] = det_fmaf(ds, ldx(qk, qrow * ldqk + (long)h * D + d, bf16), dk[d]);
+          }
+        }
+      }
+      const long krow = (long)b * T + kj;
+      for (int d = 0; d < D; ++d) {
+        stx(dqk, krow * lddqk + (long)(H + g) * D + d, dk[d], bf16);
+        stx(dqkv, krow * lddqkv + (long)(H + Hkv + g) * D + d, dv[d], bf16);
+      }
+    }
+  }
+  // dQ: owner = (b, head, query); keys ascending
+#pragma omp parallel for collapse(2) schedule(dynamic, 8)
+  for (int bh = 0; bh < B * H; ++bh) {
+    for (int qi = 0; qi < T; ++qi) {
+      const int b = bh / H, h = bh % H, g = h / G;
+      float dq[128];
+      for (int d = 0; d < D; ++d) dq[d] = 0.0f;
+      const int q0 = (qi / 128) * 128;
+      const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
+      for (int kj = jmin * 128; kj <= qi; ++kj) {
+        float p, ds;
+        if (!prob_ds(b, h, g, qi, kj, &p, &ds)) continue;
+        const long krow = (long)b * T + kj;
+        for (int d = 0; d < D; ++d) dq[d] = det_fmaf(ds, ldx(qk, krow * ldqk + (long)(H + g) * D + d, bf16), dq[d]);
+      }
+      const long qrow = (long)b * T + qi;
+      for (int d = 0; d < D; ++d) stx(dqk, qrow * lddqk + (long)h * D + d, dq[d], bf16);
+    }
+  }
+  return 0;
+}
+
+}  // extern "C"

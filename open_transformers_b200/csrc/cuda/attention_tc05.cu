@@ -1,0 +1,799 @@
+// Causal / sliding-window flash attention for sm_100a on tcgen05 tensor cores, GQA-native.
+//
+// Three kernels share one structure (warp 0: TMA producer, warp 1: tcgen05.mma issuer, warps
+// 2..9: two threads per row - one per 64-key half - doing the softmax arithmetic straight out of
+// tensor memory; warp w may touch TMEM lanes 32*(w%4)..+31, so warps w and w+4 share rows):
+//
+//   attn_fwd    CTA = (batch, query head, 128 query rows); loops over 128-key blocks in ascending
+//               key order:  S = Q K^T (TMEM) -> online softmax -> P (bf16, shared) -> P V (TMEM,
+//               fresh per block) -> O = O*alpha + PV in registers.
+//   attn_bwd_kv CTA = (batch, KV head, 128 keys); loops over the query heads of the group and
+//               the query blocks that see these keys, both ascending; dV += P^T dO and
+//               dK += dS^T Q accumulate in TMEM.
+//   attn_bwd_q  CTA = (batch, query head, 128 query rows); loops over key blocks ascending;
+//               dQ += dS K accumulates in TMEM.
+//
+// No atomics, no split accumulation: every output element has one owner CTA and a fixed
+// summation order, so results are identical for any grid, stream or GPU count. The window rule
+// is "key in (query - window, query]" (window = 0: full causal). Scores are used in the log2
+// domain: y = fma(s, c, -m) with c = scale*log2(e), p = det_exp2_attn(y) (shared with the CPU
+// twin), masked scores are -inf. The saved row statistic `lse` is m + log2(l) in that domain.
+// Row sums: each 64-key half is folded in ascending key order, l = l_half0 + l_half1 at the end.
+//
+// Layouts: q/k come from one [B*T, ld] bf16 buffer (post-RoPE; head h at column h*D, KV head g
+// at column (H+g)*D); v comes from the packed qkv buffer; O is [B*T, H*D]; lse and delta are
+// [B, H, T] fp32. Reference role: repop causal_flash_attention fwd/bwd
+// (src/pretrain/model/modules/attention_repop.py:38-53).
+#include "tc05.cuh"
+#include "common.cuh"
+#include "det_math.h"
+
+using namespace tc05;
+
+namespace {
+
+constexpr int BQ = 128;   // query rows per tile
+constexpr int BKV = 128;  // keys per block
+constexpr int ATT_THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
+
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+struct Bars {
+  uint64_t b[24];
+  uint32_t tmem_slot;
+  uint32_t abort_flag;
+};
+struct BarsX : Bars {
+  float xch[2][2][128];  // [parity][half][row] exchange between the two threads of a row
+};
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+// byte offset of the 16-byte chunk `ch` (0..7) of row r in a [rows][128 B] 128B-swizzled tile
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t ch) { return r * 128u + ((ch ^ (r & 7u)) << 4); }
+
+// K-major operand, tile made of [128 rows][64 elems] sub-tiles 16 KB apart; k-step kk = 16 elems
+__device__ __forceinline__ uint64_t desc_k(uint32_t base, int kk) {
+  return make_smem_desc(base + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+}
+// MN-major operand, tile made of [128 k-rows][64 mn elems] chunks 16 KB apart; k-step kk = 16 rows
+__device__ __forceinline__ uint64_t desc_mn(uint32_t base, int kk) {
+  return make_smem_desc(base + kk * 2048, 16384, 1024);
+}
+
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row, int b) {
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_3d(dst + c * 16384, tm, bar, col + c * 64, row, b);
+}
+
+// ---------------------------------------------------------------------------- forward
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                __nv_bfloat16* __restrict__ O, long ldo, float* __restrict__ lse_out, int T, int H, int Hkv, int window,
+                float scale, float c_log2, uint32_t* __restrict__ status) {
+  constexpr int TILE = BQ * D * 2;
+  constexpr int ST = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;
+  uint8_t* sP = sQ + TILE;
+  uint8_t* sK = sP + BQ * BKV * 2;
+  uint8_t* sV = sK + ST * TILE;
+  BarsX* bars = reinterpret_cast<BarsX*>(sV + ST * TILE);
+  uint64_t* q_full = &bars->b[0];
+  uint64_t* k_full = &bars->b[1];    // [ST]
+  uint64_t* k_empty = &bars->b[3];   // [ST]
+  uint64_t* v_full = &bars->b[5];    // [ST]
+  uint64_t* v_empty = &bars->b[7];   // [ST]
+  uint64_t* s_full = &bars->b[9];    // [2]
+  uint64_t* s_empty = &bars->b[11];  // [2]
+  uint64_t* p_ready = &bars->b[13];
+  uint64_t* pv_full = &bars->b[14];
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (T + BQ - 1) / BQ;
+  const int qt = nq - 1 - blockIdx.x;  // heavy tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (H / Hkv);
+  const int q0 = qt * BQ;
+  const int jmax = qt;
+  const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / BKV : 0;
+  const int n = jmax - jmin + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); }
+    mbar_init(p_ready, 8);
+    mbar_init(pv_full, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  const uint32_t tS = tmem, tPV = tmem + 256;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(q_full, TILE);
+      load_tile<D>(sQ, &tmQK, q_full, h * D, q0, b);
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const uint32_t ph = (i / ST) & 1;
+        const int k0 = (jmin + i) * BKV;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&k_full[st], TILE);
+        load_tile<D>(sK + st * TILE, &tmQK, &k_full[st], (H + g) * D, k0, b);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&v_full[st], TILE);
+        load_tile<D>(sV + st * TILE, &tmV, &v_full[st], (H + Hkv + g) * D, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);
+      constexpr uint32_t idPV = make_idesc(128, D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_S = [&](int i) {
+        const int st = i % ST;
+        if (!mbar_wait(&k_full[st], (i / ST) & 1, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[i & 1], ((i >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tS + (i & 1) * 128, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
+        mma_commit(&s_full[i & 1]);
+        mma_commit(&k_empty[st]);
+        return true;
+      };
+      if (ok) ok = issue_S(0);
+      for (int i = 0; i < n && ok; ++i) {
+        if (i + 1 < n) { if (!issue_S(i + 1)) { ok = false; break; } }
+        const int st = i % ST;
+        if (!mbar_wait(p_ready, i & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], (i / ST) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + st * TILE);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tPV, desc_k(aP, kk), desc_mn(aV, kk), idPV, kk != 0);
+        mma_commit(pv_full);
+        mma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    constexpr int DH = D / 2;
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = qd * 32 + lane;          // row inside the tile == TMEM lane
+    const int qi = q0 + r;                 // query position
+    const uint32_t lane_off = uint32_t(qd * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
+    float o[DH];
+#pragma unroll
+    for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const int j = jmin + i;
+      const int kbase = j * BKV + half * 64;
+      const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window);
+      ok = ok && mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
+      tc_fence_after();
+      const uint32_t tSb = tS + (i & 1) * 128 + half * 64 + lane_off;
+      // pass 1: maximum of the masked raw scores over this thread's 64 keys, then over the row
+      float mx = -INFINITY;
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tSb + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float sv = __uint_as_float(v[e]);
+            if (need_mask) {
+              const int kj = kbase + c * 32 + e;
+              if (kj > qi || (window > 0 && kj <= qi - window)) sv = -INFINITY;
+            }
+            mx = fmaxf(mx, sv);
+          }
+        }
+      }
+      bars->xch[i & 1][half][r] = mx;
+      softmax_bar();
+      mx = fmaxf(mx, bars->xch[i & 1][half ^ 1][r]);
+      const float m_new = fmaxf(m_run, __fmul_rn(mx, c_log2));
+      const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = det_exp2_attn(__fadd_rn(m_run, -m_safe));
+      // deferred accumulation of the previous block's P V (its completion also frees the P buffer)
+      if (i > 0) {
+        ok = ok && mbar_wait(pv_full, (i - 1) & 1, abort_flag);
+        tc_fence_after();
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tPV + lane_off + half * DH + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[c * 32 + e] = __fmaf_rn(o[c * 32 + e], alpha_prev, __uint_as_float(v[e]));
+          }
+        }
+      }
+      // pass 2: probabilities, half-row sum (ascending key), bf16 P into shared memory
+      float lsum = 0.0f;
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tSb + c * 32, v);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p2[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              float y = __fmaf_rn(__uint_as_float(v[e + u]), c_log2, -m_safe);
+              if (need_mask) {
+                const int kj = kbase + c * 32 + e + u;
+                if (kj > qi || (window > 0 && kj <= qi - window)) y = -INFINITY;
+              }
+              p2[u] = det_exp2_attn(y);
+              lsum = __fadd_rn(lsum, p2[u]);
+            }
+            pk[e >> 1] = pack_bf16(p2[0], p2[1]);
+          }
+          uint8_t* base = sP + half * 16384;
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
+                make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+        }
+      }
+      l_run = __fmaf_rn(l_run, alpha, lsum);
+      m_run = m_new;
+      alpha_prev = alpha;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && ok) { mbar_arrive(p_ready); mbar_arrive(&s_empty[i & 1]); }
+    }
+    ok = ok && mbar_wait(pv_full, (n - 1) & 1, abort_flag);
+    tc_fence_after();
+    bars->xch[n & 1][half][r] = l_run;
+    softmax_bar();
+    const float l_tot = __fadd_rn(bars->xch[n & 1][0][r], bars->xch[n & 1][1][r]);
+    if (ok) {
+      const bool in_range = qi < T;
+      __nv_bfloat16* orow = O + ((long)b * T + qi) * ldo + (long)h * D + half * DH;
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tPV + lane_off + half * DH + c * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float a0 = __fdiv_rn(__fmaf_rn(o[c * 32 + e], alpha_prev, __uint_as_float(v[e])), l_tot);
+          const float a1 = __fdiv_rn(__fmaf_rn(o[c * 32 + e + 1], alpha_prev, __uint_as_float(v[e + 1])), l_tot);
+          pk[e >> 1] = pack_bf16(a0, a1);
+        }
+        if (in_range) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            reinterpret_cast<uint4*>(orow + c * 32)[w] = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+        }
+      }
+      if (in_range && half == 0)
+        lse_out[((long)b * H + h) * T + qi] = __fmaf_rn(det_logf(l_tot), 1.44269504088896341f, m_run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 2u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// -------------------------------------------------------- backward: dK and dV
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmDO, const float* __restrict__ lse,
+                   const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK, long lddk,
+                   __nv_bfloat16* __restrict__ dV, long lddv, int T, int H, int Hkv, int window, float scale,
+                   float c_log2, uint32_t* __restrict__ status) {
+  constexpr int TILE = BQ * D * 2;
+  constexpr int ST = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sPdS = sV + TILE;
+  uint8_t* sQ = sPdS + BQ * BKV * 2;  // [ST]
+  uint8_t* sDO = sQ + ST * TILE;      // [ST]
+  Bars* bars = reinterpret_cast<Bars*>(sDO + ST * TILE);
+  uint64_t* kv_full = &bars->b[0];
+  uint64_t* qdo_full = &bars->b[1];   // [ST]
+  uint64_t* qdo_empty = &bars->b[3];  // [ST]
+  uint64_t* sdp_full = &bars->b[5];
+  uint64_t* sdp_empty = &bars->b[6];
+  uint64_t* p_ready = &bars->b[7];
+  uint64_t* dv_done = &bars->b[8];
+  uint64_t* ds_ready = &bars->b[9];
+  uint64_t* dk_done = &bars->b[10];
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (T + BQ - 1) / BQ;
+  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int G = H / Hkv;
+  const int k0 = kb * BKV;
+  int qlast = nq - 1;
+  if (window > 0) qlast = min(qlast, (k0 + BKV - 1 + window - 1) / BQ);
+  const int nqi = qlast - kb + 1;  // query blocks per head
+  const int n = G * nqi;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(p_ready, 8); mbar_init(dv_done, 1);
+    mbar_init(ds_ready, 8); mbar_init(dk_done, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(kv_full, 2 * TILE);
+      load_tile<D>(sK, &tmQK, kv_full, (H + g) * D, k0, b);
+      load_tile<D>(sV, &tmV, kv_full, (H + Hkv + g) * D, k0, b);
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const int h = g * G + i / nqi;
+        const int q0 = (kb + i % nqi) * BQ;
+        if (!mbar_wait(&qdo_empty[st], ((i / ST) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&qdo_full[st], 2 * TILE);
+        load_tile<D>(sQ + st * TILE, &tmQK, &qdo_full[st], h * D, q0, b);
+        load_tile<D>(sDO + st * TILE, &tmDO, &qdo_full[st], h * D, q0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);   // S = Q K^T, dP = dO V^T
+      constexpr uint32_t idG = make_idesc(128, D, 1, 1);     // dV = P^T dO, dK = dS^T Q
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sPdS);
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      auto issue_sdp = [&](int i) {
+        const int st = i % ST;
+        if (!mbar_wait(&qdo_full[st], (i / ST) & 1, abort_flag)) return false;
+        if (!mbar_wait(sdp_empty, (i & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * TILE), aDO = smem_u32(sDO + st * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tS, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tDP, desc_k(aDO, kk), desc_k(aV, kk), idS, kk != 0);
+        mma_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i % ST;
+        const uint32_t aQ = smem_u32(sQ + st * TILE), aDO = smem_u32(sDO + st * TILE);
+        if (!mbar_wait(p_ready, i & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) mma_f16_ss(tDV, desc_mn(aP, kk), desc_mn(aDO, kk), idG, (i | kk) != 0);
+        mma_commit(dv_done);
+        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
+        if (!mbar_wait(ds_ready, i & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk) mma_f16_ss(tDK, desc_mn(aP, kk), desc_mn(aQ, kk), idG, (i | kk) != 0);
+        mma_commit(dk_done);
+        mma_commit(&qdo_empty[st]);
+      }
+    }
+  } else {
+    constexpr int DH = D / 2;
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_off = uint32_t(qd * 32) << 16;
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      const int h = g * G + i / nqi;
+      const int qb = kb + i % nqi;
+      const int qi = qb * BQ + r;
+      const bool need_mask = (qb == kb) || (window > 0 && k0 < qb * BQ + BQ - window);
+      const bool row_ok = qi < T;
+      const float lse_r = row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f;
+      const float dl_r = row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f;
+      if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (i > 0) { if (!mbar_wait(dk_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
+      uint32_t dsr[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t vs[32], vd[32];
+        tmem_ld_32x32b_x32(tS + lane_off + half * 64 + c * 32, vs);
+        tmem_ld_32x32b_x32(tDP + lane_off + half * 64 + c * 32, vd);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p2[2], d2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float y = __fmaf_rn(__uint_as_float(vs[e + u]), c_log2, -lse_r);
+            const int kj = k0 + half * 64 + c * 32 + e + u;
+            bool dead = !row_ok;
+            if (need_mask) dead = dead || kj > qi || (window > 0 && kj <= qi - window);
+            const float p = dead ? 0.0f : det_exp2_attn(y);
+            p2[u] = p;
+            d2[u] = __fmul_rn(__fmul_rn(p, __fadd_rn(__uint_as_float(vd[e + u]), -dl_r)), scale);
+          }
+          pk[e >> 1] = pack_bf16(p2[0], p2[1]);
+          dsr[c * 16 + (e >> 1)] = pack_bf16(d2[0], d2[1]);
+        }
+        uint8_t* base = sPdS + half * 16384;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
+              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(p_ready); mbar_arrive(sdp_empty); }
+      if (!mbar_wait(dv_done, i & 1, abort_flag)) { ok = false; break; }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint8_t* base = sPdS + half * 16384;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
+              make_uint4(dsr[c * 16 + 4 * w], dsr[c * 16 + 4 * w + 1], dsr[c * 16 + 4 * w + 2], dsr[c * 16 + 4 * w + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok && mbar_wait(dk_done, (n - 1) & 1, abort_flag)) {
+      tc_fence_after();
+      const int kj = k0 + r;  // TMEM lane == key row
+      const bool in_range = kj < T;
+      __nv_bfloat16* dkrow = dK + ((long)b * T + kj) * lddk + (long)g * D + half * DH;
+      __nv_bfloat16* dvrow = dV + ((long)b * T + kj) * lddv + (long)g * D + half * DH;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32((which ? tDK : tDV) + lane_off + half * DH + c * 32, v);
+          tmem_ld_wait();
+          if (in_range) {
+            uint4* dst = reinterpret_cast<uint4*>((which ? dkrow : dvrow) + c * 32);
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 6]), __uint_as_float(v[8 * w + 7])));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 3u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ------------------------------------------------------------------ backward: dQ
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ CUtensorMap tmDO, const float* __restrict__ lse,
+                  const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ, long lddq, int T, int H, int Hkv,
+                  int window, float scale, float c_log2, uint32_t* __restrict__ status) {
+  constexpr int TILE = BQ * D * 2;
+  constexpr int ST = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE;
+  uint8_t* sDS = sDO + TILE;
+  uint8_t* sK = sDS + BQ * BKV * 2;  // [ST]
+  uint8_t* sV = sK + ST * TILE;      // [ST]
+  Bars* bars = reinterpret_cast<Bars*>(sV + ST * TILE);
+  uint64_t* qdo_full = &bars->b[0];
+  uint64_t* kv_full = &bars->b[1];   // [ST]
+  uint64_t* kv_empty = &bars->b[3];  // [ST]
+  uint64_t* sdp_full = &bars->b[5];
+  uint64_t* sdp_empty = &bars->b[6];
+  uint64_t* ds_ready = &bars->b[7];
+  uint64_t* dq_done = &bars->b[8];
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (T + BQ - 1) / BQ;
+  const int qt = nq - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (H / Hkv);
+  const int q0 = qt * BQ;
+  const int jmax = qt;
+  const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / BKV : 0;
+  const int n = jmax - jmin + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(ds_ready, 8); mbar_init(dq_done, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(qdo_full, 2 * TILE);
+      load_tile<D>(sQ, &tmQK, qdo_full, h * D, q0, b);
+      load_tile<D>(sDO, &tmDO, qdo_full, h * D, q0, b);
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const int k0 = (jmin + i) * BKV;
+        if (!mbar_wait(&kv_empty[st], ((i / ST) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&kv_full[st], 2 * TILE);
+        load_tile<D>(sK + st * TILE, &tmQK, &kv_full[st], (H + g) * D, k0, b);
+        load_tile<D>(sV + st * TILE, &tmV, &kv_full[st], (H + Hkv + g) * D, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);
+      constexpr uint32_t idQ = make_idesc(128, D, 0, 1);  // dQ = dS K : A K-major, B MN-major
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag);
+      auto issue_sdp = [&](int i) {
+        const int st = i % ST;
+        if (!mbar_wait(&kv_full[st], (i / ST) & 1, abort_flag)) return false;
+        if (!mbar_wait(sdp_empty, (i & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * TILE), aV = smem_u32(sV + st * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tS, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tDP, desc_k(aDO, kk), desc_k(aV, kk), idS, kk != 0);
+        mma_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i % ST;
+        if (!mbar_wait(ds_ready, i & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * TILE);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tDQ, desc_k(aDS, kk), desc_mn(aK, kk), idQ, (i | kk) != 0);
+        mma_commit(dq_done);
+        mma_commit(&kv_empty[st]);
+        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
+      }
+    }
+  } else {
+    constexpr int DH = D / 2;
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = qd * 32 + lane;
+    const int qi = q0 + r;
+    const uint32_t lane_off = uint32_t(qd * 32) << 16;
+    const bool row_ok = qi < T;
+    const float lse_r = row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f;
+    const float dl_r = row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f;
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      const int j = jmin + i;
+      const int kbase = j * BKV + half * 64;
+      const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window);
+      if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (i > 0) { if (!mbar_wait(dq_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t vs[32], vd[32];
+        tmem_ld_32x32b_x32(tS + lane_off + half * 64 + c * 32, vs);
+        tmem_ld_32x32b_x32(tDP + lane_off + half * 64 + c * 32, vd);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float d2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const float y = __fmaf_rn(__uint_as_float(vs[e + u]), c_log2, -lse_r);
+            const int kj = kbase + c * 32 + e + u;
+            bool dead = !row_ok;
+            if (need_mask) dead = dead || kj > qi || (window > 0 && kj <= qi - window);
+            const float p = dead ? 0.0f : det_exp2_attn(y);
+            d2[u] = __fmul_rn(__fmul_rn(p, __fadd_rn(__uint_as_float(vd[e + u]), -dl_r)), scale);
+          }
+          pk[e >> 1] = pack_bf16(d2[0], d2[1]);
+        }
+        uint8_t* base = sDS + half * 16384;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
+              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(ds_ready); mbar_arrive(sdp_empty); }
+    }
+    if (ok && mbar_wait(dq_done, (n - 1) & 1, abort_flag)) {
+      tc_fence_after();
+      __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D + half * DH;
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tDQ + lane_off + half * DH + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(dqrow + c * 32);
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
+                                pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
+                                pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
+                                pack_bf16(__uint_as_float(v[8 * w + 6]), __uint_as_float(v[8 * w + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 4u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,t] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (row, head), lane_tree with VW = 4
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, long lddo, const __nv_bfloat16* __restrict__ O,
+                                  long ldo, float* __restrict__ delta, int B, int T, int H, int D) {
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long rows = (long)B * T;
+  if (wid >= rows * H) return;
+  const long row = wid / H;
+  const int h = (int)(wid - row * H);
+  float acc = 0.0f;
+  if (lane * 4 < D) {
+    const __nv_bfloat16* a = dO + row * lddo + (long)h * D + lane * 4;
+    const __nv_bfloat16* o = O + row * ldo + (long)h * D + lane * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc = __fmaf_rn(__bfloat162float(a[e]), __bfloat162float(o[e]), acc);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+  if (lane == 0) {
+    const long bb = row / T, t = row - bb * T;
+    delta[(bb * H + h) * T + t] = acc;
+  }
+}
+
+CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T, uint64_t B, uint64_t ld_elems) {
+  static PFN_encodeTiled fn = get_encode_tiled();
+  if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+  cuuint64_t dims[3] = {cols, T, B};
+  cuuint64_t strides[2] = {ld_elems * 2, T * ld_elems * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+template <int D> constexpr int attn_smem_bytes() { return (1 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 512 + 2048; }
+template <int D> constexpr int attn_bwd_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 256; }
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+}  // namespace
+
+// qk: [B*T, ldqk] bf16 holding H query heads then Hkv key heads (width D each); qkv: [B*T, ldqkv] bf16 whose
+// value heads start at column (H + Hkv) * D; O: [B*T, ldo]; lse: [B, H, T] fp32. D in {64, 128}.
+extern "C" int otb_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B,
+                            int T, int H, int Hkv, int D, int window, float scale, uint32_t* status, void* stream) {
+  if ((D != 64 && D != 128) || H % Hkv || (ldqk & 7) || (ldqkv & 7) || (ldo & 7)) return -2;
+  CUtensorMap tq, tv;
+  CUresult r = encode_3d(&tq, qk, (uint64_t)ldqk, (uint64_t)T, (uint64_t)B, (uint64_t)ldqk);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_3d(&tv, qkv, (uint64_t)ldqkv, (uint64_t)T, (uint64_t)B, (uint64_t)ldqkv);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  dim3 grid((T + BQ - 1) / BQ, H, B);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) {
+    static int once = set_smem(attn_fwd_kernel<128>, attn_smem_bytes<128>());
+    if (once) return once;
+    attn_fwd_kernel<128><<<grid, ATT_THREADS, attn_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
+                                                                           window, scale, c_log2, status);
+  } else {
+    static int once = set_smem(attn_fwd_kernel<64>, attn_smem_bytes<64>());
+    if (once) return once;
+    attn_fwd_kernel<64><<<grid, ATT_THREADS, attn_smem_bytes<64>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
+                                                                         window, scale, c_log2, status);
+  }
+  return (int)cudaGetLastError();
+}
+
+// dO, O: [B*T, ld] bf16 (head h at column h*D). Outputs: dqk [B*T, lddqk] (dQ heads then dK heads),
+// dV written at column (H + Hkv) * D of dqkv [B*T, lddqkv]; delta: [B, H, T] fp32 scratch.
+extern "C" int otb_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldqkv, const void* O, long ldo,
+                            const void* dO, long lddo, const float* lse, float* delta, void* dqk, long lddqk, void* dqkv,
+                            long lddqkv, int B, int T, int H, int Hkv, int D, int window, float scale, uint32_t* status,
+                            void* stream) {
+  if ((D != 64 && D != 128) || H % Hkv || (ldqk & 7) || (ldqkv & 7) || (ldo & 7) || (lddo & 7) || (lddqk & 7) ||
+      (lddqkv & 7))
+    return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  CUtensorMap tq, tv, tdo;
+  CUresult r = encode_3d(&tq, qk, (uint64_t)ldqk, (uint64_t)T, (uint64_t)B, (uint64_t)ldqk);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_3d(&tv, qkv, (uint64_t)ldqkv, (uint64_t)T, (uint64_t)B, (uint64_t)ldqkv);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_3d(&tdo, dO, (uint64_t)lddo, (uint64_t)T, (uint64_t)B, (uint64_t)lddo);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  const long warps = (long)B * T * H;
+  attn_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dO, lddo, (const __nv_bfloat16*)O,
+                                                               ldo, delta, B, T, H, D);
+  __nv_bfloat16* dQp = (__nv_bfloat16*)dqk;
+  __nv_bfloat16* dKp = dQp + (long)H * D;
+  __nv_bfloat16* dVp = (__nv_bfloat16*)dqkv + (long)(H + Hkv) * D;
+  dim3 gkv((T + BKV - 1) / BKV, Hkv, B), gq((T + BQ - 1) / BQ, H, B);
+  if (D == 128) {
+    static int once = set_smem(attn_bwd_kv_kernel<128>, attn_bwd_smem_bytes<128>()) |
+                      set_smem(attn_bwd_q_kernel<128>, attn_bwd_smem_bytes<128>());
+    if (once) return once;
+    attn_bwd_kv_kernel<128><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
+                                                                                 lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    attn_bwd_q_kernel<128><<<gq, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dQp, lddqk, T, H,
+                                                                               Hkv, window, scale, c_log2, status);
+  } else {
+    static int once = set_smem(attn_bwd_kv_kernel<64>, attn_bwd_smem_bytes<64>()) |
+                      set_smem(attn_bwd_q_kernel<64>, attn_bwd_smem_bytes<64>());
+    if (once) return once;
+    attn_bwd_kv_kernel<64><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
+                                                                               lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    attn_bwd_q_kernel<64><<<gq, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dQp, lddqk, T, H, Hkv,
+                                                                             window, scale, c_log2, status);
+  }
+  return (int)cudaGetLastError();
+}
