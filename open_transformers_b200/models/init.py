@@ -1,0 +1,32 @@
+"""Weight initialisation from ONE counter-based Philox stream.
+
+Walking ``named_parameters()`` in module order, every parameter with >= 2 dims takes the next
+``numel`` words of the stream keyed by ``seed`` and becomes ``std * z`` with z a standard normal
+truncated to [-2, 2]; 1-D parameters are zero, norm gains one. The stream is sampled on the CPU
+and the bytes are copied to the device, so the result is identical on every backend and for any
+work split (reference src/pretrain/model/init.py:47-125).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ..ops.functional import trunc_normal_
+
+
+def init_weights(model: nn.Module, seed: int, std: float | None = None) -> None:
+    cfg = getattr(model, "cfg", None)
+    if std is None:
+        std = cfg.init.std if cfg is not None else 0.02
+    offset = 0
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() >= 2:
+                buf = torch.empty(p.shape, dtype=torch.float32)
+                trunc_normal_(buf, std, seed, offset)
+                offset += p.numel()
+                p.copy_(buf.to(p.dtype))
+            elif name.endswith("norm.weight") or ".norm" in name or "norm_" in name or name.endswith("_norm.weight"):
+                p.fill_(1.0)
+            else:
+                p.zero_()

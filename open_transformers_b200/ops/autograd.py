@@ -1,0 +1,215 @@
+"""torch.autograd bindings of the native kernels.
+
+Weight gradients do not travel through ``.grad``: a parameter may carry a *gradient slot*
+(``GradSlot``), an fp32 view into the flat gradient buffer of the virtual rank currently being
+processed, and the weight-gradient GEMM accumulates straight into it (fp32, beta = 1 epilogue).
+Without a slot the functions return ordinary gradients, so the same modules serve evaluation,
+tests and the audit replay.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import functional as K
+
+
+class GradSlot:
+    """fp32 accumulation target of one parameter (a view into a flat gradient buffer)."""
+
+    __slots__ = ("buf",)
+
+    def __init__(self, buf: torch.Tensor | None = None):
+        self.buf = buf
+
+
+def _flat2d(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1])
+
+
+class LinearFn(Function):
+    """y = x W^T (+ residual). ``master`` is the fp32 parameter autograd knows about, ``w`` the
+    compute-dtype weight actually multiplied (the same tensor in fp32 runs)."""
+
+    @staticmethod
+    def forward(ctx, x, master, w, slot, residual):
+        x2 = _flat2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if residual is not None:
+            y = K.gemm(x2, w, epi=K.EPI_RESIDUAL, residual=_flat2d(residual))
+        else:
+            y = K.gemm(x2, w)
+        ctx.save_for_backward(x2, w)
+        ctx.slot = slot
+        ctx.has_res = residual is not None
+        ctx.in_shape = x.shape
+        ctx.master_dtype = master.dtype
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _flat2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm(dy2, w, b_mn=True).view(ctx.in_shape)
+        gm = None
+        if ctx.slot is not None and ctx.slot.buf is not None:
+            K.gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.slot.buf, epi=K.EPI_ACC_F32)
+        elif ctx.needs_input_grad[1]:
+            gm = K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_STORE_F32).to(ctx.master_dtype)
+        return dx, gm, None, None, (dy if ctx.has_res else None)
+
+
+def linear(x, master, w=None, slot=None, residual=None):
+    return LinearFn.apply(x, master, master if w is None else w, slot, residual)
+
+
+class RMSNormFn(Function):
+    @staticmethod
+    def forward(ctx, x, master, w, slot, eps):
+        x2 = _flat2d(x).contiguous()
+        y, rstd = K.rmsnorm_fwd(x2, w, eps)
+        ctx.save_for_backward(x2, rstd, w if w is not None else x2.new_empty(0))
+        ctx.has_w = w is not None
+        ctx.slot = slot
+        ctx.shape = x.shape
+        ctx.master_dtype = master.dtype if master is not None else None
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, rstd, w = ctx.saved_tensors
+        w = w if ctx.has_w else None
+        dy2 = _flat2d(dy).contiguous()
+        need_dg = ctx.has_w and ((ctx.slot is not None and ctx.slot.buf is not None) or ctx.needs_input_grad[1])
+        dx, dg = K.rmsnorm_bwd(dy2, x2, w, rstd, need_dg)
+        gm = None
+        if need_dg:
+            if ctx.slot is not None and ctx.slot.buf is not None:
+                ctx.slot.buf.add_(dg)
+            else:
+                gm = dg.to(ctx.master_dtype)
+        return dx.view(ctx.shape), gm, None, None, None
+
+
+def rms_norm(x, master, w=None, slot=None, eps=1e-5):
+    if master is None:
+        return RMSNormFn.apply(x, None, None, None, eps)
+    return RMSNormFn.apply(x, master, master if w is None else w, slot, eps)
+
+
+class SwiGLUFn(Function):
+    @staticmethod
+    def forward(ctx, gu):
+        g2 = _flat2d(gu).contiguous()
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return K.swiglu_fwd(g2).view(*gu.shape[:-1], gu.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (g2,) = ctx.saved_tensors
+        return K.swiglu_bwd(g2, _flat2d(dh).contiguous()).view(ctx.shape)
+
+
+def swiglu(gate_up):
+    return SwiGLUFn.apply(gate_up)
+
+
+class AttentionFn(Function):
+    """(gain-free QK-norm) -> RoPE -> causal / sliding-window flash attention on a packed qkv
+    activation [B, T, (H + 2 Hkv) D]; returns [B, T, H D]."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, H, Hkv, D, window, qk_norm, eps):
+        B, T, _ = qkv.shape
+        q2 = qkv.reshape(B * T, -1)
+        qk, rstd = K.qknorm_rope_fwd(q2, cos, sin, H + Hkv, D, T, qk_norm, eps)
+        O, lse = K.attn_fwd(qk, q2, B, T, H, Hkv, D, window)
+        ctx.save_for_backward(q2, qk, rstd, O, lse, cos, sin)
+        ctx.cfg = (B, T, H, Hkv, D, window, qk_norm)
+        return O.view(B, T, H * D)
+
+    @staticmethod
+    def backward(ctx, dO):
+        q2, qk, rstd, O, lse, cos, sin = ctx.saved_tensors
+        B, T, H, Hkv, D, window, qk_norm = ctx.cfg
+        dO2 = dO.reshape(B * T, H * D)
+        if not dO2.is_contiguous():
+            dO2 = dO2.contiguous()
+        dqk = torch.empty_like(qk)
+        dqkv = torch.empty_like(q2)
+        K.attn_bwd(qk, q2, O, dO2, lse, dqk, dqkv, B, T, H, Hkv, D, window)
+        K.qknorm_rope_bwd(dqk, q2, rstd, dqkv, cos, sin, H + Hkv, D, T, qk_norm)
+        return dqkv.view(B, T, -1), None, None, None, None, None, None, None, None
+
+
+def attention(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps):
+    return AttentionFn.apply(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps)
+
+
+class EmbeddingFn(Function):
+    @staticmethod
+    def forward(ctx, ids, master, table, slot):
+        ctx.save_for_backward(ids)
+        ctx.slot = slot
+        ctx.tshape = table.shape
+        ctx.master_dtype = master.dtype
+        return K.embedding_fwd(ids, table).view(*ids.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        dy2 = _flat2d(dy).contiguous()
+        if ctx.slot is not None and ctx.slot.buf is not None:
+            K.embedding_bwd(dy2, ids, ctx.slot.buf, True)
+            return None, None, None, None
+        dW = torch.zeros(ctx.tshape, dtype=torch.float32, device=dy.device)
+        K.embedding_bwd(dy2, ids, dW, False)
+        return None, dW.to(ctx.master_dtype), None, None
+
+
+def embedding(ids, master, table=None, slot=None):
+    return EmbeddingFn.apply(ids, master, master if table is None else table, slot)
+
+
+class FusedCEZLossFn(Function):
+    """Mean cross-entropy and z-loss (coeff * mean lse^2) over rows with label >= 0.
+
+    The gradient w.r.t. the logits is produced in the forward pass, in place of the logits, already
+    multiplied by ``grad_scale`` (1/accum): the incoming gradients of both outputs must equal that
+    scale, which is what ``(ce + z) * (1/accum)`` gives. One log-sum-exp per row, fixed-order row
+    reduction, mean by multiplication with the host reciprocal 1/N
+    (reference src/pretrain/model/fused_loss.py:40-104)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, z_coeff, grad_scale):
+        l2 = _flat2d(logits)
+        assert l2.is_contiguous()
+        lab = labels.reshape(-1).contiguous()
+        n_valid = lab.numel()  # callers with ignored rows pass n via grad_scale themselves
+        inv_n = 1.0 / n_valid
+        need_grad = logits.requires_grad
+        ce_rows, lse_rows = K.ce_zloss_(l2, lab, z_coeff, inv_n * grad_scale, write_grad=need_grad)
+        ce = K.det_sum(ce_rows, False, inv_n)
+        z = K.det_sum(lse_rows, True, inv_n) * z_coeff
+        # The logits buffer now holds the gradient. It is an activation nobody else saved (the
+        # vocabulary projection keeps its input and weight, not its output), so overwriting it is safe.
+        ctx.grad_buf = l2 if need_grad else None
+        ctx.shape = logits.shape
+        return ce.reshape(()), z.reshape(())
+
+    @staticmethod
+    def backward(ctx, dce, dz):
+        g = ctx.grad_buf
+        ctx.grad_buf = None
+        return (g.view(ctx.shape) if g is not None else None), None, None, None
+
+
+def fused_ce_z_loss(logits, labels, z_coeff: float, grad_scale: float = 1.0):
+    ce, z = FusedCEZLossFn.apply(logits, labels, float(z_coeff), float(grad_scale))
+    return ce, z
