@@ -1,0 +1,56 @@
+"""Metrics: model FLOPs, MFU, JSONL logger, timers."""
+from __future__ import annotations
+
+import contextlib
+import json
+import time
+from pathlib import Path
+
+B200_BF16_DENSE_PEAK = 2.25e15  # nominal dense bf16 FLOP/s of one B200
+
+
+def transformer_flops_per_token(n_layers: int, d_model: int, seq_len: int, vocab_size: int) -> float:
+    """Forward + backward FLOPs per token: 72 L d^2 (dense blocks) + 12 L s d (attention) + 6 V d (head)
+    (reference src/pretrain/obs/metrics.py:23-47)."""
+    return 72.0 * n_layers * d_model ** 2 + 12.0 * n_layers * seq_len * d_model + 6.0 * vocab_size * d_model
+
+
+def mfu(tokens_per_sec_per_gpu: float, flops_per_token: float, peak_flops: float = B200_BF16_DENSE_PEAK) -> float:
+    return tokens_per_sec_per_gpu * flops_per_token / peak_flops
+
+
+class MetricsLogger:
+    """Rank-0 JSONL writer (flushed every ``flush_every`` rows and on close) with an optional W&B mirror."""
+
+    def __init__(self, path: str | Path | None, wandb_run=None, flush_every: int = 100, enabled: bool = True):
+        self.enabled = enabled and path is not None
+        self.wandb = wandb_run
+        self._n, self._every = 0, flush_every
+        self._f = None
+        if self.enabled:
+            Path(path).parent.mkdir(parents=True, exist_ok=True)
+            self._f = open(path, "a", encoding="utf-8")
+
+    def log(self, row: dict, step: int | None = None) -> None:
+        if self._f is not None:
+            self._f.write(json.dumps(row, sort_keys=True, default=str) + "\n")
+            self._n += 1
+            if self._n % self._every == 0:
+                self._f.flush()
+        if self.wandb is not None:
+            self.wandb.log(row, step=step)
+
+    def close(self) -> None:
+        if self._f is not None:
+            self._f.flush()
+            self._f.close()
+            self._f = None
+
+
+@contextlib.contextmanager
+def time_section(sink: dict, key: str):
+    t0 = time.perf_counter()
+    try:
+        yield
+    finally:
+        sink[key] = sink.get(key, 0.0) + (time.perf_counter() - t0) * 1e3

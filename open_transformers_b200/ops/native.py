@@ -76,7 +76,12 @@ class NativeError(RuntimeError):
     pass
 
 
+launch_count = 0  # native entry points called so far (each launches one to three kernels)
+
+
 def check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise NativeError("%s failed with code %d" % (what, rc))
 

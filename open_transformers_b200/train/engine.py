@@ -1,0 +1,428 @@
+"""Training engine: flat buffers, virtual ranks, deterministic gradient reduction, clip, AdamW.
+
+Topology. A run is defined by its VIRTUAL data-parallel topology (V = dp_replicate x dp_shard
+ranks, replica-major). The hashed arithmetic depends on that topology only. G physical processes
+(GPUs, or CPU ranks) each host V / G consecutive virtual ranks and step through them in order,
+which is the audit replay's virtual-rank loop (reference src/pretrain/cli/audit_replay.py:2348-2488)
+used as the trainer itself; G in {1, 2, 4, 8} and the CPU replay therefore give identical bytes.
+
+Memory (per process, sized for 180 GB HBM3e): fp32 master weights and both moments, the fp32
+reduced gradient, one fp32 gradient buffer PER HOSTED VIRTUAL RANK, and the compute-dtype weights
+(bf16 mixed precision; the master itself in fp32 runs). No activation recompute is needed at the
+OPEN-1B micro-batch (24 GB of activations).
+
+One optimizer step
+  1. for each hosted virtual rank, for each of its micro-batches: forward + backward; weight
+     gradients accumulate in fp32 straight into that rank's flat buffer (GEMM beta=1 epilogue);
+  2. `grad_reduce`: every process reduces the segments it owns by reading all V buffers (its own
+     and, over NVLink peer loads, the other GPUs') in ascending shard order, x 1/S, binary-blocks
+     tree over replicas, x 1/R, and emits per-chunk squared-norm partials in the same pass;
+  3. the partials are combined per (parameter, shard) by the pair tree, folded ascending shard then
+     ascending parameter in fp32 on the host, sqrt, clip coefficient
+     h = min(max_norm / (norm + 1e-6), 1)   (reference src/pretrain/train/global_clip.py:47-55);
+  4. `adamw_push`: g *= h, decoupled-decay AdamW on the owned segments, and the new weights are
+     stored, in compute dtype, into the weight buffer of EVERY GPU (the parameter all-gather done
+     by peer stores from inside the update kernel).
+On CPU ranks (gloo) the gradient buffers are exchanged with all_gather and every rank applies the
+identical update to all segments.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..config.schema import RootConfig
+from ..models import build_model, fused_ce_z_loss, init_weights
+from ..ops.autograd import GradSlot
+from ..ops.native import F, I, L, P, check, cpu_lib, cuda_lib, stream_ptr
+from ..parallel.flat import FlatLayout, PeerBuffer
+from . import state_hash as SH
+
+
+@dataclass
+class StepOutput:
+    ce_per_vrank: dict          # virtual rank -> list of per-micro-batch CE (python floats)
+    z_per_vrank: dict
+    grad_norm: float
+    clip_coef: float
+    skipped: bool
+
+
+def build_param_groups(named_params, no_decay_names, lr, betas, eps, weight_decay):
+    """[decay, no_decay] groups: a parameter is not decayed if it has fewer than 2 dims or its name contains
+    one of ``no_decay_names`` (reference src/pretrain/optim/adamw.py:21-63). Returns (groups, membership)."""
+    member = []
+    for name, p in named_params:
+        member.append(1 if (p.dim() < 2 or any(s in name for s in no_decay_names)) else 0)
+    base = dict(lr=float(lr), betas=[float(betas[0]), float(betas[1])], eps=float(eps), amsgrad=False)
+    groups = [dict(base, name="decay", weight_decay=float(weight_decay)), dict(base, name="no_decay", weight_decay=0.0)]
+    return groups, member
+
+
+def _ptr_array(ptrs):
+    arr = (ctypes.c_void_p * len(ptrs))()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+class TrainEngine:
+    def __init__(self, cfg: RootConfig, device: torch.device | str = "cpu", rank: int = 0, world: int = 1, group=None,
+                 seed: int | None = None, init: bool = True):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.rank, self.world, self.group = rank, world, group
+        run = cfg.run
+        self.dp_replicate = max(1, run.dp_replicate_size)
+        if run.virtual_dp_size > 0:
+            self.V = run.virtual_dp_size
+            self.dp_shard = run.dp_shard_size if run.dp_shard_size > 0 else self.V // self.dp_replicate
+        else:
+            self.dp_shard = run.dp_shard_size if run.dp_shard_size > 0 else max(1, world // self.dp_replicate)
+            self.V = self.dp_shard * self.dp_replicate
+        if self.dp_shard * self.dp_replicate != self.V:
+            raise ValueError("virtual topology mismatch: V=%d != dp_replicate %d x dp_shard %d" % (self.V, self.dp_replicate, self.dp_shard))
+        if self.V % world:
+            raise ValueError("the %d virtual ranks cannot be split evenly over %d processes" % (self.V, world))
+        per = self.V // world
+        self.hosted = list(range(rank * per, (rank + 1) * per))
+        self.mixed = bool(run.mixed_precision)
+        self.compute_dtype = torch.bfloat16 if self.mixed else torch.float32
+        self.is_cuda = self.device.type == "cuda"
+        self.lib = cuda_lib() if self.is_cuda else cpu_lib()
+        self.nccl_mode = run.reduction_mode == "nccl"
+
+        # ---- model on the meta device first: the layout decides where the parameters live
+        model = build_model(cfg.model)
+        model.compute_dtype = self.compute_dtype
+        model.activation_checkpoint = bool(run.activation_checkpoint)
+        model.ac_every_other_block = bool(run.ac_every_other_block)
+        named = list(model.named_parameters())
+        self.param_groups, member = build_param_groups(named, cfg.optim.no_decay_param_names, cfg.optim.peak_lr, cfg.optim.betas,
+                                                       cfg.optim.eps, cfg.optim.weight_decay)
+        self.layout = FlatLayout.build([(n, tuple(p.shape)) for n, p in named], self.dp_shard, member)
+        lay = self.layout
+        n = lay.total
+        peer = self.is_cuda and world > 1 and not self.nccl_mode
+        pw, pg = (rank, world) if peer else (0, 1)
+
+        def alloc(nbytes, shared):
+            return PeerBuffer(nbytes, self.device, pw if shared else 0, pg if shared else 1, group if shared else None)
+
+        self.buf_master = alloc(4 * n, shared=not self.mixed)
+        self.master = self.buf_master.typed(torch.float32)
+        if self.mixed:
+            self.buf_compute = alloc(2 * n, shared=True)
+            self.compute = self.buf_compute.typed(torch.bfloat16)
+        else:
+            self.buf_compute, self.compute = self.buf_master, self.master
+        self.m1 = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.m2 = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.grad_red = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.buf_grads = [alloc(4 * n, shared=True) for _ in self.hosted]
+        self.grads = [b.typed(torch.float32) for b in self.buf_grads]
+        self.opt_step = 0
+
+        # ---- chunk tables on the device, ownership
+        dev = self.device
+        self.chunk_start = torch.from_numpy(lay.chunk_start).to(dev)
+        self.chunk_len = torch.from_numpy(lay.chunk_len).to(dev)
+        self.chunk_group = torch.from_numpy(lay.chunk_group).to(dev)
+        self.seg_first = torch.from_numpy(lay.seg_first).to(dev)
+        self.n_chunks = len(lay.chunk_start)
+        self.n_segs = len(lay.segments)
+        if peer:
+            ranges = lay.owner_ranges(world)
+        else:
+            ranges = [(0, self.n_segs)] * world
+        self.seg_lo, self.seg_hi = ranges[rank]
+        self.chunk_lo = int(lay.seg_first[self.seg_lo])
+        self.chunk_hi = int(lay.seg_first[self.seg_hi])
+        self.peer = peer
+        self.chunk_sos = torch.zeros(max(self.n_chunks, 1), dtype=torch.float32, device=dev)
+        self.seg_sos = torch.zeros(max(self.n_segs, 1), dtype=torch.float32, device=dev)
+
+        # ---- initialise (CPU-sampled Philox, byte-copied) and move the model onto the flat buffers
+        if init:
+            init_weights(model, cfg.run.seed if seed is None else seed)
+        with torch.no_grad():
+            for i, (name, p) in enumerate(named):
+                lay.view(self.master, i).copy_(p.detach().to(torch.float32))
+        self.model = model
+        self.names = lay.names
+        self.slots = [GradSlot() for _ in named]
+        self._install_views()
+        self.refresh_compute_weights()
+        # buffers (RoPE tables) follow the device
+        for mod in self.model.modules():
+            for bname, b in list(mod.named_buffers(recurse=False)):
+                mod._buffers[bname] = b.to(self.device)
+
+    # ------------------------------------------------------------------------------ plumbing
+    def _install_views(self) -> None:
+        lay = self.layout
+        byname = dict(self.model.named_parameters())
+        modules = dict(self.model.named_modules())
+        for i, name in enumerate(lay.names):
+            p = byname[name]
+            p.data = lay.view(self.master, i)
+            mod_name, _, attr = name.rpartition(".")
+            mod = modules[mod_name]
+            setattr(mod, "_compute_" + attr, lay.view(self.compute, i))
+            setattr(mod, "_slot_" + attr, self.slots[i])
+        # fused QKV: wq|wk|wv are adjacent in the flat buffers
+        idx = {n: i for i, n in enumerate(lay.names)}
+        self._fused = []
+        for mname, mod in modules.items():
+            if all(hasattr(mod, a) for a in ("wq", "wk", "wv")):
+                iq, ik, iv = (idx["%s.%s.weight" % (mname, a)] for a in ("wq", "wk", "wv"))
+                o0 = lay.offsets[iq]
+                contiguous = lay.offsets[ik] == o0 + lay.numels[iq] and lay.offsets[iv] == lay.offsets[ik] + lay.numels[ik]
+                if not contiguous:
+                    continue
+                rows = lay.shapes[iq][0] + lay.shapes[ik][0] + lay.shapes[iv][0]
+                cols = lay.shapes[iq][1]
+                slot = GradSlot()
+                master_v = self.master[o0:o0 + rows * cols].view(rows, cols)
+                compute_v = self.compute[o0:o0 + rows * cols].view(rows, cols)
+                mod._fused_qkv = (byname["%s.wq.weight" % mname], compute_v, slot)
+                self._fused.append((slot, o0, rows, cols))
+                del master_v
+
+    def _bind_slots(self, gbuf: torch.Tensor | None) -> None:
+        lay = self.layout
+        for i, slot in enumerate(self.slots):
+            slot.buf = None if gbuf is None else lay.view(gbuf, i)
+        for slot, o0, rows, cols in self._fused:
+            slot.buf = None if gbuf is None else gbuf[o0:o0 + rows * cols].view(rows, cols)
+
+    def named_master(self):
+        return [(n, self.layout.view(self.master, i)) for i, n in enumerate(self.names)]
+
+    def optimizer_state(self):
+        lay = self.layout
+        return {n: {"step": self.opt_step, "exp_avg": lay.view(self.m1, i), "exp_avg_sq": lay.view(self.m2, i)}
+                for i, n in enumerate(self.names)}
+
+    def named_grads(self):
+        return {n: self.layout.view(self.grad_red, i) for i, n in enumerate(self.names)}
+
+    def _barrier(self) -> None:
+        if self.world > 1:
+            if self.is_cuda:
+                torch.cuda.current_stream().synchronize()
+            dist.barrier(group=self.group)
+
+    def refresh_compute_weights(self) -> None:
+        """compute weights <- master (all segments, local only); used at start-up and after a load."""
+        if not self.mixed:
+            return
+        arr = _ptr_array([self.compute.data_ptr()])
+        if self.is_cuda:
+            check(self.lib.otb_push_cast(P(self.chunk_start), P(self.chunk_len), I(self.n_chunks), P(self.master), arr, I(1), I(1),
+                                         stream_ptr()), "push_cast")
+        else:
+            check(self.lib.otb_cpu_push_cast(P(self.chunk_start), P(self.chunk_len), I(self.n_chunks), P(self.master), arr, I(1), I(1)),
+                  "push_cast")
+
+    # ---------------------------------------------------------------------------- one step
+    def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int):
+        """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
+        self._bind_slots(self.grads[vslot])
+        self.model.train()
+        out = self.model(input_ids)
+        z_coeff = self.cfg.model.z_loss.coeff if self.cfg.model.z_loss.enabled else 0.0
+        ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
+        loss = (ce + z) * (1.0 / accum)
+        loss.backward()
+        return ce, z
+
+    def zero_grads(self) -> None:
+        for g in self.grads:
+            g.zero_()
+
+    def reduce_gradients(self) -> float:
+        """Steps 2-3: deterministic reduction into ``grad_red`` and the global gradient norm."""
+        lay = self.layout
+        S, R = self.dp_shard, self.dp_replicate
+        per = self.V // self.world
+        if self.nccl_mode and self.world > 1:
+            # throughput-only baseline: library all-reduce, order not pinned
+            acc = self.grads[0]
+            for g in self.grads[1:]:
+                acc.add_(g)
+            dist.all_reduce(acc, group=self.group)
+            self.grad_red.copy_(acc).mul_(1.0 / self.V)
+            check(self._chunk_sos_all(), "chunk_sos")
+        elif not self.is_cuda and self.world > 1:
+            # CPU ranks: exchange the flat buffers, then every rank reduces everything identically
+            gathered = []
+            for g in self.grads:
+                parts = [torch.empty_like(g) for _ in range(self.world)]
+                dist.all_gather(parts, g, group=self.group)
+                gathered.append(parts)
+            srcs = [gathered[v % per][v // per].data_ptr() for v in range(self.V)]
+            self._keep = gathered
+            check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks),
+                                               P(self.grad_red), P(self.chunk_sos)), "grad_reduce")
+            self._keep = None
+        else:
+            self._barrier()  # every rank's backward is complete before anyone pulls
+            srcs = []
+            for v in range(self.V):
+                r, slot = v // per, v % per
+                srcs.append(self.buf_grads[slot].ptrs[r] if self.peer else self.grads[slot].data_ptr())
+            lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
+            cs, cl = self.chunk_start[lo:], self.chunk_len[lo:]
+            sos = self.chunk_sos[lo:]
+            if self.is_cuda:
+                check(self.lib.otb_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos), stream_ptr()),
+                      "grad_reduce")
+            else:
+                check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos)), "grad_reduce")
+            if self.peer:
+                parts = [torch.empty_like(self.chunk_sos) for _ in range(self.world)]
+                dist.all_gather(parts, self.chunk_sos, group=self.group)
+                ranges = lay.owner_ranges(self.world)
+                for r, (slo, shi) in enumerate(ranges):
+                    c0, c1 = int(lay.seg_first[slo]), int(lay.seg_first[shi])
+                    if r != self.rank and c1 > c0:
+                        self.chunk_sos[c0:c1].copy_(parts[r][c0:c1])
+        if self.is_cuda:
+            check(self.lib.otb_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos), stream_ptr()), "seg_tree")
+        else:
+            check(self.lib.otb_cpu_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos)), "seg_tree")
+        seg = self.seg_sos[: self.n_segs].detach().to("cpu").numpy()
+        return self._fold_norm(seg)
+
+    def _chunk_sos_all(self) -> int:
+        if self.is_cuda:
+            return self.lib.otb_chunk_sos(P(self.grad_red), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks), P(self.chunk_sos), stream_ptr())
+        return self.lib.otb_cpu_chunk_sos(P(self.grad_red), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks), P(self.chunk_sos))
+
+    def _fold_norm(self, seg_sos: np.ndarray) -> float:
+        """per-tensor sum over shards ascending, then over tensors ascending, all in fp32; then sqrt.
+        (grad_norm_algo = deterministic_per_tensor_sos_v1)"""
+        per_tensor = np.zeros(len(self.names), dtype=np.float32)
+        seen = np.zeros(len(self.names), dtype=bool)
+        order = sorted(range(self.n_segs), key=lambda i: (self.layout.segments[i].param, self.layout.segments[i].shard))
+        for i in order:
+            pi = self.layout.segments[i].param
+            per_tensor[pi] = seg_sos[i] if not seen[pi] else np.float32(per_tensor[pi] + seg_sos[i])
+            seen[pi] = True
+        self.per_tensor_sos = per_tensor
+        total = np.float32(0.0)
+        for v in per_tensor:
+            total = np.float32(total + v)
+        return float(np.sqrt(total, dtype=np.float32))
+
+    @staticmethod
+    def clip_coefficient(grad_norm: float, max_norm: float) -> float:
+        if max_norm <= 0:
+            return 1.0
+        h = np.float32(max_norm) / np.float32(np.float32(grad_norm) + np.float32(1e-6))
+        return float(min(h, np.float32(1.0)))
+
+    def optimizer_step(self, lr: float, clip: float) -> None:
+        """Step 4 on the owned segments; pushes the new weights to every rank."""
+        self.opt_step += 1
+        for g in self.param_groups:
+            g["lr"] = float(lr)
+        o = self.cfg.optim
+        hyper = (ctypes.c_float * 10)()
+        cpu_lib().otb_cpu_adamw_hyper(ctypes.c_double(lr), ctypes.c_double(o.betas[0]), ctypes.c_double(o.betas[1]), ctypes.c_double(o.eps),
+                                      ctypes.c_double(o.weight_decay), ctypes.c_long(self.opt_step), F(clip), hyper)
+        lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
+        cs, cl, cg = self.chunk_start[lo:], self.chunk_len[lo:], self.chunk_group[lo:]
+        dst_buf = self.buf_compute
+        dsts = dst_buf.ptrs if self.peer else [self.compute.data_ptr()]
+        if self.is_cuda:
+            check(self.lib.otb_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                          _ptr_array(dsts), I(len(dsts)), I(self.mixed), stream_ptr()), "adamw_push")
+        else:
+            check(self.lib.otb_cpu_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                              _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
+        self._barrier()  # peers' stores into this rank's weights are complete before the next forward
+
+    def skip_step(self) -> None:
+        self._barrier()
+
+    # --------------------------------------------------------------------------------- hash
+    def sharded_state_hash(self, prev, batch_digest: bytes | None, include_grads: bool = True, tensor_digest: str | None = None) -> str:
+        """v3 hash of the current state. With peer-sharded ownership each process digests the segments it
+        owns (tree digests, on the device) and the 32-byte results are gathered."""
+        td = tensor_digest or self.cfg.train.state_hash.tensor_digest
+        lay = self.layout
+        if self.peer and td != "tree":
+            raise ValueError("sharded multi-GPU hashing needs train.state_hash.tensor_digest=tree")
+        fields = [("weight", self.master), ("exp_avg", self.m1), ("exp_avg_sq", self.m2)] + ([("grad", self.grad_red)] if include_grads else [])
+        seg_digests = {}
+        if td == "tree":
+            keys, views = [], []
+            for si in range(self.seg_lo, self.seg_hi) if self.peer else range(self.n_segs):
+                seg = lay.segments[si]
+                for tag, flat in fields:
+                    keys.append((seg.param, seg.shard, tag))
+                    views.append(flat[seg.start:seg.start + seg.length])
+            seg_digests = dict(zip(keys, SH.tree_digest_batch(views)))
+            if self.peer:
+                objs: list = [None] * self.world
+                dist.all_gather_object(objs, seg_digests, group=self.group)
+                seg_digests = {k: v for d in objs for k, v in d.items()}
+        order = sorted(range(len(self.names)), key=lambda i: self.names[i])
+        locals_ = []
+        for s in range(self.dp_shard):
+            h = SH._new()
+            for pi in order:
+                shape = lay.shapes[pi] if lay.shapes[pi] else (1,)
+                lo, hi = SH.shard_rows(shape[0], self.dp_shard, s)
+                sshape = (hi - lo,) + tuple(shape[1:])
+                h.update(self.names[pi].encode() + b"\0")
+
+                def feed(tag, key, flat):
+                    h.update(tag.encode() + b"\0" + b"torch.float32\0" + str(sshape).encode() + b"\0")
+                    if td == "tree":
+                        h.update(b"tree\0")
+                        h.update(seg_digests[(pi, s, key)] if hi > lo else SH.tree_digest_bytes(b""))
+                    else:
+                        row = lay.numels[pi] // max(shape[0], 1)
+                        st = lay.offsets[pi] + lo * row
+                        h.update(SH.tensor_bytes(flat[st:st + (hi - lo) * row]))
+
+                feed("weight", "weight", self.master)
+                h.update(b"optim_step\0" + int(self.opt_step).to_bytes(8, "little", signed=True))
+                feed("optim_exp_avg", "exp_avg", self.m1)
+                feed("optim_exp_avg_sq", "exp_avg_sq", self.m2)
+                if include_grads:
+                    feed("grad", "grad", self.grad_red)
+            locals_.append(h.digest())
+        shard_state = SH.combine_shard_state(locals_, self.V)
+        return SH.finalize_state_hash(shard_state, self.param_groups, prev, batch_digest)
+
+    def full_state_hash(self, prev=None, batch_digest=None, include_grads: bool = False) -> str:
+        """v2 hash over full tensors (init hash). Only valid where this process holds every segment."""
+        grads = self.named_grads() if include_grads else None
+        return SH.compute_state_hash(self.named_master(), self.optimizer_state(), self.param_groups, prev=prev,
+                                     include_grads=include_grads, grads=grads, batch_digest=batch_digest)
+
+    def gather_full_state(self) -> None:
+        """Make master / moments / reduced gradient complete on every rank (checkpoint, init hash)."""
+        if not self.peer:
+            return
+        lay = self.layout
+        ranges = lay.owner_ranges(self.world)
+        for flat in (self.master, self.m1, self.m2, self.grad_red):
+            for r, (slo, shi) in enumerate(ranges):
+                for si in range(slo, shi):
+                    seg = lay.segments[si]
+                    dist.broadcast(flat[seg.start:seg.start + seg.length], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                                   group=self.group)
+
+    def close(self) -> None:
+        for b in [self.buf_master, self.buf_compute] + self.buf_grads:
+            b.close()

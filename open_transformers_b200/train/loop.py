@@ -1,0 +1,249 @@
+"""``train(cfg, resume_from)``: the pre-training driver.
+
+Per optimizer step (cf. reference src/pretrain/train/loop.py:789-1242): take the step's plan from the canonical
+stream; every process runs the micro-batches of the virtual ranks it hosts (batch hashed on the CPU, copied
+to the device, forward + backward); deterministic gradient reduction + global norm; spike decision on the
+globally folded loss and the pre-clip norm; clip + AdamW (or skip); token / step counters; SIGTERM poll; state
+hash when due (cadence, checkpoint, exit or final step - only cadence hashes advance the chain); checkpoint
+when due; metrics. Gradients are zeroed only at the start of the next step, so the hash sees the post-clip
+gradients of the step it describes.
+
+Run directory ``<output_dir>/<run_id>/``: ``checkpoints/``, ``checkpoints/state_hash_init.txt``,
+``logs/metrics.jsonl``, ``logs/state_hashes.jsonl``, ``logs/grad_norms.jsonl``.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import signal
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..config.schema import RootConfig
+from ..data.global_stream import GlobalStreamState
+from ..data.loader import build_global_loader, collate
+from ..obs.metrics import MetricsLogger, mfu, transformer_flops_per_token
+from ..obs.wandb_run import WandBRun
+from ..optim.schedules import build_schedule, rewarm_factor
+from ..parallel.env import init_distributed, set_seed, shutdown_distributed
+from ..utils.git import git_sha
+from . import state_hash as SH
+from .checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
+from .engine import TrainEngine
+from .midtrain import check_linear_anneal_resume
+from .qk_gain_control import clamp_qk_gains, zero_q_gain_grads
+from .spike_protocol import Halt, SpikeProtocol
+
+log = logging.getLogger("pretrain.train")
+_sigterm = {"flag": False}
+
+
+def _on_sigterm(signum, frame):
+    _sigterm["flag"] = True
+
+
+def _emergency_exit_requested(world: int, device: torch.device) -> bool:
+    """Every rank learns whether ANY rank received SIGTERM, so that all of them checkpoint at the same step."""
+    if world == 1:
+        return _sigterm["flag"]
+    t = torch.tensor([1 if _sigterm["flag"] else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return bool(t.item())
+
+
+def deterministic_scalar_sum(values: list[float], world: int) -> tuple[float, int]:
+    """Sum of python floats contributed by all ranks, folded in fp64 in rank order (telemetry and spike input)."""
+    if world > 1:
+        objs: list = [None] * world
+        dist.all_gather_object(objs, [float(v) for v in values])
+        values = [v for part in objs for v in part]
+    total = 0.0
+    for v in values:
+        total += float(v)
+    return total, len(values)
+
+
+def _assert_same_on_all_ranks(payload: str, what: str, world: int) -> None:
+    if world == 1:
+        return
+    objs: list = [None] * world
+    dist.all_gather_object(objs, payload)
+    if len(set(objs)) != 1:
+        raise RuntimeError("%s differs between ranks: %s" % (what, sorted(set(objs))))
+
+
+def _append_jsonl(path: Path, row: dict) -> None:
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "a", encoding="utf-8") as f:
+        f.write(json.dumps(row, sort_keys=True) + "\n")
+
+
+def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None = None, data_root: str | None = None,
+          max_steps: int | None = None) -> dict:
+    rank, world, dev = init_distributed(device)
+    signal.signal(signal.SIGTERM, _on_sigterm)
+    _sigterm["flag"] = False
+    set_seed(cfg.run.seed, rank)
+    run_id = cfg.run.run_id or os.environ.get("RUN_ID", "run")
+    _assert_same_on_all_ranks(run_id, "run_id", world)
+    run_dir = Path(cfg.run.output_dir) / run_id
+    ckpt = Checkpointer(run_dir, rank, world)
+    if resume_from is None and ckpt.complete_steps():
+        raise RuntimeError("%s already holds checkpoints; pass --resume-from or choose a new run_id (cold-start overwrite guard)" % run_dir)
+
+    engine = TrainEngine(cfg, dev, rank, world)
+    V, hosted = engine.V, engine.hosted
+    train_cfg = cfg.train
+    sched = build_schedule(cfg.schedule, train_cfg, cfg.optim)
+    spike = SpikeProtocol.from_config(train_cfg.spike)
+    hashers = {v: SH.RunningBatchHasher() for v in hosted}
+    consumed, step, chained, restart_count, rewarm_anchor = 0, 0, None, 0, None
+    stream_state = None
+
+    if resume_from is not None:
+        meta0 = Checkpointer.read_meta(resume_from)
+        check_linear_anneal_resume(cfg, meta0.consumed_tokens)
+        if (meta0.dp_world_size, meta0.dp_shard, meta0.dp_replicate) != (V, engine.dp_shard, engine.dp_replicate):
+            raise RuntimeError("checkpoint was written for virtual topology %s, this run uses %s (a different topology starts a new segment)"
+                               % ((meta0.dp_world_size, meta0.dp_shard, meta0.dp_replicate), (V, engine.dp_shard, engine.dp_replicate)))
+        side = ckpt.load(resume_from, engine, load_optimizer=not train_cfg.resume_reset_optimizer)
+        consumed, step, chained = meta0.consumed_tokens, meta0.step, meta0.chained_hash
+        restart_count = meta0.restart_count + 1
+        stream_state = GlobalStreamState.from_json(side["global_stream"]) if side["global_stream"] else None
+        spike.load_state_dict(side["spike_protocol"])
+        hashers = {v: SH.RunningBatchHasher(side["batch_chains"][v]) for v in hosted}
+        rewarm_anchor = consumed if cfg.schedule.rewarm_on_resume else meta0.rewarm_anchor_tokens
+    else:
+        check_linear_anneal_resume(cfg, None)
+
+    loader = build_global_loader(cfg, hosted, V, state=stream_state, consumed_tokens=consumed, start_step=step, data_root=data_root)
+    metrics = MetricsLogger(run_dir / cfg.logging.metrics_jsonl_path, WandBRun(cfg.logging.wandb_project, run_id, enabled=rank == 0),
+                            enabled=rank == 0)
+    hash_log = run_dir / "logs" / "state_hashes.jsonl"
+    gn_log = run_dir / train_cfg.grad_norm_log.path
+    sh_cfg = train_cfg.state_hash
+    flops_tok = transformer_flops_per_token(cfg.model.n_layers, cfg.model.d_model, train_cfg.seq_len, cfg.model.vocab_size)
+
+    if resume_from is None and sh_cfg.at_init and sh_cfg.every_n_steps > 0:
+        engine.gather_full_state()
+        init_hash = engine.full_state_hash()
+        if rank == 0:
+            (run_dir / "checkpoints").mkdir(parents=True, exist_ok=True)
+            (run_dir / "checkpoints" / "state_hash_init.txt").write_text(init_hash + "\n")
+            _append_jsonl(hash_log, {"step": 0, "kind": "init", "consumed_tokens": 0, "state_hash": init_hash})
+
+    def make_meta() -> CheckpointMeta:
+        return CheckpointMeta(consumed_tokens=consumed, step=step, git_sha=git_sha(), config_resolved=resolved_config_json(cfg),
+                              restart_count=restart_count, chained_hash=chained, reduction_mode=cfg.run.reduction_mode, dp_world_size=V,
+                              dp_replicate=engine.dp_replicate, dp_shard=engine.dp_shard, tensor_digest=sh_cfg.tensor_digest,
+                              rewarm_anchor_tokens=rewarm_anchor, seed=cfg.run.seed, torch_version=torch.__version__,
+                              numpy_version=np.__version__, kernel_env={k: v for k, v in os.environ.items() if k.startswith("OTB_")},
+                              windows_emitted=loader.state().windows_emitted, physical_world_size=world,
+                              mixed_precision=cfg.run.mixed_precision)
+
+    def global_batch_digest() -> bytes:
+        chains = {v: h.local_digest() for v, h in hashers.items()}
+        if world > 1:
+            objs: list = [None] * world
+            dist.all_gather_object(objs, chains)
+            chains = {k: v for d in objs for k, v in d.items()}
+        return SH.combine_batch_digests([chains[v] for v in range(V)])
+
+    result = {"run_dir": str(run_dir), "hashes": [], "losses": []}
+    zero_norm_streak: dict[str, int] = {}
+    try:
+        it = iter(loader)
+        while consumed < train_cfg.total_tokens and (max_steps is None or step < max_steps):
+            t_step = time.perf_counter()
+            plan, batches = next(it)
+            M = plan.microbatches
+            if M % V:
+                raise RuntimeError("step %d has %d micro-batches, not a multiple of the %d virtual ranks" % (step, M, V))
+            accum = M // V
+            lr = sched(consumed, train_cfg.total_tokens) * rewarm_factor(consumed, rewarm_anchor, cfg.schedule.rewarm_tokens)
+            engine.zero_grads()
+            ces, zs = [], []
+            for v, k, windows in batches:
+                batch = collate(windows, pin=engine.is_cuda)
+                if sh_cfg.include_batch:
+                    hashers[v].update(batch)
+                ids = batch["input_ids"].to(dev, non_blocking=True)
+                labels = batch["labels"].to(dev, non_blocking=True)
+                ce, z = engine.forward_backward(hosted.index(v), ids, labels, accum)
+                ces.append(ce.detach())
+                zs.append(z.detach())
+            grad_norm = engine.reduce_gradients()
+            local_ce = [float(c) for c in ces]
+            ce_sum, n_mb = deterministic_scalar_sum(local_ce, world)
+            z_sum, _ = deterministic_scalar_sum([float(z) for z in zs], world)
+            loss_mean = ce_sum / max(n_mb, 1)
+            zero_q_gain_grads(engine.named_grads(), step, train_cfg.qk_freeze_q_gains_until_step)
+            skipped = spike.should_skip(grad_norm, loss_mean, step)
+            clip = engine.clip_coefficient(grad_norm, train_cfg.grad_clip)
+            if skipped:
+                spike.record_skip(step)
+                engine.skip_step()
+            else:
+                engine.optimizer_step(lr, clip)
+                clamp_qk_gains(engine.model, train_cfg.qk_gain_clamp)
+            if train_cfg.dead_tensor_assert_steps > 0:
+                for name, sos in zip(engine.names, engine.per_tensor_sos):
+                    zero_norm_streak[name] = zero_norm_streak.get(name, 0) + 1 if sos == 0.0 else 0
+                    if zero_norm_streak[name] >= train_cfg.dead_tensor_assert_steps:
+                        raise RuntimeError("parameter %s had an exactly zero gradient for %d consecutive steps" % (name, zero_norm_streak[name]))
+            consumed += plan.tokens_this_step
+            step += 1
+
+            exit_due = _emergency_exit_requested(world, dev)
+            final_step = consumed >= train_cfg.total_tokens or (max_steps is not None and step >= max_steps)
+            hash_due = sh_cfg.every_n_steps > 0 and step % sh_cfg.every_n_steps == 0
+            ckpt_due = (train_cfg.ckpt_every_steps > 0 and step % train_cfg.ckpt_every_steps == 0) or \
+                       (train_cfg.ckpt_every_steps == 0 and train_cfg.ckpt_every_tokens > 0 and
+                        consumed // train_cfg.ckpt_every_tokens > (consumed - plan.tokens_this_step) // train_cfg.ckpt_every_tokens)
+            step_hash, t_hash = None, 0.0
+            if sh_cfg.every_n_steps > 0 and (hash_due or ckpt_due or exit_due or final_step):
+                t0 = time.perf_counter()
+                bd = global_batch_digest() if sh_cfg.include_batch else None
+                step_hash = engine.sharded_state_hash(chained, bd, include_grads=sh_cfg.include_grads)
+                if hash_due:
+                    chained = step_hash
+                t_hash = (time.perf_counter() - t0) * 1e3
+                if rank == 0:
+                    _append_jsonl(hash_log, {"step": step, "consumed_tokens": consumed, "state_hash": step_hash})
+                result["hashes"].append((step, step_hash))
+            t_ckpt = 0.0
+            if ckpt_due or exit_due or final_step:
+                t0 = time.perf_counter()
+                ckpt.save(step, engine, make_meta(), step_hash, loader.state().to_json(), spike.state_dict(),
+                          {v: h.local_digest() for v, h in hashers.items()})
+                t_ckpt = (time.perf_counter() - t0) * 1e3
+            wall_ms = (time.perf_counter() - t_step) * 1e3
+            result["losses"].append(loss_mean)
+            if rank == 0:
+                tps = plan.tokens_this_step / (wall_ms / 1e3)
+                metrics.log({"step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_sum / max(n_mb, 1), "lr": lr,
+                             "grad_norm_pre_clip": grad_norm, "clip_coef": clip, "skipped": skipped,
+                             "skipped_steps_total": spike.state.skipped_steps, "tokens_per_sec": tps, "tokens_per_sec_per_gpu": tps / world,
+                             "mfu": mfu(tps / world, flops_tok), "step_wall_time_ms": wall_ms, "hash_time_ms": t_hash,
+                             "ckpt_save_time_ms": t_ckpt, "state_hash": step_hash, "microbatches": M}, step=step)
+                gl = train_cfg.grad_norm_log
+                if gl.every_n_steps > 0 and step % gl.every_n_steps == 0:
+                    pt = np.sqrt(engine.per_tensor_sos)
+                    top = sorted(zip(engine.names, pt.tolist()), key=lambda kv: -kv[1])[: gl.top_k]
+                    _append_jsonl(gn_log, {"step": step, "grad_norm": grad_norm, "top": top})
+            if exit_due:
+                log.warning("SIGTERM received: checkpoint written at step %d, exiting", step)
+                raise SystemExit(0)
+    except Halt as h:
+        log.error("halted by the spike protocol: %s", h)
+        result["halted"] = str(h)
+    finally:
+        metrics.close()
+        engine.close()
+    result.update({"step": step, "consumed_tokens": consumed, "chained_hash": chained})
+    return result

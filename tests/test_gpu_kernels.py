@@ -1,0 +1,196 @@
+"""sm_100a kernels against their CPU twins (bitwise where the contract is bit-exactness) and against
+plain PyTorch fp32 references (tolerance) for the tensor-core family."""
+import math
+
+import pytest
+import torch
+
+from open_transformers_b200.ops import functional as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _both(fn, *tensors, **kw):
+    cpu = fn(*[t.cpu() if isinstance(t, torch.Tensor) else t for t in tensors], **kw)
+    gpu = fn(*[t.to(DEV) if isinstance(t, torch.Tensor) else t for t in tensors], **kw)
+    return cpu, gpu
+
+
+def _eq(a, b, what):
+    if isinstance(a, (tuple, list)):
+        for i, (x, y) in enumerate(zip(a, b)):
+            _eq(x, y, "%s[%d]" % (what, i))
+        return
+    if a is None:
+        assert b is None
+        return
+    b = b.cpu()
+    if not torch.equal(a, b):
+        d = (a.float() - b.float()).abs()
+        raise AssertionError("%s differs: max abs %.3e at %d of %d elements" % (what, d.max().item(), int((d > 0).sum()), d.numel()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(37, 256), (64, 2048), (5, 704)])
+def test_rmsnorm_bitwise(dtype, rows, D):
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(rows, D, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(dtype)
+    dy = torch.randn(rows, D, generator=g).to(dtype)
+    for gain in (w, None):
+        c, gq = _both(lambda x_, w_: K.rmsnorm_fwd(x_, w_, 1e-5), x, gain)
+        _eq(c, gq, "rmsnorm_fwd")
+        rstd = c[1]
+        c2, g2 = _both(lambda dy_, x_, w_, r_: K.rmsnorm_bwd(dy_, x_, w_, r_, w_ is not None), dy, x, gain, rstd)
+        _eq(c2, g2, "rmsnorm_bwd")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D,do_norm", [(128, True), (64, True), (64, False)])
+def test_qknorm_rope_bitwise(dtype, D, do_norm):
+    g = torch.Generator().manual_seed(2)
+    B, T, H, Hkv = 2, 48, 4, 2
+    qkv = torch.randn(B * T, (H + 2 * Hkv) * D, generator=g).to(dtype)
+    cos, sin = K.rope_tables(T, D, 10000.0, "cpu")
+    c, gq = _both(lambda q, c_, s_: K.qknorm_rope_fwd(q, c_, s_, H + Hkv, D, T, do_norm, 1e-5), qkv, cos, sin)
+    _eq(c[0], gq[0], "qknorm_rope_fwd")
+    if do_norm:
+        _eq(c[1], gq[1], "rstd")
+    dout = torch.randn(B * T, (H + Hkv) * D, generator=g).to(dtype)
+
+    def bwd(do_, q_, r_, c_, s_):
+        din = torch.zeros_like(q_)
+        return K.qknorm_rope_bwd(do_, q_, r_, din, c_, s_, H + Hkv, D, T, do_norm)
+
+    c2, g2 = _both(bwd, dout, qkv, c[1], cos, sin)
+    _eq(c2, g2, "qknorm_rope_bwd")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu_bitwise(dtype):
+    g = torch.Generator().manual_seed(3)
+    gu = (3 * torch.randn(33, 2 * 704, generator=g)).to(dtype)
+    dh = torch.randn(33, 704, generator=g).to(dtype)
+    _eq(*_both(K.swiglu_fwd, gu), "swiglu_fwd")
+    _eq(*_both(K.swiglu_bwd, gu, dh), "swiglu_bwd")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("V", [1024, 8192 + 128])
+def test_ce_zloss_bitwise(dtype, V):
+    g = torch.Generator().manual_seed(4)
+    rows = 19
+    logits = (4 * torch.randn(rows, V, generator=g)).to(dtype)
+    labels = torch.randint(0, V, (rows,), generator=g)
+    labels[3] = -100
+
+    def run(l_, lab_):
+        l_ = l_.clone()
+        ce, lse = K.ce_zloss_(l_, lab_, 1e-4, 1.0 / rows, True)
+        return ce, lse, l_, K.det_sum(ce, False, 1.0 / rows), K.det_sum(lse, True, 1.0 / rows)
+
+    c, gq = _both(run, logits, labels)
+    _eq(c, gq, "ce_zloss")
+    ref = torch.nn.functional.cross_entropy(logits.float(), labels, ignore_index=-100, reduction="none")
+    assert torch.allclose(c[0], ref, atol=2e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_embedding_bitwise(dtype):
+    g = torch.Generator().manual_seed(5)
+    V, D, n = 512, 256, 300
+    table = torch.randn(V, D, generator=g).to(dtype)
+    ids = torch.randint(0, 40, (n,), generator=g)
+    dy = torch.randn(n, D, generator=g).to(dtype)
+    _eq(*_both(K.embedding_fwd, ids, table), "embedding_fwd")
+
+    def bwd(dy_, ids_):
+        dW = torch.zeros(V, D, dtype=torch.float32, device=dy_.device)
+        K.embedding_bwd(dy_, ids_, dW, True)
+        K.embedding_bwd(dy_, ids_, dW, True)
+        return dW
+
+    _eq(*_both(bwd, dy, ids), "embedding_bwd")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K_", [(130, 70, 257), (256, 192, 64)])
+def test_gemm_f32_bitwise(a_mn, b_mn, M, N, K_):
+    g = torch.Generator().manual_seed(6)
+    A = torch.randn(M, K_, generator=g)
+    B = torch.randn(N, K_, generator=g)
+    As = A.t().contiguous() if a_mn else A
+    Bs = B.t().contiguous() if b_mn else B
+    _eq(*_both(lambda a, b: K.gemm(a, b, a_mn=a_mn, b_mn=b_mn), As, Bs), "gemm_f32")
+    R = torch.randn(M, N, generator=g)
+    _eq(*_both(lambda a, b, r: K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_RESIDUAL, residual=r), As, Bs, R), "gemm_f32_res")
+
+    def acc(a, b):
+        out = torch.ones(M, N, device=a.device)
+        return K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, epi=K.EPI_ACC_F32)
+
+    _eq(*_both(acc, As, Bs), "gemm_f32_acc")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16_vs_reference(a_mn, b_mn):
+    g = torch.Generator().manual_seed(7)
+    M, N, K_ = 384, 520, 328
+    A = torch.randn(M, K_, generator=g).bfloat16()
+    B = torch.randn(N, K_, generator=g).bfloat16()
+    ref = A.float() @ B.float().t()
+    As = (A.t().contiguous() if a_mn else A).to(DEV)
+    Bs = (B.t().contiguous() if b_mn else B).to(DEV)
+    out = K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_STORE_F32).cpu()
+    assert torch.allclose(out, ref, atol=2e-3, rtol=1e-4), (out - ref).abs().max()
+    out2 = K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_STORE_F32).cpu()
+    assert torch.equal(out, out2)
+    assert K.kernel_status(DEV) == 0
+
+
+@pytest.mark.parametrize("D,window,T", [(64, 0, 200), (128, 0, 256), (64, 96, 320)])
+def test_attention_f32_bitwise(D, window, T):
+    g = torch.Generator().manual_seed(8)
+    B, H, Hkv = 1, 4, 2
+    qk = torch.randn(B * T, (H + Hkv) * D, generator=g)
+    qkv = torch.randn(B * T, (H + 2 * Hkv) * D, generator=g)
+    dO = torch.randn(B * T, H * D, generator=g)
+
+    def run(qk_, qkv_, dO_):
+        O, lse = K.attn_fwd(qk_, qkv_, B, T, H, Hkv, D, window)
+        dqk, dqkv = torch.zeros_like(qk_), torch.zeros_like(qkv_)
+        K.attn_bwd(qk_, qkv_, O, dO_, lse, dqk, dqkv, B, T, H, Hkv, D, window)
+        return O, lse, dqk, dqkv[:, (H + Hkv) * D:].contiguous()
+
+    _eq(*_both(run, qk, qkv, dO), "attention_f32")
+
+
+@pytest.mark.parametrize("D,window,T", [(128, 0, 384), (64, 128, 512)])
+def test_attention_bf16_vs_twin(D, window, T):
+    g = torch.Generator().manual_seed(9)
+    B, H, Hkv = 2, 4, 2
+    qk = torch.randn(B * T, (H + Hkv) * D, generator=g).bfloat16()
+    qkv = torch.randn(B * T, (H + 2 * Hkv) * D, generator=g).bfloat16()
+    dO = (0.5 * torch.randn(B * T, H * D, generator=g)).bfloat16()
+
+    def run(qk_, qkv_, dO_):
+        O, lse = K.attn_fwd(qk_, qkv_, B, T, H, Hkv, D, window)
+        dqk, dqkv = torch.zeros_like(qk_), torch.zeros_like(qkv_)
+        K.attn_bwd(qk_, qkv_, O, dO_, lse, dqk, dqkv, B, T, H, Hkv, D, window)
+        return O.float(), lse, dqk.float(), dqkv[:, (H + Hkv) * D:].float()
+
+    c, gq = _both(run, qk, qkv, dO)
+    for name, a, b in zip(("O", "lse", "dqk", "dv"), c, gq):
+        err = (a - b.cpu()).abs().max().item()
+        assert err < 0.04 * max(1.0, a.abs().max().item()), (name, err)
+    assert K.kernel_status(DEV) == 0
+
+
+def test_tree_digest_matches_host():
+    from open_transformers_b200.train import state_hash as SH
+
+    g = torch.Generator().manual_seed(10)
+    for n in (0, 5, 1024, 1025, 300_000, 5_000_000):
+        t = torch.randn(n, generator=g)
+        assert SH.tree_digest_tensor(t) == SH.tree_digest_tensor(t.to(DEV)), n
