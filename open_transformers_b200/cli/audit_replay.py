@@ -1,0 +1,296 @@
+"""``pretrain-audit-replay``: re-execute training steps on ONE device and compare the state hash.
+
+The replay hosts all V recorded virtual ranks in a single process (GPU or plain CPU) and runs the very
+engine the cluster ran - same kernels or their bit-exact CPU twins, same reduction tree - so an honest
+checkpoint chain reproduces digest for digest. Modes:
+
+  --from-init                       rebuild the weights from the seed, check the init hash, optionally continue
+  --checkpoint DIR --until-step N   load a checkpoint, replay up to step N
+  --expect-hash HEX|FILE            digest to compare with (default: the run's logs/state_hashes.jsonl or the
+                                    target checkpoint's state_hash.txt when they can be found)
+
+Prints ``MATCH=True/False``; exit status 1 and ``AUDIT FAILED: state_hash X != Y`` on a mismatch. Result JSON:
+{step, consumed_tokens, state_hash, kernels, device, rank0_losses, expected, match, saved_checkpoint?}
+(reference src/pretrain/cli/audit_replay.py:1144-1349, 2789-2807).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import re
+import sys
+import time
+from pathlib import Path
+
+log = logging.getLogger("pretrain.audit")
+MAX_AUDIT_WORLD = 64
+_HEX64 = re.compile(r"^[0-9a-fA-F]{64}$")
+# kernel-selecting environment a checkpoint may ask the replay to re-apply; anything else is refused
+ALLOWED_KERNEL_ENV = {"OTB_EXECUTION_MODE", "OTB_ATTN_BLOCK", "OTB_TENSOR_DIGEST"}
+REFUSED_ENV_PREFIXES = ("OTB_LIB", "OTB_CXX", "OTB_REBUILD", "LD_", "PYTHON")
+
+
+class AuditError(RuntimeError):
+    pass
+
+
+def resolve_expect_hash(value: str | None) -> str | None:
+    """A 64-hex digest, or a path to a file whose first token is one."""
+    if value is None:
+        return None
+    if _HEX64.match(value.strip()):
+        return value.strip().lower()
+    p = Path(value)
+    if p.is_file():
+        tok = p.read_text().split()
+        if tok and _HEX64.match(tok[0]):
+            return tok[0].lower()
+        raise AuditError("%s does not start with a 64-hex digest" % p)
+    raise AuditError("--expect-hash must be a 64-character hex digest or a file containing one, got %r" % value)
+
+
+def apply_kernel_env(env: dict) -> dict:
+    """Re-apply the allow-listed kernel environment recorded in a checkpoint; refuse redirecting keys."""
+    applied = {}
+    for k, v in (env or {}).items():
+        if any(k.startswith(p) for p in REFUSED_ENV_PREFIXES):
+            raise AuditError("checkpoint metadata tries to set %s, which could redirect native code; refused" % k)
+        if k in ALLOWED_KERNEL_ENV:
+            os.environ[k] = str(v)
+            applied[k] = str(v)
+    return applied
+
+
+def mismatch_message(got: str, want: str) -> str:
+    return "AUDIT FAILED: state_hash %s != %s" % (got, want)
+
+
+def _find_expected(run_dir: Path | None, step: int) -> str | None:
+    if run_dir is None:
+        return None
+    logf = run_dir / "logs" / "state_hashes.jsonl"
+    if logf.is_file():
+        for line in logf.read_text().splitlines():
+            row = json.loads(line)
+            if row.get("step") == step and row.get("kind") != "init":
+                return row["state_hash"]
+    p = run_dir / "checkpoints" / ("step_%09d" % step) / "state_hash.txt"
+    return p.read_text().strip() if p.is_file() else None
+
+
+def audit_replay(checkpoint: str | None = None, *, config_name: str | None = None, overrides: list[str] | None = None,
+                 data_root: str | None = None, device: str = "cpu", cpu_threads: str | None = None, from_init: bool = False,
+                 descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
+                 save_checkpoint_dir: str | None = None, loss_log: str | None = None, run_dir: str | None = None,
+                 offload_optimizer: bool = False, offload_master: bool = False, offload_grads: bool = False, **_ignored) -> dict:
+    import numpy as np
+    import torch
+
+    from ..config import load_config, parse_config_resolved
+    from ..data.global_stream import GlobalStreamState
+    from ..data.loader import build_global_loader, collate
+    from ..optim.schedules import build_schedule, rewarm_factor
+    from ..ops import native
+    from ..train import state_hash as SH
+    from ..train.checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
+    from ..train.engine import TrainEngine
+    from ..train.spike_protocol import SpikeProtocol
+    from .cpu_threads import configure_cpu_threads
+
+    expected = resolve_expect_hash(expect_hash)
+    if device == "cpu":
+        configure_cpu_threads(cpu_threads or "auto")
+    if device.startswith("cuda") and not torch.cuda.is_available():
+        raise AuditError("--device cuda requested but no CUDA device is visible")
+    if not from_init and checkpoint is None:
+        raise AuditError("either --checkpoint or --from-init (with --config-name or --descriptor-checkpoint) is required")
+
+    meta = None
+    src = checkpoint or descriptor_checkpoint
+    if src is not None:
+        meta = Checkpointer.read_meta(src)
+        apply_kernel_env(meta.kernel_env)
+        if run_dir is None:
+            run_dir = str(Path(src).resolve().parent.parent)
+    if meta is not None and meta.config_resolved and config_name is None:
+        cfg = parse_config_resolved(meta.config_resolved)
+    elif config_name is not None:
+        cfg = load_config(config_name, overrides or [])
+    else:
+        raise AuditError("no configuration: the checkpoint has none embedded and --config-name was not given")
+    if cfg.run.reduction_mode != "deterministic_allgather":
+        raise AuditError("run.reduction_mode=%s is not auditable (only deterministic_allgather pins the reduction order)" % cfg.run.reduction_mode)
+    if meta is not None:
+        V, S, R = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
+        if not (1 <= V <= MAX_AUDIT_WORLD) or S * R != V:
+            raise AuditError("recorded topology (world %d = replicate %d x shard %d) is out of bounds" % (V, R, S))
+        if meta.clip_algo != "global" or meta.grad_norm_algo != "deterministic_per_tensor_sos_v1":
+            raise AuditError("unsupported clip / norm algorithm in checkpoint metadata")
+        cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = V, S, R
+    elif cfg.run.virtual_dp_size == 0:
+        raise AuditError("--from-init with --config-name needs run.virtual_dp_size (the topology to emulate)")
+
+    engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None)
+    V = engine.V
+    run_path = Path(run_dir) if run_dir else None
+    result: dict = {"device": device, "kernels": native.loaded_libraries(), "rank0_losses": [], "expected": expected, "match": None}
+    step, consumed, chained, stream_state = 0, 0, None, None
+    hashers = {v: SH.RunningBatchHasher() for v in range(V)}
+    spike = SpikeProtocol.from_config(cfg.train.spike)
+    rewarm_anchor = None
+
+    if from_init:
+        init_hash = engine.full_state_hash()
+        want = expected if (until_step in (None, 0)) else None
+        if want is None and run_path is not None and (run_path / "checkpoints" / "state_hash_init.txt").is_file():
+            want = (run_path / "checkpoints" / "state_hash_init.txt").read_text().strip()
+        result.update({"init_hash": init_hash, "init_expected": want, "init_match": (init_hash == want) if want else None})
+        if want and init_hash != want:
+            result.update({"step": 0, "consumed_tokens": 0, "state_hash": init_hash, "expected": want, "match": False})
+            return result
+        if until_step in (None, 0):
+            result.update({"step": 0, "consumed_tokens": 0, "state_hash": init_hash, "expected": want, "match": (init_hash == want) if want else None})
+            return result
+    else:
+        ck = Checkpointer(Path(checkpoint).parent.parent)
+        side = ck.load(checkpoint, engine)
+        step, consumed, chained = meta.step, meta.consumed_tokens, meta.chained_hash
+        stream_state = GlobalStreamState.from_json(side["global_stream"]) if side["global_stream"] else None
+        hashers = {v: SH.RunningBatchHasher(side["batch_chains"][v]) for v in range(V)}
+        spike.load_state_dict(side["spike_protocol"])
+        rewarm_anchor = meta.rewarm_anchor_tokens
+    if until_step is None:
+        until_step = step + max(cfg.train.ckpt_every_steps, 1)
+    if until_step <= step:
+        raise AuditError("--until-step %d is not beyond the starting step %d" % (until_step, step))
+
+    tr, sh_cfg = cfg.train, cfg.train.state_hash
+    sched = build_schedule(cfg.schedule, tr, cfg.optim)
+    loader = build_global_loader(cfg, list(range(V)), V, state=stream_state, consumed_tokens=consumed, start_step=step, data_root=data_root)
+    dev = torch.device(device)
+    last_hash = None
+    loss_rows = []
+    t_start = time.time()
+    for plan, batches in loader:
+        if step >= until_step:
+            break
+        accum = plan.microbatches // V
+        lr = sched(consumed, tr.total_tokens) * rewarm_factor(consumed, rewarm_anchor, cfg.schedule.rewarm_tokens)
+        engine.zero_grads()
+        ces = []
+        for v, k, windows in batches:      # replica-major virtual-rank order, micro-batches ascending
+            batch = collate(windows)
+            if sh_cfg.include_batch:
+                hashers[v].update(batch)
+            ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum)
+            ces.append((v, k, float(ce)))
+        grad_norm = engine.reduce_gradients()
+        total = 0.0
+        for _, _, c in ces:
+            total += c
+        loss_mean = total / max(len(ces), 1)
+        if spike.should_skip(grad_norm, loss_mean, step):
+            try:
+                spike.record_skip(step)
+            except Exception:
+                pass
+            engine.skip_step()
+        else:
+            engine.optimizer_step(lr, engine.clip_coefficient(grad_norm, tr.grad_clip))
+        consumed += plan.tokens_this_step
+        step += 1
+        r0 = [c for v, _, c in ces if v == 0]
+        result["rank0_losses"].extend(r0)
+        loss_rows.append({"step": step, "rank0_losses": r0, "loss": loss_mean, "grad_norm": grad_norm})
+        hash_due = sh_cfg.every_n_steps > 0 and step % sh_cfg.every_n_steps == 0
+        ckpt_due = tr.ckpt_every_steps > 0 and step % tr.ckpt_every_steps == 0
+        if hash_due or ckpt_due or step == until_step:
+            bd = SH.combine_batch_digests([hashers[v].local_digest() for v in range(V)]) if sh_cfg.include_batch else None
+            last_hash = engine.sharded_state_hash(chained, bd, include_grads=sh_cfg.include_grads, tensor_digest=sh_cfg.tensor_digest)
+            if hash_due:
+                chained = last_hash
+        log.info("replayed step %d loss %.6f grad_norm %.6f", step, loss_mean, grad_norm)
+    result["seconds_per_step"] = (time.time() - t_start) / max(len(loss_rows), 1)
+    if torch.cuda.is_available() and device.startswith("cuda"):
+        result["peak_memory_bytes"] = int(torch.cuda.max_memory_allocated())
+    if expected is None:
+        expected = _find_expected(run_path, step)
+    result.update({"step": step, "consumed_tokens": consumed, "state_hash": last_hash, "expected": expected,
+                   "match": (last_hash == expected) if expected else None})
+    if loss_log:
+        Path(loss_log).write_text("\n".join(json.dumps(r) for r in loss_rows) + "\n")
+    if save_checkpoint_dir:
+        ck = Checkpointer(save_checkpoint_dir)
+        m = CheckpointMeta(consumed_tokens=consumed, step=step, config_resolved=resolved_config_json(cfg), chained_hash=chained,
+                           reduction_mode=cfg.run.reduction_mode, dp_world_size=V, dp_replicate=engine.dp_replicate, dp_shard=engine.dp_shard,
+                           tensor_digest=sh_cfg.tensor_digest, seed=cfg.run.seed, torch_version=torch.__version__, numpy_version=np.__version__,
+                           windows_emitted=loader.state().windows_emitted, mixed_precision=cfg.run.mixed_precision)
+        d = ck.save(step, engine, m, last_hash, loader.state().to_json(), spike.state_dict(), {v: h.local_digest() for v, h in hashers.items()})
+        from .verify_handoff import write_gradient_sidecar
+
+        write_gradient_sidecar(d, engine.named_grads())
+        result["saved_checkpoint"] = str(d)
+    engine.close()
+    return result
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="pretrain-audit-replay", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--checkpoint")
+    ap.add_argument("--config-name")
+    ap.add_argument("--data-root")
+    ap.add_argument("--gcs-root")
+    ap.add_argument("--fetch-dest")
+    ap.add_argument("--device", default="cpu", choices=["cuda", "cpu", "mps"])
+    ap.add_argument("--cpu-threads", default=None)
+    ap.add_argument("--from-init", action="store_true")
+    ap.add_argument("--descriptor-checkpoint")
+    ap.add_argument("--until-step", type=int)
+    ap.add_argument("--expect-hash")
+    ap.add_argument("--fold-spill-dir")
+    ap.add_argument("--no-fold-spill", action="store_true")
+    ap.add_argument("--offload-optimizer", action="store_true")
+    ap.add_argument("--optimizer-offload-dir")
+    ap.add_argument("--offload-master", action="store_true")
+    ap.add_argument("--offload-grads", action="store_true")
+    ap.add_argument("--master-offload-dir")
+    ap.add_argument("--save-checkpoint-dir")
+    ap.add_argument("--loss-log")
+    ap.add_argument("--run-dir")
+    ap.add_argument("overrides", nargs="*")
+    return ap
+
+
+def main(argv: list[str] | None = None) -> int:
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
+    a = build_parser().parse_args(argv)
+    if a.device == "mps":
+        print("AUDIT ERROR: Apple Metal/MPS is unavailable on this platform; use --device cuda or cpu", file=sys.stderr)
+        return 2
+    if a.gcs_root or a.fetch_dest:
+        from ..data.fetch_interval import fetch_audit_interval
+
+        if a.checkpoint and a.gcs_root:
+            a.data_root = fetch_audit_interval(a.checkpoint, a.gcs_root, a.fetch_dest or "audit_data", until_step=a.until_step)
+    try:
+        res = audit_replay(a.checkpoint, config_name=a.config_name, overrides=a.overrides, data_root=a.data_root, device=a.device,
+                           cpu_threads=a.cpu_threads, from_init=a.from_init, descriptor_checkpoint=a.descriptor_checkpoint,
+                           until_step=a.until_step, expect_hash=a.expect_hash, save_checkpoint_dir=a.save_checkpoint_dir,
+                           loss_log=a.loss_log, run_dir=a.run_dir, offload_optimizer=a.offload_optimizer, offload_master=a.offload_master,
+                           offload_grads=a.offload_grads)
+    except AuditError as e:
+        print("AUDIT ERROR: %s" % e, file=sys.stderr)
+        return 2
+    print(json.dumps(res, indent=1, default=str))
+    log.info("MATCH=%s", res["match"])
+    print("MATCH=%s" % res["match"])
+    if res["match"] is False:
+        print(mismatch_message(res["state_hash"], res["expected"]), file=sys.stderr)
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
