@@ -51,13 +51,16 @@ int otb_cpu_gemm(const void* A, const void* B, void* C, const void* R, int M, in
     const float* ar = &a[(size_t)m * K];
     for (int n = 0; n < N; ++n) {
       const float* br = &b[(size_t)n * K];
-      float acc = 0.0f;
-      for (int k = 0; k < K; ++k) acc = det_fmaf(ar[k], br[k], acc);
       const long ci = (long)m * ldc + n;
+      // fp32 operands (exact family): the accumulating epilogue CONTINUES the chain from the value already
+      // in C, so that a reduction split into several calls (row panels, micro-batches) equals one long chain.
+      // bf16 operands (tensor-core family): the tile sum is formed first and added to C once, as on the GPU.
+      float acc = (epi == 2 && !in_bf16) ? ((float*)C)[ci] : 0.0f;
+      for (int k = 0; k < K; ++k) acc = det_fmaf(ar[k], br[k], acc);
       switch (epi) {
         case 0: stx(C, ci, acc, out_bf16); break;
         case 1: ((float*)C)[ci] = acc; break;
-        case 2: ((float*)C)[ci] = ((float*)C)[ci] + acc; break;
+        case 2: ((float*)C)[ci] = in_bf16 ? ((float*)C)[ci] + acc : acc; break;
         default: stx(C, ci, acc + ldx(R, (long)m * ldr + n, out_bf16), out_bf16); break;
       }
     }

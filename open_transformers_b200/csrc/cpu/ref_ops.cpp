@@ -317,21 +317,17 @@ int otb_cpu_cast(const void* in, void* out, long n, int in_bf16, int out_bf16) {
 float otb_cpu_expf(float x) { return det_expf(x); }
 float otb_cpu_logf(float x) { return det_logf(x); }
 void otb_cpu_rope_tables(float* cosb, float* sinb, int seq_len, int half, double theta) {
-  // inv_freq_j = theta^(-2j/d) evaluated as exp(-(2j/d) ln theta) in double by the shared routines
-  // is avoided: frequencies come from repeated correctly rounded double operations only.
-  //   inv_freq_j = 1 / theta^(j/half);  theta^(j/half) = r^j with r = theta^(1/half) found by
-  //   Newton iteration on x^half = theta (deterministic: multiplies/divides only).
-  double r = 1.0;
-  {  // Newton for x^half - theta = 0, started from above the root
-    double x = theta;  // monotone convergence from above
-    for (int it = 0; it < 1000000; ++it) {
-      const double xn1 = det_powi(x, half - 1);
-      const double nx = x - (xn1 * x - theta) / (half * xn1);
-      if (nx == x) break;
-      x = nx;
-    }
-    r = x;
+  // inv_freq_j = 1 / theta^(j/half) = 1 / r^j with r = theta^(1/half); everything is built from
+  // correctly rounded double operations, no libm transcendental.
+  // r = theta^(1/half) by bisection on x^half = theta (x^half may overflow to +inf for large x, which
+  // still compares correctly); only multiplications, comparisons and halvings: deterministic everywhere.
+  double lo = 1.0, hi = theta > 1.0 ? theta : 1.0;
+  for (int it = 0; it < 4000; ++it) {
+    const double mid = lo + (hi - lo) * 0.5;
+    if (mid <= lo || mid >= hi) break;
+    if (det_powi(mid, half) > theta) hi = mid; else lo = mid;
   }
+  const double r = lo;
   for (int j = 0; j < half; ++j) {
     const double inv_freq = 1.0 / det_powi(r, j);
     for (int p = 0; p < seq_len; ++p) {

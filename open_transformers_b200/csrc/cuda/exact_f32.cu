@@ -24,7 +24,11 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < 4; ++j) {
+      // the accumulating epilogue continues the chain from the value already in C
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      acc[i][j] = (EPI == 2 && m < M && n < N) ? C[(long)m * ldc + n] : 0.0f;
+    }
   for (int k0 = 0; k0 < K; k0 += GK) {
     for (int idx = threadIdx.x; idx < GT * GK; idx += 256) {
       int k, mn;
@@ -55,7 +59,6 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
       const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
       if (m < M && n < N) {
         float v = acc[i][j];
-        if (EPI == 2) v = __fadd_rn(C[(long)m * ldc + n], v);
         if (EPI == 3) v = __fadd_rn(v, R[(long)m * ldr + n]);
         C[(long)m * ldc + n] = v;
       }

@@ -1,0 +1,99 @@
+import numpy as np
+import pytest
+
+from open_transformers_b200.data.indexed_dataset import IndexedDatasetReader, IndexedDatasetWriter, MAGIC
+from open_transformers_b200.data.loader import build_global_loader, build_global_stream
+from open_transformers_b200.data.manifest import SourceManifest, blake2b_file
+from open_transformers_b200.data.mix_sampler import SourceWalker, clear_caches
+from open_transformers_b200.train.batch_schedule import (accum_for_rank, iter_step_plans, microbatches_per_step, owner_rank,
+                                                         windows_consumed_before)
+from helpers import tiny_cfg
+
+
+def test_indexed_dataset_round_trip(tmp_path):
+    docs = [np.arange(5), np.array([], dtype=np.int64), np.array([7, 8, 9])]
+    with IndexedDatasetWriter(tmp_path / "s", np.uint16) as w:
+        for d in docs:
+            w.add_document(d)
+    raw = (tmp_path / "s.idx").read_bytes()
+    assert raw[:8] == MAGIC and len(raw) == 33 + 16 * 4
+    r = IndexedDatasetReader(tmp_path / "s")
+    assert r.num_documents == 3 and r.token_count == 8 and r.dtype == np.uint16
+    for i, d in enumerate(docs):
+        assert np.array_equal(r.document(i), d) and r.document_length(i) == len(d)
+    ro = IndexedDatasetReader(tmp_path / "s", index_only=True)
+    assert ro.document_length(2) == 3
+    with pytest.raises(RuntimeError):
+        ro.document(0)
+    (tmp_path / "bad.idx").write_bytes(b"NOTMAGIC" + raw[8:])
+    with pytest.raises(ValueError):
+        IndexedDatasetReader(tmp_path / "bad", index_only=True)
+
+
+def test_manifest_hashes_and_verify(tmp_path):
+    cfg = tiny_cfg(str(tmp_path))
+    src = tmp_path / cfg.data.sources[0].path
+    man = SourceManifest.load(src / "manifest.yaml")
+    assert man.total_tokens > 0 and man.verify(src) == []
+    p = src / (man.shards[0].prefix + ".bin")
+    data = bytearray(p.read_bytes()); data[0] ^= 1; p.write_bytes(bytes(data))
+    assert man.verify(src) == [str(p)]
+    assert len(blake2b_file(p)) == 64
+
+
+def test_walker_permutation_is_a_permutation_and_strided(tmp_path):
+    cfg = tiny_cfg(str(tmp_path))
+    src = tmp_path / cfg.data.sources[0].path
+    man = SourceManifest.load(src / "manifest.yaml")
+    clear_caches()
+    full = SourceWalker(man, str(src), seed=3)
+    order = [full.next_document_ref() for _ in range(full.total_documents)]
+    assert len(set(order)) == full.total_documents
+    a, b = SourceWalker(man, str(src), 3, 0, 2), SourceWalker(man, str(src), 3, 1, 2)
+    assert [a.next_document_ref() for _ in range(5)] == order[0:10:2] and [b.next_document_ref() for _ in range(5)] == order[1:10:2]
+    full.next_document_ref()
+    assert full.epoch == 1  # wrapped into the next epoch with a new permutation
+
+
+def test_sharded_view_equals_global_stream_for_any_split(tmp_path):
+    cfg = tiny_cfg(str(tmp_path))
+    it = iter(build_global_stream(cfg, data_root=str(tmp_path)))
+    windows = [next(it) for _ in range(12)]
+    for world_ranks in ([[0, 1]], [[0], [1]]):
+        seen = {}
+        for ranks in world_ranks:
+            view = iter(build_global_loader(cfg, ranks, 2, data_root=str(tmp_path)))
+            for step in range(3):
+                plan, batches = next(view)
+                for r, k, w in batches:
+                    m = k * 2 + r
+                    for slot in range(cfg.train.micro_batch_size):
+                        seen[plan.base_window + m * cfg.train.micro_batch_size + slot] = w[slot]
+        assert sorted(seen) == list(range(12))
+        for i in range(12):
+            assert np.array_equal(seen[i], windows[i])
+
+
+def test_stream_state_resume(tmp_path):
+    cfg = tiny_cfg(str(tmp_path))
+    view = build_global_loader(cfg, [0, 1], 2, data_root=str(tmp_path))
+    it = iter(view)
+    next(it)
+    state, (step, consumed, _) = view.state(), view.position
+    want = next(it)[1]
+    resumed = build_global_loader(cfg, [0, 1], 2, state=state, consumed_tokens=consumed, start_step=step, data_root=str(tmp_path))
+    got = next(iter(resumed))[1]
+    assert all(np.array_equal(a[2], b[2]) for a, b in zip(want, got))
+    assert state.windows_emitted == windows_consumed_before(consumed, cfg.train)
+
+
+def test_batch_schedule_math():
+    from open_transformers_b200.config import load_config
+
+    tr = load_config("1b_repop_v2").train
+    assert microbatches_per_step(0, tr) == 192 and microbatches_per_step(5_000_000_000, tr) == 288 and microbatches_per_step(370_000_000_000, tr) == 576
+    assert [owner_rank(m, world_size=4) for m in range(6)] == [0, 1, 2, 3, 0, 1]
+    assert sum(accum_for_rank(10, world_size=4, rank=r) for r in range(4)) == 10
+    plans = iter_step_plans(0, 0, tr)
+    p0, p1 = next(plans), next(plans)
+    assert p1.base_window == p0.microbatches * tr.micro_batch_size and p1.consumed_tokens == p0.tokens_this_step

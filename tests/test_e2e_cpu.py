@@ -1,0 +1,150 @@
+"""End to end on the CPU: the real ``train()`` on a tiny decoder, then the real audit replay, hand-off
+verification, safetensors relay, and the same run on two gloo ranks (its hashes must equal the single-process
+run: the virtual topology, not the process count, defines the bytes)."""
+import json
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+
+from helpers import free_port, tiny_cfg
+from open_transformers_b200.cli.audit_replay import audit_replay, main as audit_main, resolve_expect_hash
+from open_transformers_b200.cli.dcp_safetensors import pack, unpack
+from open_transformers_b200.cli.hash_ckpt import hash_checkpoint
+from open_transformers_b200.cli.verify_handoff import verify_handoff
+from open_transformers_b200.train.loop import train
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def trained(tmp_path_factory):
+    tmp = str(tmp_path_factory.mktemp("run"))
+    cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=2"])
+    res = train(cfg, device="cpu", data_root=tmp)
+    return tmp, cfg, res
+
+
+def test_train_writes_the_run_directory(trained):
+    tmp, cfg, res = trained
+    run = Path(res["run_dir"])
+    assert [s for s, _ in res["hashes"]] == [1, 2, 3] and len({h for _, h in res["hashes"]}) == 3
+    rows = [json.loads(l) for l in (run / "logs" / "state_hashes.jsonl").read_text().splitlines()]
+    assert rows[0]["kind"] == "init" and [r["step"] for r in rows[1:]] == [1, 2, 3]
+    assert (run / "checkpoints" / "state_hash_init.txt").read_text().strip() == rows[0]["state_hash"]
+    for step in (2, 3):
+        d = run / "checkpoints" / ("step_%09d" % step)
+        for f in ("_COMPLETE", "meta.json", "state_hash.txt", "global_stream.json", "spike_protocol.json", "batch_hasher.rank_0.bin",
+                  "batch_hasher.rank_1.bin", "rng.rank_0.pt", "rng.rank_1.pt", "dcp/.metadata"):
+            assert (d / f).exists(), f
+        assert len((d / "batch_hasher.rank_1.bin").read_bytes()) == 32
+    metrics = [json.loads(l) for l in (run / "logs" / "metrics.jsonl").read_text().splitlines()]
+    assert len(metrics) == 3 and all(m["loss"] > 0 for m in metrics)
+
+
+def test_cold_start_guard_refuses_to_overwrite(trained):
+    tmp, cfg, res = trained
+    with pytest.raises(RuntimeError):
+        train(cfg, device="cpu", data_root=tmp)
+
+
+def test_replay_from_init_and_from_checkpoint_match(trained):
+    tmp, cfg, res = trained
+    final = res["hashes"][-1][1]
+    r = audit_replay(from_init=True, descriptor_checkpoint=res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3)
+    assert r["init_match"] is True and r["match"] is True and r["state_hash"] == final
+    r2 = audit_replay(res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3, expect_hash=final)
+    assert r2["match"] is True and len(r2["rank0_losses"]) == 1
+    bad = audit_replay(res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3, expect_hash="0" * 64)
+    assert bad["match"] is False
+
+
+def test_cli_exit_codes_and_messages(trained, capsys):
+    tmp, cfg, res = trained
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    assert audit_main(["--checkpoint", ck, "--data-root", tmp, "--until-step", "3"]) == 0
+    assert "MATCH=True" in capsys.readouterr().out
+    assert audit_main(["--checkpoint", ck, "--data-root", tmp, "--until-step", "3", "--expect-hash", "f" * 64]) == 1
+    assert "AUDIT FAILED: state_hash" in capsys.readouterr().err
+    assert audit_main(["--checkpoint", ck, "--data-root", tmp, "--until-step", "1"]) == 2
+    with pytest.raises(Exception):
+        resolve_expect_hash("not-a-digest")
+
+
+def test_tampered_checkpoint_is_detected(trained, tmp_path):
+    tmp, cfg, res = trained
+    import shutil
+
+    import torch
+
+    src = Path(res["run_dir"]) / "checkpoints" / "step_000000002"
+    dst = tmp_path / "checkpoints" / "step_000000002"
+    shutil.copytree(src, dst)
+    chain = bytearray((dst / "batch_hasher.rank_0.bin").read_bytes())
+    chain[0] ^= 1
+    (dst / "batch_hasher.rank_0.bin").write_bytes(bytes(chain))
+    r = audit_replay(str(dst), data_root=tmp, until_step=3, expect_hash=res["hashes"][-1][1])
+    assert r["match"] is False
+    (dst / "rng.rank_1.pt").unlink()
+    with pytest.raises(FileNotFoundError):
+        audit_replay(str(dst), data_root=tmp, until_step=3)
+
+
+def test_handoff_and_safetensors_relay(trained, tmp_path):
+    tmp, cfg, res = trained
+    ck2 = res["run_dir"] + "/checkpoints/step_000000002"
+    packed = pack(ck2, str(tmp_path / "ck.safetensors"))
+    assert packed["tensors"] > 0
+    un = unpack(str(tmp_path / "ck.safetensors"), str(tmp_path / "relay" / "checkpoints" / "step_000000002"))
+    assert hash_checkpoint(un["dir"]) == hash_checkpoint(ck2)
+    r = audit_replay(un["dir"], data_root=tmp, until_step=3, save_checkpoint_dir=str(tmp_path / "handoff"), expect_hash=res["hashes"][-1][1])
+    assert r["match"] is True
+    prev = dict(res["hashes"])[2]
+    v = verify_handoff(r["saved_checkpoint"], prev_hash=prev)
+    assert v["match"] is True
+    assert verify_handoff(r["saved_checkpoint"], prev_hash="1" * 64)["match"] is False
+
+
+WORKER = textwrap.dedent("""
+    import json, os, sys
+    sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
+    from helpers import tiny_cfg
+    from open_transformers_b200.train.loop import train
+    from open_transformers_b200.parallel.env import shutdown_distributed
+    cfg = tiny_cfg({tmp!r}, ["run.run_id=dist", "train.ckpt_every_steps=2"])
+    res = train(cfg, device="cpu", data_root={tmp!r})
+    if int(os.environ["RANK"]) == 0:
+        json.dump(res["hashes"], open({tmp!r} + "/dist_hashes.json", "w"))
+    shutdown_distributed()
+""")
+
+
+@pytest.mark.distributed
+def test_two_gloo_ranks_produce_the_single_process_hashes(trained):
+    tmp, cfg, res = trained
+    script = Path(tmp) / "worker.py"
+    script.write_text(WORKER.format(root=str(ROOT), tmp=tmp))
+    port = free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(out.decode())
+    assert all(p.returncode == 0 for p in procs), "\\n".join(outs)
+    got = [tuple(x) for x in json.load(open(tmp + "/dist_hashes.json"))]
+    assert got == [tuple(x) for x in res["hashes"]]
+    # and the two-rank run's checkpoint replays on one process
+    r = audit_replay(tmp + "/runs/dist/checkpoints/step_000000002", data_root=tmp, until_step=3)
+    assert r["match"] is True

@@ -1,0 +1,98 @@
+import math
+import pickle
+
+import pytest
+import torch
+
+from open_transformers_b200.config import load_config
+from open_transformers_b200.optim.schedules import build_schedule, rewarm_factor
+from open_transformers_b200.train.checkpoint import (Checkpointer, UntrustedCheckpointError, validate_dcp_metadata)
+from open_transformers_b200.train.midtrain import MidtrainConfigError, check_linear_anneal_resume
+from open_transformers_b200.train.spike_protocol import Halt, SpikeProtocol
+from open_transformers_b200.obs.metrics import mfu, transformer_flops_per_token
+
+
+def test_schedules():
+    cfg = load_config("1b_repop_v2")
+    s = build_schedule(cfg.schedule, cfg.train, cfg.optim)
+    warm = 667 * 3_145_728
+    assert s(0) == 0.0 and s(warm) == pytest.approx(4.5e-4) and s(warm // 2) == pytest.approx(2.25e-4, rel=1e-6)
+    assert s(cfg.train.total_tokens) == pytest.approx(4.5e-5)
+    w = load_config("1b_repop_v2", ["schedule=wsd"])
+    sw = build_schedule(w.schedule, w.train, w.optim)
+    assert sw(int(0.5 * w.train.total_tokens)) == pytest.approx(4.5e-4) and sw(w.train.total_tokens) == pytest.approx(4.5e-5)
+    m = load_config("1b_midtrain_math")
+    sm = build_schedule(m.schedule, m.train, m.optim)
+    assert sm(400_000_000_000) == pytest.approx(4.5e-5) and sm(405_000_000_000) == pytest.approx(2.25e-5) and sm(410_000_000_000) == 0.0
+    assert rewarm_factor(150, 100, 100) == 0.5 and rewarm_factor(10, None, 100) == 1.0
+
+
+def test_flops_formula():
+    f = transformer_flops_per_token(24, 2048, 4096, 128256)
+    assert f == pytest.approx(11.24e9, rel=2e-3)
+    assert mfu(1000.0, f, 1e15) == pytest.approx(1000.0 * f / 1e15)
+
+
+def test_spike_protocol_cooldown_halt_and_state():
+    sp = SpikeProtocol(5.0, skips_in_window_to_halt=3, halt_window_steps=100, skip_steps_on_spike=3, start_step=10)
+    assert not sp.should_skip(100.0, 1.0, step=5)            # before start_step
+    assert sp.should_skip(1.0, float("nan"), step=5)          # non-finite loss always skips
+    assert sp.should_skip(6.0, 1.0, step=10)
+    sp.record_skip(10)
+    assert sp.should_skip(0.1, 1.0, step=11)                  # cool-down
+    sd = sp.state_dict()
+    sp2 = SpikeProtocol(5.0, 3, 100, 3, 10)
+    sp2.load_state_dict(sd)
+    for s in (11, 12):
+        assert sp2.should_skip(0.1, 1.0, step=s)
+        sp2.record_skip(s)
+    assert not sp2.should_skip(0.1, 1.0, step=13)
+    sp2.record_skip(20)
+    sp2.record_skip(21); sp2.record_skip(22)
+    with pytest.raises(Halt):
+        sp2.record_skip(30)
+    assert sp2.state.halted and sp2.state.skipped_steps == 7
+
+
+def test_midtrain_guards():
+    cfg = load_config("1b_midtrain_math")
+    check_linear_anneal_resume(cfg, 400_000_000_000)
+    with pytest.raises(MidtrainConfigError):
+        check_linear_anneal_resume(cfg, None)
+    with pytest.raises(MidtrainConfigError):
+        check_linear_anneal_resume(cfg, 399_000_000_000)
+    cfg.train.resume_reset_optimizer = True
+    with pytest.raises(MidtrainConfigError):
+        check_linear_anneal_resume(cfg, 400_000_000_000)
+
+
+class _Evil:
+    def __reduce__(self):
+        import os
+        return (os.system, ("echo pwned > /dev/null",))
+
+
+def test_untrusted_dcp_metadata_is_refused(tmp_path):
+    d = tmp_path / "dcp"
+    d.mkdir()
+    (d / ".metadata").write_bytes(pickle.dumps(_Evil()))
+    with pytest.raises(UntrustedCheckpointError):
+        validate_dcp_metadata(d)
+    (d / ".metadata").write_bytes(pickle.dumps({"x": eval}))
+    with pytest.raises(UntrustedCheckpointError):
+        validate_dcp_metadata(d)
+    (d / ".metadata").write_bytes(b"not a pickle")
+    with pytest.raises(UntrustedCheckpointError):
+        validate_dcp_metadata(d)
+
+
+def test_latest_ignores_incomplete_and_gc(tmp_path):
+    ck = Checkpointer(tmp_path)
+    for s in (1, 2, 3, 4, 5, 6):
+        d = ck.step_dir(s)
+        d.mkdir(parents=True)
+        if s != 6:
+            (d / "_COMPLETE").write_text("x")
+    assert ck.latest() == ck.step_dir(5) and ck.complete_steps() == [1, 2, 3, 4, 5]
+    ck.garbage_collect(keep_last=2, keep_every=0)
+    assert ck.complete_steps() == [4, 5] and ck.step_dir(6).exists()
