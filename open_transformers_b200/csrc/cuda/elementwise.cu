@@ -198,12 +198,37 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict
   }
 }
 
-// pair_tree over the leading dimension of v[n][D], in place; result in row 0. One thread per column.
-__global__ void pair_tree_cols_kernel(float* __restrict__ v, long n, int D) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= D) return;
-  for (long s = 1; s < n; s *= 2)
-    for (long i = 0; i + s < n; i += 2 * s) v[i * D + col] = __fadd_rn(v[i * D + col], v[(i + s) * D + col]);
+// pair_tree over the leading dimension of v[n][D], in place; result in row 0.
+// The tree "for s = 1, 2, 4..: v[i] += v[i+s] for i multiple of 2s, i+s < n" only ever pairs rows inside a
+// 2s-aligned group, so groups of 64 rows are reduced independently in shared memory (levels s = 1..32) and the
+// same kernel is then applied to the 64-strided group roots (levels 64..2048), and so on: identical association,
+// log-depth instead of a serial chain. Logical row j lives at v[j * row_stride * D]. A missing partner leaves the
+// value untouched (never "+ 0.0", which would turn -0.0 into +0.0).
+__global__ void __launch_bounds__(256) pair_tree_cols_stage_kernel(float* __restrict__ v, long n, long row_stride, int D) {
+  __shared__ float sm[64][33];
+  const int c = threadIdx.x & 31, r = threadIdx.x >> 5;  // 32 columns x 8 row-threads
+  const int col = blockIdx.x * 32 + c;
+  const long g0 = (long)blockIdx.y * 64;                // first logical row of this group
+  const long rows_here = min((long)64, n - g0);
+  if (col < D)
+    for (int rr = r; rr < rows_here; rr += 8) sm[rr][c] = v[(g0 + rr) * row_stride * D + col];
+  __syncthreads();
+  for (int s = 1; s < 64; s *= 2) {
+    for (int i = r * 2 * s; i + s < rows_here; i += 16 * s) sm[i][c] = __fadd_rn(sm[i][c], sm[i + s][c]);
+    __syncthreads();
+  }
+  if (col < D && r == 0) v[g0 * row_stride * D + col] = sm[0][c];
+}
+
+inline void pair_tree_cols_launch(float* v, long n, int D, cudaStream_t s) {
+  long stride = 1;
+  while (n > 1) {
+    const long groups = (n + 63) / 64;
+    dim3 grid((D + 31) / 32, (unsigned)groups);
+    pair_tree_cols_stage_kernel<<<grid, 256, 0, s>>>(v, n, stride, D);
+    n = groups;
+    stride *= 64;
+  }
 }
 
 // --------------------------------------------------- gain-free QK-norm + RoPE
@@ -485,13 +510,13 @@ extern "C" int otb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                         (const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dgamma_partial, rows, D, inv_d);)
   if (D <= 256) { RB(1) } else if (D <= 1024) { RB(4) } else if (D <= 2048) { RB(8) } else { RB(16) }
 #undef RB
-  if (dgamma_partial) pair_tree_cols_kernel<<<blocks_for(D, 128), 128, 0, S(stream)>>>(dgamma_partial, slabs, D);
+  if (dgamma_partial) pair_tree_cols_launch(dgamma_partial, slabs, D, S(stream));
   return (int)cudaGetLastError();
 }
 extern "C" long otb_rmsnorm_slabs(long rows) { return (rows + NORM_SLAB - 1) / NORM_SLAB; }
 
 extern "C" int otb_pair_tree_cols(float* v, long n, int D, void* stream) {
-  pair_tree_cols_kernel<<<blocks_for(D, 128), 128, 0, S(stream)>>>(v, n, D);
+  pair_tree_cols_launch(v, n, D, S(stream));
   return (int)cudaGetLastError();
 }
 

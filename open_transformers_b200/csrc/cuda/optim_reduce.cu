@@ -122,16 +122,19 @@ chunk_sos_kernel(const float* __restrict__ x, const long* __restrict__ chunk_sta
   if (threadIdx.x == 0) chunk_sos[blockIdx.x] = s;
 }
 
-// segment sums: seg i = pair_tree over chunk_sos[seg_first[i] .. seg_first[i+1]). One thread per segment.
-__global__ void seg_pair_tree_kernel(float* __restrict__ chunk_sos, const int* __restrict__ seg_first, int nseg,
-                                     float* __restrict__ seg_out) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// segment sums: seg i = pair_tree over chunk_sos[seg_first[i] .. seg_first[i+1]), in place. One CTA per segment;
+// every level of the tree is a parallel sweep (the association is the stride tree of det_reduce.h).
+__global__ void __launch_bounds__(256) seg_pair_tree_kernel(float* __restrict__ chunk_sos, const int* __restrict__ seg_first,
+                                                            int nseg, float* __restrict__ seg_out) {
+  const int i = blockIdx.x;
   if (i >= nseg) return;
   float* v = chunk_sos + seg_first[i];
   const int n = seg_first[i + 1] - seg_first[i];
-  for (int s = 1; s < n; s *= 2)
-    for (int k = 0; k + s < n; k += 2 * s) v[k] = __fadd_rn(v[k], v[k + s]);
-  seg_out[i] = n > 0 ? v[0] : 0.0f;
+  for (int s = 1; s < n; s *= 2) {
+    for (int k = threadIdx.x * 2 * s; k + s < n; k += 512 * s) v[k] = __fadd_rn(v[k], v[k + s]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) seg_out[i] = n > 0 ? v[0] : 0.0f;
 }
 
 struct AdamArgs {
@@ -149,23 +152,58 @@ adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* _
   const float keep = a.lr_wd_keep[chunk_group[blockIdx.x]];
   for (int j = threadIdx.x * 8; j < len; j += 2048) {
     float pn[8];
+    const long i0 = base + j;
+    if (j + 8 <= len) {
+      float gv[8], pv[8], mv[8], vv[8];
+      *reinterpret_cast<float4*>(gv) = *reinterpret_cast<const float4*>(grad + i0);
+      *reinterpret_cast<float4*>(gv + 4) = *reinterpret_cast<const float4*>(grad + i0 + 4);
+      *reinterpret_cast<float4*>(pv) = *reinterpret_cast<const float4*>(master + i0);
+      *reinterpret_cast<float4*>(pv + 4) = *reinterpret_cast<const float4*>(master + i0 + 4);
+      *reinterpret_cast<float4*>(mv) = *reinterpret_cast<const float4*>(m1 + i0);
+      *reinterpret_cast<float4*>(mv + 4) = *reinterpret_cast<const float4*>(m1 + i0 + 4);
+      *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(m2 + i0);
+      *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(m2 + i0 + 4);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      if (j + e < len) {
-        const long i = base + j + e;
-        const float g = __fmul_rn(grad[i], a.clip);
-        grad[i] = g;
-        float p = __fmul_rn(master[i], keep);
-        const float m = __fmaf_rn(m1[i], a.beta1, __fmul_rn(g, a.one_m_b1));
-        const float v = __fmaf_rn(m2[i], a.beta2, __fmul_rn(__fmul_rn(g, g), a.one_m_b2));
-        m1[i] = m;
-        m2[i] = v;
+      for (int e = 0; e < 8; ++e) {
+        const float g = __fmul_rn(gv[e], a.clip);
+        gv[e] = g;
+        float p = __fmul_rn(pv[e], keep);
+        const float m = __fmaf_rn(mv[e], a.beta1, __fmul_rn(g, a.one_m_b1));
+        const float v = __fmaf_rn(vv[e], a.beta2, __fmul_rn(__fmul_rn(g, g), a.one_m_b2));
+        mv[e] = m;
+        vv[e] = v;
         const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.sqrt_bc2), a.eps);
         p = __fmaf_rn(-a.step_size, __fdiv_rn(m, denom), p);
-        master[i] = p;
+        pv[e] = p;
         pn[e] = p;
-      } else {
-        pn[e] = 0.0f;
+      }
+      *reinterpret_cast<float4*>(grad + i0) = *reinterpret_cast<float4*>(gv);
+      *reinterpret_cast<float4*>(grad + i0 + 4) = *reinterpret_cast<float4*>(gv + 4);
+      *reinterpret_cast<float4*>(master + i0) = *reinterpret_cast<float4*>(pv);
+      *reinterpret_cast<float4*>(master + i0 + 4) = *reinterpret_cast<float4*>(pv + 4);
+      *reinterpret_cast<float4*>(m1 + i0) = *reinterpret_cast<float4*>(mv);
+      *reinterpret_cast<float4*>(m1 + i0 + 4) = *reinterpret_cast<float4*>(mv + 4);
+      *reinterpret_cast<float4*>(m2 + i0) = *reinterpret_cast<float4*>(vv);
+      *reinterpret_cast<float4*>(m2 + i0 + 4) = *reinterpret_cast<float4*>(vv + 4);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (j + e < len) {
+          const long i = base + j + e;
+          const float g = __fmul_rn(grad[i], a.clip);
+          grad[i] = g;
+          float p = __fmul_rn(master[i], keep);
+          const float m = __fmaf_rn(m1[i], a.beta1, __fmul_rn(g, a.one_m_b1));
+          const float v = __fmaf_rn(m2[i], a.beta2, __fmul_rn(__fmul_rn(g, g), a.one_m_b2));
+          m1[i] = m;
+          m2[i] = v;
+          const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.sqrt_bc2), a.eps);
+          p = __fmaf_rn(-a.step_size, __fdiv_rn(m, denom), p);
+          master[i] = p;
+          pn[e] = p;
+        } else {
+          pn[e] = 0.0f;
+        }
       }
     }
     const bool vec = (j + 8 <= len);
@@ -233,7 +271,7 @@ extern "C" int otb_chunk_sos(const float* x, const long* chunk_start, const int*
 }
 extern "C" int otb_seg_pair_tree(float* chunk_sos, const int* seg_first, int nseg, float* seg_out, void* stream) {
   if (nseg <= 0) return 0;
-  seg_pair_tree_kernel<<<(nseg + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(chunk_sos, seg_first, nseg,
+  seg_pair_tree_kernel<<<nseg, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(chunk_sos, seg_first, nseg,
                                                                                              seg_out);
   return (int)cudaGetLastError();
 }

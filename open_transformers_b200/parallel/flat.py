@@ -117,6 +117,8 @@ class PeerBuffer:
     def __init__(self, nbytes: int, device: torch.device, rank: int = 0, world: int = 1, group=None):
         self.nbytes, self.device, self.rank, self.world = nbytes, device, rank, world
         self._peer_ptrs: list[int] = []
+        self._own_ptr = 0
+        self._group = group
         self._ipc = device.type == "cuda" and world > 1
         if not self._ipc:
             self.bytes = torch.zeros(nbytes, dtype=torch.uint8, device=device)
@@ -152,7 +154,17 @@ class PeerBuffer:
         if self._ipc:
             from ..ops.native import cuda_lib
 
+            import torch.distributed as dist
+
             lib = cuda_lib()
+            torch.cuda.synchronize()
             for p in self._peer_ptrs:
                 lib.otb_ipc_close(ctypes.c_void_p(p))
             self._peer_ptrs = []
+            if self._own_ptr:
+                # every rank unmaps its view of the others' buffers before any owner frees its memory
+                if dist.is_initialized():
+                    dist.barrier(group=self._group)
+                self.bytes = None
+                lib.otb_ipc_free(ctypes.c_void_p(self._own_ptr))
+                self._own_ptr = 0

@@ -1,0 +1,42 @@
+"""Several GPUs must reproduce the single-GPU bytes: same virtual topology, different process counts. The
+gradient reduction and the weight redistribution run over CUDA-IPC peer pointers in this test."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.distributed]
+WORKER = str(Path(__file__).resolve().parent / "multi_gpu_worker.py")
+
+
+def _run(n, out, shard=4):
+    env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_SHARD=str(shard), NCCL_NVLS_ENABLE="0")
+    if n == 1:
+        cmd = [sys.executable, WORKER]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % n, "--master-addr", "127.0.0.1",
+               "--master-port", str(free_port()), WORKER]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.load(open(out))
+
+
+@pytest.mark.parametrize("shard", [4, 2])
+def test_hashes_do_not_depend_on_the_gpu_count(tmp_path, shard):
+    n_gpus = torch.cuda.device_count()
+    if n_gpus < 2:
+        pytest.skip("needs at least 2 GPUs")
+    one = _run(1, tmp_path / "g1.json", shard)
+    assert one["status"] == 0
+    for n in (2, 4):
+        if n > n_gpus:
+            break
+        many = _run(n, tmp_path / ("g%d.json" % n), shard)
+        assert many["status"] == 0
+        assert many["hashes"] == one["hashes"], (n, many, one)
