@@ -188,14 +188,16 @@ DET_HD float det_exp_attn(float x) {
   return det_mulf(y, det_pow2i((int)kf));
 }
 
-// 2^y for the attention kernels, y in [-125, ~1] (anything below -125, -inf included, gives 0).
-// Round-to-nearest-integer by the 1.5*2^23 trick (two exact adds), r = y - k exact, degree-6
-// polynomial for 2^r on |r| <= 1/2, then k is added to the exponent field.
+// 2^max(y, -126) for the attention kernels, y <= ~1. The clamp keeps the result a normal number (so the scaling is
+// an exact exponent add) and makes the function branch-free; an input of -inf gives 2^-126, so MASKED scores are
+// zeroed by the caller, not here. Round-to-nearest-integer by the 1.5*2^23 trick (two exact adds), r = y - k exact,
+// degree-6 polynomial for 2^r on |r| <= 1/2, then k is added to the exponent field: (bits(t) << 23) is k << 23
+// because the magic constant's own bits shift out.
 DET_HD float det_exp2_attn(float y) {
-  if (!(y >= -125.0f)) return 0.0f;
-  const float t = det_addf(y, 12582912.0f);
+  const float yc = fmaxf(y, -126.0f);
+  const float t = det_addf(yc, 12582912.0f);
   const float kf = det_addf(t, -12582912.0f);
-  const float r = det_addf(y, -kf);
+  const float r = det_fmaf(kf, -1.0f, yc);
   float p = 1.5403530393381606e-4f;
   p = det_fmaf(p, r, 1.3333558146428443e-3f);
   p = det_fmaf(p, r, 9.6181291076284772e-3f);
@@ -203,7 +205,7 @@ DET_HD float det_exp2_attn(float y) {
   p = det_fmaf(p, r, 2.4022650695910071e-1f);
   p = det_fmaf(p, r, 6.9314718055994531e-1f);
   p = det_fmaf(p, r, 1.0f);
-  return det_u2f(det_f2u(p) + ((det_f2u(t) - 0x4B400000u) << 23));
+  return det_u2f(det_f2u(p) + (det_f2u(t) << 23));
 }
 
 // sigmoid(x) = 1 / (1 + exp(-x))

@@ -102,14 +102,13 @@ int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, voi
         const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
         const float alpha = det_exp2_attn(m_run + (-m_safe));
         for (int hf = 0; hf < 2; ++hf) {
-          float lsum = 0.0f;
+          float lsum2[2] = {0.0f, 0.0f};  // even / odd keys of the half, each an ascending chain
           for (int e = hf * 64; e < hf * 64 + 64; ++e) {
-            const float y = (s[e] == -INFINITY) ? -INFINITY : det_fmaf(s[e], c_log2, -m_safe);
-            const float pe = det_exp2_attn(y);
-            lsum = lsum + pe;
+            const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
+            lsum2[e & 1] = lsum2[e & 1] + pe;
             p[e] = bf16 ? det_bf2f(det_f2bf(pe)) : pe;
           }
-          l_half[hf] = det_fmaf(l_half[hf], alpha, lsum);
+          l_half[hf] = det_fmaf(l_half[hf], alpha, lsum2[0] + lsum2[1]);
         }
         for (int d = 0; d < D; ++d) pv[d] = 0.0f;
         for (int e = 0; e < 128; ++e) {

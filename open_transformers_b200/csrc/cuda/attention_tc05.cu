@@ -179,9 +179,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     const int qi = q0 + r;                 // query position
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
     float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
-    float o[DH];
+    f2 o[DH / 2];
 #pragma unroll
-    for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+    for (int d = 0; d < DH / 2; ++d) o[d] = pack2(0.0f, 0.0f);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int j = jmin + i;
@@ -225,14 +225,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
             uint32_t v[32];
             tmem_ld_32x32b_x32(tPV + lane_off + half * DH + c * 32, v);
             tmem_ld_wait();
+            const f2 a2 = pack2(alpha_prev, alpha_prev);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[c * 32 + e] = __fmaf_rn(o[c * 32 + e], alpha_prev, __uint_as_float(v[e]));
+            for (int e = 0; e < 32; e += 2)
+              o[c * 16 + (e >> 1)] = fma2(o[c * 16 + (e >> 1)], a2, pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
           }
         }
       }
-      // pass 2: probabilities, half-row sum (ascending key), bf16 P into shared memory
-      float lsum = 0.0f;
+      // pass 2: probabilities, half-row sum (even and odd keys as two ascending chains), bf16 P into shared memory
+      f2 lsum2 = pack2(0.0f, 0.0f);
       if (ok) {
+        const f2 c2 = pack2(c_log2, c_log2), nm2 = pack2(-m_safe, -m_safe);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
@@ -241,18 +244,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float p2[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              float y = __fmaf_rn(__uint_as_float(v[e + u]), c_log2, -m_safe);
-              if (need_mask) {
-                const int kj = kbase + c * 32 + e + u;
-                if (kj > qi || (window > 0 && kj <= qi - window)) y = -INFINITY;
-              }
-              p2[u] = det_exp2_attn(y);
-              lsum = __fadd_rn(lsum, p2[u]);
+            f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), c2, nm2));
+            float p0, p1;
+            unpack2(p2, p0, p1);
+            if (need_mask) {
+              const int kj = kbase + c * 32 + e;
+              if (kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
+              if (kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
+              p2 = pack2(p0, p1);
             }
-            pk[e >> 1] = pack_bf16(p2[0], p2[1]);
+            lsum2 = add2(lsum2, p2);
+            pk[e >> 1] = pack_bf16(p0, p1);
           }
           uint8_t* base = sP + half * 16384;
 #pragma unroll
@@ -261,6 +263,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
                 make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
         }
       }
+      float ls0, ls1;
+      unpack2(lsum2, ls0, ls1);
+      const float lsum = __fadd_rn(ls0, ls1);
       l_run = __fmaf_rn(l_run, alpha, lsum);
       m_run = m_new;
       alpha_prev = alpha;
@@ -285,9 +290,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          const float a0 = __fdiv_rn(__fmaf_rn(o[c * 32 + e], alpha_prev, __uint_as_float(v[e])), l_tot);
-          const float a1 = __fdiv_rn(__fmaf_rn(o[c * 32 + e + 1], alpha_prev, __uint_as_float(v[e + 1])), l_tot);
-          pk[e >> 1] = pack_bf16(a0, a1);
+          float a0, a1;
+          unpack2(fma2(o[c * 16 + (e >> 1)], pack2(alpha_prev, alpha_prev), pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1]))), a0, a1);
+          pk[e >> 1] = pack_bf16(__fdiv_rn(a0, l_tot), __fdiv_rn(a1, l_tot));
         }
         if (in_range) {
 #pragma unroll
@@ -439,19 +444,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p2[2], d2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const float y = __fmaf_rn(__uint_as_float(vs[e + u]), c_log2, -lse_r);
-            const int kj = k0 + half * 64 + c * 32 + e + u;
-            bool dead = !row_ok;
-            if (need_mask) dead = dead || kj > qi || (window > 0 && kj <= qi - window);
-            const float p = dead ? 0.0f : det_exp2_attn(y);
-            p2[u] = p;
-            d2[u] = __fmul_rn(__fmul_rn(p, __fadd_rn(__uint_as_float(vd[e + u]), -dl_r)), scale);
+          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
+          if (need_mask || !row_ok) {
+            float p0, p1;
+            unpack2(p2, p0, p1);
+            const int kj = k0 + half * 64 + c * 32 + e;
+            if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
+            if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
+            p2 = pack2(p0, p1);
           }
-          pk[e >> 1] = pack_bf16(p2[0], p2[1]);
-          dsr[c * 16 + (e >> 1)] = pack_bf16(d2[0], d2[1]);
+          const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e]), __uint_as_float(vd[e + 1])), pack2(-dl_r, -dl_r))), pack2(scale, scale));
+          float p0, p1, d0, d1;
+          unpack2(p2, p0, p1);
+          unpack2(d2, d0, d1);
+          pk[e >> 1] = pack_bf16(p0, p1);
+          dsr[c * 16 + (e >> 1)] = pack_bf16(d0, d1);
         }
         uint8_t* base = sPdS + half * 16384;
 #pragma unroll
@@ -631,17 +638,19 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float d2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const float y = __fmaf_rn(__uint_as_float(vs[e + u]), c_log2, -lse_r);
-            const int kj = kbase + c * 32 + e + u;
-            bool dead = !row_ok;
-            if (need_mask) dead = dead || kj > qi || (window > 0 && kj <= qi - window);
-            const float p = dead ? 0.0f : det_exp2_attn(y);
-            d2[u] = __fmul_rn(__fmul_rn(p, __fadd_rn(__uint_as_float(vd[e + u]), -dl_r)), scale);
+          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
+          if (need_mask || !row_ok) {
+            float p0, p1;
+            unpack2(p2, p0, p1);
+            const int kj = kbase + c * 32 + e;
+            if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
+            if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
+            p2 = pack2(p0, p1);
           }
-          pk[e >> 1] = pack_bf16(d2[0], d2[1]);
+          const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e]), __uint_as_float(vd[e + 1])), pack2(-dl_r, -dl_r))), pack2(scale, scale));
+          float d0, d1;
+          unpack2(d2, d0, d1);
+          pk[e >> 1] = pack_bf16(d0, d1);
         }
         uint8_t* base = sDS + half * 16384;
 #pragma unroll

@@ -107,14 +107,13 @@ attn_f32_fwd_kernel(const float* __restrict__ qk, long ldqk, const float* __rest
     const float alpha = det_exp2_attn(__fadd_rn(m_run, -m_safe));
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const float y = (s[u] == -INFINITY) ? -INFINITY : __fmaf_rn(s[u], c_log2, -m_safe);
-      sp[w][lane + 32 * u] = det_exp2_attn(y);
+      sp[w][lane + 32 * u] = (s[u] == -INFINITY) ? 0.0f : det_exp2_attn(__fmaf_rn(s[u], c_log2, -m_safe));
     }
     __syncwarp();
-    if (lane < 2) {  // the two half-row sums, each an ascending chain
-      float lsum = 0.0f;
-      for (int e = lane * 64; e < lane * 64 + 64; ++e) lsum = __fadd_rn(lsum, sp[w][e]);
-      l_half[lane] = __fmaf_rn(l_half[lane], alpha, lsum);
+    if (lane < 2) {  // the two half-row sums: even and odd keys are ascending chains, then added
+      float le = 0.0f, lo = 0.0f;
+      for (int e = lane * 64; e < lane * 64 + 64; e += 2) { le = __fadd_rn(le, sp[w][e]); lo = __fadd_rn(lo, sp[w][e + 1]); }
+      l_half[lane] = __fmaf_rn(l_half[lane], alpha, __fadd_rn(le, lo));
     }
     float pv[4] = {0.f, 0.f, 0.f, 0.f};
     for (int e = 0; e < 128; ++e) {

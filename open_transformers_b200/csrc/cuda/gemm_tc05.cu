@@ -5,8 +5,10 @@
 //   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) with the
 //     fp32 accumulator in tensor memory, double-buffered so the epilogue of tile i overlaps
 //     the main loop of tile i+1,
-//   * four epilogue warps read the accumulator with tcgen05.ld (one row per thread) and
-//     write C straight to global memory.
+//   * four epilogue warps read the accumulator with tcgen05.ld (one row per thread), convert it,
+//     stage 32-row x 128-byte slices in swizzled shared memory and hand them to TMA
+//     (cp.async.bulk.tensor store; cp.reduce.async.bulk.tensor .add for the fp32 accumulate
+//     epilogue, one add per element, so still a fixed order).
 //
 // Reduction order (the hashed contract): every output element is the tensor-core fp32
 // accumulation of its K products taken in ascending k, 16 at a time, with NO split-K and no
@@ -45,13 +47,16 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;       // 4 warps x 2 buffers x [32 rows][128 B]
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
 };
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv,
                  const __nv_bfloat16* __restrict__ R, int M, int N, int K, long ldc, long ldr, int group_m,
                  uint32_t* __restrict__ status) {
   using L = SmemLayout<BN, STAGES>;
@@ -182,70 +187,91 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const long row = (long)tm * BM + q * 32 + lane;
       const int col0 = tn * BN;
-      // software pipeline over 32-column chunks with two register buffers: the TMEM load of the
-      // next chunk is in flight while the current one is converted and stored.
+      // Software pipeline over 32-column chunks with two register buffers: the TMEM load of the next chunk is
+      // in flight while the current one is converted and written to this warp's staging slice
+      // ([32 rows][128 B], 128-byte swizzle = 64 bf16 or 32 fp32 columns), which TMA then stores.
       const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+      uint8_t* stage0 = smem + L::EPI_OFFSET + q * 8192;
+      constexpr bool OUT_BF16 = (EPI == EPI_BF16 || EPI == EPI_BF16_RES);
+      constexpr int COLS_PER_SLICE = OUT_BF16 ? 64 : 32;
+      auto emit_slice = [&](int slice, int col) {
+        // staging writes (generic proxy) -> visible to TMA (async proxy), then one elected lane issues the store
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t src = smem_u32(stage0 + (slice & 1) * 4096);
+          const int y = tm * BM + q * 32;
+          if (EPI == EPI_F32_ACC) {
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tmC)),
+                         "r"(src), "r"(col), "r"(y)
+                         : "memory");
+          } else {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tmC)),
+                         "r"(src), "r"(col), "r"(y)
+                         : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      };
+      auto slice_free = [&]() {
+        // the slice written two stores ago has been read by TMA
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+      };
+      int slice = 0;
       auto store_chunk = [&](const uint32_t (&v)[32], int c) {
         const int col = col0 + c;
-        if (row < M && col < N) {
-          const bool full = (col + 32 <= N);
-          if (EPI == EPI_BF16 || EPI == EPI_BF16_RES) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cv) + row * ldc + col;
-            if (full) {
-              uint32_t p[16];
-              if (EPI == EPI_BF16_RES) {
-                const uint4* rr = reinterpret_cast<const uint4*>(R + row * ldr + col);
+        if (OUT_BF16) {
+          const int part = (c >> 5) & 1;  // which 64-byte half of the 128-byte staging row
+          if (part == 0) slice_free();
+          uint8_t* st = stage0 + (slice & 1) * 4096;
+          uint32_t p[16];
+          if (EPI == EPI_BF16_RES) {
+            if (row < M && col + 32 <= N) {
+              const uint4* rr = reinterpret_cast<const uint4*>(R + row * ldr + col);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint4 r4 = rr[j];
-                  const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+              for (int j = 0; j < 4; ++j) {
+                const uint4 r4 = rr[j];
+                const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float r0 = __uint_as_float(rw[e] << 16);
-                    const float r1 = __uint_as_float(rw[e] & 0xFFFF0000u);
-                    p[j * 4 + e] = pack_bf16(__fadd_rn(__uint_as_float(v[j * 8 + e * 2]), r0),
-                                             __fadd_rn(__uint_as_float(v[j * 8 + e * 2 + 1]), r1));
-                  }
+                for (int e = 0; e < 4; ++e) {
+                  const float r0 = __uint_as_float(rw[e] << 16);
+                  const float r1 = __uint_as_float(rw[e] & 0xFFFF0000u);
+                  p[j * 4 + e] = pack_bf16(__fadd_rn(__uint_as_float(v[j * 8 + e * 2]), r0),
+                                           __fadd_rn(__uint_as_float(v[j * 8 + e * 2 + 1]), r1));
                 }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) p[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
               }
-              uint4* dst = reinterpret_cast<uint4*>(crow);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) dst[j] = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
             } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float x = __uint_as_float(v[j]);
-                if (EPI == EPI_BF16_RES) x = __fadd_rn(x, __bfloat162float(R[row * ldr + col + j]));
-                crow[j] = __float2bfloat16_rn(x);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                if (row < M && col + 2 * j < N) x0 = __fadd_rn(x0, __bfloat162float(R[row * ldr + col + 2 * j]));
+                if (row < M && col + 2 * j + 1 < N) x1 = __fadd_rn(x1, __bfloat162float(R[row * ldr + col + 2 * j + 1]));
+                p[j] = pack_bf16(x0, x1);
               }
             }
           } else {
-            float* crow = reinterpret_cast<float*>(Cv) + row * ldc + col;
-            if (full) {
-              float4* dst = reinterpret_cast<float4*>(crow);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                if (EPI == EPI_F32_ACC) {
-                  const float4 old = dst[j];
-                  o.x = __fadd_rn(old.x, o.x);
-                  o.y = __fadd_rn(old.y, o.y);
-                  o.z = __fadd_rn(old.z, o.z);
-                  o.w = __fadd_rn(old.w, o.w);
-                }
-                dst[j] = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < N; ++j) {
-                float x = __uint_as_float(v[j]);
-                if (EPI == EPI_F32_ACC) x = __fadd_rn(crow[j], x);
-                crow[j] = x;
-              }
-            }
+            for (int j = 0; j < 16; ++j) p[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(st + lane * 128 + (((part * 4 + j) ^ (lane & 7)) << 4)) =
+                make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+          if (part == 1) {
+            emit_slice(slice, col - 32);
+            ++slice;
+          }
+        } else {
+          slice_free();
+          uint8_t* st = stage0 + (slice & 1) * 4096;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          emit_slice(slice, col);
+          ++slice;
         }
       };
       uint32_t va[32], vb[32];
@@ -264,6 +290,8 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every TMA store of this warp has completed
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -283,20 +311,20 @@ struct TmapKey {
 };
 
 CUresult encode_2d(CUtensorMap* out, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t ld_elems, uint32_t box0,
-                   uint32_t box1) {
+                   uint32_t box1, bool fp32 = false) {
   static PFN_encodeTiled fn = get_encode_tiled();
   if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
   cuuint64_t dims[2] = {dim0, dim1};
-  cuuint64_t strides[1] = {ld_elems * 2};
+  cuuint64_t strides[1] = {ld_elems * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  return fn(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M, int N, int K, long ldc, long ldr,
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N, int K, long ldc, long ldr,
            uint32_t* status, int max_ctas, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_tc05_kernel<BN, STAGES, A_MN, B_MN, EPI>;
@@ -310,18 +338,18 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R,
   int grid = tiles < max_ctas ? tiles : max_ctas;
   if (grid < 1) grid = 1;
   const int group_m = 8;
-  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr,
+  kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr,
                                                 group_m, status);
   return (int)cudaGetLastError();
 }
 
 template <int BN, int STAGES, int EPI>
-int launch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, void* C, const void* R, int M, int N,
+int launch_major(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N,
                  int K, long ldc, long ldr, uint32_t* status, int max_ctas, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch<BN, STAGES, false, false, EPI>(ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
-  if (!a_mn && b_mn) return launch<BN, STAGES, false, true, EPI>(ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
-  if (a_mn && b_mn) return launch<BN, STAGES, true, true, EPI>(ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
-  return launch<BN, STAGES, true, false, EPI>(ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
+  if (!a_mn && !b_mn) return launch<BN, STAGES, false, false, EPI>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
+  if (!a_mn && b_mn) return launch<BN, STAGES, false, true, EPI>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
+  if (a_mn && b_mn) return launch<BN, STAGES, true, true, EPI>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
+  return launch<BN, STAGES, true, false, EPI>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s);
 }
 
 }  // namespace
@@ -362,13 +390,18 @@ extern "C" int otb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   r = b_mn ? encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
            : encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  CUtensorMap tc;
+  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, false)
+               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, true);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  if (reinterpret_cast<uintptr_t>(C) & 15) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define OTB_DISPATCH(BN_, ST_)                                                                                      \
   switch (epi) {                                                                                                    \
-    case EPI_BF16: return launch_major<BN_, ST_, EPI_BF16>(a_mn, b_mn, ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
-    case EPI_F32: return launch_major<BN_, ST_, EPI_F32>(a_mn, b_mn, ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s);   \
-    case EPI_F32_ACC: return launch_major<BN_, ST_, EPI_F32_ACC>(a_mn, b_mn, ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
-    case EPI_BF16_RES: return launch_major<BN_, ST_, EPI_BF16_RES>(a_mn, b_mn, ta, tb, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
+    case EPI_BF16: return launch_major<BN_, ST_, EPI_BF16>(a_mn, b_mn, ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
+    case EPI_F32: return launch_major<BN_, ST_, EPI_F32>(a_mn, b_mn, ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s);   \
+    case EPI_F32_ACC: return launch_major<BN_, ST_, EPI_F32_ACC>(a_mn, b_mn, ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
+    case EPI_BF16_RES: return launch_major<BN_, ST_, EPI_BF16_RES>(a_mn, b_mn, ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s); \
     default: return -3;                                                                                             \
   }
   if (BN == 256) {

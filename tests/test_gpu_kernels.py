@@ -146,6 +146,23 @@ def test_gemm_bf16_vs_reference(a_mn, b_mn):
     assert torch.allclose(out, ref, atol=2e-3, rtol=1e-4), (out - ref).abs().max()
     out2 = K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_STORE_F32).cpu()
     assert torch.equal(out, out2)
+    # the other epilogues must agree with the fp32 store: bf16 store, residual add, fp32 accumulate (twice)
+    o16 = K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn).cpu()
+    assert torch.equal(o16, out.bfloat16())
+    R = torch.randn(M, N, generator=g).bfloat16()
+    ores = K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_RESIDUAL, residual=R.to(DEV)).cpu()
+    assert torch.equal(ores, (out + R.float()).bfloat16())
+    acc = torch.full((M, N), 0.5, device=DEV)
+    K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, out=acc, epi=K.EPI_ACC_F32)
+    K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, out=acc, epi=K.EPI_ACC_F32)
+    assert torch.equal(acc.cpu(), (0.5 + out) + out)
+    # a strided output view (weight-gradient slot inside a flat buffer) and a canary around it
+    big = torch.full((M + 2, N + 16), 7.0, device=DEV)
+    view = big[1:M + 1, 8:N + 8]
+    K.gemm(As, Bs, a_mn=a_mn, b_mn=b_mn, out=view, epi=K.EPI_STORE_F32)
+    assert torch.equal(view.cpu(), out)
+    big[1:M + 1, 8:N + 8] = 7.0
+    assert bool((big == 7.0).all())
     assert K.kernel_status(DEV) == 0
 
 
