@@ -1,6 +1,6 @@
 // Persistent, warp-specialised bf16 GEMM for sm_100a:  C[M,N] = op(A) * op(B)^T (+ epilogue)
 //
-//   * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   * operands are staged by TMA (cp.async.bulk.tensor, 128-byte swizzle; each CTA fetches its own tiles)
 //     into a STAGES-deep shared-memory ring,
 //   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) with the
 //     fp32 accumulator in tensor memory, double-buffered so the epilogue of tile i overlaps

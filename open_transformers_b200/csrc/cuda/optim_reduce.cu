@@ -1,7 +1,7 @@
 // Deterministic gradient reduction fused with its neighbours, and the AdamW update fused with the
 // parameter all-gather. Both kernels move their inter-GPU traffic themselves with plain peer
-// loads / stores over NVLink (pointers obtained by CUDA IPC); no NCCL call, no multimem
-// reduction, no TMA multicast.
+// loads / stores over NVLink (pointers obtained by CUDA IPC); no NCCL call and no in-switch
+// reduction: every sum is formed by this kernel in a fixed order.
 //
 //  grad_reduce  (pull reduce-scatter + replica tree + squared-norm partials)
 //     For every element this GPU owns:

@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives used by the
-// kernels in this directory: mbarrier, TMA (cp.async.bulk.tensor, never with
-// cluster multicast), tcgen05 MMA / TMEM allocation / TMEM loads, and the
+// kernels in this directory: mbarrier, TMA (cp.async.bulk.tensor; every CTA loads
+// its own tiles), tcgen05 MMA / TMEM allocation / TMEM loads, and the
 // shared-memory + instruction descriptors that tcgen05.mma consumes.
 //
 // Every wait in here is BOUNDED: a spin that runs out returns false so the
