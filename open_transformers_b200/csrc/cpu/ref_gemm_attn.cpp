@@ -10,7 +10,7 @@
 //     a MODEL of the GPU (equal for exactly-representable sums, otherwise within a few ulp), not
 //     a bit-exact copy; fp32 runs are bit-exact.
 // The attention twin follows csrc/cuda/attention_tc05.cu step by step: 128-key blocks in
-// ascending order, two 64-key halves per row, log2-domain scores, det_exp2_attn, deferred
+// ascending order, four 32-key quarters per row, log2-domain scores, det_exp2_attn, deferred
 // O = fma(O, alpha, PV).
 #include <math.h>
 #include <stdint.h>
@@ -84,7 +84,7 @@ int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, voi
       const int q0 = (qi / 128) * 128;
       const int jmax = qi / 128;
       const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
-      float m_run = -INFINITY, l_half[2] = {0.0f, 0.0f};
+      float m_run = -INFINITY, l_part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       for (int j = jmin; j <= jmax; ++j) {
         float s[128];
         float mx = -INFINITY;
@@ -101,14 +101,14 @@ int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, voi
         const float m_new = fmaxf(m_run, mx * c_log2);
         const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
         const float alpha = det_exp2_attn(m_run + (-m_safe));
-        for (int hf = 0; hf < 2; ++hf) {
-          float lsum2[2] = {0.0f, 0.0f};  // even / odd keys of the half, each an ascending chain
-          for (int e = hf * 64; e < hf * 64 + 64; ++e) {
+        for (int hf = 0; hf < 4; ++hf) {
+          float lsum2[2] = {0.0f, 0.0f};  // even / odd keys of the 32-key quarter, each an ascending chain
+          for (int e = hf * 32; e < hf * 32 + 32; ++e) {
             const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
             lsum2[e & 1] = lsum2[e & 1] + pe;
             p[e] = bf16 ? det_bf2f(det_f2bf(pe)) : pe;
           }
-          l_half[hf] = det_fmaf(l_half[hf], alpha, lsum2[0] + lsum2[1]);
+          l_part[hf] = det_fmaf(l_part[hf], alpha, lsum2[0] + lsum2[1]);
         }
         for (int d = 0; d < D; ++d) pv[d] = 0.0f;
         for (int e = 0; e < 128; ++e) {
@@ -121,7 +121,7 @@ int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, voi
         for (int d = 0; d < D; ++d) o[d] = det_fmaf(o[d], alpha, pv[d]);
         m_run = m_new;
       }
-      const float l_tot = l_half[0] + l_half[1];
+      const float l_tot = ((l_part[0] + l_part[1]) + l_part[2]) + l_part[3];
       for (int d = 0; d < D; ++d) stx(O, qrow * ldo + (long)h * D + d, o[d] / l_tot, bf16);
       lse[((long)b * H + h) * T + qi] = det_fmaf(det_logf(l_tot), 1.44269504088896341f, m_run);
     }

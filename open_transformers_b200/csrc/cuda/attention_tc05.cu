@@ -1,8 +1,8 @@
 // Causal / sliding-window flash attention for sm_100a on tcgen05 tensor cores, GQA-native.
 //
 // Three kernels share one structure (warp 0: TMA producer, warp 1: tcgen05.mma issuer, warps
-// 2..9: two threads per row - one per 64-key half - doing the softmax arithmetic straight out of
-// tensor memory; warp w may touch TMEM lanes 32*(w%4)..+31, so warps w and w+4 share rows):
+// 2..17: four threads per row - one per 32-key quarter - doing the softmax arithmetic straight out of
+// tensor memory; warp w may touch TMEM lanes 32*(w%4)..+31, so warps w, w+4, w+8, w+12 share rows):
 //
 //   attn_fwd    CTA = (batch, query head, 128 query rows); loops over 128-key blocks in ascending
 //               key order:  S = Q K^T (TMEM) -> online softmax -> P (bf16, shared) -> P V (TMEM,
@@ -18,7 +18,8 @@
 // is "key in (query - window, query]" (window = 0: full causal). Scores are used in the log2
 // domain: y = fma(s, c, -m) with c = scale*log2(e), p = det_exp2_attn(y) (shared with the CPU
 // twin), masked scores are -inf. The saved row statistic `lse` is m + log2(l) in that domain.
-// Row sums: each 64-key half is folded in ascending key order, l = l_half0 + l_half1 at the end.
+// Row sums: each 32-key quarter keeps two ascending chains (even / odd keys) that are added per block;
+// the four quarter sums are combined ((l0 + l1) + l2) + l3 at the end.
 //
 // Layouts: q/k come from one [B*T, ld] bf16 buffer (post-RoPE; head h at column h*D, KV head g
 // at column (H+g)*D); v comes from the packed qkv buffer; O is [B*T, H*D]; lse and delta are
@@ -34,10 +35,20 @@ namespace {
 
 constexpr int BQ = 128;   // query rows per tile
 constexpr int BKV = 128;  // keys per block
-constexpr int ATT_THREADS = 320;
-constexpr int SOFTMAX_THREADS = 256;
+constexpr int NSPLIT = 4;                 // threads per row
+constexpr int KPT = 128 / NSPLIT;         // keys per thread and block
+constexpr int SOFTMAX_THREADS = 128 * NSPLIT;
+constexpr int ATT_THREADS = 64 + SOFTMAX_THREADS;
+constexpr int SOFTMAX_WARPS = SOFTMAX_THREADS / 32;
 
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory"); }
+
+// N (16 or 32) consecutive TMEM columns of this thread's lane
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]) {
+  if constexpr (N == 32) tmem_ld_32x32b_x32(taddr, v);
+  else tmem_ld_32x32b_x16(taddr, v);
+}
 
 struct Bars {
   uint64_t b[24];
@@ -45,7 +56,7 @@ struct Bars {
   uint32_t abort_flag;
 };
 struct BarsX : Bars {
-  float xch[2][2][128];  // [parity][half][row] exchange between the two threads of a row
+  float xch[2][NSPLIT][128];  // [parity][part][row] exchange between the threads of a row
 };
 
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -110,8 +121,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     for (int s = 0; s < ST; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); }
-    mbar_init(p_ready, 8);
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], SOFTMAX_WARPS); }
+    mbar_init(p_ready, SOFTMAX_WARPS);
     mbar_init(pv_full, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
@@ -172,9 +183,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       }
     }
   } else {
-    constexpr int DH = D / 2;
+    constexpr int DH = D / NSPLIT;            // output columns per thread
+    constexpr int CW = DH >= 32 ? 32 : 16;    // TMEM columns per load of the PV accumulator
     const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int r = qd * 32 + lane;          // row inside the tile == TMEM lane
     const int qi = q0 + r;                 // query position
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
@@ -185,33 +197,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int j = jmin + i;
-      const int kbase = j * BKV + half * 64;
+      const int kbase = j * BKV + part * KPT;
       const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window);
       ok = ok && mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
       tc_fence_after();
-      const uint32_t tSb = tS + (i & 1) * 128 + half * 64 + lane_off;
-      // pass 1: maximum of the masked raw scores over this thread's 64 keys, then over the row
+      const uint32_t tSb = tS + (i & 1) * 128 + part * KPT + lane_off;
+      // the thread's 32 raw scores stay in registers for both passes
+      uint32_t sv[KPT];
+      if (ok) {
+        tmem_ld_32x32b_x32(tSb, sv);
+        tmem_ld_wait();
+      }
       float mx = -INFINITY;
       if (ok) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tSb + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float sv = __uint_as_float(v[e]);
-            if (need_mask) {
-              const int kj = kbase + c * 32 + e;
-              if (kj > qi || (window > 0 && kj <= qi - window)) sv = -INFINITY;
-            }
-            mx = fmaxf(mx, sv);
+        for (int e = 0; e < KPT; ++e) {
+          float x = __uint_as_float(sv[e]);
+          if (need_mask) {
+            const int kj = kbase + e;
+            if (kj > qi || (window > 0 && kj <= qi - window)) x = -INFINITY;
           }
+          mx = fmaxf(mx, x);
         }
       }
-      bars->xch[i & 1][half][r] = mx;
+      bars->xch[i & 1][part][r] = mx;
       softmax_bar();
-      mx = fmaxf(mx, bars->xch[i & 1][half ^ 1][r]);
+#pragma unroll
+      for (int pp = 0; pp < NSPLIT; ++pp) mx = fmaxf(mx, bars->xch[i & 1][pp][r]);
       const float m_new = fmaxf(m_run, __fmul_rn(mx, c_log2));
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = det_exp2_attn(__fadd_rn(m_run, -m_safe));
@@ -220,48 +232,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
         ok = ok && mbar_wait(pv_full, (i - 1) & 1, abort_flag);
         tc_fence_after();
         if (ok) {
+          const f2 a2 = pack2(alpha_prev, alpha_prev);
 #pragma unroll
-          for (int c = 0; c < DH / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(tPV + lane_off + half * DH + c * 32, v);
+          for (int c = 0; c < DH / CW; ++c) {
+            uint32_t v[CW];
+            tmem_ld_cols<CW>(tPV + lane_off + part * DH + c * CW, v);
             tmem_ld_wait();
-            const f2 a2 = pack2(alpha_prev, alpha_prev);
 #pragma unroll
-            for (int e = 0; e < 32; e += 2)
-              o[c * 16 + (e >> 1)] = fma2(o[c * 16 + (e >> 1)], a2, pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+            for (int e = 0; e < CW; e += 2)
+              o[(c * CW + e) >> 1] = fma2(o[(c * CW + e) >> 1], a2, pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
           }
         }
       }
-      // pass 2: probabilities, half-row sum (even and odd keys as two ascending chains), bf16 P into shared memory
+      // probabilities, quarter-row sum (even and odd keys as two ascending chains), bf16 P into shared memory
       f2 lsum2 = pack2(0.0f, 0.0f);
       if (ok) {
         const f2 c2 = pack2(c_log2, c_log2), nm2 = pack2(-m_safe, -m_safe);
+        uint32_t pk[KPT / 2];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tSb + c * 32, v);
-          tmem_ld_wait();
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), c2, nm2));
-            float p0, p1;
-            unpack2(p2, p0, p1);
-            if (need_mask) {
-              const int kj = kbase + c * 32 + e;
-              if (kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
-              if (kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
-              p2 = pack2(p0, p1);
-            }
-            lsum2 = add2(lsum2, p2);
-            pk[e >> 1] = pack_bf16(p0, p1);
+        for (int e = 0; e < KPT; e += 2) {
+          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nm2));
+          float p0, p1;
+          unpack2(p2, p0, p1);
+          if (need_mask) {
+            const int kj = kbase + e;
+            if (kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
+            if (kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
+            p2 = pack2(p0, p1);
           }
-          uint8_t* base = sP + half * 16384;
-#pragma unroll
-          for (int w = 0; w < 4; ++w)
-            *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
-                make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+          lsum2 = add2(lsum2, p2);
+          pk[e >> 1] = pack_bf16(p0, p1);
         }
+        // keys part*32 .. +31 -> 64-key sub-tile (part >> 1), 16-byte chunks (part & 1) * 4 .. +3 of the row
+        uint8_t* base = sP + (part >> 1) * 16384;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) =
+              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
       }
       float ls0, ls1;
       unpack2(lsum2, ls0, ls1);
@@ -276,31 +283,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     }
     ok = ok && mbar_wait(pv_full, (n - 1) & 1, abort_flag);
     tc_fence_after();
-    bars->xch[n & 1][half][r] = l_run;
+    bars->xch[n & 1][part][r] = l_run;
     softmax_bar();
-    const float l_tot = __fadd_rn(bars->xch[n & 1][0][r], bars->xch[n & 1][1][r]);
+    float l_tot = bars->xch[n & 1][0][r];
+#pragma unroll
+    for (int pp = 1; pp < NSPLIT; ++pp) l_tot = __fadd_rn(l_tot, bars->xch[n & 1][pp][r]);
     if (ok) {
       const bool in_range = qi < T;
-      __nv_bfloat16* orow = O + ((long)b * T + qi) * ldo + (long)h * D + half * DH;
+      __nv_bfloat16* orow = O + ((long)b * T + qi) * ldo + (long)h * D + part * DH;
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tPV + lane_off + half * DH + c * 32, v);
+      for (int c = 0; c < DH / CW; ++c) {
+        uint32_t v[CW];
+        tmem_ld_cols<CW>(tPV + lane_off + part * DH + c * CW, v);
         tmem_ld_wait();
-        uint32_t pk[16];
+        uint32_t pk[CW / 2];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < CW; e += 2) {
           float a0, a1;
-          unpack2(fma2(o[c * 16 + (e >> 1)], pack2(alpha_prev, alpha_prev), pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1]))), a0, a1);
+          unpack2(fma2(o[(c * CW + e) >> 1], pack2(alpha_prev, alpha_prev), pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1]))), a0, a1);
           pk[e >> 1] = pack_bf16(__fdiv_rn(a0, l_tot), __fdiv_rn(a1, l_tot));
         }
         if (in_range) {
 #pragma unroll
-          for (int w = 0; w < 4; ++w)
-            reinterpret_cast<uint4*>(orow + c * 32)[w] = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+          for (int w = 0; w < CW / 8; ++w)
+            reinterpret_cast<uint4*>(orow + c * CW)[w] = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
         }
       }
-      if (in_range && half == 0)
+      if (in_range && part == 0)
         lse_out[((long)b * H + h) * T + qi] = __fmaf_rn(det_logf(l_tot), 1.44269504088896341f, m_run);
     }
   }
@@ -352,8 +361,8 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < ST; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(p_ready, 8); mbar_init(dv_done, 1);
-    mbar_init(ds_ready, 8); mbar_init(dk_done, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, SOFTMAX_WARPS); mbar_init(p_ready, SOFTMAX_WARPS); mbar_init(dv_done, 1);
+    mbar_init(ds_ready, SOFTMAX_WARPS); mbar_init(dk_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -417,9 +426,10 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       }
     }
   } else {
-    constexpr int DH = D / 2;
+    constexpr int DH = D / NSPLIT;
+    constexpr int CW = DH >= 32 ? 32 : 16;
     const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int r = qd * 32 + lane;
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
     bool ok = true;
@@ -434,21 +444,19 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (i > 0) { if (!mbar_wait(dk_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
-      uint32_t dsr[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t vs[32], vd[32];
-        tmem_ld_32x32b_x32(tS + lane_off + half * 64 + c * 32, vs);
-        tmem_ld_32x32b_x32(tDP + lane_off + half * 64 + c * 32, vd);
+      uint32_t dsr[KPT / 2], pk[KPT / 2];
+      {
+        uint32_t vs[KPT], vd[KPT];
+        tmem_ld_32x32b_x32(tS + lane_off + part * KPT, vs);
+        tmem_ld_32x32b_x32(tDP + lane_off + part * KPT, vd);
         tmem_ld_wait();
-        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < KPT; e += 2) {
           f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
           if (need_mask || !row_ok) {
             float p0, p1;
             unpack2(p2, p0, p1);
-            const int kj = k0 + half * 64 + c * 32 + e;
+            const int kj = k0 + part * KPT + e;
             if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
             if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
             p2 = pack2(p0, p1);
@@ -458,27 +466,21 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
           unpack2(p2, p0, p1);
           unpack2(d2, d0, d1);
           pk[e >> 1] = pack_bf16(p0, p1);
-          dsr[c * 16 + (e >> 1)] = pack_bf16(d0, d1);
+          dsr[e >> 1] = pack_bf16(d0, d1);
         }
-        uint8_t* base = sPdS + half * 16384;
-#pragma unroll
-        for (int w = 0; w < 4; ++w)
-          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
-              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
       }
+      uint8_t* base = sPdS + (part >> 1) * 16384;
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(p_ready); mbar_arrive(sdp_empty); }
       if (!mbar_wait(dv_done, i & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint8_t* base = sPdS + half * 16384;
-#pragma unroll
-        for (int w = 0; w < 4; ++w)
-          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
-              make_uint4(dsr[c * 16 + 4 * w], dsr[c * 16 + 4 * w + 1], dsr[c * 16 + 4 * w + 2], dsr[c * 16 + 4 * w + 3]);
-      }
+      for (int w = 0; w < 4; ++w)
+        *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) = make_uint4(dsr[4 * w], dsr[4 * w + 1], dsr[4 * w + 2], dsr[4 * w + 3]);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
@@ -487,19 +489,19 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       tc_fence_after();
       const int kj = k0 + r;  // TMEM lane == key row
       const bool in_range = kj < T;
-      __nv_bfloat16* dkrow = dK + ((long)b * T + kj) * lddk + (long)g * D + half * DH;
-      __nv_bfloat16* dvrow = dV + ((long)b * T + kj) * lddv + (long)g * D + half * DH;
+      __nv_bfloat16* dkrow = dK + ((long)b * T + kj) * lddk + (long)g * D + part * DH;
+      __nv_bfloat16* dvrow = dV + ((long)b * T + kj) * lddv + (long)g * D + part * DH;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
 #pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32((which ? tDK : tDV) + lane_off + half * DH + c * 32, v);
+        for (int c = 0; c < DH / CW; ++c) {
+          uint32_t v[CW];
+          tmem_ld_cols<CW>((which ? tDK : tDV) + lane_off + part * DH + c * CW, v);
           tmem_ld_wait();
           if (in_range) {
-            uint4* dst = reinterpret_cast<uint4*>((which ? dkrow : dvrow) + c * 32);
+            uint4* dst = reinterpret_cast<uint4*>((which ? dkrow : dvrow) + c * CW);
 #pragma unroll
-            for (int w = 0; w < 4; ++w)
+            for (int w = 0; w < CW / 8; ++w)
               dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
                                   pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
                                   pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
@@ -554,7 +556,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(ds_ready, 8); mbar_init(dq_done, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_empty, SOFTMAX_WARPS); mbar_init(ds_ready, SOFTMAX_WARPS); mbar_init(dq_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -612,9 +614,10 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
       }
     }
   } else {
-    constexpr int DH = D / 2;
+    constexpr int DH = D / NSPLIT;
+    constexpr int CW = DH >= 32 ? 32 : 16;
     const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int r = qd * 32 + lane;
     const int qi = q0 + r;
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
@@ -624,25 +627,24 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
     bool ok = true;
     for (int i = 0; i < n && ok; ++i) {
       const int j = jmin + i;
-      const int kbase = j * BKV + half * 64;
+      const int kbase = j * BKV + part * KPT;
       const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window);
       if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (i > 0) { if (!mbar_wait(dq_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t vs[32], vd[32];
-        tmem_ld_32x32b_x32(tS + lane_off + half * 64 + c * 32, vs);
-        tmem_ld_32x32b_x32(tDP + lane_off + half * 64 + c * 32, vd);
+      uint32_t pk[KPT / 2];
+      {
+        uint32_t vs[KPT], vd[KPT];
+        tmem_ld_32x32b_x32(tS + lane_off + part * KPT, vs);
+        tmem_ld_32x32b_x32(tDP + lane_off + part * KPT, vd);
         tmem_ld_wait();
-        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < KPT; e += 2) {
           f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
           if (need_mask || !row_ok) {
             float p0, p1;
             unpack2(p2, p0, p1);
-            const int kj = kbase + c * 32 + e;
+            const int kj = kbase + e;
             if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
             if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
             p2 = pack2(p0, p1);
@@ -652,12 +654,11 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
           unpack2(d2, d0, d1);
           pk[e >> 1] = pack_bf16(d0, d1);
         }
-        uint8_t* base = sDS + half * 16384;
-#pragma unroll
-        for (int w = 0; w < 4; ++w)
-          *reinterpret_cast<uint4*>(base + swz(r, c * 4 + w)) =
-              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
       }
+      uint8_t* base = sDS + (part >> 1) * 16384;
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -665,16 +666,16 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
     }
     if (ok && mbar_wait(dq_done, (n - 1) & 1, abort_flag)) {
       tc_fence_after();
-      __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D + half * DH;
+      __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D + part * DH;
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tDQ + lane_off + half * DH + c * 32, v);
+      for (int c = 0; c < DH / CW; ++c) {
+        uint32_t v[CW];
+        tmem_ld_cols<CW>(tDQ + lane_off + part * DH + c * CW, v);
         tmem_ld_wait();
         if (row_ok) {
-          uint4* dst = reinterpret_cast<uint4*>(dqrow + c * 32);
+          uint4* dst = reinterpret_cast<uint4*>(dqrow + c * CW);
 #pragma unroll
-          for (int w = 0; w < 4; ++w)
+          for (int w = 0; w < CW / 8; ++w)
             dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
                                 pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
                                 pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
@@ -725,7 +726,7 @@ CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int D> constexpr int attn_smem_bytes() { return (1 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 512 + 2048; }
+template <int D> constexpr int attn_smem_bytes() { return (1 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 512 + 4096; }
 template <int D> constexpr int attn_bwd_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 256; }
 
 template <typename K>

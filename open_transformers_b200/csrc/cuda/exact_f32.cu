@@ -86,7 +86,7 @@ attn_f32_fwd_kernel(const float* __restrict__ qk, long ldqk, const float* __rest
   float o[4] = {0.f, 0.f, 0.f, 0.f};
   const int q0 = (qi / 128) * 128, jmax = qi / 128;
   const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
-  float m_run = -INFINITY, l_half[2] = {0.f, 0.f};
+  float m_run = -INFINITY, l_part = 0.f;  // lanes 0..3 each own one 32-key quarter
   for (int j = jmin; j <= jmax; ++j) {
     float mx = -INFINITY;
     float s[4];
@@ -110,10 +110,10 @@ attn_f32_fwd_kernel(const float* __restrict__ qk, long ldqk, const float* __rest
       sp[w][lane + 32 * u] = (s[u] == -INFINITY) ? 0.0f : det_exp2_attn(__fmaf_rn(s[u], c_log2, -m_safe));
     }
     __syncwarp();
-    if (lane < 2) {  // the two half-row sums: even and odd keys are ascending chains, then added
+    if (lane < 4) {  // the four quarter-row sums: even and odd keys are ascending chains, then added
       float le = 0.0f, lo = 0.0f;
-      for (int e = lane * 64; e < lane * 64 + 64; e += 2) { le = __fadd_rn(le, sp[w][e]); lo = __fadd_rn(lo, sp[w][e + 1]); }
-      l_half[lane] = __fmaf_rn(l_half[lane], alpha, __fadd_rn(le, lo));
+      for (int e = lane * 32; e < lane * 32 + 32; e += 2) { le = __fadd_rn(le, sp[w][e]); lo = __fadd_rn(lo, sp[w][e + 1]); }
+      l_part = __fmaf_rn(l_part, alpha, __fadd_rn(le, lo));
     }
     float pv[4] = {0.f, 0.f, 0.f, 0.f};
     for (int e = 0; e < 128; ++e) {
@@ -133,8 +133,9 @@ attn_f32_fwd_kernel(const float* __restrict__ qk, long ldqk, const float* __rest
     m_run = m_new;
     __syncwarp();
   }
-  const float l0 = __shfl_sync(0xffffffffu, l_half[0], 0), l1 = __shfl_sync(0xffffffffu, l_half[1], 1);
-  const float l_tot = __fadd_rn(l0, l1);
+  const float l0 = __shfl_sync(0xffffffffu, l_part, 0), l1 = __shfl_sync(0xffffffffu, l_part, 1);
+  const float l2 = __shfl_sync(0xffffffffu, l_part, 2), l3 = __shfl_sync(0xffffffffu, l_part, 3);
+  const float l_tot = __fadd_rn(__fadd_rn(__fadd_rn(l0, l1), l2), l3);
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int d = lane + 32 * u;
