@@ -35,6 +35,15 @@ def test_fp32_gpu_matches_cpu_hashes():
     assert _run(cfg, "cuda", td="tree")[-1][2] == _run(cfg, "cpu", td="tree")[-1][2]
 
 
+def test_bf16_gpu_matches_cpu_hashes():
+    """bf16 tensor-core run on the GPU == bf16 replay on the CPU (tensor-core accumulation model), hash for hash."""
+    cfg = load_config("open1b_b200", ["model.n_layers=2", "model.d_model=256", "model.n_heads=2", "model.n_kv_heads=1", "model.ffn_intermediate=512",
+                                      "model.vocab_size=1024", "train.seq_len=128", "data.seq_len=128", "run.virtual_dp_size=2", "run.dp_shard_size=2"])
+    cpu = _run(cfg, "cpu", T=128, vocab=1024, td="tree")
+    gpu = _run(cfg, "cuda", T=128, vocab=1024, td="tree")
+    assert [h for _, _, h in cpu] == [h for _, _, h in gpu], (cpu, gpu)
+
+
 def test_bf16_gpu_finite_and_repeatable():
     cfg = load_config("open1b_b200", ["model.n_layers=2", "model.vocab_size=4096", "train.seq_len=256", "data.seq_len=256",
                                       "run.virtual_dp_size=2", "run.dp_shard_size=2"])
