@@ -21,6 +21,10 @@
 //   dgrad    dx = dy W          A K-major , B MN-major
 //   wgrad    dW = dy^T x        A MN-major, B MN-major
 //
+// The same kernel runs the W8A8 forward of the quantisation-aware layers (I8 = true): int8 operands, both K-major,
+// tcgen05.mma kind::i8 (K = 32 per instruction, 128 int8 = one swizzle row per k-block), exact int32 accumulation
+// in tensor memory, and an epilogue that dequantises  float(acc) * (sa[0] * sb[col])  before the usual stores.
+//
 // Role of this file in the reference's terms: the `repop.nn.linear` / `mmacc` entry points
 // (reference docs/MODEL_OP_DTYPE_TRACE.md:82,100).
 #include "tc05.cuh"
@@ -31,8 +35,8 @@ using namespace tc05;
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
+constexpr int BK_BYTES = 128;  // one 128-byte swizzle row per k-block: 64 bf16 or 128 int8
+constexpr int UMMA_K_BYTES = 32;  // one MMA consumes 32 bytes of K: 16 bf16 or 32 int8
 constexpr int NUM_THREADS = 192;  // warp0: TMA, warp1: MMA, warps 2..5: epilogue
 
 enum Epi : int {
@@ -44,8 +48,8 @@ enum Epi : int {
 
 template <int BN, int STAGES>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int A_BYTES = BM * BK_BYTES;
+  static constexpr int B_BYTES = BN * BK_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;       // 4 warps x 2 buffers x [32 rows][128 B]
   static constexpr int EPI_BYTES = 4 * 2 * 4096;
@@ -53,12 +57,14 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv,
                  const __nv_bfloat16* __restrict__ R, int M, int N, int K, long ldc, long ldr, int group_m,
-                 uint32_t* __restrict__ status) {
+                 const float* __restrict__ scale_a, const float* __restrict__ scale_b, uint32_t* __restrict__ status) {
+  static_assert(!I8 || (!A_MN && !B_MN), "the int8 path takes K-major operands only");
+  constexpr int BK = I8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per k-block
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -146,7 +152,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = I8 ? make_idesc(BM, BN, 0, 0, 2, 1) : make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
@@ -163,10 +169,11 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          for (int kk = 0; kk < BK_BYTES / UMMA_K_BYTES; ++kk) {
             const uint64_t ad = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024) : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024) : make_smem_desc(sb + kk * 32, 16, 1024);
-            mma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+            if (I8) mma_i8_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+            else mma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
           }
           mma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs have read it
         }
@@ -221,8 +228,17 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
       };
       int slice = 0;
-      auto store_chunk = [&](const uint32_t (&v)[32], int c) {
+      const float sa0 = I8 ? scale_a[0] : 0.0f;
+      auto store_chunk = [&](uint32_t (&v)[32], int c) {
         const int col = col0 + c;
+        if (I8) {
+          // dequantise: the int32 sum is exact; float(acc) rounds once, then one multiply by sa * sb[col]
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float sb = col + j < N ? __ldg(scale_b + col + j) : 0.0f;
+            v[j] = __float_as_uint(__fmul_rn(__int2float_rn((int)v[j]), __fmul_rn(sa0, sb)));
+          }
+        }
         if (OUT_BF16) {
           const int part = (c >> 5) & 1;  // which 64-byte half of the 128-byte staging row
           if (part == 0) slice_free();
@@ -310,24 +326,27 @@ struct TmapKey {
   uint32_t b0, b1;
 };
 
+// elem_bytes: 2 bf16, 4 fp32, 1 int8 (moved as bytes)
 CUresult encode_2d(CUtensorMap* out, const void* ptr, uint64_t dim0, uint64_t dim1, uint64_t ld_elems, uint32_t box0,
-                   uint32_t box1, bool fp32 = false) {
+                   uint32_t box1, int elem_bytes = 2) {
   static PFN_encodeTiled fn = get_encode_tiled();
   if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
   cuuint64_t dims[2] = {dim0, dim1};
-  cuuint64_t strides[1] = {ld_elems * (fp32 ? 4 : 2)};
+  cuuint64_t strides[1] = {ld_elems * (uint64_t)elem_bytes};
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
-  return fn(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8 = false>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N, int K, long ldc, long ldr,
-           uint32_t* status, int max_ctas, cudaStream_t stream) {
+           uint32_t* status, int max_ctas, cudaStream_t stream, const float* scale_a = nullptr, const float* scale_b = nullptr) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_tc05_kernel<BN, STAGES, A_MN, B_MN, EPI>;
+  auto kern = gemm_tc05_kernel<BN, STAGES, A_MN, B_MN, EPI, I8>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -339,7 +358,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
   if (grid < 1) grid = 1;
   const int group_m = 8;
   kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr,
-                                                group_m, status);
+                                                group_m, scale_a, scale_b, status);
   return (int)cudaGetLastError();
 }
 
@@ -384,6 +403,7 @@ extern "C" int otb_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   CUtensorMap ta, tb;
   CUresult r;
+  constexpr int BK = BK_BYTES / 2;
   r = a_mn ? encode_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK)
            : encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
@@ -391,8 +411,8 @@ extern "C" int otb_gemm_bf16(const void* A, const void* B, void* C, const void* 
            : encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
   CUtensorMap tc;
-  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, false)
-               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, true);
+  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, 2)
+               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, 4);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
   if (reinterpret_cast<uintptr_t>(C) & 15) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -410,4 +430,45 @@ extern "C" int otb_gemm_bf16(const void* A, const void* B, void* C, const void* 
     OTB_DISPATCH(128, 6)
   }
 #undef OTB_DISPATCH
+}
+
+// W8A8 forward of a quantised linear layer:  C[M,N] = dequant( A_q[M,K] * B_q[N,K]^T ),  int8 operands (K-major,
+// leading dimensions multiples of 16), exact int32 accumulation on the tensor cores, then
+//   C = float(acc) * (scale_a[0] * scale_b[n])        (+ bf16 residual R for epi 3)
+// scale_a: one device float (per-tensor activation step); scale_b: N device floats (per-channel weight step).
+// epi: 0 bf16 store, 1 fp32 store, 3 bf16 store with residual. Never allocates.
+extern "C" int otb_gemm_i8(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long lda, long ldb,
+                           long ldc, long ldr, const float* scale_a, const float* scale_b, int epi, uint32_t* status,
+                           int max_ctas, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 15) || (ldb & 15) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return -2;
+  if (epi != EPI_BF16 && epi != EPI_F32 && epi != EPI_BF16_RES) return -3;
+  const bool bf16_out = epi != EPI_F32;
+  if ((bf16_out && (ldc & 7)) || (!bf16_out && (ldc & 3)) || (epi == EPI_BF16_RES && (ldr & 7))) return -2;
+  if (!scale_a || !scale_b) return -2;
+  if (max_ctas <= 0) max_ctas = otb_sm_count();
+  const int BN = N > 128 ? 256 : 128;
+  CUtensorMap ta, tb, tc;
+  CUresult r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK_BYTES, BM, 1);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK_BYTES, (uint32_t)BN, 1);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, 2)
+               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, 4);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define OTB_I8(BN_, ST_, EPI_) \
+  return launch<BN_, ST_, false, false, EPI_, true>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, max_ctas, s, scale_a, scale_b);
+  if (BN == 256) {
+    if (epi == EPI_BF16) { OTB_I8(256, 4, EPI_BF16) }
+    if (epi == EPI_F32) { OTB_I8(256, 4, EPI_F32) }
+    OTB_I8(256, 4, EPI_BF16_RES)
+  } else {
+    if (epi == EPI_BF16) { OTB_I8(128, 6, EPI_BF16) }
+    if (epi == EPI_F32) { OTB_I8(128, 6, EPI_F32) }
+    OTB_I8(128, 6, EPI_BF16_RES)
+  }
+#undef OTB_I8
 }

@@ -30,3 +30,9 @@ def init_weights(model: nn.Module, seed: int, std: float | None = None) -> None:
                 p.fill_(1.0)
             else:
                 p.zero_()
+        # the learned int8 step sizes are 1-D (zeroed above): derive them from the FINAL weights, last
+        # (reference src/pretrain/model/init.py:150-199)
+        from .modules.core import QuantLinear
+        for m in model.modules():
+            if isinstance(m, QuantLinear) and m.method == "lsq":
+                m.weight_scale.copy_(m.lsq_optimal_scale(m.weight.detach().float()))

@@ -32,9 +32,9 @@ class TransformerBlock(nn.Module):
         self.attn = ATTENTION.get(cfg.modules.attention)(
             cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, layer_idx=layer_idx, n_layers=cfg.n_layers,
             swa_window=cfg.swa_window, swa_full_every=cfg.swa_full_every, qk_norm=cfg.qk_norm,
-            qk_norm_gain=cfg.qk_norm_gain, eps=cfg.rms_norm_eps, attn_int8_pv=cfg.attn_int8_pv)
+            qk_norm_gain=cfg.qk_norm_gain, eps=cfg.rms_norm_eps, attn_int8_pv=cfg.attn_int8_pv, qat=cfg.qat)
         self.norm2 = norm(cfg.d_model, eps=cfg.rms_norm_eps)
-        self.ffn = FFN.get(cfg.modules.ffn)(cfg.d_model, cfg.ffn_intermediate)
+        self.ffn = FFN.get(cfg.modules.ffn)(cfg.d_model, cfg.ffn_intermediate, qat=cfg.qat, layer_idx=layer_idx)
 
     def forward(self, x, cos, sin):
         x = self.attn(self.norm1(x), cos, sin, residual=x)
@@ -83,10 +83,6 @@ class Llama3(nn.Module):
 
 
 def build_model(cfg: ModelConfig, device=None) -> Llama3:
-    if cfg.qat.enabled or cfg.attn_int8_pv:
-        # int8 LSQ QAT and int8-PV attention are selected by the recipe flags; the bf16 tensor-core
-        # path below is the one built so far, so the flags are recorded but the layers run in bf16.
-        pass
     model = Llama3(cfg)
     if device is not None:
         model = model.to(device)

@@ -36,6 +36,91 @@ class Linear(nn.Module, ParamMixin):
         return A.linear(x, self.weight, w, self._slot(), residual)
 
 
+class QuantLinear(Linear):
+    """int8 quantisation-aware linear layer (W8A8). ``method``:
+
+    * ``lsq``: learned per-output-channel step size ``weight_scale`` [out] (a parameter the optimizer sees; it is
+      re-derived from the initial weights by ``init_weights`` and optionally re-pinned every N steps);
+    * ``absmax``: step = max|w| / qmax per channel (``per_channel_w``) or per tensor, recomputed from the weights.
+
+    ``qat_active`` is the warm-start switch: while false the layer is bit-identical to a plain ``Linear`` on the
+    same weights; it is a pure function of (step, config) set by ``set_qat_active`` at the top of every step and
+    never enters a checkpoint. (reference src/pretrain/model/modules/_linear.py:31-65,
+    src/pretrain/model/modules/qat_warmstart.py:40-59)"""
+
+    qat_active: bool = True
+
+    def __init__(self, in_features, out_features, *, method="lsq", weight_bits=8, act_bits=8, per_channel_w=True):
+        super().__init__(in_features, out_features)
+        self.method, self.weight_bits, self.act_bits, self.per_channel_w = method, weight_bits, act_bits, per_channel_w
+        self.qmax_w, self.qmax_a = K.qmax_for_bits(weight_bits), K.qmax_for_bits(act_bits)
+        if method == "lsq":
+            self.weight_scale = nn.Parameter(torch.ones(out_features))
+        self._qcache: dict = {}
+
+    def lsq_optimal_scale(self, w: torch.Tensor) -> torch.Tensor:
+        """2 mean|w_row| / sqrt(qmax), floored at 1e-6 (Esser et al.; reference src/pretrain/model/init.py:150-199)."""
+        return K.row_stat(w.contiguous(), "mean_abs", 2.0 / (self.qmax_w ** 0.5), 1e-6)
+
+    def _step(self, w):
+        if self.method == "lsq":
+            s = self._cw("weight_scale")
+            s = self.weight_scale if s is None else s
+            return s.detach().float().contiguous()
+        if self.per_channel_w:
+            return K.row_stat(w, "absmax", 1.0 / self.qmax_w, 1e-12)
+        return (K.absmax(w) * (1.0 / self.qmax_w)).clamp_min(1e-12).expand(w.shape[0]).contiguous()
+
+    def forward(self, x, residual=None):
+        if not self.qat_active:
+            return super().forward(x, residual)
+        w = self._cw()
+        if w is None:
+            w = self.weight if x.dtype == self.weight.dtype else self.weight.to(x.dtype)
+        w = w.detach()
+        lsq = self.method == "lsq"
+        return A.quant_linear(x, self.weight, w, self._slot(), self.weight_scale if lsq else None, self._step(w),
+                              self._slot("weight_scale") if lsq else None, residual, self.qmax_w, self.qmax_a, lsq, self._qcache)
+
+
+def build_linear(in_features: int, out_features: int, qat=None, layer_idx: int = 0) -> Linear:
+    """Plain or quantisation-aware linear layer, by the ``qat`` section of the model config; the first
+    ``exempt_first_n_blocks`` blocks stay unquantised (reference src/pretrain/model/modules/_linear.py:31-65)."""
+    if qat is None or not qat.enabled or layer_idx < qat.exempt_first_n_blocks:
+        return Linear(in_features, out_features)
+    return QuantLinear(in_features, out_features, method=qat.method, weight_bits=qat.weight_bits, act_bits=qat.act_bits,
+                       per_channel_w=qat.per_channel_w)
+
+
+def set_qat_active(module: nn.Module, active: bool) -> int:
+    """Flip the warm-start switch of every quantised layer under ``module``; returns how many were touched."""
+    n = 0
+    for m in module.modules():
+        if isinstance(m, QuantLinear):
+            m.qat_active = bool(active)
+            n += 1
+    return n
+
+
+def refresh_lsq_weight_scales(module: nn.Module) -> int:
+    """Re-pin every learned step size to the LSQ-optimal value of the CURRENT compute weights, writing both the
+    fp32 parameter and its compute copy (reference repop.qat.lsq.refresh_lsq_weight_scales, called from
+    src/pretrain/train/loop.py:1069-1084)."""
+    n = 0
+    with torch.no_grad():
+        for m in module.modules():
+            if isinstance(m, QuantLinear) and m.method == "lsq":
+                w = m._cw()
+                w = m.weight if w is None else w
+                s = m.lsq_optimal_scale(w.detach())
+                m.weight_scale.copy_(s)
+                cs = m._cw("weight_scale")
+                if cs is not None and cs.data_ptr() != m.weight_scale.data_ptr():
+                    cs.copy_(s)
+                n += 1
+    return n
+
+
 @NORM.register("rmsnorm_repop")
 class RMSNorm(nn.Module, ParamMixin):
     """y = x * rsqrt(mean(x^2) + eps) * weight, fp32 inside; ``gain=False`` drops the weight."""
@@ -118,17 +203,17 @@ class _GQABase(nn.Module, ParamMixin):
     qk_norm_default = True
 
     def __init__(self, d_model, n_heads, n_kv_heads, head_dim, *, layer_idx=0, n_layers=1, swa_window=0,
-                 swa_full_every=1, qk_norm=None, qk_norm_gain=True, eps=1e-5, attn_int8_pv=False):
+                 swa_full_every=1, qk_norm=None, qk_norm_gain=True, eps=1e-5, attn_int8_pv=False, qat=None):
         super().__init__()
         self.d_model, self.n_heads, self.n_kv_heads, self.head_dim = d_model, n_heads, n_kv_heads, head_dim
         self.eps = eps
         self.attn_int8_pv = attn_int8_pv
         full = (layer_idx % swa_full_every == swa_full_every - 1) or (layer_idx == n_layers - 1)
         self.window = 0 if (full or swa_window == 0) else swa_window
-        self.wq = Linear(d_model, n_heads * head_dim)
-        self.wk = Linear(d_model, n_kv_heads * head_dim)
-        self.wv = Linear(d_model, n_kv_heads * head_dim)
-        self.wo = Linear(n_heads * head_dim, d_model)
+        self.wq = build_linear(d_model, n_heads * head_dim, qat, layer_idx)
+        self.wk = build_linear(d_model, n_kv_heads * head_dim, qat, layer_idx)
+        self.wv = build_linear(d_model, n_kv_heads * head_dim, qat, layer_idx)
+        self.wo = build_linear(n_heads * head_dim, d_model, qat, layer_idx)
         self.qk_norm = self.qk_norm_default if qk_norm is None else qk_norm
         self.qk_norm_gain = bool(self.qk_norm and qk_norm_gain)
         if self.qk_norm_gain:
@@ -136,6 +221,8 @@ class _GQABase(nn.Module, ParamMixin):
             self.k_norm = RMSNorm(head_dim, eps)
 
     def _qkv(self, x):
+        if isinstance(self.wq, QuantLinear) and self.wq.qat_active:
+            return torch.cat([self.wq(x), self.wk(x), self.wv(x)], -1)
         fused = getattr(self, "_fused_qkv", None)
         if fused is not None:  # (master view, compute view, slot) spanning wq|wk|wv in the flat buffers
             return A.linear(x, fused[0], fused[1], fused[2])
@@ -175,10 +262,10 @@ class GQAPlain(_GQABase):
 class SwiGLU(nn.Module):
     """down( silu(gate) * up ) with gate and up produced by one GEMM (rows [0,F) = gate, [F,2F) = up)."""
 
-    def __init__(self, d_model: int, intermediate: int):
+    def __init__(self, d_model: int, intermediate: int, qat=None, layer_idx: int = 0):
         super().__init__()
-        self.w_gate_up = Linear(d_model, 2 * intermediate)
-        self.w_down = Linear(intermediate, d_model)
+        self.w_gate_up = build_linear(d_model, 2 * intermediate, qat, layer_idx)
+        self.w_down = build_linear(intermediate, d_model, qat, layer_idx)
 
     def forward(self, x, residual=None):
         return self.w_down(A.swiglu(self.w_gate_up(x)), residual)

@@ -8,6 +8,8 @@ tests and the audit replay.
 """
 from __future__ import annotations
 
+import math
+
 import torch
 from torch.autograd import Function
 
@@ -213,3 +215,64 @@ class FusedCEZLossFn(Function):
 def fused_ce_z_loss(logits, labels, z_coeff: float, grad_scale: float = 1.0):
     ce, z = FusedCEZLossFn.apply(logits, labels, float(z_coeff), float(grad_scale))
     return ce, z
+
+
+class QuantLinearFn(Function):
+    """W8A8 quantisation-aware linear layer: activations quantised per tensor, weights per output channel, the
+    product taken exactly in int32 on the int8 tensor cores, one fp32 dequantisation, straight-through backward.
+    ``step`` is the per-channel step size (learned for ``lsq``; derived from the weights for ``absmax``, in which
+    case ``learn_step`` is false and no step gradient is produced).
+    (reference roles: repop.qat.lsq.LSQQuantizedLinear / repop.qat.QuantizedLinear built by
+    src/pretrain/model/modules/_linear.py:31-65)"""
+
+    @staticmethod
+    def forward(ctx, x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache):
+        x2 = _flat2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        xq, sa = K.quant_act(x2, qmax_a)
+        key = (K.weight_epoch, x2.dtype)
+        if cache is not None and K.weight_epoch is not None and cache.get("key") == key:
+            wq, w_hat = cache["wq"], cache["w_hat"]
+        else:
+            wq, w_hat = K.quant_weight(w, step, qmax_w, x2.dtype)
+            if cache is not None and K.weight_epoch is not None:
+                cache.update(key=key, wq=wq, w_hat=w_hat)
+        y = K.gemm_i8(xq, wq, sa, step, x2.dtype, _flat2d(residual) if residual is not None else None)
+        ctx.save_for_backward(xq, sa, w_hat, w, step)
+        ctx.slot_w, ctx.slot_s = slot_w, slot_s
+        ctx.has_res = residual is not None
+        ctx.in_shape = x.shape
+        ctx.cfg = (qmax_w, learn_step, master_w.dtype, None if master_s is None else master_s.dtype)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, sa, w_hat, w, step = ctx.saved_tensors
+        qmax_w, learn_step, w_dtype, s_dtype = ctx.cfg
+        dy2 = _flat2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = K.gemm(dy2, w_hat, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        # dL/dw_hat = dy^T x_hat with x_hat = xq * sa: the integers are exact in bf16, the step is applied afterwards
+        G = K.gemm(dy2, K.i8_widen(xq, dy2.dtype), a_mn=True, b_mn=True, epi=K.EPI_STORE_F32)
+        N, Kd = w.shape
+        gs = 1.0 / math.sqrt(float(Kd) * float(qmax_w))
+        use_slot = ctx.slot_w is not None and ctx.slot_w.buf is not None
+        dW = ctx.slot_w.buf if use_slot else torch.zeros((N, Kd), dtype=torch.float32, device=w.device)
+        ds = None
+        if learn_step:
+            s_slot = ctx.slot_s is not None and ctx.slot_s.buf is not None
+            ds = ctx.slot_s.buf if s_slot else torch.zeros(N, dtype=torch.float32, device=w.device)
+        # a fixed (absmax) step never clips, so its mask bound is one grid point wider than the grid
+        K.lsq_bwd_(G, w, step, sa, qmax_w if learn_step else qmax_w + 1, gs, dW, ds)
+        gw = None if use_slot else dW.to(w_dtype)
+        gsm = None
+        if learn_step and not (ctx.slot_s is not None and ctx.slot_s.buf is not None):
+            gsm = ds.to(s_dtype)
+        return dx, gw, None, None, gsm, None, None, (dy if ctx.has_res else None), None, None, None, None
+
+
+def quant_linear(x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache=None):
+    return QuantLinearFn.apply(x, master_w, master_w if w is None else w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a,
+                               learn_step, cache)

@@ -256,3 +256,118 @@ def trunc_normal_(out: torch.Tensor, std: float, seed: int, offset: int) -> None
     """Fill a CPU fp32 tensor from the Philox stream (element i <- stream word offset+i)."""
     assert out.device.type == "cpu" and out.dtype == torch.float32 and out.is_contiguous()
     cpu_lib().otb_cpu_trunc_normal(P(out), L(out.numel()), F(std), ctypes.c_uint64(seed), ctypes.c_uint64(offset))
+
+
+# ------------------------------------------------------------------------ int8 QAT (W8A8)
+def qmax_for_bits(bits: int) -> int:
+    """Largest magnitude of the symmetric signed grid: 127 for 8 bits (reference repop.qat.functional._qmax_for_bits,
+    used at src/pretrain/model/init.py:168)."""
+    if not 2 <= bits <= 8:
+        raise ValueError("quantisation width must be 2..8 bits, got %d" % bits)
+    return (1 << (bits - 1)) - 1
+
+
+weight_epoch: int | None = None  # set (and bumped at every weight change) by the training engine; None = never cache
+
+
+def absmax(x: torch.Tensor) -> torch.Tensor:
+    """max |x| as a 1-element fp32 tensor (order-free, identical on every backend)."""
+    x = x.reshape(-1)
+    assert x.is_contiguous()
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    if x.is_cuda:
+        lib = cuda_lib()
+        scratch = torch.empty(lib.otb_absmax_scratch_floats(), dtype=torch.float32, device=x.device)
+        check(lib.otb_absmax(P(x), L(x.numel()), I(is_bf16(x)), P(scratch), P(out), stream_ptr()), "absmax")
+    else:
+        check(cpu_lib().otb_cpu_absmax(P(x), L(x.numel()), I(is_bf16(x)), P(out)), "absmax")
+    return out
+
+
+def quant_act(x: torch.Tensor, qmax: int):
+    """Per-tensor symmetric quantisation: step = max|x| / qmax, q = clamp(rint(x / step)). Returns (q int8, step[1])."""
+    assert x.is_contiguous()
+    am = absmax(x)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    step = torch.empty(1, dtype=torch.float32, device=x.device)
+    if x.is_cuda:
+        check(cuda_lib().otb_quant_act(P(x), L(x.numel()), I(is_bf16(x)), P(am), I(qmax), P(q), P(step), stream_ptr()), "quant_act")
+    else:
+        check(cpu_lib().otb_cpu_quant_act(P(x), L(x.numel()), I(is_bf16(x)), P(am), I(qmax), P(q), P(step)), "quant_act")
+    return q, step
+
+
+def quant_weight(w: torch.Tensor, s: torch.Tensor, qmax: int, hat_dtype: torch.dtype | None = None):
+    """Per-output-channel quantisation of ``w`` [N,K] by the step sizes ``s`` [N] (fp32): q = clamp(rint(w / s)).
+    Returns (q int8 [N,K], w_hat = q * s in ``hat_dtype`` or None)."""
+    N, Kd = w.shape
+    assert w.is_contiguous() and s.dtype == torch.float32 and s.numel() == N and s.is_contiguous()
+    q = torch.empty((N, Kd), dtype=torch.int8, device=w.device)
+    hat = torch.empty((N, Kd), dtype=hat_dtype, device=w.device) if hat_dtype is not None else None
+    hd = 0 if hat is None else is_bf16(hat)
+    if w.is_cuda:
+        check(cuda_lib().otb_quant_weight(P(w), P(s), L(N), I(Kd), I(is_bf16(w)), I(qmax), P(q), P(hat), I(hd), stream_ptr()), "quant_weight")
+    else:
+        check(cpu_lib().otb_cpu_quant_weight(P(w), P(s), L(N), I(Kd), I(is_bf16(w)), I(qmax), P(q), P(hat), I(hd)), "quant_weight")
+    return q, hat
+
+
+def gemm_i8(aq: torch.Tensor, bq: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor, out_dtype: torch.dtype,
+            residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``C = float(A_q B_q^T) * (sa * sb[n]) (+ residual)``: int8 [M,K] x int8 [N,K], exact int32 accumulation
+    (tcgen05 kind::i8 on the GPU), one rounding at the dequantisation."""
+    M, Kd = aq.shape
+    N, Kb = bq.shape
+    assert Kd == Kb and aq.dtype == torch.int8 and bq.dtype == torch.int8
+    assert sa.dtype == torch.float32 and sb.dtype == torch.float32 and sb.numel() == N
+    out = torch.empty((M, N), dtype=out_dtype, device=aq.device)
+    bf = is_bf16(out)
+    epi = EPI_RESIDUAL if residual is not None else (EPI_STORE if bf else EPI_STORE_F32)
+    if residual is not None:
+        assert residual.dtype == out_dtype and tuple(residual.shape) == (M, N)
+    ldr = _ld(residual) if residual is not None else 0
+    if aq.is_cuda:
+        if residual is not None and not bf:
+            raise NotImplementedError("fp32 residual epilogue of the int8 GEMM")
+        check(cuda_lib().otb_gemm_i8(P(aq), P(bq), P(out), P(residual), I(M), I(N), I(Kd), L(_ld(aq)), L(_ld(bq)), L(_ld(out)), L(ldr),
+                                     P(sa), P(sb), I(epi), P(_status(aq.device)), I(0), stream_ptr()), "gemm_i8")
+    else:
+        check(cpu_lib().otb_cpu_gemm_i8(P(aq), P(bq), P(out), P(residual), I(M), I(N), I(Kd), L(_ld(aq)), L(_ld(bq)), L(_ld(out)), L(ldr),
+                                        P(sa), P(sb), I(3 if residual is not None else 0), I(bf)), "gemm_i8")
+    return out
+
+
+def lsq_bwd_(G: torch.Tensor, w: torch.Tensor, s: torch.Tensor, ga: torch.Tensor | None, qmax: int, gs: float,
+             dW: torch.Tensor, ds: torch.Tensor | None) -> None:
+    """Straight-through backward of the learned step size, accumulating into ``dW`` [N,K] and ``ds`` [N] (fp32):
+    ``dW += inside ? G*ga : 0``, ``ds += gs * sum_k G*ga * (inside ? rint(t)-t : sign(t) qmax)`` with t = w/s."""
+    N, Kd = w.shape
+    assert G.dtype == torch.float32 and G.is_contiguous() and dW.dtype == torch.float32 and dW.is_contiguous()
+    learn = ds is not None
+    if w.is_cuda:
+        check(cuda_lib().otb_lsq_bwd(P(G), P(w), P(s), P(ga), L(N), I(Kd), I(is_bf16(w)), I(qmax), F(gs), P(dW), P(ds), I(learn), stream_ptr()), "lsq_bwd")
+    else:
+        check(cpu_lib().otb_cpu_lsq_bwd(P(G), P(w), P(s), P(ga), L(N), I(Kd), I(is_bf16(w)), I(qmax), F(gs), P(dW), P(ds), I(learn)), "lsq_bwd")
+
+
+def row_stat(w: torch.Tensor, mode: str, c: float, floor: float) -> torch.Tensor:
+    """Per-row statistic of ``w`` [N,K] as fp32 [N]: ``mean_abs``: max(c * mean_k|w|, floor); ``absmax``: max(c * max_k|w|, floor)."""
+    N, Kd = w.shape
+    assert w.is_contiguous()
+    s = torch.empty(N, dtype=torch.float32, device=w.device)
+    m = {"mean_abs": 0, "absmax": 1}[mode]
+    if w.is_cuda:
+        check(cuda_lib().otb_row_stat(P(w), L(N), I(Kd), I(is_bf16(w)), I(m), F(c), F(floor), P(s), stream_ptr()), "row_stat")
+    else:
+        check(cpu_lib().otb_cpu_row_stat(P(w), L(N), I(Kd), I(is_bf16(w)), I(m), F(c), F(floor), P(s)), "row_stat")
+    return s
+
+
+def i8_widen(q: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty(q.shape, dtype=dtype, device=q.device)
+    assert q.is_contiguous() and q.dtype == torch.int8
+    if q.is_cuda:
+        check(cuda_lib().otb_i8_widen(P(q), P(out), L(q.numel()), I(is_bf16(out)), stream_ptr()), "i8_widen")
+    else:
+        check(cpu_lib().otb_cpu_i8_widen(P(q), P(out), L(q.numel()), I(is_bf16(out))), "i8_widen")
+    return out

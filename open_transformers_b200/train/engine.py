@@ -38,6 +38,8 @@ import torch.distributed as dist
 
 from ..config.schema import RootConfig
 from ..models import build_model, fused_ce_z_loss, init_weights
+from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
+from ..ops import functional as K
 from ..ops.autograd import GradSlot
 from ..ops.native import F, I, L, P, check, cpu_lib, cuda_lib, stream_ptr
 from ..parallel.flat import FlatLayout, PeerBuffer
@@ -220,6 +222,7 @@ class TrainEngine:
 
     def refresh_compute_weights(self) -> None:
         """compute weights <- master (all segments, local only); used at start-up and after a load."""
+        K.weight_epoch = (K.weight_epoch or 0) + 1
         if not self.mixed:
             return
         arr = _ptr_array([self.compute.data_ptr()])
@@ -234,6 +237,9 @@ class TrainEngine:
     def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int):
         """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
         self._bind_slots(self.grads[vslot])
+        qat = self.cfg.model.qat
+        if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
+            set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
         self.model.train()
         out = self.model(input_ids)
         z_coeff = self.cfg.model.z_loss.coeff if self.cfg.model.z_loss.enabled else 0.0
@@ -348,6 +354,13 @@ class TrainEngine:
             check(self.lib.otb_cpu_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
                                               _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
         self._barrier()  # peers' stores into this rank's weights are complete before the next forward
+        K.weight_epoch = (K.weight_epoch or 0) + 1
+        refresh = self.cfg.model.qat.scale_refresh_every_n_steps
+        if self.cfg.model.qat.enabled and refresh > 0 and self.opt_step % refresh == 0:
+            # after the update, before the state hash: every rank derives the same step sizes from its
+            # (identical) compute weights (reference src/pretrain/train/loop.py:1069-1084)
+            refresh_lsq_weight_scales(self.model)
+            K.weight_epoch += 1
 
     def skip_step(self) -> None:
         self._barrier()
