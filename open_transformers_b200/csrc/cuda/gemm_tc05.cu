@@ -25,6 +25,21 @@
 // tcgen05.mma kind::i8 (K = 32 per instruction, 128 int8 = one swizzle row per k-block), exact int32 accumulation
 // in tensor memory, and an epilogue that dequantises  float(acc) * (sa[0] * sb[col])  before the usual stores.
 //
+// Tensor-parallel variants (TP template parameter), each ONE kernel that moves data over NVLink peer pointers
+// while the tensor cores work, with no library collective involved:
+//   TP = 1  all-gather -> GEMM.  The A operand is token-sharded over P ranks. A few extra CTAs of the same launch
+//           push this rank's rows into every peer's full-size A buffer (plain 16-byte peer stores) and then set a
+//           per-128-row flag on that peer; the GEMM CTAs start with the rows that are already local and, before
+//           the TMA loads of a row block owned by a peer, wait (bounded) for that block's flag.
+//   TP = 2  GEMM -> ordered reduction over ranks (row-parallel layer: K is split over the P ranks). The partial
+//           sums are NOT added after the fact: rank r receives the fp32 accumulator tile of rank r-1 in its inbox,
+//           loads it into tensor memory (tcgen05.st), continues the SAME ascending-k accumulation chain over its own
+//           K slice, and TMA-stores the tile into rank r+1's inbox (the last rank: into the buffer of the rank that
+//           owns those rows) followed by a release flag per 32-row quarter. The result is therefore bit-identical
+//           to the unsplit GEMM on one GPU, and ranks work on different tiles at the same time (a pipeline).
+// Every wait on a peer is bounded (two seconds of %globaltimer); when it runs out the kernel raises the abort
+// flag, drains its own copies, frees its tensor memory and reports through the status word.
+//
 // Role of this file in the reference's terms: the `repop.nn.linear` / `mmacc` entry points
 // (reference docs/MODEL_OP_DTYPE_TRACE.md:82,100).
 #include "tc05.cuh"
@@ -46,6 +61,45 @@ enum Epi : int {
   EPI_BF16_RES = 3,  // C(bf16)  = bf16(acc + float(R))
 };
 
+struct TpNone {};
+struct TpArgs {
+  CUtensorMap tmOut[8];        // TP 2: [0] = next rank's inbox, or (last rank) the fp32 result buffer of each row owner
+  uint32_t* flags_out[8];      // TP 2: flag arrays matching tmOut
+  const float* inbox;          // TP 2: this rank's inbox (fp32 [M, ld_in]) and its flags [tiles * 4]
+  const uint32_t* flags_in;    // TP 1: this rank's row-block flags [P * tiles_per_shard]
+  long ld_in;
+  const uint4* ag_src;         // TP 1: this rank's own rows inside its full-size A buffer
+  uint4* ag_dst[8];            // TP 1: the same rows inside every peer's A buffer (null for this rank)
+  uint32_t* ag_flags[8];       // TP 1: every peer's row-block flags
+  long ag_block_u4;            // 16-byte units per 128-row block
+  uint32_t seq;                // value a flag takes when its data of THIS call has landed
+  int rank, P, tiles_per_shard, gemm_ctas;
+};
+
+// Bounded wait for a flag written by a peer GPU (release at system scope on their side).
+__device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t seq, volatile uint32_t* abort_flag) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t i = 0;; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == seq) return true;
+    if (*abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) break;
+    }
+    __nanosleep(100);
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void release_peer_flag(uint32_t* flag, uint32_t seq) {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+}
+
 template <int BN, int STAGES>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK_BYTES;
@@ -57,13 +111,46 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8, int TP, typename TPA>
+__global__ void __launch_bounds__(TP == 2 ? NUM_THREADS + 128 : NUM_THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv,
                  const __nv_bfloat16* __restrict__ R, int M, int N, int K, long ldc, long ldr, int group_m,
-                 const float* __restrict__ scale_a, const float* __restrict__ scale_b, uint32_t* __restrict__ status) {
+                 const float* __restrict__ scale_a, const float* __restrict__ scale_b, uint32_t* __restrict__ status,
+                 const __grid_constant__ TPA tp) {
   static_assert(!I8 || (!A_MN && !B_MN), "the int8 path takes K-major operands only");
+  static_assert(TP == 0 || !I8, "the tensor-parallel variants are bf16");
+  static_assert(TP != 2 || EPI == EPI_F32, "the chained GEMM hands fp32 accumulator tiles on");
+  int nctas = gridDim.x;
+  if constexpr (TP == 1) {
+    nctas = tp.gemm_ctas;
+    if ((int)blockIdx.x >= nctas) {
+      // ---------------------------------------------------- all-gather pusher CTAs (no tensor cores, no barriers)
+      const int copiers = gridDim.x - nctas;
+      for (int blk = blockIdx.x - nctas; blk < tp.tiles_per_shard; blk += copiers) {
+        const uint4* src = tp.ag_src + (long)blk * tp.ag_block_u4;
+        for (int p = 0; p < tp.P; ++p) {
+          if (p == tp.rank) continue;
+          uint4* dst = tp.ag_dst[p] + (long)blk * tp.ag_block_u4;
+          for (long i = threadIdx.x; i < tp.ag_block_u4; i += 4 * blockDim.x) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (i + u * blockDim.x < tp.ag_block_u4) v[u] = __ldg(src + i + u * blockDim.x);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (i + u * blockDim.x < tp.ag_block_u4) dst[i + u * blockDim.x] = v[u];
+          }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < tp.P && (int)threadIdx.x != tp.rank)
+          release_peer_flag(tp.ag_flags[threadIdx.x] + tp.rank * tp.tiles_per_shard + blk, tp.seq);
+        __syncthreads();
+      }
+      return;
+    }
+  }
   constexpr int BK = I8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per k-block
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -72,8 +159,11 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;  // [2]
   uint64_t* tempty_bar = tfull_bar + 2;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* tloaded_bar = tempty_bar + 2;    // [2] (chained GEMM: incoming accumulator is in tensor memory)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tloaded_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  bool chain_in = false;
+  if constexpr (TP == 2) chain_in = tp.rank > 0;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -92,6 +182,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 4);  // one arrive per epilogue warp
+      mbar_init(&tloaded_bar[b], 4);  // one arrive per accumulator-loading warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -115,6 +206,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int r = t - g * per_group;
     tm = first_m + r % gsz;
     tn = r / gsz;
+    if constexpr (TP == 1) tm = (tm + tp.rank * tp.tiles_per_shard) % tiles_m;  // own rows first, then the peers' in ring order
   };
 
   if (warp == 0) {
@@ -124,9 +216,16 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += nctas) {
         int tm, tn;
         tile_coord(t, tm, tn);
+        if constexpr (TP == 1) {
+          const int owner = tm / tp.tiles_per_shard;
+          if (owner != tp.rank) {
+            if (!wait_peer_flag(tp.flags_in + owner * tp.tiles_per_shard + tm % tp.tiles_per_shard, tp.seq, abort_flag)) { ok = false; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");  // the peer's generic stores, then our TMA (async proxy) reads
+          }
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -155,10 +254,14 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = I8 ? make_idesc(BM, BN, 0, 0, 2, 1) : make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
         const uint32_t buf = lt & 1;
         const uint32_t bph = (lt >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[buf], bph ^ 1, abort_flag)) { ok = false; break; }
+        if (chain_in) {  // the loading warps waited for the buffer to be free and filled it with the incoming partial sum
+          if (!mbar_wait(&tloaded_bar[buf], bph, abort_flag)) { ok = false; break; }
+        } else {
+          if (!mbar_wait(&tempty_bar[buf], bph ^ 1, abort_flag)) { ok = false; break; }
+        }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -173,11 +276,50 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint64_t ad = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024) : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024) : make_smem_desc(sb + kk * 32, 16, 1024);
             if (I8) mma_i8_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
-            else mma_f16_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+            else mma_f16_ss(d_tmem, ad, bd, idesc, ((kb | kk) != 0) || chain_in);
           }
           mma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs have read it
         }
         if (ok) mma_commit(&tfull_bar[buf]);  // accumulator complete
+      }
+    }
+  } else if (TP == 2 && warp >= 6) {
+    // ------------------------------------------ chained GEMM: incoming fp32 accumulator tile -> tensor memory
+    if constexpr (TP == 2) {
+      if (chain_in) {
+        const int q = warp & 3;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
+          int tm, tn;
+          tile_coord(t, tm, tn);
+          const uint32_t buf = lt & 1;
+          const uint32_t bph = (lt >> 1) & 1;
+          if (!mbar_wait(&tempty_bar[buf], bph ^ 1, abort_flag)) { ok = false; break; }
+          uint32_t got = 1;
+          if (lane == 0) got = wait_peer_flag(tp.flags_in + ((long)tm * tiles_n + tn) * 4 + q, tp.seq, abort_flag) ? 1u : 0u;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) { ok = false; break; }
+          tc_fence_after();
+          const long row = (long)tm * BM + q * 32 + lane;
+          const float* src = tp.inbox + row * tp.ld_in + (long)tn * BN;
+          const uint32_t tdst = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 f = __ldcg(reinterpret_cast<const float4*>(src + c) + j);  // L2 only: written by a peer GPU
+              v[4 * j] = __float_as_uint(f.x); v[4 * j + 1] = __float_as_uint(f.y);
+              v[4 * j + 2] = __float_as_uint(f.z); v[4 * j + 3] = __float_as_uint(f.w);
+            }
+            tmem_st_32x32b_x32(tdst + c, v);
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tloaded_bar[buf]);
+        }
       }
     }
   } else {
@@ -185,9 +327,15 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
     uint32_t lt = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
       int tm, tn;
       tile_coord(t, tm, tn);
+      const CUtensorMap* tmc = &tmC;
+      int out_sel = 0;
+      if constexpr (TP == 2) {
+        out_sel = tp.rank == tp.P - 1 ? tm / tp.tiles_per_shard : 0;
+        tmc = &tp.tmOut[out_sel];
+      }
       const uint32_t buf = lt & 1;
       const uint32_t bph = (lt >> 1) & 1;
       if (!mbar_wait(&tfull_bar[buf], bph, abort_flag)) { ok = false; break; }
@@ -210,12 +358,12 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int y = tm * BM + q * 32;
           if (EPI == EPI_F32_ACC) {
             asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                             reinterpret_cast<uint64_t>(&tmC)),
+                             reinterpret_cast<uint64_t>(tmc)),
                          "r"(src), "r"(col), "r"(y)
                          : "memory");
           } else {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                             reinterpret_cast<uint64_t>(&tmC)),
+                             reinterpret_cast<uint64_t>(tmc)),
                          "r"(src), "r"(col), "r"(y)
                          : "memory");
           }
@@ -305,6 +453,15 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if constexpr (TP == 2) {
+        // this warp's 32 rows of the tile have been written into the next rank's memory: tell it
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          asm volatile("fence.proxy.async;" ::: "memory");
+          release_peer_flag(tp.flags_out[out_sel] + ((long)tm * tiles_n + tn) * 4 + q, tp.seq);
+        }
+        __syncwarp();
+      }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every TMA store of this warp has completed
     __syncwarp();
@@ -346,7 +503,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8 = false>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N, int K, long ldc, long ldr,
            uint32_t* status, int max_ctas, cudaStream_t stream, const float* scale_a = nullptr, const float* scale_b = nullptr) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_tc05_kernel<BN, STAGES, A_MN, B_MN, EPI, I8>;
+  auto kern = gemm_tc05_kernel<BN, STAGES, A_MN, B_MN, EPI, I8, 0, TpNone>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -358,8 +515,67 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
   if (grid < 1) grid = 1;
   const int group_m = 8;
   kern<<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr,
-                                                group_m, scale_a, scale_b, status);
+                                                group_m, scale_a, scale_b, status, TpNone{});
   return (int)cudaGetLastError();
+}
+
+template <int BN, int STAGES, bool B_MN, int EPI, int TP>
+int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N, int K, long ldc,
+              long ldr, uint32_t* status, int grid, const TpArgs& tp, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_tc05_kernel<BN, STAGES, false, B_MN, EPI, false, TP, TpArgs>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  kern<<<grid, TP == 2 ? NUM_THREADS + 128 : NUM_THREADS, L::TOTAL, stream>>>(
+      ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr, 8, nullptr, nullptr, status, tp);
+  return (int)cudaGetLastError();
+}
+
+// y[rows of this rank] = bf16( acc (+ R) ) once the last rank of the chain has delivered the tile quarter
+__global__ void tp_finish_kernel(const float* __restrict__ acc, const uint32_t* __restrict__ flags, uint32_t seq,
+                                 const __nv_bfloat16* __restrict__ R, __nv_bfloat16* __restrict__ y, int rows_per_rank,
+                                 int N, int BN, int rank, long ld_acc, long ldr, long ldy, uint32_t* __restrict__ status) {
+  __shared__ uint32_t ok_sh;
+  __shared__ uint32_t abort_sh;
+  const int tn = blockIdx.x;
+  const int rb = blockIdx.y;                       // 32-row block inside this rank's rows
+  const long row0 = (long)rank * rows_per_rank + (long)rb * 32;
+  const int tm = (int)(row0 / BM), q = (int)((row0 % BM) / 32);
+  const int tiles_n = (N + BN - 1) / BN;
+  if (threadIdx.x == 0) {
+    abort_sh = 0;
+    ok_sh = wait_peer_flag(flags + ((long)tm * tiles_n + tn) * 4 + q, seq, &abort_sh) ? 1u : 0u;
+    if (!ok_sh && status) atomicExch(status, 2u);
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const int col0 = tn * BN;
+  const int vec_per_row = BN / 8;
+  for (int i = threadIdx.x; i < 32 * vec_per_row; i += blockDim.x) {
+    const int r = i / vec_per_row, c = col0 + (i % vec_per_row) * 8;
+    if (c >= N) continue;
+    const long row = row0 + r;
+    const long lrow = (long)rb * 32 + r;           // row inside this rank's shard (R and y are shard-local)
+    const float4 a0 = __ldcg(reinterpret_cast<const float4*>(acc + row * ld_acc + c));
+    const float4 a1 = __ldcg(reinterpret_cast<const float4*>(acc + row * ld_acc + c) + 1);
+    float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    if (R) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(R + lrow * ldr + c);
+      const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        f[2 * e] = __fadd_rn(f[2 * e], __uint_as_float(w[e] << 16));
+        f[2 * e + 1] = __fadd_rn(f[2 * e + 1], __uint_as_float(w[e] & 0xFFFF0000u));
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]); o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(y + lrow * ldy + c) = o;
+  }
 }
 
 template <int BN, int STAGES, int EPI>
@@ -471,4 +687,140 @@ extern "C" int otb_gemm_i8(const void* A, const void* B, void* C, const void* R,
     OTB_I8(128, 6, EPI_BF16_RES)
   }
 #undef OTB_I8
+}
+
+namespace {
+struct PtrTable8 { uint32_t* p[8]; };
+__global__ void peer_barrier_tab_kernel(PtrTable8 slots, int rank, int P, uint32_t seq, uint32_t* status) {
+  __shared__ uint32_t abort_sh;
+  if (threadIdx.x == 0) abort_sh = 0;
+  __syncthreads();
+  const int p = threadIdx.x;
+  if (p < P) {
+    release_peer_flag(slots.p[p] + rank, seq);
+    if (!wait_peer_flag(slots.p[rank] + p, seq, &abort_sh) && status) atomicExch(status, 3u);
+  }
+}
+inline int tp_chain_bn(int N) { return N >= 256 ? 256 : 128; }
+}  // namespace
+
+// Cross-GPU barrier on the stream: slots[p] is rank p's array of P words (peer pointers); seq must grow by one per call.
+extern "C" int otb_peer_barrier(void* const* slots, int rank, int P, unsigned seq, uint32_t* status, void* stream) {
+  if (P < 1 || P > 8) return -2;
+  PtrTable8 t{};
+  for (int p = 0; p < P; ++p) t.p[p] = reinterpret_cast<uint32_t*>(slots[p]);
+  peer_barrier_tab_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, rank, P, seq, status);
+  return (int)cudaGetLastError();
+}
+
+// All-gather -> GEMM in one kernel.  a_full[p]: rank p's full-size A buffer [M,K] bf16 (peer pointers; this rank's own
+// rows [rank*M/P, (rank+1)*M/P) must already be in a_full[rank]); ag_flags[p]: rank p's P*(M/P/128) flag words.
+//   C[M,N] = A_full * op(B)^T      B: [N,K] (b_mn = 0) or [K,N] (b_mn = 1), local.
+// `copier_ctas` CTAs of the launch push this rank's rows to the peers while the others compute. epi 0 (bf16) or 1 (fp32).
+// M must be a multiple of P*128. seq: a value unique to this call on this flag array (same on every rank).
+extern "C" int otb_tp_ag_gemm(void* const* a_full, void* const* ag_flags, int rank, int P, unsigned seq, const void* B, void* C,
+                              int M, int N, int K, long ldb, long ldc, int b_mn, int epi, int copier_ctas, uint32_t* status,
+                              void* stream) {
+  if (P < 1 || P > 8 || rank < 0 || rank >= P || M % (P * BM) || (K & 7) || (ldb & 7)) return -2;
+  if (epi != EPI_BF16 && epi != EPI_F32) return -3;
+  const bool bf16_out = epi == EPI_BF16;
+  if ((bf16_out && (ldc & 7)) || (!bf16_out && (ldc & 3))) return -2;
+  const int sms = otb_sm_count();
+  if (copier_ctas < 1) copier_ctas = 1;
+  if (P == 1) copier_ctas = 0;
+  int gemm_ctas = sms - copier_ctas;
+  const int BN = N > 128 ? 256 : 128;
+  const long tiles = (long)(M / BM) * ((N + BN - 1) / BN);
+  if (gemm_ctas > tiles) gemm_ctas = (int)tiles;
+  constexpr int BK = BK_BYTES / 2;
+  const void* A = a_full[rank];
+  CUtensorMap ta, tb, tc;
+  CUresult r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = b_mn ? encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
+           : encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, 2)
+               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, 4);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  TpArgs tp{};
+  tp.rank = rank; tp.P = P; tp.seq = seq; tp.gemm_ctas = gemm_ctas;
+  tp.tiles_per_shard = M / BM / P;
+  tp.flags_in = reinterpret_cast<const uint32_t*>(ag_flags[rank]);
+  tp.ag_block_u4 = (long)BM * K * 2 / 16;
+  const long shard_u4 = (long)tp.tiles_per_shard * tp.ag_block_u4;
+  tp.ag_src = reinterpret_cast<const uint4*>(A) + rank * shard_u4;
+  for (int p = 0; p < P; ++p) {
+    tp.ag_dst[p] = p == rank ? nullptr : reinterpret_cast<uint4*>(a_full[p]) + rank * shard_u4;
+    tp.ag_flags[p] = reinterpret_cast<uint32_t*>(ag_flags[p]);
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = gemm_ctas + copier_ctas;
+#define OTB_AG(BN_, ST_, BMN_, EPI_) return launch_tp<BN_, ST_, BMN_, EPI_, 1>(ta, tb, tc, C, nullptr, M, N, K, ldc, 0, status, grid, tp, s);
+  if (BN == 256) {
+    if (b_mn) { if (bf16_out) { OTB_AG(256, 4, true, EPI_BF16) } OTB_AG(256, 4, true, EPI_F32) }
+    if (bf16_out) { OTB_AG(256, 4, false, EPI_BF16) } OTB_AG(256, 4, false, EPI_F32)
+  }
+  if (b_mn) { if (bf16_out) { OTB_AG(128, 6, true, EPI_BF16) } OTB_AG(128, 6, true, EPI_F32) }
+  if (bf16_out) { OTB_AG(128, 6, false, EPI_BF16) } OTB_AG(128, 6, false, EPI_F32)
+#undef OTB_AG
+}
+
+extern "C" int otb_tp_chain_bn(int N) { return tp_chain_bn(N); }
+
+// One rank's part of the K-split GEMM whose partial sums travel rank 0 -> 1 -> ... -> P-1 INSIDE the accumulation:
+//   acc_r = acc_{r-1} (+)= A_r[M,Kr] * op(B_r)^T, continued in tensor memory, ascending k, so the last rank holds
+//   exactly the bits of the unsplit GEMM. A_r: [M,Kr] bf16 K-major; B_r: [N,Kr] (b_mn 0) or [Kr,N] (b_mn 1).
+// inbox / flags_in: this rank's fp32 [M, ld_acc] buffer and its (M/128)*(N/BN)*4 flag words (unused on rank 0).
+// out_bufs / out_flags: rank < P-1: one entry, the next rank's inbox and flags; rank P-1: P entries, the result
+// buffer and flags of each row owner (rows [p*M/P, (p+1)*M/P) belong to rank p). All buffers are [M, ld_acc] fp32.
+extern "C" int otb_tp_chain_gemm(const void* A, const void* B, int M, int N, int K, long lda, long ldb, int b_mn, const float* inbox,
+                                 const void* flags_in, void* const* out_bufs, void* const* out_flags, long ld_acc, int rank, int P,
+                                 unsigned seq, uint32_t* status, void* stream) {
+  if (P < 1 || P > 8 || rank < 0 || rank >= P || M % (P * BM) || (lda & 7) || (ldb & 7) || (ld_acc & 3)) return -2;
+  const int BN = tp_chain_bn(N);
+  constexpr int BK = BK_BYTES / 2;
+  CUtensorMap ta, tb;
+  CUresult r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = b_mn ? encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
+           : encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  TpArgs tp{};
+  tp.rank = rank; tp.P = P; tp.seq = seq;
+  tp.tiles_per_shard = M / BM / P;
+  tp.inbox = inbox; tp.ld_in = ld_acc;
+  tp.flags_in = reinterpret_cast<const uint32_t*>(flags_in);
+  const int n_out = rank == P - 1 ? P : 1;
+  for (int i = 0; i < n_out; ++i) {
+    r = encode_2d(&tp.tmOut[i], out_bufs[i], (uint64_t)N, (uint64_t)M, (uint64_t)ld_acc, 32, 32, 4);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    tp.flags_out[i] = reinterpret_cast<uint32_t*>(out_flags[i]);
+  }
+  const long tiles = (long)(M / BM) * ((N + BN - 1) / BN);
+  int grid = otb_sm_count();
+  if (grid > tiles) grid = (int)tiles;
+  tp.gemm_ctas = grid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const CUtensorMap& tc = tp.tmOut[0];
+  if (BN == 256) {
+    if (b_mn) return launch_tp<256, 4, true, EPI_F32, 2>(ta, tb, tc, nullptr, nullptr, M, N, K, ld_acc, 0, status, grid, tp, s);
+    return launch_tp<256, 4, false, EPI_F32, 2>(ta, tb, tc, nullptr, nullptr, M, N, K, ld_acc, 0, status, grid, tp, s);
+  }
+  if (b_mn) return launch_tp<128, 6, true, EPI_F32, 2>(ta, tb, tc, nullptr, nullptr, M, N, K, ld_acc, 0, status, grid, tp, s);
+  return launch_tp<128, 6, false, EPI_F32, 2>(ta, tb, tc, nullptr, nullptr, M, N, K, ld_acc, 0, status, grid, tp, s);
+}
+
+// This rank's rows of the chained GEMM, once they have arrived:  y[M/P, N] (bf16) = bf16( acc (+ R) ).
+// acc / flags: this rank's result buffer [M, ld_acc] fp32 and flag words; R, y: shard-local [M/P, *] bf16.
+extern "C" int otb_tp_finish(const float* acc, const void* flags, unsigned seq, const void* R, void* y, int M, int N, int rank, int P,
+                             long ld_acc, long ldr, long ldy, uint32_t* status, void* stream) {
+  if (P < 1 || M % (P * BM) || (N & 7) || (ldy & 7) || (R && (ldr & 7))) return -2;
+  const int BN = tp_chain_bn(N);
+  const int rows = M / P;
+  dim3 grid((N + BN - 1) / BN, rows / 32);
+  tp_finish_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      acc, reinterpret_cast<const uint32_t*>(flags), seq, reinterpret_cast<const __nv_bfloat16*>(R),
+      reinterpret_cast<__nv_bfloat16*>(y), rows, N, BN, rank, ld_acc, ldr, ldy, status);
+  return (int)cudaGetLastError();
 }

@@ -327,10 +327,13 @@ def gemm_i8(aq: torch.Tensor, bq: torch.Tensor, sa: torch.Tensor, sb: torch.Tens
         assert residual.dtype == out_dtype and tuple(residual.shape) == (M, N)
     ldr = _ld(residual) if residual is not None else 0
     if aq.is_cuda:
-        if residual is not None and not bf:
-            raise NotImplementedError("fp32 residual epilogue of the int8 GEMM")
-        check(cuda_lib().otb_gemm_i8(P(aq), P(bq), P(out), P(residual), I(M), I(N), I(Kd), L(_ld(aq)), L(_ld(bq)), L(_ld(out)), L(ldr),
-                                     P(sa), P(sb), I(epi), P(_status(aq.device)), I(0), stream_ptr()), "gemm_i8")
+        late_add = residual is not None and not bf  # exact family: one IEEE add after the fp32 store, same bits as the twin
+        if late_add:
+            epi = EPI_STORE_F32
+        check(cuda_lib().otb_gemm_i8(P(aq), P(bq), P(out), P(None if late_add else residual), I(M), I(N), I(Kd), L(_ld(aq)), L(_ld(bq)),
+                                     L(_ld(out)), L(ldr), P(sa), P(sb), I(epi), P(_status(aq.device)), I(0), stream_ptr()), "gemm_i8")
+        if late_add:
+            out.add_(residual)
     else:
         check(cpu_lib().otb_cpu_gemm_i8(P(aq), P(bq), P(out), P(residual), I(M), I(N), I(Kd), L(_ld(aq)), L(_ld(bq)), L(_ld(out)), L(ldr),
                                         P(sa), P(sb), I(3 if residual is not None else 0), I(bf)), "gemm_i8")
