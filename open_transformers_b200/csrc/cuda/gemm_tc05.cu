@@ -309,7 +309,9 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             uint32_t v[32];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 f = __ldcg(reinterpret_cast<const float4*>(src + c) + j);  // L2 only: written by a peer GPU
+              float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // columns past N (N % 4 == 0) are never stored
+              if (tn * BN + c + 4 * j + 4 <= N)
+                f = __ldcg(reinterpret_cast<const float4*>(src + c) + j);  // L2 only: written by a peer GPU
               v[4 * j] = __float_as_uint(f.x); v[4 * j + 1] = __float_as_uint(f.y);
               v[4 * j + 2] = __float_as_uint(f.z); v[4 * j + 3] = __float_as_uint(f.w);
             }
