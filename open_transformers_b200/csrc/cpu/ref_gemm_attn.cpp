@@ -37,9 +37,33 @@ inline float ldb(const void* p, long i) { return det_bf2f(((const uint16_t*)p)[i
 inline float rbf(float x) { return det_bf2f(det_f2bf(x)); }
 inline bool masked_pair(int qi, int kj, int window) { return kj > qi || (window > 0 && kj <= qi - window); }
 
+// i8pv: P V on the int8 grid (values quantised per (KV head, 128-key block), probabilities q = rint(127 p), exact
+// integer sums, one fp32 dequantisation per block) - the twin of attn_fwd_kernel<128, true>.
 int attn_fwd_tc(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B, int T, int H, int Hkv, int D,
-                int window, float c_log2) {
+                int window, float c_log2, int i8pv = 0) {
   const int G = H / Hkv;
+  const int nblk = (T + 127) / 128;
+  std::vector<float> vstep;
+  std::vector<int8_t> vq;
+  if (i8pv) {
+    vstep.assign((size_t)B * Hkv * nblk, 0.0f);
+    vq.assign((size_t)B * T * Hkv * D, 0);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int bg = 0; bg < B * Hkv; ++bg)
+      for (int blk = 0; blk < nblk; ++blk) {
+        const int b = bg / Hkv, g = bg % Hkv;
+        float m = 0.0f;
+        for (int r = 0; r < 128 && blk * 128 + r < T; ++r)
+          for (int d = 0; d < D; ++d) m = fmaxf(m, fabsf(ldb(qkv, ((long)b * T + blk * 128 + r) * ldqkv + (long)(H + Hkv + g) * D + d)));
+        const float step = fmaxf(m * (1.0f / 127.0f), 1.17549435e-38f);
+        vstep[(size_t)bg * nblk + blk] = step;
+        for (int r = 0; r < 128 && blk * 128 + r < T; ++r)
+          for (int d = 0; d < D; ++d) {
+            const float f = ldb(qkv, ((long)b * T + blk * 128 + r) * ldqkv + (long)(H + Hkv + g) * D + d);
+            vq[((size_t)b * T + blk * 128 + r) * Hkv * D + (size_t)g * D + d] = (int8_t)(int)fminf(fmaxf(rintf(f / step), -127.0f), 127.0f);
+          }
+      }
+  }
 #pragma omp parallel for collapse(2) schedule(dynamic, 4)
   for (int bh = 0; bh < B * H; ++bh) {
     for (int qi = 0; qi < T; ++qi) {
@@ -68,16 +92,26 @@ int attn_fwd_tc(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O,
           for (int e = part * 32; e < part * 32 + 32; ++e) {
             const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
             ls[e & 1] = ls[e & 1] + pe;
-            p[e] = rbf(pe);
+            p[e] = i8pv ? rintf(pe * 127.0f) : rbf(pe);
           }
           l_part[part] = det_fmaf(l_part[part], alpha, ls[0] + ls[1]);
         }
-        for (int d = 0; d < D; ++d) {
-          for (int e = 0; e < 128; ++e) {
-            const int kj = j * 128 + e;
-            vcol[e] = kj < T ? ldb(qkv, ((long)b * T + kj) * ldqkv + (long)(H + Hkv + g) * D + d) : 0.0f;
+        if (i8pv) {
+          const float cblk = vstep[((size_t)b * Hkv + g) * nblk + j] * (1.0f / 127.0f);
+          for (int d = 0; d < D; ++d) {
+            int32_t acc = 0;
+            for (int e = 0; e < 128 && j * 128 + e < T; ++e)
+              acc += (int32_t)p[e] * (int32_t)vq[((size_t)b * T + j * 128 + e) * Hkv * D + (size_t)g * D + d];
+            o[d] = det_fmaf(o[d], alpha, (float)acc * cblk);
           }
-          o[d] = det_fmaf(o[d], alpha, tcmodel::dot(p, vcol, 128));
+        } else {
+          for (int d = 0; d < D; ++d) {
+            for (int e = 0; e < 128; ++e) {
+              const int kj = j * 128 + e;
+              vcol[e] = kj < T ? ldb(qkv, ((long)b * T + kj) * ldqkv + (long)(H + Hkv + g) * D + d) : 0.0f;
+            }
+            o[d] = det_fmaf(o[d], alpha, tcmodel::dot(p, vcol, 128));
+          }
         }
         m_run = m_new;
       }
@@ -264,6 +298,14 @@ int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, voi
     }
   }
   return 0;
+}
+
+// int8 P V forward (bf16 activations, head_dim 128): twin of otb_attn_fwd_i8pv
+int otb_cpu_attn_fwd_i8pv(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B, int T, int H,
+                          int Hkv, int D, int window, float scale) {
+  if (D != 128) return -2;
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  return attn_fwd_tc(qk, ldqk, qkv, ldqkv, O, ldo, lse, B, T, H, Hkv, D, window, c_log2, 1);
 }
 
 // Backward. dqk: [B*T, lddqk] (dQ heads then dK heads); dV at column (H+Hkv)*D of dqkv; delta: [B,H,T] scratch.

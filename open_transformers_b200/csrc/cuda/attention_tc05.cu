@@ -21,6 +21,13 @@
 // Row sums: each 32-key quarter keeps two ascending chains (even / odd keys) that are added per block;
 // the four quarter sums are combined ((l0 + l1) + l2) + l3 at the end.
 //
+// int8-PV variant of the forward (I8PV): V is quantised beforehand to int8 per (KV head, 128-key block) with one
+// fp32 step per block (quant_v_kernel), the probabilities are quantised on the fly to q = rint(127 p), P V runs on
+// the int8 tensor cores (tcgen05 kind::i8, exact int32 sums over the 128 keys of a block) and is dequantised in
+// fp32: O = O*alpha + float(sum) * (step / 127). Softmax statistics stay fp32 on the unquantised probabilities;
+// the backward is the straight-through float shadow (the ordinary backward kernels on the bf16 q, k, v).
+// Reference role: int8pv_causal_flash_attention (attention_repop.py:52; docs/MODEL_OP_DTYPE_TRACE.md:80,117-119).
+//
 // Layouts: q/k come from one [B*T, ld] bf16 buffer (post-RoPE; head h at column h*D, KV head g
 // at column (H+g)*D); v comes from the packed qkv buffer; O is [B*T, H*D]; lse and delta are
 // [B, H, T] fp32. Reference role: repop causal_flash_attention fwd/bwd
@@ -81,11 +88,12 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, u
 }
 
 // ---------------------------------------------------------------------------- forward
-template <int D>
+template <int D, bool I8PV>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
                 __nv_bfloat16* __restrict__ O, long ldo, float* __restrict__ lse_out, int T, int H, int Hkv, int window,
-                float scale, float c_log2, uint32_t* __restrict__ status) {
+                float scale, float c_log2, const float* __restrict__ vstep, uint32_t* __restrict__ status) {
+  static_assert(!I8PV || D == 128, "the int8 P V path needs 128-byte value rows");
   constexpr int TILE = BQ * D * 2;
   constexpr int ST = 2;
   extern __shared__ uint8_t smem_raw[];
@@ -146,14 +154,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
         mbar_expect_tx(&k_full[st], TILE);
         load_tile<D>(sK + st * TILE, &tmQK, &k_full[st], (H + g) * D, k0, b);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&v_full[st], TILE);
-        load_tile<D>(sV + st * TILE, &tmV, &v_full[st], (H + Hkv + g) * D, k0, b);
+        if (I8PV) {  // int8 values: [128 keys][D bytes], one swizzle row per key
+          mbar_expect_tx(&v_full[st], BKV * D);
+          tma_load_3d(sV + st * TILE, &tmV, &v_full[st], g * D, k0, b);
+        } else {
+          mbar_expect_tx(&v_full[st], TILE);
+          load_tile<D>(sV + st * TILE, &tmV, &v_full[st], (H + Hkv + g) * D, k0, b);
+        }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);
-      constexpr uint32_t idPV = make_idesc(128, D, 0, 1);
+      constexpr uint32_t idPV = I8PV ? make_idesc(128, D, 0, 1, 2, 1) : make_idesc(128, D, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_S = [&](int i) {
@@ -176,8 +189,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
         if (!mbar_wait(&v_full[st], (i / ST) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aV = smem_u32(sV + st * TILE);
+        if (I8PV) {
+          // P: [128 rows][128 int8 keys] K-major, 32 keys per instruction; V: [128 keys][128 int8] MN-major, 32 key rows per instruction
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tPV, desc_k(aP, kk), desc_mn(aV, kk), idPV, kk != 0);
+          for (int kk = 0; kk < BKV / 32; ++kk)
+            mma_i8_ss(tPV, make_smem_desc(aP + kk * 32, 16, 1024), make_smem_desc(aV + kk * 4096, 16384, 1024), idPV, kk != 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tPV, desc_k(aP, kk), desc_mn(aV, kk), idPV, kk != 0);
+        }
         mma_commit(pv_full);
         mma_commit(&v_empty[st]);
       }
@@ -191,6 +211,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     const int qi = q0 + r;                 // query position
     const uint32_t lane_off = uint32_t(qd * 32) << 16;
     float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
+    float c_prev = 0.0f;  // int8 P V: dequantisation factor (value step / 127) of the block whose P V is pending
+    const int nblk = (T + BKV - 1) / BKV;
+    // accumulator word -> fp32 contribution
+    auto pv_val = [&](uint32_t w) { return I8PV ? __fmul_rn(__int2float_rn((int)w), c_prev) : __uint_as_float(w); };
     f2 o[DH / 2];
 #pragma unroll
     for (int d = 0; d < DH / 2; ++d) o[d] = pack2(0.0f, 0.0f);
@@ -240,7 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
             tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < CW; e += 2)
-              o[(c * CW + e) >> 1] = fma2(o[(c * CW + e) >> 1], a2, pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+              o[(c * CW + e) >> 1] = fma2(o[(c * CW + e) >> 1], a2, pack2(pv_val(v[e]), pv_val(v[e + 1])));
           }
         }
       }
@@ -261,14 +285,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
             p2 = pack2(p0, p1);
           }
           lsum2 = add2(lsum2, p2);
-          pk[e >> 1] = pack_bf16(p0, p1);
+          if (I8PV) {
+            const uint32_t q0b = (uint32_t)(int)rintf(__fmul_rn(p0, 127.0f)), q1b = (uint32_t)(int)rintf(__fmul_rn(p1, 127.0f));
+            if ((e & 3) == 0) pk[e >> 2] = 0;
+            pk[e >> 2] |= (q0b | (q1b << 8)) << (8 * (e & 3));
+          } else {
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
         }
-        // keys part*32 .. +31 -> 64-key sub-tile (part >> 1), 16-byte chunks (part & 1) * 4 .. +3 of the row
-        uint8_t* base = sP + (part >> 1) * 16384;
+        if (I8PV) {
+          // keys part*32 .. +31 are bytes part*32 .. +31 of the 128-byte row: chunks part*2, part*2 + 1
 #pragma unroll
-        for (int w = 0; w < 4; ++w)
-          *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) =
-              make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+          for (int w = 0; w < 2; ++w)
+            *reinterpret_cast<uint4*>(sP + swz(r, part * 2 + w)) = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+        } else {
+          // keys part*32 .. +31 -> 64-key sub-tile (part >> 1), 16-byte chunks (part & 1) * 4 .. +3 of the row
+          uint8_t* base = sP + (part >> 1) * 16384;
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) =
+                make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+        }
       }
       float ls0, ls1;
       unpack2(lsum2, ls0, ls1);
@@ -276,6 +313,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       l_run = __fmaf_rn(l_run, alpha, lsum);
       m_run = m_new;
       alpha_prev = alpha;
+      if (I8PV) c_prev = __fmul_rn(vstep[((long)b * Hkv + g) * nblk + j], 1.0f / 127.0f);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -300,7 +338,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
 #pragma unroll
         for (int e = 0; e < CW; e += 2) {
           float a0, a1;
-          unpack2(fma2(o[(c * CW + e) >> 1], pack2(alpha_prev, alpha_prev), pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1]))), a0, a1);
+          unpack2(fma2(o[(c * CW + e) >> 1], pack2(alpha_prev, alpha_prev), pack2(pv_val(v[e]), pv_val(v[e + 1]))), a0, a1);
           pk[e >> 1] = pack_bf16(__fdiv_rn(a0, l_tot), __fdiv_rn(a1, l_tot));
         }
         if (in_range) {
@@ -714,6 +752,62 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, long ldd
   }
 }
 
+// One CTA per (128-key block, KV head, batch): step = max(max|V| / 127, FLT_MIN) over the block, V_q = clamp(rint(V / step)).
+template <int D>
+__global__ void quant_v_kernel(const __nv_bfloat16* __restrict__ qkv, long ldqkv, int vcol0, int8_t* __restrict__ vq, long ldvq,
+                               float* __restrict__ vstep, int T, int Hkv) {
+  __shared__ float sh[32];
+  const int blk = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int nblk = gridDim.x;
+  const int k0 = blk * BKV;
+  constexpr int VPR = D / 8;  // 16-byte vectors per row
+  float m = 0.0f;
+  for (int i = threadIdx.x; i < BKV * VPR; i += blockDim.x) {
+    const int r = i / VPR, c = (i % VPR) * 8;
+    if (k0 + r >= T) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + ((long)b * T + k0 + r) * ldqkv + vcol0 + g * D + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      m = fmaxf(m, fabsf(__uint_as_float(w[e] << 16)));
+      m = fmaxf(m, fabsf(__uint_as_float(w[e] & 0xFFFF0000u)));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = 0.0f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, sh[w]);
+  const float step = fmaxf(__fmul_rn(m, 1.0f / 127.0f), 1.17549435e-38f);
+  if (threadIdx.x == 0) vstep[((long)b * Hkv + g) * nblk + blk] = step;
+  for (int i = threadIdx.x; i < BKV * VPR; i += blockDim.x) {
+    const int r = i / VPR, c = (i % VPR) * 8;
+    if (k0 + r >= T) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + ((long)b * T + k0 + r) * ldqkv + vcol0 + g * D + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float f = (e & 1) ? __uint_as_float(w[e >> 1] & 0xFFFF0000u) : __uint_as_float(w[e >> 1] << 16);
+      const int qv = (int)fminf(fmaxf(rintf(__fdiv_rn(f, step)), -127.0f), 127.0f);
+      o[e >> 2] |= (uint32_t)(qv & 0xFF) << (8 * (e & 3));
+    }
+    *reinterpret_cast<uint2*>(vq + ((long)b * T + k0 + r) * ldvq + g * D + c) = make_uint2(o[0], o[1]);
+  }
+}
+
+CUresult encode_3d_u8(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T, uint64_t B, uint64_t ld_bytes) {
+  static PFN_encodeTiled fn = get_encode_tiled();
+  if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+  cuuint64_t dims[3] = {cols, T, B};
+  cuuint64_t strides[2] = {ld_bytes, T * ld_bytes};
+  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
 CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T, uint64_t B, uint64_t ld_elems) {
   static PFN_encodeTiled fn = get_encode_tiled();
   if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
@@ -750,16 +844,40 @@ extern "C" int otb_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldq
   dim3 grid((T + BQ - 1) / BQ, H, B);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) {
-    static int once = set_smem(attn_fwd_kernel<128>, attn_smem_bytes<128>());
+    static int once = set_smem(attn_fwd_kernel<128, false>, attn_smem_bytes<128>());
     if (once) return once;
-    attn_fwd_kernel<128><<<grid, ATT_THREADS, attn_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
-                                                                           window, scale, c_log2, status);
+    attn_fwd_kernel<128, false><<<grid, ATT_THREADS, attn_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
+                                                                                  window, scale, c_log2, nullptr, status);
   } else {
-    static int once = set_smem(attn_fwd_kernel<64>, attn_smem_bytes<64>());
+    static int once = set_smem(attn_fwd_kernel<64, false>, attn_smem_bytes<64>());
     if (once) return once;
-    attn_fwd_kernel<64><<<grid, ATT_THREADS, attn_smem_bytes<64>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
-                                                                         window, scale, c_log2, status);
+    attn_fwd_kernel<64, false><<<grid, ATT_THREADS, attn_smem_bytes<64>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
+                                                                                window, scale, c_log2, nullptr, status);
   }
+  return (int)cudaGetLastError();
+}
+
+// Forward with P V on the int8 tensor cores (head_dim 128 only). vq: int8 scratch [B*T, Hkv*D]; vstep: fp32 scratch
+// [B, Hkv, ceil(T/128)]; both are written here (the per-block value quantisation) and read by the attention kernel.
+extern "C" int otb_attn_fwd_i8pv(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, void* vq,
+                                 float* vstep, int B, int T, int H, int Hkv, int D, int window, float scale, uint32_t* status,
+                                 void* stream) {
+  if (D != 128 || H % Hkv || (ldqk & 7) || (ldqkv & 7) || (ldo & 7)) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nblk = (T + BKV - 1) / BKV;
+  const long ldvq = (long)Hkv * D;
+  quant_v_kernel<128><<<dim3(nblk, Hkv, B), 256, 0, s>>>((const __nv_bfloat16*)qkv, ldqkv, (H + Hkv) * D, (int8_t*)vq, ldvq, vstep, T, Hkv);
+  CUtensorMap tq, tv;
+  CUresult r = encode_3d(&tq, qk, (uint64_t)ldqk, (uint64_t)T, (uint64_t)B, (uint64_t)ldqk);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_3d_u8(&tv, vq, (uint64_t)ldvq, (uint64_t)T, (uint64_t)B, (uint64_t)ldvq);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  dim3 grid((T + BQ - 1) / BQ, H, B);
+  static int once = set_smem(attn_fwd_kernel<128, true>, attn_smem_bytes<128>());
+  if (once) return once;
+  attn_fwd_kernel<128, true><<<grid, ATT_THREADS, attn_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv, window,
+                                                                               scale, c_log2, vstep, status);
   return (int)cudaGetLastError();
 }
 

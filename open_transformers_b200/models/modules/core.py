@@ -220,6 +220,20 @@ class _GQABase(nn.Module, ParamMixin):
             self.q_norm = RMSNorm(head_dim, eps)
             self.k_norm = RMSNorm(head_dim, eps)
 
+    def _int8_pv(self, qkv) -> bool:
+        """``attn_int8_pv`` selects the int8 P V forward where the kernels exist (bf16 activations, head_dim 128);
+        other shapes keep the float P V kernels and say so once."""
+        if not self.attn_int8_pv:
+            return False
+        if K.int8_pv_supported(qkv.dtype, self.head_dim):
+            return True
+        if not getattr(_GQABase, "_warned_int8_pv", False):
+            _GQABase._warned_int8_pv = True
+            import logging
+            logging.getLogger(__name__).warning("attn_int8_pv needs bf16 activations and head_dim 128 (got %s, %d): float P V kernels used",
+                                                qkv.dtype, self.head_dim)
+        return False
+
     def _qkv(self, x):
         if isinstance(self.wq, QuantLinear) and self.wq.qat_active:
             return torch.cat([self.wq(x), self.wk(x), self.wv(x)], -1)
@@ -238,9 +252,9 @@ class _GQABase(nn.Module, ParamMixin):
             q = self.q_norm(q.reshape(B, T, H, D)).reshape(B, T, H * D)
             k = self.k_norm(k.reshape(B, T, Hkv, D)).reshape(B, T, Hkv * D)
             qkv = torch.cat([q, k, v], -1)
-            o = A.attention(qkv, cos, sin, H, Hkv, D, self.window, False, self.eps)
+            o = A.attention(qkv, cos, sin, H, Hkv, D, self.window, False, self.eps, self._int8_pv(qkv))
         else:
-            o = A.attention(qkv, cos, sin, H, Hkv, D, self.window, self.qk_norm, self.eps)
+            o = A.attention(qkv, cos, sin, H, Hkv, D, self.window, self.qk_norm, self.eps, self._int8_pv(qkv))
         return self.wo(o, residual)
 
 

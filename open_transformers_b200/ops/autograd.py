@@ -127,11 +127,12 @@ class AttentionFn(Function):
     activation [B, T, (H + 2 Hkv) D]; returns [B, T, H D]."""
 
     @staticmethod
-    def forward(ctx, qkv, cos, sin, H, Hkv, D, window, qk_norm, eps):
+    def forward(ctx, qkv, cos, sin, H, Hkv, D, window, qk_norm, eps, int8_pv=False):
         B, T, _ = qkv.shape
         q2 = qkv.reshape(B * T, -1)
         qk, rstd = K.qknorm_rope_fwd(q2, cos, sin, H + Hkv, D, T, qk_norm, eps)
-        O, lse = K.attn_fwd(qk, q2, B, T, H, Hkv, D, window)
+        # int8 P V: quantised forward, straight-through (float shadow) backward through the ordinary kernels
+        O, lse = K.attn_fwd(qk, q2, B, T, H, Hkv, D, window, int8_pv)
         ctx.save_for_backward(q2, qk, rstd, O, lse, cos, sin)
         ctx.cfg = (B, T, H, Hkv, D, window, qk_norm)
         return O.view(B, T, H * D)
@@ -147,11 +148,11 @@ class AttentionFn(Function):
         dqkv = torch.empty_like(q2)
         K.attn_bwd(qk, q2, O, dO2, lse, dqk, dqkv, B, T, H, Hkv, D, window)
         K.qknorm_rope_bwd(dqk, q2, rstd, dqkv, cos, sin, H + Hkv, D, T, qk_norm)
-        return dqkv.view(B, T, -1), None, None, None, None, None, None, None, None
+        return dqkv.view(B, T, -1), None, None, None, None, None, None, None, None, None
 
 
-def attention(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps):
-    return AttentionFn.apply(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps)
+def attention(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps, int8_pv=False):
+    return AttentionFn.apply(qkv, cos, sin, H, Hkv, D, window, qk_norm, eps, int8_pv)
 
 
 class EmbeddingFn(Function):

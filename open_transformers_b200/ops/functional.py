@@ -122,12 +122,30 @@ def qknorm_rope_bwd(dout, qkv, rstd, din, cos, sin, heads: int, D: int, seq_len:
     return din
 
 
-def attn_fwd(qk, qkv, B: int, T: int, H: int, Hkv: int, D: int, window: int):
+def int8_pv_supported(dtype: torch.dtype, D: int) -> bool:
+    """The int8 P V kernels take bf16 activations and 128-wide heads (one 128-byte value row per key)."""
+    return dtype == torch.bfloat16 and D == 128
+
+
+def attn_fwd(qk, qkv, B: int, T: int, H: int, Hkv: int, D: int, window: int, int8_pv: bool = False):
     """qk: [B*T, (H+Hkv)*D] rotated queries+keys; qkv: [B*T, (H+2Hkv)*D] (values read from it).
-    Returns O [B*T, H*D] and the row statistic lse [B,H,T] (log2 domain)."""
+    Returns O [B*T, H*D] and the row statistic lse [B,H,T] (log2 domain). ``int8_pv``: P V on the int8 tensor
+    cores with per-block value quantisation (reference int8pv_causal_flash_attention, attention_repop.py:52)."""
     O = torch.empty((B * T, H * D), dtype=qk.dtype, device=qk.device)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=qk.device)
     scale = 1.0 / math.sqrt(D)
+    if int8_pv:
+        if not int8_pv_supported(qk.dtype, D):
+            raise ValueError("int8 P V attention needs bf16 activations and head_dim 128 (got %s, %d)" % (qk.dtype, D))
+        if qk.is_cuda:
+            vq = torch.empty((B * T, Hkv * D), dtype=torch.int8, device=qk.device)
+            vstep = torch.empty((B, Hkv, (T + 127) // 128), dtype=torch.float32, device=qk.device)
+            check(cuda_lib().otb_attn_fwd_i8pv(P(qk), L(_ld(qk)), P(qkv), L(_ld(qkv)), P(O), L(_ld(O)), P(lse), P(vq), P(vstep), I(B), I(T),
+                                               I(H), I(Hkv), I(D), I(window), F(scale), P(_status(qk.device)), stream_ptr()), "attn_fwd_i8pv")
+        else:
+            check(cpu_lib().otb_cpu_attn_fwd_i8pv(P(qk), L(_ld(qk)), P(qkv), L(_ld(qkv)), P(O), L(_ld(O)), P(lse), I(B), I(T), I(H), I(Hkv),
+                                                  I(D), I(window), F(scale)), "cpu_attn_fwd_i8pv")
+        return O, lse
     if qk.is_cuda:
         lib = cuda_lib()
         if is_bf16(qk):

@@ -203,3 +203,53 @@ def test_gpu_qat_engine_matches_cpu_hashes(mixed):
 
     cpu, gpu = run("cpu"), run("cuda")
     assert [h for _, _, h in cpu] == [h for _, _, h in gpu], (cpu, gpu)
+
+
+# ------------------------------------------------------------------------------ int8 P V attention
+def _attn_inputs(T=300, H=4, Hkv=2, D=128, seed=12):
+    g = torch.Generator().manual_seed(seed)
+    qk = torch.randn(T, (H + Hkv) * D, generator=g).bfloat16()
+    qkv = torch.randn(T, (H + 2 * Hkv) * D, generator=g).bfloat16()
+    return qk, qkv
+
+
+@pytest.mark.parametrize("window", [0, 160])
+def test_int8_pv_attention_is_close_to_the_float_kernel(window):
+    qk, qkv = _attn_inputs()
+    O0, l0 = K.attn_fwd(qk, qkv, 1, 300, 4, 2, 128, window)
+    O1, l1 = K.attn_fwd(qk, qkv, 1, 300, 4, 2, 128, window, int8_pv=True)
+    assert torch.equal(l0, l1)  # softmax statistics stay fp32 on the unquantised probabilities
+    err = (O0.float() - O1.float()).abs().max().item()
+    assert 0 < err < 0.05 * O0.float().abs().max().item()
+    with pytest.raises(ValueError):
+        K.attn_fwd(qk.float(), qkv.float(), 1, 300, 4, 2, 128, window, int8_pv=True)
+
+
+def test_int8_pv_module_trains_with_the_float_shadow_backward():
+    from open_transformers_b200.models.modules.core import GQAQKNorm
+    from open_transformers_b200.ops import functional as KK
+
+    torch.manual_seed(0)
+    m = GQAQKNorm(256, 2, 1, 128, attn_int8_pv=True, qk_norm_gain=False).to(torch.bfloat16)
+    ref = GQAQKNorm(256, 2, 1, 128, attn_int8_pv=False, qk_norm_gain=False).to(torch.bfloat16)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.copy_(torch.randn_like(p.float()).mul(0.05))
+    ref.load_state_dict(m.state_dict())
+    cos, sin = KK.rope_tables(128, 128, 10000.0, "cpu")
+    x = torch.randn(1, 128, 256).bfloat16().requires_grad_(True)
+    y = m(x, cos, sin)
+    y.float().square().sum().backward()
+    y0 = ref(x.detach(), cos, sin)
+    assert not torch.equal(y, y0) and (y.float() - y0.float()).abs().max() < 0.05 * y0.float().abs().max() + 1e-3
+    assert torch.isfinite(x.grad.float()).all() and x.grad.float().abs().sum() > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("window,T", [(0, 300), (160, 512)])
+def test_gpu_int8_pv_attention_bitwise_vs_twin(window, T):
+    qk, qkv = _attn_inputs(T=2 * T)
+    cpu = K.attn_fwd(qk, qkv, 2, T, 4, 2, 128, window, int8_pv=True)
+    gpu = K.attn_fwd(qk.cuda(), qkv.cuda(), 2, T, 4, 2, 128, window, int8_pv=True)
+    _eq(cpu, gpu, "int8 P V attention")
+    assert K.kernel_status("cuda") == 0
