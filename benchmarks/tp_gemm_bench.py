@@ -83,7 +83,8 @@ def main():
     # ---- all-gather -> GEMM
     for name, N in (("qkv", a.qkv), ("gate_up", 2 * a.ffn)):
         Np = N // P
-        x_shard = torch.randn(M // P, d, generator=g).bfloat16().to(dev)
+        x_shard = ws.site(name, M, d).full[rows]  # the producing kernel writes its rows straight into the gathered buffer
+        x_shard.copy_(torch.randn(M // P, d, generator=g).bfloat16())
         w = (torch.randn(Np, d, generator=g) * 0.02).bfloat16().to(dev)
         x_full = torch.empty(M, d, dtype=torch.bfloat16, device=dev)
 

@@ -97,6 +97,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     from ..train.checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
     from ..train.engine import TrainEngine
     from ..train.spike_protocol import SpikeProtocol
+    from ..train.qk_gain_control import clamp_qk_gains, zero_q_gain_grads
     from .cpu_threads import configure_cpu_threads
 
     expected = resolve_expect_hash(expect_hash)
@@ -191,6 +192,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         for _, _, c in ces:
             total += c
         loss_mean = total / max(len(ces), 1)
+        zero_q_gain_grads(engine.named_grads(), step, tr.qk_freeze_q_gains_until_step)  # mirrors train/loop.py
         if spike.should_skip(grad_norm, loss_mean, step):
             try:
                 spike.record_skip(step)
@@ -199,6 +201,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             engine.skip_step()
         else:
             engine.optimizer_step(lr, engine.clip_coefficient(grad_norm, tr.grad_clip))
+            clamp_qk_gains(engine.model, tr.qk_gain_clamp)
         consumed += plan.tokens_this_step
         step += 1
         r0 = [c for v, _, c in ces if v == 0]

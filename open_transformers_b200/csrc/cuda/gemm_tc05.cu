@@ -132,13 +132,14 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int p = 0; p < tp.P; ++p) {
           if (p == tp.rank) continue;
           uint4* dst = tp.ag_dst[p] + (long)blk * tp.ag_block_u4;
-          for (long i = threadIdx.x; i < tp.ag_block_u4; i += 4 * blockDim.x) {
-            uint4 v[4];
+          // 16 independent 16-byte loads per thread in flight (48 KB per CTA), then the peer stores
+          for (long i = threadIdx.x; i < tp.ag_block_u4; i += 16 * blockDim.x) {
+            uint4 v[16];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 16; ++u)
               if (i + u * blockDim.x < tp.ag_block_u4) v[u] = __ldg(src + i + u * blockDim.x);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 16; ++u)
               if (i + u * blockDim.x < tp.ag_block_u4) dst[i + u * blockDim.x] = v[u];
           }
         }
@@ -305,17 +306,20 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const float* src = tp.inbox + row * tp.ld_in + (long)tn * BN;
           const uint32_t tdst = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-          for (int c = 0; c < BN; c += 32) {
-            uint32_t v[32];
+          for (int c = 0; c < BN; c += 64) {
+            uint32_t v[2][32];  // 16 independent 16-byte loads in flight per thread
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // columns past N (N % 4 == 0) are never stored
-              if (tn * BN + c + 4 * j + 4 <= N)
-                f = __ldcg(reinterpret_cast<const float4*>(src + c) + j);  // L2 only: written by a peer GPU
-              v[4 * j] = __float_as_uint(f.x); v[4 * j + 1] = __float_as_uint(f.y);
-              v[4 * j + 2] = __float_as_uint(f.z); v[4 * j + 3] = __float_as_uint(f.w);
-            }
-            tmem_st_32x32b_x32(tdst + c, v);
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // columns past N (N % 4 == 0) are never stored
+                if (tn * BN + c + u * 32 + 4 * j + 4 <= N)
+                  f = __ldcg(reinterpret_cast<const float4*>(src + c + u * 32) + j);  // L2 only: written by a peer GPU
+                v[u][4 * j] = __float_as_uint(f.x); v[u][4 * j + 1] = __float_as_uint(f.y);
+                v[u][4 * j + 2] = __float_as_uint(f.z); v[u][4 * j + 3] = __float_as_uint(f.w);
+              }
+            tmem_st_32x32b_x32(tdst + c, v[0]);
+            tmem_st_32x32b_x32(tdst + c + 32, v[1]);
           }
           tmem_st_wait();
           tc_fence_before();

@@ -113,7 +113,9 @@ class TpWorkspace:
         M = rows * self.P
         N = w.shape[1] if b_mn else w.shape[0]
         s = self.site(key, M, K)
-        s.full[self.shard_rows(M)].copy_(x_shard)
+        mine = s.full[self.shard_rows(M)]
+        if x_shard.data_ptr() != mine.data_ptr():  # a producer may write its rows straight into ``site(...).full``
+            mine.copy_(x_shard)
         s.seq += 1
         C = torch.empty((M, N), dtype=out_dtype, device=self.device)
         epi = 0 if out_dtype == torch.bfloat16 else 1

@@ -21,6 +21,13 @@ def clamp_qk_gains(model, max_gain: float) -> int:
         for _, p in _gains(model, which):
             p.clamp_(max=max_gain)
             n += 1
+    # the compute-dtype copies that the forward pass reads (installed by the training engine) follow on every rank
+    for mod in model.modules():
+        cw = getattr(mod, "_compute_weight", None)
+        if cw is not None and type(mod).__name__ == "RMSNorm" and any(mod is getattr(parent, a, None)
+                                                                       for parent in model.modules() for a in ("q_norm", "k_norm")):
+            if cw.data_ptr() != mod.weight.data_ptr():
+                cw.clamp_(max=max_gain)
     return n
 
 

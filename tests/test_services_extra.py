@@ -1,0 +1,160 @@
+"""Smaller services around the training loop: the stand-alone z-loss, QK-gain control, global-norm clip, the audit's
+environment allow-list, CPU thread selection, the step -> document map, the interval fetcher and Muon.
+(reference test strategy: tests/test_z_loss.py, tests/test_global_clip.py, tests/test_doc_map.py,
+tests/test_fetch_interval.py, tests/test_cpu_threads.py)"""
+import json
+import math
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import tiny_cfg
+
+
+# ------------------------------------------------------------------------------------------ z-loss
+def test_z_loss_value_gradient_and_row_independence():
+    from open_transformers_b200.models.fused_loss import fused_ce_z_loss
+    from open_transformers_b200.models.z_loss import compute_z_loss, row_lse, z_loss_grad
+
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(6, 40, generator=g) * 3
+    lse = row_lse(logits)
+    assert torch.allclose(lse, torch.logsumexp(logits, -1), atol=1e-5)
+    assert torch.equal(row_lse(logits[2:5]), lse[2:5])  # a row does not depend on its neighbours
+    x = logits.clone().requires_grad_(True)
+    z = compute_z_loss(x, 1e-2)
+    z.backward()
+    y = logits.clone().requires_grad_(True)
+    zr = 1e-2 * torch.logsumexp(y, -1).square().mean()
+    zr.backward()
+    assert abs(float(z) - float(zr)) < 1e-6 and torch.allclose(x.grad, y.grad, atol=1e-6)
+    assert torch.equal(z_loss_grad(logits, 1e-2, 1.0, chunk_rows=2), z_loss_grad(logits, 1e-2, 1.0, chunk_rows=6))
+    # same bits as the z term of the fused loss
+    _, zf = fused_ce_z_loss(logits.clone(), torch.zeros(6, dtype=torch.long), 1e-2)
+    assert float(zf) == float(z)
+
+    class Off:
+        enabled, coeff = False, 1e-2
+
+    assert float(compute_z_loss(logits, Off())) == 0.0 and not compute_z_loss(x, 0.0).requires_grad
+
+
+# ------------------------------------------------------------------------------------- QK-gain control
+def test_qk_gain_clamp_and_frozen_query_gains():
+    from open_transformers_b200.models.modules.core import GQAQKNorm
+    from open_transformers_b200.train.qk_gain_control import clamp_qk_gains, zero_q_gain_grads
+
+    m = GQAQKNorm(64, 2, 1, 32)
+    with torch.no_grad():
+        m.q_norm.weight.fill_(3.0)
+        m.k_norm.weight.fill_(0.5)
+    assert clamp_qk_gains(m, 0.0) == 0 and float(m.q_norm.weight[0]) == 3.0
+    assert clamp_qk_gains(m, 2.0) == 2
+    assert float(m.q_norm.weight.max()) == 2.0 and float(m.k_norm.weight.max()) == 0.5
+    grads = {"attn.q_norm.weight": torch.ones(32), "attn.k_norm.weight": torch.ones(32), "attn.wq.weight": torch.ones(4, 4)}
+    assert zero_q_gain_grads(grads, step=3, freeze_until_step=5) == 1
+    assert float(grads["attn.q_norm.weight"].sum()) == 0.0 and float(grads["attn.k_norm.weight"].sum()) == 32.0
+    assert zero_q_gain_grads(grads, step=5, freeze_until_step=5) == 0
+
+
+# ---------------------------------------------------------------------------------------- global clip
+def test_global_norm_and_clip():
+    from open_transformers_b200.train.global_clip import clip_coefficient, clip_grads_, deterministic_global_norm
+
+    g = torch.Generator().manual_seed(1)
+    named = [("a", torch.randn(32, 8, generator=g)), ("b", torch.randn(8, generator=g)), ("c", None), ("d", torch.randn(64, 64, generator=g))]
+    norm, per = deterministic_global_norm(named, num_shards=2)
+    ref = math.sqrt(sum(float(t.double().square().sum()) for _, t in named if t is not None))
+    assert abs(norm - ref) < 1e-4 * ref and len(per) == 3
+    assert deterministic_global_norm(named, 2)[0] == norm  # same call, same bits
+    assert clip_coefficient(norm, 0.0) == 1.0 and clip_coefficient(0.5, 1.0) == 1.0
+    assert abs(clip_coefficient(4.0, 1.0) - 0.25) < 1e-6
+    pre = clip_grads_(named, 1.0, 2)
+    assert pre == norm
+    post, _ = deterministic_global_norm(named, 2)
+    assert abs(post - 1.0) < 1e-3
+
+
+# ------------------------------------------------------------------------------ audit environment allow-list
+def test_audit_env_allow_list(monkeypatch):
+    from open_transformers_b200.cli.audit_replay import AuditError, apply_kernel_env
+
+    monkeypatch.delenv("OTB_TENSOR_DIGEST", raising=False)
+    applied = apply_kernel_env({"OTB_TENSOR_DIGEST": "tree", "SOME_OTHER_KEY": "x"})
+    assert applied == {"OTB_TENSOR_DIGEST": "tree"} and os.environ["OTB_TENSOR_DIGEST"] == "tree" and "SOME_OTHER_KEY" not in os.environ
+    for bad in ("LD_PRELOAD", "PYTHONPATH", "OTB_LIB_DIR", "OTB_CXX"):
+        with pytest.raises(AuditError):
+            apply_kernel_env({bad: "/tmp/evil"})
+
+
+# ----------------------------------------------------------------------------------------- cpu threads
+def test_cpu_threads_parsing():
+    from open_transformers_b200.cli.cpu_threads import available_cpus, configure_cpu_threads, parse_cpu_threads
+
+    assert parse_cpu_threads("auto") == available_cpus() >= 1 and parse_cpu_threads(None) == available_cpus()
+    assert parse_cpu_threads("3") == 3 and parse_cpu_threads(2) == 2
+    for bad in ("0", -1):
+        with pytest.raises(ValueError):
+            parse_cpu_threads(bad)
+    before = torch.get_num_threads()
+    assert configure_cpu_threads(1) == 1 and os.environ["OMP_NUM_THREADS"] == "1"
+    configure_cpu_threads(before)
+
+
+# ------------------------------------------------------------------------- doc map and interval fetcher
+def test_doc_map_covers_every_window_slot_and_fetch_interval_brings_only_touched_shards(tmp_path):
+    import pyarrow.parquet as pq
+
+    from open_transformers_b200.data.doc_map import COLUMNS, write_doc_map
+    from open_transformers_b200.data.fetch_interval import DirMirror, fetch_audit_interval
+    from open_transformers_b200.data.loader import build_global_loader
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path)
+    cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=1"])
+    V = cfg.run.virtual_dp_size or 2
+    loader = build_global_loader(cfg, list(range(V)), V, data_root=tmp)
+    out = tmp_path / "doc_map.parquet"
+    n = write_doc_map(loader, 2, V, out)
+    tab = pq.read_table(str(out)).to_pandas()
+    assert list(tab.columns) == COLUMNS and len(tab) == n > 0
+    per_step = cfg.train.global_batch_tokens.warmup // cfg.train.seq_len
+    assert set(tab["step"]) == {0, 1}
+    # every window slot of every micro-batch is covered by document pieces that add up to seq_len + 1 tokens or less
+    grp = tab.groupby(["step", "microbatch", "slot"])["length"].sum()
+    assert len(grp) == 2 * per_step and int(grp.max()) <= cfg.train.seq_len + 1 and int(grp.min()) > 0
+    assert set(tab["dp_rank"]) <= set(range(V))
+
+    res = train(cfg, device="cpu", data_root=tmp, max_steps=2)
+    ck = Path(res["run_dir"]) / "checkpoints" / "step_000000001"
+    dest = tmp_path / "fetched"
+    fetch_audit_interval(ck, DirMirror(tmp), dest, until_step=2)
+    from open_transformers_b200.cli.audit_replay import audit_replay
+
+    r = audit_replay(str(ck), data_root=str(dest), until_step=2, expect_hash=res["hashes"][-1][1])
+    assert r["match"] is True
+
+
+# ------------------------------------------------------------------------------------------------ Muon
+def test_muon_orthogonalises_and_the_aux_optimizer_takes_the_rest():
+    from open_transformers_b200.optim.muon import Muon, MuonWithAuxAdamW, newton_schulz5
+
+    g = torch.Generator().manual_seed(2)
+    G = torch.randn(32, 16, generator=g)
+    O = newton_schulz5(G)
+    sv = torch.linalg.svdvals(O)
+    assert float(sv.max()) < 1.3 and float(sv.min()) > 0.3  # singular values pushed toward one
+    w = torch.nn.Parameter(torch.randn(8, 8, generator=g))
+    b = torch.nn.Parameter(torch.zeros(8))
+    from open_transformers_b200.config.schema import OptimConfig
+
+    opt = MuonWithAuxAdamW([("blocks.0.w", w), ("blocks.0.b", b)], OptimConfig(), muon_lr=0.02)
+    (w.sum() + b.sum()).backward()
+    before = w.detach().clone()
+    opt.step()
+    opt.zero_grad()
+    assert not torch.equal(before, w.detach()) and float(b.detach().abs().sum()) > 0
+    assert isinstance(opt.muon, Muon)
