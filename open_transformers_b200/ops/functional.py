@@ -11,6 +11,7 @@ import math
 
 import torch
 
+from . import native as _native
 from .native import D as _D, F, I, L, P, check, cpu_lib, cuda_lib, is_bf16, stream_ptr
 
 _status_words: dict[int, torch.Tensor] = {}
@@ -60,7 +61,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         lib = cuda_lib()
         if bf:
             check(lib.otb_gemm_bf16(P(a), P(b), P(out), P(residual), I(M), I(N), I(K), L(_ld(a)), L(_ld(b)), L(_ld(out)),
-                                    L(ldr), I(a_mn), I(b_mn), I(epi), P(_status(a.device)), I(0), stream_ptr()), "gemm_bf16")
+                                    L(ldr), I(a_mn), I(b_mn), I(epi), P(_status(a.device)), I(0), stream_ptr()),
+                  "gemm_bf16" if _native._timing is None else "gemm_bf16 %dx%dx%d %s%s epi%d" % (M, N, K, "tn"[a_mn], "tn"[b_mn], epi))
         else:
             check(lib.otb_gemm_f32(P(a), P(b), P(out), P(residual), I(M), I(N), I(K), L(_ld(a)), L(_ld(b)), L(_ld(out)),
                                    L(ldr), I(a_mn), I(b_mn), I(epi), stream_ptr()), "gemm_f32")
@@ -150,7 +152,8 @@ def attn_fwd(qk, qkv, B: int, T: int, H: int, Hkv: int, D: int, window: int, int
         lib = cuda_lib()
         if is_bf16(qk):
             check(lib.otb_attn_fwd(P(qk), L(_ld(qk)), P(qkv), L(_ld(qkv)), P(O), L(_ld(O)), P(lse), I(B), I(T), I(H), I(Hkv), I(D),
-                                   I(window), F(scale), P(_status(qk.device)), stream_ptr()), "attn_fwd")
+                                   I(window), F(scale), P(_status(qk.device)), stream_ptr()),
+                  "attn_fwd" if _native._timing is None else "attn_fwd w%d" % window)
         else:
             check(lib.otb_attn_f32_fwd(P(qk), L(_ld(qk)), P(qkv), L(_ld(qkv)), P(O), L(_ld(O)), P(lse), I(B), I(T), I(H), I(Hkv),
                                        I(D), I(window), F(scale), stream_ptr()), "attn_f32_fwd")
@@ -169,7 +172,8 @@ def attn_bwd(qk, qkv, O, dO, lse, dqk, dqkv, B: int, T: int, H: int, Hkv: int, D
     if qk.is_cuda:
         lib = cuda_lib()
         if is_bf16(qk):
-            check(lib.otb_attn_bwd(*common, P(_status(qk.device)), stream_ptr()), "attn_bwd")
+            check(lib.otb_attn_bwd(*common, P(_status(qk.device)), stream_ptr()),
+                  "attn_bwd" if _native._timing is None else "attn_bwd w%d" % window)
         else:
             check(lib.otb_attn_f32_bwd(*common, stream_ptr()), "attn_f32_bwd")
     else:

@@ -78,12 +78,48 @@ class NativeError(RuntimeError):
 
 launch_count = 0  # native entry points called so far (each launches one to three kernels)
 
+# Per-entry-point device timing (OTB_KERNEL_TIMING=1 or ``start_timing()``): one CUDA event is recorded after
+# every native call; the time between two consecutive events is charged to the later call, so PyTorch ops issued
+# between two native calls (views, small copies) are charged to the call that follows them. Resolved once, at
+# ``timing_report()``, after a device synchronise - the step itself is never synchronised by the tracer.
+# (counterpart of the reference's PRETRAIN_CUDA_EVENT_TIMING phase timers, src/pretrain/train/loop.py:733-743)
+_timing: list | None = [] if os.environ.get("OTB_KERNEL_TIMING") == "1" else None
+
+
+def start_timing() -> None:
+    global _timing
+    _timing = []
+
+
+def timing_report(reset: bool = True) -> dict[str, tuple[int, float]]:
+    """{entry point: (calls, milliseconds)} since ``start_timing()``; ends the trace when ``reset``."""
+    global _timing
+    out: dict[str, tuple[int, float]] = {}
+    if _timing:
+        torch.cuda.synchronize()
+        for (_, e0), (what, e1) in zip(_timing[:-1], _timing[1:]):
+            n, ms = out.get(what, (0, 0.0))
+            out[what] = (n + 1, ms + e0.elapsed_time(e1))
+    if reset:
+        _timing = None
+    return out
+
+
+def mark(what: str) -> None:
+    """Close the current interval under the name ``what`` (for PyTorch-side phases between native calls)."""
+    if _timing is not None and torch.cuda.is_available():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        _timing.append((what, e))
+
 
 def check(rc: int, what: str) -> None:
     global launch_count
     launch_count += 1
     if rc != 0:
         raise NativeError("%s failed with code %d" % (what, rc))
+    if _timing is not None:
+        mark(what)
 
 
 def is_bf16(t: torch.Tensor) -> int:
