@@ -87,6 +87,57 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, u
   for (int c = 0; c < D / 64; ++c) tma_load_3d(dst + c * 16384, tm, bar, col + c * 64, row, b);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// key kj is hidden from query qi (causal, and the sliding window when window > 0)
+__device__ __forceinline__ bool key_hidden(int kj, int qi, int window) { return kj > qi || (window > 0 && kj <= qi - window); }
+
+// Maximum of a thread's KPT raw scores. MASK = false is the common (fully visible) block: no position tests at all.
+template <bool MASK>
+__device__ __forceinline__ float scores_max(const uint32_t (&sv)[KPT], int kbase, int qi, int window) {
+  float mx = -INFINITY;
+  if constexpr (MASK) {
+#pragma unroll
+    for (int e = 0; e < KPT; ++e) mx = fmaxf(mx, key_hidden(kbase + e, qi, window) ? -INFINITY : __uint_as_float(sv[e]));
+  } else {
+#pragma unroll
+    for (int e = 0; e < KPT; e += 2) mx = max3(mx, __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
+  }
+  return mx;
+}
+
+// p = exp2(s * c - m) for the thread's KPT scores, packed for the P V product (bf16 pairs, or int8 quadruples when I8),
+// and the two ascending row-sum chains (even keys, odd keys) as one packed value.
+template <bool MASK, bool I8>
+__device__ __forceinline__ f2 probs_pack(const uint32_t (&sv)[KPT], float c_log2, float m_safe, int kbase, int qi, int window,
+                                         uint32_t (&pk)[KPT / 2]) {
+  const f2 c2 = pack2(c_log2, c_log2), nm2 = pack2(-m_safe, -m_safe);
+  f2 lsum2 = pack2(0.0f, 0.0f);
+#pragma unroll
+  for (int e = 0; e < KPT; e += 2) {
+    f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nm2));
+    float p0, p1;
+    unpack2(p2, p0, p1);
+    if constexpr (MASK) {
+      if (key_hidden(kbase + e, qi, window)) p0 = 0.0f;
+      if (key_hidden(kbase + e + 1, qi, window)) p1 = 0.0f;
+      p2 = pack2(p0, p1);
+    }
+    lsum2 = add2(lsum2, p2);
+    if constexpr (I8) {
+      const uint32_t q0b = (uint32_t)(int)rintf(__fmul_rn(p0, 127.0f)), q1b = (uint32_t)(int)rintf(__fmul_rn(p1, 127.0f));
+      if ((e & 3) == 0) pk[e >> 2] = 0;
+      pk[e >> 2] |= (q0b | (q1b << 8)) << (8 * (e & 3));
+    } else {
+      pk[e >> 1] = pack_bf16(p0, p1);
+    }
+  }
+  return lsum2;
+}
+
 // ---------------------------------------------------------------------------- forward
 template <int D, bool I8PV>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -204,7 +255,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
     }
   } else {
     constexpr int DH = D / NSPLIT;            // output columns per thread
-    constexpr int CW = DH >= 32 ? 32 : 16;    // TMEM columns per load of the PV accumulator
+    constexpr int CW = 16;                    // TMEM columns per load of the PV accumulator (short loads keep registers free)
     const int qd = warp & 3;
     const int part = (warp - 2) >> 2;
     const int r = qd * 32 + lane;          // row inside the tile == TMEM lane
@@ -226,24 +277,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       ok = ok && mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag);
       tc_fence_after();
       const uint32_t tSb = tS + (i & 1) * 128 + part * KPT + lane_off;
-      // the thread's 32 raw scores stay in registers for both passes
+      // the thread's 32 raw scores stay in registers for both passes; once they are there the S buffer is free
       uint32_t sv[KPT];
       if (ok) {
         tmem_ld_32x32b_x32(tSb, sv);
         tmem_ld_wait();
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(&s_empty[i & 1]);
       float mx = -INFINITY;
-      if (ok) {
-#pragma unroll
-        for (int e = 0; e < KPT; ++e) {
-          float x = __uint_as_float(sv[e]);
-          if (need_mask) {
-            const int kj = kbase + e;
-            if (kj > qi || (window > 0 && kj <= qi - window)) x = -INFINITY;
-          }
-          mx = fmaxf(mx, x);
-        }
-      }
+      if (ok) mx = need_mask ? scores_max<true>(sv, kbase, qi, window) : scores_max<false>(sv, kbase, qi, window);
       bars->xch[i & 1][part][r] = mx;
       softmax_bar();
 #pragma unroll
@@ -251,6 +295,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       const float m_new = fmaxf(m_run, __fmul_rn(mx, c_log2));
       const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = det_exp2_attn(__fadd_rn(m_run, -m_safe));
+      // probabilities and the quarter-row sum first (independent of O), while the tensor core finishes the previous P V
+      f2 lsum2 = pack2(0.0f, 0.0f);
+      uint32_t pk[KPT / 2];
+      if (ok)
+        lsum2 = need_mask ? probs_pack<true, I8PV>(sv, c_log2, m_safe, kbase, qi, window, pk)
+                          : probs_pack<false, I8PV>(sv, c_log2, m_safe, kbase, qi, window, pk);
       // deferred accumulation of the previous block's P V (its completion also frees the P buffer)
       if (i > 0) {
         ok = ok && mbar_wait(pv_full, (i - 1) & 1, abort_flag);
@@ -268,31 +318,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
           }
         }
       }
-      // probabilities, quarter-row sum (even and odd keys as two ascending chains), bf16 P into shared memory
-      f2 lsum2 = pack2(0.0f, 0.0f);
       if (ok) {
-        const f2 c2 = pack2(c_log2, c_log2), nm2 = pack2(-m_safe, -m_safe);
-        uint32_t pk[KPT / 2];
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nm2));
-          float p0, p1;
-          unpack2(p2, p0, p1);
-          if (need_mask) {
-            const int kj = kbase + e;
-            if (kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
-            if (kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
-            p2 = pack2(p0, p1);
-          }
-          lsum2 = add2(lsum2, p2);
-          if (I8PV) {
-            const uint32_t q0b = (uint32_t)(int)rintf(__fmul_rn(p0, 127.0f)), q1b = (uint32_t)(int)rintf(__fmul_rn(p1, 127.0f));
-            if ((e & 3) == 0) pk[e >> 2] = 0;
-            pk[e >> 2] |= (q0b | (q1b << 8)) << (8 * (e & 3));
-          } else {
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-        }
         if (I8PV) {
           // keys part*32 .. +31 are bytes part*32 .. +31 of the 128-byte row: chunks part*2, part*2 + 1
 #pragma unroll
@@ -317,7 +343,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0 && ok) { mbar_arrive(p_ready); mbar_arrive(&s_empty[i & 1]); }
+      if (lane == 0 && ok) mbar_arrive(p_ready);
     }
     ok = ok && mbar_wait(pv_full, (n - 1) & 1, abort_flag);
     tc_fence_after();
@@ -355,6 +381,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
   __syncthreads();
   if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 2u);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// Backward element math for a thread's KPT (score, dP) pairs: p = exp2(s * c - lse) (0 where hidden or the row is out of
+// range), ds = (p * (dp - delta)) * scale; both packed to bf16 pairs.
+template <bool MASK, bool WANT_P>
+__device__ __forceinline__ void bwd_probs(const uint32_t (&vs)[KPT], const uint32_t (&vd)[KPT], float c_log2, float lse_r, float dl_r,
+                                          float scale, bool row_ok, int kbase, int qi, int window, uint32_t (&pk)[KPT / 2],
+                                          uint32_t (&dsr)[KPT / 2]) {
+  const f2 c2 = pack2(c_log2, c_log2), nl2 = pack2(-lse_r, -lse_r), nd2 = pack2(-dl_r, -dl_r), sc2 = pack2(scale, scale);
+#pragma unroll
+  for (int e = 0; e < KPT; e += 2) {
+    f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), c2, nl2));
+    if constexpr (MASK) {
+      float p0, p1;
+      unpack2(p2, p0, p1);
+      if (!row_ok || key_hidden(kbase + e, qi, window)) p0 = 0.0f;
+      if (!row_ok || key_hidden(kbase + e + 1, qi, window)) p1 = 0.0f;
+      p2 = pack2(p0, p1);
+    }
+    const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e]), __uint_as_float(vd[e + 1])), nd2)), sc2);
+    float d0, d1;
+    unpack2(d2, d0, d1);
+    dsr[e >> 1] = pack_bf16(d0, d1);
+    if constexpr (WANT_P) {
+      float p0, p1;
+      unpack2(p2, p0, p1);
+      pk[e >> 1] = pack_bf16(p0, p1);
+    }
+  }
 }
 
 // -------------------------------------------------------- backward: dK and dV
@@ -449,12 +504,14 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       for (int i = 0; i < n && ok; ++i) {
         const int st = i % ST;
         const uint32_t aQ = smem_u32(sQ + st * TILE), aDO = smem_u32(sDO + st * TILE);
+        // S and dP of the next block run while the softmax warps work on this one (they released the buffers
+        // as soon as the values were in registers)
+        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
         if (!mbar_wait(p_ready, i & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk) mma_f16_ss(tDV, desc_mn(aP, kk), desc_mn(aDO, kk), idG, (i | kk) != 0);
         mma_commit(dv_done);
-        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
         if (!mbar_wait(ds_ready, i & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -475,38 +532,26 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       const int h = g * G + i / nqi;
       const int qb = kb + i % nqi;
       const int qi = qb * BQ + r;
-      const bool need_mask = (qb == kb) || (window > 0 && k0 < qb * BQ + BQ - window);
       const bool row_ok = qi < T;
+      const bool need_mask = (qb == kb) || (window > 0 && k0 < qb * BQ + BQ - window) || (qb * BQ + BQ > T);
       const float lse_r = row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f;
       const float dl_r = row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f;
       if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      if (i > 0) { if (!mbar_wait(dk_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
       uint32_t dsr[KPT / 2], pk[KPT / 2];
       {
         uint32_t vs[KPT], vd[KPT];
         tmem_ld_32x32b_x32(tS + lane_off + part * KPT, vs);
         tmem_ld_32x32b_x32(tDP + lane_off + part * KPT, vd);
         tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
-          if (need_mask || !row_ok) {
-            float p0, p1;
-            unpack2(p2, p0, p1);
-            const int kj = k0 + part * KPT + e;
-            if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
-            if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
-            p2 = pack2(p0, p1);
-          }
-          const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e]), __uint_as_float(vd[e + 1])), pack2(-dl_r, -dl_r))), pack2(scale, scale));
-          float p0, p1, d0, d1;
-          unpack2(p2, p0, p1);
-          unpack2(d2, d0, d1);
-          pk[e >> 1] = pack_bf16(p0, p1);
-          dsr[e >> 1] = pack_bf16(d0, d1);
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_empty);  // S and dP are in registers: the next block's products may overwrite them
+        if (need_mask) bwd_probs<true, true>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, k0 + part * KPT, qi, window, pk, dsr);
+        else bwd_probs<false, true>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, k0 + part * KPT, qi, window, pk, dsr);
       }
+      // the shared P / dS buffer is free once the previous block's dK product has read it
+      if (i > 0) { if (!mbar_wait(dk_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
       uint8_t* base = sPdS + (part >> 1) * 16384;
 #pragma unroll
       for (int w = 0; w < 4; ++w)
@@ -514,7 +559,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(p_ready); mbar_arrive(sdp_empty); }
+      if (lane == 0) mbar_arrive(p_ready);
       if (!mbar_wait(dv_done, i & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
       for (int w = 0; w < 4; ++w)
@@ -641,6 +686,8 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
       if (ok) ok = issue_sdp(0);
       for (int i = 0; i < n && ok; ++i) {
         const int st = i % ST;
+        // S and dP of the next block run while the softmax warps work on this one
+        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
         if (!mbar_wait(ds_ready, i & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * TILE);
@@ -648,7 +695,6 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
         for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tDQ, desc_k(aDS, kk), desc_mn(aK, kk), idQ, (i | kk) != 0);
         mma_commit(dq_done);
         mma_commit(&kv_empty[st]);
-        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
       }
     }
   } else {
@@ -666,33 +712,23 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
     for (int i = 0; i < n && ok; ++i) {
       const int j = jmin + i;
       const int kbase = j * BKV + part * KPT;
-      const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window);
+      const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window) || (q0 + BQ > T);
       if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      if (i > 0) { if (!mbar_wait(dq_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
       uint32_t pk[KPT / 2];
       {
-        uint32_t vs[KPT], vd[KPT];
+        uint32_t vs[KPT], vd[KPT], unused[KPT / 2];
         tmem_ld_32x32b_x32(tS + lane_off + part * KPT, vs);
         tmem_ld_32x32b_x32(tDP + lane_off + part * KPT, vd);
         tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < KPT; e += 2) {
-          f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), pack2(c_log2, c_log2), pack2(-lse_r, -lse_r)));
-          if (need_mask || !row_ok) {
-            float p0, p1;
-            unpack2(p2, p0, p1);
-            const int kj = kbase + e;
-            if (!row_ok || kj > qi || (window > 0 && kj <= qi - window)) p0 = 0.0f;
-            if (!row_ok || kj + 1 > qi || (window > 0 && kj + 1 <= qi - window)) p1 = 0.0f;
-            p2 = pack2(p0, p1);
-          }
-          const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e]), __uint_as_float(vd[e + 1])), pack2(-dl_r, -dl_r))), pack2(scale, scale));
-          float d0, d1;
-          unpack2(d2, d0, d1);
-          pk[e >> 1] = pack_bf16(d0, d1);
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_empty);  // S and dP are in registers: the next block's products may overwrite them
+        if (need_mask) bwd_probs<true, false>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, kbase, qi, window, unused, pk);
+        else bwd_probs<false, false>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, kbase, qi, window, unused, pk);
       }
+      // the dS buffer is free once the previous block's dQ product has read it
+      if (i > 0) { if (!mbar_wait(dq_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
       uint8_t* base = sDS + (part >> 1) * 16384;
 #pragma unroll
       for (int w = 0; w < 4; ++w)
@@ -700,7 +736,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(ds_ready); mbar_arrive(sdp_empty); }
+      if (lane == 0) mbar_arrive(ds_ready);
     }
     if (ok && mbar_wait(dq_done, (n - 1) & 1, abort_flag)) {
       tc_fence_after();
