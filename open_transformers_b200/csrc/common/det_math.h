@@ -191,19 +191,17 @@ DET_HD float det_exp_attn(float x) {
 // 2^max(y, -126) for the attention kernels, y <= ~1. The clamp keeps the result a normal number (so the scaling is
 // an exact exponent add) and makes the function branch-free; an input of -inf gives 2^-126, so MASKED scores are
 // zeroed by the caller, not here. Round-to-nearest-integer by the 1.5*2^23 trick (two exact adds), r = y - k exact,
-// degree-6 polynomial for 2^r on |r| <= 1/2, then k is added to the exponent field: (bits(t) << 23) is k << 23
+// degree-4 polynomial for 2^r on |r| <= 1/2, then k is added to the exponent field: (bits(t) << 23) is k << 23
 // because the magic constant's own bits shift out.
 DET_HD float det_exp2_attn(float y) {
   const float yc = fmaxf(y, -126.0f);
   const float t = det_addf(yc, 12582912.0f);
   const float kf = det_addf(t, -12582912.0f);
   const float r = det_fmaf(kf, -1.0f, yc);
-  float p = 1.5403530393381606e-4f;
-  p = det_fmaf(p, r, 1.3333558146428443e-3f);
-  p = det_fmaf(p, r, 9.6181291076284772e-3f);
-  p = det_fmaf(p, r, 5.5504108664821580e-2f);
-  p = det_fmaf(p, r, 2.4022650695910071e-1f);
-  p = det_fmaf(p, r, 6.9314718055994531e-1f);
+  float p = 9.582852944731712e-3f;  // degree-4 minimax of 2^r on [-1/2, 1/2] with p(0) = 1: relative error 2.9e-6
+  p = det_fmaf(p, r, 5.5906426161527634e-2f);
+  p = det_fmaf(p, r, 2.4024099111557007e-1f);
+  p = det_fmaf(p, r, 6.931241750717163e-1f);
   p = det_fmaf(p, r, 1.0f);
   return det_u2f(det_f2u(p) + (det_f2u(t) << 23));
 }
