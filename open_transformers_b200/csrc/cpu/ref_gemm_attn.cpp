@@ -110,7 +110,8 @@ int attn_fwd_tc(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O,
               const int kj = j * 128 + e;
               vcol[e] = kj < T ? ldb(qkv, ((long)b * T + kj) * ldqkv + (long)(H + Hkv + g) * D + d) : 0.0f;
             }
-            o[d] = det_fmaf(o[d], alpha, tcmodel::dot(p, vcol, 128));
+            // the accumulator stays in tensor memory: scaled in place, then the block's 8 k-steps add to it
+            o[d] = tcmodel::dot(p, vcol, 128, j > jmin ? o[d] * alpha : 0.0f);
           }
         }
         m_run = m_new;

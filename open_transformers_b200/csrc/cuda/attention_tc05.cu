@@ -383,6 +383,247 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
+// ------------------------------------------------- forward, two query tiles per CTA
+// The bf16 forward. One CTA owns TWO adjacent 128-row query tiles (A, B) of one (batch, head) and walks the key blocks
+// both need; warp 0 loads K and V once for both tiles, warp 1 issues every tensor-core product, warps 2..5 are tile A's
+// softmax (ONE THREAD PER ROW, so no value ever crosses threads) and warps 6..9 tile B's. While one tile's softmax
+// runs, the tensor core works for the other tile. Tensor memory: S_A | S_B | O_A | O_B, 128 columns each.
+//   S = Q K^T lands in S_X; the row's thread reads it twice (maximum, then probabilities) and overwrites its first 64
+//   columns with P as bf16 pairs, which is the A operand of P V (tcgen05.mma with A in tensor memory); O_X is the
+//   accumulator of P V over all key blocks: before block i > first the thread multiplies its O row by
+//   alpha = exp2(m_old - m_new) in place (skipped, with identical bits, when alpha == 1 for the whole warp), then the
+//   tensor core adds the block's 8 k-steps to it. The row sum keeps the four 32-key quarter chains of the CPU twin.
+constexpr int F2_THREADS = 64 + 256;
+
+struct Bars2 {
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2];
+  uint32_t tmem_slot;
+  uint32_t abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(F2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                 __nv_bfloat16* __restrict__ O, long ldo, float* __restrict__ lse_out, int T, int H, int Hkv, int window,
+                 float c_log2, uint32_t* __restrict__ status) {
+  constexpr int TILE = BQ * D * 2;
+  constexpr int ST = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;                  // [2] tiles A, B
+  uint8_t* sK = sQ + 2 * TILE;         // [ST]
+  uint8_t* sV = sK + ST * TILE;        // [ST]
+  Bars2* bars = reinterpret_cast<Bars2*>(sV + ST * TILE);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (T + BQ - 1) / BQ;
+  const int pr = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy pairs first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (H / Hkv);
+  const int tile0 = 2 * pr;
+  const bool hasB = tile0 + 1 < nq;
+  // key-block range [jlo_X, jhi_X] of tile X; the CTA walks [jlo_A, jhi_B] (jlo_A <= jlo_B, jhi_A < jhi_B)
+  auto jlo_of = [&](int t) { const int q0 = t * BQ; return (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / BKV : 0; };
+  const int jloA = jlo_of(tile0), jhiA = tile0;
+  const int jloB = hasB ? jlo_of(tile0 + 1) : 0, jhiB = tile0 + 1;
+  const int jlo = jloA, jhi = hasB ? jhiB : jhiA;
+  const int n = jhi - jlo + 1;
+  auto act = [&](int X, int j) { return X == 0 ? (j <= jhiA) : (hasB && j >= jloB && j <= jhiB); };
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int x = 0; x < 2; ++x) { mbar_init(&bars->s_full[x], 1); mbar_init(&bars->p_ready[x], 4); mbar_init(&bars->o_done[x], 1); }
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&bars->q_full, hasB ? 2 * TILE : TILE);
+      load_tile<D>(sQ, &tmQK, &bars->q_full, h * D, tile0 * BQ, b);
+      if (hasB) load_tile<D>(sQ + TILE, &tmQK, &bars->q_full, h * D, (tile0 + 1) * BQ, b);
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const uint32_t ph = (i / ST) & 1;
+        const int k0 = (jlo + i) * BKV;
+        if (!mbar_wait(&bars->k_empty[st], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&bars->k_full[st], TILE);
+        load_tile<D>(sK + st * TILE, &tmQK, &bars->k_full[st], (H + g) * D, k0, b);
+        if (!mbar_wait(&bars->v_empty[st], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&bars->v_full[st], TILE);
+        load_tile<D>(sV + st * TILE, &tmV, &bars->v_full[st], (H + Hkv + g) * D, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);
+      constexpr uint32_t idPV = make_idesc(128, D, 0, 1);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      int done[2] = {0, 0};  // P V products issued per tile
+      // S of block i for every tile that takes part in it; frees the K stage afterwards
+      auto issue_S = [&](int i) {
+        const int st = i % ST;
+        if (!mbar_wait(&bars->k_full[st], (i / ST) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * TILE);
+        for (int X = 0; X < 2; ++X) {
+          if (!act(X, jlo + i)) continue;
+          const uint32_t aQ = smem_u32(sQ + X * TILE);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tmem + X * 128, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
+          mma_commit(&bars->s_full[X]);
+        }
+        mma_commit(&bars->k_empty[st]);
+        return true;
+      };
+      // S of tile X only (block i), K stage not released
+      auto issue_S1 = [&](int X, int i) {
+        const uint32_t aK = smem_u32(sK + (i % ST) * TILE), aQ = smem_u32(sQ + X * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tmem + X * 128, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
+        mma_commit(&bars->s_full[X]);
+      };
+      if (ok) ok = issue_S(0);
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i % ST, j = jlo + i;
+        const bool more = i + 1 < n;
+        bool k_next = false;  // K of block i + 1 is in shared memory
+        for (int X = 0; X < 2 && ok; ++X) {
+          if (act(X, j)) {
+            if (!mbar_wait(&bars->p_ready[X], done[X] & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&bars->v_full[st], (i / ST) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t aV = smem_u32(sV + st * TILE);
+#pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk)
+              mma_f16_ts(tmem + 256 + X * 128, tmem + X * 128 + kk * 8, desc_mn(aV, kk), idPV, (done[X] | kk) != 0);
+            ++done[X];
+            if (j == (X == 0 ? jhiA : jhiB)) mma_commit(&bars->o_done[X]);
+          }
+          // this tile's next S goes right behind its P V (it overwrites the P just consumed)
+          if (more && act(X, j + 1)) {
+            if (!k_next) {
+              if (!mbar_wait(&bars->k_full[(i + 1) % ST], ((i + 1) / ST) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              k_next = true;
+            }
+            issue_S1(X, i + 1);
+          }
+        }
+        if (!ok) break;
+        mma_commit(&bars->v_empty[st]);
+        if (more) mma_commit(&bars->k_empty[(i + 1) % ST]);
+      }
+    }
+  } else {
+    const int X = (warp - 2) >> 2;           // tile of this warp
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may touch
+    const int r = quad * 32 + lane;          // row inside the tile == TMEM lane
+    const int q0 = (tile0 + X) * BQ;
+    const int qi = q0 + r;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tmem + X * 128 + lane_off, tO = tmem + 256 + X * 128 + lane_off;
+    const int jhiX = X == 0 ? jhiA : jhiB;
+    float m_run = -INFINITY, l_run[NSPLIT] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int cnt = 0;
+    bool ok = true;
+    if (X == 0 || hasB) {
+      for (int i = 0; i < n && ok; ++i) {
+        const int j = jlo + i;
+        if (!act(X, j)) continue;
+        const bool need_mask = (j == jhiX) || (window > 0 && j * BKV < q0 + BQ - window);
+        if (!mbar_wait(&bars->s_full[X], cnt & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // pass 1: row maximum
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < NSPLIT; ++c) {
+          uint32_t sv[KPT];
+          tmem_ld_32x32b_x32(tS + c * KPT, sv);
+          tmem_ld_wait();
+          mx = fmaxf(mx, need_mask ? scores_max<true>(sv, j * BKV + c * KPT, qi, window) : scores_max<false>(sv, j * BKV + c * KPT, qi, window));
+        }
+        const float m_new = fmaxf(m_run, __fmul_rn(mx, c_log2));
+        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float alpha = det_exp2_attn(__fadd_rn(m_run, -m_safe));
+        // O row *= alpha (the previous P V is complete: its S product was issued behind it)
+        if (cnt > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+          const f2 a2 = pack2(alpha, alpha);
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tO + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              float a0, a1;
+              unpack2(mul2(pack2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), a2), a0, a1);
+              v[e] = __float_as_uint(a0);
+              v[e + 1] = __float_as_uint(a1);
+            }
+            tmem_st_32x32b_x32(tO + c * 32, v);
+          }
+        }
+        // pass 2: probabilities, quarter sums, P (bf16 pairs) over the first 64 columns of S
+#pragma unroll
+        for (int c = 0; c < NSPLIT; ++c) {
+          uint32_t sv[KPT], pk[KPT / 2];
+          tmem_ld_32x32b_x32(tS + c * KPT, sv);
+          tmem_ld_wait();
+          const f2 lsum2 = need_mask ? probs_pack<true, false>(sv, c_log2, m_safe, j * BKV + c * KPT, qi, window, pk)
+                                     : probs_pack<false, false>(sv, c_log2, m_safe, j * BKV + c * KPT, qi, window, pk);
+          float ls0, ls1;
+          unpack2(lsum2, ls0, ls1);
+          l_run[c] = __fmaf_rn(l_run[c], alpha, __fadd_rn(ls0, ls1));
+          tmem_st_32x32b_x16(tS + c * (KPT / 2), pk);
+        }
+        tmem_st_wait();
+        m_run = m_new;
+        ++cnt;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_ready[X]);
+      }
+      ok = ok && mbar_wait(&bars->o_done[X], 0, abort_flag);
+      tc_fence_after();
+      if (ok) {
+        const float l_tot = __fadd_rn(__fadd_rn(__fadd_rn(l_run[0], l_run[1]), l_run[2]), l_run[3]);
+        const bool in_range = qi < T;
+        __nv_bfloat16* orow = O + ((long)b * T + qi) * ldo + (long)h * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tO + c * 32, v);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            pk[e >> 1] = pack_bf16(__fdiv_rn(__uint_as_float(v[e]), l_tot), __fdiv_rn(__uint_as_float(v[e + 1]), l_tot));
+          if (in_range) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              reinterpret_cast<uint4*>(orow + c * 32)[w] = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
+          }
+        }
+        if (in_range) lse_out[((long)b * H + h) * T + qi] = __fmaf_rn(det_logf(l_tot), 1.44269504088896341f, m_run);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 2u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
 // Backward element math for a thread's KPT (score, dP) pairs: p = exp2(s * c - lse) (0 where hidden or the row is out of
 // range), ds = (p * (dp - delta)) * scale; both packed to bf16 pairs.
 template <bool MASK, bool WANT_P>
@@ -859,6 +1100,8 @@ CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T,
 template <int D> constexpr int attn_smem_bytes() { return (1 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 512 + 4096; }
 template <int D> constexpr int attn_bwd_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 256; }
 
+template <int D> constexpr int attn_fwd2_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + 1024 + 256; }
+
 template <typename K>
 int set_smem(K kern, int bytes) {
   return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -877,18 +1120,19 @@ extern "C" int otb_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldq
   r = encode_3d(&tv, qkv, (uint64_t)ldqkv, (uint64_t)T, (uint64_t)B, (uint64_t)ldqkv);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
   const float c_log2 = (float)((double)scale * 1.4426950408889634);
-  dim3 grid((T + BQ - 1) / BQ, H, B);
+  const int nq = (T + BQ - 1) / BQ;
+  dim3 grid((nq + 1) / 2, H, B);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) {
-    static int once = set_smem(attn_fwd_kernel<128, false>, attn_smem_bytes<128>());
+    static int once = set_smem(attn_fwd2_kernel<128>, attn_fwd2_smem_bytes<128>());
     if (once) return once;
-    attn_fwd_kernel<128, false><<<grid, ATT_THREADS, attn_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
-                                                                                  window, scale, c_log2, nullptr, status);
+    attn_fwd2_kernel<128><<<grid, F2_THREADS, attn_fwd2_smem_bytes<128>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv, window,
+                                                                              c_log2, status);
   } else {
-    static int once = set_smem(attn_fwd_kernel<64, false>, attn_smem_bytes<64>());
+    static int once = set_smem(attn_fwd2_kernel<64>, attn_fwd2_smem_bytes<64>());
     if (once) return once;
-    attn_fwd_kernel<64, false><<<grid, ATT_THREADS, attn_smem_bytes<64>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv,
-                                                                                window, scale, c_log2, nullptr, status);
+    attn_fwd2_kernel<64><<<grid, F2_THREADS, attn_fwd2_smem_bytes<64>(), s>>>(tq, tv, (__nv_bfloat16*)O, ldo, lse, T, H, Hkv, window,
+                                                                            c_log2, status);
   }
   return (int)cudaGetLastError();
 }
