@@ -543,14 +543,31 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant
         const bool need_mask = (j == jhiX) || (window > 0 && j * BKV < q0 + BQ - window);
         if (!mbar_wait(&bars->s_full[X], cnt & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        // pass 1: row maximum
+        // pass 1: row maximum. Fully visible blocks take the unrolled path with the next 32 columns already in flight
+        // while the current ones are reduced; blocks on the diagonal or the window edge take a compact loop.
         float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < NSPLIT; ++c) {
-          uint32_t sv[KPT];
-          tmem_ld_32x32b_x32(tS + c * KPT, sv);
+        if (!need_mask) {
+          uint32_t sa[KPT], sb[KPT];
+          tmem_ld_32x32b_x32(tS, sa);
           tmem_ld_wait();
-          mx = fmaxf(mx, need_mask ? scores_max<true>(sv, j * BKV + c * KPT, qi, window) : scores_max<false>(sv, j * BKV + c * KPT, qi, window));
+          tmem_ld_32x32b_x32(tS + KPT, sb);
+          mx = scores_max<false>(sa, 0, 0, 0);
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(tS + 2 * KPT, sa);
+          mx = fmaxf(mx, scores_max<false>(sb, 0, 0, 0));
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(tS + 3 * KPT, sb);
+          mx = fmaxf(mx, scores_max<false>(sa, 0, 0, 0));
+          tmem_ld_wait();
+          mx = fmaxf(mx, scores_max<false>(sb, 0, 0, 0));
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < NSPLIT; ++c) {
+            uint32_t sv[KPT];
+            tmem_ld_32x32b_x32(tS + c * KPT, sv);
+            tmem_ld_wait();
+            mx = fmaxf(mx, scores_max<true>(sv, j * BKV + c * KPT, qi, window));
+          }
         }
         const float m_new = fmaxf(m_run, __fmul_rn(mx, c_log2));
         const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
@@ -573,18 +590,46 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant
             tmem_st_32x32b_x32(tO + c * 32, v);
           }
         }
-        // pass 2: probabilities, quarter sums, P (bf16 pairs) over the first 64 columns of S
-#pragma unroll
-        for (int c = 0; c < NSPLIT; ++c) {
-          uint32_t sv[KPT], pk[KPT / 2];
-          tmem_ld_32x32b_x32(tS + c * KPT, sv);
-          tmem_ld_wait();
-          const f2 lsum2 = need_mask ? probs_pack<true, false>(sv, c_log2, m_safe, j * BKV + c * KPT, qi, window, pk)
-                                     : probs_pack<false, false>(sv, c_log2, m_safe, j * BKV + c * KPT, qi, window, pk);
+        // pass 2: probabilities, quarter sums, P (bf16 pairs) over the first 64 columns of S (a P store only ever
+        // covers columns whose scores have been read already)
+        if (!need_mask) {
+          uint32_t sa[KPT], sb[KPT], pk[KPT / 2];
           float ls0, ls1;
-          unpack2(lsum2, ls0, ls1);
-          l_run[c] = __fmaf_rn(l_run[c], alpha, __fadd_rn(ls0, ls1));
-          tmem_st_32x32b_x16(tS + c * (KPT / 2), pk);
+          tmem_ld_32x32b_x32(tS, sa);
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(tS + KPT, sb);
+          unpack2(probs_pack<false, false>(sa, c_log2, m_safe, 0, 0, 0, pk), ls0, ls1);
+          l_run[0] = __fmaf_rn(l_run[0], alpha, __fadd_rn(ls0, ls1));
+          tmem_ld_wait();
+          tmem_st_32x32b_x16(tS, pk);
+          tmem_ld_32x32b_x32(tS + 2 * KPT, sa);
+          unpack2(probs_pack<false, false>(sb, c_log2, m_safe, 0, 0, 0, pk), ls0, ls1);
+          l_run[1] = __fmaf_rn(l_run[1], alpha, __fadd_rn(ls0, ls1));
+          tmem_ld_wait();
+          tmem_st_32x32b_x16(tS + KPT / 2, pk);
+          tmem_ld_32x32b_x32(tS + 3 * KPT, sb);
+          unpack2(probs_pack<false, false>(sa, c_log2, m_safe, 0, 0, 0, pk), ls0, ls1);
+          l_run[2] = __fmaf_rn(l_run[2], alpha, __fadd_rn(ls0, ls1));
+          tmem_ld_wait();
+          tmem_st_32x32b_x16(tS + KPT, pk);
+          unpack2(probs_pack<false, false>(sb, c_log2, m_safe, 0, 0, 0, pk), ls0, ls1);
+          l_run[3] = __fmaf_rn(l_run[3], alpha, __fadd_rn(ls0, ls1));
+          tmem_st_32x32b_x16(tS + 3 * (KPT / 2), pk);
+        } else {
+          float lq[NSPLIT];
+#pragma unroll 1
+          for (int c = 0; c < NSPLIT; ++c) {
+            uint32_t sv[KPT], pk[KPT / 2];
+            tmem_ld_32x32b_x32(tS + c * KPT, sv);
+            tmem_ld_wait();
+            float ls0, ls1;
+            unpack2(probs_pack<true, false>(sv, c_log2, m_safe, j * BKV + c * KPT, qi, window, pk), ls0, ls1);
+            const float lq_c = __fadd_rn(ls0, ls1);
+            lq[0] = c == 0 ? lq_c : lq[0]; lq[1] = c == 1 ? lq_c : lq[1]; lq[2] = c == 2 ? lq_c : lq[2]; lq[3] = c == 3 ? lq_c : lq[3];
+            tmem_st_32x32b_x16(tS + c * (KPT / 2), pk);
+          }
+#pragma unroll
+          for (int c = 0; c < NSPLIT; ++c) l_run[c] = __fmaf_rn(l_run[c], alpha, lq[c]);
         }
         tmem_st_wait();
         m_run = m_new;
