@@ -671,13 +671,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant
 
 // Backward element math for a thread's KPT (score, dP) pairs: p = exp2(s * c - lse) (0 where hidden or the row is out of
 // range), ds = (p * (dp - delta)) * scale; both packed to bf16 pairs.
-template <bool MASK, bool WANT_P>
-__device__ __forceinline__ void bwd_probs(const uint32_t (&vs)[KPT], const uint32_t (&vd)[KPT], float c_log2, float lse_r, float dl_r,
-                                          float scale, bool row_ok, int kbase, int qi, int window, uint32_t (&pk)[KPT / 2],
-                                          uint32_t (&dsr)[KPT / 2]) {
+template <bool MASK, bool WANT_P, int N = KPT>
+__device__ __forceinline__ void bwd_probs(const uint32_t (&vs)[N], const uint32_t (&vd)[N], float c_log2, float lse_r, float dl_r,
+                                          float scale, bool row_ok, int kbase, int qi, int window, uint32_t (&pk)[N / 2],
+                                          uint32_t (&dsr)[N / 2]) {
   const f2 c2 = pack2(c_log2, c_log2), nl2 = pack2(-lse_r, -lse_r), nd2 = pack2(-dl_r, -dl_r), sc2 = pack2(scale, scale);
 #pragma unroll
-  for (int e = 0; e < KPT; e += 2) {
+  for (int e = 0; e < N; e += 2) {
     f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e]), __uint_as_float(vs[e + 1])), c2, nl2));
     if constexpr (MASK) {
       float p0, p1;
@@ -1050,9 +1050,452 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-// delta[b,h,t] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (row, head), lane_tree with VW = 4
+// ------------------------------------------------ backward: dQ, two query tiles per CTA
+// Same organisation as the forward: one CTA owns two adjacent 128-row query tiles, one thread per query row, and the
+// tensor core serves one tile while the other tile's threads do the element math. Keys advance in steps of 64:
+// S = Q K^T and dP = dO V^T (128 x 64 each) land in tensor memory, the row's thread turns them into
+// dS = p (dP - delta) scale, stores it as bf16 pairs over the first 32 columns of S, and dQ += dS K runs with dS as the
+// tensor-memory A operand. dQ accumulates over ascending keys in 16-key tensor-core steps, exactly as before.
+// Tensor memory per tile: S 64 | dP 64 | dQ 128 columns.
+constexpr int HK = 64;  // keys per step
+
+template <int D, int ROWS>
+__device__ __forceinline__ void load_tile_r(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int col, int row, int b) {
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_3d(dst + c * (ROWS * 128), tm, bar, col + c * 64, row, b);
+}
+// K-major / MN-major operand descriptors for tiles of ROWS rows ([ROWS][64 elems] sub-tiles ROWS * 128 bytes apart)
+template <int ROWS>
+__device__ __forceinline__ uint64_t desc_k_r(uint32_t base, int kk) {
+  return make_smem_desc(base + (kk >> 2) * (ROWS * 128) + (kk & 3) * 32, 16, 1024);
+}
+template <int ROWS>
+__device__ __forceinline__ uint64_t desc_mn_r(uint32_t base, int kk) {
+  return make_smem_desc(base + kk * 2048, ROWS * 128, 1024);
+}
+
+struct BarsQ2 {
+  uint64_t qdo_full, kv_full[3], kv_empty[3], sdp_full[2], ds_ready[2], dq_done[2];
+  uint32_t tmem_slot;
+  uint32_t abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(F2_THREADS, 1)
+attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
+                   const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ, long lddq, int T,
+                   int H, int Hkv, int window, float scale, float c_log2, uint32_t* __restrict__ status) {
+  constexpr int TILE = BQ * D * 2;    // a [128][D] query-side tile
+  constexpr int KT = HK * D * 2;      // a [64][D] key-side tile
+  constexpr int ST = 3;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;                 // [2]
+  uint8_t* sDO = sQ + 2 * TILE;       // [2]
+  uint8_t* sK = sDO + 2 * TILE;       // [ST]
+  uint8_t* sV = sK + ST * KT;         // [ST]
+  BarsQ2* bars = reinterpret_cast<BarsQ2*>(sV + ST * KT);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (T + BQ - 1) / BQ;
+  const int pr = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (H / Hkv);
+  const int tile0 = 2 * pr;
+  const bool hasB = tile0 + 1 < nq;
+  // 64-key steps [ulo_X, uhi_X] of tile X: every step that holds a key some row of the tile can see
+  auto ulo_of = [&](int t) { const int q0 = t * BQ; return (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / HK : 0; };
+  const int uloA = ulo_of(tile0), uhiA = 2 * tile0 + 1;
+  const int uloB = hasB ? ulo_of(tile0 + 1) : 0, uhiB = 2 * tile0 + 3;
+  const int ulo = uloA, uhi = hasB ? uhiB : uhiA;
+  const int n = uhi - ulo + 1;
+  auto act = [&](int X, int u) { return X == 0 ? (u <= uhiA) : (hasB && u >= uloB && u <= uhiB); };
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->qdo_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
+    for (int x = 0; x < 2; ++x) { mbar_init(&bars->sdp_full[x], 1); mbar_init(&bars->ds_ready[x], 4); mbar_init(&bars->dq_done[x], 1); }
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&bars->qdo_full, (hasB ? 4 : 2) * TILE);
+      for (int X = 0; X < (hasB ? 2 : 1); ++X) {
+        load_tile<D>(sQ + X * TILE, &tmQK, &bars->qdo_full, h * D, (tile0 + X) * BQ, b);
+        load_tile<D>(sDO + X * TILE, &tmDO, &bars->qdo_full, h * D, (tile0 + X) * BQ, b);
+      }
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const int k0 = (ulo + i) * HK;
+        if (!mbar_wait(&bars->kv_empty[st], ((i / ST) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&bars->kv_full[st], 2 * KT);
+        load_tile_r<D, HK>(sK + st * KT, &tmK64, &bars->kv_full[st], (H + g) * D, k0, b);
+        load_tile_r<D, HK>(sV + st * KT, &tmV64, &bars->kv_full[st], (H + Hkv + g) * D, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, HK, 0, 0);  // S = Q K^T, dP = dO V^T: 128 x 64
+      constexpr uint32_t idQ = make_idesc(128, D, 0, 1);   // dQ = dS K: A in tensor memory, B MN-major
+      bool ok = mbar_wait(&bars->qdo_full, 0, abort_flag);
+      int done[2] = {0, 0};
+      auto issue_sdp = [&](int X, int i) {
+        const uint32_t aK = smem_u32(sK + (i % ST) * KT), aV = smem_u32(sV + (i % ST) * KT);
+        const uint32_t aQ = smem_u32(sQ + X * TILE), aDO = smem_u32(sDO + X * TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tmem + X * 256, desc_k(aQ, kk), desc_k_r<HK>(aK, kk), idS, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tmem + X * 256 + 64, desc_k(aDO, kk), desc_k_r<HK>(aV, kk), idS, kk != 0);
+        mma_commit(&bars->sdp_full[X]);
+      };
+      if (ok) ok = mbar_wait(&bars->kv_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        for (int X = 0; X < 2; ++X)
+          if (act(X, ulo)) issue_sdp(X, 0);
+      }
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i % ST, u = ulo + i;
+        const bool more = i + 1 < n;
+        bool kv_next = false;
+        for (int X = 0; X < 2 && ok; ++X) {
+          if (act(X, u)) {
+            if (!mbar_wait(&bars->ds_ready[X], done[X] & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t aK = smem_u32(sK + st * KT);
+#pragma unroll
+            for (int kk = 0; kk < HK / 16; ++kk)
+              mma_f16_ts(tmem + X * 256 + 128, tmem + X * 256 + kk * 8, desc_mn_r<HK>(aK, kk), idQ, (done[X] | kk) != 0);
+            ++done[X];
+            if (u == (X == 0 ? uhiA : uhiB)) mma_commit(&bars->dq_done[X]);
+          }
+          if (more && act(X, u + 1)) {
+            if (!kv_next) {
+              if (!mbar_wait(&bars->kv_full[(i + 1) % ST], ((i + 1) / ST) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              kv_next = true;
+            }
+            issue_sdp(X, i + 1);
+          }
+        }
+        if (!ok) break;
+        mma_commit(&bars->kv_empty[st]);
+      }
+    }
+  } else {
+    const int X = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int q0 = (tile0 + X) * BQ;
+    const int qi = q0 + r;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    const uint32_t tS = tmem + X * 256 + lane_off, tDP = tS + 64, tDQ = tS + 128;
+    const int uhiX = X == 0 ? uhiA : uhiB;
+    const bool row_ok = qi < T;
+    bool ok = true;
+    if (X == 0 || hasB) {
+      const float lse_r = row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f;
+      const float dl_r = row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f;
+      int cnt = 0;
+      for (int i = 0; i < n && ok; ++i) {
+        const int u = ulo + i;
+        if (!act(X, u)) continue;
+        const int k0 = u * HK;
+        // some (row, key) pair of this step is hidden, or the tile has rows past the end of the sequence
+        const bool need_mask = (k0 + HK - 1 > q0) || (window > 0 && k0 <= q0 + BQ - 1 - window) || (q0 + BQ > T);
+        if (!mbar_wait(&bars->sdp_full[X], cnt & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t unused[8];
+        if (!need_mask) {
+          // 16 keys at a time; the next 16 scores and dP values are in flight while the current ones are processed
+          uint32_t sa[16], da[16], sb[16], db[16], pk[8];
+          tmem_ld_32x32b_x16(tS, sa);
+          tmem_ld_32x32b_x16(tDP, da);
+          tmem_ld_wait();
+          tmem_ld_32x32b_x16(tS + 16, sb);
+          tmem_ld_32x32b_x16(tDP + 16, db);
+          bwd_probs<false, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
+          tmem_ld_wait();
+          tmem_st_32x32b_x8(tS, pk);
+          tmem_ld_32x32b_x16(tS + 32, sa);
+          tmem_ld_32x32b_x16(tDP + 32, da);
+          bwd_probs<false, false, 16>(sb, db, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
+          tmem_ld_wait();
+          tmem_st_32x32b_x8(tS + 8, pk);
+          tmem_ld_32x32b_x16(tS + 48, sb);
+          tmem_ld_32x32b_x16(tDP + 48, db);
+          bwd_probs<false, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
+          tmem_ld_wait();
+          tmem_st_32x32b_x8(tS + 16, pk);
+          bwd_probs<false, false, 16>(sb, db, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
+          tmem_st_32x32b_x8(tS + 24, pk);
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < HK / 16; ++c) {
+            uint32_t sa[16], da[16], pk[8];
+            tmem_ld_32x32b_x16(tS + c * 16, sa);
+            tmem_ld_32x32b_x16(tDP + c * 16, da);
+            tmem_ld_wait();
+            bwd_probs<true, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, row_ok, k0 + c * 16, qi, window, unused, pk);
+            tmem_st_32x32b_x8(tS + c * 8, pk);
+          }
+        }
+        tmem_st_wait();
+        ++cnt;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->ds_ready[X]);
+      }
+      ok = ok && mbar_wait(&bars->dq_done[X], 0, abort_flag);
+      tc_fence_after();
+      if (ok) {
+        __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tDQ + c * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(dqrow + c * 32);
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 6]), __uint_as_float(v[8 * w + 7])));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 4u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ------------------------------------------- backward: dK and dV, transposed scores
+// One CTA owns 128 keys of one KV head and walks, head by head of the group and in ascending query order, the 64-row
+// query steps that see those keys. The products are formed TRANSPOSED, S^T = K Q^T and dP^T = V dO^T (128 keys x 64
+// queries), so a tensor-memory lane is a key: the threads of a key row write P^T and dS^T back over their own columns
+// as bf16 pairs and both accumulations, dV += P^T dO and dK += dS^T Q, take their A operand straight from tensor memory.
+// Two score buffers alternate, so the tensor core forms the next step's scores while the 16 element warps (four threads
+// per key row, 16 queries each, no value crosses threads) work on the current one. Per-query statistics (-lse, -delta)
+// arrive through a small bulk copy beside each Q / dO tile. dV and dK accumulate over (head, query) in 16-query
+// tensor-core steps in the same order as the one-buffer kernel above, so the bits are the same.
+// Tensor memory: dV 128 | dK 128 | buffer 0: S^T 64, dP^T 64 | buffer 1: S^T 64, dP^T 64. Needs T % 64 == 0.
+constexpr int KV2_ST = 4;
+
+struct BarsKV2 {
+  uint64_t kv_full, qdo_full[KV2_ST], qdo_empty[KV2_ST], sdp_full[2], pds_ready[2], acc_done;
+  uint32_t tmem_slot;
+  uint32_t abort_flag;
+};
+
+template <bool MASK>
+__device__ __forceinline__ void bwd_probs_t(const uint32_t (&vs)[16], const uint32_t (&vd)[16], const float* __restrict__ nl,
+                                            const float* __restrict__ nd, float c_log2, float scale, int kj, int qbase, int window,
+                                            uint32_t (&pk)[8], uint32_t (&dsr)[8]) {
+  const f2 c2 = pack2(c_log2, c_log2), sc2 = pack2(scale, scale);
+#pragma unroll
+  for (int e = 0; e < 16; e += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(nl + e), d4 = *reinterpret_cast<const float4*>(nd + e);
+#pragma unroll
+    for (int w = 0; w < 4; w += 2) {
+      const f2 nl2 = w ? pack2(l4.z, l4.w) : pack2(l4.x, l4.y), nd2 = w ? pack2(d4.z, d4.w) : pack2(d4.x, d4.y);
+      f2 p2 = exp2_attn2(fma2(pack2(__uint_as_float(vs[e + w]), __uint_as_float(vs[e + w + 1])), c2, nl2));
+      float p0, p1;
+      unpack2(p2, p0, p1);
+      if constexpr (MASK) {
+        if (key_hidden(kj, qbase + e + w, window)) p0 = 0.0f;
+        if (key_hidden(kj, qbase + e + w + 1, window)) p1 = 0.0f;
+        p2 = pack2(p0, p1);
+      }
+      const f2 d2 = mul2(mul2(p2, add2(pack2(__uint_as_float(vd[e + w]), __uint_as_float(vd[e + w + 1])), nd2)), sc2);
+      float d0, d1;
+      unpack2(d2, d0, d1);
+      pk[(e + w) >> 1] = pack_bf16(p0, p1);
+      dsr[(e + w) >> 1] = pack_bf16(d0, d1);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_kv2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
+                    const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
+                    const float* __restrict__ nlse, const float* __restrict__ ndelta, __nv_bfloat16* __restrict__ dK, long lddk,
+                    __nv_bfloat16* __restrict__ dV, long lddv, int T, int H, int Hkv, int window, float scale, float c_log2,
+                    uint32_t* __restrict__ status) {
+  constexpr int TILE = BKV * D * 2;  // [128 keys][D]
+  constexpr int QT = HK * D * 2;     // [64 queries][D]
+  constexpr int ST = KV2_ST;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;           // [ST]
+  uint8_t* sDO = sQ + ST * QT;       // [ST]
+  float* sStat = reinterpret_cast<float*>(sDO + ST * QT);  // [ST][2][64]: -lse, -delta of the step's queries
+  BarsKV2* bars = reinterpret_cast<BarsKV2*>(sStat + ST * 2 * HK);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int G = H / Hkv;
+  const int k0 = kb * BKV;
+  const int nu = T / HK;  // query steps in the sequence
+  const int ulo = k0 / HK;
+  int uhi = nu - 1;
+  if (window > 0) uhi = min(uhi, (k0 + BKV - 1 + window - 1) / HK);
+  const int nqi = uhi - ulo + 1;  // query steps per head
+  const int n = G * nqi;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&bars->qdo_full[s], 1); mbar_init(&bars->qdo_empty[s], 1); }
+    for (int z = 0; z < 2; ++z) { mbar_init(&bars->sdp_full[z], 1); mbar_init(&bars->pds_ready[z], SOFTMAX_WARPS); }
+    mbar_init(&bars->acc_done, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_slot;
+  const uint32_t tDV = tmem, tDK = tmem + 128, tBuf = tmem + 256;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(&bars->kv_full, 2 * TILE);
+      load_tile<D>(sK, &tmQK, &bars->kv_full, (H + g) * D, k0, b);
+      load_tile<D>(sV, &tmV, &bars->kv_full, (H + Hkv + g) * D, k0, b);
+      for (int i = 0; i < n; ++i) {
+        const int st = i % ST;
+        const int h = g * G + i / nqi;
+        const int q0 = (ulo + i % nqi) * HK;
+        if (!mbar_wait(&bars->qdo_empty[st], ((i / ST) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&bars->qdo_full[st], 2 * QT + 2 * HK * 4);
+        load_tile_r<D, HK>(sQ + st * QT, &tmQ64, &bars->qdo_full[st], h * D, q0, b);
+        load_tile_r<D, HK>(sDO + st * QT, &tmDO64, &bars->qdo_full[st], h * D, q0, b);
+        bulk_load(sStat + st * 2 * HK, nlse + ((long)b * H + h) * T + q0, HK * 4, &bars->qdo_full[st]);
+        bulk_load(sStat + st * 2 * HK + HK, ndelta + ((long)b * H + h) * T + q0, HK * 4, &bars->qdo_full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idS = make_idesc(128, HK, 0, 0);  // S^T = K Q^T, dP^T = V dO^T: 128 keys x 64 queries
+      constexpr uint32_t idG = make_idesc(128, D, 0, 1);   // dV = P^T dO, dK = dS^T Q: A in tensor memory, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+      auto issue_sdp = [&](int i) {
+        const int st = i % ST, z = i & 1;
+        if (!mbar_wait(&bars->qdo_full[st], (i / ST) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * QT), aDO = smem_u32(sDO + st * QT);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tBuf + z * 128, desc_k(aK, kk), desc_k_r<HK>(aQ, kk), idS, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tBuf + z * 128 + 64, desc_k(aV, kk), desc_k_r<HK>(aDO, kk), idS, kk != 0);
+        mma_commit(&bars->sdp_full[z]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      if (ok && n > 1) ok = issue_sdp(1);
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i % ST, z = i & 1;
+        if (!mbar_wait(&bars->pds_ready[z], (i >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * QT), aDO = smem_u32(sDO + st * QT);
+#pragma unroll
+        for (int kk = 0; kk < HK / 16; ++kk)
+          mma_f16_ts(tDV, tBuf + z * 128 + kk * 16, desc_mn_r<HK>(aDO, kk), idG, (i | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < HK / 16; ++kk)
+          mma_f16_ts(tDK, tBuf + z * 128 + 64 + kk * 16, desc_mn_r<HK>(aQ, kk), idG, (i | kk) != 0);
+        mma_commit(&bars->qdo_empty[st]);
+        if (i + 1 == n) mma_commit(&bars->acc_done);
+        if (i + 2 < n) { if (!issue_sdp(i + 2)) { ok = false; break; } }  // into the buffer just consumed
+      }
+    }
+  } else {
+    constexpr int DH = D / NSPLIT;
+    const int quad = warp & 3;
+    const int cq = (warp - 2) >> 2;          // which 16 of the step's 64 queries
+    const int r = quad * 32 + lane;          // key row == TMEM lane
+    const int kj = k0 + r;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i % ST, z = i & 1;
+      const int q0 = (ulo + i % nqi) * HK;
+      const int qbase = q0 + cq * 16;
+      // some (key, query) pair of the step is hidden
+      const bool need_mask = (k0 + BKV - 1 > q0) || (window > 0 && k0 <= q0 + HK - 1 - window);
+      if (!mbar_wait(&bars->qdo_full[st], (i / ST) & 1, abort_flag)) { ok = false; break; }  // the statistics are in shared memory
+      if (!mbar_wait(&bars->sdp_full[z], (i >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tSt = tBuf + z * 128 + cq * 16 + lane_off, tDPt = tSt + 64;
+      const float* nl = sStat + st * 2 * HK + cq * 16;
+      const float* nd = nl + HK;
+      uint32_t vs[16], vd[16], pk[8], dsr[8];
+      tmem_ld_32x32b_x16(tSt, vs);
+      tmem_ld_32x32b_x16(tDPt, vd);
+      tmem_ld_wait();
+      if (need_mask) bwd_probs_t<true>(vs, vd, nl, nd, c_log2, scale, kj, qbase, window, pk, dsr);
+      else bwd_probs_t<false>(vs, vd, nl, nd, c_log2, scale, kj, qbase, window, pk, dsr);
+      tmem_st_32x32b_x8(tSt, pk);
+      tmem_st_32x32b_x8(tDPt, dsr);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->pds_ready[z]);
+    }
+    if (ok && mbar_wait(&bars->acc_done, 0, abort_flag)) {
+      tc_fence_after();
+      const bool in_range = kj < T;
+      __nv_bfloat16* dkrow = dK + ((long)b * T + kj) * lddk + (long)g * D + cq * DH;
+      __nv_bfloat16* dvrow = dV + ((long)b * T + kj) * lddv + (long)g * D + cq * DH;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int c = 0; c < DH / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16((which ? tDK : tDV) + lane_off + cq * DH + c * 16, v);
+          tmem_ld_wait();
+          if (in_range) {
+            uint4* dst = reinterpret_cast<uint4*>((which ? dkrow : dvrow) + c * 16);
+#pragma unroll
+            for (int w = 0; w < 2; ++w)
+              dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
+                                  pack_bf16(__uint_as_float(v[8 * w + 6]), __uint_as_float(v[8 * w + 7])));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 3u);
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,t] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (row, head), lane_tree with VW = 4. The scratch has three
+// [B, H, T] planes: delta, -lse and -delta (the negated copies feed the transposed dK/dV kernel's packed arithmetic).
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, long lddo, const __nv_bfloat16* __restrict__ O,
-                                  long ldo, float* __restrict__ delta, int B, int T, int H, int D) {
+                                  long ldo, const float* __restrict__ lse, float* __restrict__ delta, int B, int T, int H, int D) {
   const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const long rows = (long)B * T;
@@ -1070,7 +1513,10 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, long ldd
   for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
   if (lane == 0) {
     const long bb = row / T, t = row - bb * T;
-    delta[(bb * H + h) * T + t] = acc;
+    const long idx = (bb * H + h) * T + t, plane = (long)B * H * T;
+    delta[idx] = acc;
+    delta[plane + idx] = -lse[idx];
+    delta[2 * plane + idx] = -acc;
   }
 }
 
@@ -1130,12 +1576,12 @@ CUresult encode_3d_u8(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
-CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T, uint64_t B, uint64_t ld_elems) {
+CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T, uint64_t B, uint64_t ld_elems, uint32_t box_rows = 128) {
   static PFN_encodeTiled fn = get_encode_tiled();
   if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
   cuuint64_t dims[3] = {cols, T, B};
   cuuint64_t strides[2] = {ld_elems * 2, T * ld_elems * 2};
-  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t box[3] = {64, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1145,6 +1591,8 @@ CUresult encode_3d(CUtensorMap* out, const void* ptr, uint64_t cols, uint64_t T,
 template <int D> constexpr int attn_smem_bytes() { return (1 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 512 + 4096; }
 template <int D> constexpr int attn_bwd_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + BQ * BKV * 2 + 1024 + 256; }
 
+template <int D> constexpr int attn_bwd_q2_smem_bytes() { return 4 * (BQ * D * 2) + 2 * 3 * (HK * D * 2) + 1024 + 256; }
+template <int D> constexpr int attn_bwd_kv2_smem_bytes() { return 2 * (BKV * D * 2) + 2 * KV2_ST * (HK * D * 2) + KV2_ST * 2 * HK * 4 + 1024 + 256; }
 template <int D> constexpr int attn_fwd2_smem_bytes() { return (2 + 2 * 2) * (BQ * D * 2) + 1024 + 256; }
 
 template <typename K>
@@ -1207,7 +1655,7 @@ extern "C" int otb_attn_fwd_i8pv(const void* qk, long ldqk, const void* qkv, lon
 }
 
 // dO, O: [B*T, ld] bf16 (head h at column h*D). Outputs: dqk [B*T, lddqk] (dQ heads then dK heads),
-// dV written at column (H + Hkv) * D of dqkv [B*T, lddqkv]; delta: [B, H, T] fp32 scratch.
+// dV written at column (H + Hkv) * D of dqkv [B*T, lddqkv]; delta: [3, B, H, T] fp32 scratch (delta, -lse, -delta).
 extern "C" int otb_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldqkv, const void* O, long ldo,
                             const void* dO, long lddo, const float* lse, float* delta, void* dqk, long lddqk, void* dqkv,
                             long lddqkv, int B, int T, int H, int Hkv, int D, int window, float scale, uint32_t* status,
@@ -1226,27 +1674,52 @@ extern "C" int otb_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldq
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
   const long warps = (long)B * T * H;
   attn_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dO, lddo, (const __nv_bfloat16*)O,
-                                                               ldo, delta, B, T, H, D);
+                                                               ldo, lse, delta, B, T, H, D);
   __nv_bfloat16* dQp = (__nv_bfloat16*)dqk;
   __nv_bfloat16* dKp = dQp + (long)H * D;
   __nv_bfloat16* dVp = (__nv_bfloat16*)dqkv + (long)(H + Hkv) * D;
-  dim3 gkv((T + BKV - 1) / BKV, Hkv, B), gq((T + BQ - 1) / BQ, H, B);
+  CUtensorMap tk64, tv64;
+  r = encode_3d(&tk64, qk, (uint64_t)ldqk, (uint64_t)T, (uint64_t)B, (uint64_t)ldqk, HK);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_3d(&tv64, qkv, (uint64_t)ldqkv, (uint64_t)T, (uint64_t)B, (uint64_t)ldqkv, HK);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  const int nq = (T + BQ - 1) / BQ;
+  dim3 gkv((T + BKV - 1) / BKV, Hkv, B), gq((nq + 1) / 2, H, B);
+  const bool kv2 = T % HK == 0;  // the transposed dK/dV kernel walks whole 64-query steps
+  const long plane = (long)B * H * T;
+  CUtensorMap tq64, tdo64;
+  if (kv2) {
+    r = encode_3d(&tq64, qk, (uint64_t)ldqk, (uint64_t)T, (uint64_t)B, (uint64_t)ldqk, HK);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    r = encode_3d(&tdo64, dO, (uint64_t)lddo, (uint64_t)T, (uint64_t)B, (uint64_t)lddo, HK);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  }
   if (D == 128) {
     static int once = set_smem(attn_bwd_kv_kernel<128>, attn_bwd_smem_bytes<128>()) |
-                      set_smem(attn_bwd_q_kernel<128>, attn_bwd_smem_bytes<128>());
+                      set_smem(attn_bwd_kv2_kernel<128>, attn_bwd_kv2_smem_bytes<128>()) |
+                      set_smem(attn_bwd_q2_kernel<128>, attn_bwd_q2_smem_bytes<128>());
     if (once) return once;
-    attn_bwd_kv_kernel<128><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
-                                                                                 lddqkv, T, H, Hkv, window, scale, c_log2, status);
-    attn_bwd_q_kernel<128><<<gq, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dQp, lddqk, T, H,
-                                                                               Hkv, window, scale, c_log2, status);
+    if (kv2)
+      attn_bwd_kv2_kernel<128><<<gkv, ATT_THREADS, attn_bwd_kv2_smem_bytes<128>(), s>>>(
+          tq, tv, tq64, tdo64, delta + plane, delta + 2 * plane, dKp, lddqk, dVp, lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    else
+      attn_bwd_kv_kernel<128><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
+                                                                                   lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    attn_bwd_q2_kernel<128><<<gq, F2_THREADS, attn_bwd_q2_smem_bytes<128>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H,
+                                                                                  Hkv, window, scale, c_log2, status);
   } else {
     static int once = set_smem(attn_bwd_kv_kernel<64>, attn_bwd_smem_bytes<64>()) |
-                      set_smem(attn_bwd_q_kernel<64>, attn_bwd_smem_bytes<64>());
+                      set_smem(attn_bwd_kv2_kernel<64>, attn_bwd_kv2_smem_bytes<64>()) |
+                      set_smem(attn_bwd_q2_kernel<64>, attn_bwd_q2_smem_bytes<64>());
     if (once) return once;
-    attn_bwd_kv_kernel<64><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
-                                                                               lddqkv, T, H, Hkv, window, scale, c_log2, status);
-    attn_bwd_q_kernel<64><<<gq, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dQp, lddqk, T, H, Hkv,
-                                                                             window, scale, c_log2, status);
+    if (kv2)
+      attn_bwd_kv2_kernel<64><<<gkv, ATT_THREADS, attn_bwd_kv2_smem_bytes<64>(), s>>>(
+          tq, tv, tq64, tdo64, delta + plane, delta + 2 * plane, dKp, lddqk, dVp, lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    else
+      attn_bwd_kv_kernel<64><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
+                                                                                 lddqkv, T, H, Hkv, window, scale, c_log2, status);
+    attn_bwd_q2_kernel<64><<<gq, F2_THREADS, attn_bwd_q2_smem_bytes<64>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H, Hkv,
+                                                                                window, scale, c_log2, status);
   }
   return (int)cudaGetLastError();
 }

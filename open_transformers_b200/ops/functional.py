@@ -165,7 +165,7 @@ def attn_fwd(qk, qkv, B: int, T: int, H: int, Hkv: int, D: int, window: int, int
 
 def attn_bwd(qk, qkv, O, dO, lse, dqk, dqkv, B: int, T: int, H: int, Hkv: int, D: int, window: int):
     """Writes dQ|dK into ``dqk`` and dV into the value columns of ``dqkv``."""
-    delta = torch.empty((B, H, T), dtype=torch.float32, device=qk.device)
+    delta = torch.empty((3, B, H, T), dtype=torch.float32, device=qk.device)  # delta, and the kernels' negated copies of lse / delta
     scale = 1.0 / math.sqrt(D)
     common = (P(qk), L(_ld(qk)), P(qkv), L(_ld(qkv)), P(O), L(_ld(O)), P(dO), L(_ld(dO)), P(lse), P(delta), P(dqk), L(_ld(dqk)),
               P(dqkv), L(_ld(dqkv)), I(B), I(T), I(H), I(Hkv), I(D), I(window), F(scale))
