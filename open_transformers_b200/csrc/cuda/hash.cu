@@ -11,14 +11,77 @@
 #include "common.cuh"
 
 namespace {
+// Device version of the compression function with the twelve rounds written out, so the message words and the
+// permutation are compile-time register choices (the shared host/device b2_compress indexes the message through the
+// sigma table, which the device compiler can only do through local memory). Same function, same bytes.
+#define B2D_G(a, b, c, d, x, y)                              \
+  v[a] = v[a] + v[b] + (x); v[d] = b2_rotr(v[d] ^ v[a], 32); \
+  v[c] = v[c] + v[d];       v[b] = b2_rotr(v[b] ^ v[c], 24); \
+  v[a] = v[a] + v[b] + (y); v[d] = b2_rotr(v[d] ^ v[a], 16); \
+  v[c] = v[c] + v[d];       v[b] = b2_rotr(v[b] ^ v[c], 63);
+#define B2D_ROUND(s0, s1, s2, s3, s4, s5, s6, s7, s8, s9, s10, s11, s12, s13, s14, s15)  \
+  B2D_G(0, 4, 8, 12, m[s0], m[s1]) B2D_G(1, 5, 9, 13, m[s2], m[s3])                      \
+  B2D_G(2, 6, 10, 14, m[s4], m[s5]) B2D_G(3, 7, 11, 15, m[s6], m[s7])                    \
+  B2D_G(0, 5, 10, 15, m[s8], m[s9]) B2D_G(1, 6, 11, 12, m[s10], m[s11])                  \
+  B2D_G(2, 7, 8, 13, m[s12], m[s13]) B2D_G(3, 4, 9, 14, m[s14], m[s15])
+__device__ __forceinline__ void b2d_compress(uint64_t (&h)[8], const uint64_t (&m)[16], uint64_t t, bool last) {
+  uint64_t v[16];
+  v[0] = h[0]; v[1] = h[1]; v[2] = h[2]; v[3] = h[3]; v[4] = h[4]; v[5] = h[5]; v[6] = h[6]; v[7] = h[7];
+  v[8] = 0x6a09e667f3bcc908ULL; v[9] = 0xbb67ae8584caa73bULL; v[10] = 0x3c6ef372fe94f82bULL; v[11] = 0xa54ff53a5f1d36f1ULL;
+  v[12] = 0x510e527fade682d1ULL ^ t; v[13] = 0x9b05688c2b3e6c1fULL;
+  v[14] = last ? ~0x1f83d9abfb41bd6bULL : 0x1f83d9abfb41bd6bULL; v[15] = 0x5be0cd19137e2179ULL;
+  B2D_ROUND(0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15)
+  B2D_ROUND(14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3)
+  B2D_ROUND(11, 8, 12, 0, 5, 2, 15, 13, 10, 14, 3, 6, 7, 1, 9, 4)
+  B2D_ROUND(7, 9, 3, 1, 13, 12, 11, 14, 2, 6, 5, 10, 4, 0, 15, 8)
+  B2D_ROUND(9, 0, 5, 7, 2, 4, 10, 15, 14, 1, 11, 12, 6, 8, 3, 13)
+  B2D_ROUND(2, 12, 6, 10, 0, 11, 8, 3, 4, 13, 7, 5, 15, 14, 1, 9)
+  B2D_ROUND(12, 5, 1, 15, 14, 13, 4, 10, 0, 7, 6, 3, 9, 2, 8, 11)
+  B2D_ROUND(13, 11, 7, 14, 12, 1, 3, 9, 5, 0, 15, 4, 8, 6, 2, 10)
+  B2D_ROUND(6, 15, 14, 9, 11, 3, 0, 8, 12, 2, 13, 7, 1, 4, 10, 5)
+  B2D_ROUND(10, 2, 8, 4, 7, 6, 1, 5, 15, 11, 9, 14, 3, 12, 13, 0)
+  B2D_ROUND(0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15)
+  B2D_ROUND(14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) h[i] ^= v[i] ^ v[i + 8];
+}
+#undef B2D_ROUND
+#undef B2D_G
+
+// 32-byte digest of one leaf (len <= OTB_TREE_LEAF bytes at a 16-byte aligned address) into out (8-byte aligned).
+// Whole 128-byte blocks come in as 16-byte loads; a ragged tail goes through the shared byte-wise routine.
+__device__ __forceinline__ void leaf_digest(const uint8_t* __restrict__ data, uint64_t len, uint8_t* __restrict__ out) {
+  if (len == 0 || (len & 127) != 0 || (reinterpret_cast<uintptr_t>(data) & 15) != 0) {
+    uint8_t d[32];
+    b2_hash(data, len, d, 32);
+    for (int k = 0; k < 32; ++k) out[k] = d[k];
+    return;
+  }
+  uint64_t h[8] = {0x6a09e667f3bcc908ULL ^ 0x01010020ULL, 0xbb67ae8584caa73bULL, 0x3c6ef372fe94f82bULL, 0xa54ff53a5f1d36f1ULL,
+                   0x510e527fade682d1ULL, 0x9b05688c2b3e6c1fULL, 0x1f83d9abfb41bd6bULL, 0x5be0cd19137e2179ULL};
+  const ulonglong2* src = reinterpret_cast<const ulonglong2*>(data);
+  const uint64_t blocks = len >> 7;
+#pragma unroll 1
+  for (uint64_t blk = 0; blk < blocks; ++blk) {
+    uint64_t m[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const ulonglong2 w = src[blk * 8 + i];
+      m[2 * i] = w.x;
+      m[2 * i + 1] = w.y;
+    }
+    b2d_compress(h, m, (blk + 1) << 7, blk + 1 == blocks);
+  }
+  uint64_t* o = reinterpret_cast<uint64_t*>(out);
+  o[0] = h[0]; o[1] = h[1]; o[2] = h[2]; o[3] = h[3];
+}
+
 __global__ void tree_level_kernel(const uint8_t* __restrict__ data, uint64_t n, uint8_t* __restrict__ out, uint64_t leaves) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= leaves) return;
   const uint64_t off = i * OTB_TREE_LEAF;
   const uint64_t l = (n - off < OTB_TREE_LEAF) ? n - off : OTB_TREE_LEAF;
-  uint8_t d[32];
-  b2_hash(data + off, l, d, 32);
-  for (int k = 0; k < 32; ++k) out[i * 32 + k] = d[k];
+  leaf_digest(data + off, l, out + i * 32);
 }
 __global__ void tree_final_kernel(const uint8_t* __restrict__ data, uint64_t n, uint64_t total_len, uint8_t* __restrict__ out) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -80,10 +143,7 @@ __global__ void tree_level_batch_kernel(BatchLevel lv, int n, uint64_t total_lea
   const uint64_t nbytes = lv.len[lo];
   const uint64_t off = leaf * OTB_TREE_LEAF;
   const uint64_t l = (nbytes - off < OTB_TREE_LEAF) ? nbytes - off : OTB_TREE_LEAF;
-  uint8_t d[32];
-  b2_hash(lv.src[lo] + off, l, d, 32);
-  uint8_t* o = lv.dst[lo] + leaf * 32;
-  for (int k = 0; k < 32; ++k) o[k] = d[k];
+  leaf_digest(lv.src[lo] + off, l, lv.dst[lo] + leaf * 32);
 }
 __global__ void tree_final_batch_kernel(const uint8_t* const* src, const uint64_t* len, const uint64_t* total_len, int n,
                                         uint8_t* out) {
