@@ -151,8 +151,16 @@ def main() -> int:
         eng.optimizer_step(lr, eng.clip_coefficient(norm, cfg.train.grad_clip))
         state["consumed"] += tokens_per_step
         if not args.no_hash:
-            state["prev"] = eng.sharded_state_hash(state["prev"], None, include_grads=cfg.train.state_hash.include_grads)
+            # the digests of this step's state run on a side stream under the next step's forward/backward;
+            # the previous step's hash is folded into the chain here
+            flush_hash()
+            state["pending"] = eng.begin_state_hash(include_grads=cfg.train.state_hash.include_grads)
         return last_ce, norm
+
+    def flush_hash():
+        if state.get("pending") is not None:
+            state["prev"] = eng.finish_state_hash(state["pending"], state["prev"], None)
+            state["pending"] = None
 
     def timed(first_step: int, n: int, resident_mode: bool):
         resident = None
@@ -169,6 +177,7 @@ def main() -> int:
             ce, norm = one_step(s, resident)
             if not resident_mode:
                 loss = float(ce.detach().to("cpu"))  # the step's result is read on the host every step
+        flush_hash()  # every hash of the timed steps completes inside the timed region
         e1.record()
         torch.cuda.synchronize()
         if world > 1:

@@ -223,3 +223,75 @@ extern "C" int otb_tree_digest_batch(const void* const* data, const uint64_t* le
   OTB_CUDA_CHECK_RET(cudaStreamSynchronize(s));
   return (int)cudaGetLastError();
 }
+
+// ---- planned variant: the level tables are built once, the launches never synchronise ----------------------------
+// A plan covers n messages of fixed addresses and lengths (the state tensors of a training run never move). Table
+// layout, 8-byte words, one block of (4n + 1) words per tree level: src[n] dst[n] len[n] prefix[n + 1]; then the final
+// block: src[n] len[n] total[n]. otb_tree_plan fills the HOST copy of the table and the per-level leaf counts and
+// returns the number of levels (or a negative error); the caller copies the table to the device once and then calls
+// otb_tree_run on any stream, as often as it likes, with no host synchronisation inside.
+extern "C" uint64_t otb_tree_plan_words(int n) { return (uint64_t)8 * (4 * (uint64_t)n + 1) + 3 * (uint64_t)n; }
+extern "C" long otb_tree_plan(const void* const* data, const uint64_t* lens, int n, void* work, uint64_t work_bytes, uint64_t* tab,
+                              uint64_t tab_words, uint64_t* level_leaves, int max_levels) {
+  if (n <= 0) return 0;
+  if (tab_words < otb_tree_plan_words(n) || max_levels > 8) return -2;
+  uint64_t need = 0;
+  for (int i = 0; i < n; ++i) need += otb_tree_digest_scratch(lens[i]);
+  if (work_bytes < need) return -3;
+  uint8_t* pool = reinterpret_cast<uint8_t*>(work);
+  uint64_t pool_off = 0;
+  const size_t blk = 4 * (size_t)n + 1;
+  uint64_t* cur_src = new uint64_t[n];
+  uint64_t* cur_len = new uint64_t[n];
+  for (int i = 0; i < n; ++i) { cur_src[i] = reinterpret_cast<uint64_t>(data[i]); cur_len[i] = lens[i]; }
+  int levels = 0;
+  for (;;) {
+    uint64_t total_leaves = 0;
+    uint64_t* t = tab + (size_t)levels * blk;
+    bool any = false;
+    for (int i = 0; i < n; ++i) any = any || cur_len[i] > OTB_TREE_LEAF;
+    if (!any) break;
+    if (levels >= max_levels) { delete[] cur_src; delete[] cur_len; return -4; }
+    for (int i = 0; i < n; ++i) {
+      t[i] = cur_src[i];
+      t[2 * (size_t)n + i] = cur_len[i];
+      t[3 * (size_t)n + i] = total_leaves;
+      if (cur_len[i] > OTB_TREE_LEAF) {
+        const uint64_t leaves = (cur_len[i] + OTB_TREE_LEAF - 1) / OTB_TREE_LEAF;
+        t[(size_t)n + i] = reinterpret_cast<uint64_t>(pool + pool_off);
+        pool_off += (leaves * 32 + 255) & ~uint64_t(255);
+        total_leaves += leaves;
+      } else {
+        t[(size_t)n + i] = 0;
+        t[2 * (size_t)n + i] = 0;  // takes no part in this level (zero leaves)
+      }
+    }
+    t[4 * (size_t)n] = total_leaves;
+    level_leaves[levels] = total_leaves;
+    for (int i = 0; i < n; ++i)
+      if (cur_len[i] > OTB_TREE_LEAF) {
+        cur_src[i] = t[(size_t)n + i];
+        cur_len[i] = ((cur_len[i] + OTB_TREE_LEAF - 1) / OTB_TREE_LEAF) * 32;
+      }
+    ++levels;
+  }
+  uint64_t* f = tab + (size_t)levels * blk;
+  for (int i = 0; i < n; ++i) { f[i] = cur_src[i]; f[(size_t)n + i] = cur_len[i]; f[2 * (size_t)n + i] = lens[i]; }
+  delete[] cur_src;
+  delete[] cur_len;
+  return levels;
+}
+extern "C" int otb_tree_run(const uint64_t* tab_dev, int n, int levels, const uint64_t* level_leaves, void* out, void* stream) {
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t blk = 4 * (size_t)n + 1;
+  for (int l = 0; l < levels; ++l) {
+    const uint64_t* t = tab_dev + (size_t)l * blk;
+    BatchLevel lv{reinterpret_cast<const uint8_t* const*>(t), t + 2 * (size_t)n, t + 3 * (size_t)n,
+                  reinterpret_cast<uint8_t* const*>(t + n)};
+    tree_level_batch_kernel<<<(unsigned)((level_leaves[l] + 63) / 64), 64, 0, s>>>(lv, n, level_leaves[l]);
+  }
+  const uint64_t* f = tab_dev + (size_t)levels * blk;
+  tree_final_batch_kernel<<<(n + 31) / 32, 32, 0, s>>>(reinterpret_cast<const uint8_t* const*>(f), f + n, f + 2 * (size_t)n, n,
+                                                       reinterpret_cast<uint8_t*>(out));
+  return (int)cudaGetLastError();
+}

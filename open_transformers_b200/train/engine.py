@@ -257,6 +257,7 @@ class TrainEngine:
         lay = self.layout
         S, R = self.dp_shard, self.dp_replicate
         per = self.V // self.world
+        self._wait_pending_hash()
         if self.nccl_mode and self.world > 1:
             # throughput-only baseline: library all-reduce, order not pinned
             acc = self.grads[0]
@@ -336,6 +337,7 @@ class TrainEngine:
 
     def optimizer_step(self, lr: float, clip: float) -> None:
         """Step 4 on the owned segments; pushes the new weights to every rank."""
+        self._wait_pending_hash()
         self.opt_step += 1
         for g in self.param_groups:
             g["lr"] = float(lr)
@@ -366,28 +368,75 @@ class TrainEngine:
         self._barrier()
 
     # --------------------------------------------------------------------------------- hash
-    def sharded_state_hash(self, prev, batch_digest: bytes | None, include_grads: bool = True, tensor_digest: str | None = None) -> str:
-        """v3 hash of the current state. With peer-sharded ownership each process digests the segments it
-        owns (tree digests, on the device) and the 32-byte results are gathered."""
+    def _hash_fields(self, include_grads: bool):
+        return [("weight", self.master), ("exp_avg", self.m1), ("exp_avg_sq", self.m2)] + ([("grad", self.grad_red)] if include_grads else [])
+
+    def _wait_pending_hash(self) -> None:
+        """Kernels that overwrite hashed state wait (on the device) for a state hash still running on the side stream."""
+        ev = getattr(self, "_hash_done", None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self._hash_done = None
+
+    def begin_state_hash(self, include_grads: bool = True, tensor_digest: str | None = None) -> dict:
+        """Start the v3 hash of the CURRENT state and return a handle for ``finish_state_hash``. With tree digests on a
+        GPU the per-segment digests are computed on a low-priority side stream, so the next step's forward and backward
+        (which touch neither the master weights, the moments nor the reduced gradient) run on top of them; the kernels
+        that do overwrite that state (gradient reduction, optimizer step) wait for the digests first."""
         td = tensor_digest or self.cfg.train.state_hash.tensor_digest
         lay = self.layout
         if self.peer and td != "tree":
             raise ValueError("sharded multi-GPU hashing needs train.state_hash.tensor_digest=tree")
-        fields = [("weight", self.master), ("exp_avg", self.m1), ("exp_avg_sq", self.m2)] + ([("grad", self.grad_red)] if include_grads else [])
+        handle = {"td": td, "include_grads": include_grads, "opt_step": self.opt_step, "keys": None, "plan": None, "digests": None}
+        if td != "tree":
+            return handle
+        fields = self._hash_fields(include_grads)
+        keys, views = [], []
+        for si in range(self.seg_lo, self.seg_hi) if self.peer else range(self.n_segs):
+            seg = lay.segments[si]
+            for tag, flat in fields:
+                keys.append((seg.param, seg.shard, tag))
+                views.append(flat[seg.start:seg.start + seg.length])
+        handle["keys"] = keys
+        if self.is_cuda and views:
+            plans = self.__dict__.setdefault("_hash_plans", {})
+            plan = plans.get(include_grads)
+            if plan is None:
+                plan = plans[include_grads] = SH.TreeDigestPlan(views)
+                lo, _hi = torch.cuda.Stream.priority_range()
+                self._hash_stream = getattr(self, "_hash_stream", None) or torch.cuda.Stream(device=self.device, priority=lo)
+            ready = torch.cuda.Event()
+            ready.record()
+            self._hash_stream.wait_event(ready)
+            plan.launch(self._hash_stream)
+            done = torch.cuda.Event()
+            done.record(self._hash_stream)
+            self._hash_done = done
+            handle["plan"], handle["done"] = plan, done
+        else:
+            handle["digests"] = SH.tree_digest_batch(views)
+        return handle
+
+    def finish_state_hash(self, handle: dict, prev, batch_digest: bytes | None) -> str:
+        """Complete a hash started by ``begin_state_hash``: wait for the digests, gather them from the other processes
+        when ownership is sharded, and fold everything into the v3 byte stream on the host."""
+        td, include_grads = handle["td"], handle["include_grads"]
+        lay = self.layout
         seg_digests = {}
         if td == "tree":
-            keys, views = [], []
-            for si in range(self.seg_lo, self.seg_hi) if self.peer else range(self.n_segs):
-                seg = lay.segments[si]
-                for tag, flat in fields:
-                    keys.append((seg.param, seg.shard, tag))
-                    views.append(flat[seg.start:seg.start + seg.length])
-            seg_digests = dict(zip(keys, SH.tree_digest_batch(views)))
+            if handle["plan"] is not None:
+                handle["done"].synchronize()
+                digs = handle["plan"].digests()
+            else:
+                digs = handle["digests"]
+            seg_digests = dict(zip(handle["keys"], digs))
             if self.peer:
                 objs: list = [None] * self.world
                 dist.all_gather_object(objs, seg_digests, group=self.group)
                 seg_digests = {k: v for d in objs for k, v in d.items()}
         order = sorted(range(len(self.names)), key=lambda i: self.names[i])
+        step_bytes = b"optim_step\0" + int(handle["opt_step"]).to_bytes(8, "little", signed=True)
+        empty = SH.tree_digest_bytes(b"") if td == "tree" else None
         locals_ = []
         for s in range(self.dp_shard):
             h = SH._new()
@@ -396,26 +445,31 @@ class TrainEngine:
                 lo, hi = SH.shard_rows(shape[0], self.dp_shard, s)
                 sshape = (hi - lo,) + tuple(shape[1:])
                 h.update(self.names[pi].encode() + b"\0")
+                head = b"\0torch.float32\0" + str(sshape).encode() + b"\0"
 
                 def feed(tag, key, flat):
-                    h.update(tag.encode() + b"\0" + b"torch.float32\0" + str(sshape).encode() + b"\0")
                     if td == "tree":
-                        h.update(b"tree\0")
-                        h.update(seg_digests[(pi, s, key)] if hi > lo else SH.tree_digest_bytes(b""))
+                        h.update(tag + head + b"tree\0" + (seg_digests[(pi, s, key)] if hi > lo else empty))
                     else:
+                        h.update(tag + head)
                         row = lay.numels[pi] // max(shape[0], 1)
                         st = lay.offsets[pi] + lo * row
                         h.update(SH.tensor_bytes(flat[st:st + (hi - lo) * row]))
 
-                feed("weight", "weight", self.master)
-                h.update(b"optim_step\0" + int(self.opt_step).to_bytes(8, "little", signed=True))
-                feed("optim_exp_avg", "exp_avg", self.m1)
-                feed("optim_exp_avg_sq", "exp_avg_sq", self.m2)
+                feed(b"weight", "weight", self.master)
+                h.update(step_bytes)
+                feed(b"optim_exp_avg", "exp_avg", self.m1)
+                feed(b"optim_exp_avg_sq", "exp_avg_sq", self.m2)
                 if include_grads:
-                    feed("grad", "grad", self.grad_red)
+                    feed(b"grad", "grad", self.grad_red)
             locals_.append(h.digest())
         shard_state = SH.combine_shard_state(locals_, self.V)
         return SH.finalize_state_hash(shard_state, self.param_groups, prev, batch_digest)
+
+    def sharded_state_hash(self, prev, batch_digest: bytes | None, include_grads: bool = True, tensor_digest: str | None = None) -> str:
+        """v3 hash of the current state. With peer-sharded ownership each process digests the segments it
+        owns (tree digests, on the device) and the 32-byte results are gathered."""
+        return self.finish_state_hash(self.begin_state_hash(include_grads, tensor_digest), prev, batch_digest)
 
     def full_state_hash(self, prev=None, batch_digest=None, include_grads: bool = False) -> str:
         """v2 hash over full tensors (init hash). Only valid where this process holds every segment."""
@@ -427,6 +481,7 @@ class TrainEngine:
         """Make master / moments / reduced gradient complete on every rank (checkpoint, init hash)."""
         if not self.peer:
             return
+        self._wait_pending_hash()
         lay = self.layout
         ranges = lay.owner_ranges(self.world)
         for flat in (self.master, self.m1, self.m2, self.grad_red):

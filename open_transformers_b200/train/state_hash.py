@@ -114,6 +114,57 @@ def tree_digest_batch(tensors) -> list[bytes]:
     return [raw[i * 32:(i + 1) * 32] for i in range(n)]
 
 
+class TreeDigestPlan:
+    """Tree digests of a FIXED set of CUDA tensors (same addresses and sizes every time, like the flat state buffers
+    of a training run), launched without any host synchronisation so they can run on a side stream under the next
+    step's compute. ``launch(stream)`` enqueues the level kernels and the copy of the n x 32 digest bytes into pinned
+    host memory; ``digests()`` (after the caller has waited for the stream or an event) returns them."""
+
+    MAX_LEVELS = 8
+
+    def __init__(self, tensors):
+        from ..ops.native import P, cuda_lib
+
+        tensors = [t.detach() for t in tensors]
+        assert tensors and all(t.is_cuda and t.is_contiguous() for t in tensors)
+        self._keep = tensors
+        lib = cuda_lib()
+        n = self.n = len(tensors)
+        dev = tensors[0].device
+        ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors])
+        lens = (ctypes.c_uint64 * n)(*[t.numel() * t.element_size() for t in tensors])
+        lib.otb_tree_digest_scratch.restype = ctypes.c_uint64
+        need = sum(int(lib.otb_tree_digest_scratch(ctypes.c_uint64(l))) for l in lens)
+        self.work = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        lib.otb_tree_plan_words.restype = ctypes.c_uint64
+        words = int(lib.otb_tree_plan_words(ctypes.c_int(n)))
+        tab = np.zeros(words, dtype=np.uint64)
+        self.level_leaves = (ctypes.c_uint64 * self.MAX_LEVELS)()
+        lib.otb_tree_plan.restype = ctypes.c_long
+        levels = int(lib.otb_tree_plan(ptrs, lens, ctypes.c_int(n), P(self.work), ctypes.c_uint64(self.work.numel()),
+                                       tab.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(words), self.level_leaves,
+                                       ctypes.c_int(self.MAX_LEVELS)))
+        if levels < 0:
+            raise RuntimeError("tree digest plan failed with code %d" % levels)
+        self.levels = levels
+        self.tab = torch.from_numpy(tab.view(np.int64)).to(dev)
+        self.out = torch.empty(n * 32, dtype=torch.uint8, device=dev)
+        self.host = torch.empty(n * 32, dtype=torch.uint8).pin_memory()
+
+    def launch(self, stream=None) -> None:
+        from ..ops.native import P, check, cuda_lib
+
+        st = stream if stream is not None else torch.cuda.current_stream()
+        with torch.cuda.stream(st):
+            check(cuda_lib().otb_tree_run(P(self.tab), ctypes.c_int(self.n), ctypes.c_int(self.levels), self.level_leaves, P(self.out),
+                                          ctypes.c_void_p(st.cuda_stream)), "tree_digest_plan")
+            self.host.copy_(self.out, non_blocking=True)
+
+    def digests(self) -> list[bytes]:
+        raw = self.host.numpy().tobytes()
+        return [raw[i * 32:(i + 1) * 32] for i in range(self.n)]
+
+
 def _prev_bytes(prev: bytes | str | None) -> bytes:
     if prev is None:
         return ZERO_DIGEST

@@ -52,3 +52,28 @@ def test_bf16_gpu_finite_and_repeatable():
     assert all(torch.isfinite(torch.tensor(x[0])) and x[1] > 0 for x in a), a
     assert a == b
     assert kernel_status("cuda") == 0
+
+
+def test_overlapped_state_hash_equals_the_synchronous_one():
+    """begin_state_hash lets the digests run on a side stream under the next step's forward/backward; the chain it
+    yields must be the one the synchronous call gives."""
+    cfg = load_config("open1b_b200", ["model.n_layers=2", "model.vocab_size=4096", "train.seq_len=256", "data.seq_len=256",
+                                      "run.virtual_dp_size=2", "run.dp_shard_size=2"])
+    sync = [h for _, _, h in _run(cfg, "cuda", steps=3, T=256, vocab=4096, td="tree")]
+    eng = TrainEngine(cfg, "cuda")
+    g = torch.Generator().manual_seed(0)
+    prev, pending, got = None, None, []
+    for _ in range(3):
+        eng.zero_grads()
+        for v in range(2):
+            ids = torch.randint(0, 4096, (2, 256), generator=g).to("cuda")
+            lab = torch.randint(0, 4096, (2, 256), generator=g).to("cuda")
+            eng.forward_backward(v, ids, lab, 1)
+        norm = eng.reduce_gradients()  # waits, on the device, for the digests still in flight
+        eng.optimizer_step(3e-4, eng.clip_coefficient(norm, 1.0))
+        if pending is not None:
+            prev = eng.finish_state_hash(pending, prev, None)
+            got.append(prev)
+        pending = eng.begin_state_hash(tensor_digest="tree")
+    got.append(eng.finish_state_hash(pending, prev, None))
+    assert got == sync
