@@ -156,6 +156,22 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
 
     result = {"run_dir": str(run_dir), "hashes": [], "losses": []}
     zero_norm_streak: dict[str, int] = {}
+    pending_hash: list = []  # at most one (step, consumed, handle, batch digest, advances the chain) whose digests are in flight
+
+    def finish_pending_hash():
+        """Fold the state hash whose device digests were started at the end of an earlier step into the chain and the log."""
+        nonlocal chained
+        if not pending_hash:
+            return None
+        h_step, h_consumed, handle, bd, due = pending_hash.pop()
+        digest = engine.finish_state_hash(handle, chained, bd)
+        if due:
+            chained = digest
+        if rank == 0:
+            _append_jsonl(hash_log, {"step": h_step, "consumed_tokens": h_consumed, "state_hash": digest})
+        result["hashes"].append((h_step, digest))
+        return digest
+
     try:
         it = iter(loader)
         while consumed < train_cfg.total_tokens and (max_steps is None or step < max_steps):
@@ -177,6 +193,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                 ce, z = engine.forward_backward(hosted.index(v), ids, labels, accum)
                 ces.append(ce.detach())
                 zs.append(z.detach())
+            finish_pending_hash()  # the previous step's digests ran under this step's forward/backward
             grad_norm = engine.reduce_gradients()
             local_ce = [float(c) for c in ces]
             ce_sum, n_mb = deterministic_scalar_sum(local_ce, world)
@@ -209,13 +226,12 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             if sh_cfg.every_n_steps > 0 and (hash_due or ckpt_due or exit_due or final_step):
                 t0 = time.perf_counter()
                 bd = global_batch_digest() if sh_cfg.include_batch else None
-                step_hash = engine.sharded_state_hash(chained, bd, include_grads=sh_cfg.include_grads)
-                if hash_due:
-                    chained = step_hash
+                pending_hash.append((step, consumed, engine.begin_state_hash(include_grads=sh_cfg.include_grads), bd, hash_due))
+                # a checkpoint, an exit or the last step needs the digest now; a plain cadence hash on a GPU is folded in
+                # during the next step, after its forward/backward has been queued
+                if ckpt_due or exit_due or final_step or not engine.is_cuda:
+                    step_hash = finish_pending_hash()
                 t_hash = (time.perf_counter() - t0) * 1e3
-                if rank == 0:
-                    _append_jsonl(hash_log, {"step": step, "consumed_tokens": consumed, "state_hash": step_hash})
-                result["hashes"].append((step, step_hash))
             t_ckpt = 0.0
             if ckpt_due or exit_due or final_step:
                 t0 = time.perf_counter()
@@ -242,6 +258,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
     except Halt as h:
         log.error("halted by the spike protocol: %s", h)
         result["halted"] = str(h)
+        finish_pending_hash()
     finally:
         metrics.close()
         engine.close()
