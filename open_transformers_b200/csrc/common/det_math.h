@@ -206,6 +206,23 @@ DET_HD float det_exp2_attn(float y) {
   return det_u2f(det_f2u(p) + (det_f2u(t) << 23));
 }
 
+// 2^max(y, -126) with a degree-6 polynomial (relative error about 1e-7): the loss kernels' exponential, where the sum
+// of 128 K terms and the probabilities of the gradient want fp32 accuracy. Same construction as det_exp2_attn.
+DET_HD float det_exp2_acc(float y) {
+  const float yc = fmaxf(y, -126.0f);
+  const float t = det_addf(yc, 12582912.0f);
+  const float kf = det_addf(t, -12582912.0f);
+  const float r = det_fmaf(kf, -1.0f, yc);
+  float p = 1.5403530393381606e-4f;
+  p = det_fmaf(p, r, 1.3333558146428443e-3f);
+  p = det_fmaf(p, r, 9.6181291076284772e-3f);
+  p = det_fmaf(p, r, 5.5504108664821580e-2f);
+  p = det_fmaf(p, r, 2.4022650695910071e-1f);
+  p = det_fmaf(p, r, 6.9314718055994531e-1f);
+  p = det_fmaf(p, r, 1.0f);
+  return det_u2f(det_f2u(p) + (det_f2u(t) << 23));
+}
+
 // sigmoid(x) = 1 / (1 + exp(-x))
 DET_HD float det_sigmoidf(float x) { return det_divf(1.0f, det_addf(1.0f, det_expf(-x))); }
 

@@ -194,26 +194,30 @@ void ce_zloss(T* logits, const long* labels, float* ce_out, float* lse_out, long
       if (write_grad) for (int i = 0; i < V; ++i) st(xr, i, 0.0f);
       continue;
     }
+    const float x_label = ld(xr, label);
     float mx = -INFINITY;
     for (int i = 0; i < V; ++i) mx = fmaxf(mx, ld(xr, i));
-    float part[256];
-    for (int t = 0; t < 256; ++t) part[t] = 0.0f;
+    const float LOG2E = 1.44269504088896341f;
+    const float nm = -(mx * LOG2E);
+    float even[512], odd[512], part[512];
+    for (int t = 0; t < 512; ++t) even[t] = odd[t] = 0.0f;
     for (int i = 0; i < V; ++i) {
-      const int t = (i / 8) % 256;
-      part[t] = part[t] + det_expf(ld(xr, i) + (-mx));
+      const int t = (i / 8) % 512;
+      const float e = det_exp2_acc(det_fmaf(ld(xr, i), LOG2E, nm));
+      if (i & 1) odd[t] = odd[t] + e; else even[t] = even[t] + e;
     }
-    const float s = block_tree_host(part, 256);
+    for (int t = 0; t < 512; ++t) part[t] = even[t] + odd[t];
+    const float s = block_tree_host(part, 512);
     const float lse = det_logf(s) + mx;
-    ce_out[row] = lse + (-ld(xr, label));
+    ce_out[row] = lse + (-x_label);
     lse_out[row] = lse;
     if (!write_grad) continue;
-    const float a = det_fmaf(two_z, lse, 1.0f);
+    const float k = (det_fmaf(two_z, lse, 1.0f) / s) * scale;
     for (int i = 0; i < V; ++i) {
-      const float p = det_expf(ld(xr, i) + (-mx)) / s;
-      float g = p * a;
-      if (i == label) g = g + (-1.0f);
-      st(xr, i, g * scale);
+      if (i == label) continue;
+      st(xr, i, det_exp2_acc(det_fmaf(ld(xr, i), LOG2E, nm)) * k);
     }
+    st(xr, label, det_fmaf(det_exp2_acc(det_fmaf(x_label, LOG2E, nm)), k, -scale));
   }
 }
 

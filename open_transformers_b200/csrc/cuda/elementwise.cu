@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "det_math.h"
 #include "ew_common.cuh"
+#include "tc05.cuh"
 
 namespace {
 
@@ -296,16 +297,22 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gu, const T* __restrict_
 }
 
 // --------------------------------------------------------- fused CE + z-loss
-// One CTA of 256 threads per row of logits [rows, V] (V % 8 == 0). Element i belongs to thread
-// (i / 8) % 256, folded in ascending i; block combine = block_tree_sum. Writes ce[row] = lse - x[label],
-// lse_out[row] = lse, and overwrites the row with d loss / d logits =
-//   (softmax * (1 + 2 z lse) - onehot) * scale      (scale = 1 / (tokens * accum), host reciprocal)
+// One CTA of 512 threads per row of logits [rows, V] (V % 8 == 0). With m = max of the row and L = log2(e):
+//   e_i = exp2(fma(x_i, L, -(m * L)))        (det_exp2_acc, evaluated two at a time with packed fp32 arithmetic)
+//   s   = sum e_i: the 8-element group g = i / 8 belongs to thread g % 512; a thread keeps two ascending chains, the
+//         even and the odd elements of its groups, adds them, and the 512 thread sums go through block_tree_sum
+//   lse = log(s) + m,  ce[row] = lse - x[label],  lse_out[row] = lse
+// and the row is overwritten with d loss / d logits = e_i * k - onehot * scale, k = ((1 + 2 z lse) / s) * scale
+// (scale = 1 / (tokens * accum), host reciprocal; the label's element is fma(e, k, -scale)).
 // Rows with label < 0 are ignored: zero loss, zero gradient.
+constexpr int CE_THREADS = 512;
 template <typename T>
-__global__ void __launch_bounds__(256) ce_zloss_kernel(T* __restrict__ logits, const long* __restrict__ labels,
-                                                       float* __restrict__ ce_out, float* __restrict__ lse_out,
-                                                       long rows, int V, float two_z, float scale, int write_grad) {
+__global__ void __launch_bounds__(CE_THREADS) ce_zloss_kernel(T* __restrict__ logits, const long* __restrict__ labels,
+                                                              float* __restrict__ ce_out, float* __restrict__ lse_out,
+                                                              long rows, int V, float two_z, float scale, int write_grad) {
+  using namespace tc05;
   __shared__ float sh[32];
+  constexpr int SWEEP = CE_THREADS * 8;
   const long row = blockIdx.x;
   T* xr = logits + row * V;
   const long label = labels[row];
@@ -313,45 +320,50 @@ __global__ void __launch_bounds__(256) ce_zloss_kernel(T* __restrict__ logits, c
     if (threadIdx.x == 0) { ce_out[row] = 0.0f; lse_out[row] = 0.0f; }
     if (write_grad) {
       float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int c = threadIdx.x * 8; c < V; c += 2048) Vec8<T>::store(xr + c, z);
+      for (int c = threadIdx.x * 8; c < V; c += SWEEP) Vec8<T>::store(xr + c, z);
     }
     return;
   }
+  const float x_label = to_f<T>(xr[label]);
   float mx = -INFINITY;
-  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+  for (int c = threadIdx.x * 8; c < V; c += SWEEP) {
     float f[8];
     Vec8<T>::load(xr + c, f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) mx = fmaxf(mx, f[e]);
   }
   mx = block_max(mx, sh);
-  float acc = 0.0f;
-  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+  const float LOG2E = 1.44269504088896341f;
+  const f2 l2 = pack2(LOG2E, LOG2E);
+  const float nm = -__fmul_rn(mx, LOG2E);
+  const f2 nm2 = pack2(nm, nm);
+  f2 acc2 = pack2(0.0f, 0.0f);
+  for (int c = threadIdx.x * 8; c < V; c += SWEEP) {
     float f[8];
     Vec8<T>::load(xr + c, f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc = __fadd_rn(acc, det_expf(__fadd_rn(f[e], -mx)));
+    for (int e = 0; e < 8; e += 2) acc2 = add2(acc2, exp2_acc2(fma2(pack2(f[e], f[e + 1]), l2, nm2)));
   }
-  const float s = block_tree_sum(acc, sh);
+  float a0, a1;
+  unpack2(acc2, a0, a1);
+  const float s = block_tree_sum(__fadd_rn(a0, a1), sh);
   const float lse = __fadd_rn(det_logf(s), mx);
   if (threadIdx.x == 0) {
-    ce_out[row] = __fadd_rn(lse, -to_f<T>(xr[label]));
+    ce_out[row] = __fadd_rn(lse, -x_label);
     lse_out[row] = lse;
   }
   if (!write_grad) return;
-  __syncthreads();  // the label logit was read before anyone overwrites it
-  const float a = __fmaf_rn(two_z, lse, 1.0f);
-  for (int c = threadIdx.x * 8; c < V; c += 2048) {
+  __syncthreads();  // every thread has its copy of the label logit before anyone overwrites the row
+  const float k = __fmul_rn(__fdiv_rn(__fmaf_rn(two_z, lse, 1.0f), s), scale);
+  const f2 k2 = pack2(k, k);
+  for (int c = threadIdx.x * 8; c < V; c += SWEEP) {
     float f[8], o[8];
     Vec8<T>::load(xr + c, f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float p = __fdiv_rn(det_expf(__fadd_rn(f[e], -mx)), s);
-      float g = __fmul_rn(p, a);
-      if (c + e == label) g = __fadd_rn(g, -1.0f);
-      o[e] = __fmul_rn(g, scale);
-    }
+    for (int e = 0; e < 8; e += 2) unpack2(mul2(exp2_acc2(fma2(pack2(f[e], f[e + 1]), l2, nm2)), k2), o[e], o[e + 1]);
     Vec8<T>::store(xr + c, o);
+    if (label >= c && label < c + 8)  // the owner of the label's group rewrites that one element
+      xr[label] = from_f<T>(__fmaf_rn(det_exp2_acc(__fmaf_rn(x_label, LOG2E, nm)), k, -scale));
   }
 }
 
@@ -483,7 +495,7 @@ extern "C" int otb_swiglu_bwd(const void* gu, const void* dh, void* dgu, long ro
 extern "C" int otb_ce_zloss(void* logits, const long* labels, float* ce, float* lse, long rows, int V, float two_z,
                             float scale, int write_grad, int dtype, void* stream) {
   if (V % 8) return -2;
-  DISPATCH_T(dtype, ce_zloss_kernel<T><<<(unsigned)rows, 256, 0, S(stream)>>>((T*)logits, labels, ce, lse, rows, V,
+  DISPATCH_T(dtype, ce_zloss_kernel<T><<<(unsigned)rows, CE_THREADS, 0, S(stream)>>>((T*)logits, labels, ce, lse, rows, V,
                                                                                two_z, scale, write_grad);)
   return (int)cudaGetLastError();
 }

@@ -261,6 +261,30 @@ __device__ __forceinline__ f2 exp2_attn2(f2 y) {
   return pack2(__uint_as_float(e0), __uint_as_float(e1));
 }
 
+// det_exp2_acc (csrc/common/det_math.h) on two values at once: same operations, same bits
+__device__ __forceinline__ f2 exp2_acc2(f2 y) {
+  float y0, y1;
+  unpack2(y, y0, y1);
+  const f2 yc = pack2(fmaxf(y0, -126.0f), fmaxf(y1, -126.0f));
+  const f2 t = add2(yc, pack2(12582912.0f, 12582912.0f));
+  const f2 kf = add2(t, pack2(-12582912.0f, -12582912.0f));
+  const f2 r = fma2(kf, pack2(-1.0f, -1.0f), yc);
+  f2 p = pack2(1.5403530393381606e-4f, 1.5403530393381606e-4f);
+  p = fma2(p, r, pack2(1.3333558146428443e-3f, 1.3333558146428443e-3f));
+  p = fma2(p, r, pack2(9.6181291076284772e-3f, 9.6181291076284772e-3f));
+  p = fma2(p, r, pack2(5.5504108664821580e-2f, 5.5504108664821580e-2f));
+  p = fma2(p, r, pack2(2.4022650695910071e-1f, 2.4022650695910071e-1f));
+  p = fma2(p, r, pack2(6.9314718055994531e-1f, 6.9314718055994531e-1f));
+  p = fma2(p, r, pack2(1.0f, 1.0f));
+  float p0, p1, t0, t1;
+  unpack2(p, p0, p1);
+  unpack2(t, t0, t1);
+  uint32_t e0, e1;
+  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(e0) : "r"(__float_as_uint(t0)), "r"(__float_as_uint(p0)));
+  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(e1) : "r"(__float_as_uint(t1)), "r"(__float_as_uint(p1)));
+  return pack2(__uint_as_float(e0), __uint_as_float(e1));
+}
+
 // bf16 pack helpers
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
