@@ -291,14 +291,18 @@ int otb_cpu_embedding_fwd(const long* ids, const void* table, void* out, long ro
     memcpy((char*)out + r * D * es, (const char*)table + ids[r] * D * es, D * es);
   return 0;
 }
-int otb_cpu_embedding_bwd(const void* dy, const long* sorted_tok, const long* seg_start, const long* u_ids,
-                          long n_unique, float* dW, int D, int accumulate, int dtype) {
-#pragma omp parallel for schedule(dynamic, 16)
-  for (long u = 0; u < n_unique; ++u) {
-    float* out = dW + u_ids[u] * D;
+int otb_cpu_embedding_bwd(const void* dy, const long* sorted_ids, const long* sorted_tok, long n, float* dW, int D, int accumulate,
+                          int dtype) {
+#pragma omp parallel for schedule(dynamic, 64)
+  for (long b = 0; b < n; ++b) {
+    const long id = sorted_ids[b];
+    if (b > 0 && sorted_ids[b - 1] == id) continue;  // not the head of its run
+    long e = b + 1;
+    while (e < n && sorted_ids[e] == id) ++e;
+    float* out = dW + id * D;
     for (int c = 0; c < D; ++c) {
       float acc = 0.0f;
-      for (long i = seg_start[u]; i < seg_start[u + 1]; ++i) {
+      for (long i = b; i < e; ++i) {
         const long tok = sorted_tok[i];
         acc = acc + (dtype ? det_bf2f(((const uint16_t*)dy)[tok * D + c]) : ((const float*)dy)[tok * D + c]);
       }

@@ -392,15 +392,20 @@ __global__ void embedding_fwd_kernel(const long* __restrict__ ids, const T* __re
   const int nvec = D * (int)sizeof(T) / 16;
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
 }
-// sorted_tok: token positions stably sorted by id; seg_start[u]..seg_start[u+1] is the run of unique id u_ids[u].
+// sorted_ids: the n token ids in ascending order (stable sort); sorted_tok: the token position of each. One CTA per
+// sorted position: the CTA at the HEAD of a run of equal ids owns that id's row, the others exit at once, so the
+// launch needs no count of distinct ids (no device-to-host read of a data-dependent size).
 // dW[id, :] (+)= sum over the run in ascending token position, fp32.
 template <typename T>
-__global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long* __restrict__ sorted_tok,
-                                     const long* __restrict__ seg_start, const long* __restrict__ u_ids,
-                                     float* __restrict__ dW, int D, int accumulate) {
-  const long u = blockIdx.x;
-  const long b = seg_start[u], e = seg_start[u + 1];
-  float* out = dW + u_ids[u] * D;
+__global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long* __restrict__ sorted_ids,
+                                     const long* __restrict__ sorted_tok, long n, float* __restrict__ dW, int D,
+                                     int accumulate) {
+  const long b = blockIdx.x;
+  const long id = sorted_ids[b];
+  if (b > 0 && sorted_ids[b - 1] == id) return;
+  long e = b + 1;
+  while (e < n && sorted_ids[e] == id) ++e;
+  float* out = dW + id * D;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float acc = 0.0f;
     for (long i = b; i < e; ++i) acc = __fadd_rn(acc, to_f<T>(dy[sorted_tok[i] * D + c]));
@@ -510,11 +515,11 @@ extern "C" int otb_embedding_fwd(const long* ids, const void* table, void* out, 
                                                                                     D);)
   return (int)cudaGetLastError();
 }
-extern "C" int otb_embedding_bwd(const void* dy, const long* sorted_tok, const long* seg_start, const long* u_ids,
-                                 long n_unique, float* dW, int D, int accumulate, int dtype, void* stream) {
-  if (n_unique <= 0) return 0;
-  DISPATCH_T(dtype, embedding_bwd_kernel<T><<<(unsigned)n_unique, 256, 0, S(stream)>>>(
-                        (const T*)dy, sorted_tok, seg_start, u_ids, dW, D, accumulate);)
+extern "C" int otb_embedding_bwd(const void* dy, const long* sorted_ids, const long* sorted_tok, long n, float* dW, int D,
+                                 int accumulate, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  DISPATCH_T(dtype, embedding_bwd_kernel<T><<<(unsigned)n, 256, 0, S(stream)>>>((const T*)dy, sorted_ids, sorted_tok, n, dW, D,
+                                                                               accumulate);)
   return (int)cudaGetLastError();
 }
 extern "C" int otb_cast(const void* in, void* out, long n, int in_bf16, int out_bf16, void* stream) {

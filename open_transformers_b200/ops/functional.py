@@ -244,16 +244,13 @@ def embedding_bwd(dy: torch.Tensor, ids: torch.Tensor, dW: torch.Tensor, accumul
     """dW[id] (+)= sum of dy rows with that id, in ascending token position (stable sort, no atomics)."""
     ids = ids.reshape(-1)
     sorted_ids, order = torch.sort(ids, stable=True)
-    uniq, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
-    seg = torch.zeros(uniq.numel() + 1, dtype=torch.int64, device=ids.device)
-    torch.cumsum(counts, 0, out=seg[1:])
-    order = order.contiguous()
+    sorted_ids, order, n = sorted_ids.contiguous(), order.contiguous(), ids.numel()
     if dy.is_cuda:
-        check(cuda_lib().otb_embedding_bwd(P(dy), P(order), P(seg), P(uniq), L(uniq.numel()), P(dW), I(dW.shape[1]), I(accumulate),
-                                           I(is_bf16(dy)), stream_ptr()), "embedding_bwd")
+        check(cuda_lib().otb_embedding_bwd(P(dy), P(sorted_ids), P(order), L(n), P(dW), I(dW.shape[1]), I(accumulate), I(is_bf16(dy)),
+                                           stream_ptr()), "embedding_bwd")
     else:
-        check(cpu_lib().otb_cpu_embedding_bwd(P(dy), P(order), P(seg), P(uniq), L(uniq.numel()), P(dW), I(dW.shape[1]), I(accumulate),
-                                              I(is_bf16(dy))), "embedding_bwd")
+        check(cpu_lib().otb_cpu_embedding_bwd(P(dy), P(sorted_ids), P(order), L(n), P(dW), I(dW.shape[1]), I(accumulate), I(is_bf16(dy))),
+              "embedding_bwd")
 
 
 # --------------------------------------------------------------------------- RoPE tables
