@@ -58,41 +58,49 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
-// one warp per slab of SLAB rows; dgamma partial [slab][D] = ascending-row fold inside the slab.
+// One CTA of SLAB warps per slab of SLAB rows, one warp per row: the row stays in registers (as loaded, 16-byte
+// vectors) between the dot product and the dx pass, so x and dy are read once. dgamma partial [slab][D] is the
+// ascending-row fold inside the slab: every warp leaves its row's dy * xhat products in shared memory and, after one
+// barrier, the CTA adds the SLAB rows of each column in row order (the same chain a single warp would have run).
 // MAXC = max number of 8-wide column chunks per lane (D <= 256 * MAXC).
 constexpr int NORM_SLAB = 8;
 template <typename T, int MAXC>
-__global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
-                                   const float* __restrict__ rstd_in, T* __restrict__ dx,
-                                   float* __restrict__ dgamma_partial, long rows, int D, float inv_d) {
-  const long slab = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const long r0 = slab * NORM_SLAB;
-  if (r0 >= rows) return;
-  float dg[MAXC][8];
-#pragma unroll
-  for (int j = 0; j < MAXC; ++j)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) dg[j][e] = 0.0f;
-  for (long row = r0; row < r0 + NORM_SLAB && row < rows; ++row) {
+__global__ void __launch_bounds__(NORM_SLAB * 32) rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                                                    const float* __restrict__ rstd_in, T* __restrict__ dx,
+                                                                    float* __restrict__ dgamma_partial, long rows, int D, float inv_d) {
+  extern __shared__ float prod[];  // [NORM_SLAB][MAXC * 256] when dgamma is wanted
+  const long slab = blockIdx.x;
+  const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5;
+  const long row = slab * NORM_SLAB + wrow;
+  const bool live = row < rows;
+  if (live) {
     const float rstd = rstd_in[row];
     const T* xr = x + row * D;
     const T* dyr = dy + row * D;
+    Raw8<T> xraw[MAXC], draw[MAXC];
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane * 8 + j * 256;
+      if (c < D) {
+        xraw[j].load(xr + c);
+        draw[j].load(dyr + c);
+      }
+    }
     float acc = 0.0f;
 #pragma unroll
     for (int j = 0; j < MAXC; ++j) {
       const int c = lane * 8 + j * 256;
       if (c < D) {
         float xf[8], df[8], g[8];
-        Vec8<T>::load(xr + c, xf);
-        Vec8<T>::load(dyr + c, df);
+        xraw[j].unpack(xf);
+        draw[j].unpack(df);
         if (w) Vec8<T>::load(w + c, g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float xh = __fmul_rn(xf[e], rstd);
           const float gy = w ? __fmul_rn(df[e], g[e]) : df[e];
           acc = __fmaf_rn(gy, xh, acc);
-          dg[j][e] = __fadd_rn(dg[j][e], __fmul_rn(df[e], xh));
+          if (dgamma_partial) prod[wrow * (MAXC * 256) + j * 256 + e * 32 + lane] = __fmul_rn(df[e], xh);  // lanes side by side: no bank conflict
         }
       }
     }
@@ -103,8 +111,8 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict
       const int c = lane * 8 + j * 256;
       if (c < D) {
         float xf[8], df[8], g[8], o[8];
-        Vec8<T>::load(xr + c, xf);
-        Vec8<T>::load(dyr + c, df);
+        xraw[j].unpack(xf);
+        draw[j].unpack(df);
         if (w) Vec8<T>::load(w + c, g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -117,13 +125,21 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict
     }
   }
   if (dgamma_partial) {
+    __syncthreads();
+    const int nrow = (int)((rows - slab * NORM_SLAB < NORM_SLAB) ? rows - slab * NORM_SLAB : NORM_SLAB);
     float* out = dgamma_partial + slab * D;
-#pragma unroll
-    for (int j = 0; j < MAXC; ++j) {
+    for (int j = wrow; j < MAXC; j += NORM_SLAB) {  // warp j folds column chunk j; a lane owns the same 8 columns as above
       const int c = lane * 8 + j * 256;
       if (c < D) {
-        *reinterpret_cast<float4*>(out + c) = make_float4(dg[j][0], dg[j][1], dg[j][2], dg[j][3]);
-        *reinterpret_cast<float4*>(out + c + 4) = make_float4(dg[j][4], dg[j][5], dg[j][6], dg[j][7]);
+        float a[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float t = 0.0f;
+          for (int r = 0; r < nrow; ++r) t = __fadd_rn(t, prod[r * (MAXC * 256) + j * 256 + e * 32 + lane]);
+          a[e] = t;
+        }
+        *reinterpret_cast<float4*>(out + c) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(out + c + 4) = make_float4(a[4], a[5], a[6], a[7]);
       }
     }
   }
@@ -452,9 +468,13 @@ extern "C" int otb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                float* dgamma_partial, long rows, int D, float inv_d, int dtype, void* stream) {
   if (D % 8 || D > 256 * 16) return -2;
   const long slabs = (rows + NORM_SLAB - 1) / NORM_SLAB;
-#define RB(MAXC)                                                                                     \
-  DISPATCH_T(dtype, rmsnorm_bwd_kernel<T, MAXC><<<blocks_for(slabs, 4), 128, 0, S(stream)>>>(         \
-                        (const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dgamma_partial, rows, D, inv_d);)
+#define RB(MAXC)                                                                                                          \
+  DISPATCH_T(dtype, {                                                                                                     \
+    static int attr = cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, NORM_SLAB * 256 * MAXC * 4); \
+    if (attr) return attr;                                                                                                \
+    rmsnorm_bwd_kernel<T, MAXC><<<(unsigned)slabs, NORM_SLAB * 32, dgamma_partial ? NORM_SLAB * 256 * MAXC * 4 : 0, S(stream)>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, \
+                                                                                     dgamma_partial, rows, D, inv_d);     \
+  })
   if (D <= 256) { RB(1) } else if (D <= 1024) { RB(4) } else if (D <= 2048) { RB(8) } else { RB(16) }
 #undef RB
   if (dgamma_partial) pair_tree_cols_launch(dgamma_partial, slabs, D, S(stream));
