@@ -40,7 +40,7 @@ from ..config.schema import RootConfig
 from ..models import build_model, fused_ce_z_loss, init_weights
 from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
 from ..ops import functional as K
-from ..ops.autograd import GradSlot
+from ..ops.autograd import GradSlot, wgrad_join
 from ..ops.native import F, I, L, P, check, cpu_lib, cuda_lib, stream_ptr
 from ..parallel.flat import FlatLayout, PeerBuffer
 from . import state_hash as SH
@@ -258,6 +258,8 @@ class TrainEngine:
         S, R = self.dp_shard, self.dp_replicate
         per = self.V // self.world
         self._wait_pending_hash()
+        if self.is_cuda:
+            wgrad_join()  # weight-gradient GEMMs run on a second stream during the backward pass
         if self.nccl_mode and self.world > 1:
             # throughput-only baseline: library all-reduce, order not pinned
             acc = self.grads[0]
