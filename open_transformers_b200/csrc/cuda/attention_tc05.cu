@@ -1052,10 +1052,10 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constan
 
 // ------------------------------------------------ backward: dQ, two query tiles per CTA
 // Same organisation as the forward: one CTA owns two adjacent 128-row query tiles, one thread per query row, and the
-// tensor core serves one tile while the other tile's threads do the element math. Keys advance in steps of 64:
-// S = Q K^T and dP = dO V^T (128 x 64 each) land in tensor memory, the row's thread turns them into
-// dS = p (dP - delta) scale, stores it as bf16 pairs over the first 32 columns of S, and dQ += dS K runs with dS as the
-// tensor-memory A operand. dQ accumulates over ascending keys in 16-key tensor-core steps, exactly as before.
+// tensor core serves one tile while the other tile's threads do the element math (two threads per row, each with half
+// of the step's keys; nothing crosses threads in the backward). Keys advance in steps of 64: S = Q K^T and
+// dP = dO V^T (128 x 64 each) land in tensor memory, the row's threads turn them into dS = p (dP - delta) scale, store
+// it as bf16 pairs over their own score columns, and dQ += dS K runs with dS as the tensor-memory A operand. dQ accumulates over ascending keys in 16-key tensor-core steps, exactly as before.
 // Tensor memory per tile: S 64 | dP 64 | dQ 128 columns.
 constexpr int HK = 64;  // keys per step
 
@@ -1081,7 +1081,7 @@ struct BarsQ2 {
 };
 
 template <int D>
-__global__ void __launch_bounds__(F2_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ, long lddq, int T,
@@ -1116,7 +1116,7 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&bars->qdo_full, 1);
     for (int s = 0; s < ST; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
-    for (int x = 0; x < 2; ++x) { mbar_init(&bars->sdp_full[x], 1); mbar_init(&bars->ds_ready[x], 4); mbar_init(&bars->dq_done[x], 1); }
+    for (int x = 0; x < 2; ++x) { mbar_init(&bars->sdp_full[x], 1); mbar_init(&bars->ds_ready[x], 8); mbar_init(&bars->dq_done[x], 1); }
     bars->abort_flag = 0;
     mbar_fence_init();
   }
@@ -1174,7 +1174,7 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
             const uint32_t aK = smem_u32(sK + st * KT);
 #pragma unroll
             for (int kk = 0; kk < HK / 16; ++kk)
-              mma_f16_ts(tmem + X * 256 + 128, tmem + X * 256 + kk * 8, desc_mn_r<HK>(aK, kk), idQ, (done[X] | kk) != 0);
+              mma_f16_ts(tmem + X * 256 + 128, tmem + X * 256 + (kk >> 1) * 32 + (kk & 1) * 8, desc_mn_r<HK>(aK, kk), idQ, (done[X] | kk) != 0);
             ++done[X];
             if (u == (X == 0 ? uhiA : uhiB)) mma_commit(&bars->dq_done[X]);
           }
@@ -1192,14 +1192,15 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       }
     }
   } else {
-    const int X = (warp - 2) >> 2;
+    // sixteen element warps: two threads per query row (32 of the step's 64 keys each), 8 warps per tile
+    const int X = (warp - 2) >> 3;
     const int quad = warp & 3;
+    const int hf = ((warp - 2) & 7) >> 2;    // which half of the step's keys
     const int r = quad * 32 + lane;
     const int q0 = (tile0 + X) * BQ;
     const int qi = q0 + r;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
-    const uint32_t tS = tmem + X * 256 + lane_off, tDP = tS + 64, tDQ = tS + 128;
-    const int uhiX = X == 0 ? uhiA : uhiB;
+    const uint32_t tS = tmem + X * 256 + lane_off + hf * 32, tDP = tS + 64, tDQ = tmem + X * 256 + 128 + lane_off;
     const bool row_ok = qi < T;
     bool ok = true;
     if (X == 0 || hasB) {
@@ -1214,40 +1215,16 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
         const bool need_mask = (k0 + HK - 1 > q0) || (window > 0 && k0 <= q0 + BQ - 1 - window) || (q0 + BQ > T);
         if (!mbar_wait(&bars->sdp_full[X], cnt & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        uint32_t unused[8];
-        if (!need_mask) {
-          // 16 keys at a time; the next 16 scores and dP values are in flight while the current ones are processed
-          uint32_t sa[16], da[16], sb[16], db[16], pk[8];
-          tmem_ld_32x32b_x16(tS, sa);
-          tmem_ld_32x32b_x16(tDP, da);
+        // dS (bf16 pairs, 8 columns per 16 keys) goes over the thread's own score columns, which it has read by then
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sa[16], da[16], pk[8], unused[8];
+          tmem_ld_32x32b_x16(tS + c * 16, sa);
+          tmem_ld_32x32b_x16(tDP + c * 16, da);
           tmem_ld_wait();
-          tmem_ld_32x32b_x16(tS + 16, sb);
-          tmem_ld_32x32b_x16(tDP + 16, db);
-          bwd_probs<false, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
-          tmem_ld_wait();
-          tmem_st_32x32b_x8(tS, pk);
-          tmem_ld_32x32b_x16(tS + 32, sa);
-          tmem_ld_32x32b_x16(tDP + 32, da);
-          bwd_probs<false, false, 16>(sb, db, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
-          tmem_ld_wait();
-          tmem_st_32x32b_x8(tS + 8, pk);
-          tmem_ld_32x32b_x16(tS + 48, sb);
-          tmem_ld_32x32b_x16(tDP + 48, db);
-          bwd_probs<false, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
-          tmem_ld_wait();
-          tmem_st_32x32b_x8(tS + 16, pk);
-          bwd_probs<false, false, 16>(sb, db, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
-          tmem_st_32x32b_x8(tS + 24, pk);
-        } else {
-#pragma unroll 1
-          for (int c = 0; c < HK / 16; ++c) {
-            uint32_t sa[16], da[16], pk[8];
-            tmem_ld_32x32b_x16(tS + c * 16, sa);
-            tmem_ld_32x32b_x16(tDP + c * 16, da);
-            tmem_ld_wait();
-            bwd_probs<true, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, row_ok, k0 + c * 16, qi, window, unused, pk);
-            tmem_st_32x32b_x8(tS + c * 8, pk);
-          }
+          if (need_mask) bwd_probs<true, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, row_ok, k0 + hf * 32 + c * 16, qi, window, unused, pk);
+          else bwd_probs<false, false, 16>(sa, da, c_log2, lse_r, dl_r, scale, true, 0, 0, 0, unused, pk);
+          tmem_st_32x32b_x8(tS + c * 8, pk);
         }
         tmem_st_wait();
         ++cnt;
@@ -1258,11 +1235,12 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
       ok = ok && mbar_wait(&bars->dq_done[X], 0, abort_flag);
       tc_fence_after();
       if (ok) {
-        __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D;
+        constexpr int DHALF = D / 2;
+        __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D + hf * DHALF;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < DHALF / 32; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tDQ + c * 32, v);
+          tmem_ld_32x32b_x32(tDQ + hf * DHALF + c * 32, v);
           tmem_ld_wait();
           if (row_ok) {
             uint4* dst = reinterpret_cast<uint4*>(dqrow + c * 32);
@@ -1705,7 +1683,7 @@ extern "C" int otb_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldq
     else
       attn_bwd_kv_kernel<128><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<128>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
                                                                                    lddqkv, T, H, Hkv, window, scale, c_log2, status);
-    attn_bwd_q2_kernel<128><<<gq, F2_THREADS, attn_bwd_q2_smem_bytes<128>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H,
+    attn_bwd_q2_kernel<128><<<gq, ATT_THREADS, attn_bwd_q2_smem_bytes<128>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H,
                                                                                   Hkv, window, scale, c_log2, status);
   } else {
     static int once = set_smem(attn_bwd_kv_kernel<64>, attn_bwd_smem_bytes<64>()) |
@@ -1718,7 +1696,7 @@ extern "C" int otb_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldq
     else
       attn_bwd_kv_kernel<64><<<gkv, ATT_THREADS, attn_bwd_smem_bytes<64>(), s>>>(tq, tv, tdo, lse, delta, dKp, lddqk, dVp,
                                                                                  lddqkv, T, H, Hkv, window, scale, c_log2, status);
-    attn_bwd_q2_kernel<64><<<gq, F2_THREADS, attn_bwd_q2_smem_bytes<64>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H, Hkv,
+    attn_bwd_q2_kernel<64><<<gq, ATT_THREADS, attn_bwd_q2_smem_bytes<64>(), s>>>(tq, tdo, tk64, tv64, lse, delta, dQp, lddqk, T, H, Hkv,
                                                                                 window, scale, c_log2, status);
   }
   return (int)cudaGetLastError();
