@@ -146,14 +146,14 @@ def main() -> int:
                     ids, labels = a.to(device, non_blocking=True), b.to(device, non_blocking=True)
                 ce, z = eng.forward_backward(vi, ids, labels, accum)
                 last_ce = ce
+        if not args.no_hash:
+            flush_hash()  # the previous step's digests ran under this step's forward/backward; fold them in while it drains
         norm = eng.reduce_gradients()
         lr = sched(state["consumed"], cfg.train.total_tokens)
         eng.optimizer_step(lr, eng.clip_coefficient(norm, cfg.train.grad_clip))
         state["consumed"] += tokens_per_step
         if not args.no_hash:
-            # the digests of this step's state run on a side stream under the next step's forward/backward;
-            # the previous step's hash is folded into the chain here
-            flush_hash()
+            # the digests of this step's state run on a side stream under the next step's forward/backward
             state["pending"] = eng.begin_state_hash(include_grads=cfg.train.state_hash.include_grads)
         return last_ce, norm
 

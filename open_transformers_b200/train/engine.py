@@ -433,9 +433,28 @@ class TrainEngine:
                 digs = handle["digests"]
             seg_digests = dict(zip(handle["keys"], digs))
             if self.peer:
-                objs: list = [None] * self.world
-                dist.all_gather_object(objs, seg_digests, group=self.group)
-                seg_digests = {k: v for d in objs for k, v in d.items()}
+                # every process knows which (parameter, shard, field) digests every other one owns, so only the 32-byte
+                # values travel: one all-gather of a fixed-size byte tensor
+                cache = self.__dict__.setdefault("_hash_keys_by_rank", {})
+                keys_by_rank = cache.get(include_grads)
+                if keys_by_rank is None:
+                    fields = [tag for tag, _ in self._hash_fields(include_grads)]
+                    keys_by_rank = cache[include_grads] = [
+                        [(lay.segments[si].param, lay.segments[si].shard, tag) for si in range(slo, shi) for tag in fields]
+                        for slo, shi in lay.owner_ranges(self.world)]
+                width = 32 * max(max(len(k) for k in keys_by_rank), 1)
+                mine = torch.zeros(width, dtype=torch.uint8)
+                raw = b"".join(digs)
+                mine[: len(raw)] = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+                mine = mine.to(self.device)
+                parts = [torch.empty_like(mine) for _ in range(self.world)]
+                dist.all_gather(parts, mine, group=self.group)
+                allraw = torch.stack(parts).cpu().numpy().tobytes()
+                seg_digests = {}
+                for r, keys in enumerate(keys_by_rank):
+                    base = r * width
+                    for j, k in enumerate(keys):
+                        seg_digests[k] = allraw[base + 32 * j: base + 32 * j + 32]
         order = sorted(range(len(self.names)), key=lambda i: self.names[i])
         step_bytes = b"optim_step\0" + int(handle["opt_step"]).to_bytes(8, "little", signed=True)
         empty = SH.tree_digest_bytes(b"") if td == "tree" else None
