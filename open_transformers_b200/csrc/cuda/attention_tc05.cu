@@ -1,17 +1,18 @@
 // Causal / sliding-window flash attention for sm_100a on tcgen05 tensor cores, GQA-native.
 //
-// Three kernels share one structure (warp 0: TMA producer, warp 1: tcgen05.mma issuer, warps
-// 2..17: four threads per row - one per 32-key quarter - doing the softmax arithmetic straight out of
-// tensor memory; warp w may touch TMEM lanes 32*(w%4)..+31, so warps w, w+4, w+8, w+12 share rows):
+// Kernels (all: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer, the rest = element warps working straight out of
+// tensor memory; a warp may touch TMEM lanes 32*(w%4)..+31 only):
 //
-//   attn_fwd    CTA = (batch, query head, 128 query rows); loops over 128-key blocks in ascending
-//               key order:  S = Q K^T (TMEM) -> online softmax -> P (bf16, shared) -> P V (TMEM,
-//               fresh per block) -> O = O*alpha + PV in registers.
-//   attn_bwd_kv CTA = (batch, KV head, 128 keys); loops over the query heads of the group and
-//               the query blocks that see these keys, both ascending; dV += P^T dO and
-//               dK += dS^T Q accumulate in TMEM.
-//   attn_bwd_q  CTA = (batch, query head, 128 query rows); loops over key blocks ascending;
-//               dQ += dS K accumulates in TMEM.
+//   attn_fwd2     CTA = (batch, query head, TWO 128-row query tiles); one thread per row; S = Q K^T (TMEM) -> online
+//                 softmax -> P written back over S as bf16 (the A operand of P V) -> O accumulates in TMEM.
+//   attn_bwd_kv2  CTA = (batch, KV head, 128 keys); scores formed transposed (S^T, dP^T: lanes are keys), P^T / dS^T
+//                 written back in place, dV += P^T dO and dK += dS^T Q with the A operand in TMEM; 64-query steps over
+//                 the heads of the group and the query blocks that see these keys, both ascending.
+//   attn_bwd_q2   CTA = (batch, query head, two query tiles); two threads per row; dS written back over S;
+//                 dQ += dS K with dS in TMEM; 64-key steps ascending.
+//   attn_fwd      (one tile per CTA, four threads per row, P through shared memory, O in registers) serves the int8 P V
+//                 variant; attn_bwd_kv (one score buffer, P / dS through shared memory) serves sequence lengths that
+//                 are not a multiple of 64.
 //
 // No atomics, no split accumulation: every output element has one owner CTA and a fixed
 // summation order, so results are identical for any grid, stream or GPU count. The window rule
@@ -883,170 +884,6 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 3u);
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
-}
-
-// ------------------------------------------------------------------ backward: dQ
-template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
-attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant__ CUtensorMap tmV,
-                  const __grid_constant__ CUtensorMap tmDO, const float* __restrict__ lse,
-                  const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ, long lddq, int T, int H, int Hkv,
-                  int window, float scale, float c_log2, uint32_t* __restrict__ status) {
-  constexpr int TILE = BQ * D * 2;
-  constexpr int ST = 2;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
-  uint8_t* sQ = smem;
-  uint8_t* sDO = sQ + TILE;
-  uint8_t* sDS = sDO + TILE;
-  uint8_t* sK = sDS + BQ * BKV * 2;  // [ST]
-  uint8_t* sV = sK + ST * TILE;      // [ST]
-  Bars* bars = reinterpret_cast<Bars*>(sV + ST * TILE);
-  uint64_t* qdo_full = &bars->b[0];
-  uint64_t* kv_full = &bars->b[1];   // [ST]
-  uint64_t* kv_empty = &bars->b[3];  // [ST]
-  uint64_t* sdp_full = &bars->b[5];
-  uint64_t* sdp_empty = &bars->b[6];
-  uint64_t* ds_ready = &bars->b[7];
-  uint64_t* dq_done = &bars->b[8];
-  volatile uint32_t* abort_flag = &bars->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = (T + BQ - 1) / BQ;
-  const int qt = nq - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int g = h / (H / Hkv);
-  const int q0 = qt * BQ;
-  const int jmax = qt;
-  const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / BKV : 0;
-  const int n = jmax - jmin + 1;
-
-  if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1);
-    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(sdp_empty, SOFTMAX_WARPS); mbar_init(ds_ready, SOFTMAX_WARPS); mbar_init(dq_done, 1);
-    bars->abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) { tmem_alloc(&bars->tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bars->tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-
-  if (warp == 0) {
-    if (elect_one()) {
-      mbar_expect_tx(qdo_full, 2 * TILE);
-      load_tile<D>(sQ, &tmQK, qdo_full, h * D, q0, b);
-      load_tile<D>(sDO, &tmDO, qdo_full, h * D, q0, b);
-      for (int i = 0; i < n; ++i) {
-        const int st = i % ST;
-        const int k0 = (jmin + i) * BKV;
-        if (!mbar_wait(&kv_empty[st], ((i / ST) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&kv_full[st], 2 * TILE);
-        load_tile<D>(sK + st * TILE, &tmQK, &kv_full[st], (H + g) * D, k0, b);
-        load_tile<D>(sV + st * TILE, &tmV, &kv_full[st], (H + Hkv + g) * D, k0, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (elect_one()) {
-      constexpr uint32_t idS = make_idesc(128, BKV, 0, 0);
-      constexpr uint32_t idQ = make_idesc(128, D, 0, 1);  // dQ = dS K : A K-major, B MN-major
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(qdo_full, 0, abort_flag);
-      auto issue_sdp = [&](int i) {
-        const int st = i % ST;
-        if (!mbar_wait(&kv_full[st], (i / ST) & 1, abort_flag)) return false;
-        if (!mbar_wait(sdp_empty, (i & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t aK = smem_u32(sK + st * TILE), aV = smem_u32(sV + st * TILE);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tS, desc_k(aQ, kk), desc_k(aK, kk), idS, kk != 0);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_f16_ss(tDP, desc_k(aDO, kk), desc_k(aV, kk), idS, kk != 0);
-        mma_commit(sdp_full);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
-      for (int i = 0; i < n && ok; ++i) {
-        const int st = i % ST;
-        // S and dP of the next block run while the softmax warps work on this one
-        if (i + 1 < n) { if (!issue_sdp(i + 1)) { ok = false; break; } }
-        if (!mbar_wait(ds_ready, i & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t aK = smem_u32(sK + st * TILE);
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) mma_f16_ss(tDQ, desc_k(aDS, kk), desc_mn(aK, kk), idQ, (i | kk) != 0);
-        mma_commit(dq_done);
-        mma_commit(&kv_empty[st]);
-      }
-    }
-  } else {
-    constexpr int DH = D / NSPLIT;
-    constexpr int CW = DH >= 32 ? 32 : 16;
-    const int qd = warp & 3;
-    const int part = (warp - 2) >> 2;
-    const int r = qd * 32 + lane;
-    const int qi = q0 + r;
-    const uint32_t lane_off = uint32_t(qd * 32) << 16;
-    const bool row_ok = qi < T;
-    const float lse_r = row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f;
-    const float dl_r = row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f;
-    bool ok = true;
-    for (int i = 0; i < n && ok; ++i) {
-      const int j = jmin + i;
-      const int kbase = j * BKV + part * KPT;
-      const bool need_mask = (j == jmax) || (window > 0 && j * BKV < q0 + BQ - window) || (q0 + BQ > T);
-      if (!mbar_wait(sdp_full, i & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t pk[KPT / 2];
-      {
-        uint32_t vs[KPT], vd[KPT], unused[KPT / 2];
-        tmem_ld_32x32b_x32(tS + lane_off + part * KPT, vs);
-        tmem_ld_32x32b_x32(tDP + lane_off + part * KPT, vd);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sdp_empty);  // S and dP are in registers: the next block's products may overwrite them
-        if (need_mask) bwd_probs<true, false>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, kbase, qi, window, unused, pk);
-        else bwd_probs<false, false>(vs, vd, c_log2, lse_r, dl_r, scale, row_ok, kbase, qi, window, unused, pk);
-      }
-      // the dS buffer is free once the previous block's dQ product has read it
-      if (i > 0) { if (!mbar_wait(dq_done, (i - 1) & 1, abort_flag)) { ok = false; break; } }
-      uint8_t* base = sDS + (part >> 1) * 16384;
-#pragma unroll
-      for (int w = 0; w < 4; ++w)
-        *reinterpret_cast<uint4*>(base + swz(r, (part & 1) * 4 + w)) = make_uint4(pk[4 * w], pk[4 * w + 1], pk[4 * w + 2], pk[4 * w + 3]);
-      fence_proxy_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
-    }
-    if (ok && mbar_wait(dq_done, (n - 1) & 1, abort_flag)) {
-      tc_fence_after();
-      __nv_bfloat16* dqrow = dQ + ((long)b * T + qi) * lddq + (long)h * D + part * DH;
-#pragma unroll
-      for (int c = 0; c < DH / CW; ++c) {
-        uint32_t v[CW];
-        tmem_ld_cols<CW>(tDQ + lane_off + part * DH + c * CW, v);
-        tmem_ld_wait();
-        if (row_ok) {
-          uint4* dst = reinterpret_cast<uint4*>(dqrow + c * CW);
-#pragma unroll
-          for (int w = 0; w < CW / 8; ++w)
-            dst[w] = make_uint4(pack_bf16(__uint_as_float(v[8 * w]), __uint_as_float(v[8 * w + 1])),
-                                pack_bf16(__uint_as_float(v[8 * w + 2]), __uint_as_float(v[8 * w + 3])),
-                                pack_bf16(__uint_as_float(v[8 * w + 4]), __uint_as_float(v[8 * w + 5])),
-                                pack_bf16(__uint_as_float(v[8 * w + 6]), __uint_as_float(v[8 * w + 7])));
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && bars->abort_flag && status) atomicExch(status, 4u);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 

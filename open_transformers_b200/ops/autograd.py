@@ -18,12 +18,30 @@ from . import functional as K
 
 
 class GradSlot:
-    """fp32 accumulation target of one parameter (a view into a flat gradient buffer)."""
+    """fp32 accumulation target of one parameter (a view into a flat gradient buffer).
 
-    __slots__ = ("buf",)
+    ``fresh`` means the buffer's current contents are stale (first micro-batch of a virtual rank in this step): the
+    first writer STORES its result instead of accumulating, which spares the step a 4-byte-per-parameter memset and the
+    read half of the accumulate, and sets ``written``. Whoever owns the slots zeroes those still unwritten after the
+    backward pass (parameters that received no gradient)."""
+
+    __slots__ = ("buf", "fresh", "written")
 
     def __init__(self, buf: torch.Tensor | None = None):
         self.buf = buf
+        self.fresh = False
+        self.written = False
+
+    def take(self) -> bool:
+        """True if the caller must overwrite (store); later callers accumulate."""
+        first = self.fresh and not self.written
+        self.written = True
+        return first
+
+    def zero_if_first(self) -> None:
+        """For writers that can only accumulate: clear a stale buffer before the first accumulation."""
+        if self.take():
+            self.buf.zero_()
 
 
 def _flat2d(x: torch.Tensor) -> torch.Tensor:
@@ -95,12 +113,13 @@ class LinearFn(Function):
                 ready = torch.cuda.Event()
                 ready.record()
                 side.wait_event(ready)  # dy exists; earlier accumulations into this slot were issued on `side` too
+                epi = K.EPI_STORE_F32 if ctx.slot.take() else K.EPI_ACC_F32
                 with torch.cuda.stream(side):
-                    K.gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.slot.buf, epi=K.EPI_ACC_F32)
+                    K.gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.slot.buf, epi=epi)
                 dy2.record_stream(side)  # the allocator must not hand these blocks out again before the GEMM has read them
                 x2.record_stream(side)
             else:
-                K.gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.slot.buf, epi=K.EPI_ACC_F32)
+                K.gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.slot.buf, epi=K.EPI_STORE_F32 if ctx.slot.take() else K.EPI_ACC_F32)
         elif ctx.needs_input_grad[1]:
             gm = K.gemm(dy2, x2, a_mn=True, b_mn=True, epi=K.EPI_STORE_F32).to(ctx.master_dtype)
         return dx, gm, None, None, (dy if ctx.has_res else None)
@@ -132,7 +151,10 @@ class RMSNormFn(Function):
         gm = None
         if need_dg:
             if ctx.slot is not None and ctx.slot.buf is not None:
-                ctx.slot.buf.add_(dg)
+                if ctx.slot.take():
+                    ctx.slot.buf.copy_(dg)
+                else:
+                    ctx.slot.buf.add_(dg)
             else:
                 gm = dg.to(ctx.master_dtype)
         return dx.view(ctx.shape), gm, None, None, None
@@ -209,6 +231,7 @@ class EmbeddingFn(Function):
         (ids,) = ctx.saved_tensors
         dy2 = _flat2d(dy).contiguous()
         if ctx.slot is not None and ctx.slot.buf is not None:
+            ctx.slot.zero_if_first()  # rows of tokens that do not occur must read zero
             K.embedding_bwd(dy2, ids, ctx.slot.buf, True)
             return None, None, None, None
         dW = torch.zeros(ctx.tshape, dtype=torch.float32, device=dy.device)
@@ -300,10 +323,14 @@ class QuantLinearFn(Function):
         N, Kd = w.shape
         gs = 1.0 / math.sqrt(float(Kd) * float(qmax_w))
         use_slot = ctx.slot_w is not None and ctx.slot_w.buf is not None
+        if use_slot:
+            ctx.slot_w.zero_if_first()
         dW = ctx.slot_w.buf if use_slot else torch.zeros((N, Kd), dtype=torch.float32, device=w.device)
         ds = None
         if learn_step:
             s_slot = ctx.slot_s is not None and ctx.slot_s.buf is not None
+            if s_slot:
+                ctx.slot_s.zero_if_first()
             ds = ctx.slot_s.buf if s_slot else torch.zeros(N, dtype=torch.float32, device=w.device)
         # a fixed (absmax) step never clips, so its mask bound is one grid point wider than the grid
         K.lsq_bwd_(G, w, step, sa, qmax_w if learn_step else qmax_w + 1, gs, dW, ds)

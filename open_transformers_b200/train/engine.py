@@ -128,6 +128,9 @@ class TrainEngine:
         self.grad_red = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.buf_grads = [alloc(4 * n, shared=True) for _ in self.hosted]
         self.grads = [b.typed(torch.float32) for b in self.buf_grads]
+        for g in self.grads:
+            g.zero_()
+        self._stale = [False] * len(self.grads)
         self.opt_step = 0
 
         # ---- chunk tables on the device, ownership
@@ -190,18 +193,30 @@ class TrainEngine:
                 rows = lay.shapes[iq][0] + lay.shapes[ik][0] + lay.shapes[iv][0]
                 cols = lay.shapes[iq][1]
                 slot = GradSlot()
-                master_v = self.master[o0:o0 + rows * cols].view(rows, cols)
                 compute_v = self.compute[o0:o0 + rows * cols].view(rows, cols)
                 mod._fused_qkv = (byname["%s.wq.weight" % mname], compute_v, slot)
-                self._fused.append((slot, o0, rows, cols))
-                del master_v
+                self._fused.append((slot, o0, rows, cols, (iq, ik, iv)))
 
-    def _bind_slots(self, gbuf: torch.Tensor | None) -> None:
+    def _bind_slots(self, gbuf: torch.Tensor | None, fresh: bool = False) -> None:
+        """Point every gradient slot at its view of ``gbuf``. ``fresh``: the buffer holds last step's values, so the
+        first writer of each slot stores instead of accumulating (see ``GradSlot``)."""
         lay = self.layout
         for i, slot in enumerate(self.slots):
             slot.buf = None if gbuf is None else lay.view(gbuf, i)
-        for slot, o0, rows, cols in self._fused:
+            slot.fresh, slot.written = fresh, False
+        for slot, o0, rows, cols, _members in self._fused:
             slot.buf = None if gbuf is None else gbuf[o0:o0 + rows * cols].view(rows, cols)
+            slot.fresh, slot.written = fresh, False
+
+    def _zero_unwritten_slots(self) -> None:
+        """After the first backward pass into a stale buffer: parameters nobody wrote get an explicit zero."""
+        covered = set()
+        for slot, _o0, _rows, _cols, members in self._fused:
+            if slot.written:
+                covered.update(members)
+        for i, slot in enumerate(self.slots):
+            if not slot.written and i not in covered and slot.buf is not None:
+                slot.buf.zero_()
 
     def named_master(self):
         return [(n, self.layout.view(self.master, i)) for i, n in enumerate(self.names)]
@@ -236,7 +251,8 @@ class TrainEngine:
     # ---------------------------------------------------------------------------- one step
     def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int):
         """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
-        self._bind_slots(self.grads[vslot])
+        fresh = self._stale[vslot]
+        self._bind_slots(self.grads[vslot], fresh)
         qat = self.cfg.model.qat
         if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
             set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
@@ -246,11 +262,16 @@ class TrainEngine:
         ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
         loss = (ce + z) * (1.0 / accum)
         loss.backward()
+        if fresh:
+            self._zero_unwritten_slots()
+            self._stale[vslot] = False
         return ce, z
 
     def zero_grads(self) -> None:
-        for g in self.grads:
-            g.zero_()
+        """Start a step: every hosted virtual rank's gradient buffer is declared stale. Nothing is written here - the
+        first micro-batch of each virtual rank stores its weight gradients (GEMM epilogue without the read), later
+        ones accumulate."""
+        self._stale = [True] * len(self.grads)
 
     def reduce_gradients(self) -> float:
         """Steps 2-3: deterministic reduction into ``grad_red`` and the global gradient norm."""
@@ -258,6 +279,10 @@ class TrainEngine:
         S, R = self.dp_shard, self.dp_replicate
         per = self.V // self.world
         self._wait_pending_hash()
+        for g, stale in zip(self.grads, self._stale):
+            if stale:  # a hosted virtual rank that ran no micro-batch this step contributes zeros, not last step's values
+                g.zero_()
+        self._stale = [False] * len(self.grads)
         if self.is_cuda:
             wgrad_join()  # weight-gradient GEMMs run on a second stream during the backward pass
         if self.nccl_mode and self.world > 1:

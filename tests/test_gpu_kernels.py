@@ -206,7 +206,7 @@ def test_gemm_bf16_matches_tensor_core_model(a_mn, b_mn):
     _eq(*_both(acc, As, Bs), "gemm_bf16 accumulate")
 
 
-@pytest.mark.parametrize("D,window,T", [(128, 0, 300), (64, 96, 384)])
+@pytest.mark.parametrize("D,window,T", [(128, 0, 300), (64, 96, 384), (128, 192, 448), (128, 0, 640)])
 def test_attention_bf16_bitwise_vs_twin(D, window, T):
     g = torch.Generator().manual_seed(12)
     B, H, Hkv = 1, 4, 2
