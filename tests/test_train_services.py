@@ -96,3 +96,37 @@ def test_latest_ignores_incomplete_and_gc(tmp_path):
     assert ck.latest() == ck.step_dir(5) and ck.complete_steps() == [1, 2, 3, 4, 5]
     ck.garbage_collect(keep_last=2, keep_every=0)
     assert ck.complete_steps() == [4, 5] and ck.step_dir(6).exists()
+
+
+def test_stale_gradient_buffers_are_overwritten_not_accumulated_into(tmp_path):
+    """``zero_grads`` writes nothing: the first micro-batch of a virtual rank stores its weight gradients and whatever
+    no kernel wrote is zeroed afterwards; a second micro-batch accumulates. Poisoned buffers must not leak through."""
+    import torch
+
+    from helpers import tiny_cfg
+    from open_transformers_b200.train.engine import TrainEngine
+
+    cfg = tiny_cfg(str(tmp_path))
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+    lab = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+
+    def grads(poison: bool, micro_batches: int):
+        eng = TrainEngine(cfg, "cpu")
+        if poison:
+            for buf in eng.grads:
+                buf.fill_(123.0)
+        eng.zero_grads()
+        for _ in range(micro_batches):
+            for v in range(len(eng.grads)):
+                eng.forward_backward(v, ids, lab, micro_batches)
+        out = [b.clone() for b in eng.grads]
+        eng.close()
+        return out
+
+    clean1, dirty1 = grads(False, 1), grads(True, 1)
+    assert all(torch.equal(a, b) for a, b in zip(clean1, dirty1))
+    clean2, dirty2 = grads(False, 2), grads(True, 2)
+    assert all(torch.equal(a, b) for a, b in zip(clean2, dirty2))
+    # unseen vocabulary rows of the embedding table read zero, seen ones do not
+    assert float(clean1[0].abs().sum()) > 0 and bool((clean1[0] == 0).any())
