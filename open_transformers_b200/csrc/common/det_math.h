@@ -226,6 +226,22 @@ DET_HD float det_exp2_acc(float y) {
 // sigmoid(x) = 1 / (1 + exp(-x))
 DET_HD float det_sigmoidf(float x) { return det_divf(1.0f, det_addf(1.0f, det_expf(-x))); }
 
+// 1 / d for a normal d >= 1: integer-seeded first guess (within 12.5 %) and three Newton steps r <- r (2 - d r), every
+// step one fma and one multiply; relative error about 1e-7. Not correctly rounded, but the same bits everywhere.
+DET_HD float det_recip_ge1(float d) {
+  float r = det_u2f(0x7EF311C7u - det_f2u(d));
+  r = det_mulf(r, det_fmaf(-d, r, 2.0f));
+  r = det_mulf(r, det_fmaf(-d, r, 2.0f));
+  r = det_mulf(r, det_fmaf(-d, r, 2.0f));
+  return r;
+}
+// sigmoid for the SwiGLU kernels: e = 2^clamp(-x log2(e), -126, 126) through det_exp2_acc, then 1 / (1 + e) by
+// det_recip_ge1. Branch-free, so two values go through packed fp32 instructions on the GPU.
+DET_HD float det_sigmoid_fastf(float x) {
+  const float y = fminf(fmaxf(det_mulf(x, -1.44269504088896341f), -126.0f), 126.0f);
+  return det_recip_ge1(det_addf(1.0f, det_exp2_acc(y)));
+}
+
 // ---- double precision sin/cos for the RoPE tables (argument up to ~1e6) ---------------
 // Cody-Waite reduction by pi/2 in three parts followed by Taylor polynomials; the table value
 // is the double result rounded once to binary32.

@@ -164,7 +164,7 @@ void swiglu_fwd(const T* gu, T* h, long rows, int F) {
   for (long row = 0; row < rows; ++row)
     for (int c = 0; c < F; ++c) {
       const float g = ld(gu, row * 2 * F + c), u = ld(gu, row * 2 * F + F + c);
-      st(h, row * F + c, (g * det_sigmoidf(g)) * u);
+      st(h, row * F + c, (g * det_sigmoid_fastf(g)) * u);
     }
 }
 template <typename T>
@@ -173,7 +173,7 @@ void swiglu_bwd(const T* gu, const T* dh, T* dgu, long rows, int F) {
   for (long row = 0; row < rows; ++row)
     for (int c = 0; c < F; ++c) {
       const float g = ld(gu, row * 2 * F + c), u = ld(gu, row * 2 * F + F + c), d = ld(dh, row * F + c);
-      const float sg = det_sigmoidf(g);
+      const float sg = det_sigmoid_fastf(g);
       const float silu = g * sg;
       const float dsilu = sg * det_fmaf(g, 1.0f + (-sg), 1.0f);
       st(dgu, row * 2 * F + c, (d * u) * dsilu);

@@ -284,7 +284,10 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ h, l
   Vec8<T>::load(gu + row * 2 * F + col, g);
   Vec8<T>::load(gu + row * 2 * F + F + col, u);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) o[e] = __fmul_rn(__fmul_rn(g[e], det_sigmoidf(g[e])), u[e]);
+  for (int e = 0; e < 8; e += 2) {
+    const tc05::f2 g2 = tc05::pack2(g[e], g[e + 1]);
+    tc05::unpack2(tc05::mul2(tc05::mul2(g2, tc05::sigmoid_fast2(g2)), tc05::pack2(u[e], u[e + 1])), o[e], o[e + 1]);
+  }
   Vec8<T>::store(h + idx, o);
 }
 // d_gate_up [rows, 2F] from dh [rows, F]
@@ -300,13 +303,16 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gu, const T* __restrict_
   Vec8<T>::load(gu + row * 2 * F + F + col, u);
   Vec8<T>::load(dh + idx, d);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float sg = det_sigmoidf(g[e]);
-    const float silu = __fmul_rn(g[e], sg);
+  for (int e = 0; e < 8; e += 2) {
+    using namespace tc05;
+    const f2 g2 = pack2(g[e], g[e + 1]), u2 = pack2(u[e], u[e + 1]), d2 = pack2(d[e], d[e + 1]);
+    const f2 sg = sigmoid_fast2(g2);
+    const f2 silu = mul2(g2, sg);
     // d silu / dg = sg * (1 + g (1 - sg))
-    const float dsilu = __fmul_rn(sg, __fmaf_rn(g[e], __fadd_rn(1.0f, -sg), 1.0f));
-    og[e] = __fmul_rn(__fmul_rn(d[e], u[e]), dsilu);
-    ou[e] = __fmul_rn(d[e], silu);
+    const f2 one = pack2(1.0f, 1.0f);
+    const f2 dsilu = mul2(sg, fma2(g2, add2(one, mul2(sg, pack2(-1.0f, -1.0f))), one));
+    unpack2(mul2(mul2(d2, u2), dsilu), og[e], og[e + 1]);
+    unpack2(mul2(d2, silu), ou[e], ou[e + 1]);
   }
   Vec8<T>::store(dgu + row * 2 * F + col, og);
   Vec8<T>::store(dgu + row * 2 * F + F + col, ou);

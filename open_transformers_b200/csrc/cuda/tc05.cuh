@@ -285,6 +285,22 @@ __device__ __forceinline__ f2 exp2_acc2(f2 y) {
   return pack2(__uint_as_float(e0), __uint_as_float(e1));
 }
 
+// det_sigmoid_fastf (csrc/common/det_math.h) on two values at once: same operations, same bits
+__device__ __forceinline__ f2 sigmoid_fast2(f2 x) {
+  float y0, y1;
+  unpack2(mul2(x, pack2(-1.44269504088896341f, -1.44269504088896341f)), y0, y1);
+  const f2 e = exp2_acc2(pack2(fminf(fmaxf(y0, -126.0f), 126.0f), fminf(fmaxf(y1, -126.0f), 126.0f)));
+  const f2 d = add2(pack2(1.0f, 1.0f), e);
+  float d0, d1;
+  unpack2(d, d0, d1);
+  f2 r = pack2(__uint_as_float(0x7EF311C7u - __float_as_uint(d0)), __uint_as_float(0x7EF311C7u - __float_as_uint(d1)));
+  const f2 nd = mul2(d, pack2(-1.0f, -1.0f)), two = pack2(2.0f, 2.0f);
+  r = mul2(r, fma2(nd, r, two));
+  r = mul2(r, fma2(nd, r, two));
+  r = mul2(r, fma2(nd, r, two));
+  return r;
+}
+
 // bf16 pack helpers
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
