@@ -13,6 +13,7 @@ import torch
 from torch import nn
 
 from ..config.schema import ModelConfig
+from ..ops import autograd as A
 from .registry import ATTENTION, EMBEDDING, FFN, NORM, ROPE
 from . import modules as _modules  # noqa: F401  (fills the registries)
 
@@ -61,6 +62,13 @@ class Llama3(nn.Module):
     def forward_hidden(self, input_ids: torch.Tensor) -> torch.Tensor:
         B, T = input_ids.shape
         cos, sin = self.rope(T)
+        st = A.tp()
+        if st is not None:
+            # tensor parallel: from here to the logits the residual stream is this rank's token rows [B*T / P, d]
+            if self.activation_checkpoint and self.training:
+                raise NotImplementedError("activation checkpointing is not combined with tensor parallelism")
+            st.batch_shape = (B, T)
+            input_ids = input_ids.reshape(-1)[st.rows(B * T)]
         x = self.embedding.encode(input_ids, self.compute_dtype)
         if self.emb_norm is not None:
             x = self.emb_norm(x)

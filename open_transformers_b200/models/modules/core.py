@@ -29,10 +29,28 @@ class Linear(nn.Module, ParamMixin):
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
 
+    # how a tensor-parallel group splits this layer: None (replicated compute), "col" (output features; ``tp_slices``
+    # lists, per call, the (start, stop) ranges of one rank), "row" (inner dimension), "token" (token rows, full weight)
+    tp_mode: str | None = None
+
+    def tp_slices(self, st) -> list:
+        """Output-feature ranges of every rank for a column-parallel layer (default: one contiguous block each)."""
+        return [[st.split(self.out_features, r)] for r in range(st.size)]
+
     def forward(self, x, residual=None):
         w = self._cw()
         if w is None and x.dtype != self.weight.dtype:
             w = self.weight.to(x.dtype)
+        st = A.tp()
+        if st is not None and self.tp_mode is not None:
+            wc = self.weight if w is None else w
+            if self.tp_mode == "col":
+                assert residual is None
+                return A.tp_column_linear(x, self.weight, wc, self._slot(), self.tp_slices(st))
+            if self.tp_mode == "row":
+                return A.tp_row_linear(x, self.weight, wc, self._slot(), residual, [st.split(self.in_features, r) for r in range(st.size)])
+            assert residual is None
+            return A.tp_token_linear(x, self.weight, wc, self._slot())
         return A.linear(x, self.weight, w, self._slot(), residual)
 
 
@@ -74,6 +92,8 @@ class QuantLinear(Linear):
     def forward(self, x, residual=None):
         if not self.qat_active:
             return super().forward(x, residual)
+        if A.tp() is not None:
+            raise NotImplementedError("quantisation-aware layers are not split over a tensor-parallel group")
         w = self._cw()
         if w is None:
             w = self.weight if x.dtype == self.weight.dtype else self.weight.to(x.dtype)
@@ -214,6 +234,7 @@ class _GQABase(nn.Module, ParamMixin):
         self.wk = build_linear(d_model, n_kv_heads * head_dim, qat, layer_idx)
         self.wv = build_linear(d_model, n_kv_heads * head_dim, qat, layer_idx)
         self.wo = build_linear(n_heads * head_dim, d_model, qat, layer_idx)
+        self.wo.tp_mode = "row"   # heads are split over a tensor-parallel group; wq/wk/wv go through the fused weight
         self.qk_norm = self.qk_norm_default if qk_norm is None else qk_norm
         self.qk_norm_gain = bool(self.qk_norm and qk_norm_gain)
         if self.qk_norm_gain:
@@ -243,7 +264,29 @@ class _GQABase(nn.Module, ParamMixin):
         w = torch.cat([self.wq.weight, self.wk.weight, self.wv.weight], 0)
         return A.linear(x, w, w if w.dtype == x.dtype else w.to(x.dtype))
 
+    def _forward_tp(self, st, x, cos, sin, residual):
+        """Tensor-parallel attention: ``x`` and ``residual`` are this rank's token rows [M/P, d]; the rank attends with
+        H/P query heads and Hkv/P key/value heads over all tokens."""
+        H, Hkv, D, P = self.n_heads, self.n_kv_heads, self.head_dim, st.size
+        if H % P or Hkv % P:
+            raise ValueError("%d query / %d key-value heads do not split over %d tensor-parallel ranks" % (H, Hkv, P))
+        if self.qk_norm_gain:
+            raise NotImplementedError("QK-norm gains are not supported under tensor parallelism")
+        fused = getattr(self, "_fused_qkv", None)
+        if fused is None or (isinstance(self.wq, QuantLinear) and self.wq.qat_active):
+            raise NotImplementedError("tensor-parallel attention needs the fused QKV weight of the training engine")
+        hq, hk = H * D // P, Hkv * D // P
+        slices = [[(r * hq, (r + 1) * hq), (H * D + r * hk, H * D + (r + 1) * hk), ((H + Hkv) * D + r * hk, (H + Hkv) * D + (r + 1) * hk)]
+                  for r in range(P)]
+        qkv = A.tp_column_linear(x, fused[0], fused[1], fused[2], slices)
+        B, T = st.batch_shape
+        o = A.attention(qkv.view(B, T, -1), cos, sin, H // P, Hkv // P, D, self.window, self.qk_norm, self.eps, False)
+        return self.wo(o.reshape(B * T, -1), residual)
+
     def forward(self, x, cos, sin, residual=None):
+        st = A.tp()
+        if st is not None:
+            return self._forward_tp(st, x, cos, sin, residual)
         B, T, _ = x.shape
         H, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self._qkv(x)
@@ -278,8 +321,13 @@ class SwiGLU(nn.Module):
 
     def __init__(self, d_model: int, intermediate: int, qat=None, layer_idx: int = 0):
         super().__init__()
+        self.intermediate = intermediate
         self.w_gate_up = build_linear(d_model, 2 * intermediate, qat, layer_idx)
         self.w_down = build_linear(intermediate, d_model, qat, layer_idx)
+        # tensor parallel: rank r takes gate columns and up columns [r F/P, (r+1) F/P) and the matching inner slice of w_down
+        self.w_gate_up.tp_mode, self.w_down.tp_mode = "col", "row"
+        F = intermediate
+        self.w_gate_up.tp_slices = lambda st: [[st.split(F, r), tuple(F + v for v in st.split(F, r))] for r in range(st.size)]
 
     def forward(self, x, residual=None):
         return self.w_down(A.swiglu(self.w_gate_up(x)), residual)
@@ -306,6 +354,7 @@ class UntiedEmbedding(nn.Module):
         super().__init__()
         self.tok_embeddings = Embedding(vocab_size, d_model)
         self.output = Linear(d_model, vocab_size)
+        self.output.tp_mode = "token"  # the head keeps the whole vocabulary and works on the rank's token rows
 
     def encode(self, ids, dtype=None):
         return self.tok_embeddings(ids, dtype)

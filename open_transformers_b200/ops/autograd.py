@@ -129,6 +129,188 @@ def linear(x, master, w=None, slot=None, residual=None):
     return LinearFn.apply(x, master, master if w is None else w, slot, residual)
 
 
+# ----------------------------------------------------------------------------- tensor parallelism
+# A tensor-parallel group of P processes works on ONE micro-batch together. The residual stream is sharded by token
+# rows (rank t holds rows [t M/P, (t+1) M/P) of the flattened [B*T] tokens), the projections are split the Megatron way
+# (column-parallel: QKV, gate/up; row-parallel: attention output, FFN down), and the vocabulary head stays token-sharded.
+# Every weight is still held in full by every process (the engine replicates the compute weights), so "parallel" here
+# means who multiplies which slice. The rule that keeps the bits of the unsplit model: whenever a reduction index
+# (features of a column-parallel layer in its data gradient, the inner dimension of a row-parallel layer, tokens in a
+# weight gradient) would be split over ranks, the operand is first brought together in the canonical order of the
+# unsplit layout and the owner of the output rows runs ONE GEMM over the whole index, ascending. Gradients of a weight
+# slice are written by the rank that owns the slice; everything else in that rank's gradient buffer stays zero, and the
+# engine assembles a virtual rank's gradient as the element-wise integer sum over the group (at most one non-zero bit
+# pattern per element, so the assembly is exact). The collectives are torch.distributed all-gathers on the group (gloo
+# on CPU ranks, NCCL on GPUs); the fused peer-memory kernels of parallel/tensor_parallel.py implement the same two
+# patterns for the column- and row-parallel forward on GPUs.
+class TpState:
+    def __init__(self, group, rank: int, size: int):
+        self.group, self.rank, self.size = group, rank, size
+        self.batch_shape = None  # (B, T) of the micro-batch being processed
+
+    def rows(self, M: int) -> slice:
+        assert M % self.size == 0, "token count %d does not split over %d tensor-parallel ranks" % (M, self.size)
+        per = M // self.size
+        return slice(self.rank * per, (self.rank + 1) * per)
+
+    def split(self, n: int, rank: int | None = None) -> tuple[int, int]:
+        assert n % self.size == 0, "%d does not split over %d tensor-parallel ranks" % (n, self.size)
+        per = n // self.size
+        r = self.rank if rank is None else rank
+        return r * per, (r + 1) * per
+
+
+_TP: TpState | None = None
+
+
+def set_tp(state: TpState | None) -> None:
+    global _TP
+    _TP = state if (state is not None and state.size > 1) else None
+
+
+def tp() -> TpState | None:
+    return _TP
+
+
+def _all_gather(x: torch.Tensor) -> list[torch.Tensor]:
+    import torch.distributed as dist
+
+    x = x.contiguous()
+    carrier = x.view(torch.uint8) if x.dtype == torch.bfloat16 else x  # byte transport; gloo has no bf16 type
+    parts = [torch.empty_like(carrier) for _ in range(_TP.size)]
+    dist.all_gather(parts, carrier, group=_TP.group)
+    return [p.view(x.dtype) for p in parts] if carrier is not x else parts
+
+
+def tp_gather_rows(x_shard: torch.Tensor) -> torch.Tensor:
+    """[m, ...] per rank -> [m * P, ...], rank order."""
+    return torch.cat(_all_gather(x_shard), 0)
+
+
+def tp_gather_cols(y_t: torch.Tensor, slices_by_rank, n_total: int) -> torch.Tensor:
+    """[M, n_t] per rank -> [M, n_total] with rank r's columns placed at ``slices_by_rank[r]`` (a list of (start, stop)
+    in the unsplit layout, consumed left to right)."""
+    parts = _all_gather(y_t)
+    out = torch.empty((y_t.shape[0], n_total), dtype=y_t.dtype, device=y_t.device)
+    for r, sl in enumerate(slices_by_rank):
+        off = 0
+        for a, b in sl:
+            out[:, a:b] = parts[r][:, off:off + (b - a)]
+            off += b - a
+    return out
+
+
+def _tp_slot(slot) -> "GradSlot":
+    if slot is None or slot.buf is None:
+        raise NotImplementedError("tensor-parallel layers accumulate into gradient slots (training engine only)")
+    if slot.take():
+        slot.buf.zero_()  # the other ranks' slices of this parameter must read zero in this rank's buffer
+    return slot
+
+
+class TpColumnLinearFn(Function):
+    """Column-parallel y_t = gather_rows(x) W_t^T: rank t owns the output features ``slices_by_rank[t]`` of W [N, K]."""
+
+    @staticmethod
+    def forward(ctx, x_shard, master, w, slot, slices_by_rank):
+        st = _TP
+        x_full = tp_gather_rows(_flat2d(x_shard))
+        mine = slices_by_rank[st.rank]
+        w_t = w[mine[0][0]:mine[0][1]] if len(mine) == 1 else torch.cat([w[a:b] for a, b in mine], 0)
+        y = K.gemm(x_full, w_t.contiguous())
+        ctx.save_for_backward(x_full, w)
+        ctx.slot, ctx.slices = slot, slices_by_rank
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_t):
+        x_full, w = ctx.saved_tensors
+        st = _TP
+        dy_t = dy_t.contiguous()
+        slot = _tp_slot(ctx.slot)
+        off = 0
+        for a, b in ctx.slices[st.rank]:  # weight gradient of the owned rows: every token, ascending
+            K.gemm(dy_t[:, off:off + (b - a)], x_full, a_mn=True, b_mn=True, out=slot.buf[a:b], epi=K.EPI_ACC_F32)
+            off += b - a
+        # data gradient: the reduction runs over ALL output features in the unsplit order, for this rank's token rows
+        dy_full = tp_gather_cols(dy_t, ctx.slices, w.shape[0])
+        dx = K.gemm(dy_full[st.rows(dy_full.shape[0])].contiguous(), w, b_mn=True)
+        return dx, None, None, None, None
+
+
+class TpRowLinearFn(Function):
+    """Row-parallel y = a W^T (+ residual) with the inner dimension split: rank t holds columns ``cols_by_rank[t]`` of
+    ``a``; the result comes back sharded by token rows."""
+
+    @staticmethod
+    def forward(ctx, a_t, master, w, slot, residual_shard, cols_by_rank):
+        st = _TP
+        a_t = _flat2d(a_t).contiguous()
+        a_full = tp_gather_cols(a_t, [[c] for c in cols_by_rank], w.shape[1])
+        mine = a_full[st.rows(a_full.shape[0])].contiguous()
+        if residual_shard is not None:
+            y = K.gemm(mine, w, epi=K.EPI_RESIDUAL, residual=_flat2d(residual_shard))
+        else:
+            y = K.gemm(mine, w)
+        ctx.save_for_backward(a_t, w)
+        ctx.slot, ctx.cols, ctx.has_res = slot, cols_by_rank, residual_shard is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        a_t, w = ctx.saved_tensors
+        st = _TP
+        dy_full = tp_gather_rows(dy_shard.contiguous())
+        a, b = ctx.cols[st.rank]
+        da_t = K.gemm(dy_full, w[:, a:b], b_mn=True)
+        slot = _tp_slot(ctx.slot)
+        K.gemm(dy_full, a_t, a_mn=True, b_mn=True, out=slot.buf[:, a:b], epi=K.EPI_ACC_F32)
+        return da_t, None, None, None, (dy_shard if ctx.has_res else None), None
+
+
+class TpTokenLinearFn(Function):
+    """Token-sharded linear layer with the full weight (the vocabulary head): forward and data gradient are local to
+    the rank's token rows; the weight gradient needs every token, so rank t forms the rows ``split(N, t)`` of dW from the
+    gathered dy columns and the gathered input."""
+
+    @staticmethod
+    def forward(ctx, x_shard, master, w, slot):
+        x2 = _flat2d(x_shard).contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.slot = slot
+        return K.gemm(x2, w)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x2, w = ctx.saved_tensors
+        st = _TP
+        dy_shard = dy_shard.contiguous()
+        dx = K.gemm(dy_shard, w, b_mn=True)
+        a, b = st.split(w.shape[0])
+        dy_cols = None
+        for r in range(st.size):  # a transpose of the sharding: rank r collects columns split(N, r) of every rank's rows
+            ra, rb = st.split(w.shape[0], r)
+            got = tp_gather_rows(dy_shard[:, ra:rb].contiguous())
+            if r == st.rank:
+                dy_cols = got
+        x_full = tp_gather_rows(x2)
+        slot = _tp_slot(ctx.slot)
+        K.gemm(dy_cols, x_full, a_mn=True, b_mn=True, out=slot.buf[a:b], epi=K.EPI_ACC_F32)
+        return dx, None, None, None
+
+
+def tp_column_linear(x_shard, master, w, slot, slices_by_rank):
+    return TpColumnLinearFn.apply(x_shard, master, w, slot, slices_by_rank)
+
+
+def tp_row_linear(a_t, master, w, slot, residual_shard, cols_by_rank):
+    return TpRowLinearFn.apply(a_t, master, w, slot, residual_shard, cols_by_rank)
+
+
+def tp_token_linear(x_shard, master, w, slot):
+    return TpTokenLinearFn.apply(x_shard, master, w, slot)
+
+
 class RMSNormFn(Function):
     @staticmethod
     def forward(ctx, x, master, w, slot, eps):
@@ -149,6 +331,18 @@ class RMSNormFn(Function):
         need_dg = ctx.has_w and ((ctx.slot is not None and ctx.slot.buf is not None) or ctx.needs_input_grad[1])
         dx, dg = K.rmsnorm_bwd(dy2, x2, w, rstd, need_dg)
         gm = None
+        if need_dg and _TP is not None:
+            # each rank's dg is the root of the slab pair tree over its own token rows (a sub-tree of the unsplit tree when
+            # the rank holds a power-of-two number of slabs); the roots are combined in rank order by the same tree, and
+            # rank 0 alone adds the result to its gradient buffer
+            n_slabs = (x2.shape[0] + K.NORM_SLAB - 1) // K.NORM_SLAB
+            assert n_slabs & (n_slabs - 1) == 0, "tensor parallelism needs a power-of-two number of 8-row slabs per rank"
+            roots = _all_gather(dg)
+            while len(roots) > 1:
+                roots = [roots[i] + roots[i + 1] if i + 1 < len(roots) else roots[i] for i in range(0, len(roots), 2)]
+            dg = roots[0]
+            if _TP.rank != 0:
+                need_dg = False
         if need_dg:
             if ctx.slot is not None and ctx.slot.buf is not None:
                 if ctx.slot.take():
@@ -230,6 +424,13 @@ class EmbeddingFn(Function):
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
         dy2 = _flat2d(dy).contiguous()
+        if _TP is not None:
+            # rows accumulate in ascending token position over the WHOLE micro-batch: rank 0 gets every row and runs the
+            # one deterministic scatter
+            dy2 = tp_gather_rows(dy2)
+            ids = tp_gather_rows(ids.reshape(-1))
+            if _TP.rank != 0:
+                return None, None, None, None
         if ctx.slot is not None and ctx.slot.buf is not None:
             ctx.slot.zero_if_first()  # rows of tokens that do not occur must read zero
             K.embedding_bwd(dy2, ids, ctx.slot.buf, True)
@@ -257,10 +458,12 @@ class FusedCEZLossFn(Function):
         l2 = _flat2d(logits)
         assert l2.is_contiguous()
         lab = labels.reshape(-1).contiguous()
-        n_valid = lab.numel()  # callers with ignored rows pass n via grad_scale themselves
+        n_valid = lab.numel() * (_TP.size if _TP is not None else 1)  # callers with ignored rows pass n via grad_scale themselves
         inv_n = 1.0 / n_valid
         need_grad = logits.requires_grad
         ce_rows, lse_rows = K.ce_zloss_(l2, lab, z_coeff, inv_n * grad_scale, write_grad=need_grad)
+        if _TP is not None:  # the means run over every row of the micro-batch in the unsplit order
+            ce_rows, lse_rows = tp_gather_rows(ce_rows), tp_gather_rows(lse_rows)
         ce = K.det_sum(ce_rows, False, inv_n)
         z = K.det_sum(lse_rows, True, inv_n) * z_coeff
         # The logits buffer now holds the gradient. It is an activation nobody else saved (the

@@ -40,7 +40,7 @@ from ..config.schema import RootConfig
 from ..models import build_model, fused_ce_z_loss, init_weights
 from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
 from ..ops import functional as K
-from ..ops.autograd import GradSlot, wgrad_join
+from ..ops.autograd import GradSlot, set_tp, wgrad_join
 from ..ops.native import F, I, L, P, check, cpu_lib, cuda_lib, stream_ptr
 from ..parallel.flat import FlatLayout, PeerBuffer
 from . import state_hash as SH
@@ -89,10 +89,28 @@ class TrainEngine:
             self.V = self.dp_shard * self.dp_replicate
         if self.dp_shard * self.dp_replicate != self.V:
             raise ValueError("virtual topology mismatch: V=%d != dp_replicate %d x dp_shard %d" % (self.V, self.dp_replicate, self.dp_shard))
-        if self.V % world:
-            raise ValueError("the %d virtual ranks cannot be split evenly over %d processes" % (self.V, world))
-        per = self.V // world
-        self.hosted = list(range(rank * per, (rank + 1) * per))
+        # tensor parallelism: ``tp`` consecutive processes form a group that works on each micro-batch together; the
+        # ``dp_groups`` groups share the virtual ranks between them
+        self.tp = max(1, int(run.tp_size))
+        if world % self.tp:
+            raise ValueError("world size %d is not a multiple of run.tp_size %d" % (world, self.tp))
+        self.dp_groups, self.dp_rank, self.tp_rank = world // self.tp, rank // self.tp, rank % self.tp
+        if self.V % self.dp_groups:
+            raise ValueError("the %d virtual ranks cannot be split evenly over %d data-parallel groups" % (self.V, self.dp_groups))
+        per = self.V // self.dp_groups
+        self.hosted = list(range(self.dp_rank * per, (self.dp_rank + 1) * per))
+        self._tp_state = None
+        if self.tp > 1:
+            from ..ops.autograd import TpState
+
+            tp_group = group
+            if self.dp_groups > 1:  # every process creates every group, in the same order
+                tp_group = None
+                for d in range(self.dp_groups):
+                    g_ = dist.new_group([d * self.tp + t for t in range(self.tp)])
+                    if d == self.dp_rank:
+                        tp_group = g_
+            self._tp_state = TpState(tp_group, self.tp_rank, self.tp)
         self.mixed = bool(run.mixed_precision)
         self.compute_dtype = torch.bfloat16 if self.mixed else torch.float32
         self.is_cuda = self.device.type == "cuda"
@@ -110,7 +128,11 @@ class TrainEngine:
         self.layout = FlatLayout.build([(n, tuple(p.shape)) for n, p in named], self.dp_shard, member)
         lay = self.layout
         n = lay.total
-        peer = self.is_cuda and world > 1 and not self.nccl_mode
+        if self.tp > 1 and self.is_cuda and self.dp_groups > 1:
+            raise NotImplementedError("tensor parallelism on GPUs is limited to one data-parallel group in this version")
+        # with a tensor-parallel group every process ends up with the whole gradient of its virtual ranks, so each
+        # reduces and updates everything itself (no peer-sharded ownership)
+        peer = self.is_cuda and world > 1 and not self.nccl_mode and self.tp == 1
         pw, pg = (rank, world) if peer else (0, 1)
 
         def alloc(nbytes, shared):
@@ -253,6 +275,9 @@ class TrainEngine:
         """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
         fresh = self._stale[vslot]
         self._bind_slots(self.grads[vslot], fresh)
+        set_tp(self._tp_state)
+        if self._tp_state is not None:  # this rank's token rows of the labels
+            labels = labels.reshape(-1)[self._tp_state.rows(labels.numel())]
         qat = self.cfg.model.qat
         if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
             set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
@@ -277,7 +302,7 @@ class TrainEngine:
         """Steps 2-3: deterministic reduction into ``grad_red`` and the global gradient norm."""
         lay = self.layout
         S, R = self.dp_shard, self.dp_replicate
-        per = self.V // self.world
+        per = self.V // self.dp_groups
         self._wait_pending_hash()
         for g, stale in zip(self.grads, self._stale):
             if stale:  # a hosted virtual rank that ran no micro-batch this step contributes zeros, not last step's values
@@ -285,6 +310,11 @@ class TrainEngine:
         self._stale = [False] * len(self.grads)
         if self.is_cuda:
             wgrad_join()  # weight-gradient GEMMs run on a second stream during the backward pass
+        if self.tp > 1:
+            # assemble each virtual rank's gradient from the slices its tensor-parallel ranks wrote: at most one rank holds
+            # a non-zero bit pattern per element, so the integer sum of the bit patterns is that pattern, exactly
+            for g in self.grads:
+                dist.all_reduce(g.view(torch.int32), op=dist.ReduceOp.SUM, group=self._tp_state.group)
         if self.nccl_mode and self.world > 1:
             # throughput-only baseline: library all-reduce, order not pinned
             acc = self.grads[0]
@@ -293,14 +323,14 @@ class TrainEngine:
             dist.all_reduce(acc, group=self.group)
             self.grad_red.copy_(acc).mul_(1.0 / self.V)
             check(self._chunk_sos_all(), "chunk_sos")
-        elif not self.is_cuda and self.world > 1:
+        elif not self.is_cuda and self.dp_groups > 1:
             # CPU ranks: exchange the flat buffers, then every rank reduces everything identically
             gathered = []
             for g in self.grads:
                 parts = [torch.empty_like(g) for _ in range(self.world)]
                 dist.all_gather(parts, g, group=self.group)
                 gathered.append(parts)
-            srcs = [gathered[v % per][v // per].data_ptr() for v in range(self.V)]
+            srcs = [gathered[v % per][(v // per) * self.tp].data_ptr() for v in range(self.V)]  # any rank of the owning group
             self._keep = gathered
             check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks),
                                                P(self.grad_red), P(self.chunk_sos)), "grad_reduce")

@@ -1,0 +1,49 @@
+"""Tensor parallelism on CPU ranks: a tensor-parallel group of 2 gloo processes (and 2 groups of 2) must write the very
+hashes, losses and gradient norms of the single-process run - fp32 (exact family) and bf16 (tensor-core model twin)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from helpers import free_port
+
+WORKER = str(Path(__file__).resolve().parent / "tp_cpu_worker.py")
+
+
+def _run(world, tp, bf16, out):
+    port = free_port()
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   OMP_NUM_THREADS="2", OTB_TEST_TP=str(tp), OTB_TEST_BF16="1" if bf16 else "0", OTB_TEST_OUT=str(out))
+        procs.append(subprocess.Popen([sys.executable, WORKER], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(o.decode())
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-6000:]
+    return json.load(open(out))
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("bf16", [False, True])
+def test_tensor_parallel_group_reproduces_the_single_process_bytes(tmp_path, bf16):
+    base = _run(1, 1, bf16, tmp_path / "base.json")
+    tp2 = _run(2, 2, bf16, tmp_path / "tp2.json")
+    assert tp2 == base, (tp2, base)
+
+
+@pytest.mark.distributed
+def test_two_tensor_parallel_groups_share_the_virtual_ranks(tmp_path):
+    base = _run(1, 1, False, tmp_path / "base.json")
+    got = _run(4, 2, False, tmp_path / "tp2dp2.json")          # TP = 2 x DP = 2: each group hosts one virtual rank
+    assert [h for _, _, h in got] == [h for _, _, h in base]
+    assert [n for n, _, _ in got] == [n for n, _, _ in base]
