@@ -88,6 +88,7 @@ def main() -> int:
     ap.add_argument("--config", default="open1b_b200")
     ap.add_argument("--override", action="append", default=[], help="config override (debugging; makes the number invalid)")
     ap.add_argument("--no-hash", action="store_true", help="debugging: skip the per-step state hash (makes the number invalid)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (run.tp_size); the GPUs form one group")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -113,7 +114,7 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
     native.cuda_lib()
 
-    cfg = load_config(args.config, args.override)
+    cfg = load_config(args.config, args.override + (["run.tp_size=%d" % args.tp] if args.tp > 1 else []))
     V = cfg.run.virtual_dp_size
     eng = TrainEngine(cfg, device, rank, world, None)
     mb, T = cfg.train.micro_batch_size, cfg.train.seq_len
@@ -212,7 +213,7 @@ def main() -> int:
             "vs_baseline": (tps / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": cfg.model.name, "params": eng.layout.total, "global_batch": V * accum * mb, "seq_len": T,
-                       "global_batch_tokens": tokens_per_step, "parallelism": "virtual dp8 (shard 8) on %d GPU(s)" % world,
+                       "global_batch_tokens": tokens_per_step, "parallelism": "virtual dp8 (shard 8) on %d GPU(s)%s" % (world, ", tensor-parallel groups of %d" % args.tp if args.tp > 1 else ""),
                        "l2": "inputs larger than L2 (3.2 GB of bf16 weights + 6.4 GB fp32 gradients per micro-batch)",
                        "state_hash": "none" if args.no_hash else "every step, tree digests on device",
                        "overrides": args.override},
