@@ -74,7 +74,7 @@ class ClockSampler:
 
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
-                      "pip install of /root/reference fails offline (build backend hatchling absent) and its model modules import "
+                      "pip install of the reference source tree fails offline (build backend hatchling absent) and its model modules import "
                       "the closed-source `repop` kernel library plus hydra-core/omegaconf, none of which exist on this image"}))
     return 0
 
