@@ -133,6 +133,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     elif cfg.run.virtual_dp_size == 0:
         raise AuditError("--from-init with --config-name needs run.virtual_dp_size (the topology to emulate)")
 
+    cfg.run.tp_size = 1  # a tensor-parallel run is replayed unsplit: the split never changes a bit
     engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None)
     V = engine.V
     run_path = Path(run_dir) if run_dir else None

@@ -15,7 +15,7 @@ def load_model_from_checkpoint(checkpoint: str, device: str = "cpu"):
 
     meta = Checkpointer.read_meta(checkpoint)
     cfg = parse_config_resolved(meta.config_resolved)
-    cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = 1, 1, 1
+    cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size, cfg.run.tp_size = 1, 1, 1, 1
     eng = TrainEngine(cfg, device, 0, 1, init=False)
     Checkpointer(Path(checkpoint).parent.parent).load(checkpoint, eng, load_optimizer=False)
     eng._bind_slots(None)

@@ -70,6 +70,7 @@ def verify_handoff(checkpoint: str, expect_hash: str | None = None, prev_hash: s
     meta = Checkpointer.read_meta(checkpoint)
     cfg = load_config(config_name) if config_name else parse_config_resolved(meta.config_resolved)
     cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
+    cfg.run.tp_size = 1  # the hash does not depend on how a tensor-parallel group split the work
     engine = TrainEngine(cfg, device, 0, 1, init=False)
     Checkpointer(Path(checkpoint).parent.parent).load(checkpoint, engine)
     grads = read_gradient_sidecar(checkpoint)
