@@ -196,8 +196,9 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             finish_pending_hash()  # the previous step's digests ran under this step's forward/backward
             grad_norm = engine.reduce_gradients()
             local_ce = [float(c) for c in ces]
-            ce_sum, n_mb = deterministic_scalar_sum(local_ce, world)
-            z_sum, _ = deterministic_scalar_sum([float(z) for z in zs], world)
+            lead = engine.tp_rank == 0  # the ranks of a tensor-parallel group hold the same values: one of them reports
+            ce_sum, n_mb = deterministic_scalar_sum(local_ce if lead else [], world)
+            z_sum, _ = deterministic_scalar_sum([float(z) for z in zs] if lead else [], world)
             loss_mean = ce_sum / max(n_mb, 1)
             zero_q_gain_grads(engine.named_grads(), step, train_cfg.qk_freeze_q_gains_until_step)
             skipped = spike.should_skip(grad_norm, loss_mean, step)

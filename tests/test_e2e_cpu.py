@@ -114,19 +114,17 @@ WORKER = textwrap.dedent("""
     from helpers import tiny_cfg
     from open_transformers_b200.train.loop import train
     from open_transformers_b200.parallel.env import shutdown_distributed
-    cfg = tiny_cfg({tmp!r}, ["run.run_id=dist", "train.ckpt_every_steps=2"])
+    cfg = tiny_cfg({tmp!r}, ["run.run_id={run_id}", "train.ckpt_every_steps=2", "run.tp_size={tp}"])
     res = train(cfg, device="cpu", data_root={tmp!r})
     if int(os.environ["RANK"]) == 0:
-        json.dump(res["hashes"], open({tmp!r} + "/dist_hashes.json", "w"))
+        json.dump(res["hashes"], open({tmp!r} + "/{run_id}_hashes.json", "w"))
     shutdown_distributed()
 """)
 
 
-@pytest.mark.distributed
-def test_two_gloo_ranks_produce_the_single_process_hashes(trained):
-    tmp, cfg, res = trained
-    script = Path(tmp) / "worker.py"
-    script.write_text(WORKER.format(root=str(ROOT), tmp=tmp))
+def _two_ranks(tmp, run_id, tp):
+    script = Path(tmp) / ("worker_%s.py" % run_id)
+    script.write_text(WORKER.format(root=str(ROOT), tmp=tmp, run_id=run_id, tp=tp))
     port = free_port()
     procs = []
     for rank in range(2):
@@ -142,9 +140,24 @@ def test_two_gloo_ranks_produce_the_single_process_hashes(trained):
                 q.kill()
             raise
         outs.append(out.decode())
-    assert all(p.returncode == 0 for p in procs), "\\n".join(outs)
-    got = [tuple(x) for x in json.load(open(tmp + "/dist_hashes.json"))]
-    assert got == [tuple(x) for x in res["hashes"]]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    return [tuple(x) for x in json.load(open(tmp + "/%s_hashes.json" % run_id))]
+
+
+@pytest.mark.distributed
+def test_two_gloo_ranks_produce_the_single_process_hashes(trained):
+    tmp, cfg, res = trained
+    assert _two_ranks(tmp, "dist", 1) == [tuple(x) for x in res["hashes"]]
     # and the two-rank run's checkpoint replays on one process
     r = audit_replay(tmp + "/runs/dist/checkpoints/step_000000002", data_root=tmp, until_step=3)
+    assert r["match"] is True
+
+
+@pytest.mark.distributed
+def test_a_tensor_parallel_pair_trains_to_the_single_process_hashes(trained):
+    """The real ``train()`` with run.tp_size = 2 on two gloo ranks: same hash log as the unsplit run, and its checkpoint
+    (written by a tensor-parallel run) replays unsplit on one process."""
+    tmp, cfg, res = trained
+    assert _two_ranks(tmp, "tp2", 2) == [tuple(x) for x in res["hashes"]]
+    r = audit_replay(tmp + "/runs/tp2/checkpoints/step_000000002", data_root=tmp, until_step=3)
     assert r["match"] is True
