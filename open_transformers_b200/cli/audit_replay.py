@@ -187,7 +187,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             if sh_cfg.include_batch:
                 hashers[v].update(batch)
             ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum)
-            ces.append((v, k, float(ce)))
+            ces.append((v, k, float(ce.detach())))
         grad_norm = engine.reduce_gradients()
         total = 0.0
         for _, _, c in ces:

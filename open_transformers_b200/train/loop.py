@@ -156,6 +156,13 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
 
     result = {"run_dir": str(run_dir), "hashes": [], "losses": []}
     zero_norm_streak: dict[str, int] = {}
+    heartbeat = None
+    if world > 1 and cfg.run.heartbeat_timeout_s > 0:
+        from ..parallel.heartbeat import Heartbeat
+
+        heartbeat = Heartbeat(rank, world, os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                              int(os.environ.get("OTB_HEARTBEAT_PORT") or int(os.environ.get("MASTER_PORT", "29500")) + 1),
+                              timeout_s=cfg.run.heartbeat_timeout_s)
     pending_hash: list = []  # at most one (step, consumed, handle, batch digest, advances the chain) whose digests are in flight
 
     def finish_pending_hash():
@@ -176,6 +183,8 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
         it = iter(loader)
         while consumed < train_cfg.total_tokens and (max_steps is None or step < max_steps):
             t_step = time.perf_counter()
+            if heartbeat is not None:
+                heartbeat.check()  # a peer that left or died is noticed here, before this step's collectives
             plan, batches = next(it)
             M = plan.microbatches
             if M % V:
@@ -260,7 +269,13 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
         log.error("halted by the spike protocol: %s", h)
         result["halted"] = str(h)
         finish_pending_hash()
+    except BaseException as e:
+        if heartbeat is not None and not isinstance(e, SystemExit):
+            heartbeat.report_failure("%s: %s" % (type(e).__name__, e))  # the others leave at their next check
+        raise
     finally:
+        if heartbeat is not None:
+            heartbeat.close()
         metrics.close()
         engine.close()
     result.update({"step": step, "consumed_tokens": consumed, "chained_hash": chained})
