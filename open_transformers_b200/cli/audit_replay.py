@@ -84,7 +84,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                  data_root: str | None = None, device: str = "cpu", cpu_threads: str | None = None, from_init: bool = False,
                  descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
                  save_checkpoint_dir: str | None = None, loss_log: str | None = None, run_dir: str | None = None,
-                 offload_optimizer: bool = False, offload_master: bool = False, offload_grads: bool = False, **_ignored) -> dict:
+                 offload_optimizer: bool = False, offload_master: bool = False, offload_grads: bool = False,
+                 fold_spill_dir: str | None = None, no_fold_spill: bool = False, **_ignored) -> dict:
     import numpy as np
     import torch
 
@@ -134,7 +135,11 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         raise AuditError("--from-init with --config-name needs run.virtual_dp_size (the topology to emulate)")
 
     cfg.run.tp_size = 1  # a tensor-parallel run is replayed unsplit: the split never changes a bit
-    engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None)
+    # --offload-grads: one work buffer plus one partial per replica instead of one gradient buffer per virtual rank
+    # (each finished virtual rank is folded into its replica's partial, ascending shard order); --fold-spill-dir puts
+    # the finished partials on disk with a digest that is checked when they are read back
+    spill = None if (no_fold_spill or not offload_grads) else fold_spill_dir
+    engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None, fold_gradients=offload_grads, fold_spill_dir=spill)
     V = engine.V
     run_path = Path(run_dir) if run_dir else None
     result: dict = {"device": device, "kernels": native.loaded_libraries(), "rank0_losses": [], "expected": expected, "match": None}
@@ -188,6 +193,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                 hashers[v].update(batch)
             ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum)
             ces.append((v, k, float(ce.detach())))
+            if engine.fold and k == accum - 1:
+                engine.fold_virtual_rank(v)  # batches arrive virtual rank by virtual rank, micro-batches ascending
         grad_norm = engine.reduce_gradients()
         total = 0.0
         for _, _, c in ces:
@@ -283,7 +290,7 @@ def main(argv: list[str] | None = None) -> int:
                            cpu_threads=a.cpu_threads, from_init=a.from_init, descriptor_checkpoint=a.descriptor_checkpoint,
                            until_step=a.until_step, expect_hash=a.expect_hash, save_checkpoint_dir=a.save_checkpoint_dir,
                            loss_log=a.loss_log, run_dir=a.run_dir, offload_optimizer=a.offload_optimizer, offload_master=a.offload_master,
-                           offload_grads=a.offload_grads)
+                           offload_grads=a.offload_grads, fold_spill_dir=a.fold_spill_dir, no_fold_spill=a.no_fold_spill)
     except AuditError as e:
         print("AUDIT ERROR: %s" % e, file=sys.stderr)
         return 2

@@ -55,6 +55,10 @@ class StepOutput:
     skipped: bool
 
 
+class SpillCorruption(RuntimeError):
+    """A gradient partial read back from disk does not match the digest written with it."""
+
+
 def build_param_groups(named_params, no_decay_names, lr, betas, eps, weight_decay):
     """[decay, no_decay] groups: a parameter is not decayed if it has fewer than 2 dims or its name contains
     one of ``no_decay_names`` (reference src/pretrain/optim/adamw.py:21-63). Returns (groups, membership)."""
@@ -75,7 +79,7 @@ def _ptr_array(ptrs):
 
 class TrainEngine:
     def __init__(self, cfg: RootConfig, device: torch.device | str = "cpu", rank: int = 0, world: int = 1, group=None,
-                 seed: int | None = None, init: bool = True):
+                 seed: int | None = None, init: bool = True, fold_gradients: bool = False, fold_spill_dir: str | None = None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.rank, self.world, self.group = rank, world, group
@@ -148,7 +152,16 @@ class TrainEngine:
         self.m1 = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.m2 = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.grad_red = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.buf_grads = [alloc(4 * n, shared=True) for _ in self.hosted]
+        # Folded gradients (single-process replay with little memory): instead of one gradient buffer per hosted virtual
+        # rank there is ONE work buffer plus one partial per replica; ``fold_virtual_rank`` adds a finished virtual rank
+        # into its replica's partial in ascending shard order - the same left fold, element by element, that the reduction
+        # kernel runs over separate buffers - and a finished partial may be spilled to disk with a digest beside it.
+        self.fold = bool(fold_gradients)
+        if self.fold and (world != 1 or self.tp != 1):
+            raise ValueError("folded gradients are for the single-process replay")
+        self._fold_spill = fold_spill_dir
+        self._partials: dict[int, object] = {}   # replica -> fp32 tensor, or the path it was spilled to
+        self.buf_grads = [alloc(4 * n, shared=True) for _ in (self.hosted[:1] if self.fold else self.hosted)]
         self.grads = [b.typed(torch.float32) for b in self.buf_grads]
         for g in self.grads:
             g.zero_()
@@ -273,6 +286,8 @@ class TrainEngine:
     # ---------------------------------------------------------------------------- one step
     def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int):
         """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
+        if self.fold:
+            vslot = 0  # every virtual rank is processed in the one work buffer, then folded away
         fresh = self._stale[vslot]
         self._bind_slots(self.grads[vslot], fresh)
         set_tp(self._tp_state)
@@ -291,6 +306,53 @@ class TrainEngine:
             self._zero_unwritten_slots()
             self._stale[vslot] = False
         return ce, z
+
+    def fold_virtual_rank(self, v: int) -> None:
+        """Folded-gradient mode: virtual rank ``v`` has run all its micro-batches of this step; add its gradient (the
+        work buffer) into its replica's partial. Must be called for v = 0, 1, 2, ... in order."""
+        assert self.fold
+        S = self.dp_shard
+        r, sh = v // S, v % S
+        work = self.grads[0]
+        if self._stale[0]:
+            work.zero_()  # a virtual rank without micro-batches contributes zeros
+        if sh == 0:
+            part = work.clone()
+        else:
+            part = self._partials[r]
+            part.add_(work)
+        if sh == S - 1:
+            part.mul_(torch.tensor(1.0, dtype=torch.float32, device=part.device) / torch.tensor(float(S), dtype=torch.float32, device=part.device))
+            if self._fold_spill:
+                part = self._spill(r, part)
+        self._partials[r] = part
+        self._stale[0] = True
+
+    def _spill(self, r: int, part: torch.Tensor) -> str:
+        """Write a finished replica partial to disk with its blake2b digest beside it; returns the path."""
+        import hashlib
+        from pathlib import Path
+
+        d = Path(self._fold_spill)
+        d.mkdir(parents=True, exist_ok=True)
+        path = d / ("replica_%03d.f32" % r)
+        raw = part.detach().to("cpu").numpy()
+        raw.tofile(path)
+        h = hashlib.blake2b(digest_size=32)
+        h.update(raw.tobytes())
+        Path(str(path) + ".blake2b").write_text(h.hexdigest())
+        return str(path)
+
+    def _unspill(self, path: str) -> torch.Tensor:
+        import hashlib
+        from pathlib import Path
+
+        raw = np.fromfile(path, dtype=np.float32)
+        h = hashlib.blake2b(digest_size=32)
+        h.update(raw.tobytes())
+        if h.hexdigest() != Path(path + ".blake2b").read_text().strip():
+            raise SpillCorruption("%s does not match the digest written beside it" % path)
+        return torch.from_numpy(raw).to(self.device)
 
     def zero_grads(self) -> None:
         """Start a step: every hosted virtual rank's gradient buffer is declared stale. Nothing is written here - the
@@ -338,7 +400,14 @@ class TrainEngine:
         else:
             self._barrier()  # every rank's backward is complete before anyone pulls
             srcs = []
-            for v in range(self.V):
+            if self.fold:
+                # the shard fold and the 1/S scaling are done; what is left is the pair tree over the R replica partials
+                parts = [self._partials[r] for r in range(R)]
+                parts = [self._unspill(p) if isinstance(p, str) else p for p in parts]
+                self._keep = parts
+                srcs, S = [p.data_ptr() for p in parts], 1
+                self._partials = {}
+            for v in range(self.V if not self.fold else 0):
                 r, slot = v // per, v % per
                 srcs.append(self.buf_grads[slot].ptrs[r] if self.peer else self.grads[slot].data_ptr())
             lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
@@ -349,6 +418,8 @@ class TrainEngine:
                       "grad_reduce")
             else:
                 check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos)), "grad_reduce")
+            if self.fold:
+                self._keep = None
             if self.peer:
                 parts = [torch.empty_like(self.chunk_sos) for _ in range(self.world)]
                 dist.all_gather(parts, self.chunk_sos, group=self.group)

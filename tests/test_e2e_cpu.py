@@ -161,3 +161,30 @@ def test_a_tensor_parallel_pair_trains_to_the_single_process_hashes(trained):
     assert _two_ranks(tmp, "tp2", 2) == [tuple(x) for x in res["hashes"]]
     r = audit_replay(tmp + "/runs/tp2/checkpoints/step_000000002", data_root=tmp, until_step=3)
     assert r["match"] is True
+
+
+def test_replay_with_folded_gradients_and_verified_spill(trained, tmp_path):
+    """--offload-grads (one work buffer + one partial per replica) and --fold-spill-dir give the very digests of the plain
+    replay; a spilled partial that was tampered with is refused."""
+    from open_transformers_b200.train.engine import SpillCorruption, TrainEngine
+
+    tmp, cfg, res = trained
+    ck = tmp + "/runs/t/checkpoints/step_000000002"
+    plain = audit_replay(ck, data_root=tmp, until_step=3)
+    folded = audit_replay(ck, data_root=tmp, until_step=3, offload_grads=True)
+    spilled = audit_replay(ck, data_root=tmp, until_step=3, offload_grads=True, fold_spill_dir=str(tmp_path / "spill"))
+    assert plain["match"] and folded["match"] and spilled["match"]
+    assert plain["state_hash"] == folded["state_hash"] == spilled["state_hash"]
+    assert (tmp_path / "spill" / "replica_000.f32.blake2b").exists()
+    # corruption of a spilled partial
+    eng = TrainEngine(cfg, "cpu", fold_gradients=True, fold_spill_dir=str(tmp_path / "spill2"))
+    eng.zero_grads()
+    for v in range(eng.V):
+        eng.fold_virtual_rank(v)
+    path = tmp_path / "spill2" / "replica_000.f32"
+    raw = bytearray(path.read_bytes())
+    raw[5] ^= 1
+    path.write_bytes(bytes(raw))
+    with pytest.raises(SpillCorruption):
+        eng.reduce_gradients()
+    eng.close()
