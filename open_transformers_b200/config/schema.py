@@ -51,6 +51,7 @@ class QATConfig(_Strict):
     exempt_first_n_blocks: int = 0
     scale_refresh_every_n_steps: int = 0
     enable_at_step: int = 0
+    ste_bwd_hadamard: bool = False  # run both straight-through backward GEMMs as Hadamard-rotated int8 products
 
     @model_validator(mode="after")
     def _check(self):

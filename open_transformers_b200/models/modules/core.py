@@ -68,8 +68,9 @@ class QuantLinear(Linear):
 
     qat_active: bool = True
 
-    def __init__(self, in_features, out_features, *, method="lsq", weight_bits=8, act_bits=8, per_channel_w=True):
+    def __init__(self, in_features, out_features, *, method="lsq", weight_bits=8, act_bits=8, per_channel_w=True, ste_bwd_hadamard=False):
         super().__init__(in_features, out_features)
+        self.ste_bwd_hadamard = bool(ste_bwd_hadamard)  # both backward GEMMs as Hadamard-rotated int8 products
         self.method, self.weight_bits, self.act_bits, self.per_channel_w = method, weight_bits, act_bits, per_channel_w
         self.qmax_w, self.qmax_a = K.qmax_for_bits(weight_bits), K.qmax_for_bits(act_bits)
         if method == "lsq":
@@ -100,7 +101,7 @@ class QuantLinear(Linear):
         w = w.detach()
         lsq = self.method == "lsq"
         return A.quant_linear(x, self.weight, w, self._slot(), self.weight_scale if lsq else None, self._step(w),
-                              self._slot("weight_scale") if lsq else None, residual, self.qmax_w, self.qmax_a, lsq, self._qcache)
+                              self._slot("weight_scale") if lsq else None, residual, self.qmax_w, self.qmax_a, lsq, self._qcache, self.ste_bwd_hadamard)
 
 
 def build_linear(in_features: int, out_features: int, qat=None, layer_idx: int = 0) -> Linear:
@@ -109,7 +110,7 @@ def build_linear(in_features: int, out_features: int, qat=None, layer_idx: int =
     if qat is None or not qat.enabled or layer_idx < qat.exempt_first_n_blocks:
         return Linear(in_features, out_features)
     return QuantLinear(in_features, out_features, method=qat.method, weight_bits=qat.weight_bits, act_bits=qat.act_bits,
-                       per_channel_w=qat.per_channel_w)
+                       per_channel_w=qat.per_channel_w, ste_bwd_hadamard=qat.ste_bwd_hadamard)
 
 
 def set_qat_active(module: nn.Module, active: bool) -> int:

@@ -493,7 +493,7 @@ class QuantLinearFn(Function):
     src/pretrain/model/modules/_linear.py:31-65)"""
 
     @staticmethod
-    def forward(ctx, x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache):
+    def forward(ctx, x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache, hadamard=False):
         x2 = _flat2d(x)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
@@ -511,6 +511,7 @@ class QuantLinearFn(Function):
         ctx.has_res = residual is not None
         ctx.in_shape = x.shape
         ctx.cfg = (qmax_w, learn_step, master_w.dtype, None if master_s is None else master_s.dtype)
+        ctx.hadamard = bool(hadamard)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -520,9 +521,17 @@ class QuantLinearFn(Function):
         dy2 = _flat2d(dy)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx = K.gemm(dy2, w_hat, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
-        # dL/dw_hat = dy^T x_hat with x_hat = xq * sa: the integers are exact in bf16, the step is applied afterwards
-        G = K.gemm(dy2, K.i8_widen(xq, dy2.dtype), a_mn=True, b_mn=True, epi=K.EPI_STORE_F32)
+        B = K.HADAMARD_BLOCK
+        if ctx.hadamard and dy2.shape[0] % B == 0 and dy2.shape[1] % B == 0:
+            # both straight-through GEMMs on the int8 tensor cores, operands Hadamard-rotated along the contraction index
+            dx = None
+            if ctx.needs_input_grad[0]:
+                dx = K.ste_matmul_hadamard(dy2, w_hat.t().contiguous()).to(dy2.dtype).view(ctx.in_shape)
+            G = K.ste_matmul_hadamard(dy2.t().contiguous(), K.i8_widen(xq, torch.float32).t().contiguous())
+        else:
+            dx = K.gemm(dy2, w_hat, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+            # dL/dw_hat = dy^T x_hat with x_hat = xq * sa: the integers are exact in bf16, the step is applied afterwards
+            G = K.gemm(dy2, K.i8_widen(xq, dy2.dtype), a_mn=True, b_mn=True, epi=K.EPI_STORE_F32)
         N, Kd = w.shape
         gs = 1.0 / math.sqrt(float(Kd) * float(qmax_w))
         use_slot = ctx.slot_w is not None and ctx.slot_w.buf is not None
@@ -541,9 +550,9 @@ class QuantLinearFn(Function):
         gsm = None
         if learn_step and not (ctx.slot_s is not None and ctx.slot_s.buf is not None):
             gsm = ds.to(s_dtype)
-        return dx, gw, None, None, gsm, None, None, (dy if ctx.has_res else None), None, None, None, None
+        return dx, gw, None, None, gsm, None, None, (dy if ctx.has_res else None), None, None, None, None, None
 
 
-def quant_linear(x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache=None):
+def quant_linear(x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache=None, hadamard=False):
     return QuantLinearFn.apply(x, master_w, master_w if w is None else w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a,
-                               learn_step, cache)
+                               learn_step, cache, hadamard)

@@ -393,3 +393,45 @@ def i8_widen(q: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     else:
         check(cpu_lib().otb_cpu_i8_widen(P(q), P(out), L(q.numel()), I(is_bf16(out))), "i8_widen")
     return out
+
+
+HADAMARD_BLOCK = 128
+
+
+def fwht_blocks(x: torch.Tensor, block: int = HADAMARD_BLOCK) -> torch.Tensor:
+    """Unnormalised Walsh-Hadamard transform of every aligned ``block`` of the last dimension of an fp32 matrix
+    (H_block x_block, entries +-1). log2(block) butterfly stages of one correctly rounded add and one subtract per pair,
+    in a fixed order, so the result is the same on every device; H H^T = block * I."""
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] % block == 0 and block & (block - 1) == 0
+    R, C = x.shape
+    y = x
+    h = 1
+    while h < block:
+        y = y.reshape(R, C // (2 * h), 2, h)
+        a, b = y[:, :, 0, :], y[:, :, 1, :]
+        y = torch.stack((a + b, a - b), dim=2)
+        h *= 2
+    return y.reshape(R, C)
+
+
+def quant_rows(x: torch.Tensor, qmax: int):
+    """Per-row symmetric int8 quantisation of an fp32 / bf16 matrix: step_r = max(max_k |x_rk| / qmax, tiny); returns
+    (q int8, step fp32 [rows])."""
+    x = x.contiguous()
+    step = row_stat(x, "absmax", 1.0 / qmax, 1e-30)
+    q, _ = quant_weight(x, step, qmax)
+    return q, step
+
+
+def ste_matmul_hadamard(a: torch.Tensor, b: torch.Tensor, qmax: int = 127) -> torch.Tensor:
+    """``a b^T`` ([R1, C] x [R2, C] -> fp32 [R1, R2]) on the int8 tensor cores: both operands are rotated by the block
+    Hadamard transform along the contraction index (which cancels in the product and spreads outliers over the block),
+    quantised per row to int8, multiplied exactly in int32 and dequantised in fp32:
+    ``(float(acc) * sb[n]) * sa[m] * (1 / block)``. The contraction length must be a multiple of the block.
+    (reference role: repop `_ste_matmul_hadamard` / bfr_hadamard_int8_gemm, docs/MODEL_OP_DTYPE_TRACE.md:104,113-116)"""
+    ha, hb = fwht_blocks(a.float().contiguous()), fwht_blocks(b.float().contiguous())
+    aq, sa = quant_rows(ha, qmax)
+    bq, sb = quant_rows(hb, qmax)
+    one = torch.ones(1, dtype=torch.float32, device=a.device)
+    acc = gemm_i8(aq, bq, one, sb, torch.float32)
+    return (acc * sa[:, None]) * (1.0 / HADAMARD_BLOCK)

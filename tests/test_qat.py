@@ -111,6 +111,85 @@ def test_qat_run_trains_and_replays(tmp_path):
     assert plain["hashes"][-1][1] != res["hashes"][-1][1]
 
 
+def test_block_hadamard_is_the_sign_matrix_and_cancels_in_a_product():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 256, generator=g)
+    n = torch.arange(128)
+    H = torch.tensor([[(-1.0) ** bin(int(i & j)).count("1") for j in n] for i in n])
+    want = torch.cat([x[:, :128] @ H, x[:, 128:] @ H], 1)
+    got = K.fwht_blocks(x)
+    assert torch.allclose(got, want, atol=1e-4)
+    assert torch.equal(got, K.fwht_blocks(x.clone()))
+    y = torch.randn(7, 256, generator=g)
+    assert torch.allclose(K.fwht_blocks(x) @ K.fwht_blocks(y).t() / 128, x @ y.t(), atol=1e-3)
+
+
+def test_hadamard_int8_product_is_close_and_robust_to_an_outlier():
+    g = torch.Generator().manual_seed(4)
+    a, b = torch.randn(128, 256, generator=g), torch.randn(64, 256, generator=g)
+    a[3, 17] = 200.0  # one outlier would cost a plainly quantised row almost all of its grid
+    want = a @ b.t()
+    got = K.ste_matmul_hadamard(a, b)
+    assert got.dtype == torch.float32 and got.shape == (128, 64)
+    assert (got - want).norm() / want.norm() < 0.02
+    # the same rows quantised without the rotation: the outlier row is far worse
+    aq, sa = K.quant_rows(a, 127)
+    bq, sb = K.quant_rows(b, 127)
+    plain = (aq.float() * sa[:, None]) @ (bq.float() * sb[:, None]).t()
+    assert (got[3] - want[3]).norm() < 0.5 * (plain[3] - want[3]).norm()
+
+
+@pytest.mark.parametrize("method", ["lsq", "absmax"])
+def test_hadamard_backward_is_close_to_the_float_backward(method):
+    def run(flag):
+        g = torch.Generator().manual_seed(5)
+        m = QuantLinear(128, 256, method=method, ste_bwd_hadamard=flag)
+        with torch.no_grad():
+            m.weight.copy_(torch.randn(256, 128, generator=g) * 0.05)
+            if method == "lsq":
+                m.weight_scale.copy_(m.lsq_optimal_scale(m.weight))
+        x = torch.randn(2, 64, 128, generator=g, requires_grad=True)
+        y = m(x)
+        y.backward(torch.randn(y.shape, generator=g))
+        return y.detach(), x.grad, m.weight.grad, (m.weight_scale.grad if method == "lsq" else None)
+
+    y0, dx0, dw0, ds0 = run(False)
+    y1, dx1, dw1, ds1 = run(True)
+    assert torch.equal(y0, y1)  # the forward is untouched
+    assert not torch.equal(dx0, dx1)
+    assert (dx1 - dx0).norm() / dx0.norm() < 0.03 and (dw1 - dw0).norm() / dw0.norm() < 0.03
+    if ds0 is not None:
+        assert (ds1 - ds0).norm() / ds0.norm() < 0.1
+    again = run(True)
+    assert torch.equal(dx1, again[1]) and torch.equal(dw1, again[2])
+    # a contraction length off the block falls back to the float GEMMs, bit for bit
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(3, 128, generator=g)
+    outs = []
+    for flag in (False, True):
+        m, _ = _layer(method, 128, 256)
+        m.ste_bwd_hadamard = flag
+        xx = x.clone().requires_grad_(True)
+        m(xx).sum().backward()
+        outs.append((xx.grad, m.weight.grad))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_hadamard_qat_run_trains_and_replays(tmp_path):
+    from open_transformers_b200.cli.audit_replay import audit_replay
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path)
+    over = ["++model.qat.enabled=true", "train.ckpt_every_steps=2"]
+    res = train(tiny_cfg(tmp, over + ["++model.qat.ste_bwd_hadamard=true"]), device="cpu", data_root=tmp)
+    assert all(math.isfinite(l) for l in res["losses"])
+    r = audit_replay(from_init=True, descriptor_checkpoint=res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3)
+    assert r["match"] is True and r["state_hash"] == res["hashes"][-1][1]
+    plain = train(tiny_cfg(tmp + "/p", over), device="cpu", data_root=tmp + "/p")
+    assert plain["hashes"][-1][1] != res["hashes"][-1][1]  # the tiny model's shapes reach the int8 backward
+    assert plain["losses"][0] == res["losses"][0]
+
+
 # ------------------------------------------------------------------------------------------ GPU
 def _both(fn, *cpu_args):
     a = fn(*cpu_args)
@@ -169,6 +248,16 @@ def test_gpu_int8_gemm_is_exact(M, N, Kd):
     exact = (a.double() @ b.double().t())
     got = K.gemm_i8(a.cuda(), b.cuda(), torch.ones(1).cuda(), torch.ones(N).cuda(), torch.float32).cpu().double()
     assert (got - exact).abs().max() <= exact.abs().max() * 2 ** -24
+    assert K.kernel_status("cuda") == 0
+
+
+@pytest.mark.gpu
+def test_gpu_hadamard_int8_product_bitwise_vs_cpu():
+    """rotation (IEEE adds), row statistics, quantiser and the tcgen05 kind::i8 GEMM give the CPU twin's bits"""
+    g = torch.Generator().manual_seed(8)
+    a, b = torch.randn(256, 384, generator=g), torch.randn(136, 384, generator=g).bfloat16()
+    a[5, 100] = 90.0
+    _eq(*_both(lambda a_, b_: K.ste_matmul_hadamard(a_, b_), a, b), "ste_matmul_hadamard")
     assert K.kernel_status("cuda") == 0
 
 
