@@ -85,7 +85,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                  descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
                  save_checkpoint_dir: str | None = None, loss_log: str | None = None, run_dir: str | None = None,
                  offload_optimizer: bool = False, offload_master: bool = False, offload_grads: bool = False,
-                 fold_spill_dir: str | None = None, no_fold_spill: bool = False, **_ignored) -> dict:
+                 fold_spill_dir: str | None = None, no_fold_spill: bool = False, optimizer_offload_dir: str | None = None,
+                 master_offload_dir: str | None = None, **_ignored) -> dict:
     import numpy as np
     import torch
 
@@ -139,7 +140,12 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     # (each finished virtual rank is folded into its replica's partial, ascending shard order); --fold-spill-dir puts
     # the finished partials on disk with a digest that is checked when they are read back
     spill = None if (no_fold_spill or not offload_grads) else fold_spill_dir
-    engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None, fold_gradients=offload_grads, fold_spill_dir=spill)
+    # --offload-optimizer / --offload-master: moments / fp32 master weights live in files between steps
+    engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None, fold_gradients=offload_grads, fold_spill_dir=spill,
+                         offload_optimizer=offload_optimizer, optimizer_offload_dir=optimizer_offload_dir,
+                         offload_master=offload_master, master_offload_dir=master_offload_dir)
+    if engine.master_offload_inert:
+        log.warning("--offload-master changes nothing on a GPU: the fp32 master weights stay resident")
     V = engine.V
     run_path = Path(run_dir) if run_dir else None
     result: dict = {"device": device, "kernels": native.loaded_libraries(), "rank0_losses": [], "expected": expected, "match": None}
@@ -222,6 +228,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             last_hash = engine.sharded_state_hash(chained, bd, include_grads=sh_cfg.include_grads, tensor_digest=sh_cfg.tensor_digest)
             if hash_due:
                 chained = last_hash
+        engine.release_state()
         log.info("replayed step %d loss %.6f grad_norm %.6f", step, loss_mean, grad_norm)
     result["seconds_per_step"] = (time.time() - t_start) / max(len(loss_rows), 1)
     if torch.cuda.is_available() and device.startswith("cuda"):
@@ -290,7 +297,8 @@ def main(argv: list[str] | None = None) -> int:
                            cpu_threads=a.cpu_threads, from_init=a.from_init, descriptor_checkpoint=a.descriptor_checkpoint,
                            until_step=a.until_step, expect_hash=a.expect_hash, save_checkpoint_dir=a.save_checkpoint_dir,
                            loss_log=a.loss_log, run_dir=a.run_dir, offload_optimizer=a.offload_optimizer, offload_master=a.offload_master,
-                           offload_grads=a.offload_grads, fold_spill_dir=a.fold_spill_dir, no_fold_spill=a.no_fold_spill)
+                           offload_grads=a.offload_grads, fold_spill_dir=a.fold_spill_dir, no_fold_spill=a.no_fold_spill,
+                           optimizer_offload_dir=a.optimizer_offload_dir, master_offload_dir=a.master_offload_dir)
     except AuditError as e:
         print("AUDIT ERROR: %s" % e, file=sys.stderr)
         return 2

@@ -114,14 +114,16 @@ class PeerBuffer:
     seen from this process (CUDA IPC mapping for r != rank). On the CPU, or with a single rank, it is
     an ordinary tensor."""
 
-    def __init__(self, nbytes: int, device: torch.device, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, nbytes: int, device: torch.device, rank: int = 0, world: int = 1, group=None, storage: torch.Tensor | None = None):
         self.nbytes, self.device, self.rank, self.world = nbytes, device, rank, world
         self._peer_ptrs: list[int] = []
         self._own_ptr = 0
         self._group = group
         self._ipc = device.type == "cuda" and world > 1
+        if storage is not None:  # caller-provided bytes (a file mapping): single rank only
+            assert not self._ipc and storage.dtype == torch.uint8 and storage.numel() >= nbytes
         if not self._ipc:
-            self.bytes = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            self.bytes = storage[:nbytes] if storage is not None else torch.zeros(nbytes, dtype=torch.uint8, device=device)
             self.ptrs = [self.bytes.data_ptr()]
             return
         import torch.distributed as dist

@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -53,6 +54,9 @@ class StepOutput:
     grad_norm: float
     clip_coef: float
     skipped: bool
+
+
+_OFFLOAD_BLOCK = 1 << 26  # elements per copy between a state file and the GPU (256 MiB of fp32)
 
 
 class SpillCorruption(RuntimeError):
@@ -79,7 +83,9 @@ def _ptr_array(ptrs):
 
 class TrainEngine:
     def __init__(self, cfg: RootConfig, device: torch.device | str = "cpu", rank: int = 0, world: int = 1, group=None,
-                 seed: int | None = None, init: bool = True, fold_gradients: bool = False, fold_spill_dir: str | None = None):
+                 seed: int | None = None, init: bool = True, fold_gradients: bool = False, fold_spill_dir: str | None = None,
+                 offload_optimizer: bool = False, optimizer_offload_dir: str | None = None,
+                 offload_master: bool = False, master_offload_dir: str | None = None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.rank, self.world, self.group = rank, world, group
@@ -142,15 +148,39 @@ class TrainEngine:
         def alloc(nbytes, shared):
             return PeerBuffer(nbytes, self.device, pw if shared else 0, pg if shared else 1, group if shared else None)
 
-        self.buf_master = alloc(4 * n, shared=not self.mixed)
+        # State kept off the compute device between steps (single-process replay of a model whose training state does
+        # not fit beside the activations). Moments: on the CPU the two flat buffers ARE file mappings in
+        # ``optimizer_offload_dir`` (the kernels work on them in place and ``release_state`` lets the OS drop the pages);
+        # on a GPU they are written to those files after the step's hash and read back for the next optimizer step, so
+        # they are absent during forward and backward, when the activations peak. Master weights: file mapping on the
+        # CPU; on a GPU they stay resident (the parameters are views of that buffer).
+        # (reference: --offload-optimizer / --offload-master, src/pretrain/cli/audit_replay.py:1249-1290)
+        self._off_opt, self._off_master = bool(offload_optimizer), bool(offload_master)
+        if (self._off_opt or self._off_master) and (world != 1 or self.tp != 1):
+            raise ValueError("state offload is for the single-process replay")
+        self._off_tmp = []
+        self._off_files: dict[str, np.memmap] = {}
+        self.master_offload_inert = self._off_master and self.is_cuda
+        if self._off_master and not self.is_cuda:
+            backing = torch.from_numpy(self._mapped_file("master", master_offload_dir, 4 * n, np.uint8))
+            self.buf_master = PeerBuffer(4 * n, self.device, storage=backing)
+        else:
+            self.buf_master = alloc(4 * n, shared=not self.mixed)
         self.master = self.buf_master.typed(torch.float32)
         if self.mixed:
             self.buf_compute = alloc(2 * n, shared=True)
             self.compute = self.buf_compute.typed(torch.bfloat16)
         else:
             self.buf_compute, self.compute = self.buf_master, self.master
-        self.m1 = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.m2 = torch.zeros(n, dtype=torch.float32, device=self.device)
+        if self._off_opt:
+            for key in ("exp_avg", "exp_avg_sq"):
+                self._mapped_file(key, optimizer_offload_dir, n, np.float32)
+        if self._off_opt and not self.is_cuda:
+            self._m1 = torch.from_numpy(self._off_files["exp_avg"])
+            self._m2 = torch.from_numpy(self._off_files["exp_avg_sq"])
+        else:
+            self._m1 = torch.zeros(n, dtype=torch.float32, device=self.device)
+            self._m2 = torch.zeros(n, dtype=torch.float32, device=self.device)
         self.grad_red = torch.zeros(n, dtype=torch.float32, device=self.device)
         # Folded gradients (single-process replay with little memory): instead of one gradient buffer per hosted virtual
         # rank there is ONE work buffer plus one partial per replica; ``fold_virtual_rank`` adds a finished virtual rank
@@ -202,6 +232,73 @@ class TrainEngine:
         for mod in self.model.modules():
             for bname, b in list(mod.named_buffers(recurse=False)):
                 mod._buffers[bname] = b.to(self.device)
+
+    # ------------------------------------------------------------------------------ state offload
+    def _mapped_file(self, key: str, directory: str | None, count: int, dtype) -> np.memmap:
+        """A zero-filled file mapping of ``count`` elements in ``directory`` (a temporary directory when None)."""
+        import tempfile
+
+        if directory is None:
+            tmp = tempfile.TemporaryDirectory(prefix="otb_offload_")
+            self._off_tmp.append(tmp)
+            directory = tmp.name
+        os.makedirs(directory, exist_ok=True)
+        mm = np.memmap(os.path.join(directory, key + ".bin"), dtype=dtype, mode="w+", shape=(max(int(count), 1),))
+        self._off_files[key] = mm
+        return mm
+
+    def _moments_in(self) -> None:
+        if self._m1 is None:  # GPU, released: read the two files back
+            for attr, key in (("_m1", "exp_avg"), ("_m2", "exp_avg_sq")):
+                t = torch.empty(self.layout.total, dtype=torch.float32, device=self.device)
+                src = self._off_files[key]
+                for lo in range(0, t.numel(), _OFFLOAD_BLOCK):
+                    hi = min(lo + _OFFLOAD_BLOCK, t.numel())
+                    t[lo:hi].copy_(torch.from_numpy(src[lo:hi]))
+                setattr(self, attr, t)
+
+    @property
+    def m1(self) -> torch.Tensor:
+        self._moments_in()
+        return self._m1
+
+    @property
+    def m2(self) -> torch.Tensor:
+        self._moments_in()
+        return self._m2
+
+    def release_state(self) -> None:
+        """Between two steps of a replay with offloaded state: after the step's hash, before the next forward. Moments
+        leave the GPU (written to their files) or, on the CPU, their pages are handed back to the OS; the same for a
+        file-mapped master copy when a separate compute copy serves forward and backward. No value changes."""
+        if not (self._off_opt or self._off_master):
+            return
+        import mmap
+
+        if self.is_cuda:
+            self._wait_pending_hash()
+            torch.cuda.synchronize()
+        if self._off_opt and self.is_cuda and self._m1 is not None:
+            for attr, key in (("_m1", "exp_avg"), ("_m2", "exp_avg_sq")):
+                t, dst = getattr(self, attr), self._off_files[key]
+                for lo in range(0, t.numel(), _OFFLOAD_BLOCK):
+                    hi = min(lo + _OFFLOAD_BLOCK, t.numel())
+                    dst[lo:hi] = t[lo:hi].cpu().numpy()
+                setattr(self, attr, None)
+            self.__dict__.pop("_hash_plans", None)  # the digest plans hold the freed addresses
+            torch.cuda.empty_cache()
+        drop = []
+        if self._off_opt:
+            drop += ["exp_avg", "exp_avg_sq"]
+        if self._off_master and not self.is_cuda and self.mixed:
+            drop.append("master")
+        for key in drop:
+            mm = self._off_files[key]
+            mm.flush()
+            try:
+                mm._mmap.madvise(mmap.MADV_DONTNEED)  # a shared file mapping: the data stays in the file
+            except (AttributeError, OSError, ValueError):
+                pass
 
     # ------------------------------------------------------------------------------ plumbing
     def _install_views(self) -> None:
@@ -641,3 +738,10 @@ class TrainEngine:
     def close(self) -> None:
         for b in [self.buf_master, self.buf_compute] + self.buf_grads:
             b.close()
+        self._off_files.clear()
+        for tmp in self._off_tmp:
+            try:
+                tmp.cleanup()
+            except OSError:
+                pass
+        self._off_tmp = []

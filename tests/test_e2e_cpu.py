@@ -188,3 +188,24 @@ def test_replay_with_folded_gradients_and_verified_spill(trained, tmp_path):
     with pytest.raises(SpillCorruption):
         eng.reduce_gradients()
     eng.close()
+
+
+def test_replay_with_offloaded_moments_and_master(trained, tmp_path):
+    """--offload-optimizer / --offload-master keep the moments and the fp32 master weights in files; the digests are
+    those of the plain replay, from a checkpoint and from the initial state, and the files hold the final state."""
+    import numpy as np
+
+    tmp, cfg, res = trained
+    ck = tmp + "/runs/t/checkpoints/step_000000002"
+    plain = audit_replay(ck, data_root=tmp, until_step=4, save_checkpoint_dir=str(tmp_path / "plain"))
+    od, md = tmp_path / "moments", tmp_path / "master"
+    off = audit_replay(ck, data_root=tmp, until_step=4, offload_optimizer=True, optimizer_offload_dir=str(od),
+                       offload_master=True, master_offload_dir=str(md), offload_grads=True, save_checkpoint_dir=str(tmp_path / "off"))
+    assert plain["state_hash"] == off["state_hash"] and off["state_hash"] is not None
+    assert {p.name for p in od.iterdir()} == {"exp_avg.bin", "exp_avg_sq.bin"} and (md / "master.bin").exists()
+    m1 = np.fromfile(od / "exp_avg.bin", dtype=np.float32)
+    assert np.isfinite(m1).all() and np.abs(m1).max() > 0 and np.fromfile(od / "exp_avg_sq.bin", dtype=np.float32).min() >= 0
+    # temporary directories when none is named; from the initial state
+    a = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=2)
+    b = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=2, offload_optimizer=True, offload_master=True)
+    assert a["match"] is True and b["match"] is True and a["state_hash"] == b["state_hash"]
