@@ -138,8 +138,6 @@ class TrainEngine:
         self.layout = FlatLayout.build([(n, tuple(p.shape)) for n, p in named], self.dp_shard, member)
         lay = self.layout
         n = lay.total
-        if self.tp > 1 and self.is_cuda and self.dp_groups > 1:
-            raise NotImplementedError("tensor parallelism on GPUs is limited to one data-parallel group in this version")
         # with a tensor-parallel group every process ends up with the whole gradient of its virtual ranks, so each
         # reduces and updates everything itself (no peer-sharded ownership)
         peer = self.is_cuda and world > 1 and not self.nccl_mode and self.tp == 1
@@ -482,8 +480,9 @@ class TrainEngine:
             dist.all_reduce(acc, group=self.group)
             self.grad_red.copy_(acc).mul_(1.0 / self.V)
             check(self._chunk_sos_all(), "chunk_sos")
-        elif not self.is_cuda and self.dp_groups > 1:
-            # CPU ranks: exchange the flat buffers, then every rank reduces everything identically
+        elif self.dp_groups > 1 and not self.peer:
+            # CPU ranks, and GPU ranks that run tensor-parallel groups: exchange the flat buffers (gloo / NCCL all-gather),
+            # then every rank reduces everything identically from its own copies
             gathered = []
             for g in self.grads:
                 parts = [torch.empty_like(g) for _ in range(self.world)]
@@ -491,8 +490,12 @@ class TrainEngine:
                 gathered.append(parts)
             srcs = [gathered[v % per][(v // per) * self.tp].data_ptr() for v in range(self.V)]  # any rank of the owning group
             self._keep = gathered
-            check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks),
-                                               P(self.grad_red), P(self.chunk_sos)), "grad_reduce")
+            if self.is_cuda:
+                check(self.lib.otb_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks),
+                                               P(self.grad_red), P(self.chunk_sos), stream_ptr()), "grad_reduce")
+            else:
+                check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self.chunk_start), P(self.chunk_len), I(self.n_chunks),
+                                                   P(self.grad_red), P(self.chunk_sos)), "grad_reduce")
             self._keep = None
         else:
             self._barrier()  # every rank's backward is complete before anyone pulls
