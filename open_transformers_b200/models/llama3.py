@@ -65,8 +65,6 @@ class Llama3(nn.Module):
         st = A.tp()
         if st is not None:
             # tensor parallel: from here to the logits the residual stream is this rank's token rows [B*T / P, d]
-            if self.activation_checkpoint and self.training:
-                raise NotImplementedError("activation checkpointing is not combined with tensor parallelism")
             st.batch_shape = (B, T)
             input_ids = input_ids.reshape(-1)[st.rows(B * T)]
         x = self.embedding.encode(input_ids, self.compute_dtype)

@@ -154,13 +154,13 @@ class RMSNorm(nn.Module, ParamMixin):
         else:
             self.register_parameter("weight", None)
 
-    def forward(self, x):
+    def forward(self, x, tp_heads: int = 0):
         if self.weight is None:
             return A.rms_norm(x, None, eps=self.eps)
         w = self._cw()
         if w is None and x.dtype != self.weight.dtype:
             w = self.weight.to(x.dtype)
-        return A.rms_norm(x, self.weight, w, self._slot(), self.eps)
+        return A.rms_norm(x, self.weight, w, self._slot(), self.eps, tp_heads)
 
 
 @ROPE.register("rope_default")
@@ -271,8 +271,6 @@ class _GQABase(nn.Module, ParamMixin):
         H, Hkv, D, P = self.n_heads, self.n_kv_heads, self.head_dim, st.size
         if H % P or Hkv % P:
             raise ValueError("%d query / %d key-value heads do not split over %d tensor-parallel ranks" % (H, Hkv, P))
-        if self.qk_norm_gain:
-            raise NotImplementedError("QK-norm gains are not supported under tensor parallelism")
         fused = getattr(self, "_fused_qkv", None)
         if fused is None or (isinstance(self.wq, QuantLinear) and self.wq.qat_active):
             raise NotImplementedError("tensor-parallel attention needs the fused QKV weight of the training engine")
@@ -281,7 +279,13 @@ class _GQABase(nn.Module, ParamMixin):
                   for r in range(P)]
         qkv = A.tp_column_linear(x, fused[0], fused[1], fused[2], slices)
         B, T = st.batch_shape
-        o = A.attention(qkv.view(B, T, -1), cos, sin, H // P, Hkv // P, D, self.window, self.qk_norm, self.eps, False)
+        qk_norm = self.qk_norm
+        if self.qk_norm_gain:  # the gains' gradients run over all heads: see RMSNormFn
+            q, k, v = qkv.split([hq, hk, hk], -1)
+            q = self.q_norm(q.reshape(B * T, H // P, D), tp_heads=H // P).reshape(B * T, hq)
+            k = self.k_norm(k.reshape(B * T, Hkv // P, D), tp_heads=Hkv // P).reshape(B * T, hk)
+            qkv, qk_norm = torch.cat([q, k, v], -1), False
+        o = A.attention(qkv.view(B, T, -1), cos, sin, H // P, Hkv // P, D, self.window, qk_norm, self.eps, False)
         return self.wo(o.reshape(B * T, -1), residual)
 
     def forward(self, x, cos, sin, residual=None):

@@ -313,12 +313,13 @@ def tp_token_linear(x_shard, master, w, slot):
 
 class RMSNormFn(Function):
     @staticmethod
-    def forward(ctx, x, master, w, slot, eps):
+    def forward(ctx, x, master, w, slot, eps, tp_heads=0):
         x2 = _flat2d(x).contiguous()
         y, rstd = K.rmsnorm_fwd(x2, w, eps)
         ctx.save_for_backward(x2, rstd, w if w is not None else x2.new_empty(0))
         ctx.has_w = w is not None
         ctx.slot = slot
+        ctx.tp_heads = int(tp_heads)
         ctx.shape = x.shape
         ctx.master_dtype = master.dtype if master is not None else None
         return y.view(x.shape)
@@ -331,7 +332,22 @@ class RMSNormFn(Function):
         need_dg = ctx.has_w and ((ctx.slot is not None and ctx.slot.buf is not None) or ctx.needs_input_grad[1])
         dx, dg = K.rmsnorm_bwd(dy2, x2, w, rstd, need_dg)
         gm = None
-        if need_dg and _TP is not None:
+        if need_dg and _TP is not None and ctx.tp_heads:
+            # rows are (token, head) pairs and the HEADS are split over the group, so a rank's rows interleave with the
+            # others' in the unsplit order and its 8-row slabs are not slabs of the unsplit tree: the operands are
+            # gathered, put back into (token, all heads) order, and rank 0 runs the gain gradient over the whole of them
+            h, P_ = ctx.tp_heads, _TP.size
+
+            def canon(t):
+                parts = torch.stack([p.reshape(-1, h, *t.shape[1:]) for p in _all_gather(t)], 1)  # [tokens, P, h, ...]
+                return parts.reshape(-1, *t.shape[1:]).contiguous()
+
+            dy_f, x_f, rstd_f = canon(dy2), canon(x2), canon(rstd)
+            if _TP.rank == 0:
+                _, dg = K.rmsnorm_bwd(dy_f, x_f, w, rstd_f, True)
+            else:
+                need_dg = False
+        elif need_dg and _TP is not None:
             # each rank's dg is the root of the slab pair tree over its own token rows (a sub-tree of the unsplit tree when
             # the rank holds a power-of-two number of slabs); the roots are combined in rank order by the same tree, and
             # rank 0 alone adds the result to its gradient buffer
@@ -351,13 +367,15 @@ class RMSNormFn(Function):
                     ctx.slot.buf.add_(dg)
             else:
                 gm = dg.to(ctx.master_dtype)
-        return dx.view(ctx.shape), gm, None, None, None
+        return dx.view(ctx.shape), gm, None, None, None, None
 
 
-def rms_norm(x, master, w=None, slot=None, eps=1e-5):
+def rms_norm(x, master, w=None, slot=None, eps=1e-5, tp_heads=0):
+    """``tp_heads``: under tensor parallelism, the rows of ``x`` are (token, head) pairs with this many local heads per
+    token (the heads are split over the group); 0 = the rows are this rank's tokens."""
     if master is None:
         return RMSNormFn.apply(x, None, None, None, eps)
-    return RMSNormFn.apply(x, master, master if w is None else w, slot, eps)
+    return RMSNormFn.apply(x, master, master if w is None else w, slot, eps, tp_heads)
 
 
 class SwiGLUFn(Function):

@@ -13,12 +13,12 @@ from helpers import free_port
 WORKER = str(Path(__file__).resolve().parent / "tp_cpu_worker.py")
 
 
-def _run(world, tp, bf16, out):
+def _run(world, tp, bf16, out, extra=""):
     port = free_port()
     procs = []
     for rank in range(world):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   OMP_NUM_THREADS="2", OTB_TEST_TP=str(tp), OTB_TEST_BF16="1" if bf16 else "0", OTB_TEST_OUT=str(out))
+                   OMP_NUM_THREADS="2", OTB_TEST_TP=str(tp), OTB_TEST_BF16="1" if bf16 else "0", OTB_TEST_OUT=str(out), OTB_TEST_EXTRA=extra)
         procs.append(subprocess.Popen([sys.executable, WORKER], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
     outs = []
     for p in procs:
@@ -47,3 +47,22 @@ def test_two_tensor_parallel_groups_share_the_virtual_ranks(tmp_path):
     got = _run(4, 2, False, tmp_path / "tp2dp2.json")          # TP = 2 x DP = 2: each group hosts one virtual rank
     assert [h for _, _, h in got] == [h for _, _, h in base]
     assert [n for n, _, _ in got] == [n for n, _, _ in base]
+
+
+@pytest.mark.distributed
+def test_qk_norm_gains_under_tensor_parallelism(tmp_path):
+    """heads are split over the group, the gains' gradients run over all (token, head) rows in the unsplit order"""
+    extra = "model.modules.attention=gqa_qknorm_repop model.qk_norm=true model.qk_norm_gain=true model.n_heads=4 model.n_kv_heads=2 model.head_dim=32"
+    base = _run(1, 1, True, tmp_path / "base.json", extra)
+    tp2 = _run(2, 2, True, tmp_path / "tp2.json", extra)
+    assert tp2 == base, (tp2, base)
+    plain = _run(1, 1, True, tmp_path / "plain.json", extra.replace("qk_norm_gain=true", "qk_norm_gain=false"))
+    assert plain[-1][2] != base[-1][2]
+
+
+@pytest.mark.distributed
+def test_activation_checkpointing_under_tensor_parallelism(tmp_path):
+    """the recomputed forward repeats the group's gathers in the same order on every rank; no bit changes"""
+    base = _run(1, 1, True, tmp_path / "base.json")
+    tp2 = _run(2, 2, True, tmp_path / "tp2.json", "run.activation_checkpoint=true")
+    assert tp2 == base, (tp2, base)

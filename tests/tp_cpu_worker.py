@@ -27,7 +27,7 @@ def main():
     cfg = load_config("tiny_cpu", ["model.n_layers=2", "model.d_model=128", "model.n_heads=2", "model.n_kv_heads=2", "model.ffn_intermediate=256",
                                    "model.vocab_size=%d" % vocab, "train.seq_len=%d" % T, "data.seq_len=%d" % T, "model.max_seq_len_pretrain=%d" % T,
                                    "run.virtual_dp_size=%d" % V, "run.dp_shard_size=%d" % V, "run.dp_replicate_size=1", "run.tp_size=%d" % tp,
-                                   "run.mixed_precision=%s" % ("true" if bf16 else "false")])
+                                   "run.mixed_precision=%s" % ("true" if bf16 else "false")] + os.environ.get("OTB_TEST_EXTRA", "").split())
     eng = TrainEngine(cfg, device, rank, world)
     prev, out = None, []
     for step in range(3):
