@@ -89,6 +89,7 @@ def main() -> int:
     ap.add_argument("--override", action="append", default=[], help="config override (debugging; makes the number invalid)")
     ap.add_argument("--no-hash", action="store_true", help="debugging: skip the per-step state hash (makes the number invalid)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (run.tp_size); the GPUs form one group")
+    ap.add_argument("--tp-fused", action="store_true", help="with --tp: peer-memory all-gather->GEMM / chained GEMM kernels (run.tp_fused)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -114,7 +115,8 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
     native.cuda_lib()
 
-    cfg = load_config(args.config, args.override + (["run.tp_size=%d" % args.tp] if args.tp > 1 else []))
+    cfg = load_config(args.config, args.override + (["run.tp_size=%d" % args.tp] if args.tp > 1 else [])
+                      + (["run.tp_fused=true"] if args.tp_fused else []))
     V = cfg.run.virtual_dp_size
     eng = TrainEngine(cfg, device, rank, world, None)
     mb, T = cfg.train.micro_batch_size, cfg.train.seq_len

@@ -251,6 +251,7 @@ class RunConfig(_Strict):
     # B200 additions
     virtual_dp_size: int = 0  # 0 = dp_shard * dp_replicate of the launch (one virtual rank per process)
     tp_size: int = 1
+    tp_fused: bool = False  # tensor-parallel traffic through the peer-memory GEMM kernels instead of library all-gathers (GPUs)
     heartbeat_timeout_s: float = 0.0  # > 0: host-side failure detection between the processes (parallel/heartbeat.py)
 
     @model_validator(mode="after")

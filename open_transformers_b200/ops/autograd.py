@@ -147,6 +147,13 @@ class TpState:
     def __init__(self, group, rank: int, size: int):
         self.group, self.rank, self.size = group, rank, size
         self.batch_shape = None  # (B, T) of the micro-batch being processed
+        # peer-memory workspace (parallel.tensor_parallel.TpWorkspace) when the fused all-gather -> GEMM and chained
+        # GEMM -> ordered-reduction kernels carry the group's traffic instead of library all-gathers; None otherwise
+        self.ws = None
+
+    def fused(self, x: torch.Tensor, M: int) -> bool:
+        """Whether the peer-memory kernels take this call: bf16 activations on a GPU, whole 128-row blocks per rank."""
+        return self.ws is not None and x.is_cuda and x.dtype == torch.bfloat16 and M % (self.size * 128) == 0
 
     def rows(self, M: int) -> slice:
         assert M % self.size == 0, "token count %d does not split over %d tensor-parallel ranks" % (M, self.size)
@@ -214,10 +221,16 @@ class TpColumnLinearFn(Function):
     @staticmethod
     def forward(ctx, x_shard, master, w, slot, slices_by_rank):
         st = _TP
-        x_full = tp_gather_rows(_flat2d(x_shard))
         mine = slices_by_rank[st.rank]
         w_t = w[mine[0][0]:mine[0][1]] if len(mine) == 1 else torch.cat([w[a:b] for a, b in mine], 0)
-        y = K.gemm(x_full, w_t.contiguous())
+        x2 = _flat2d(x_shard)
+        if st.fused(x2, x2.shape[0] * st.size):
+            # one kernel: this rank's rows go to the peers' buffers while the tensor-core CTAs start on the local rows;
+            # the gathered activation stays in the (per-layer) peer buffer for the weight gradient
+            y, x_full = st.ws.ag_gemm(("col", master.data_ptr()), x2.contiguous(), w_t.contiguous())
+        else:
+            x_full = tp_gather_rows(x2)
+            y = K.gemm(x_full, w_t.contiguous())
         ctx.save_for_backward(x_full, w)
         ctx.slot, ctx.slices = slot, slices_by_rank
         return y
@@ -246,12 +259,21 @@ class TpRowLinearFn(Function):
     def forward(ctx, a_t, master, w, slot, residual_shard, cols_by_rank):
         st = _TP
         a_t = _flat2d(a_t).contiguous()
-        a_full = tp_gather_cols(a_t, [[c] for c in cols_by_rank], w.shape[1])
-        mine = a_full[st.rows(a_full.shape[0])].contiguous()
-        if residual_shard is not None:
-            y = K.gemm(mine, w, epi=K.EPI_RESIDUAL, residual=_flat2d(residual_shard))
+        ascending = all(cols_by_rank[r][1] == cols_by_rank[r + 1][0] for r in range(st.size - 1))
+        if st.fused(a_t, a_t.shape[0]) and ascending:
+            # the fp32 accumulator tile travels rank 0 -> ... -> P-1, each rank continuing the ascending-k accumulation
+            # in tensor memory; the last rank stores every tile at the owner of its token rows
+            a0, b0 = cols_by_rank[st.rank]
+            res = _flat2d(residual_shard).contiguous() if residual_shard is not None else None
+            y = st.ws.chain_gemm(("row", master.data_ptr()), a_t, w[:, a0:b0].contiguous(), residual_shard=res)
         else:
-            y = K.gemm(mine, w)
+            a_full = tp_gather_cols(a_t, [[c] for c in cols_by_rank], w.shape[1])
+            mine = a_full[st.rows(a_full.shape[0])].contiguous()
+            if residual_shard is not None:
+                y = K.gemm(mine, w, epi=K.EPI_RESIDUAL, residual=_flat2d(residual_shard))
+            else:
+                y = K.gemm(mine, w)
+        ctx.master_key = master.data_ptr()
         ctx.save_for_backward(a_t, w)
         ctx.slot, ctx.cols, ctx.has_res = slot, cols_by_rank, residual_shard is not None
         return y
@@ -260,9 +282,13 @@ class TpRowLinearFn(Function):
     def backward(ctx, dy_shard):
         a_t, w = ctx.saved_tensors
         st = _TP
-        dy_full = tp_gather_rows(dy_shard.contiguous())
         a, b = ctx.cols[st.rank]
-        da_t = K.gemm(dy_full, w[:, a:b], b_mn=True)
+        dy_shard = dy_shard.contiguous()
+        if st.fused(dy_shard, dy_shard.shape[0] * st.size):
+            da_t, dy_full = st.ws.ag_gemm(("row_bwd", ctx.master_key), dy_shard, w[:, a:b].contiguous(), b_mn=True)
+        else:
+            dy_full = tp_gather_rows(dy_shard)
+            da_t = K.gemm(dy_full, w[:, a:b], b_mn=True)
         slot = _tp_slot(ctx.slot)
         K.gemm(dy_full, a_t, a_mn=True, b_mn=True, out=slot.buf[:, a:b], epi=K.EPI_ACC_F32)
         return da_t, None, None, None, (dy_shard if ctx.has_res else None), None

@@ -121,9 +121,16 @@ class TrainEngine:
                     if d == self.dp_rank:
                         tp_group = g_
             self._tp_state = TpState(tp_group, self.tp_rank, self.tp)
+            self._tp_group = tp_group
         self.mixed = bool(run.mixed_precision)
         self.compute_dtype = torch.bfloat16 if self.mixed else torch.float32
         self.is_cuda = self.device.type == "cuda"
+        if self.tp > 1 and run.tp_fused and self.is_cuda and self.mixed:
+            if run.activation_checkpoint:
+                raise ValueError("run.tp_fused keeps each layer's gathered activation in its peer buffer; it is not combined with activation checkpointing")
+            from ..parallel.tensor_parallel import TpWorkspace
+
+            self._tp_state.ws = TpWorkspace(self.device, self.tp_rank, self.tp, self._tp_group)
         self.lib = cuda_lib() if self.is_cuda else cpu_lib()
         self.nccl_mode = run.reduction_mode == "nccl"
 
@@ -388,6 +395,10 @@ class TrainEngine:
         set_tp(self._tp_state)
         if self._tp_state is not None:  # this rank's token rows of the labels
             labels = labels.reshape(-1)[self._tp_state.rows(labels.numel())]
+            if self._tp_state.ws is not None:
+                # the per-layer peer buffers are reused by every micro-batch: nobody overwrites one while a peer's previous
+                # backward pass may still read it (a flag exchange on the stream, no host synchronisation)
+                self._tp_state.ws.barrier()
         qat = self.cfg.model.qat
         if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
             set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
@@ -739,6 +750,9 @@ class TrainEngine:
                                    group=self.group)
 
     def close(self) -> None:
+        if self._tp_state is not None and self._tp_state.ws is not None:
+            self._tp_state.ws.close()
+            self._tp_state.ws = None
         for b in [self.buf_master, self.buf_compute] + self.buf_grads:
             b.close()
         self._off_files.clear()

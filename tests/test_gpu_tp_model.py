@@ -15,8 +15,9 @@ pytestmark = [pytest.mark.gpu, pytest.mark.distributed]
 WORKER = str(Path(__file__).resolve().parent / "tp_cpu_worker.py")
 
 
-def _run(n, tp, out):
-    env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_TP=str(tp), OTB_TEST_BF16="1", OTB_TEST_DEVICE="cuda", OTB_TEST_T="128", NCCL_NVLS_ENABLE="0")
+def _run(n, tp, out, extra=""):
+    env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_TP=str(tp), OTB_TEST_BF16="1", OTB_TEST_DEVICE="cuda", OTB_TEST_T="128", NCCL_NVLS_ENABLE="0",
+               OTB_TEST_EXTRA=extra)
     if n == 1:
         cmd = [sys.executable, WORKER]
     else:
@@ -43,3 +44,12 @@ def test_two_tensor_parallel_groups_on_four_gpus_reproduce_the_single_gpu_hashes
     four = _run(4, 2, tmp_path / "g4.json")
     assert [h for _, _, h in four] == [h for _, _, h in one]
     assert [n for n, _, _ in four] == [n for n, _, _ in one]
+
+
+def test_fused_peer_memory_kernels_carry_the_tensor_parallel_model_step(tmp_path):
+    """run.tp_fused: all-gather -> GEMM and chained GEMM -> ordered reduction inside the model step; same bytes as one GPU"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    one = _run(1, 1, tmp_path / "g1.json")
+    two = _run(2, 2, tmp_path / "g2.json", "run.tp_fused=true")
+    assert two == one, (two, one)

@@ -44,6 +44,10 @@ def main():
         eng.optimizer_step(3e-4, eng.clip_coefficient(norm, 1.0))
         prev = eng.sharded_state_hash(prev, None, tensor_digest="raw" if not device.startswith("cuda") else "tree")
         out.append([norm, ces, prev])
+    if device.startswith("cuda"):
+        from open_transformers_b200.ops.functional import kernel_status
+
+        assert kernel_status(device) == 0, "a bounded wait inside a kernel ran out"
     if rank == 0:
         json.dump(out, open(os.environ["OTB_TEST_OUT"], "w"))
     if world > 1:
