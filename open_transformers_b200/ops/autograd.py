@@ -153,7 +153,8 @@ class TpState:
 
     def fused(self, x: torch.Tensor, M: int) -> bool:
         """Whether the peer-memory kernels take this call: bf16 activations on a GPU, whole 128-row blocks per rank."""
-        return self.ws is not None and x.is_cuda and x.dtype == torch.bfloat16 and M % (self.size * 128) == 0
+        on_device = x.is_cuda or getattr(self.ws, "any_device", False)  # (a host stand-in of the workspace, for tests)
+        return self.ws is not None and on_device and x.dtype == torch.bfloat16 and M % (self.size * 128) == 0
 
     def rows(self, M: int) -> slice:
         assert M % self.size == 0, "token count %d does not split over %d tensor-parallel ranks" % (M, self.size)

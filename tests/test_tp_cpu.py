@@ -13,12 +13,12 @@ from helpers import free_port
 WORKER = str(Path(__file__).resolve().parent / "tp_cpu_worker.py")
 
 
-def _run(world, tp, bf16, out, extra=""):
+def _run(world, tp, bf16, out, extra="", **env_extra):
     port = free_port()
     procs = []
     for rank in range(world):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   OMP_NUM_THREADS="2", OTB_TEST_TP=str(tp), OTB_TEST_BF16="1" if bf16 else "0", OTB_TEST_OUT=str(out), OTB_TEST_EXTRA=extra)
+                   OMP_NUM_THREADS="2", OTB_TEST_TP=str(tp), OTB_TEST_BF16="1" if bf16 else "0", OTB_TEST_OUT=str(out), OTB_TEST_EXTRA=extra, **env_extra)
         procs.append(subprocess.Popen([sys.executable, WORKER], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
     outs = []
     for p in procs:
@@ -65,4 +65,13 @@ def test_activation_checkpointing_under_tensor_parallelism(tmp_path):
     """the recomputed forward repeats the group's gathers in the same order on every rank; no bit changes"""
     base = _run(1, 1, True, tmp_path / "base.json")
     tp2 = _run(2, 2, True, tmp_path / "tp2.json", "run.activation_checkpoint=true")
+    assert tp2 == base, (tp2, base)
+
+
+@pytest.mark.distributed
+def test_fused_kernel_call_sites_of_the_model_step(tmp_path):
+    """the model step routed through the workspace's two fused operations (a host stand-in with their documented meaning):
+    operand layouts, keys and saved tensors of the three call sites give the unsplit bytes"""
+    base = _run(1, 1, True, tmp_path / "base.json", OTB_TEST_T="128")
+    tp2 = _run(2, 2, True, tmp_path / "tp2.json", OTB_TEST_T="128", OTB_TEST_HOST_WS="1")
     assert tp2 == base, (tp2, base)

@@ -14,6 +14,46 @@ from open_transformers_b200.config import load_config
 from open_transformers_b200.train.engine import TrainEngine
 
 
+class HostWorkspace:
+    """Stand-in for the peer-memory workspace on CPU ranks: the two fused operations with their documented meaning
+    (all-gather -> GEMM; K-split GEMM whose result arrives sharded by token rows), built from gathers."""
+
+    any_device = True
+
+    def __init__(self, rank, P, group=None):
+        self.rank, self.P, self.group, self.calls = rank, P, group, []
+
+    def _gather(self, t):
+        parts = [torch.empty_like(t.view(torch.uint8)) for _ in range(self.P)]
+        dist.all_gather(parts, t.contiguous().view(torch.uint8), group=self.group)
+        return [p.view(t.dtype) for p in parts]
+
+    def barrier(self):
+        dist.barrier(group=self.group)
+
+    def ag_gemm(self, key, x_shard, w, b_mn=False, out_dtype=torch.bfloat16):
+        from open_transformers_b200.ops import functional as K
+
+        self.calls.append(("ag",) + tuple(key[:1]))
+        x_full = torch.cat(self._gather(x_shard), 0)
+        return K.gemm(x_full, w, b_mn=b_mn), x_full
+
+    def chain_gemm(self, key, a, w, b_mn=False, residual_shard=None):
+        from open_transformers_b200.ops import functional as K
+
+        self.calls.append(("chain",) + tuple(key[:1]))
+        a_full = torch.cat(self._gather(a), 1)
+        w_full = torch.cat(self._gather(w), 0 if b_mn else 1)
+        per = a.shape[0] // self.P
+        mine = a_full[self.rank * per:(self.rank + 1) * per].contiguous()
+        if residual_shard is not None:
+            return K.gemm(mine, w_full, b_mn=b_mn, epi=K.EPI_RESIDUAL, residual=residual_shard)
+        return K.gemm(mine, w_full, b_mn=b_mn)
+
+    def close(self):
+        pass
+
+
 def main():
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     tp, bf16 = int(os.environ.get("OTB_TEST_TP", "1")), os.environ.get("OTB_TEST_BF16", "0") == "1"
@@ -29,6 +69,8 @@ def main():
                                    "run.virtual_dp_size=%d" % V, "run.dp_shard_size=%d" % V, "run.dp_replicate_size=1", "run.tp_size=%d" % tp,
                                    "run.mixed_precision=%s" % ("true" if bf16 else "false")] + os.environ.get("OTB_TEST_EXTRA", "").split())
     eng = TrainEngine(cfg, device, rank, world)
+    if os.environ.get("OTB_TEST_HOST_WS") == "1" and tp > 1:
+        eng._tp_state.ws = HostWorkspace(eng.tp_rank, eng.tp, eng._tp_group)
     prev, out = None, []
     for step in range(3):
         eng.zero_grads()
@@ -48,6 +90,9 @@ def main():
         from open_transformers_b200.ops.functional import kernel_status
 
         assert kernel_status(device) == 0, "a bounded wait inside a kernel ran out"
+    if os.environ.get("OTB_TEST_HOST_WS") == "1" and tp > 1:
+        kinds = {c for c in eng._tp_state.ws.calls}
+        assert kinds == {("ag", "col"), ("ag", "row_bwd"), ("chain", "row")}, kinds
     if rank == 0:
         json.dump(out, open(os.environ["OTB_TEST_OUT"], "w"))
     if world > 1:
