@@ -90,16 +90,23 @@ class QuantLinear(Linear):
             return K.row_stat(w, "absmax", 1.0 / self.qmax_w, 1e-12)
         return (K.absmax(w) * (1.0 / self.qmax_w)).clamp_min(1e-12).expand(w.shape[0]).contiguous()
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, tp_mode=None):
         if not self.qat_active:
             return super().forward(x, residual)
-        if A.tp() is not None:
-            raise NotImplementedError("quantisation-aware layers are not split over a tensor-parallel group")
         w = self._cw()
         if w is None:
             w = self.weight if x.dtype == self.weight.dtype else self.weight.to(x.dtype)
         w = w.detach()
         lsq = self.method == "lsq"
+        st = A.tp()
+        mode = tp_mode or self.tp_mode
+        if st is not None and mode is not None:
+            if self.ste_bwd_hadamard:
+                raise NotImplementedError("the Hadamard int8 backward is not split over a tensor-parallel group")
+            parts = self.tp_slices(st) if mode == "col" else [st.split(self.in_features, r) for r in range(st.size)]
+            return A.tp_quant_linear(x, self.weight, w, self._slot(), self.weight_scale if lsq else None, self._step(w),
+                                     self._slot("weight_scale") if lsq else None, residual, self.qmax_w, self.qmax_a, lsq, self._qcache,
+                                     mode, parts)
         return A.quant_linear(x, self.weight, w, self._slot(), self.weight_scale if lsq else None, self._step(w),
                               self._slot("weight_scale") if lsq else None, residual, self.qmax_w, self.qmax_a, lsq, self._qcache, self.ste_bwd_hadamard)
 
@@ -272,12 +279,16 @@ class _GQABase(nn.Module, ParamMixin):
         if H % P or Hkv % P:
             raise ValueError("%d query / %d key-value heads do not split over %d tensor-parallel ranks" % (H, Hkv, P))
         fused = getattr(self, "_fused_qkv", None)
-        if fused is None or (isinstance(self.wq, QuantLinear) and self.wq.qat_active):
-            raise NotImplementedError("tensor-parallel attention needs the fused QKV weight of the training engine")
         hq, hk = H * D // P, Hkv * D // P
-        slices = [[(r * hq, (r + 1) * hq), (H * D + r * hk, H * D + (r + 1) * hk), ((H + Hkv) * D + r * hk, (H + Hkv) * D + (r + 1) * hk)]
-                  for r in range(P)]
-        qkv = A.tp_column_linear(x, fused[0], fused[1], fused[2], slices)
+        if isinstance(self.wq, QuantLinear) and self.wq.qat_active:
+            # quantised projections keep their own step sizes: three column-parallel layers, this rank's heads of each
+            qkv = torch.cat([self.wq(x, tp_mode="col"), self.wk(x, tp_mode="col"), self.wv(x, tp_mode="col")], -1)
+        elif fused is None:
+            raise NotImplementedError("tensor-parallel attention needs the fused QKV weight of the training engine")
+        else:
+            slices = [[(r * hq, (r + 1) * hq), (H * D + r * hk, H * D + (r + 1) * hk), ((H + Hkv) * D + r * hk, (H + Hkv) * D + (r + 1) * hk)]
+                      for r in range(P)]
+            qkv = A.tp_column_linear(x, fused[0], fused[1], fused[2], slices)
         B, T = st.batch_shape
         qk_norm = self.qk_norm
         if self.qk_norm_gain:  # the gains' gradients run over all heads: see RMSNormFn

@@ -598,6 +598,75 @@ class QuantLinearFn(Function):
         return dx, gw, None, None, gsm, None, None, (dy if ctx.has_res else None), None, None, None, None, None
 
 
+class TpQuantLinearFn(Function):
+    """The W8A8 layer under tensor parallelism. ``mode`` "col": ``x`` is this rank's token rows, the rank produces the output
+    features ``parts[rank]`` (ranges of W's rows) for all tokens. ``mode`` "row": ``x`` holds the input features
+    ``parts[rank]`` (one range of W's columns) of all tokens, the result comes back as this rank's token rows (+ residual).
+    The activation step is the absmax of the WHOLE activation, as in the unsplit layer, so the operand is gathered before it
+    is quantised; integer products are exact, and the float reductions (data gradient over all output features, weight
+    gradient over all tokens, step gradient over all input features) each run unsplit on the rank that owns the result:
+    for "row" the weight and step gradients are split by OUTPUT rows, which needs no further exchange."""
+
+    @staticmethod
+    def forward(ctx, x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache, mode, parts):
+        st = _TP
+        x2 = _flat2d(x).contiguous()
+        x_full = tp_gather_rows(x2) if mode == "col" else tp_gather_cols(x2, [[c] for c in parts], w.shape[1])
+        xq, sa = K.quant_act(x_full, qmax_a)
+        key = (K.weight_epoch, x2.dtype)
+        if cache is not None and K.weight_epoch is not None and cache.get("key") == key:
+            wq, w_hat = cache["wq"], cache["w_hat"]
+        else:
+            wq, w_hat = K.quant_weight(w, step, qmax_w, x2.dtype)
+            if cache is not None and K.weight_epoch is not None:
+                cache.update(key=key, wq=wq, w_hat=w_hat)
+        if mode == "col":
+            mine = parts[st.rank]
+            y = torch.cat([K.gemm_i8(xq, wq[a:b], sa, step[a:b].contiguous(), x2.dtype) for a, b in mine], 1)
+        else:
+            res = _flat2d(residual).contiguous() if residual is not None else None
+            y = K.gemm_i8(xq[st.rows(xq.shape[0])], wq, sa, step, x2.dtype, res)
+        ctx.save_for_backward(xq, sa, w_hat, w, step)
+        ctx.slot_w, ctx.slot_s = slot_w, slot_s
+        ctx.has_res = residual is not None
+        ctx.cfg = (qmax_w, learn_step, mode, parts)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, sa, w_hat, w, step = ctx.saved_tensors
+        qmax_w, learn_step, mode, parts = ctx.cfg
+        st = _TP
+        dy = dy.contiguous()
+        N, Kd = w.shape
+        if mode == "col":
+            rows_w = parts[st.rank]                       # this rank's output features: their gradient rows
+            dy_mine = dy                                  # [M, n_t], all tokens
+            dy_full = tp_gather_cols(dy, parts, N)
+            dx = K.gemm(dy_full[st.rows(dy_full.shape[0])].contiguous(), w_hat, b_mn=True)
+        else:
+            dy_full = tp_gather_rows(dy)                  # [M, N]
+            a, b = parts[st.rank]
+            dx = K.gemm(dy_full, w_hat[:, a:b], b_mn=True)
+            rows_w = [st.split(N)]
+            dy_mine = dy_full[:, rows_w[0][0]:rows_w[0][1]].contiguous()
+        G = K.gemm(dy_mine, K.i8_widen(xq, dy.dtype), a_mn=True, b_mn=True, epi=K.EPI_STORE_F32)  # [n_t, K], every token
+        gs = 1.0 / math.sqrt(float(Kd) * float(qmax_w))
+        slot_w = _tp_slot(ctx.slot_w)
+        slot_s = _tp_slot(ctx.slot_s) if learn_step else None
+        off = 0
+        for a, b in rows_w:
+            K.lsq_bwd_(G[off:off + (b - a)], w[a:b], step[a:b].contiguous(), sa, qmax_w if learn_step else qmax_w + 1, gs,
+                       slot_w.buf[a:b], slot_s.buf[a:b] if learn_step else None)
+            off += b - a
+        return dx, None, None, None, None, None, None, (dy if ctx.has_res else None), None, None, None, None, None, None
+
+
+def tp_quant_linear(x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache, mode, parts):
+    return TpQuantLinearFn.apply(x, master_w, master_w if w is None else w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a,
+                                 learn_step, cache, mode, parts)
+
+
 def quant_linear(x, master_w, w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a, learn_step, cache=None, hadamard=False):
     return QuantLinearFn.apply(x, master_w, master_w if w is None else w, slot_w, master_s, step, slot_s, residual, qmax_w, qmax_a,
                                learn_step, cache, hadamard)

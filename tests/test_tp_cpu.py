@@ -75,3 +75,15 @@ def test_fused_kernel_call_sites_of_the_model_step(tmp_path):
     base = _run(1, 1, True, tmp_path / "base.json", OTB_TEST_T="128")
     tp2 = _run(2, 2, True, tmp_path / "tp2.json", OTB_TEST_T="128", OTB_TEST_HOST_WS="1")
     assert tp2 == base, (tp2, base)
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("method", ["lsq", "absmax"])
+def test_quantisation_aware_layers_under_tensor_parallelism(tmp_path, method):
+    """W8A8 layers split over the group: whole-activation absmax, exact integer products, unsplit float reductions"""
+    extra = "++model.qat.enabled=true ++model.qat.method=%s ++model.qat.scale_refresh_every_n_steps=2" % method
+    base = _run(1, 1, True, tmp_path / "base.json", extra)
+    tp2 = _run(2, 2, True, tmp_path / "tp2.json", extra)
+    assert tp2 == base, (tp2, base)
+    plain = _run(1, 1, True, tmp_path / "plain.json")
+    assert plain[-1][2] != base[-1][2]
