@@ -6,6 +6,11 @@ from __future__ import annotations
 import torch
 
 
+def is_hidden_matrix(name: str, shape) -> bool:
+    """Muon's share of the model: 2-D weights that are neither an embedding / vocabulary matrix nor a norm gain."""
+    return len(shape) == 2 and "embedding" not in name and "norm" not in name
+
+
 def newton_schulz5(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
     a, b, c = 3.4445, -4.7750, 2.0315
     X = G.to(torch.bfloat16)
@@ -49,8 +54,8 @@ class MuonWithAuxAdamW:
 
     def __init__(self, named_params, optim_cfg, muon_lr: float = 0.02):
         named = list(named_params)
-        hidden = [p for n, p in named if p.dim() == 2 and "embedding" not in n]
-        rest = [p for n, p in named if not (p.dim() == 2 and "embedding" not in n)]
+        hidden = [p for n, p in named if is_hidden_matrix(n, p.shape)]
+        rest = [p for n, p in named if not is_hidden_matrix(n, p.shape)]
         self.muon = Muon(hidden, lr=muon_lr, weight_decay=optim_cfg.weight_decay)
         self.adamw = torch.optim.AdamW(rest, lr=optim_cfg.peak_lr, betas=tuple(optim_cfg.betas), eps=optim_cfg.eps, weight_decay=0.0)
 

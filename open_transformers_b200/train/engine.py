@@ -219,6 +219,22 @@ class TrainEngine:
         self.chunk_lo = int(lay.seg_first[self.seg_lo])
         self.chunk_hi = int(lay.seg_first[self.seg_hi])
         self.peer = peer
+        # ``optim.name: muon_hybrid`` (experimental, outside the audited path): Muon on the 2-D block weights, the AdamW
+        # kernel on everything else through a chunk table without those parameters
+        # (reference src/pretrain/optim/muon.py:24-164, gated by config in src/pretrain/optim/registry.py:13-27)
+        self.muon_params: list[int] = []
+        if cfg.optim.name == "muon_hybrid":
+            if peer or self.tp > 1:
+                raise NotImplementedError("optim.name=muon_hybrid needs every process to hold whole gradients: one GPU, CPU ranks, "
+                                          "or run.reduction_mode=nccl")
+            from ..optim.muon import is_hidden_matrix
+
+            self.muon_params = [i for i, (nm, shp) in enumerate(zip(lay.names, lay.shapes)) if is_hidden_matrix(nm, shp)]
+            hidden = set(self.muon_params)
+            keep = np.concatenate([np.arange(sg.first_chunk, sg.first_chunk + sg.n_chunks) for sg in lay.segments if sg.param not in hidden]
+                                  or [np.zeros(0, dtype=np.int64)]).astype(np.int64)
+            self._aux_chunks = (torch.from_numpy(lay.chunk_start[keep]).to(dev), torch.from_numpy(lay.chunk_len[keep]).to(dev),
+                                torch.from_numpy(lay.chunk_group[keep]).to(dev), int(len(keep)))
         self.chunk_sos = torch.zeros(max(self.n_chunks, 1), dtype=torch.float32, device=dev)
         self.seg_sos = torch.zeros(max(self.n_segs, 1), dtype=torch.float32, device=dev)
 
@@ -586,6 +602,9 @@ class TrainEngine:
                                       ctypes.c_double(o.weight_decay), ctypes.c_long(self.opt_step), F(clip), hyper)
         lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
         cs, cl, cg = self.chunk_start[lo:], self.chunk_len[lo:], self.chunk_group[lo:]
+        if self.muon_params:
+            cs, cl, cg, cnt = self._aux_chunks
+            self._muon_step(float(lr), float(clip))
         dst_buf = self.buf_compute
         dsts = dst_buf.ptrs if self.peer else [self.compute.data_ptr()]
         if self.is_cuda:
@@ -602,6 +621,26 @@ class TrainEngine:
             # (identical) compute weights (reference src/pretrain/train/loop.py:1069-1084)
             refresh_lsq_weight_scales(self.model)
             K.weight_epoch += 1
+
+    def _muon_step(self, lr: float, clip: float) -> None:
+        """Muon on the hidden matrices: momentum (kept in the first-moment buffer; the second stays zero), Nesterov
+        look-ahead, five Newton-Schulz iterations in bf16, decoupled weight decay; then the compute copies follow."""
+        from ..optim.muon import newton_schulz5
+
+        lay, o = self.layout, self.cfg.optim
+        mom = float(o.betas[1])
+        with torch.no_grad():
+            for i in self.muon_params:
+                p, g, buf = lay.view(self.master, i), lay.view(self.grad_red, i), lay.view(self.m1, i)
+                if clip != 1.0:
+                    g.mul_(clip)
+                buf.mul_(mom).add_(g)
+                upd = newton_schulz5(g.add(buf, alpha=mom))
+                if o.weight_decay:
+                    p.mul_(1.0 - lr * o.weight_decay)
+                p.add_(upd, alpha=-lr * max(1.0, p.shape[0] / p.shape[1]) ** 0.5)
+                if self.mixed:
+                    lay.view(self.compute, i).copy_(p)
 
     def skip_step(self) -> None:
         self._barrier()

@@ -158,3 +158,44 @@ def test_muon_orthogonalises_and_the_aux_optimizer_takes_the_rest():
     opt.zero_grad()
     assert not torch.equal(before, w.detach()) and float(b.detach().abs().sum()) > 0
     assert isinstance(opt.muon, Muon)
+
+
+def test_muon_hybrid_in_the_engine_updates_hidden_matrices_orthogonally_and_the_rest_by_adamw(tmp_path):
+    import numpy as np
+
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.train.engine import TrainEngine
+
+    def run(name, steps=2):
+        cfg = load_config("tiny_cpu", ["optim.name=%s" % name])
+        eng = TrainEngine(cfg, "cpu")
+        before = {n: p.clone() for n, p in eng.named_master()}
+        g = torch.Generator().manual_seed(0)
+        for _ in range(steps):
+            eng.zero_grads()
+            for v in range(eng.V):
+                ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+                eng.forward_backward(v, ids, torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), 1)
+            norm = eng.reduce_gradients()
+            eng.optimizer_step(1e-2, eng.clip_coefficient(norm, 1.0))
+        after = dict(eng.named_master())
+        return eng, before, after
+
+    eng, before, after = run("muon_hybrid")
+    hidden = [eng.names[i] for i in eng.muon_params]
+    assert hidden and all("embedding" not in n and "norm" not in n for n in hidden)
+    assert any(n.endswith("wo.weight") for n in hidden) and any("w_down" in n for n in hidden)
+    _, b2, a2 = run("adamw")
+    for n in before:
+        assert not torch.equal(before[n], after[n]) or "norm" in n, n          # everything trains
+    for n in hidden:   # Muon's step is (nearly) orthogonal: its singular values sit near 1, unlike AdamW's
+        d = (after[n] - before[n] * (1 - 1e-2 * eng.cfg.optim.weight_decay) ** 2)
+        assert not torch.equal(after[n], a2[n])
+        sv = torch.linalg.svdvals(d.float())
+        assert sv.max() / sv.median() < 4.0, (n, sv.max() / sv.median())
+    emb = [n for n in before if "embedding" in n]
+    _, _, m1 = run("muon_hybrid", 1)
+    _, _, p1 = run("adamw", 1)
+    assert emb and all(torch.equal(m1[n], p1[n]) for n in emb)                  # the aux AdamW is the engine's kernel
+    assert float(eng.m2[eng.layout.offsets[eng.muon_params[0]]]) == 0.0
+    eng.close()
