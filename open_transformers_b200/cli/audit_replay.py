@@ -125,6 +125,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         raise AuditError("no configuration: the checkpoint has none embedded and --config-name was not given")
     if cfg.run.reduction_mode != "deterministic_allgather":
         raise AuditError("run.reduction_mode=%s is not auditable (only deterministic_allgather pins the reduction order)" % cfg.run.reduction_mode)
+    if cfg.run.parallel == "ddp":
+        raise AuditError("run.parallel=ddp is not auditable (library all-reduce, reduction order not pinned)")
     if meta is not None:
         V, S, R = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
         if not (1 <= V <= MAX_AUDIT_WORLD) or S * R != V:

@@ -132,7 +132,9 @@ class TrainEngine:
 
             self._tp_state.ws = TpWorkspace(self.device, self.tp_rank, self.tp, self._tp_group)
         self.lib = cuda_lib() if self.is_cuda else cpu_lib()
-        self.nccl_mode = run.reduction_mode == "nccl"
+        # ``run.parallel: ddp`` (replicated parameters, library all-reduce of the gradients; reference src/pretrain/parallel/fsdp.py:24-54)
+        # is the throughput-only mode here as well: same path as ``reduction_mode: nccl``, order not pinned, not auditable
+        self.nccl_mode = run.reduction_mode == "nccl" or run.parallel == "ddp"
 
         # ---- model on the meta device first: the layout decides where the parameters live
         model = build_model(cfg.model)

@@ -87,3 +87,16 @@ def test_quantisation_aware_layers_under_tensor_parallelism(tmp_path, method):
     assert tp2 == base, (tp2, base)
     plain = _run(1, 1, True, tmp_path / "plain.json")
     assert plain[-1][2] != base[-1][2]
+
+
+@pytest.mark.distributed
+def test_ddp_mode_uses_the_library_all_reduce_and_is_refused_by_the_audit(tmp_path):
+    """run.parallel=ddp: gradients summed by the backend's all-reduce (order not pinned, so only closeness is asked)"""
+    from open_transformers_b200.cli.audit_replay import AuditError, audit_replay
+
+    base = _run(1, 1, False, tmp_path / "base.json")
+    ddp = _run(2, 1, False, tmp_path / "ddp.json", "run.parallel=ddp")
+    for (n0, _, _), (n1, _, _) in zip(base, ddp):
+        assert abs(n1 - n0) <= 1e-5 * n0
+    with pytest.raises(AuditError):
+        audit_replay(from_init=True, config_name="tiny_cpu", overrides=["run.parallel=ddp", "run.virtual_dp_size=2"], until_step=1)
