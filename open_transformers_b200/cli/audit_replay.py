@@ -80,6 +80,28 @@ def _find_expected(run_dir: Path | None, step: int) -> str | None:
     return p.read_text().strip() if p.is_file() else None
 
 
+def memlog(tag: str, device: str = "cpu") -> dict | None:
+    """With PRETRAIN_AUDIT_MEMLOG=1: log (and return) the process's resident set and, on a GPU, the allocator's current,
+    peak and reserved bytes at the named point of the replay (reference src/pretrain/cli/audit_replay.py:241-294)."""
+    if os.environ.get("PRETRAIN_AUDIT_MEMLOG") != "1":
+        return None
+    import resource
+
+    rec = {"at": tag, "rss_peak_gib": round(resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 2 ** 20, 3)}
+    try:
+        with open("/proc/self/statm") as fh:
+            rec["rss_gib"] = round(int(fh.read().split()[1]) * os.sysconf("SC_PAGE_SIZE") / 2 ** 30, 3)
+    except OSError:
+        pass
+    if device.startswith("cuda"):
+        import torch
+
+        rec.update(cuda_alloc_gib=round(torch.cuda.memory_allocated() / 2 ** 30, 3), cuda_peak_gib=round(torch.cuda.max_memory_allocated() / 2 ** 30, 3),
+                   cuda_reserved_gib=round(torch.cuda.memory_reserved() / 2 ** 30, 3))
+    log.info("memlog %s", json.dumps(rec))
+    return rec
+
+
 def audit_replay(checkpoint: str | None = None, *, config_name: str | None = None, overrides: list[str] | None = None,
                  data_root: str | None = None, device: str = "cpu", cpu_threads: str | None = None, from_init: bool = False,
                  descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
@@ -148,6 +170,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                          offload_master=offload_master, master_offload_dir=master_offload_dir)
     if engine.master_offload_inert:
         log.warning("--offload-master changes nothing on a GPU: the fp32 master weights stay resident")
+    memlog("engine built", device)
     V = engine.V
     run_path = Path(run_dir) if run_dir else None
     result: dict = {"device": device, "kernels": native.loaded_libraries(), "rank0_losses": [], "expected": expected, "match": None}
@@ -203,6 +226,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             ces.append((v, k, float(ce.detach())))
             if engine.fold and k == accum - 1:
                 engine.fold_virtual_rank(v)  # batches arrive virtual rank by virtual rank, micro-batches ascending
+        memlog("step %d: after forward/backward" % (step + 1), device)
         grad_norm = engine.reduce_gradients()
         total = 0.0
         for _, _, c in ces:
@@ -231,6 +255,10 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             if hash_due:
                 chained = last_hash
         engine.release_state()
+        memlog("step %d: end" % step, device)
+        phases = engine.phase_report()  # PRETRAIN_CUDA_EVENT_TIMING=1
+        if phases:
+            log.info("step %d phases %s", step, json.dumps({k: round(v, 3) for k, v in phases.items()}))
         log.info("replayed step %d loss %.6f grad_norm %.6f", step, loss_mean, grad_norm)
     result["seconds_per_step"] = (time.time() - t_start) / max(len(loss_rows), 1)
     if torch.cuda.is_available() and device.startswith("cuda"):

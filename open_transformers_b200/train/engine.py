@@ -193,6 +193,7 @@ class TrainEngine:
         # rank there is ONE work buffer plus one partial per replica; ``fold_virtual_rank`` adds a finished virtual rank
         # into its replica's partial in ascending shard order - the same left fold, element by element, that the reduction
         # kernel runs over separate buffers - and a finished partial may be spilled to disk with a digest beside it.
+        self._phase: list | None = [] if os.environ.get("PRETRAIN_CUDA_EVENT_TIMING") == "1" else None
         self.fold = bool(fold_gradients)
         if self.fold and (world != 1 or self.tp != 1):
             raise ValueError("folded gradients are for the single-process replay")
@@ -255,6 +256,36 @@ class TrainEngine:
         for mod in self.model.modules():
             for bname, b in list(mod.named_buffers(recurse=False)):
                 mod._buffers[bname] = b.to(self.device)
+
+    # ------------------------------------------------------------------------------ phase timing
+    def _tick(self, phase: str | None):
+        """Phase timers (PRETRAIN_CUDA_EVENT_TIMING=1): a CUDA event on the current stream (a host clock on the CPU) at
+        every phase boundary; ``phase`` names the interval that ENDS here (None opens one). Nothing is synchronised
+        until ``phase_report`` (reference src/pretrain/train/loop.py:733-743, 875-909, 1036-1051)."""
+        if self._phase is None:
+            return
+        if self.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+        else:
+            import time
+
+            ev = time.perf_counter()
+        self._phase.append((phase, ev))
+
+    def phase_report(self) -> dict:
+        """{"phase_fwd_ms", "phase_bwd_ms", "phase_clip_ms", "phase_opt_ms"} since the last report (one synchronise)."""
+        out: dict[str, float] = {}
+        if not self._phase:
+            return out
+        if self.is_cuda:
+            self._phase[-1][1].synchronize()
+        for (_, a), (name, b) in zip(self._phase[:-1], self._phase[1:]):
+            if name is not None:
+                ms = a.elapsed_time(b) if self.is_cuda else (b - a) * 1e3
+                out["phase_%s_ms" % name] = out.get("phase_%s_ms" % name, 0.0) + ms
+        self._phase = []
+        return out
 
     # ------------------------------------------------------------------------------ state offload
     def _mapped_file(self, key: str, directory: str | None, count: int, dtype) -> np.memmap:
@@ -376,6 +407,12 @@ class TrainEngine:
     def named_master(self):
         return [(n, self.layout.view(self.master, i)) for i, n in enumerate(self.names)]
 
+    def named_weights_for_stats(self):
+        """Complete current weights for telemetry: the fp32 master where this process holds all of it, else the compute
+        copy (with peer-sharded ownership only the owned segments of the master are current; the compute copy is whole)."""
+        src = self.compute if self.peer else self.master
+        return [(n, self.layout.view(src, i)) for i, n in enumerate(self.names)]
+
     def optimizer_state(self):
         lay = self.layout
         return {n: {"step": self.opt_step, "exp_avg": lay.view(self.m1, i), "exp_avg_sq": lay.view(self.m2, i)}
@@ -421,11 +458,14 @@ class TrainEngine:
         if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
             set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
         self.model.train()
+        self._tick(None)
         out = self.model(input_ids)
         z_coeff = self.cfg.model.z_loss.coeff if self.cfg.model.z_loss.enabled else 0.0
         ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
         loss = (ce + z) * (1.0 / accum)
+        self._tick("fwd")
         loss.backward()
+        self._tick("bwd")
         if fresh:
             self._zero_unwritten_slots()
             self._stale[vslot] = False
@@ -490,6 +530,7 @@ class TrainEngine:
         S, R = self.dp_shard, self.dp_replicate
         per = self.V // self.dp_groups
         self._wait_pending_hash()
+        self._tick(None)
         for g, stale in zip(self.grads, self._stale):
             if stale:  # a hosted virtual rank that ran no micro-batch this step contributes zeros, not last step's values
                 g.zero_()
@@ -561,6 +602,7 @@ class TrainEngine:
             check(self.lib.otb_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos), stream_ptr()), "seg_tree")
         else:
             check(self.lib.otb_cpu_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos)), "seg_tree")
+        self._tick("clip")
         seg = self.seg_sos[: self.n_segs].detach().to("cpu").numpy()
         return self._fold_norm(seg)
 
@@ -595,6 +637,7 @@ class TrainEngine:
     def optimizer_step(self, lr: float, clip: float) -> None:
         """Step 4 on the owned segments; pushes the new weights to every rank."""
         self._wait_pending_hash()
+        self._tick(None)
         self.opt_step += 1
         for g in self.param_groups:
             g["lr"] = float(lr)
@@ -615,6 +658,7 @@ class TrainEngine:
         else:
             check(self.lib.otb_cpu_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
                                               _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
+        self._tick("opt")
         self._barrier()  # peers' stores into this rank's weights are complete before the next forward
         K.weight_epoch = (K.weight_epoch or 0) + 1
         refresh = self.cfg.model.qat.scale_refresh_every_n_steps

@@ -250,18 +250,22 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                 t_ckpt = (time.perf_counter() - t0) * 1e3
             wall_ms = (time.perf_counter() - t_step) * 1e3
             result["losses"].append(loss_mean)
+            phases = engine.phase_report()  # empty unless PRETRAIN_CUDA_EVENT_TIMING=1
             if rank == 0:
                 tps = plan.tokens_this_step / (wall_ms / 1e3)
-                metrics.log({"step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_sum / max(n_mb, 1), "lr": lr,
+                metrics.log({**phases, "step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_sum / max(n_mb, 1), "lr": lr,
                              "grad_norm_pre_clip": grad_norm, "clip_coef": clip, "skipped": skipped,
                              "skipped_steps_total": spike.state.skipped_steps, "tokens_per_sec": tps, "tokens_per_sec_per_gpu": tps / world,
                              "mfu": mfu(tps / world, flops_tok), "step_wall_time_ms": wall_ms, "hash_time_ms": t_hash,
                              "ckpt_save_time_ms": t_ckpt, "state_hash": step_hash, "microbatches": M}, step=step)
                 gl = train_cfg.grad_norm_log
                 if gl.every_n_steps > 0 and step % gl.every_n_steps == 0:
-                    pt = np.sqrt(engine.per_tensor_sos)
-                    top = sorted(zip(engine.names, pt.tolist()), key=lambda kv: -kv[1])[: gl.top_k]
-                    _append_jsonl(gn_log, {"step": step, "grad_norm": grad_norm, "top": top})
+                    from ..obs import grad_norm_log as GN
+
+                    stats = gl.weight_stats_every_n_steps > 0 and step % gl.weight_stats_every_n_steps == 0
+                    master = engine.named_weights_for_stats() if stats else None
+                    GN.append(gn_log, GN.build_record(step, consumed, engine.names, engine.per_tensor_sos, gl.top_k,
+                                                      GN.weight_norms(master) if stats else None, GN.qk_gain_max(master) if stats else None))
             if exit_due:
                 log.warning("SIGTERM received: checkpoint written at step %d, exiting", step)
                 raise SystemExit(0)

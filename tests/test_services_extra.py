@@ -199,3 +199,13 @@ def test_muon_hybrid_in_the_engine_updates_hidden_matrices_orthogonally_and_the_
     assert emb and all(torch.equal(m1[n], p1[n]) for n in emb)                  # the aux AdamW is the engine's kernel
     assert float(eng.m2[eng.layout.offsets[eng.muon_params[0]]]) == 0.0
     eng.close()
+
+
+def test_audit_memory_log_is_opt_in(monkeypatch):
+    from open_transformers_b200.cli.audit_replay import memlog
+
+    monkeypatch.delenv("PRETRAIN_AUDIT_MEMLOG", raising=False)
+    assert memlog("x") is None
+    monkeypatch.setenv("PRETRAIN_AUDIT_MEMLOG", "1")
+    rec = memlog("after load")
+    assert rec["at"] == "after load" and rec["rss_peak_gib"] > 0 and rec.get("rss_gib", 1) > 0 and "cuda_peak_gib" not in rec

@@ -130,3 +130,45 @@ def test_stale_gradient_buffers_are_overwritten_not_accumulated_into(tmp_path):
     assert all(torch.equal(a, b) for a, b in zip(clean2, dirty2))
     # unseen vocabulary rows of the embedding table read zero, seen ones do not
     assert float(clean1[0].abs().sum()) > 0 and bool((clean1[0] == 0).any())
+
+
+def test_grad_norm_log_folds_categories_and_blocks_from_per_tensor_norms(tmp_path):
+    import json
+    import math
+
+    from helpers import tiny_cfg
+    from open_transformers_b200.obs import grad_norm_log as GN
+    from open_transformers_b200.train.loop import train
+
+    names = ["embedding.tok_embeddings.weight", "blocks.0.attn.wq.weight", "blocks.0.attn.wq.weight_scale", "blocks.1.ffn.w_down.weight",
+             "blocks.1.norm2.weight", "norm_out.weight", "embedding.output.weight"]
+    assert [GN.category(n) for n in names] == ["embed", "attn", "lsq_scale", "ffn", "norm", "norm", "lm_head"]
+    rec = GN.build_record(3, 99, names, [4.0, 9.0, 1.0, 16.0, 0.0, 1.0, 25.0], top_k=2)
+    assert rec["global"] == round(math.sqrt(56.0), 6) and rec["by_layer"] == {"0": round(math.sqrt(10.0), 6), "1": 4.0}
+    assert rec["by_category"]["norm"] == 1.0 and rec["top"] == [["embedding.output.weight", 5.0], ["blocks.1.ffn.w_down.weight", 4.0]]
+    tmp = str(tmp_path)
+    res = train(tiny_cfg(tmp, ["++train.grad_norm_log.every_n_steps=1", "++train.grad_norm_log.weight_stats_every_n_steps=2"]), device="cpu", data_root=tmp)
+    rows = [json.loads(l) for l in open(res["run_dir"] + "/logs/grad_norms.jsonl")]
+    assert [r["step"] for r in rows] == [1, 2, 3] and all(set(r) >= {"global", "by_category", "by_layer", "top"} for r in rows)
+    metrics = [json.loads(l) for l in open(res["run_dir"] + "/logs/metrics.jsonl")]
+    assert abs(rows[0]["global"] - metrics[0]["grad_norm_pre_clip"]) < 1e-4 * rows[0]["global"]
+    assert "weight_norms" in rows[1] and "weight_norms" not in rows[0] and rows[1]["weight_norms"]["norm_out.weight"] > 0
+
+
+def test_phase_timers_land_in_the_metrics_rows(tmp_path, monkeypatch):
+    import json
+
+    from helpers import tiny_cfg
+    from open_transformers_b200.train.loop import train
+
+    monkeypatch.setenv("PRETRAIN_CUDA_EVENT_TIMING", "1")
+    tmp = str(tmp_path)
+    res = train(tiny_cfg(tmp, []), device="cpu", data_root=tmp)
+    rows = [json.loads(l) for l in open(res["run_dir"] + "/logs/metrics.jsonl")]
+    for r in rows:
+        assert all(r["phase_%s_ms" % k] > 0 for k in ("fwd", "bwd", "clip", "opt"))
+        assert r["phase_fwd_ms"] + r["phase_bwd_ms"] + r["phase_clip_ms"] + r["phase_opt_ms"] <= r["step_wall_time_ms"]
+    monkeypatch.delenv("PRETRAIN_CUDA_EVENT_TIMING")
+    res2 = train(tiny_cfg(tmp + "/b", []), device="cpu", data_root=tmp + "/b")
+    assert res2["hashes"] == res["hashes"]
+    assert "phase_fwd_ms" not in json.loads(open(res2["run_dir"] + "/logs/metrics.jsonl").readline())
