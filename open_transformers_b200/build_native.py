@@ -96,6 +96,27 @@ def build_cpu(force: bool = False, verbose: bool = False) -> Path:
     return _build_lib("otb_cpu", srcs, hdrs, os.environ.get("OTB_CXX") or ("/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"), flags, ["-fopenmp"], force, verbose)
 
 
+SANITIZE_FLAGS = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+
+
+def build_cpu_sanitized(force: bool = False, verbose: bool = False) -> Path:
+    """``_ext/libotb_cpu_san.so``: the CPU twins built with AddressSanitizer and UndefinedBehaviorSanitizer (same
+    floating-point flags, so the bits do not change). Loaded instead of the plain library when OTB_CPU_SANITIZE=1; the
+    Python process then needs the sanitizer runtime first in its link order (LD_PRELOAD of ``sanitizer_runtime()``)."""
+    d = CSRC / "cpu"
+    srcs = sorted(d.glob("*.cpp"))
+    hdrs = sorted(d.glob("*.h")) + sorted((CSRC / "common").glob("*.h"))
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + SANITIZE_FLAGS + ["-I", str(CSRC / "common")]
+    cxx = os.environ.get("OTB_CXX") or ("/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++")
+    return _build_lib("otb_cpu_san", srcs, hdrs, cxx, flags, ["-fopenmp", "-fsanitize=address,undefined"], force, verbose)
+
+
+def sanitizer_runtime() -> str:
+    """Path of the AddressSanitizer runtime of the host compiler (for LD_PRELOAD)."""
+    cc = "/usr/bin/gcc" if Path("/usr/bin/gcc").exists() else "gcc"
+    return subprocess.run([cc, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+
+
 def build(force: bool = False, verbose: bool = False):
     return build_cpu(force, verbose), build_cuda(force, verbose)
 

@@ -34,6 +34,8 @@ def _load(name: str, builder: str) -> ctypes.CDLL:
 
 
 def cpu_lib() -> ctypes.CDLL:
+    if os.environ.get("OTB_CPU_SANITIZE") == "1":  # AddressSanitizer + UBSan build of the same sources (race / bounds checks)
+        return _load("otb_cpu_san", "build_cpu_sanitized")
     return _load("otb_cpu", "build_cpu")
 
 
