@@ -191,8 +191,16 @@ def _all_gather(x: torch.Tensor) -> list[torch.Tensor]:
 
 
 def tp_gather_rows(x_shard: torch.Tensor) -> torch.Tensor:
-    """[m, ...] per rank -> [m * P, ...], rank order."""
-    return torch.cat(_all_gather(x_shard), 0)
+    """[m, ...] per rank -> [m * P, ...], rank order (one collective straight into the result, no concatenation copy)."""
+    import torch.distributed as dist
+
+    x = x_shard.contiguous()
+    out = torch.empty((x.shape[0] * _TP.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if x.dtype == torch.bfloat16:  # byte transport; gloo has no bf16 type
+        dist.all_gather_into_tensor(out.view(torch.uint8), x.view(torch.uint8), group=_TP.group)
+    else:
+        dist.all_gather_into_tensor(out, x, group=_TP.group)
+    return out
 
 
 def tp_gather_cols(y_t: torch.Tensor, slices_by_rank, n_total: int) -> torch.Tensor:
