@@ -1,0 +1,85 @@
+"""The deterministic gradient reduction against a plain restatement of its rule, bit for bit: per replica the shard
+gradients are added in ascending shard order and scaled by 1/S; the replica values are combined by the lower-index-left
+pair tree (strides 1, 2, 4, ...) and scaled by 1/R. Replica counts 1..9 (powers of two and not), element counts that end
+inside a chunk, and the association itself checked symbolically.
+(reference test strategy: tests/distributed/test_deterministic_reduce.py:56-185, tests/test_binary_blocks_tree.py:56-70)"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from open_transformers_b200.ops.native import I, P, cpu_lib
+from open_transformers_b200.train.engine import _ptr_array
+
+CHUNK = 8192
+
+
+def pair_tree(values, add):
+    v = list(values)
+    s = 1
+    while s < len(v):
+        for i in range(0, len(v) - s, 2 * s):
+            v[i] = add(v[i], v[i + s])
+        s *= 2
+    return v[0]
+
+
+def spec(grads, S, R):
+    f = np.float32
+    reps = []
+    for r in range(R):
+        acc = grads[r * S].copy()
+        for s in range(1, S):
+            acc = (acc + grads[r * S + s]).astype(f)
+        reps.append((acc * f(1.0 / S)).astype(f))
+    return (pair_tree(reps, lambda a, b: (a + b).astype(f)) * f(1.0 / R)).astype(f)
+
+
+def native_reduce(grads, S, R, n):
+    starts = np.arange(0, n, CHUNK, dtype=np.int64)
+    lens = np.minimum(CHUNK, n - starts).astype(np.int32)
+    ts = [torch.from_numpy(g) for g in grads]
+    out, sos = torch.empty(n), torch.empty(len(starts))
+    cs, cl = torch.from_numpy(starts), torch.from_numpy(lens)
+    rc = cpu_lib().otb_cpu_grad_reduce(_ptr_array([t.data_ptr() for t in ts]), I(S), I(R), P(cs), P(cl), I(len(starts)), P(out), P(sos))
+    assert rc == 0
+    return out.numpy(), sos.numpy()
+
+
+@pytest.mark.parametrize("n", [1, 7, 257, 4097, 2 * CHUNK + 5])
+@pytest.mark.parametrize("S,R", [(1, 1), (2, 1), (4, 1), (1, 2), (3, 2), (2, 3), (1, 5), (2, 6), (1, 7), (4, 8), (1, 9)])
+def test_reduction_equals_the_stated_rule_bit_for_bit(S, R, n):
+    rng = np.random.default_rng(1000 * S + 10 * R + n)
+    grads = [(rng.standard_normal(n) * 10.0 ** rng.integers(-3, 3)).astype(np.float32) for _ in range(S * R)]
+    got, sos = native_reduce(grads, S, R, n)
+    want = spec(grads, S, R)
+    assert got.tobytes() == want.tobytes()
+    # the squared-norm partials describe the reduced gradient
+    assert abs(float(sos.astype(np.float64).sum()) - float((want.astype(np.float64) ** 2).sum())) <= 1e-5 * float((want.astype(np.float64) ** 2).sum()) + 1e-30
+
+
+def test_order_matters_so_the_rule_is_really_pinned():
+    """a permutation of the shard gradients changes bits somewhere (otherwise the test above would prove nothing)"""
+    rng = np.random.default_rng(5)
+    n, S, R = 4097, 4, 3
+    grads = [(rng.standard_normal(n) * 10.0 ** rng.integers(-3, 3)).astype(np.float32) for _ in range(S * R)]
+    a, _ = native_reduce(grads, S, R, n)
+    b, _ = native_reduce(grads[::-1], S, R, n)
+    assert a.tobytes() != b.tobytes() and np.allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("n,want", [
+    (1, "0"), (2, "(0+1)"), (3, "((0+1)+2)"), (4, "((0+1)+(2+3))"), (5, "(((0+1)+(2+3))+4)"), (6, "(((0+1)+(2+3))+(4+5))"),
+    (7, "(((0+1)+(2+3))+((4+5)+6))"), (8, "(((0+1)+(2+3))+((4+5)+(6+7)))"), (9, "((((0+1)+(2+3))+((4+5)+(6+7)))+8)")])
+def test_pair_tree_parenthesisation(n, want):
+    assert pair_tree([str(i) for i in range(n)], lambda a, b: "(%s+%s)" % (a, b)) == want
+
+
+def test_every_aligned_power_of_two_range_is_a_subtree():
+    """what lets token and K ranges be split over ranks without changing a bit"""
+    whole = pair_tree([str(i) for i in range(16)], lambda a, b: "(%s+%s)" % (a, b))
+    for size in (2, 4, 8):
+        for lo in range(0, 16, size):
+            sub = pair_tree([str(i) for i in range(lo, lo + size)], lambda a, b: "(%s+%s)" % (a, b))
+            assert sub in whole
