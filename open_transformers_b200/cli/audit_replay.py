@@ -132,13 +132,22 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     if not from_init and checkpoint is None:
         raise AuditError("either --checkpoint or --from-init (with --config-name or --descriptor-checkpoint) is required")
 
+    # Two roles of a checkpoint's metadata. The DESCRIPTOR says how the interval was trained (configuration, topology,
+    # kernel environment, re-warm anchor): it comes from --descriptor-checkpoint when given, else from --checkpoint. The
+    # POSITION (step, consumed tokens, chained hash, stream state) always comes from --checkpoint, whose state is loaded.
+    # A resume boundary is audited with the old run's last checkpoint as the state and the resumed run's first checkpoint
+    # as the descriptor. (reference src/pretrain/cli/audit_replay.py:1166-1186)
     meta = None
-    src = checkpoint or descriptor_checkpoint
+    src = descriptor_checkpoint or checkpoint
+    state_meta = Checkpointer.read_meta(checkpoint) if (checkpoint is not None and not from_init) else None
     if src is not None:
         meta = Checkpointer.read_meta(src)
         apply_kernel_env(meta.kernel_env)
         if run_dir is None:
             run_dir = str(Path(src).resolve().parent.parent)
+        if state_meta is not None and descriptor_checkpoint is not None and state_meta.seed != meta.seed:
+            raise AuditError("--descriptor-checkpoint was trained with seed %s, --checkpoint with seed %s: not the same run lineage"
+                             % (meta.seed, state_meta.seed))
     if meta is not None and meta.config_resolved and config_name is None:
         cfg = parse_config_resolved(meta.config_resolved)
     elif config_name is not None:
@@ -194,11 +203,11 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     else:
         ck = Checkpointer(Path(checkpoint).parent.parent)
         side = ck.load(checkpoint, engine)
-        step, consumed, chained = meta.step, meta.consumed_tokens, meta.chained_hash
+        step, consumed, chained = state_meta.step, state_meta.consumed_tokens, state_meta.chained_hash
         stream_state = GlobalStreamState.from_json(side["global_stream"]) if side["global_stream"] else None
         hashers = {v: SH.RunningBatchHasher(side["batch_chains"][v]) for v in range(V)}
         spike.load_state_dict(side["spike_protocol"])
-        rewarm_anchor = meta.rewarm_anchor_tokens
+        rewarm_anchor = meta.rewarm_anchor_tokens if descriptor_checkpoint is not None else state_meta.rewarm_anchor_tokens
     if until_step is None:
         until_step = step + max(cfg.train.ckpt_every_steps, 1)
     if until_step <= step:

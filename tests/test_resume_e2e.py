@@ -1,0 +1,69 @@
+"""Resume through the real train loop: a run that stops and is resumed from its checkpoint writes the hashes of the
+uninterrupted run (weights, moments, optimizer step, data stream position, batch-hash chains, spike state and chained
+hash all survive); a resumed run with a changed recipe is audited across the resume boundary with the old run's
+checkpoint as the state and the new run's first checkpoint as the descriptor.
+(reference test strategy: tests/e2e/test_100m_one_step.py, tests/distributed/test_checkpoint_resume_invariants.py)"""
+import json
+import shutil
+from pathlib import Path
+
+import pytest
+
+from helpers import tiny_cfg
+from open_transformers_b200.cli.audit_replay import AuditError, audit_replay
+from open_transformers_b200.train.checkpoint import Checkpointer
+from open_transformers_b200.train.loop import train
+
+LONG = ["train.total_tokens=1280", "train.ckpt_every_steps=2"]  # 5 optimizer steps of 256 tokens
+
+
+@pytest.fixture(scope="module")
+def runs(tmp_path_factory):
+    tmp = str(tmp_path_factory.mktemp("resume"))
+    whole = train(tiny_cfg(tmp, LONG + ["run.run_id=whole"]), device="cpu", data_root=tmp)
+    first = train(tiny_cfg(tmp, LONG + ["run.run_id=parts"]), device="cpu", data_root=tmp, max_steps=2)
+    return tmp, whole, first
+
+
+def test_resumed_run_writes_the_uninterrupted_hashes(runs):
+    tmp, whole, first = runs
+    assert [s for s, _ in whole["hashes"]] == [1, 2, 3, 4, 5]
+    assert first["hashes"] == whole["hashes"][:2]
+    ck = first["run_dir"] + "/checkpoints/step_000000002"
+    second = train(tiny_cfg(tmp, LONG + ["run.run_id=parts"]), resume_from=ck, device="cpu", data_root=tmp)
+    assert second["hashes"] == whole["hashes"][2:]
+    assert second["losses"] == whole["losses"][2:]
+    meta = Checkpointer.read_meta(first["run_dir"] + "/checkpoints/step_000000004")
+    assert meta.restart_count == 1 and meta.step == 4 and meta.chained_hash == dict(whole["hashes"])[4]
+    rows = [json.loads(l) for l in open(first["run_dir"] + "/logs/state_hashes.jsonl")]
+    assert [r["step"] for r in rows] == [0, 1, 2, 3, 4, 5]
+
+
+def test_resume_with_a_reset_optimizer_forks_the_run(runs, tmp_path):
+    tmp, whole, first = runs
+    src = Path(first["run_dir"]) / "checkpoints" / "step_000000002"
+    dst = tmp_path / "runs" / "fork" / "checkpoints" / "step_000000002"
+    shutil.copytree(src, dst)
+    cfg = tiny_cfg(tmp, LONG + ["run.run_id=fork", "run.output_dir=%s/runs" % tmp_path, "++train.resume_reset_optimizer=true"])
+    forked = train(cfg, resume_from=str(dst), device="cpu", data_root=tmp, max_steps=3)
+    assert forked["hashes"][0][0] == 3 and forked["hashes"][0][1] != dict(whole["hashes"])[3]
+
+
+def test_resume_boundary_is_audited_with_the_new_runs_descriptor(runs, tmp_path):
+    """the interval after a resume was trained by the resumed run's recipe: state from the old checkpoint, descriptor
+    (configuration, topology) from the resumed run's first checkpoint"""
+    tmp, whole, first = runs
+    old = first["run_dir"] + "/checkpoints/step_000000002"
+    new_cfg = tiny_cfg(tmp, LONG + ["run.run_id=fixed", "run.output_dir=%s/runs" % tmp_path, "train.grad_clip=0.05"])
+    fixed = train(new_cfg, resume_from=old, device="cpu", data_root=tmp)
+    new_first = fixed["run_dir"] + "/checkpoints/step_000000004"
+    want = dict(fixed["hashes"])[4]
+    assert want != dict(whole["hashes"])[4]                      # the changed clip really changed the run
+    ok = audit_replay(old, descriptor_checkpoint=new_first, data_root=tmp, until_step=4, expect_hash=new_first + "/state_hash.txt")
+    assert ok["match"] is True and ok["state_hash"] == want
+    stale = audit_replay(old, data_root=tmp, until_step=4, expect_hash=want)   # the old run's own descriptor
+    assert stale["match"] is False and stale["state_hash"] == dict(whole["hashes"])[4]
+    # a descriptor from another lineage (different seed) is refused
+    other = train(tiny_cfg(tmp, LONG + ["run.run_id=other", "run.output_dir=%s/runs" % tmp_path, "run.seed=7"]), device="cpu", data_root=tmp, max_steps=2)
+    with pytest.raises(AuditError):
+        audit_replay(old, descriptor_checkpoint=other["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=4)
