@@ -67,3 +67,61 @@ def test_resume_boundary_is_audited_with_the_new_runs_descriptor(runs, tmp_path)
     other = train(tiny_cfg(tmp, LONG + ["run.run_id=other", "run.output_dir=%s/runs" % tmp_path, "run.seed=7"]), device="cpu", data_root=tmp, max_steps=2)
     with pytest.raises(AuditError):
         audit_replay(old, descriptor_checkpoint=other["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=4)
+
+
+WORKER = """
+import json, os, sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
+from helpers import tiny_cfg
+from open_transformers_b200.train.loop import train
+from open_transformers_b200.parallel.env import shutdown_distributed
+cfg = tiny_cfg({tmp!r}, {extra!r})
+res = train(cfg, resume_from={resume!r}, device="cpu", data_root={tmp!r}, max_steps={max_steps!r})
+if int(os.environ["RANK"]) == 0:
+    json.dump(res["hashes"], open({out!r}, "w"))
+shutdown_distributed()
+"""
+
+
+def _ranks(n, tmp, extra, resume, max_steps, out):
+    import os
+    import subprocess
+    import sys
+
+    from helpers import free_port
+
+    root = str(Path(__file__).resolve().parent.parent)
+    script = Path(out + ".py")
+    script.write_text(WORKER.format(root=root, tmp=tmp, extra=extra, resume=resume, max_steps=max_steps, out=out))
+    port = free_port()
+    procs = [subprocess.Popen([sys.executable, str(script)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              env=dict(os.environ, RANK=str(r), WORLD_SIZE=str(n), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                                       MASTER_PORT=str(port), OMP_NUM_THREADS="2")) for r in range(n)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=300)[0].decode())
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-5000:]
+    return [tuple(x) for x in json.load(open(out))]
+
+
+@pytest.mark.distributed
+def test_a_run_resumes_on_a_different_number_of_processes(runs, tmp_path):
+    """the virtual topology, not the process count, defines the run: two processes write the checkpoint, one process
+    resumes it (and the other way round), and the hashes are those of the uninterrupted single-process run"""
+    tmp, whole, first = runs
+    base = LONG + ["run.output_dir=%s/runs" % tmp_path]
+    two = _ranks(2, tmp, base + ["run.run_id=g2"], None, 2, str(tmp_path / "g2_first.json"))
+    assert two == whole["hashes"][:2]
+    ck = "%s/runs/g2/checkpoints/step_000000002" % tmp_path
+    for f in ("rng.rank_0.pt", "rng.rank_1.pt", "batch_hasher.rank_0.bin", "batch_hasher.rank_1.bin"):
+        assert (Path(ck) / f).exists(), f                          # one file per VIRTUAL rank, whoever hosted it
+    one = train(tiny_cfg(tmp, base + ["run.run_id=g2"]), resume_from=ck, device="cpu", data_root=tmp)
+    assert one["hashes"] == whole["hashes"][2:]
+    # and a single-process checkpoint resumed by two processes
+    back = _ranks(2, tmp, base + ["run.run_id=g1to2"], first["run_dir"] + "/checkpoints/step_000000002", None, str(tmp_path / "g1to2.json"))
+    assert back == whole["hashes"][2:]
