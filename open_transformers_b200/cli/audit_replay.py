@@ -217,6 +217,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     sched = build_schedule(cfg.schedule, tr, cfg.optim)
     loader = build_global_loader(cfg, list(range(V)), V, state=stream_state, consumed_tokens=consumed, start_step=step, data_root=data_root)
     dev = torch.device(device)
+    # PRETRAIN_AUDIT_EMPTY_CACHE_PER_MB=1: hand cached allocator blocks back after every micro-batch (tight GPUs)
+    empty_cache_per_mb = os.environ.get("PRETRAIN_AUDIT_EMPTY_CACHE_PER_MB") == "1" and device.startswith("cuda")
     last_hash = None
     loss_rows = []
     t_start = time.time()
@@ -233,6 +235,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                 hashers[v].update(batch)
             ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum)
             ces.append((v, k, float(ce.detach())))
+            if empty_cache_per_mb:
+                torch.cuda.empty_cache()
             if engine.fold and k == accum - 1:
                 engine.fold_virtual_rank(v)  # batches arrive virtual rank by virtual rank, micro-batches ascending
         memlog("step %d: after forward/backward" % (step + 1), device)

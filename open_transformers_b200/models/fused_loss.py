@@ -24,13 +24,17 @@ def cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
 
 
 def streaming_head_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, z_coeff: float,
-                        panel_rows: int = 2048, grad_scale: float = 1.0):
+                        panel_rows: int = 2048, grad_scale: float = 1.0, slot=None):
     """Vocabulary head + loss in row panels: for each panel of ``panel_rows`` tokens the logits are
     produced, reduced to their loss rows, turned into gradients in place and immediately consumed by
     the two gradient GEMMs, so only one panel of logits exists at a time. dW accumulates over panels
     in ascending panel order with the fp32 accumulate epilogue, i.e. one long ascending-row chain per
     element, equal to the unstreamed weight gradient of the exact family
     (reference src/pretrain/model/streaming_head_loss.py:15-118).
+
+    ``slot``: a gradient slot of the training engine (``ops.autograd.GradSlot``); the weight gradient then continues the
+    chain already in ``slot.buf`` (or starts it, when this is the slot's first writer of the step) exactly as the
+    unstreamed layer's accumulate epilogue does, and no separate dW is allocated.
 
     Returns (ce, z, d_hidden, d_weight[fp32])."""
     h2 = hidden.reshape(-1, hidden.shape[-1]).contiguous()
@@ -40,7 +44,11 @@ def streaming_head_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torc
     ce_rows = torch.empty(n, dtype=torch.float32, device=h2.device)
     lse_rows = torch.empty(n, dtype=torch.float32, device=h2.device)
     dh = torch.empty_like(h2)
-    dW = torch.zeros(weight.shape, dtype=torch.float32, device=h2.device)
+    store_first = False
+    if slot is not None and slot.buf is not None:
+        dW, store_first = slot.buf, slot.take()
+    else:
+        dW = torch.zeros(weight.shape, dtype=torch.float32, device=h2.device)
     for r0 in range(0, n, panel_rows):
         r1 = min(n, r0 + panel_rows)
         logits = K.gemm(h2[r0:r1], weight)
@@ -48,7 +56,7 @@ def streaming_head_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torc
         ce_rows[r0:r1] = ce
         lse_rows[r0:r1] = lse
         K.gemm(logits, weight, b_mn=True, out=dh[r0:r1])
-        K.gemm(logits, h2[r0:r1], a_mn=True, b_mn=True, out=dW, epi=K.EPI_ACC_F32)
+        K.gemm(logits, h2[r0:r1], a_mn=True, b_mn=True, out=dW, epi=K.EPI_STORE_F32 if (store_first and r0 == 0) else K.EPI_ACC_F32)
     ce = K.det_sum(ce_rows, False, inv_n).reshape(())
     z = (K.det_sum(lse_rows, True, inv_n) * z_coeff).reshape(())
     return ce, z, dh.view(hidden.shape), dW

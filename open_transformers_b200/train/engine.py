@@ -38,7 +38,7 @@ import torch
 import torch.distributed as dist
 
 from ..config.schema import RootConfig
-from ..models import build_model, fused_ce_z_loss, init_weights
+from ..models import build_model, fused_ce_z_loss, init_weights, streaming_head_loss
 from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
 from ..ops import functional as K
 from ..ops.autograd import GradSlot, set_tp, wgrad_join
@@ -193,6 +193,10 @@ class TrainEngine:
         # rank there is ONE work buffer plus one partial per replica; ``fold_virtual_rank`` adds a finished virtual rank
         # into its replica's partial in ascending shard order - the same left fold, element by element, that the reduction
         # kernel runs over separate buffers - and a finished partial may be spilled to disk with a digest beside it.
+        # Streaming vocabulary head (exact fp32 family only, where a weight gradient accumulated panel by panel is the
+        # same sequential chain as the unstreamed one): PRETRAIN_AUDIT_STREAM_HEAD=1, or the ``stream_head`` attribute.
+        # (reference src/pretrain/model/streaming_head_loss.py:15-118, used by src/pretrain/cli/audit_replay.py:2312)
+        self.stream_head = os.environ.get("PRETRAIN_AUDIT_STREAM_HEAD") == "1" and not self.mixed and self.tp == 1
         self._phase: list | None = [] if os.environ.get("PRETRAIN_CUDA_EVENT_TIMING") == "1" else None
         self.fold = bool(fold_gradients)
         if self.fold and (world != 1 or self.tp != 1):
@@ -459,12 +463,22 @@ class TrainEngine:
             set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
         self.model.train()
         self._tick(None)
-        out = self.model(input_ids)
         z_coeff = self.cfg.model.z_loss.coeff if self.cfg.model.z_loss.enabled else 0.0
-        ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
-        loss = (ce + z) * (1.0 / accum)
-        self._tick("fwd")
-        loss.backward()
+        if self.stream_head:
+            # vocabulary head and loss in row panels: the [tokens, vocabulary] logits never exist as a whole
+            hidden = self.model.forward_hidden(input_ids)
+            head = self.model.lm_head
+            panel = int(os.environ.get("PRETRAIN_AUDIT_HEAD_CHUNK_ROWS", "2048"))
+            ce, z, dh, _ = streaming_head_loss(hidden.detach(), head._cw() if head._cw() is not None else head.weight.detach(), labels,
+                                               z_coeff, panel, 1.0 / accum, head._slot())
+            self._tick("fwd")
+            hidden.backward(dh)
+        else:
+            out = self.model(input_ids)
+            ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
+            loss = (ce + z) * (1.0 / accum)
+            self._tick("fwd")
+            loss.backward()
         self._tick("bwd")
         if fresh:
             self._zero_unwritten_slots()

@@ -209,3 +209,21 @@ def test_replay_with_offloaded_moments_and_master(trained, tmp_path):
     a = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=2)
     b = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=2, offload_optimizer=True, offload_master=True)
     assert a["match"] is True and b["match"] is True and a["state_hash"] == b["state_hash"]
+
+
+def test_replay_with_the_streaming_vocabulary_head(trained, monkeypatch):
+    """PRETRAIN_AUDIT_STREAM_HEAD=1: head and loss in row panels (here 48 rows of 128, so with a ragged last panel);
+    the fp32 replay keeps every bit"""
+    tmp, cfg, res = trained
+    ck = tmp + "/runs/t/checkpoints/step_000000002"
+    monkeypatch.setenv("PRETRAIN_AUDIT_STREAM_HEAD", "1")
+    monkeypatch.setenv("PRETRAIN_AUDIT_HEAD_CHUNK_ROWS", "48")
+    from open_transformers_b200.train import engine as E
+
+    calls = []
+    real = E.streaming_head_loss
+    monkeypatch.setattr(E, "streaming_head_loss", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    r = audit_replay(ck, data_root=tmp, until_step=3)
+    assert r["match"] is True and calls
+    r0 = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=2)
+    assert r0["match"] is True
