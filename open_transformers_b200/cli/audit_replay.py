@@ -102,6 +102,45 @@ def memlog(tag: str, device: str = "cpu") -> dict | None:
     return rec
 
 
+def memory_plan(n_params: int, V: int, R: int, mixed: bool, activation_bytes: int, free_bytes: int | None, reserve_bytes: int,
+                offload_grads: bool, offload_optimizer: bool) -> dict:
+    """Decide the replay's memory plan before the engine is built. Resident state is 16 bytes per parameter (fp32 master,
+    two moments, reduced gradient) plus 2 for bf16 compute weights, plus one 4-byte gradient buffer per virtual rank.
+    When that, the activations of one micro-batch and the reserve do not fit into ``free_bytes``, folded gradients are
+    switched on first (V buffers -> R + 1), then the moment offload (-8 bytes per parameter). Explicit requests are kept.
+    ``free_bytes`` None (unknown) leaves the requests as they are.
+    (reference src/pretrain/cli/audit_replay.py:508-711: _plan_optimizer_offload / _plan_master_offload / _plan_grad_offload)"""
+    def need(fold: bool, off_opt: bool) -> int:
+        per = 16 + (2 if mixed else 0) - (8 if off_opt else 0)
+        bufs = (R + 1) if fold else V
+        return n_params * (per + 4 * bufs) + activation_bytes + reserve_bytes
+
+    plan = {"offload_grads": bool(offload_grads), "offload_optimizer": bool(offload_optimizer), "auto": [], "free_bytes": free_bytes}
+    if free_bytes is not None:
+        if need(plan["offload_grads"], plan["offload_optimizer"]) > free_bytes and not plan["offload_grads"] and V > R + 1:
+            plan["offload_grads"] = True
+            plan["auto"].append("offload_grads")
+        if need(plan["offload_grads"], plan["offload_optimizer"]) > free_bytes and not plan["offload_optimizer"]:
+            plan["offload_optimizer"] = True
+            plan["auto"].append("offload_optimizer")
+    plan["need_bytes"] = need(plan["offload_grads"], plan["offload_optimizer"])
+    plan["fits"] = free_bytes is None or plan["need_bytes"] <= free_bytes
+    return plan
+
+
+def _free_bytes(device: str) -> int | None:
+    try:
+        if device.startswith("cuda"):
+            import torch
+
+            return int(torch.cuda.mem_get_info()[0])
+        import psutil
+
+        return int(psutil.virtual_memory().available)
+    except Exception:  # noqa: BLE001 - an unknown amount of memory only disables the automatic plan
+        return None
+
+
 def audit_replay(checkpoint: str | None = None, *, config_name: str | None = None, overrides: list[str] | None = None,
                  data_root: str | None = None, device: str = "cpu", cpu_threads: str | None = None, from_init: bool = False,
                  descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
@@ -172,6 +211,21 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     # --offload-grads: one work buffer plus one partial per replica instead of one gradient buffer per virtual rank
     # (each finished virtual rank is folded into its replica's partial, ascending shard order); --fold-spill-dir puts
     # the finished partials on disk with a digest that is checked when they are read back
+    from ..obs.metrics import count_parameters
+
+    m = cfg.model
+    mb_tokens = cfg.train.micro_batch_size * cfg.train.seq_len
+    act = mb_tokens * (m.n_layers * 30 * m.d_model * (2 if cfg.run.mixed_precision else 4) // 2 + 6 * m.vocab_size)
+    plan = memory_plan(count_parameters(m), cfg.run.virtual_dp_size, max(1, cfg.run.dp_replicate_size), bool(cfg.run.mixed_precision), act,
+                       _free_bytes(device), int(float(os.environ.get("PRETRAIN_AUDIT_MEM_RESERVE_GB", "4")) * 2 ** 30),
+                       offload_grads, offload_optimizer)
+    for what in plan["auto"]:
+        log.warning("memory plan: %s AUTO-ENABLED - %.1f GiB free is less than the default plan needs; pass the flag to make it explicit",
+                    what, plan["free_bytes"] / 2 ** 30)
+    if not plan["fits"]:
+        log.warning("memory plan: about %.1f GiB needed, %.1f GiB free - the replay may run out of memory", plan["need_bytes"] / 2 ** 30,
+                    plan["free_bytes"] / 2 ** 30)
+    offload_grads, offload_optimizer = plan["offload_grads"], plan["offload_optimizer"]
     spill = None if (no_fold_spill or not offload_grads) else fold_spill_dir
     # --offload-optimizer / --offload-master: moments / fp32 master weights live in files between steps
     engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None, fold_gradients=offload_grads, fold_spill_dir=spill,

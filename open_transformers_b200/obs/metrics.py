@@ -15,6 +15,16 @@ def transformer_flops_per_token(n_layers: int, d_model: int, seq_len: int, vocab
     return 72.0 * n_layers * d_model ** 2 + 12.0 * n_layers * seq_len * d_model + 6.0 * vocab_size * d_model
 
 
+def count_parameters(m) -> int:
+    """Parameter count of the decoder described by a ``ModelConfig`` (untied embedding and head, GQA projections, fused
+    gate/up, two block norms, final norm; optional embedding norm and QK-norm gains)."""
+    d, hd = m.d_model, m.head_dim
+    attn = d * (m.n_heads * hd) * 2 + d * (m.n_kv_heads * hd) * 2
+    qk = 2 * hd if (getattr(m, "qk_norm", False) and getattr(m, "qk_norm_gain", False)) else 0
+    block = attn + 3 * d * m.ffn_intermediate + 2 * d + qk
+    return 2 * m.vocab_size * d + m.n_layers * block + d + (d if getattr(m, "emb_norm", False) else 0)
+
+
 def mfu(tokens_per_sec_per_gpu: float, flops_per_token: float, peak_flops: float = B200_BF16_DENSE_PEAK) -> float:
     return tokens_per_sec_per_gpu * flops_per_token / peak_flops
 

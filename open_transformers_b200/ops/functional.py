@@ -263,8 +263,8 @@ def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> tuple[torc
     key = (seq_len, head_dim, float(theta))
     if key not in _rope_cache:
         half = head_dim // 2
-        cos = torch.empty((seq_len, half), dtype=torch.float32)
-        sin = torch.empty((seq_len, half), dtype=torch.float32)
+        cos = torch.empty((seq_len, half), dtype=torch.float32, device="cpu")  # explicit: a caller may build the model under
+        sin = torch.empty((seq_len, half), dtype=torch.float32, device="cpu")  # a ``torch.device("meta")`` context
         cpu_lib().otb_cpu_rope_tables(P(cos), P(sin), I(seq_len), I(half), _D(theta))
         _rope_cache[key] = (cos, sin)
     cos, sin = _rope_cache[key]

@@ -51,6 +51,8 @@ def P(t) -> ctypes.c_void_p:
     """Pointer argument from a tensor (None -> NULL)."""
     if t is None:
         return c_void_p(0)
+    if t.device.type == "meta":
+        raise NativeError("a tensor on the meta device has no memory to hand to a native kernel")
     return c_void_p(t.data_ptr())
 
 

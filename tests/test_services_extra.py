@@ -209,3 +209,32 @@ def test_audit_memory_log_is_opt_in(monkeypatch):
     monkeypatch.setenv("PRETRAIN_AUDIT_MEMLOG", "1")
     rec = memlog("after load")
     assert rec["at"] == "after load" and rec["rss_peak_gib"] > 0 and rec.get("rss_gib", 1) > 0 and "cuda_peak_gib" not in rec
+
+
+def test_replay_memory_plan_switches_offloads_on_in_order_and_keeps_requests():
+    from open_transformers_b200.cli.audit_replay import memory_plan
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.models import build_model
+    from open_transformers_b200.obs.metrics import count_parameters
+
+    for name in ("tiny_cpu", "100m_smoke_repop"):
+        cfg = load_config(name)
+        with torch.device("meta"):
+            model = build_model(cfg.model)
+        lsq = sum(p.numel() for n, p in model.named_parameters() if n.endswith("weight_scale"))
+        assert count_parameters(cfg.model) == model.num_parameters() - lsq, name
+    n, G = 1_600_000_000, 2 ** 30
+    act, reserve = 24 * G, 4 * G
+    roomy = memory_plan(n, 8, 1, True, act, 180 * G, reserve, False, False)
+    assert roomy["auto"] == [] and roomy["fits"] and not roomy["offload_grads"]
+    assert abs(roomy["need_bytes"] - (n * (18 + 32) + act + reserve)) == 0
+    tight = memory_plan(n, 8, 1, True, act, 80 * G, reserve, False, False)           # 102.5 GiB by default: fold the gradients
+    assert tight["auto"] == ["offload_grads"] and tight["fits"] and not tight["offload_optimizer"]
+    tighter = memory_plan(n, 8, 1, True, act, 60 * G, reserve, False, False)         # 66.7 GiB folded: moments go too
+    assert tighter["auto"] == ["offload_grads", "offload_optimizer"] and tighter["fits"]
+    hopeless = memory_plan(n, 8, 1, True, act, 20 * G, reserve, False, False)
+    assert not hopeless["fits"] and hopeless["offload_optimizer"] and hopeless["offload_grads"]
+    asked = memory_plan(n, 8, 1, True, act, 180 * G, reserve, True, True)
+    assert asked["auto"] == [] and asked["offload_grads"] and asked["offload_optimizer"]
+    assert memory_plan(n, 8, 1, True, act, None, reserve, False, False)["auto"] == []
+    assert memory_plan(n, 2, 1, True, act, 40 * G, reserve, False, False)["auto"] == ["offload_optimizer"]  # folding 2 -> 2 buffers gains nothing
