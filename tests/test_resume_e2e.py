@@ -125,3 +125,26 @@ def test_a_run_resumes_on_a_different_number_of_processes(runs, tmp_path):
     # and a single-process checkpoint resumed by two processes
     back = _ranks(2, tmp, base + ["run.run_id=g1to2"], first["run_dir"] + "/checkpoints/step_000000002", None, str(tmp_path / "g1to2.json"))
     assert back == whole["hashes"][2:]
+
+
+def test_off_cadence_final_checkpoint_hash_equals_log_and_replay_and_does_not_advance_the_chain(tmp_path):
+    """hash every 2 steps, run of 3 steps: the final checkpoint's hash is computed off the cadence; it is the logged one and
+    the replayed one, and the chain a resumed run continues from is still the step-2 hash
+    (reference tests/e2e/test_final_emergency_ckpt_hash.py:135-178)"""
+    tmp = str(tmp_path)
+    over = ["train.state_hash.every_n_steps=2", "train.ckpt_every_steps=100", "train.total_tokens=1280"]
+    short = train(tiny_cfg(tmp, over + ["run.run_id=short"]), device="cpu", data_root=tmp, max_steps=3)
+    assert [s for s, _ in short["hashes"]] == [2, 3]
+    ck = Path(short["run_dir"]) / "checkpoints" / "step_000000003"
+    final = (ck / "state_hash.txt").read_text().strip()
+    rows = [json.loads(l) for l in open(short["run_dir"] + "/logs/state_hashes.jsonl")]
+    assert rows[-1]["step"] == 3 and rows[-1]["state_hash"] == final == dict(short["hashes"])[3]
+    meta = Checkpointer.read_meta(ck)
+    assert meta.chained_hash == dict(short["hashes"])[2]                                                        # not the off-cadence one
+    r = audit_replay(from_init=True, descriptor_checkpoint=str(ck), data_root=tmp, until_step=3, expect_hash=final)
+    assert r["match"] is True
+    # a longer run with the same cadence, and the short run resumed to the same length, agree on the step-4 hash
+    long_over = over
+    whole = train(tiny_cfg(tmp, long_over + ["run.run_id=long"]), device="cpu", data_root=tmp)
+    resumed = train(tiny_cfg(tmp, long_over + ["run.run_id=short"]), resume_from=str(ck), device="cpu", data_root=tmp)
+    assert dict(resumed["hashes"])[4] == dict(whole["hashes"])[4] and dict(resumed["hashes"])[5] == dict(whole["hashes"])[5]
