@@ -93,3 +93,46 @@ def test_tree_digest_definition():
     assert SH.tree_digest_bytes(b"") == hashlib.blake2b((0).to_bytes(8, "little"), digest_size=32).digest()
     t = torch.arange(6400, dtype=torch.float32)
     assert SH.tree_digest_batch([t, t[:10]]) == [SH.tree_digest_tensor(t), SH.tree_digest_tensor(t[:10])]
+
+
+def test_native_blake2b_is_hashlib_at_every_block_and_leaf_boundary():
+    """the C++ compressor behind the tree digests (and its GPU twin's reference) against hashlib, byte for byte
+    (reference test strategy: tests/test_native_hash_wire_format.py)"""
+    import ctypes
+
+    import numpy as np
+
+    from open_transformers_b200.ops.native import cpu_lib
+
+    lib = cpu_lib()
+    rng = np.random.default_rng(0)
+    for n in (0, 1, 63, 64, 127, 128, 129, 255, 256, 257, 4095, 4096, 4097, 8191, 8192, 8193, 100_003):
+        data = rng.integers(0, 256, n, dtype=np.uint8)
+        for outlen in (32, 64):
+            out = (ctypes.c_ubyte * outlen)()
+            lib.otb_cpu_blake2b(data.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(n), out, ctypes.c_int(outlen))
+            assert bytes(out) == hashlib.blake2b(data.tobytes(), digest_size=outlen).digest(), (n, outlen)
+        level = data.tobytes()
+        while len(level) > 4096:  # leaves of 4096 bytes -> 32 bytes each, until at most one leaf's worth remains
+            level = b"".join(hashlib.blake2b(level[i:i + 4096], digest_size=32).digest() for i in range(0, len(level), 4096))
+        assert SH.tree_digest_bytes(data.tobytes()) == hashlib.blake2b(level + n.to_bytes(8, "little"), digest_size=32).digest(), n
+    big = rng.integers(0, 256, 4096 * 129 + 5, dtype=np.uint8).tobytes()  # 130 leaves -> 4160 bytes -> a second level
+    level = big
+    while len(level) > 4096:
+        level = b"".join(hashlib.blake2b(level[i:i + 4096], digest_size=32).digest() for i in range(0, len(level), 4096))
+    assert SH.tree_digest_bytes(big) == hashlib.blake2b(level + len(big).to_bytes(8, "little"), digest_size=32).digest()
+
+
+def test_tree_and_raw_digest_modes_separate_and_each_detects_one_flipped_bit():
+    g = torch.Generator().manual_seed(1)
+    params = [("a.weight", torch.randn(33, 17, generator=g)), ("b.weight", torch.randn(5000, generator=g))]
+    state = {n: {"step": 3, "exp_avg": torch.randn(p.shape, generator=g), "exp_avg_sq": torch.rand(p.shape, generator=g)} for n, p in params}
+    groups = [{"lr": 1e-3, "betas": [0.9, 0.95], "eps": 1e-8, "weight_decay": 0.1, "amsgrad": False, "params": [0, 1]}]
+    out = {}
+    for td in ("raw", "tree"):
+        base = SH.compute_state_hash(params, state, groups, tensor_digest=td)
+        flipped = [(n, p.clone()) for n, p in params]
+        flipped[1][1].view(torch.int32)[4999] ^= 1
+        assert SH.compute_state_hash(flipped, state, groups, tensor_digest=td) != base
+        out[td] = base
+    assert out["raw"] != out["tree"]
