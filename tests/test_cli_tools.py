@@ -1,0 +1,105 @@
+"""The data-preparation and checkpoint command-line tools, end to end on small inputs: tokenizer training, sharding
+(whole files and a byte segment), manifest merge, shard inspection, token statistics, synthetic sources, the windows of a
+step, document dump to Parquet, checkpoint inspection and fingerprint.
+(reference: src/pretrain/cli/prepare_data.py:300-378, cli/dump_documents.py, cli/inspect_checkpoint.py, cli/hash_ckpt.py)"""
+import json
+
+import pytest
+
+from helpers import tiny_cfg
+
+tokenizers = pytest.importorskip("tokenizers")
+
+
+def _run(main, argv, capsys):
+    capsys.readouterr()
+    rc = main(argv)
+    return rc, capsys.readouterr().out
+
+
+@pytest.fixture(scope="module")
+def corpus(tmp_path_factory):
+    root = tmp_path_factory.mktemp("corpus")
+    words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "12", "345", "6789"]
+    paths = []
+    for f in range(2):
+        p = root / ("part%d.jsonl" % f)
+        with open(p, "w") as fh:
+            for i in range(60):
+                fh.write(json.dumps({"text": " ".join(words[(i * 7 + j * 3 + f) % len(words)] for j in range(5 + i % 9)), "id": i}) + "\n")
+        paths.append(str(p))
+    return root, paths
+
+
+def test_tokenizer_shards_manifests_and_dumps(corpus, capsys):
+    from open_transformers_b200.cli.dump_documents import main as dump_main
+    from open_transformers_b200.cli.prepare_data import main as prep
+    from open_transformers_b200.data.indexed_dataset import IndexedDatasetReader
+    from open_transformers_b200.data.manifest import SourceManifest
+    from open_transformers_b200.data.tokenizer import Tokenizer, compute_hash
+
+    root, paths = corpus
+    tok_path = str(root / "tok.json")
+    rc, out = _run(prep, ["train-tokenizer", *paths, "--output", tok_path, "--vocab-size", "320", "--min-frequency", "1"], capsys)
+    assert rc == 0 and json.loads(out)["hash"] == compute_hash(tok_path)
+    tok = Tokenizer(tok_path)
+    assert tok.decode(tok.encode("alpha 345 kappa")) == "alpha 345 kappa" and tok.eos_id is not None
+
+    rc, out = _run(prep, ["shard", *paths, "--tokenizer", tok_path, "--out-dir", str(root / "src_a"), "--name", "a", "--shard-bytes", "1024"], capsys)
+    info = json.loads(out)
+    assert rc == 0 and info["documents"] == 120 and info["shards"] >= 2
+    man = SourceManifest.load(root / "src_a" / "manifest.yaml")
+    assert man.total_documents == 120 and man.verify(root / "src_a") == [] and man.tokenizer_hash == compute_hash(tok_path)
+    first = IndexedDatasetReader(root / "src_a" / man.shards[0].prefix)
+    assert tok.decode(first.document(0)) == json.loads(open(paths[0]).readline())["text"]
+
+    # a byte segment of one file (what the fan-out workers do): the two halves together hold every document of the file
+    size = (root / "part0.jsonl").stat().st_size
+    docs = 0
+    for k, (lo, hi) in enumerate(((0, size // 2), (size // 2, size))):
+        rc, out = _run(prep, ["shard", paths[0], "--tokenizer", tok_path, "--out-dir", str(root / ("seg%d" % k)), "--name", "seg%d" % k,
+                              "--segment", "%d:%d" % (lo, hi)], capsys)
+        docs += json.loads(out)["documents"]
+    assert docs == 60
+    rc, out = _run(prep, ["merge-manifests", str(root / "seg0" / "manifest.yaml"), str(root / "seg1" / "manifest.yaml"), "--name", "merged",
+                          "--output", str(root / "merged.yaml")], capsys)
+    assert rc == 0 and SourceManifest.load(root / "merged.yaml").total_documents == 60
+
+    rc, out = _run(prep, ["token-stats", str(root / "src_a" / "manifest.yaml"), str(root / "merged.yaml")], capsys)
+    rows = json.loads(out)
+    assert [r["name"] for r in rows] == ["a", "merged"] and abs(sum(r["token_share"] for r in rows) - 1) < 1e-9
+    rc, out = _run(prep, ["inspect", str(root / "src_a" / man.shards[0].prefix), "--tokenizer", tok_path, "--docs", "2"], capsys)
+    assert rc == 0 and "alpha" in out or "beta" in out
+
+    rc, out = _run(dump_main, ["--source-dir", str(root / "src_a"), "--tokenizer", tok_path, "--out-dir", str(root / "dump"), "--workers", "1"], capsys)
+    assert rc == 0 and json.loads(out)["documents"] == 120
+    import pyarrow.parquet as pq
+
+    table = pq.read_table(root / "dump" / (man.shards[0].prefix + ".parquet")).to_pylist()
+    assert table[0]["text"] == json.loads(open(paths[0]).readline())["text"] and table[0]["length"] == first.document_length(0)
+
+
+def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
+    from open_transformers_b200.cli.hash_ckpt import hash_checkpoint, main as hash_main
+    from open_transformers_b200.cli.inspect_checkpoint import main as inspect_main
+    from open_transformers_b200.cli.prepare_data import main as prep
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path)
+    cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=2"])
+    over = ["train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64", "train.micro_batch_size=2",
+            "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=256", "train.global_batch_tokens.late=256"]
+    rc, out = _run(prep, ["replay-step", "--config-name", "tiny_cpu", "--data-root", tmp, "--step", "1", "--max-tokens", "8", *over], capsys)
+    rows = [json.loads(l) for l in out.splitlines()]
+    assert rc == 0 and len(rows) == 4 and all(r["step"] == 1 and len(r["tokens"]) == 8 for r in rows)
+    assert sorted((r["dp_rank"], r["slot"]) for r in rows) == [(0, 0), (0, 1), (1, 0), (1, 1)]
+
+    res = train(cfg, device="cpu", data_root=tmp)
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    rc, out = _run(inspect_main, [ck], capsys)
+    assert rc == 0 and '"step": 2' in out and "complete: True" in out and dict(res["hashes"])[2] in out and "bytes, --full-config" in out
+    rc, out = _run(hash_main, [ck], capsys)
+    assert rc == 0 and out.strip() == hash_checkpoint(ck) and len(out.strip()) == 64
+    rc, weights_only = _run(hash_main, [ck, "--weights-only"], capsys)
+    assert weights_only.strip() != out.strip()
+    assert hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000003") != hash_checkpoint(ck)
