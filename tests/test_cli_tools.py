@@ -103,3 +103,34 @@ def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
     rc, weights_only = _run(hash_main, [ck, "--weights-only"], capsys)
     assert weights_only.strip() != out.strip()
     assert hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000003") != hash_checkpoint(ck)
+
+
+def test_train_command_creates_synthetic_data_resumes_and_refuses_to_overwrite(tmp_path, capsys):
+    """the console entry of training, as a subprocess user would call it: first run with --synthetic-data and --max-steps,
+    then --resume-from, and a second cold start into the same run directory is refused"""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = str(Path(__file__).resolve().parent.parent)
+    tmp = str(tmp_path)
+    over = ["run.output_dir=%s/runs" % tmp, "run.run_id=cli", "model.n_layers=1", "model.d_model=128", "model.n_heads=2", "model.n_kv_heads=2",
+            "model.ffn_intermediate=256", "model.vocab_size=256", "train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64",
+            "train.micro_batch_size=2", "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=256",
+            "train.global_batch_tokens.late=256", "train.total_tokens=1024", "train.ckpt_every_steps=2"]
+    base = [sys.executable, "-m", "open_transformers_b200.cli.train", "--config-name", "tiny_cpu", "--device", "cpu", "--data-root", tmp]
+    env = dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2", WANDB_MODE="disabled")
+    first = subprocess.run(base + ["--synthetic-data", "--max-steps", "2", *over], env=env, capture_output=True, text=True, timeout=300)
+    assert first.returncode == 0, first.stderr[-3000:]
+    out1 = json.loads(first.stdout.strip().splitlines()[-1])
+    assert out1["step"] == 2 and len(out1["hashes"]) == 2
+    again = subprocess.run(base + over, env=env, capture_output=True, text=True, timeout=300)
+    assert again.returncode != 0 and "cold-start overwrite guard" in again.stderr
+    ck = "%s/runs/cli/checkpoints/step_000000002" % tmp
+    second = subprocess.run(base + ["--resume-from", ck, *over], env=env, capture_output=True, text=True, timeout=300)
+    assert second.returncode == 0, second.stderr[-3000:]
+    out2 = json.loads(second.stdout.strip().splitlines()[-1])
+    assert out2["step"] == 4 and [s for s, _ in out2["hashes"]] == [3, 4]
+    rows = [json.loads(l) for l in open("%s/runs/cli/logs/state_hashes.jsonl" % tmp)]
+    assert [r["step"] for r in rows] == [0, 1, 2, 3, 4]
