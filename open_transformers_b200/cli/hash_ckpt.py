@@ -23,8 +23,6 @@ def hash_checkpoint(ckpt_dir: str, include_optimizer: bool = True) -> str:
     template = {}
     for key, m in md.state_dict_metadata.items():
         if isinstance(m, TensorStorageMetadata):
-            node = template
-            parts = key.split(".")
             # keys are flattened "model.<name>" / "optim.state.<name>.<field>": keep them flat
             template[key] = torch.empty(m.size, dtype=m.properties.dtype)
     dcp.load(template, storage_reader=reader, no_dist=True)

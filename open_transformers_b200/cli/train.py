@@ -30,7 +30,10 @@ def main(argv: list[str] | None = None) -> int:
 
         if int(os.environ.get("RANK", "0")) == 0:
             ensure_synthetic_sources(cfg, a.data_root or ".", cfg.train.total_tokens)
+    from ..parallel.env import shutdown_distributed
+
     res = train(cfg, a.resume_from, device=a.device, data_root=a.data_root, max_steps=a.max_steps)
+    shutdown_distributed()  # after a clean run only: a barrier, then the process group is destroyed (a failed rank's peers may be gone)
     print(json.dumps({k: v for k, v in res.items() if k != "losses"}, default=str))
     return 0
 

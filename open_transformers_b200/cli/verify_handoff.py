@@ -63,7 +63,6 @@ def read_batch_digest(ckpt_dir, dp_world_size: int) -> bytes:
 def verify_handoff(checkpoint: str, expect_hash: str | None = None, prev_hash: str | None = None, config_name: str | None = None,
                    device: str = "cpu") -> dict:
     from ..config import load_config, parse_config_resolved
-    from ..train import state_hash as SH
     from ..train.checkpoint import Checkpointer
     from ..train.engine import TrainEngine
 

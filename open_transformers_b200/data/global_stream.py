@@ -18,7 +18,7 @@ from typing import Iterator
 
 import numpy as np
 
-from ..train.batch_schedule import StepPlan, iter_step_plans, owner_rank
+from ..train.batch_schedule import iter_step_plans, owner_rank
 from .manifest import SourceManifest
 from .mix_sampler import SourceWalker
 

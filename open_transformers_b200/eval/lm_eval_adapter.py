@@ -6,8 +6,6 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import functional as K
-
 
 class PretrainLM:
     def __init__(self, model, tokenizer, max_length: int = 4096, device=None):

@@ -21,7 +21,6 @@ from __future__ import annotations
 import dataclasses
 import io
 import json
-import os
 import pickle
 import re
 import shutil
@@ -29,7 +28,6 @@ import time
 from pathlib import Path
 from typing import Any
 
-import numpy as np
 import torch
 
 COMPLETE = "_COMPLETE"

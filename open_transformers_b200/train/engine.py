@@ -29,7 +29,6 @@ identical update to all segments.
 from __future__ import annotations
 
 import ctypes
-import math
 import os
 from dataclasses import dataclass
 
@@ -42,7 +41,7 @@ from ..models import build_model, fused_ce_z_loss, init_weights, streaming_head_
 from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
 from ..ops import functional as K
 from ..ops.autograd import GradSlot, set_tp, wgrad_join
-from ..ops.native import F, I, L, P, check, cpu_lib, cuda_lib, stream_ptr
+from ..ops.native import F, I, P, check, cpu_lib, cuda_lib, stream_ptr
 from ..parallel.flat import FlatLayout, PeerBuffer
 from . import state_hash as SH
 

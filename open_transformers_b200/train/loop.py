@@ -30,7 +30,7 @@ from ..data.loader import build_global_loader, collate
 from ..obs.metrics import MetricsLogger, mfu, transformer_flops_per_token
 from ..obs.wandb_run import WandBRun
 from ..optim.schedules import build_schedule, rewarm_factor
-from ..parallel.env import init_distributed, set_seed, shutdown_distributed
+from ..parallel.env import init_distributed, set_seed
 from ..utils.git import git_sha
 from . import state_hash as SH
 from .checkpoint import CheckpointMeta, Checkpointer, resolved_config_json

@@ -3,7 +3,6 @@
 otherwise a CSV dump)."""
 import argparse
 import json
-import sys
 from pathlib import Path
 
 
