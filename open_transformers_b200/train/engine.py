@@ -148,7 +148,33 @@ class TrainEngine:
         n = lay.total
         # with a tensor-parallel group every process ends up with the whole gradient of its virtual ranks, so each
         # reduces and updates everything itself (no peer-sharded ownership)
-        peer = self.is_cuda and world > 1 and not self.nccl_mode and self.tp == 1
+        # How the gradient buffers of the other processes are reached (OTB_GRAD_TRANSPORT = auto | peer | collective | gather):
+        #   peer       - sharded ownership, plain loads from the other GPUs' buffers (CUDA IPC over NVLink; one machine);
+        #   collective - sharded ownership, every process SENDS each owner its segments (point-to-point messages of the
+        #                process group: NCCL between machines, gloo on CPU ranks), the owner reduces its own copies with
+        #                the same kernel and the updated weights come back by all-gather;
+        #   gather     - every process gathers whole buffers and reduces everything itself (small models, CPU tests,
+        #                tensor-parallel groups).
+        # ``auto``: GPUs of one machine -> peer, GPUs of several machines -> collective, CPU ranks -> gather.
+        transport = os.environ.get("OTB_GRAD_TRANSPORT", "auto")
+        if transport not in ("auto", "peer", "collective", "gather"):
+            raise ValueError("OTB_GRAD_TRANSPORT=%s (auto, peer, collective or gather)" % transport)
+        can_shard = world > 1 and not self.nccl_mode and self.tp == 1
+        if transport == "auto":
+            transport = "gather"
+            if can_shard and self.is_cuda:
+                import socket
+
+                hosts: list = [None] * world
+                dist.all_gather_object(hosts, socket.gethostname(), group=group)
+                transport = "peer" if len(set(hosts)) == 1 else "collective"
+        if not can_shard:
+            transport = "gather"
+        if transport == "peer" and not self.is_cuda:
+            raise ValueError("OTB_GRAD_TRANSPORT=peer needs GPUs (peer loads over NVLink)")
+        peer = transport == "peer"
+        self.collective = transport == "collective"
+        self.sharded = peer or self.collective
         pw, pg = (rank, world) if peer else (0, 1)
 
         def alloc(nbytes, shared):
@@ -217,7 +243,7 @@ class TrainEngine:
         self.seg_first = torch.from_numpy(lay.seg_first).to(dev)
         self.n_chunks = len(lay.chunk_start)
         self.n_segs = len(lay.segments)
-        if peer:
+        if self.sharded:
             ranges = lay.owner_ranges(world)
         else:
             ranges = [(0, self.n_segs)] * world
@@ -225,12 +251,29 @@ class TrainEngine:
         self.chunk_lo = int(lay.seg_first[self.seg_lo])
         self.chunk_hi = int(lay.seg_first[self.seg_hi])
         self.peer = peer
+        if self.collective:
+            # packed layout of every owner's segments (each starting at a multiple of 64 elements) and, for this process,
+            # the chunk table of its own segments inside its packed buffer
+            self._pack_off, self._pack_len = [], []
+            for slo, shi in ranges:
+                offs, off = [], 0
+                for sg in lay.segments[slo:shi]:
+                    offs.append(off)
+                    off += -(-sg.length // 64) * 64
+                self._pack_off.append(offs)
+                self._pack_len.append(max(off, 64))
+            mine = []
+            for sg, off in zip(lay.segments[self.seg_lo:self.seg_hi], self._pack_off[rank]):
+                for c in range(sg.first_chunk, sg.first_chunk + sg.n_chunks):
+                    mine.append(off + int(lay.chunk_start[c]) - sg.start)
+            self._packed_chunk_start = torch.from_numpy(np.asarray(mine, dtype=np.int64)).to(dev)
+            self._owner_ranges = ranges
         # ``optim.name: muon_hybrid`` (experimental, outside the audited path): Muon on the 2-D block weights, the AdamW
         # kernel on everything else through a chunk table without those parameters
         # (reference src/pretrain/optim/muon.py:24-164, gated by config in src/pretrain/optim/registry.py:13-27)
         self.muon_params: list[int] = []
         if cfg.optim.name == "muon_hybrid":
-            if peer or self.tp > 1:
+            if self.sharded or self.tp > 1:
                 raise NotImplementedError("optim.name=muon_hybrid needs every process to hold whole gradients: one GPU, CPU ranks, "
                                           "or run.reduction_mode=nccl")
             from ..optim.muon import is_hidden_matrix
@@ -413,7 +456,7 @@ class TrainEngine:
     def named_weights_for_stats(self):
         """Complete current weights for telemetry: the fp32 master where this process holds all of it, else the compute
         copy (with peer-sharded ownership only the owned segments of the master are current; the compute copy is whole)."""
-        src = self.compute if self.peer else self.master
+        src = self.compute if self.sharded else self.master
         return [(n, self.layout.view(src, i)) for i, n in enumerate(self.names)]
 
     def optimizer_state(self):
@@ -563,6 +606,8 @@ class TrainEngine:
             dist.all_reduce(acc, group=self.group)
             self.grad_red.copy_(acc).mul_(1.0 / self.V)
             check(self._chunk_sos_all(), "chunk_sos")
+        elif self.collective:
+            self._reduce_by_messages(S, R, per)
         elif self.dp_groups > 1 and not self.peer:
             # CPU ranks, and GPU ranks that run tensor-parallel groups: exchange the flat buffers (gloo / NCCL all-gather),
             # then every rank reduces everything identically from its own copies
@@ -604,13 +649,7 @@ class TrainEngine:
             if self.fold:
                 self._keep = None
             if self.peer:
-                parts = [torch.empty_like(self.chunk_sos) for _ in range(self.world)]
-                dist.all_gather(parts, self.chunk_sos, group=self.group)
-                ranges = lay.owner_ranges(self.world)
-                for r, (slo, shi) in enumerate(ranges):
-                    c0, c1 = int(lay.seg_first[slo]), int(lay.seg_first[shi])
-                    if r != self.rank and c1 > c0:
-                        self.chunk_sos[c0:c1].copy_(parts[r][c0:c1])
+                self._share_chunk_sos()
         if self.is_cuda:
             check(self.lib.otb_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos), stream_ptr()), "seg_tree")
         else:
@@ -618,6 +657,78 @@ class TrainEngine:
         self._tick("clip")
         seg = self.seg_sos[: self.n_segs].detach().to("cpu").numpy()
         return self._fold_norm(seg)
+
+    # ----------------------------------------------------------------- collective transport (several machines, CPU ranks)
+    def _pack(self, flat: torch.Tensor, owner: int) -> torch.Tensor:
+        """The segments ``owner`` owns, copied out of a flat buffer into one packed tensor."""
+        slo, shi = self._owner_ranges[owner]
+        out = torch.zeros(self._pack_len[owner], dtype=flat.dtype, device=flat.device)
+        for sg, off in zip(self.layout.segments[slo:shi], self._pack_off[owner]):
+            out[off:off + sg.length].copy_(flat[sg.start:sg.start + sg.length])
+        return out
+
+    def _unpack(self, packed: torch.Tensor, owner: int, flat: torch.Tensor) -> None:
+        slo, shi = self._owner_ranges[owner]
+        for sg, off in zip(self.layout.segments[slo:shi], self._pack_off[owner]):
+            flat[sg.start:sg.start + sg.length].copy_(packed[off:off + sg.length])
+
+    def _exchange(self, sends: list, recvs: list) -> None:
+        """``sends[r]`` goes to process r, ``recvs[p]`` arrives from process p (point-to-point, any backend)."""
+        recvs[self.rank].copy_(sends[self.rank])
+        ops = []
+        for r in range(self.world):
+            if r != self.rank:
+                peer = dist.get_global_rank(self.group, r) if self.group is not None else r
+                ops.append(dist.P2POp(dist.isend, sends[r], peer, group=self.group))
+                ops.append(dist.P2POp(dist.irecv, recvs[r], peer, group=self.group))
+        for req in dist.batch_isend_irecv(ops) if ops else []:
+            req.wait()
+
+    def _reduce_by_messages(self, S: int, R: int, per: int) -> None:
+        """Sharded reduction without peer memory: every process sends each owner that owner's segments of every virtual
+        rank it hosts; the owner then holds all V copies of its segments and runs the reduction kernel over them - the
+        same ascending shard fold and replica tree, on the same values, as the peer-load path."""
+        mine = self._pack_len[self.rank]
+        got: dict[int, torch.Tensor] = {}
+        for j, g in enumerate(self.grads):
+            sends = [self._pack(g, r) for r in range(self.world)]
+            recvs = [torch.empty(mine, dtype=torch.float32, device=self.device) for _ in range(self.world)]
+            self._exchange(sends, recvs)
+            for p_, t in enumerate(recvs):
+                got[p_ * per + j] = t
+        srcs = [got[v].data_ptr() for v in range(self.V)]
+        red = torch.empty(mine, dtype=torch.float32, device=self.device)
+        lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
+        cl, sos = self.chunk_len[lo:], self.chunk_sos[lo:]
+        if self.is_cuda:
+            check(self.lib.otb_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self._packed_chunk_start), P(cl), I(cnt), P(red), P(sos), stream_ptr()),
+                  "grad_reduce")
+        else:
+            check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self._packed_chunk_start), P(cl), I(cnt), P(red), P(sos)), "grad_reduce")
+        self._unpack(red, self.rank, self.grad_red)
+        self._share_chunk_sos()
+
+    def _share_chunk_sos(self) -> None:
+        """Every process learns the squared-norm partials of the chunks the others own."""
+        lay = self.layout
+        parts = [torch.empty_like(self.chunk_sos) for _ in range(self.world)]
+        dist.all_gather(parts, self.chunk_sos, group=self.group)
+        for r, (slo, shi) in enumerate(lay.owner_ranges(self.world)):
+            c0, c1 = int(lay.seg_first[slo]), int(lay.seg_first[shi])
+            if r != self.rank and c1 > c0:
+                self.chunk_sos[c0:c1].copy_(parts[r][c0:c1])
+
+    def _share_updated_weights(self) -> None:
+        """After the update of the owned segments: every process receives the others' new compute weights."""
+        width = max(self._pack_len)
+        mine = torch.zeros(width, dtype=self.compute.dtype, device=self.device)
+        mine[: self._pack_len[self.rank]].copy_(self._pack(self.compute, self.rank))
+        carrier = mine.view(torch.uint8)  # byte transport (gloo has no bf16 type)
+        parts = [torch.empty_like(carrier) for _ in range(self.world)]
+        dist.all_gather(parts, carrier, group=self.group)
+        for r in range(self.world):
+            if r != self.rank:
+                self._unpack(parts[r].view(self.compute.dtype), r, self.compute)
 
     def _chunk_sos_all(self) -> int:
         if self.is_cuda:
@@ -671,6 +782,8 @@ class TrainEngine:
         else:
             check(self.lib.otb_cpu_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
                                               _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
+        if self.collective:
+            self._share_updated_weights()
         self._tick("opt")
         self._barrier()  # peers' stores into this rank's weights are complete before the next forward
         K.weight_epoch = (K.weight_epoch or 0) + 1
@@ -722,14 +835,14 @@ class TrainEngine:
         that do overwrite that state (gradient reduction, optimizer step) wait for the digests first."""
         td = tensor_digest or self.cfg.train.state_hash.tensor_digest
         lay = self.layout
-        if self.peer and td != "tree":
+        if self.sharded and td != "tree":
             raise ValueError("sharded multi-GPU hashing needs train.state_hash.tensor_digest=tree")
         handle = {"td": td, "include_grads": include_grads, "opt_step": self.opt_step, "keys": None, "plan": None, "digests": None}
         if td != "tree":
             return handle
         fields = self._hash_fields(include_grads)
         keys, views = [], []
-        for si in range(self.seg_lo, self.seg_hi) if self.peer else range(self.n_segs):
+        for si in range(self.seg_lo, self.seg_hi) if self.sharded else range(self.n_segs):
             seg = lay.segments[si]
             for tag, flat in fields:
                 keys.append((seg.param, seg.shard, tag))
@@ -767,7 +880,7 @@ class TrainEngine:
             else:
                 digs = handle["digests"]
             seg_digests = dict(zip(handle["keys"], digs))
-            if self.peer:
+            if self.sharded:
                 # every process knows which (parameter, shard, field) digests every other one owns, so only the 32-byte
                 # values travel: one all-gather of a fixed-size byte tensor
                 cache = self.__dict__.setdefault("_hash_keys_by_rank", {})
@@ -835,7 +948,7 @@ class TrainEngine:
 
     def gather_full_state(self) -> None:
         """Make master / moments / reduced gradient complete on every rank (checkpoint, init hash)."""
-        if not self.peer:
+        if not self.sharded:
             return
         self._wait_pending_hash()
         lay = self.layout

@@ -83,7 +83,7 @@ shutdown_distributed()
 """
 
 
-def _ranks(n, tmp, extra, resume, max_steps, out):
+def _ranks(n, tmp, extra, resume, max_steps, out, **env_extra):
     import os
     import subprocess
     import sys
@@ -96,7 +96,7 @@ def _ranks(n, tmp, extra, resume, max_steps, out):
     port = free_port()
     procs = [subprocess.Popen([sys.executable, str(script)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                               env=dict(os.environ, RANK=str(r), WORLD_SIZE=str(n), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
-                                       MASTER_PORT=str(port), OMP_NUM_THREADS="2")) for r in range(n)]
+                                       MASTER_PORT=str(port), OMP_NUM_THREADS="2", **env_extra)) for r in range(n)]
     outs = []
     for p in procs:
         try:
@@ -148,3 +148,16 @@ def test_off_cadence_final_checkpoint_hash_equals_log_and_replay_and_does_not_ad
     whole = train(tiny_cfg(tmp, long_over + ["run.run_id=long"]), device="cpu", data_root=tmp)
     resumed = train(tiny_cfg(tmp, long_over + ["run.run_id=short"]), resume_from=str(ck), device="cpu", data_root=tmp)
     assert dict(resumed["hashes"])[4] == dict(whole["hashes"])[4] and dict(resumed["hashes"])[5] == dict(whole["hashes"])[5]
+
+
+@pytest.mark.distributed
+def test_sharded_ownership_by_messages_through_the_train_loop_and_a_checkpoint(tmp_path):
+    """two processes with sharded ownership over point-to-point messages (the transport of GPUs on several machines): hashes
+    of the single-process run, a checkpoint whose state was completed by broadcasts, and a single-process resume from it"""
+    tmp = str(tmp_path)
+    over = LONG + ["++train.state_hash.tensor_digest=tree"]
+    whole = train(tiny_cfg(tmp, over + ["run.run_id=one"]), device="cpu", data_root=tmp)
+    two = _ranks(2, tmp, over + ["run.run_id=msg"], None, 2, str(tmp_path / "msg.json"), OTB_GRAD_TRANSPORT="collective")
+    assert two == whole["hashes"][:2]
+    rest = train(tiny_cfg(tmp, over + ["run.run_id=msg"]), resume_from="%s/runs/msg/checkpoints/step_000000002" % tmp, device="cpu", data_root=tmp)
+    assert rest["hashes"] == whole["hashes"][2:]

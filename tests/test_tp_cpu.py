@@ -113,3 +113,16 @@ def test_ddp_mode_uses_the_library_all_reduce_and_is_refused_by_the_audit(tmp_pa
         assert abs(n1 - n0) <= 1e-5 * n0
     with pytest.raises(AuditError):
         audit_replay(from_init=True, config_name="tiny_cpu", overrides=["run.parallel=ddp", "run.virtual_dp_size=2"], until_step=1)
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world,bf16", [(2, True), (4, False)])
+def test_sharded_ownership_over_point_to_point_messages(tmp_path, world, bf16):
+    """OTB_GRAD_TRANSPORT=collective (what GPUs on several machines use): every process sends each owner its segments, the
+    owner reduces, updates and digests them, new weights come back by all-gather; four virtual ranks on 2 or 4 processes
+    write the single-process hashes, losses and norms"""
+    env = dict(OTB_TEST_V="4", OTB_TEST_TD="tree")
+    base = _run(1, 1, bf16, tmp_path / "base.json", **env)
+    got = _run(world, 1, bf16, tmp_path / "sharded.json", OTB_GRAD_TRANSPORT="collective", **env)
+    assert [h for _, _, h in got] == [h for _, _, h in base]
+    assert [n for n, _, _ in got] == [n for n, _, _ in base]

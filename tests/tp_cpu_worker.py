@@ -63,7 +63,7 @@ def main():
         device = "cuda:%d" % int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         dist.init_process_group("nccl" if device.startswith("cuda") else "gloo")
-    V, B, T, vocab = 2, 2, int(os.environ.get("OTB_TEST_T", "64")), 256
+    V, B, T, vocab = int(os.environ.get("OTB_TEST_V", "2")), 2, int(os.environ.get("OTB_TEST_T", "64")), 256
     cfg = load_config("tiny_cpu", ["model.n_layers=2", "model.d_model=128", "model.n_heads=2", "model.n_kv_heads=2", "model.ffn_intermediate=256",
                                    "model.vocab_size=%d" % vocab, "train.seq_len=%d" % T, "data.seq_len=%d" % T, "model.max_seq_len_pretrain=%d" % T,
                                    "run.virtual_dp_size=%d" % V, "run.dp_shard_size=%d" % V, "run.dp_replicate_size=1", "run.tp_size=%d" % tp,
@@ -71,6 +71,8 @@ def main():
     eng = TrainEngine(cfg, device, rank, world)
     if os.environ.get("OTB_TEST_HOST_WS") == "1" and tp > 1:
         eng._tp_state.ws = HostWorkspace(eng.tp_rank, eng.tp, eng._tp_group)
+    if os.environ.get("OTB_GRAD_TRANSPORT") == "collective" and world > 1:
+        assert eng.collective and eng.sharded and not eng.peer and 0 < eng.seg_hi - eng.seg_lo < eng.n_segs
     prev, out = None, []
     for step in range(3):
         eng.zero_grads()
@@ -84,7 +86,7 @@ def main():
                 ces.append(float(ce))
         norm = eng.reduce_gradients()
         eng.optimizer_step(3e-4, eng.clip_coefficient(norm, 1.0))
-        prev = eng.sharded_state_hash(prev, None, tensor_digest="raw" if not device.startswith("cuda") else "tree")
+        prev = eng.sharded_state_hash(prev, None, tensor_digest=os.environ.get("OTB_TEST_TD") or ("raw" if not device.startswith("cuda") else "tree"))
         out.append([norm, ces, prev])
     if device.startswith("cuda"):
         from open_transformers_b200.ops.functional import kernel_status
