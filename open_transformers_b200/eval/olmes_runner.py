@@ -1,6 +1,6 @@
 """Duck-typed HuggingFace-style wrapper so OLMES / lm-eval style runners can drive the decoder: ``__call__``
-returns an object with ``.logits``, inputs are right-padded to a multiple of 128 positions (one attention
-tile; the causal mask keeps padding from influencing real positions), plus a multiple-choice scorer
+returns an object with ``.logits``, inputs are right-padded to a multiple of 32 positions (the causal mask keeps
+padding from influencing real positions), plus a multiple-choice scorer that runs all choices of a question in one pass
 (reference src/pretrain/eval/olmes_runner.py:134-151)."""
 from __future__ import annotations
 
@@ -42,11 +42,15 @@ class HFStyleModel:
 def score_multiple_choice(hf_model: HFStyleModel, context: str, choices: list[str], normalise: str = "per_token") -> dict:
     tok = hf_model.tokenizer
     ctx = tok.encode(context) or [tok.eos_id]
+    conts = [tok.encode(ch) for ch in choices]
+    # all choices of a question in ONE forward pass: rows right-padded to the longest (the causal mask keeps the padding
+    # from reaching a real position)
+    width = max(len(ctx) + len(c) for c in conts)
+    ids = torch.tensor([ctx + c + [tok.eos_id] * (width - len(ctx) - len(c)) for c in conts])
+    logits = hf_model(ids).logits
     scores = []
-    for ch in choices:
-        cont = tok.encode(ch)
-        ids = torch.tensor([ctx + cont])
-        lp = torch.log_softmax(hf_model(ids).logits[0, len(ctx) - 1: -1].float(), -1)
-        s = float(lp.gather(-1, torch.tensor(cont, device=lp.device)[:, None]).sum())
+    for i, cont in enumerate(conts):
+        lp = torch.log_softmax(logits[i, len(ctx) - 1: len(ctx) + len(cont) - 1].float(), -1)
+        s = float(lp.gather(-1, torch.tensor(cont, device=lp.device)[:, None]).sum()) if cont else 0.0
         scores.append(s / max(len(cont), 1) if normalise == "per_token" else s)
     return {"scores": scores, "prediction": max(range(len(choices)), key=scores.__getitem__)}

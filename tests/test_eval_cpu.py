@@ -62,6 +62,21 @@ def test_adapter_and_multiple_choice(ckpt):
     assert len(r["scores"]) == 3 and r["prediction"] in (0, 1, 2)
 
 
+def test_batched_scoring_equals_one_request_at_a_time(ckpt):
+    model, _, _ = load_model_from_checkpoint(ckpt[0], "cpu")
+    tok = Tokenizer(ckpt[1])
+    reqs = [("the quick brown", " fox"), ("", " the lazy dog jumps over"), ("the quick brown fox jumps over the lazy dog 17 times and", " again"),
+            ("dog", " times 3"), ("the lazy", " dog 12 times"), ("over the", " lazy")]
+    one = PretrainLM(model, tok, max_length=64).loglikelihood(reqs)
+    many = PretrainLM(model, tok, max_length=64, batch_size=4).loglikelihood(reqs)
+    assert [g for _, g in one] == [g for _, g in many]
+    assert all(abs(a - b) <= 1e-5 * max(1.0, abs(a)) for (a, _), (b, _) in zip(one, many)), (one, many)
+    texts = ["the lazy dog jumps", "the quick brown fox jumps over the lazy dog " * 12]      # the second spans several windows
+    r1 = PretrainLM(model, tok, max_length=64).loglikelihood_rolling(texts)
+    r4 = PretrainLM(model, tok, max_length=64, batch_size=4).loglikelihood_rolling(texts)
+    assert all(abs(a - b) <= 1e-5 * abs(a) for a, b in zip(r1, r4)) and r1[1] < r1[0]
+
+
 def test_olmes_cli_writes_the_summary_the_plot_script_reads(ckpt, tmp_path, capsys):
     task = tmp_path / "toy_task.jsonl"
     task.write_text("\n".join(json.dumps({"context": "the quick brown", "choices": [" fox", " dog"], "answer": i % 2}) for i in range(4)))
@@ -74,3 +89,17 @@ def test_olmes_cli_writes_the_summary_the_plot_script_reads(ckpt, tmp_path, caps
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert (tmp_path / "o.png").exists() or "macro" in r.stdout
+
+
+def test_multiple_choice_scores_in_one_pass_equal_one_choice_at_a_time(ckpt):
+    model, _, _ = load_model_from_checkpoint(ckpt[0], "cpu")
+    tok = Tokenizer(ckpt[1])
+    hf = HFStyleModel(model, tok)
+    ctx, choices = "the quick brown", [" fox", " dog jumps over the lazy", " cat 7"]
+    got = score_multiple_choice(hf, ctx, choices, normalise="sum")["scores"]
+    c = tok.encode(ctx)
+    for ch, g in zip(choices, got):
+        k = tok.encode(ch)
+        lp = torch.log_softmax(hf(torch.tensor([c + k])).logits[0, len(c) - 1: -1].float(), -1)
+        want = float(lp.gather(-1, torch.tensor(k)[:, None]).sum())
+        assert abs(want - g) <= 1e-5 * max(1.0, abs(want))
