@@ -29,6 +29,7 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--max-tokens", type=int, default=1 << 20)
     ap.add_argument("--stride", type=int)
+    ap.add_argument("--batch-windows", type=int, default=8, help="windows of equal length scored per forward pass")
     ap.add_argument("--task-accuracies", help="JSON file {task: accuracy} for the DCLM-CORE aggregate")
     a = ap.parse_args(argv)
     import numpy as np
@@ -41,7 +42,7 @@ def main(argv=None) -> int:
     model, cfg, _ = load_model_from_checkpoint(a.checkpoint, a.device)
     r = IndexedDatasetReader(a.shard_prefix)
     toks = np.concatenate([np.asarray(r.document(i), dtype=np.int64) for i in range(r.num_documents)])[: a.max_tokens]
-    out = {"perplexity": perplexity(model, torch.from_numpy(toks), cfg.train.seq_len, a.stride), "tokens": int(len(toks))}
+    out = {"perplexity": perplexity(model, torch.from_numpy(toks), cfg.train.seq_len, a.stride, a.batch_windows), "tokens": int(len(toks))}
     if a.task_accuracies:
         out["dclm_core"] = dclm_core_score(json.loads(Path(a.task_accuracies).read_text()))
     print(json.dumps(out))

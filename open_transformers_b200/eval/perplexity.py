@@ -11,29 +11,44 @@ from ..ops import functional as K
 
 
 @torch.no_grad()
-def sliding_window_nll(model, tokens: torch.Tensor, seq_len: int, stride: int | None = None, device=None) -> tuple[float, int]:
-    """Sum of negative log-likelihoods (nats) and number of scored tokens for a 1-D token tensor."""
+def sliding_window_nll(model, tokens: torch.Tensor, seq_len: int, stride: int | None = None, device=None,
+                       batch_windows: int = 1) -> tuple[float, int]:
+    """Sum of negative log-likelihoods (nats) and number of scored tokens for a 1-D token tensor. ``batch_windows``
+    windows of equal length share one forward pass; the per-window sums stay on the device until the end (one host
+    synchronisation per call, not per window)."""
     stride = stride or seq_len
     device = device or next(model.parameters()).device
     model.eval()
     n = tokens.numel()
-    total, count, prev_end = 0.0, 0, 0
+    windows, prev_end = [], 0
     for begin in range(0, max(n - 1, 1), stride):
         end = min(begin + seq_len, n - 1)
-        ids = tokens[begin:end].unsqueeze(0).to(device)
-        labels = tokens[begin + 1:end + 1].clone().unsqueeze(0)
-        labels[:, : max(prev_end - begin, 0)] = -100      # already scored by the previous window
-        logits = model(ids).logits
-        l2 = logits.reshape(-1, logits.shape[-1]).contiguous()
-        ce, _ = K.ce_zloss_(l2, labels.reshape(-1).to(device).contiguous(), 0.0, 1.0, write_grad=False)
-        total += float(ce.double().sum())
-        count += int((labels >= 0).sum())
+        windows.append((begin, end, max(prev_end - begin, 0)))   # the first ``skip`` labels were scored by the previous window
         prev_end = end
         if end >= n - 1:
             break
-    return total, count
+    total = torch.zeros((), dtype=torch.float64, device=device)
+    count = 0
+    i = 0
+    while i < len(windows):
+        length = windows[i][1] - windows[i][0]
+        group = [windows[i]]
+        while len(group) < max(1, batch_windows) and i + len(group) < len(windows) and \
+                windows[i + len(group)][1] - windows[i + len(group)][0] == length:
+            group.append(windows[i + len(group)])
+        i += len(group)
+        ids = torch.stack([tokens[b:e] for b, e, _ in group]).to(device)
+        labels = torch.stack([tokens[b + 1:e + 1] for b, e, _ in group]).clone()
+        for row, (_, _, skip) in enumerate(group):
+            labels[row, :skip] = -100
+        logits = model(ids).logits
+        l2 = logits.reshape(-1, logits.shape[-1]).contiguous()
+        ce, _ = K.ce_zloss_(l2, labels.reshape(-1).to(device).contiguous(), 0.0, 1.0, write_grad=False)
+        total += ce.double().sum()
+        count += int((labels >= 0).sum())
+    return float(total), count
 
 
-def perplexity(model, tokens: torch.Tensor, seq_len: int, stride: int | None = None) -> float:
-    nll, n = sliding_window_nll(model, tokens, seq_len, stride)
+def perplexity(model, tokens: torch.Tensor, seq_len: int, stride: int | None = None, batch_windows: int = 1) -> float:
+    nll, n = sliding_window_nll(model, tokens, seq_len, stride, batch_windows=batch_windows)
     return math.exp(nll / max(n, 1))

@@ -41,6 +41,10 @@ def test_perplexity_windows_cover_every_token_once(ckpt):
     nll_b, n_b = sliding_window_nll(model, tokens, 64, 32)   # overlapping windows score each token once as well
     assert n_a == n_b == 199
     assert nll_a > 0 and nll_b > 0
+    for stride in (64, 32):   # several windows per forward pass: same sum
+        nll_1, n_1 = sliding_window_nll(model, tokens, 64, stride)
+        nll_4, n_4 = sliding_window_nll(model, tokens, 64, stride, batch_windows=4)
+        assert n_1 == n_4 == 199 and abs(nll_1 - nll_4) <= 1e-6 * nll_1
     ppl = perplexity(model, tokens, 64)
     assert math.isfinite(ppl) and 50 < ppl < 5000            # an untrained 512-way model sits near the vocabulary size
 
