@@ -137,8 +137,15 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             (run_dir / "checkpoints" / "state_hash_init.txt").write_text(init_hash + "\n")
             _append_jsonl(hash_log, {"step": 0, "kind": "init", "consumed_tokens": 0, "state_hash": init_hash})
 
+    tokenizer_hash = ""
+    if cfg.run.tokenizer_path and Path(cfg.run.tokenizer_path).is_file():
+        from ..data.tokenizer import compute_hash
+
+        tokenizer_hash = compute_hash(cfg.run.tokenizer_path)
+
     def make_meta() -> CheckpointMeta:
         return CheckpointMeta(consumed_tokens=consumed, step=step, git_sha=git_sha(), config_resolved=resolved_config_json(cfg),
+                              tokenizer_hash=tokenizer_hash, container_digest=os.environ.get("CONTAINER_DIGEST", ""),
                               restart_count=restart_count, chained_hash=chained, reduction_mode=cfg.run.reduction_mode, dp_world_size=V,
                               dp_replicate=engine.dp_replicate, dp_shard=engine.dp_shard, tensor_digest=sh_cfg.tensor_digest,
                               rewarm_anchor_tokens=rewarm_anchor, seed=cfg.run.seed, torch_version=torch.__version__,
