@@ -34,7 +34,11 @@ def kernel_status(device=None) -> int:
 
 
 def _ld(t: torch.Tensor) -> int:
-    assert t.dim() == 2 and t.stride(1) == 1, "operand must be a 2-D tensor with unit inner stride"
+    """Leading dimension (row pitch in elements) of a 2-D operand. A dimension of size 1 may carry any stride (PyTorch
+    calls such a tensor contiguous whatever it says), so it is ignored."""
+    assert t.dim() == 2 and (t.stride(1) == 1 or t.shape[1] == 1), "operand must be a 2-D tensor with unit inner stride"
+    if t.shape[0] == 1 and t.stride(0) < t.shape[1]:
+        return t.shape[1]
     return t.stride(0)
 
 
