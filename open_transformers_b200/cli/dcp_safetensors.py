@@ -61,14 +61,15 @@ def unpack(in_file: str, out_dir: str) -> dict:
             raise ValueError("%s: not a %s file (pretrain.format=%r)" % (in_file, FORMAT, md.get("pretrain.format")))
         tensors = {k: f.get_tensor(k) for k in f.keys()}
     sidecar = json.loads(md.get("pretrain.sidecar", "{}"))
+    for name in sidecar:  # names come from an untrusted header: checked before anything is written
+        if not isinstance(name, str) or not SIDECAR_ALLOW.match(name):
+            raise ValueError("sidecar entry %r is not an allowed file name" % (name,))
     d = Path(out_dir)
     (d / "dcp").mkdir(parents=True, exist_ok=True)
     nested: dict = {}
     for k, v in tensors.items():
-        node = nested
-        parts = k.split(".")
         # keys were flattened by DCP with "." separators at the TOP levels only: model.<name>, optim.state.<name>.<field>
-        if parts[0] == "model":
+        if k.startswith("model."):
             nested.setdefault("model", {})[k[len("model."):]] = v
         elif k.startswith("optim.state."):
             name, field = k[len("optim.state."):].rsplit(".", 1)
@@ -82,8 +83,6 @@ def unpack(in_file: str, out_dir: str) -> dict:
     dcp.save(nested, storage_writer=dcp.FileSystemWriter(str(d / "dcp"), thread_count=1), no_dist=True)
     written = []
     for name, b64 in sidecar.items():
-        if not SIDECAR_ALLOW.match(name):
-            raise ValueError("sidecar entry %r is not an allowed file name" % name)
         (d / name).write_bytes(base64.b64decode(b64))
         written.append(name)
     (d / COMPLETE).write_text("unpacked\n")

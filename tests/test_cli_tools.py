@@ -134,3 +134,33 @@ def test_train_command_creates_synthetic_data_resumes_and_refuses_to_overwrite(t
     assert out2["step"] == 4 and [s for s, _ in out2["hashes"]] == [3, 4]
     rows = [json.loads(l) for l in open("%s/runs/cli/logs/state_hashes.jsonl" % tmp)]
     assert [r["step"] for r in rows] == [0, 1, 2, 3, 4]
+
+
+def test_safetensors_interchange_refuses_foreign_files_and_path_like_sidecar_names(tmp_path):
+    """the header of an interchange file is untrusted input: a wrong format tag or a sidecar name that is not on the
+    allow-list (anything path-like in particular) is refused before a single file is written"""
+    import torch
+    from safetensors.torch import save_file
+
+    from open_transformers_b200.cli.dcp_safetensors import FORMAT, pack, unpack
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path)
+    res = train(tiny_cfg(tmp, ["train.ckpt_every_steps=2"]), device="cpu", data_root=tmp, max_steps=2)
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    info = pack(ck, str(tmp_path / "ok.safetensors"))
+    assert "meta.json" in info["sidecar_files"] and "batch_hasher.rank_1.bin" in info["sidecar_files"]
+    back = unpack(str(tmp_path / "ok.safetensors"), str(tmp_path / "back" / "checkpoints" / "step_000000002"))
+    assert back["tensors"] == info["tensors"] and (tmp_path / "back" / "checkpoints" / "step_000000002" / "_COMPLETE").exists()
+    t = {"model.w": torch.zeros(2)}
+    save_file(t, str(tmp_path / "foreign.safetensors"), metadata={"pretrain.format": "something/9"})
+    with pytest.raises(ValueError):
+        unpack(str(tmp_path / "foreign.safetensors"), str(tmp_path / "o1"))
+    for bad in ("../escape.txt", "/tmp/abs.txt", "sub/meta.json", "meta.json.bak", "rng.rank_x.pt"):
+        save_file(t, str(tmp_path / "evil.safetensors"), metadata={"pretrain.format": FORMAT, "pretrain.skeleton": "{}",
+                                                                    "pretrain.sidecar": json.dumps({bad: "aGk="})})
+        with pytest.raises(ValueError):
+            unpack(str(tmp_path / "evil.safetensors"), str(tmp_path / "o2"))
+        assert not (tmp_path / "o2").exists() and not (tmp_path / "escape.txt").exists()
+    with pytest.raises(FileNotFoundError):
+        pack(str(tmp_path / "nowhere"), str(tmp_path / "x.safetensors"))
