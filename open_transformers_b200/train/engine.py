@@ -172,6 +172,11 @@ class TrainEngine:
             transport = "gather"
         if transport == "peer" and not self.is_cuda:
             raise ValueError("OTB_GRAD_TRANSPORT=peer needs GPUs (peer loads over NVLink)")
+        self.transport = transport
+        if world > 1 and rank == 0:
+            import logging
+
+            logging.getLogger(__name__).info("gradient transport: %s (%d processes, tensor-parallel groups of %d)", transport, world, self.tp)
         peer = transport == "peer"
         self.collective = transport == "collective"
         self.sharded = peer or self.collective
