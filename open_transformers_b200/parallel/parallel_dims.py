@@ -20,7 +20,7 @@ class ParallelDims:
             raise ValueError("world_size %d not divisible by tp %d" % (self.world_size, self.tp))
         dp_procs = self.world_size // self.tp
         shard = self.dp_shard
-        v = self.virtual_dp or (shard if shard > 0 else dp_procs // self.dp_replicate) * self.dp_replicate
+        v = self.virtual_dp or (shard if shard > 0 else max(1, dp_procs // self.dp_replicate)) * self.dp_replicate
         if shard <= 0:
             shard = v // self.dp_replicate
         if shard * self.dp_replicate != v:

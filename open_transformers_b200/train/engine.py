@@ -39,10 +39,12 @@ import torch.distributed as dist
 from ..config.schema import RootConfig
 from ..models import build_model, fused_ce_z_loss, init_weights, streaming_head_loss
 from ..models.modules.core import refresh_lsq_weight_scales, set_qat_active
+from ..models.precision import PrecisionPolicy
 from ..ops import functional as K
 from ..ops.autograd import GradSlot, set_tp, wgrad_join
 from ..ops.native import F, I, P, check, cpu_lib, cuda_lib, stream_ptr
 from ..parallel.flat import FlatLayout, PeerBuffer
+from ..parallel.parallel_dims import ParallelDims
 from . import state_hash as SH
 
 
@@ -89,25 +91,13 @@ class TrainEngine:
         self.device = torch.device(device)
         self.rank, self.world, self.group = rank, world, group
         run = cfg.run
-        self.dp_replicate = max(1, run.dp_replicate_size)
-        if run.virtual_dp_size > 0:
-            self.V = run.virtual_dp_size
-            self.dp_shard = run.dp_shard_size if run.dp_shard_size > 0 else self.V // self.dp_replicate
-        else:
-            self.dp_shard = run.dp_shard_size if run.dp_shard_size > 0 else max(1, world // self.dp_replicate)
-            self.V = self.dp_shard * self.dp_replicate
-        if self.dp_shard * self.dp_replicate != self.V:
-            raise ValueError("virtual topology mismatch: V=%d != dp_replicate %d x dp_shard %d" % (self.V, self.dp_replicate, self.dp_shard))
-        # tensor parallelism: ``tp`` consecutive processes form a group that works on each micro-batch together; the
-        # ``dp_groups`` groups share the virtual ranks between them
-        self.tp = max(1, int(run.tp_size))
-        if world % self.tp:
-            raise ValueError("world size %d is not a multiple of run.tp_size %d" % (world, self.tp))
-        self.dp_groups, self.dp_rank, self.tp_rank = world // self.tp, rank // self.tp, rank % self.tp
-        if self.V % self.dp_groups:
-            raise ValueError("the %d virtual ranks cannot be split evenly over %d data-parallel groups" % (self.V, self.dp_groups))
-        per = self.V // self.dp_groups
-        self.hosted = list(range(self.dp_rank * per, (self.dp_rank + 1) * per))
+        # virtual topology arithmetic (V = dp_replicate x dp_shard virtual ranks; ``tp`` consecutive processes form a group
+        # that works on each micro-batch together; the ``dp_groups`` groups share the virtual ranks between them)
+        dims = ParallelDims(max(1, run.dp_replicate_size), run.dp_shard_size, world, max(1, int(run.tp_size)), max(0, run.virtual_dp_size))
+        self.dims = dims
+        self.dp_replicate, self.dp_shard, self.V, self.tp = dims.dp_replicate, dims.dp_shard, dims.virtual_dp, dims.tp
+        self.dp_groups, self.dp_rank, self.tp_rank = dims.dp_processes, rank // dims.tp, dims.tp_rank(rank)
+        self.hosted = dims.hosted_virtual_ranks(rank)
         self._tp_state = None
         if self.tp > 1:
             from ..ops.autograd import TpState
@@ -122,7 +112,8 @@ class TrainEngine:
             self._tp_state = TpState(tp_group, self.tp_rank, self.tp)
             self._tp_group = tp_group
         self.mixed = bool(run.mixed_precision)
-        self.compute_dtype = torch.bfloat16 if self.mixed else torch.float32
+        self.precision = PrecisionPolicy.from_run(self.mixed)
+        self.compute_dtype = self.precision.param_dtype
         self.is_cuda = self.device.type == "cuda"
         if self.tp > 1 and run.tp_fused and self.is_cuda and self.mixed:
             if run.activation_checkpoint:

@@ -172,3 +172,18 @@ def test_phase_timers_land_in_the_metrics_rows(tmp_path, monkeypatch):
     res2 = train(tiny_cfg(tmp + "/b", []), device="cpu", data_root=tmp + "/b")
     assert res2["hashes"] == res["hashes"]
     assert "phase_fwd_ms" not in json.loads(open(res2["run_dir"] + "/logs/metrics.jsonl").readline())
+
+
+def test_parallel_dims_arithmetic():
+    from open_transformers_b200.parallel import ParallelDims
+
+    d = ParallelDims(1, 8, 2, 1, 8)                       # 8 virtual ranks (shard 8) on 2 processes
+    assert (d.virtual_dp, d.dp_shard, d.dp_processes) == (8, 8, 2) and d.hosted_virtual_ranks(1) == [4, 5, 6, 7]
+    d = ParallelDims(2, -1, 8, 2, 0)                      # 8 processes, tensor-parallel pairs: 4 data-parallel processes, 2 x 2
+    assert (d.virtual_dp, d.dp_shard, d.dp_processes) == (4, 2, 4) and d.hosted_virtual_ranks(5) == [2] and d.tp_rank(5) == 1
+    assert d.coords(3) == (1, 1)
+    assert ParallelDims(2, -1, 1).virtual_dp == 2         # more replicas than processes: one process hosts both
+    assert ParallelDims(1, -1, 1, 1, 6).dp_shard == 6
+    for bad in ((1, 3, 2, 1, 4), (1, 4, 3, 1, 4), (1, 2, 3, 2, 0), (0, 1, 1)):
+        with pytest.raises(ValueError):
+            ParallelDims(*bad)
