@@ -238,3 +238,47 @@ def test_replay_memory_plan_switches_offloads_on_in_order_and_keeps_requests():
     assert asked["auto"] == [] and asked["offload_grads"] and asked["offload_optimizer"]
     assert memory_plan(n, 8, 1, True, act, None, reserve, False, False)["auto"] == []
     assert memory_plan(n, 2, 1, True, act, 40 * G, reserve, False, False)["auto"] == ["offload_optimizer"]  # folding 2 -> 2 buffers gains nothing
+
+
+def test_standalone_adamw_and_clip_helpers_give_the_engine_bits():
+    """the torch.optim-style AdamW and the plain-tensor norm / clip helpers against the flat-buffer engine, on the same
+    gradients: identical norm, identical updated weights and moments, two steps (bias corrections advance)"""
+    from torch import nn
+
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.optim.adamw import build_adamw, prime_optimizer_state
+    from open_transformers_b200.optim.registry import build_optimizer
+    from open_transformers_b200.train.engine import TrainEngine
+    from open_transformers_b200.train.global_clip import clip_coefficient, deterministic_global_norm
+
+    cfg = load_config("tiny_cpu")
+    eng = TrainEngine(cfg, "cpu")
+    params = [(n, nn.Parameter(p.detach().clone())) for n, p in eng.named_master()]
+    opt = build_optimizer(params, cfg.optim)
+    assert type(opt).__name__ == "DeterministicAdamW" and type(build_adamw(params, cfg.optim)) is type(opt)
+    prime_optimizer_state(opt)
+    assert all(int(opt.state[p]["step"]) == 0 for _, p in params)
+    g = torch.Generator().manual_seed(0)
+    for step in range(2):
+        eng.zero_grads()
+        for v in range(eng.V):
+            ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+            eng.forward_backward(v, ids, torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), 1)
+        norm = eng.reduce_gradients()
+        grads = eng.named_grads()
+        norm2, _ = deterministic_global_norm([(n, grads[n]) for n in eng.names], eng.dp_shard)
+        assert norm2 == norm
+        clip = eng.clip_coefficient(norm, 0.5)
+        assert clip == clip_coefficient(norm, 0.5) and clip < 1.0
+        for n, p in params:
+            p.grad = grads[n].detach().clone()
+        for group in opt.param_groups:
+            group["lr"] = 1e-3
+        opt.step(clip=clip)
+        eng.optimizer_step(1e-3, clip)
+        after = dict(eng.named_master())
+        state = eng.optimizer_state()
+        for n, p in params:
+            assert torch.equal(p.detach(), after[n]), (step, n)
+            assert torch.equal(opt.state[p]["exp_avg"], state[n]["exp_avg"]) and torch.equal(opt.state[p]["exp_avg_sq"], state[n]["exp_avg_sq"]), n
+    eng.close()
