@@ -190,3 +190,30 @@ def test_missing_per_rank_file_and_run_id_disagreement_are_loud(tmp_path):
         Checkpointer(ck.parent.parent).load(str(ck), eng)
     eng.close()
     _assert_same_on_all_ranks("x", "run_id", 1)   # a single process trivially agrees with itself
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("how", ["tcp_store", "file_store"])
+def test_rendezvous_through_a_tcp_store_or_a_file_store(tmp_path, how):
+    """DIST_MASTER_FQDN / DIST_MASTER_STORE_PORT and TORCH_DIST_STORE_FILE replace the env:// variables"""
+    script = tmp_path / "w.py"
+    script.write_text(
+        "import sys, os\n"
+        "sys.path.insert(0, %r)\n"
+        "import torch, torch.distributed as dist\n"
+        "from open_transformers_b200.parallel.env import init_distributed, shutdown_distributed\n"
+        "rank, world, dev = init_distributed('cpu', timeout_s=60)\n"
+        "t = torch.tensor([float(rank + 1)])\n"
+        "dist.all_reduce(t)\n"
+        "assert t.item() == 3.0 and world == 2 and dev.type == 'cpu'\n"
+        "shutdown_distributed()\n"
+        "print('ok', rank)\n" % str(ROOT))
+    env = {k: v for k, v in os.environ.items() if k not in ("MASTER_ADDR", "MASTER_PORT")}
+    if how == "tcp_store":
+        env.update(DIST_MASTER_FQDN="127.0.0.1", DIST_MASTER_STORE_PORT=str(free_port()))
+    else:
+        env.update(TORCH_DIST_STORE_FILE=str(tmp_path / "store"))
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0].decode() for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-3000:]
