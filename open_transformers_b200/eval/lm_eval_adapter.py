@@ -81,7 +81,42 @@ class PretrainLM:
         return out
 
     @torch.no_grad()
+    def _generate_lockstep(self, requests, max_new_tokens: int) -> list[str]:
+        """Greedy decoding of several requests at once: every round runs all unfinished rows in one forward pass (right-
+        padded; each row's next token is read at its own last position) and appends one token per row."""
+        rows = [self.tok.encode(c) or [self.tok.eos_id] for c, _ in requests]
+        new: list[list[int]] = [[] for _ in requests]
+        live = list(range(len(requests)))
+        for _ in range(max_new_tokens):
+            if not live:
+                break
+            logits = self._logits_batch([(rows[i] + new[i])[-self.max_length:] for i in live])
+            still = []
+            for i, lg in zip(live, logits):
+                nxt = int(lg[-1].argmax())
+                if nxt == self.tok.eos_id:
+                    continue
+                new[i].append(nxt)
+                text = self.tok.decode(new[i])
+                if not any(s in text for s in (requests[i][1] or [])):
+                    still.append(i)
+            live = still
+        out = []
+        for i, (_, stops) in enumerate(requests):
+            text = self.tok.decode(new[i])
+            for s in (stops or []):
+                text = text.split(s)[0]
+            out.append(text)
+        return out
+
+    @torch.no_grad()
     def generate_until(self, requests, max_new_tokens: int = 64) -> list[str]:
+        requests = list(requests)
+        if self.batch_size > 1 and len(requests) > 1:
+            out: list[str] = []
+            for b in range(0, len(requests), self.batch_size):
+                out += self._generate_lockstep(requests[b: b + self.batch_size], max_new_tokens)
+            return out
         res = []
         for context, stops in requests:
             ids = self.tok.encode(context) or [self.tok.eos_id]

@@ -95,6 +95,15 @@ def test_olmes_cli_writes_the_summary_the_plot_script_reads(ckpt, tmp_path, caps
     assert (tmp_path / "o.png").exists() or "macro" in r.stdout
 
 
+def test_lockstep_generation_equals_one_request_at_a_time(ckpt):
+    model, _, _ = load_model_from_checkpoint(ckpt[0], "cpu")
+    tok = Tokenizer(ckpt[1])
+    reqs = [("the quick", ["\n"]), ("the lazy dog jumps over the quick brown", None), ("fox", ["zzz"]), ("", None), ("dog 17 times", [" "])]
+    one = PretrainLM(model, tok, max_length=64).generate_until(reqs, max_new_tokens=6)
+    many = PretrainLM(model, tok, max_length=64, batch_size=3).generate_until(reqs, max_new_tokens=6)
+    assert one == many and len(one) == 5
+
+
 def test_multiple_choice_scores_in_one_pass_equal_one_choice_at_a_time(ckpt):
     model, _, _ = load_model_from_checkpoint(ckpt[0], "cpu")
     tok = Tokenizer(ckpt[1])
