@@ -31,7 +31,7 @@ class InitConfig(_Strict):
 
 class ZLossConfig(_Strict):
     enabled: bool = True
-    coeff: float = 1.0e-5
+    coeff: float = Field(1.0e-5, ge=0.0)
 
 
 class ModuleSelection(_Strict):
@@ -45,8 +45,8 @@ class ModuleSelection(_Strict):
 class QATConfig(_Strict):
     enabled: bool = False
     method: Literal["lsq", "absmax"] = "lsq"
-    weight_bits: int = 8
-    act_bits: int = 8
+    weight_bits: int = Field(8, ge=2, le=8)   # the int8 tensor-core path carries any symmetric grid up to 8 bits
+    act_bits: int = Field(8, ge=2, le=8)
     per_channel_w: bool = True
     exempt_first_n_blocks: int = 0
     scale_refresh_every_n_steps: int = 0
@@ -145,17 +145,25 @@ class OptimConfig(_Strict):
     weight_decay: float = 0.1
     fused: bool = True
     no_decay_param_names: list[str] = Field(default_factory=lambda: [".bias", "norm.weight", ".rope_"])
-    peak_lr: float = 3.0e-4
+    peak_lr: float = Field(3.0e-4, gt=0.0)
+
+    @model_validator(mode="after")
+    def _check(self):
+        if not (0.0 <= self.betas[0] < 1.0 and 0.0 <= self.betas[1] < 1.0):
+            raise ValueError("optim.betas must lie in [0, 1), got %s" % (self.betas,))
+        if self.eps <= 0.0 or self.weight_decay < 0.0:
+            raise ValueError("optim.eps must be > 0 and optim.weight_decay >= 0")
+        return self
 
 
 class ScheduleConfig(_Strict):
     name: Literal["cosine", "wsd", "linear_anneal"] = "cosine"
-    warmup_steps: int = 2000
-    min_lr_frac: float = 0.10
-    wsd_decay_start_frac: float = 0.90
-    wsd_decay_to_frac: float = 0.10
-    anneal_start_tokens: int = 0
-    rewarm_tokens: int = 0
+    warmup_steps: int = Field(2000, ge=0)
+    min_lr_frac: float = Field(0.10, ge=0.0, le=1.0)
+    wsd_decay_start_frac: float = Field(0.90, ge=0.0, le=1.0)
+    wsd_decay_to_frac: float = Field(0.10, ge=0.0, le=1.0)
+    anneal_start_tokens: int = Field(0, ge=0)
+    rewarm_tokens: int = Field(0, ge=0)
     rewarm_on_resume: bool = False
 
 
@@ -212,9 +220,9 @@ class GradNormLogConfig(_Strict):
 
 
 class TrainConfig(_Strict):
-    total_tokens: int = 150_000_000_000
-    seq_len: int = 4096
-    micro_batch_size: int = 4
+    total_tokens: int = Field(150_000_000_000, ge=1)
+    seq_len: int = Field(4096, ge=1)
+    micro_batch_size: int = Field(4, ge=1)
     global_batch_tokens: GlobalBatchTokens = Field(default_factory=GlobalBatchTokens)
     warmup_to_main_at_tokens: int = 4_000_000_000
     main_to_late_at_tokens: int = 140_000_000_000
@@ -222,9 +230,9 @@ class TrainConfig(_Strict):
     ckpt_every_steps: int = 0
     resume_reset_optimizer: bool = False
     spike: SpikeConfig = Field(default_factory=SpikeConfig)
-    grad_clip: float = 1.0
-    qk_gain_clamp: float = 0.0
-    qk_freeze_q_gains_until_step: int = 0
+    grad_clip: float = Field(1.0, ge=0.0)   # 0 disables clipping
+    qk_gain_clamp: float = Field(0.0, ge=0.0)
+    qk_freeze_q_gains_until_step: int = Field(0, ge=0)
     state_hash: StateHashConfig = Field(default_factory=StateHashConfig)
     grad_norm_log: GradNormLogConfig = Field(default_factory=GradNormLogConfig)
     dead_tensor_assert_steps: int = 0

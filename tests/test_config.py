@@ -46,6 +46,12 @@ def test_unknown_key_and_validators():
         load_config("tiny_cpu", ["data.seq_len=256"])
     with pytest.raises(Exception):  # halt can never trigger: 4 * 5 > 10
         load_config("tiny_cpu", ["train.spike.halt_window_steps=10"])
+    for bad in (["model.d_model=130"], ["model.n_kv_heads=3"], ["++model.qat.weight_bits=9"], ["++model.qat.act_bits=1"], ["optim.peak_lr=-1"],
+                ["optim.betas=[1.2,0.9]"], ["optim.eps=0"], ["train.micro_batch_size=0"], ["schedule.min_lr_frac=1.5"], ["train.grad_clip=-1"],
+                ["model.z_loss.coeff=-1"], ["train.state_hash.every_n_steps=-1"]):
+        with pytest.raises(Exception):
+            load_config("tiny_cpu", bad)
+    assert load_config("tiny_cpu", ["train.grad_clip=0", "++model.qat.weight_bits=4"]).model.qat.weight_bits == 4
 
 
 def test_resolved_config_round_trip_and_retired_keys():
