@@ -236,7 +236,10 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     memlog("engine built", device)
     V = engine.V
     run_path = Path(run_dir) if run_dir else None
-    result: dict = {"device": device, "kernels": native.loaded_libraries(), "rank0_losses": [], "expected": expected, "match": None}
+    from ..utils.git import run_provenance
+
+    result: dict = {"device": device, "kernels": native.loaded_libraries(), "build": run_provenance(), "rank0_losses": [], "expected": expected,
+                    "match": None}
     step, consumed, chained, stream_state = 0, 0, None, None
     hashers = {v: SH.RunningBatchHasher() for v in range(V)}
     spike = SpikeProtocol.from_config(cfg.train.spike)

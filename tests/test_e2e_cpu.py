@@ -56,6 +56,7 @@ def test_replay_from_init_and_from_checkpoint_match(trained):
     final = res["hashes"][-1][1]
     r = audit_replay(from_init=True, descriptor_checkpoint=res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3)
     assert r["init_match"] is True and r["match"] is True and r["state_hash"] == final
+    assert r["kernels"] == ["otb_cpu"] and len(r["build"]["native_source_digests"]["otb_cpu"]) == 64 and r["build"]["git_sha"]
     r2 = audit_replay(res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3, expect_hash=final)
     assert r2["match"] is True and len(r2["rank0_losses"]) == 1
     bad = audit_replay(res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=3, expect_hash="0" * 64)
