@@ -57,6 +57,7 @@ class CheckpointMeta:
     torch_version: str = ""
     numpy_version: str = ""
     kernel_env: dict = dataclasses.field(default_factory=dict)
+    native_source_digests: dict = dataclasses.field(default_factory=dict)   # sha256 of each native library's sources + flags
     windows_emitted: int = 0
     physical_world_size: int = 1
     mixed_precision: bool = True

@@ -31,7 +31,7 @@ from ..obs.metrics import MetricsLogger, mfu, transformer_flops_per_token
 from ..obs.wandb_run import WandBRun
 from ..optim.schedules import build_schedule, rewarm_factor
 from ..parallel.env import init_distributed, set_seed
-from ..utils.git import git_sha
+from ..utils.git import git_sha, native_source_digests
 from . import state_hash as SH
 from .checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
 from .engine import TrainEngine
@@ -146,6 +146,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
     def make_meta() -> CheckpointMeta:
         return CheckpointMeta(consumed_tokens=consumed, step=step, git_sha=git_sha(), config_resolved=resolved_config_json(cfg),
                               tokenizer_hash=tokenizer_hash, container_digest=os.environ.get("CONTAINER_DIGEST", ""),
+                              native_source_digests=native_source_digests(),
                               restart_count=restart_count, chained_hash=chained, reduction_mode=cfg.run.reduction_mode, dp_world_size=V,
                               dp_replicate=engine.dp_replicate, dp_shard=engine.dp_shard, tensor_digest=sh_cfg.tensor_digest,
                               rewarm_anchor_tokens=rewarm_anchor, seed=cfg.run.seed, torch_version=torch.__version__,
