@@ -141,6 +141,12 @@ def _free_bytes(device: str) -> int | None:
         return None
 
 
+def run_provenance_digests() -> dict:
+    from ..utils.git import native_source_digests
+
+    return native_source_digests()
+
+
 def audit_replay(checkpoint: str | None = None, *, config_name: str | None = None, overrides: list[str] | None = None,
                  data_root: str | None = None, device: str = "cpu", cpu_threads: str | None = None, from_init: bool = False,
                  descriptor_checkpoint: str | None = None, until_step: int | None = None, expect_hash: str | None = None,
@@ -233,6 +239,12 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                          offload_master=offload_master, master_offload_dir=master_offload_dir)
     if engine.master_offload_inert:
         log.warning("--offload-master changes nothing on a GPU: the fp32 master weights stay resident")
+    if meta is not None and meta.native_source_digests:
+        here = run_provenance_digests()
+        differing = sorted(k for k, v in meta.native_source_digests.items() if k in here and here[k] != v)
+        if differing:
+            log.warning("native sources differ from the build that wrote the checkpoint (%s): a mismatch may come from the build, "
+                        "not from the run", ", ".join(differing))
     memlog("engine built", device)
     V = engine.V
     run_path = Path(run_dir) if run_dir else None
