@@ -56,12 +56,26 @@ def _run(cmd):
 
 
 def _build_lib(name: str, srcs, hdrs, compiler: str, flags, link_flags, force: bool, verbose: bool) -> Path:
+    import fcntl
+
     EXT.mkdir(exist_ok=True)
     out = EXT / ("lib%s.so" % name)
     stamp = EXT / ("%s.stamp" % name)
     dig = _digest(list(srcs) + list(hdrs), flags)
     if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
         return out
+    # several ranks may find the library missing at the same moment: one builds, the others wait and then find it built
+    with open(EXT / ("%s.lock" % name), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
+                return out
+            return _compile_and_link(name, srcs, compiler, flags, link_flags, out, stamp, dig, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _compile_and_link(name: str, srcs, compiler: str, flags, link_flags, out: Path, stamp: Path, dig: str, verbose: bool) -> Path:
     objdir = EXT / ("obj_" + name)
     objdir.mkdir(exist_ok=True)
     objs = []
@@ -75,7 +89,9 @@ def _build_lib(name: str, srcs, hdrs, compiler: str, flags, link_flags, force: b
 
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(one, srcs))
-    _run([compiler, "-shared", "-o", str(out), *map(str, objs), *link_flags])
+    tmp = out.with_suffix(".so.tmp")
+    _run([compiler, "-shared", "-o", str(tmp), *map(str, objs), *link_flags])
+    os.replace(tmp, out)  # a reader never sees a half-written library
     stamp.write_text(dig)
     return out
 
