@@ -1,3 +1,4 @@
+import json
 import glob
 import os
 
@@ -63,3 +64,28 @@ def test_resolved_config_round_trip_and_retired_keys():
     d = json.loads(blob)
     d["train"]["clip_algo"] = "per_tensor"  # a key an older checkpoint may carry
     assert parse_config_resolved(d) == cfg
+
+
+def test_describe_lists_every_schema_leaf_and_prints_resolved_recipes(capsys):
+    import yaml
+
+    from open_transformers_b200.config.describe import main, schema_rows
+
+    rows = {k: (kind, default) for k, kind, default in schema_rows()}
+    assert rows["run.tp_size"] == ("int", "1") and rows["model.n_layers"][1] == "(required)" and rows["train.spike.start_step"][0] == "int"
+    cfg = load_config("tiny_cpu")
+
+    def leaves(d, prefix=""):
+        for k, v in d.items():
+            if isinstance(v, dict):
+                yield from leaves(v, prefix + k + ".")
+            else:
+                yield prefix + k
+
+    resolved = set(leaves(json.loads(cfg.model_dump_json())))
+    listed = set(rows)
+    # every scalar of a resolved recipe is a listed key (lists of sources / names are listed as one key)
+    assert {k for k in resolved if not k.startswith("data.sources")} <= listed | {"optim.betas"}, sorted(resolved - listed)[:5]
+    assert main([]) == 0 and "train.grad_clip" in capsys.readouterr().out
+    assert main(["--config-name", "tiny_cpu", "train.grad_clip=0.25"]) == 0
+    assert yaml.safe_load(capsys.readouterr().out)["train"]["grad_clip"] == 0.25
