@@ -101,3 +101,36 @@ def test_every_document_appears_once_per_epoch(tmp_path):
     ids = [int(r[0]) for r in np.split(flat, np.where(flat == 0)[0] + 1)[:-1]]
     first, second = ids[:30], ids[30:60]
     assert sorted(first) == list(range(100, 130)) and sorted(second) == list(range(100, 130)) and first != second
+
+
+def test_token_share_weights_become_document_probabilities(tmp_path):
+    """``weights_are_token_shares``: a source with documents ten times longer gets a tenth of the document draws per
+    unit of weight, so that the TOKEN shares of the stream follow the weights"""
+    import types
+
+    from open_transformers_b200.data.loader import resolve_sources
+
+    clear_caches()
+    rng = np.random.default_rng(0)
+    mans = []
+    for name, tok, length in (("short", 5, 8), ("long", 6, 80)):
+        d = tmp_path / name
+        d.mkdir()
+        with IndexedDatasetWriter(d / "shard_00000", np.uint32) as w:
+            for _ in range(300):
+                w.add_document(np.full(length, tok, dtype=np.uint32))
+        man = SourceManifest(name=name, tokenizer_hash="none", dtype="uint32",
+                             shards=[ShardInfo("shard_00000", 300, 300 * length, blake2b_file(d / "shard_00000.bin"), blake2b_file(d / "shard_00000.idx"))])
+        man.save(d / "manifest.yaml")
+        mans.append(man)
+
+    def data_cfg(token_shares):
+        srcs = [types.SimpleNamespace(name="short", path="short", weight=1.0), types.SimpleNamespace(name="long", path="long", weight=1.0)]
+        return types.SimpleNamespace(sources=srcs, weights_are_token_shares=token_shares, normalised_weights=lambda: [0.5, 0.5])
+
+    _, dirs, w_doc = resolve_sources(data_cfg(False), str(tmp_path))
+    _, _, w_tok = resolve_sources(data_cfg(True), str(tmp_path))
+    assert w_doc == [0.5, 0.5] and abs(w_tok[0] - 10 / 11) < 1e-12 and abs(sum(w_tok) - 1) < 1e-12
+    flat = np.concatenate(_take(GlobalStream(mans, dirs, w_tok, 64, seed=3, eos_id=0), 400))
+    share_short = float((flat == 5).sum()) / float(((flat == 5) | (flat == 6)).sum())
+    assert 0.42 < share_short < 0.58                      # equal TOKEN shares, as the weights say
