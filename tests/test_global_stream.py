@@ -134,3 +134,44 @@ def test_token_share_weights_become_document_probabilities(tmp_path):
     flat = np.concatenate(_take(GlobalStream(mans, dirs, w_tok, 64, seed=3, eos_id=0), 400))
     share_short = float((flat == 5).sum()) / float(((flat == 5) | (flat == 6)).sum())
     assert 0.42 < share_short < 0.58                      # equal TOKEN shares, as the weights say
+
+
+def test_legacy_per_rank_sampler_is_strided_resumable_and_topology_dependent(tmp_path):
+    """the legacy sampler (DDP runs): ranks walk disjoint strides of each source's permutation, the state round-trips, and
+    - unlike the canonical stream - the windows depend on the world size"""
+    from open_transformers_b200.data.mix_sampler import MixSampler, MixSamplerState
+
+    clear_caches()
+    man, d = _source(tmp_path, "a", 5, 40)
+    two = [_take(MixSampler([man], [d], [1.0], 16, seed=4, rank=r, world_size=2, eos_id=3), 6) for r in range(2)]
+    again = _take(MixSampler([man], [d], [1.0], 16, seed=4, rank=1, world_size=2, eos_id=3), 6)
+    assert all(np.array_equal(a, b) for a, b in zip(two[1], again))
+    assert not all(np.array_equal(a, b) for a, b in zip(two[0], two[1]))
+    one = _take(MixSampler([man], [d], [1.0], 16, seed=4, rank=0, world_size=1, eos_id=3), 6)
+    assert not all(np.array_equal(a, b) for a, b in zip(one, two[0]))
+    s = MixSampler([man], [d], [1.0], 16, seed=4, rank=0, world_size=2, eos_id=3)
+    it = iter(s)
+    for _ in range(3):
+        next(it)
+    st = MixSamplerState(**json.loads(json.dumps(s.state().__dict__)))
+    rest = _take(MixSampler([man], [d], [1.0], 16, seed=4, rank=0, world_size=2, eos_id=3, state=st), 3)
+    assert all(np.array_equal(a, b) for a, b in zip(rest, two[0][3:]))
+
+
+def test_text_iterators_read_jsonl_parquet_and_byte_segments(tmp_path):
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from open_transformers_b200.data.prepare import iter_jsonl, iter_jsonl_segment, iter_parquet, iter_texts
+
+    texts = ["doc %d %s" % (i, "x" * (i % 7)) for i in range(50)]
+    j = tmp_path / "a.jsonl"
+    j.write_text("\n".join(json.dumps({"text": t, "other": i}) for i, t in enumerate(texts)) + "\n")
+    p = tmp_path / "b.parquet"
+    pq.write_table(pa.table({"text": texts[::-1], "n": list(range(50))}), p)
+    assert list(iter_jsonl(j)) == texts and list(iter_parquet(p, batch_size=7)) == texts[::-1]
+    assert list(iter_texts([j, p])) == texts + texts[::-1]
+    size = j.stat().st_size
+    for cuts in ([0, size], [0, 1, size], [0, size // 3, size // 2, size - 1, size], [0, 17, 18, 19, size]):
+        got = [t for a, b in zip(cuts[:-1], cuts[1:]) for t in iter_jsonl_segment(j, a, b)]
+        assert got == texts, cuts                    # every line belongs to exactly one segment, wherever the cuts fall
