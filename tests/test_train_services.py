@@ -187,3 +187,52 @@ def test_parallel_dims_arithmetic():
     for bad in ((1, 3, 2, 1, 4), (1, 4, 3, 1, 4), (1, 2, 3, 2, 0), (0, 1, 1)):
         with pytest.raises(ValueError):
             ParallelDims(*bad)
+
+
+def test_metrics_logger_flushes_on_cadence_and_mirrors_to_the_tracker(tmp_path, monkeypatch):
+    import json
+    import sys
+    import types
+
+    from open_transformers_b200.obs.metrics import MetricsLogger, mfu, time_section, transformer_flops_per_token
+    from open_transformers_b200.obs.wandb_run import WandBRun
+
+    seen = []
+    tracker = types.SimpleNamespace(log=lambda row, step=None: seen.append((step, row["loss"])))
+    path = tmp_path / "logs" / "m.jsonl"
+    lg = MetricsLogger(path, tracker, flush_every=3)
+    for i in range(4):
+        lg.log({"loss": float(i), "b": "x"}, step=i)
+    assert len(path.read_text().splitlines()) == 3                 # flushed after the third row, the fourth still buffered
+    lg.close()
+    rows = [json.loads(l) for l in path.read_text().splitlines()]
+    assert [r["loss"] for r in rows] == [0.0, 1.0, 2.0, 3.0] and seen == [(0, 0.0), (1, 1.0), (2, 2.0), (3, 3.0)]
+    off = MetricsLogger(tmp_path / "no" / "m.jsonl", enabled=False)
+    off.log({"loss": 1.0})
+    off.close()
+    assert not (tmp_path / "no").exists()
+    sink = {}
+    with time_section(sink, "a"):
+        pass
+    with time_section(sink, "a"):
+        pass
+    assert sink["a"] >= 0.0 and len(sink) == 1
+    f = transformer_flops_per_token(24, 2048, 4096, 128256)
+    assert f == 72 * 24 * 2048 ** 2 + 12 * 24 * 4096 * 2048 + 6 * 128256 * 2048 and abs(mfu(1e5, f, 2.25e15) - 1e5 * f / 2.25e15) < 1e-12
+    # the tracker wrapper is a null object without credentials, with WANDB_MODE=disabled, and off rank 0
+    monkeypatch.delenv("WANDB_API_KEY", raising=False)
+    for kw, mode in (({}, ""), ({}, "disabled"), ({"enabled": False}, "offline")):
+        monkeypatch.setenv("WANDB_MODE", mode)
+        w = WandBRun("p", "r", **kw)
+        w.log({"loss": 1.0}, step=1)
+        w.finish()
+        assert w._run is None
+    # with a tracker module present and offline mode it initialises and forwards
+    calls = []
+    fake_run = types.SimpleNamespace(log=lambda row, step=None: calls.append(("log", step)), finish=lambda: calls.append(("finish", None)))
+    monkeypatch.setitem(sys.modules, "wandb", types.SimpleNamespace(init=lambda **kw: (calls.append(("init", kw["project"])), fake_run)[1]))
+    monkeypatch.setenv("WANDB_MODE", "offline")
+    w = WandBRun("proj", "run1")
+    w.log({"loss": 2.0}, step=5)
+    w.finish()
+    assert calls == [("init", "proj"), ("log", 5), ("finish", None)]
