@@ -55,6 +55,8 @@ class MetricsLogger:
             self._f.flush()
             self._f.close()
             self._f = None
+        if self.wandb is not None and hasattr(self.wandb, "finish"):
+            self.wandb.finish()
 
 
 @contextlib.contextmanager
