@@ -449,6 +449,14 @@ class TrainEngine:
     def named_master(self):
         return [(n, self.layout.view(self.master, i)) for i, n in enumerate(self.names)]
 
+    def resident_bytes(self) -> dict:
+        """Bytes of training state this process holds, by kind (activations and collective staging excluded)."""
+        n = self.layout.total
+        out = {"master": 4 * n, "moments": 0 if (self._off_opt and self._m1 is None) else 8 * n, "reduced_gradient": 4 * n,
+               "gradient_buffers": 4 * n * len(self.grads), "compute_weights": 2 * n if self.mixed else 0}
+        out["total"] = sum(out.values())
+        return out
+
     def named_weights_for_stats(self):
         """Complete current weights for telemetry: the fp32 master where this process holds all of it, else the compute
         copy (with peer-sharded ownership only the owned segments of the master are current; the compute copy is whole)."""

@@ -98,6 +98,10 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
 
     engine = TrainEngine(cfg, dev, rank, world)
     V, hosted = engine.V, engine.hosted
+    if rank == 0:
+        rb = engine.resident_bytes()
+        log.info("training state per process: %.2f GiB (%s); %d virtual ranks hosted; gradient transport %s", rb["total"] / 2 ** 30,
+                 ", ".join("%s %.2f" % (k, v / 2 ** 30) for k, v in rb.items() if k != "total" and v), len(hosted), engine.transport)
     train_cfg = cfg.train
     sched = build_schedule(cfg.schedule, train_cfg, cfg.optim)
     spike = SpikeProtocol.from_config(train_cfg.spike)
