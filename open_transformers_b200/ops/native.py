@@ -117,11 +117,26 @@ def mark(what: str) -> None:
         _timing.append((what, e))
 
 
+def explain(rc: int) -> str:
+    """What a non-zero return code of a native entry point means."""
+    if rc == -2:
+        return "unsupported shape or alignment (operand rows and leading dimensions must be multiples of 16 bytes, sizes within the kernel's limits)"
+    if rc == -3:
+        return "unknown mode / epilogue / dtype selector"
+    if rc == -4:
+        return "work-space allocation or capacity limit of the entry point"
+    if rc >= 1000:
+        return "CUDA driver error %d while encoding a tensor map or configuring the launch" % (rc - 1000)
+    if rc > 0:
+        return "CUDA runtime error %d at launch" % rc
+    return "argument rejected"
+
+
 def check(rc: int, what: str) -> None:
     global launch_count
     launch_count += 1
     if rc != 0:
-        raise NativeError("%s failed with code %d" % (what, rc))
+        raise NativeError("%s failed with code %d: %s" % (what, rc, explain(rc)))
     if _timing is not None:
         mark(what)
 
