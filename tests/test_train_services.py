@@ -236,3 +236,42 @@ def test_metrics_logger_flushes_on_cadence_and_mirrors_to_the_tracker(tmp_path, 
     w.log({"loss": 2.0}, step=5)
     w.finish()
     assert calls == [("init", "proj"), ("log", 5), ("finish", None)]
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_activation_checkpointing_changes_no_bit(bf16, monkeypatch):
+    """recompute runs the same deterministic kernels: every block, every other block and no checkpointing give one hash;
+    and it really recomputes (the block forward runs again during the backward pass)"""
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.ops import functional as K
+    from open_transformers_b200.train.engine import TrainEngine
+
+    def run(extra):
+        cfg = load_config("tiny_cpu", ["model.n_layers=3", "run.mixed_precision=%s" % ("true" if bf16 else "false"), *extra])
+        eng = TrainEngine(cfg, "cpu")
+        g = torch.Generator().manual_seed(0)
+        calls = {"n": 0}
+        orig = K.rmsnorm_fwd
+
+        def counted(*a, **k):
+            calls["n"] += 1
+            return orig(*a, **k)
+
+        monkeypatch.setattr(K, "rmsnorm_fwd", counted)      # two norms per block and the final one, per forward pass
+        eng.zero_grads()
+        for v in range(eng.V):
+            ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+            eng.forward_backward(v, ids, torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), 1)
+        norm = eng.reduce_gradients()
+        eng.optimizer_step(1e-3, 1.0)
+        h = eng.sharded_state_hash(None, None)
+        monkeypatch.setattr(K, "rmsnorm_fwd", orig)
+        eng.close()
+        return h, norm, calls["n"]
+
+    plain = run(["run.activation_checkpoint=false"])
+    every = run(["run.activation_checkpoint=true"])
+    other = run(["run.activation_checkpoint=true", "run.ac_every_other_block=true"])
+    assert plain[:2] == every[:2] == other[:2]
+    per_pass = 2 * 3 + 1
+    assert plain[2] == 2 * per_pass and every[2] == 2 * (per_pass + 6) and other[2] == 2 * (per_pass + 4)   # blocks 0 and 2 of 3 recomputed
