@@ -70,3 +70,33 @@ def test_learned_quantisation_steps_follow_the_initialised_weights():
     lin = m.blocks[0].ffn.w_down
     want = (lin.weight.detach().abs().mean(1) * (2.0 / math.sqrt(lin.qmax_w))).clamp_min(1e-6)
     assert torch.allclose(lin.weight_scale.detach(), want, rtol=1e-6) and float(lin.weight_scale.detach().min()) > 0
+
+
+def test_yarn_rope_keeps_high_frequencies_and_stretches_low_ones():
+    """NTK-by-parts tables: the fastest-rotating pairs equal the plain tables, the slowest rotate ``factor`` times slower,
+    and a model that selects the variant runs a training step"""
+    import numpy as np
+
+    from open_transformers_b200.models.modules.core import RoPE, RoPEYarn
+    from open_transformers_b200.train.engine import TrainEngine
+
+    plain = RoPE(64, 256, 10000.0)
+    yarn = RoPEYarn(64, 256, 10000.0, factor=4.0, original_max=64)
+    pc, ps = plain(256)
+    yc, ys = yarn(256)
+    assert yc.dtype == torch.float32 and yc.shape == pc.shape == (256, 32)
+    assert torch.allclose(yc[:, 0], pc[:, 0], atol=1e-6) and torch.allclose(ys[:, 0], ps[:, 0], atol=1e-6)     # highest frequency kept
+    inv_last = 1.0 / 10000.0 ** (31 / 32)
+    pos = np.arange(256, dtype=np.float64)
+    assert np.allclose(yc[:, 31].numpy(), np.cos(pos * inv_last / 4.0), atol=1e-6)                           # lowest: divided by the factor
+    assert not torch.allclose(yc[:, 31], pc[:, 31], atol=1e-4)
+    cfg = load_config("tiny_cpu", ["model.modules.rope=rope_yarn"])
+    eng = TrainEngine(cfg, "cpu")
+    assert type(eng.model.rope).__name__ == "RoPEYarn"
+    g = torch.Generator().manual_seed(0)
+    eng.zero_grads()
+    for v in range(eng.V):
+        ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+        ce, _ = eng.forward_backward(v, ids, ids, 1)
+    assert torch.isfinite(ce) and eng.reduce_gradients() > 0
+    eng.close()
