@@ -201,7 +201,84 @@ int attn_bwd_tc(const void* qk, long ldqk, const void* qkv, long ldqkv, const vo
 }
 }  // namespace
 
+namespace {
+// fp32 family, fast path. Every output element is still ONE chain acc = fma(a_k, b_k, acc), k ascending; the speed comes from
+// running many independent chains side by side: a 4-row x 16-column block of outputs keeps 64 accumulators live, the 16
+// columns of a row sit in SIMD lanes (B is repacked K-major in 16-column panels, tails zero-filled) and the 4 rows hide the
+// latency of the fused multiply-add. A lane never sees another lane's values, so the bits are those of the plain loop. The
+// function is cloned for CPUs with hardware FMA (x86-64-v3); elsewhere fmaf stays the library's correctly rounded routine.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define OTB_FMA_CLONES __attribute__((target_clones("arch=x86-64-v3", "default")))
+#else
+#define OTB_FMA_CLONES
+#endif
+constexpr int FB_N = 16, FB_M = 4;
+
+OTB_FMA_CLONES void chains_4x16(const float* a0, const float* a1, const float* a2, const float* a3, const float* bt, int K, float* acc) {
+  float r0[FB_N], r1[FB_N], r2[FB_N], r3[FB_N];
+  for (int j = 0; j < FB_N; ++j) { r0[j] = acc[j]; r1[j] = acc[FB_N + j]; r2[j] = acc[2 * FB_N + j]; r3[j] = acc[3 * FB_N + j]; }
+  for (int k = 0; k < K; ++k) {
+    const float* row = bt + (size_t)k * FB_N;
+    const float x0 = a0[k], x1 = a1[k], x2 = a2[k], x3 = a3[k];
+#pragma omp simd
+    for (int j = 0; j < FB_N; ++j) {
+      r0[j] = __builtin_fmaf(x0, row[j], r0[j]);
+      r1[j] = __builtin_fmaf(x1, row[j], r1[j]);
+      r2[j] = __builtin_fmaf(x2, row[j], r2[j]);
+      r3[j] = __builtin_fmaf(x3, row[j], r3[j]);
+    }
+  }
+  for (int j = 0; j < FB_N; ++j) { acc[j] = r0[j]; acc[FB_N + j] = r1[j]; acc[2 * FB_N + j] = r2[j]; acc[3 * FB_N + j] = r3[j]; }
+}
+
+// a: [M][K] fp32 panel, b: [N][K] fp32 panel. acc_init: epi 2 continues the chain from C.
+void gemm_f32_chains(const float* a, const float* b, void* C, const void* R, int M, int N, int K, long ldc, long ldr, int epi, int out_bf16) {
+  const int nb = (N + FB_N - 1) / FB_N;
+  std::vector<float> bt((size_t)nb * K * FB_N, 0.0f);
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    float* dst = &bt[((size_t)(n / FB_N) * K) * FB_N + (n % FB_N)];
+    const float* src = b + (size_t)n * K;
+    for (int k = 0; k < K; ++k) dst[(size_t)k * FB_N] = src[k];
+  }
+  const int mb = (M + FB_M - 1) / FB_M;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int bm = 0; bm < mb; ++bm) {
+    for (int bn = 0; bn < nb; ++bn) {
+      float acc[FB_M * FB_N];
+      const float* rows[FB_M];
+      for (int i = 0; i < FB_M; ++i) {
+        const int m = bm * FB_M + i < M ? bm * FB_M + i : M - 1;  // a short last block repeats its last row; the copy is discarded
+        rows[i] = a + (size_t)m * K;
+        for (int j = 0; j < FB_N; ++j) {
+          const int n = bn * FB_N + j;
+          acc[i * FB_N + j] = (epi == 2 && n < N && bm * FB_M + i < M) ? ((const float*)C)[(long)m * ldc + n] : 0.0f;
+        }
+      }
+      chains_4x16(rows[0], rows[1], rows[2], rows[3], &bt[(size_t)bn * K * FB_N], K, acc);
+      for (int i = 0; i < FB_M && bm * FB_M + i < M; ++i) {
+        const int m = bm * FB_M + i;
+        for (int j = 0; j < FB_N && bn * FB_N + j < N; ++j) {
+          const int n = bn * FB_N + j;
+          const long ci = (long)m * ldc + n;
+          const float v = acc[i * FB_N + j];
+          switch (epi) {
+            case 0: stx(C, ci, v, out_bf16); break;
+            case 1: case 2: ((float*)C)[ci] = v; break;
+            default: stx(C, ci, v + ldx(R, (long)m * ldr + n, out_bf16), out_bf16); break;
+          }
+        }
+      }
+    }
+  }
+}
+}  // namespace
+
 extern "C" {
+
+// 1: the fp32 family runs the plain one-element-at-a-time loop (the definition the fast path is tested against).
+static int g_gemm_plain = 0;
+void otb_cpu_gemm_set_plain(int on) { g_gemm_plain = on; }
 
 // C[M,N] = op(A) op(B)^T. a_mn = 0: A is [M,K] (lda), 1: A is [K,M]. b_mn = 0: B is [N,K], 1: B is [K,N].
 // epi: 0 store in out dtype, 1 store fp32, 2 accumulate into fp32 C, 3 store out dtype of acc + R.
@@ -216,6 +293,10 @@ int otb_cpu_gemm(const void* A, const void* B, void* C, const void* R, int M, in
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; ++n)
     for (int k = 0; k < K; ++k) b[(size_t)n * K + k] = b_mn ? ldx(B, (long)k * ldb + n, in_bf16) : ldx(B, (long)n * ldb + k, in_bf16);
+  if (!in_bf16 && !g_gemm_plain && M > 0 && N > 0) {
+    gemm_f32_chains(a.data(), b.data(), C, R, M, N, K, ldc, ldr, epi, out_bf16);
+    return 0;
+  }
 #pragma omp parallel for schedule(static)
   for (int m = 0; m < M; ++m) {
     const float* ar = &a[(size_t)m * K];

@@ -126,3 +126,44 @@ def test_embedding_backward_with_heavy_repeats_and_untouched_rows():
     for pos, i in enumerate(ids.reshape(-1).tolist()):
         want[i] = want[i] + gy.reshape(-1, D)[pos]
     assert torch.equal(gw, want) and torch.count_nonzero(gw[5:96]) == 0
+
+
+def test_fast_fp32_gemm_path_equals_the_plain_chain_loop_bit_for_bit():
+    """the 4 x 16 micro-kernel (independent fused-multiply-add chains in SIMD lanes) against the one-element-at-a-time
+    definition, over storage orders, epilogues, block tails and operand magnitudes"""
+    from open_transformers_b200.ops.native import cpu_lib
+
+    lib = cpu_lib()
+    g = torch.Generator().manual_seed(0)
+
+    def both(fn):
+        lib.otb_cpu_gemm_set_plain(1)
+        try:
+            a = fn()
+        finally:
+            lib.otb_cpu_gemm_set_plain(0)
+        return a, fn()
+
+    for M, N, Kd in [(1, 1, 1), (1, 17, 5), (3, 16, 64), (5, 33, 129), (130, 70, 257), (4, 16, 16), (7, 15, 1000), (9, 48, 0)]:
+        A = torch.randn(M, Kd, generator=g) * 10.0 ** torch.randint(-3, 3, (M, 1), generator=g).float()
+        B, R, C0 = torch.randn(N, Kd, generator=g), torch.randn(M, N, generator=g), torch.randn(M, N, generator=g)
+        for a_mn in (False, True):
+            for b_mn in (False, True):
+                aa, bb = (A.t().contiguous() if a_mn else A), (B.t().contiguous() if b_mn else B)
+                if Kd == 0 and (a_mn or b_mn):
+                    continue
+
+                def acc():
+                    c = C0.clone()
+                    K.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out=c, epi=K.EPI_ACC_F32)
+                    return c
+
+                def store():
+                    c = torch.full((M, N), 3.0)
+                    K.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out=c, epi=K.EPI_STORE_F32)
+                    return c
+
+                for fn in (lambda: K.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn), lambda: K.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, epi=K.EPI_RESIDUAL, residual=R),
+                           acc, store):
+                    x, y = both(fn)
+                    assert torch.equal(x, y), (M, N, Kd, a_mn, b_mn)
