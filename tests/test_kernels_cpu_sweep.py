@@ -167,3 +167,52 @@ def test_fast_fp32_gemm_path_equals_the_plain_chain_loop_bit_for_bit():
                            acc, store):
                     x, y = both(fn)
                     assert torch.equal(x, y), (M, N, Kd, a_mn, b_mn)
+
+
+def test_fast_tensor_core_model_gemm_equals_the_plain_model_bit_for_bit():
+    """bf16 family: the pre-decoded, 16-columns-at-a-time restatement of the accumulation rule against tcmodel::dot, over
+    wide exponent spreads, sparse operands, near-cancellation, magnitudes at both ends of the fast path's range and beyond
+    it (where it hands the element back to the plain routine), all epilogues and block tails"""
+    from open_transformers_b200.ops.native import cpu_lib
+
+    lib = cpu_lib()
+    g = torch.Generator().manual_seed(1)
+
+    def both(fn):
+        lib.otb_cpu_gemm_set_plain(1)
+        try:
+            a = fn()
+        finally:
+            lib.otb_cpu_gemm_set_plain(0)
+        return a, fn()
+
+    def make(rows, Kd, mode):
+        x = torch.randn(rows, Kd, generator=g)
+        if mode == "spread":
+            x = x * 2.0 ** torch.randint(-30, 30, (rows, Kd), generator=g).float()
+        elif mode == "sparse":
+            x = x * (torch.rand(rows, Kd, generator=g) < 0.3)
+        elif mode == "cancel" and Kd > 1:
+            half = x[:, 1::2].shape[1]
+            x[:, 1::2] = -x[:, 0::2][:, :half] * (1 + 2.0 ** -7 * torch.randint(-1, 2, (rows, half), generator=g))
+        elif mode in ("big", "small", "huge", "tiny", "subnormal"):
+            x = x * 2.0 ** {"big": 45, "small": -55, "huge": 62, "tiny": -70, "subnormal": -130}[mode]
+        return x.bfloat16()
+
+    modes = ["normal", "spread", "sparse", "cancel", "big", "small", "huge", "tiny", "subnormal"]
+    for M, N, Kd in [(1, 1, 1), (3, 17, 16), (5, 33, 40), (9, 70, 257), (2, 5, 1000)]:
+        for i, ma in enumerate(modes):
+            mb = modes[(i * 4 + M) % len(modes)]
+            A, B = make(M, Kd, ma), make(N, Kd, mb)
+            R, C0 = torch.randn(M, N, generator=g).bfloat16(), torch.randn(M, N, generator=g)
+
+            def acc():
+                c = C0.clone()
+                K.gemm(A, B, out=c, epi=K.EPI_ACC_F32)
+                return c
+
+            for fn in (lambda: K.gemm(A, B), lambda: K.gemm(A, B.t().contiguous(), b_mn=True), lambda: K.gemm(A, B, epi=K.EPI_RESIDUAL, residual=R),
+                       acc, lambda: K.gemm(A, B, epi=K.EPI_STORE_F32)):
+                x, y = both(fn)
+                same = torch.equal(torch.isnan(x), torch.isnan(y)) and torch.equal(torch.nan_to_num(x.float()), torch.nan_to_num(y.float()))
+                assert same, (M, N, Kd, ma, mb)
