@@ -35,8 +35,13 @@ def _load(name: str, builder: str) -> ctypes.CDLL:
 
 def cpu_lib() -> ctypes.CDLL:
     if os.environ.get("OTB_CPU_SANITIZE") == "1":  # AddressSanitizer + UBSan build of the same sources (race / bounds checks)
-        return _load("otb_cpu_san", "build_cpu_sanitized")
-    return _load("otb_cpu", "build_cpu")
+        lib = _load("otb_cpu_san", "build_cpu_sanitized")
+    else:
+        lib = _load("otb_cpu", "build_cpu")
+    if os.environ.get("OTB_CPU_GEMM_PLAIN") == "1" and not getattr(lib, "_otb_plain_set", False):
+        lib.otb_cpu_gemm_set_plain(1)  # the one-element-at-a-time GEMM loops (the definition) instead of the lane-parallel ones
+        lib._otb_plain_set = True
+    return lib
 
 
 def cuda_lib() -> ctypes.CDLL:
