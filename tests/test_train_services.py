@@ -275,3 +275,34 @@ def test_activation_checkpointing_changes_no_bit(bf16, monkeypatch):
     assert plain[:2] == every[:2] == other[:2]
     per_pass = 2 * 3 + 1
     assert plain[2] == 2 * per_pass and every[2] == 2 * (per_pass + 6) and other[2] == 2 * (per_pass + 4)   # blocks 0 and 2 of 3 recomputed
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_training_step_hash_is_the_same_on_the_plain_and_the_lane_parallel_gemm_twins(bf16):
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.ops.native import cpu_lib
+    from open_transformers_b200.train.engine import TrainEngine
+
+    def run():
+        cfg = load_config("tiny_cpu", ["run.mixed_precision=%s" % ("true" if bf16 else "false")])
+        eng = TrainEngine(cfg, "cpu")
+        g = torch.Generator().manual_seed(0)
+        prev = None
+        for _ in range(2):
+            eng.zero_grads()
+            for v in range(eng.V):
+                ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+                eng.forward_backward(v, ids, torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), 1)
+            norm = eng.reduce_gradients()
+            eng.optimizer_step(1e-3, eng.clip_coefficient(norm, 1.0))
+            prev = eng.sharded_state_hash(prev, None)
+        eng.close()
+        return prev
+
+    lib = cpu_lib()
+    lib.otb_cpu_gemm_set_plain(1)
+    try:
+        plain = run()
+    finally:
+        lib.otb_cpu_gemm_set_plain(0)
+    assert run() == plain
