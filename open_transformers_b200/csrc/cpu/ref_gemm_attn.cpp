@@ -294,10 +294,19 @@ inline Dec dec_bf16_value(float x) {
   return Dec{m8, t.e + 16, t.e + tcmodel::bitlen(t.m) - 1};
 }
 
-OTB_FMA_CLONES void tc_rows_x16(const Dec* a, const int32_t* bm, const int32_t* be, const int32_t* bl, int K, float* out, uint8_t* redo) {
-  // a: [K] decoded row of A; bm / be / bl: [K][16] decoded panel of B; out: [16]; redo[j] = 1 asks for the plain routine
+OTB_FMA_CLONES void tc_rows_x16(const Dec* a, const int32_t* bm, const int32_t* be, const int32_t* bl, int K, float* out, uint8_t* redo,
+                                const float* acc_in = nullptr) {
+  // a: [K] decoded row of A; bm / be / bl: [K][16] decoded panel of B; out: [16]; redo[j] = 1 asks for the plain routine;
+  // acc_in: [16] values the chains continue from (nullptr: they start at zero)
   int32_t am[FB_N], ae[FB_N], al[FB_N];
-  for (int j = 0; j < FB_N; ++j) { am[j] = 0; ae[j] = 0; al[j] = NO_LEAD; redo[j] = 0; }
+  for (int j = 0; j < FB_N; ++j) {
+    am[j] = 0; ae[j] = 0; al[j] = NO_LEAD; redo[j] = 0;
+    tcmodel::Term t;
+    if (acc_in != nullptr && tcmodel::decode(acc_in[j], &t)) {
+      am[j] = (int32_t)t.m; ae[j] = t.e; al[j] = t.e + tcmodel::bitlen(t.m) - 1;
+      if (al[j] > 120 || al[j] < -120) redo[j] = 1;
+    }
+  }
   for (int k0 = 0; k0 < K; k0 += 16) {
     const int kn = K - k0 < 16 ? K - k0 : 16;
     int32_t E[FB_N];
@@ -361,6 +370,111 @@ OTB_FMA_CLONES void tc_rows_x16(const Dec* a, const int32_t* bm, const int32_t* 
     const float r = am[j] == 0 ? 0.0f : ldexpf((float)mag, ae[j]);
     out[j] = am[j] < 0 ? -r : r;
   }
+}
+
+// acc[m * ldacc + n] <- tcmodel::dot(a_m, b_n, K, acc[m * ldacc + n]): an [M][K] and an [N][K] panel of bf16-representable
+// floats, every chain continuing from the value already in acc (pass zeros to start one).
+void tc_block(const float* a, const float* b, int M, int N, int K, float* acc, long ldacc) {
+  const int nb = (N + FB_N - 1) / FB_N;
+  std::vector<Dec> ad((size_t)M * K);
+  std::vector<int32_t> bm((size_t)nb * K * FB_N, 0), be((size_t)nb * K * FB_N, 0), bl((size_t)nb * K * FB_N, NO_LEAD);
+  bool wild = false;
+  for (size_t i = 0; i < (size_t)M * K; ++i) {
+    ad[i] = dec_bf16_value(a[i]);
+    wild = wild || (ad[i].m != 0 && (ad[i].l > 60 || ad[i].l < -60));
+  }
+  for (int n = 0; n < N; ++n)
+    for (int k = 0; k < K; ++k) {
+      const Dec d = dec_bf16_value(b[(size_t)n * K + k]);
+      const size_t at = ((size_t)(n / FB_N) * K + k) * FB_N + (n % FB_N);
+      bm[at] = d.m; be[at] = d.e; bl[at] = d.l;
+      wild = wild || (d.m != 0 && (d.l > 60 || d.l < -60));
+    }
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int m = 0; m < M; ++m) {
+    for (int bn = 0; bn < nb; ++bn) {
+      float in[FB_N], out[FB_N];
+      uint8_t redo[FB_N];
+      for (int j = 0; j < FB_N; ++j) in[j] = bn * FB_N + j < N ? acc[(long)m * ldacc + bn * FB_N + j] : 0.0f;
+      if (!wild) tc_rows_x16(ad.data() + (size_t)m * K, bm.data() + (size_t)bn * K * FB_N, be.data() + (size_t)bn * K * FB_N,
+                             bl.data() + (size_t)bn * K * FB_N, K, out, redo, in);
+      for (int j = 0; j < FB_N && bn * FB_N + j < N; ++j) {
+        const int n = bn * FB_N + j;
+        acc[(long)m * ldacc + n] = (wild || redo[j]) ? tcmodel::dot(a + (size_t)m * K, b + (size_t)n * K, K, in[j]) : out[j];
+      }
+    }
+  }
+}
+
+// The backward pass of attn_bwd_tc, block by block: for every (query block, key block) pair the scores and dP are formed
+// ONCE (the plain routine forms them in its dK/dV sweep and again in its dQ sweep, with the same result) and the three
+// gradient chains continue through tc_block in the plain routine's order: dV and dK of a key block over (head of the group
+// ascending, query block ascending, 16 rows per step), dQ of a query block over key blocks ascending, 16 keys per step.
+// Blocks without an unmasked pair are skipped by both routines or contribute zero products, which leave a chain unchanged.
+int attn_bwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, const void* dO, long lddo, const float* lse, const float* delta,
+                       void* dqk, long lddqk, void* dqkv, long lddqkv, int B, int T, int H, int Hkv, int D, int window, float c_log2, float scale) {
+  const int G = H / Hkv, nq = (T + 127) / 128;
+  std::vector<float> Qb(128 * D), dOb(128 * D), Kb(128 * D), Vb(128 * D), QbT(128 * D), dObT(128 * D), KbT(128 * D);
+  std::vector<float> S(128 * 128), dP(128 * 128), P(128 * 128), dS(128 * 128), PT(128 * 128), dST(128 * 128), dQ(128 * D);
+  auto load = [&](const void* src, long ld, int b, int r0, long col0, float* rows, float* rowsT) {
+    for (int r = 0; r < 128; ++r)
+      for (int d = 0; d < D; ++d) {
+        const int t = r0 + r;
+        const float v = t < T ? ldb(src, ((long)b * T + t) * ld + col0 + d) : 0.0f;
+        rows[r * D + d] = v;
+        if (rowsT != nullptr) rowsT[d * 128 + r] = v;
+      }
+  };
+  for (int b = 0; b < B; ++b) {
+    for (int g = 0; g < Hkv; ++g) {
+      std::vector<float> dKacc((size_t)nq * 128 * D, 0.0f), dVacc((size_t)nq * 128 * D, 0.0f);
+      for (int hh = 0; hh < G; ++hh) {
+        const int h = g * G + hh;
+        for (int qb = 0; qb < nq; ++qb) {
+          load(qk, ldqk, b, qb * 128, (long)h * D, Qb.data(), QbT.data());
+          load(dO, lddo, b, qb * 128, (long)h * D, dOb.data(), dObT.data());
+          for (auto& v : dQ) v = 0.0f;
+          const int q0 = qb * 128;
+          const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
+          for (int j = jmin; j <= qb; ++j) {
+            load(qk, ldqk, b, j * 128, (long)(H + g) * D, Kb.data(), KbT.data());
+            load(qkv, ldqkv, b, j * 128, (long)(H + Hkv + g) * D, Vb.data(), nullptr);
+            for (auto& v : S) v = 0.0f;
+            for (auto& v : dP) v = 0.0f;
+            tc_block(Qb.data(), Kb.data(), 128, 128, D, S.data(), 128);
+            tc_block(dOb.data(), Vb.data(), 128, 128, D, dP.data(), 128);
+#pragma omp parallel for schedule(static)
+            for (int r = 0; r < 128; ++r) {
+              const int qi = q0 + r;
+              for (int e = 0; e < 128; ++e) {
+                const int kj = j * 128 + e;
+                float p = 0.0f, ds = 0.0f;
+                if (qi < T && kj < T && !masked_pair(qi, kj, window)) {
+                  const float l2 = lse[((long)b * H + h) * T + qi], dl = delta[((long)b * H + h) * T + qi];
+                  const float pe = det_exp2_attn(det_fmaf(S[r * 128 + e], c_log2, -l2));
+                  p = rbf(pe);
+                  ds = rbf((pe * (dP[r * 128 + e] + (-dl))) * scale);
+                }
+                P[r * 128 + e] = p; dS[r * 128 + e] = ds;
+                PT[e * 128 + r] = p; dST[e * 128 + r] = ds;
+              }
+            }
+            tc_block(PT.data(), dObT.data(), 128, D, 128, dVacc.data() + (size_t)j * 128 * D, D);
+            tc_block(dST.data(), QbT.data(), 128, D, 128, dKacc.data() + (size_t)j * 128 * D, D);
+            tc_block(dS.data(), KbT.data(), 128, D, 128, dQ.data(), D);
+          }
+          for (int r = 0; r < 128 && q0 + r < T; ++r)
+            for (int d = 0; d < D; ++d) ((uint16_t*)dqk)[((long)b * T + q0 + r) * lddqk + (long)h * D + d] = det_f2bf(dQ[r * D + d]);
+        }
+      }
+      for (int kj = 0; kj < T; ++kj)
+        for (int d = 0; d < D; ++d) {
+          ((uint16_t*)dqk)[((long)b * T + kj) * lddqk + (long)(H + g) * D + d] = det_f2bf(dKacc[(size_t)kj * D + d]);
+          ((uint16_t*)dqkv)[((long)b * T + kj) * lddqkv + (long)(H + Hkv + g) * D + d] = det_f2bf(dVacc[(size_t)kj * D + d]);
+        }
+    }
+  }
+  return 0;
 }
 
 // a: [M][K], b: [N][K] fp32 panels holding bf16-representable values. Epilogues as in otb_cpu_gemm.
@@ -541,6 +655,8 @@ int otb_cpu_attn_bwd(const void* qk, long ldqk, const void* qkv, long ldqkv, con
     const long b = row / T, t = row % T;
     delta[(b * H + h) * T + t] = det_butterfly_host(part, 32);
   }
+  if (bf16 && !g_gemm_plain)
+    return attn_bwd_tc_blocks(qk, ldqk, qkv, ldqkv, dO, lddo, lse, delta, dqk, lddqk, dqkv, lddqkv, B, T, H, Hkv, D, window, c_log2, scale);
   if (bf16) return attn_bwd_tc(qk, ldqk, qkv, ldqkv, dO, lddo, lse, delta, dqk, lddqk, dqkv, lddqkv, B, T, H, Hkv, D, window, c_log2, scale);
   auto prob_ds = [&](int b, int h, int g, int qi, int kj, float* p_out, float* ds_out) {
     // returns false when the pair is masked

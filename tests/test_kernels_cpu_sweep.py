@@ -216,3 +216,28 @@ def test_fast_tensor_core_model_gemm_equals_the_plain_model_bit_for_bit():
                 x, y = both(fn)
                 same = torch.equal(torch.isnan(x), torch.isnan(y)) and torch.equal(torch.nan_to_num(x.float()), torch.nan_to_num(y.float()))
                 assert same, (M, N, Kd, ma, mb)
+
+
+@pytest.mark.parametrize("B,H,Hkv,T,D,window,qk_norm", [(1, 2, 1, 96, 64, 0, False), (2, 4, 2, 300, 64, 0, True), (1, 4, 1, 384, 128, 128, False),
+                                                        (1, 2, 2, 260, 32, 64, True), (1, 4, 4, 130, 64, 32, False)])
+def test_block_wise_bf16_attention_backward_equals_the_plain_twin(B, H, Hkv, T, D, window, qk_norm):
+    """the bf16 attention backward twin computed block by block through the lane-parallel accumulation kernel (scores and dP
+    formed once per block pair, the three gradient chains continued in the plain routine's order) against the plain twin"""
+    from open_transformers_b200.ops.native import cpu_lib
+
+    lib = cpu_lib()
+    g = torch.Generator().manual_seed(T + D)
+    qkv = (torch.randn(B, T, (H + 2 * Hkv) * D, generator=g) * 0.7).bfloat16().requires_grad_(True)
+    cos, sin = K.rope_tables(T, D, 10000.0, "cpu")
+    go = torch.randn(B, T, H * D, generator=g).bfloat16()
+    got = []
+    for plain in (1, 0):
+        lib.otb_cpu_gemm_set_plain(plain)
+        try:
+            o = A.attention(qkv, cos, sin, H, Hkv, D, window, qk_norm, 1e-5)
+            (gq,) = torch.autograd.grad(o, qkv, go)
+        finally:
+            lib.otb_cpu_gemm_set_plain(0)
+        got.append((o.detach().clone(), gq.clone()))
+    assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1])
+    assert float(got[1][1].float().abs().max()) > 0
