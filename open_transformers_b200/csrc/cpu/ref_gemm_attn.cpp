@@ -477,6 +477,74 @@ int attn_bwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, c
   return 0;
 }
 
+// The forward pass of attn_fwd_tc (float P V), block by block: the 128 x 128 scores of a (query block, key block) pair
+// come from one tc_block call, the per-row softmax bookkeeping is the plain routine's, and the block's P V continues each
+// output chain from o * alpha (zero for a row's first key block) through tc_block, 16 keys per step.
+int attn_fwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B, int T, int H, int Hkv, int D,
+                       int window, float c_log2) {
+  const int G = H / Hkv, nq = (T + 127) / 128;
+  std::vector<float> Qb(128 * D), Kb(128 * D), VbT(128 * D), S(128 * 128), P(128 * 128), Oacc(128 * D), m_run(128), lp(128 * 4);
+  for (int b = 0; b < B; ++b) {
+    for (int h = 0; h < H; ++h) {
+      const int g = h / G;
+      for (int qb = 0; qb < nq; ++qb) {
+        const int q0 = qb * 128;
+        const int jmin = (window > 0 && q0 - window + 1 > 0) ? (q0 - window + 1) / 128 : 0;
+        for (int r = 0; r < 128; ++r) {
+          for (int d = 0; d < D; ++d) { Qb[r * D + d] = q0 + r < T ? ldb(qk, ((long)b * T + q0 + r) * ldqk + (long)h * D + d) : 0.0f; Oacc[r * D + d] = 0.0f; }
+          m_run[r] = -INFINITY;
+          for (int i = 0; i < 4; ++i) lp[r * 4 + i] = 0.0f;
+        }
+        for (int j = jmin; j <= qb; ++j) {
+          for (int e = 0; e < 128; ++e)
+            for (int d = 0; d < D; ++d) {
+              const int kj = j * 128 + e;
+              Kb[e * D + d] = kj < T ? ldb(qk, ((long)b * T + kj) * ldqk + (long)(H + g) * D + d) : 0.0f;
+              VbT[d * 128 + e] = kj < T ? ldb(qkv, ((long)b * T + kj) * ldqkv + (long)(H + Hkv + g) * D + d) : 0.0f;
+            }
+          for (auto& v : S) v = 0.0f;
+          tc_block(Qb.data(), Kb.data(), 128, 128, D, S.data(), 128);
+#pragma omp parallel for schedule(static)
+          for (int r = 0; r < 128; ++r) {
+            const int qi = q0 + r;
+            float* s = &S[r * 128];
+            float* p = &P[r * 128];
+            if (qi >= T) { for (int e = 0; e < 128; ++e) p[e] = 0.0f; continue; }
+            float mx = -INFINITY;
+            for (int e = 0; e < 128; ++e) {
+              const int kj = j * 128 + e;
+              if (masked_pair(qi, kj, window) || kj >= T) { s[e] = -INFINITY; continue; }
+              mx = fmaxf(mx, s[e]);
+            }
+            const float m_new = fmaxf(m_run[r], mx * c_log2);
+            const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float alpha = det_exp2_attn(m_run[r] + (-m_safe));
+            for (int part = 0; part < 4; ++part) {
+              float ls[2] = {0.0f, 0.0f};
+              for (int e = part * 32; e < part * 32 + 32; ++e) {
+                const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
+                ls[e & 1] = ls[e & 1] + pe;
+                p[e] = rbf(pe);
+              }
+              lp[r * 4 + part] = det_fmaf(lp[r * 4 + part], alpha, ls[0] + ls[1]);
+            }
+            for (int d = 0; d < D; ++d) Oacc[r * D + d] = j > jmin ? Oacc[r * D + d] * alpha : 0.0f;
+            m_run[r] = m_new;
+          }
+          tc_block(P.data(), VbT.data(), 128, D, 128, Oacc.data(), D);
+        }
+        for (int r = 0; r < 128 && q0 + r < T; ++r) {
+          const long qrow = (long)b * T + q0 + r;
+          const float l_tot = ((lp[r * 4] + lp[r * 4 + 1]) + lp[r * 4 + 2]) + lp[r * 4 + 3];
+          for (int d = 0; d < D; ++d) ((uint16_t*)O)[qrow * ldo + (long)h * D + d] = det_f2bf(Oacc[r * D + d] / l_tot);
+          lse[((long)b * H + h) * T + q0 + r] = det_fmaf(det_logf(l_tot), 1.44269504088896341f, m_run[r]);
+        }
+      }
+    }
+  }
+  return 0;
+}
+
 // a: [M][K], b: [N][K] fp32 panels holding bf16-representable values. Epilogues as in otb_cpu_gemm.
 void gemm_tc_fast(const float* a, const float* b, void* C, const void* R, int M, int N, int K, long ldc, long ldr, int epi, int out_bf16) {
   const int nb = (N + FB_N - 1) / FB_N;
@@ -572,6 +640,7 @@ int otb_cpu_gemm(const void* A, const void* B, void* C, const void* R, int M, in
 int otb_cpu_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B, int T,
                      int H, int Hkv, int D, int window, float scale, int bf16) {
   const float c_log2 = (float)((double)scale * 1.4426950408889634);
+  if (bf16 && !g_gemm_plain) return attn_fwd_tc_blocks(qk, ldqk, qkv, ldqkv, O, ldo, lse, B, T, H, Hkv, D, window, c_log2);
   if (bf16) return attn_fwd_tc(qk, ldqk, qkv, ldqkv, O, ldo, lse, B, T, H, Hkv, D, window, c_log2);
   const int G = H / Hkv;
 #pragma omp parallel for collapse(2) schedule(dynamic, 8)

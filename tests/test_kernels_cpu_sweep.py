@@ -220,8 +220,8 @@ def test_fast_tensor_core_model_gemm_equals_the_plain_model_bit_for_bit():
 
 @pytest.mark.parametrize("B,H,Hkv,T,D,window,qk_norm", [(1, 2, 1, 96, 64, 0, False), (2, 4, 2, 300, 64, 0, True), (1, 4, 1, 384, 128, 128, False),
                                                         (1, 2, 2, 260, 32, 64, True), (1, 4, 4, 130, 64, 32, False)])
-def test_block_wise_bf16_attention_backward_equals_the_plain_twin(B, H, Hkv, T, D, window, qk_norm):
-    """the bf16 attention backward twin computed block by block through the lane-parallel accumulation kernel (scores and dP
+def test_block_wise_bf16_attention_equals_the_plain_twin(B, H, Hkv, T, D, window, qk_norm):
+    """the bf16 attention twins (forward: output and row statistic; backward) computed block by block through the lane-parallel accumulation kernel (scores and dP
     formed once per block pair, the three gradient chains continued in the plain routine's order) against the plain twin"""
     from open_transformers_b200.ops.native import cpu_lib
 
@@ -236,8 +236,11 @@ def test_block_wise_bf16_attention_backward_equals_the_plain_twin(B, H, Hkv, T, 
         try:
             o = A.attention(qkv, cos, sin, H, Hkv, D, window, qk_norm, 1e-5)
             (gq,) = torch.autograd.grad(o, qkv, go)
+            q2 = qkv.detach().reshape(B * T, -1)
+            rot, _ = K.qknorm_rope_fwd(q2, cos, sin, H + Hkv, D, T, qk_norm, 1e-5)
+            _, lse = K.attn_fwd(rot, q2, B, T, H, Hkv, D, window, False)
         finally:
             lib.otb_cpu_gemm_set_plain(0)
-        got.append((o.detach().clone(), gq.clone()))
-    assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1])
+        got.append((o.detach().clone(), gq.clone(), lse.clone()))
+    assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1]) and torch.equal(got[0][2], got[1][2])
     assert float(got[1][1].float().abs().max()) > 0
