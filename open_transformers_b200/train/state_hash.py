@@ -57,10 +57,14 @@ def tree_digest_bytes(data: bytes | np.ndarray) -> bytes:
     from ..ops.native import cpu_lib
 
     arr = np.frombuffer(data, dtype=np.uint8) if not isinstance(data, np.ndarray) else data.reshape(-1).view(np.uint8)
-    buf = np.empty(arr.size + 8, dtype=np.uint8)  # numpy allocations are 16-byte aligned
-    buf[: arr.size] = arr
+    if not (arr.flags["C_CONTIGUOUS"] and arr.ctypes.data % 8 == 0 and arr.size > 0):
+        buf = np.empty(arr.size + 8, dtype=np.uint8)  # the native routine wants 8-byte aligned input; numpy allocations are 16-byte aligned
+        buf[: arr.size] = arr
+        src = buf
+    else:
+        src = arr  # tensors and aligned arrays are digested in place: no copy of the state
     out = (ctypes.c_ubyte * 32)()
-    cpu_lib().otb_cpu_tree_digest(buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(arr.size), out)
+    cpu_lib().otb_cpu_tree_digest(src.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(arr.size), out)
     return bytes(out)
 
 
