@@ -322,6 +322,36 @@ int otb_cpu_cast(const void* in, void* out, long n, int in_bf16, int out_bf16) {
   return 0;
 }
 // unit-test hooks for the shared math header
+// Elementwise maps with the shared deterministic routines. op: 0 exp, 1 log, 2 sqrt, 3 1/sqrt, 4 sigmoid, 5 sin, 6 cos
+// (sin / cos: double-precision evaluation rounded once to binary32, as for the RoPE tables).
+int otb_cpu_map(int op, const float* x, float* y, long n) {
+  if (op < 0 || op > 6) return -3;
+#pragma omp parallel for schedule(static)
+  for (long i = 0; i < n; ++i) {
+    const float v = x[i];
+    float r;
+    switch (op) {
+      case 0: r = det_expf(v); break;
+      case 1: r = det_logf(v); break;
+      case 2: r = det_sqrtf(v); break;
+      case 3: r = det_rsqrtf(v); break;
+      case 4: r = det_sigmoidf(v); break;
+      default: {
+        double sv, cv;
+        det_sincos((double)v, &sv, &cv);
+        r = (float)(op == 5 ? sv : cv);
+      }
+    }
+    y[i] = r;
+  }
+  return 0;
+}
+// Canonical sums of the rows of a [rows, n] fp32 matrix (mode 1: sums of squares), each times post_scale.
+int otb_cpu_row_sums(const float* x, long rows, long n, int mode, float post_scale, float* out) {
+#pragma omp parallel for schedule(static)
+  for (long r = 0; r < rows; ++r) otb_cpu_det_sum(x + r * n, n, mode, post_scale, out + r);
+  return 0;
+}
 float otb_cpu_expf(float x) { return det_expf(x); }
 float otb_cpu_logf(float x) { return det_logf(x); }
 void otb_cpu_rope_tables(float* cosb, float* sinb, int seq_len, int half, double theta) {
