@@ -332,3 +332,24 @@ def test_gpu_int8_pv_attention_bitwise_vs_twin(window, T):
     gpu = K.attn_fwd(qk.cuda(), qkv.cuda(), 2, T, 4, 2, 128, window, int8_pv=True)
     _eq(cpu, gpu, "int8 P V attention")
     assert K.kernel_status("cuda") == 0
+
+
+def test_every_recipe_switch_together_trains_and_replays_in_bf16(tmp_path):
+    """bf16 compute, sliding-window layers, int8 P V, QK-norm gains, quantisation-aware layers past an exempt block with a
+    step-size refresh, activation checkpointing: the run's digests are reproduced from its checkpoint and from the seed
+    (the second time with folded gradients and offloaded moments)"""
+    from open_transformers_b200.cli.audit_replay import audit_replay
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path)
+    over = ["run.mixed_precision=true", "model.n_layers=2", "model.swa_window=32", "model.swa_full_every=2", "model.attn_int8_pv=true", "model.head_dim=64",
+            "model.n_heads=2", "model.n_kv_heads=1", "model.d_model=128", "train.seq_len=128", "data.seq_len=128", "model.max_seq_len_pretrain=128",
+            "train.global_batch_tokens.warmup=512", "train.global_batch_tokens.main=512", "train.global_batch_tokens.late=512", "train.total_tokens=1536",
+            "++model.qat.enabled=true", "++model.qat.exempt_first_n_blocks=1", "++model.qat.scale_refresh_every_n_steps=2", "train.ckpt_every_steps=2",
+            "model.modules.attention=gqa_qknorm_repop", "model.qk_norm=true", "model.qk_norm_gain=true", "run.activation_checkpoint=true"]
+    res = train(tiny_cfg(tmp, over), device="cpu", data_root=tmp)
+    assert len({h for _, h in res["hashes"]}) == 3 and all(math.isfinite(l) for l in res["losses"])
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    assert audit_replay(ck, data_root=tmp, until_step=3)["match"] is True
+    r = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=3, offload_grads=True, offload_optimizer=True)
+    assert r["match"] is True and r["state_hash"] == res["hashes"][-1][1]
