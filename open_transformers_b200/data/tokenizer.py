@@ -15,13 +15,15 @@ SPECIAL_TOKENS = ["<|endoftext|>", "<|begin_of_text|>", "<|start_header|>", "<|e
 
 def train_tokenizer(text_iterator: Iterable[str], output_path: str | Path, vocab_size: int = 128_256, min_frequency: int = 2,
                     special_tokens: list[str] | None = None, show_progress: bool = False) -> Path:
+    from tokenizers import Regex
     from tokenizers import Tokenizer as HFTokenizer
     from tokenizers import decoders, models, pre_tokenizers, processors, trainers
 
     out = Path(output_path)
     out.parent.mkdir(parents=True, exist_ok=True)
     tok = HFTokenizer(models.BPE(byte_fallback=True))
-    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(pattern=r"\d", behavior="isolated"),
+    # every digit its own piece (a Regex: a plain string pattern would be matched literally), then GPT-2 byte-level pieces
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(pattern=Regex(r"\d"), behavior="isolated"),
                                                  pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)])
     tok.decoder = decoders.ByteLevel()
     tok.post_processor = processors.ByteLevel(trim_offsets=False)

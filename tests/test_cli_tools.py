@@ -164,3 +164,20 @@ def test_safetensors_interchange_refuses_foreign_files_and_path_like_sidecar_nam
         assert not (tmp_path / "o2").exists() and not (tmp_path / "escape.txt").exists()
     with pytest.raises(FileNotFoundError):
         pack(str(tmp_path / "nowhere"), str(tmp_path / "x.safetensors"))
+
+
+def test_tokenizer_isolates_digits_keeps_specials_and_hashes_canonically(corpus, tmp_path):
+    from open_transformers_b200.data.tokenizer import SPECIAL_TOKENS, Tokenizer, compute_hash, train_tokenizer
+
+    root, paths = corpus
+    texts = [json.loads(l)["text"] for p in paths for l in open(p)]
+    out = train_tokenizer(iter(texts), tmp_path / "t.json", vocab_size=330, min_frequency=1)
+    tok = Tokenizer(out)
+    assert [tok._tok.token_to_id(s) for s in SPECIAL_TOKENS] == list(range(6)) and tok.eos_id == 0
+    assert len(tok.encode("6789")) == 4 and len(tok.encode("12")) == 2          # one token per digit, however frequent the number
+    assert tok.decode(tok.encode("alpha 6789 beta")) == "alpha 6789 beta"
+    assert tok.decode(tok.encode("héllo ☃")) == "héllo ☃"                        # bytes outside the training text still round-trip
+    assert len(tok.encode_batch(["alpha", "beta gamma"])) == 2 and 256 < tok.vocab_size <= 330
+    pretty = tmp_path / "pretty.json"                                            # the same tokenizer, re-serialised with other whitespace / key order
+    pretty.write_text(json.dumps(json.loads(out.read_text()), indent=4, sort_keys=True, ensure_ascii=False))
+    assert compute_hash(pretty) == compute_hash(out) == tok.hash
