@@ -181,3 +181,34 @@ def test_tokenizer_isolates_digits_keeps_specials_and_hashes_canonically(corpus,
     pretty = tmp_path / "pretty.json"                                            # the same tokenizer, re-serialised with other whitespace / key order
     pretty.write_text(json.dumps(json.loads(out.read_text()), indent=4, sort_keys=True, ensure_ascii=False))
     assert compute_hash(pretty) == compute_hash(out) == tok.hash
+
+
+def test_doc_map_and_fetch_commands_and_a_replay_on_fetched_data(tmp_path, capsys):
+    """the step -> document map from a config and from a checkpoint's position; the fetcher brings what the interval reads
+    (verified) and stubs for the rest; the replay runs on the fetched copy, also when asked to fetch by itself"""
+    import pyarrow.parquet as pq
+
+    from open_transformers_b200.cli.audit_replay import main as audit_main
+    from open_transformers_b200.cli.dump_doc_map import main as map_main
+    from open_transformers_b200.cli.fetch_audit_data import main as fetch_main
+    from open_transformers_b200.train.loop import train
+
+    tmp = str(tmp_path / "origin")
+    res = train(tiny_cfg(tmp, ["train.ckpt_every_steps=2"]), device="cpu", data_root=tmp)
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    over = ["train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64", "train.micro_batch_size=2",
+            "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=256", "train.global_batch_tokens.late=256"]
+    rc, out = _run(map_main, ["--config-name", "tiny_cpu", "--data-root", tmp, "--steps", "2", "--output", str(tmp_path / "m0.parquet"), *over], capsys)
+    rows0 = pq.read_table(tmp_path / "m0.parquet").to_pylist()
+    assert rc == 0 and json.loads(out)["rows"] == len(rows0) > 0 and {r["step"] for r in rows0} == {0, 1}
+    rc, out = _run(map_main, ["--checkpoint", ck, "--data-root", tmp, "--steps", "1", "--output", str(tmp_path / "m2.parquet")], capsys)
+    rows2 = pq.read_table(tmp_path / "m2.parquet").to_pylist()
+    assert rc == 0 and {r["step"] for r in rows2} == {2} and sum(r["length"] for r in rows2) <= 4 * 65
+    dest = tmp_path / "fetched"
+    rc, out = _run(fetch_main, ["--checkpoint", ck, "--mirror", tmp, "--dest", str(dest), "--until-step", "3"], capsys)
+    assert rc == 0 and out.strip() == str(dest) and list(dest.rglob("manifest.yaml"))
+    assert audit_main(["--checkpoint", ck, "--data-root", str(dest), "--until-step", "3"]) == 0
+    assert "MATCH=True" in capsys.readouterr().out
+    # the replay fetching for itself: --gcs-root names the mirror, --fetch-dest where to put the interval's data
+    assert audit_main(["--checkpoint", ck, "--gcs-root", tmp, "--fetch-dest", str(tmp_path / "auto"), "--until-step", "3"]) == 0
+    assert "MATCH=True" in capsys.readouterr().out and list((tmp_path / "auto").rglob("*.bin"))
