@@ -116,3 +116,40 @@ def test_multiple_choice_scores_in_one_pass_equal_one_choice_at_a_time(ckpt):
         lp = torch.log_softmax(hf(torch.tensor([c + k])).logits[0, len(c) - 1: -1].float(), -1)
         want = float(lp.gather(-1, torch.tensor(k)[:, None]).sum())
         assert abs(want - g) <= 1e-5 * max(1.0, abs(want))
+
+
+def test_eval_command_scripts_and_core_aggregate(ckpt, tmp_path, capsys):
+    """pretrain-eval on a held-out shard with a task-accuracy file; the DCLM-CORE style aggregate; the curve-plotting,
+    system-information and prompt scripts as a user runs them"""
+    import numpy as np
+
+    from open_transformers_b200.cli.eval import main as eval_main
+    from open_transformers_b200.data.indexed_dataset import IndexedDatasetWriter
+    from open_transformers_b200.eval.dclm_core import DCLM_CORE_TASKS, centred, dclm_core_score
+
+    rng = np.random.default_rng(0)
+    with IndexedDatasetWriter(tmp_path / "heldout", np.uint32) as w:
+        for _ in range(6):
+            w.add_document(rng.integers(0, 512, 90).astype(np.uint32))
+    acc = {"arc_easy": 0.40, "piqa": 0.60, "lambada_openai": 0.10, "not_a_core_task": 0.99}
+    (tmp_path / "acc.json").write_text(json.dumps(acc))
+    capsys.readouterr()
+    assert eval_main(["--checkpoint", ckpt[0], "--shard-prefix", str(tmp_path / "heldout"), "--max-tokens", "300", "--batch-windows", "2",
+                      "--task-accuracies", str(tmp_path / "acc.json")]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["tokens"] == 300 and 50 < out["perplexity"] < 5000
+    want = {"arc_easy": (0.40 - 0.25) / 0.75, "piqa": (0.60 - 0.5) / 0.5, "lambada_openai": 0.10}
+    assert out["dclm_core"]["per_task"] == pytest.approx(want) and out["dclm_core"]["core"] == pytest.approx(sum(want.values()) / 3)
+    assert "not_a_core_task" not in out["dclm_core"]["per_task"] and len(out["dclm_core"]["missing"]) == len(DCLM_CORE_TASKS) - 3
+    assert centred(1.0, 0.25) == 1.0 and centred(0.25, 0.25) == 0.0 and dclm_core_score({})["core"] == 0.0
+    run_dir = Path(ckpt[2])
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "plot_evals.py"), str(run_dir / "logs" / "metrics.jsonl"), "--out", str(tmp_path / "c.png")],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert (tmp_path / "c.png").exists() or r.stdout.count("\n") >= 3          # a figure, or the CSV dump where matplotlib is absent
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "collect_system_info.py")], capture_output=True, text=True, timeout=300)
+    info = json.loads(r.stdout)
+    assert r.returncode == 0 and info["cpus"] >= 1 and "torch" in info and isinstance(info["env"], dict)
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "prompt_checkpoint.py"), "--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--prompt", "the quick",
+                        "--max-new-tokens", "3", "--temperature", "0"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.startswith("the quick"), r.stderr[-2000:]
