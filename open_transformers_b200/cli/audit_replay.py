@@ -395,7 +395,9 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv: list[str] | None = None) -> int:
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
-    a = build_parser().parse_args(argv)
+    from ._args import parse_with_overrides
+
+    a = parse_with_overrides(build_parser(), argv)
     if a.device == "mps":
         print("AUDIT ERROR: Apple Metal/MPS is unavailable on this platform; use --device cuda or cpu", file=sys.stderr)
         return 2

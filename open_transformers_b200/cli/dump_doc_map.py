@@ -16,7 +16,9 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, required=True)
     ap.add_argument("--output", required=True)
     ap.add_argument("overrides", nargs="*")
-    a = ap.parse_args(argv)
+    from ._args import parse_with_overrides
+
+    a = parse_with_overrides(ap, argv)
     from ..config import load_config, parse_config_resolved
     from ..data.doc_map import write_doc_map
     from ..data.global_stream import GlobalStreamState

@@ -114,7 +114,10 @@ def main(argv=None) -> int:
     p.add_argument("overrides", nargs="*"); p.set_defaults(fn=cmd_synthetic)
     p = sub.add_parser("replay-step"); p.add_argument("--config-name", required=True); p.add_argument("--data-root", default="."); p.add_argument("--step", type=int, required=True)
     p.add_argument("--tokenizer"); p.add_argument("--max-tokens", type=int, default=64); p.add_argument("overrides", nargs="*"); p.set_defaults(fn=cmd_replay_step)
-    a = ap.parse_args(argv)
+    from ._args import parse_with_overrides
+
+    a = ap.parse_known_args(argv)[0]
+    a = parse_with_overrides(ap, argv) if hasattr(a, "overrides") else ap.parse_args(argv)  # only two subcommands take overrides
     return a.fn(a)
 
 

@@ -17,7 +17,9 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-steps", type=int)
     ap.add_argument("--synthetic-data", action="store_true", help="create missing sources as seed-generated uniform-random shards")
     ap.add_argument("overrides", nargs="*")
-    a = ap.parse_args(argv)
+    from ._args import parse_with_overrides
+
+    a = parse_with_overrides(ap, argv)
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(name)s %(message)s")
     from ..config import load_config
     from ..train.loop import train

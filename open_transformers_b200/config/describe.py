@@ -42,7 +42,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m open_transformers_b200.config.describe", description=__doc__.split("\n\n")[1])
     ap.add_argument("--config-name")
     ap.add_argument("overrides", nargs="*")
-    a = ap.parse_args(argv)
+    from ..cli._args import parse_with_overrides
+
+    a = parse_with_overrides(ap, argv)
     if a.config_name:
         import yaml
 

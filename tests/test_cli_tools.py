@@ -212,3 +212,43 @@ def test_doc_map_and_fetch_commands_and_a_replay_on_fetched_data(tmp_path, capsy
     # the replay fetching for itself: --gcs-root names the mirror, --fetch-dest where to put the interval's data
     assert audit_main(["--checkpoint", ck, "--gcs-root", tmp, "--fetch-dest", str(tmp_path / "auto"), "--until-step", "3"]) == 0
     assert "MATCH=True" in capsys.readouterr().out and list((tmp_path / "auto").rglob("*.bin"))
+
+
+def test_overrides_and_options_may_come_in_any_order():
+    import argparse
+
+    from open_transformers_b200.cli._args import parse_with_overrides
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config-name", required=True)
+    ap.add_argument("--flag", action="store_true")
+    ap.add_argument("overrides", nargs="*")
+    a = parse_with_overrides(ap, ["a.b=1", "--config-name", "x", "++c.d=[1,2]", "--flag", "~e.f", "+g=h=i"])
+    assert a.config_name == "x" and a.flag and a.overrides == ["a.b=1", "++c.d=[1,2]", "~e.f", "+g=h=i"]
+    for bad in (["--config-name", "x", "--nope"], ["a.b=1", "--config-name", "x", "loose_word"], ["a.b=1", "--config-name", "x", "=3"]):
+        with pytest.raises(SystemExit):
+            parse_with_overrides(ap, bad)
+
+
+@pytest.mark.distributed
+def test_launcher_script_runs_two_cpu_ranks_with_overrides_after_options(tmp_path):
+    """scripts/launch_single_node.sh as documented: config, process count, then options and overrides in any order; two
+    CPU ranks (gloo) write the hashes of the single-process run of the same recipe"""
+    import os
+    import subprocess
+    from pathlib import Path
+
+    from open_transformers_b200.train.loop import train
+
+    root = Path(__file__).resolve().parent.parent
+    tmp = str(tmp_path)
+    over = ["model.n_layers=1", "train.total_tokens=768"]
+    env = dict(os.environ, RUN_ID="launched", PYTHONPATH=str(root), OMP_NUM_THREADS="2", WANDB_MODE="disabled", MASTER_PORT="0")
+    r = subprocess.run(["bash", str(root / "scripts" / "launch_single_node.sh"), "tiny_cpu", "2", "--synthetic-data", "--data-root", tmp, "--device", "cpu",
+                        "run.output_dir=%s/runs" % tmp, *over], env=env, capture_output=True, text=True, timeout=600, cwd=str(root))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    got = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])["hashes"]
+    from open_transformers_b200.config import load_config
+
+    one = train(load_config("tiny_cpu", ["run.output_dir=%s/one" % tmp, "run.run_id=one", *over]), device="cpu", data_root=tmp)
+    assert [tuple(h) for h in got] == [tuple(h) for h in one["hashes"]] and len(got) >= 1
