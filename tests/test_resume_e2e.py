@@ -161,3 +161,17 @@ def test_sharded_ownership_by_messages_through_the_train_loop_and_a_checkpoint(t
     assert two == whole["hashes"][:2]
     rest = train(tiny_cfg(tmp, over + ["run.run_id=msg"]), resume_from="%s/runs/msg/checkpoints/step_000000002" % tmp, device="cpu", data_root=tmp)
     assert rest["hashes"] == whole["hashes"][2:]
+
+
+def test_replay_loss_log_equals_the_training_metrics_bit_for_bit(runs, tmp_path):
+    """--loss-log: the replay's per-step mean loss and gradient norm are the numbers the trainer logged, exactly"""
+    tmp, whole, first = runs
+    log = tmp_path / "losses.jsonl"
+    r = audit_replay(from_init=True, descriptor_checkpoint=whole["run_dir"] + "/checkpoints/step_000000004", data_root=tmp, until_step=4,
+                     loss_log=str(log))
+    assert r["match"] is True
+    mine = [json.loads(l) for l in log.read_text().splitlines()]
+    theirs = [json.loads(l) for l in open(whole["run_dir"] + "/logs/metrics.jsonl")][:4]
+    assert [m["step"] for m in mine] == [1, 2, 3, 4]
+    assert [m["loss"] for m in mine] == [t["loss"] for t in theirs]
+    assert [m["grad_norm"] for m in mine] == [t["grad_norm_pre_clip"] for t in theirs]
