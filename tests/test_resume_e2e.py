@@ -175,3 +175,33 @@ def test_replay_loss_log_equals_the_training_metrics_bit_for_bit(runs, tmp_path)
     assert [m["step"] for m in mine] == [1, 2, 3, 4]
     assert [m["loss"] for m in mine] == [t["loss"] for t in theirs]
     assert [m["grad_norm"] for m in mine] == [t["grad_norm_pre_clip"] for t in theirs]
+
+
+def test_skipped_steps_are_replayed_as_skips_and_a_halt_ends_the_run(tmp_path):
+    """spike protocol through the loop: with a threshold below every gradient norm every step from ``start_step`` on is
+    skipped (a fresh spike, then its cool-down skip, alternately): weights stay untouched while data is consumed, and the
+    replay takes the same decisions, from the seed and from a checkpoint taken inside a cool-down; with a shorter cool-down
+    the fresh spikes reach the halt count and the run stops"""
+    tmp = str(tmp_path)
+    over = LONG + ["train.spike.grad_norm_threshold=0.0001", "train.spike.skip_steps_on_spike=2", "train.spike.skips_in_window_to_halt=3",
+                   "train.spike.halt_window_steps=100", "train.spike.start_step=1"]
+    res = train(tiny_cfg(tmp, over + ["run.run_id=spiky"]), device="cpu", data_root=tmp)
+    rows = [json.loads(l) for l in open(res["run_dir"] + "/logs/metrics.jsonl")]
+    skipped = [r["skipped"] for r in rows]
+    assert skipped == [False, True, True, True, True], skipped                       # the first step is before start_step
+    assert rows[-1]["skipped_steps_total"] == 4 and "halted" not in res                # fresh spikes at steps 1 and 3 only: below the halt count
+    from open_transformers_b200.cli.hash_ckpt import hash_checkpoint
+
+    assert hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000002", include_optimizer=False) == \
+        hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000004", include_optimizer=False)   # no update in between
+    ck = res["run_dir"] + "/checkpoints/step_000000004"
+    r = audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=4)
+    assert r["match"] is True
+    r = audit_replay(res["run_dir"] + "/checkpoints/step_000000002", data_root=tmp, until_step=4)     # spike state restored from the checkpoint
+    assert r["match"] is True
+    calm = train(tiny_cfg(tmp, LONG + ["run.run_id=calm"]), device="cpu", data_root=tmp)
+    assert dict(calm["hashes"])[4] != dict(res["hashes"])[4]
+    halting = over[:-4] + ["train.spike.skip_steps_on_spike=1", "train.spike.skips_in_window_to_halt=2", "train.spike.halt_window_steps=100",
+                           "train.spike.start_step=0"]
+    halted = train(tiny_cfg(tmp, halting + ["run.run_id=halts"]), device="cpu", data_root=tmp)
+    assert "halted" in halted and halted["step"] < 5
