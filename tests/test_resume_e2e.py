@@ -205,3 +205,21 @@ def test_skipped_steps_are_replayed_as_skips_and_a_halt_ends_the_run(tmp_path):
                            "train.spike.start_step=0"]
     halted = train(tiny_cfg(tmp, halting + ["run.run_id=halts"]), device="cpu", data_root=tmp)
     assert "halted" in halted and halted["step"] < 5
+
+
+def test_batch_size_phase_change_mid_run_trains_replays_and_resumes(tmp_path):
+    """the global batch doubles after 512 tokens (two micro-batches per virtual rank instead of one): trained, replayed from
+    the seed across the change, and resumed from the checkpoint that sits on it"""
+    tmp = str(tmp_path)
+    over = ["train.total_tokens=2048", "train.ckpt_every_steps=2", "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=512",
+            "train.global_batch_tokens.late=512", "train.warmup_to_main_at_tokens=512", "train.main_to_late_at_tokens=100000"]
+    res = train(tiny_cfg(tmp, ["run.run_id=phases"] + over), device="cpu", data_root=tmp)
+    rows = [json.loads(l) for l in open(res["run_dir"] + "/logs/metrics.jsonl")]
+    assert [r["microbatches"] for r in rows] == [2, 2, 4, 4, 4] and [r["consumed_tokens"] for r in rows] == [256, 512, 1024, 1536, 2048]
+    ck4 = res["run_dir"] + "/checkpoints/step_000000004"
+    assert audit_replay(from_init=True, descriptor_checkpoint=ck4, data_root=tmp, until_step=4)["match"] is True
+    ck2 = res["run_dir"] + "/checkpoints/step_000000002"
+    assert audit_replay(ck2, data_root=tmp, until_step=4)["match"] is True
+    first = train(tiny_cfg(tmp, ["run.run_id=phases2"] + over), device="cpu", data_root=tmp, max_steps=2)
+    rest = train(tiny_cfg(tmp, ["run.run_id=phases2"] + over), resume_from=first["run_dir"] + "/checkpoints/step_000000002", device="cpu", data_root=tmp)
+    assert first["hashes"] + rest["hashes"] == res["hashes"]
