@@ -223,3 +223,21 @@ def test_batch_size_phase_change_mid_run_trains_replays_and_resumes(tmp_path):
     first = train(tiny_cfg(tmp, ["run.run_id=phases2"] + over), device="cpu", data_root=tmp, max_steps=2)
     rest = train(tiny_cfg(tmp, ["run.run_id=phases2"] + over), resume_from=first["run_dir"] + "/checkpoints/step_000000002", device="cpu", data_root=tmp)
     assert first["hashes"] + rest["hashes"] == res["hashes"]
+
+
+def test_rewarm_after_a_resume_is_recorded_and_replayed(runs, tmp_path):
+    """schedule.rewarm_on_resume: the resumed run ramps the learning rate from zero over ``rewarm_tokens``, anchored at the
+    resume point; the anchor travels in the resumed run's checkpoints, so the boundary interval replays with them as
+    descriptor"""
+    tmp, whole, first = runs
+    old = first["run_dir"] + "/checkpoints/step_000000002"
+    cfg = tiny_cfg(tmp, LONG + ["run.run_id=rewarm", "run.output_dir=%s/runs" % tmp_path, "++schedule.rewarm_on_resume=true", "++schedule.rewarm_tokens=512"])
+    res = train(cfg, resume_from=old, device="cpu", data_root=tmp)
+    rows = [json.loads(l) for l in open(res["run_dir"] + "/logs/metrics.jsonl")]
+    base = {r["step"]: r["lr"] for r in (json.loads(l) for l in open(whole["run_dir"] + "/logs/metrics.jsonl"))}
+    assert [r["step"] for r in rows] == [3, 4, 5]
+    assert rows[0]["lr"] == 0.0 and rows[1]["lr"] == pytest.approx(0.5 * base[4]) and rows[2]["lr"] == pytest.approx(base[5])
+    new_first = res["run_dir"] + "/checkpoints/step_000000004"
+    assert Checkpointer.read_meta(new_first).rewarm_anchor_tokens == 512
+    r = audit_replay(old, descriptor_checkpoint=new_first, data_root=tmp, until_step=4, expect_hash=dict(res["hashes"])[4])
+    assert r["match"] is True and dict(res["hashes"])[4] != dict(whole["hashes"])[4]
