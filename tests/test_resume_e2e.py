@@ -241,3 +241,19 @@ def test_rewarm_after_a_resume_is_recorded_and_replayed(runs, tmp_path):
     assert Checkpointer.read_meta(new_first).rewarm_anchor_tokens == 512
     r = audit_replay(old, descriptor_checkpoint=new_first, data_root=tmp, until_step=4, expect_hash=dict(res["hashes"])[4])
     assert r["match"] is True and dict(res["hashes"])[4] != dict(whole["hashes"])[4]
+
+
+@pytest.mark.parametrize("extra", [["++train.state_hash.include_grads=false"], ["++train.state_hash.include_batch=false"],
+                                   ["++train.state_hash.tensor_digest=tree", "++train.state_hash.include_grads=false", "++train.state_hash.include_batch=false"],
+                                   ["model.modules.attention=gqa_qknorm_repop", "model.qk_norm=true", "model.qk_norm_gain=true", "++train.qk_gain_clamp=1.0001",
+                                    "++train.qk_freeze_q_gains_until_step=2"]])
+def test_hash_content_switches_and_gain_controls_replay(tmp_path, extra):
+    """what the state hash covers (gradients, batch digest, raw bytes or tree digests) and the QK-gain controls (clamp
+    after the update, query gains frozen for the first steps) are part of the recipe: the replay follows them"""
+    tmp = str(tmp_path)
+    res = train(tiny_cfg(tmp, ["train.ckpt_every_steps=2", *extra]), device="cpu", data_root=tmp)
+    ck = res["run_dir"] + "/checkpoints/step_000000002"
+    assert audit_replay(ck, data_root=tmp, until_step=3)["match"] is True
+    assert audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=3)["match"] is True
+    plain = train(tiny_cfg(tmp + "/p", ["train.ckpt_every_steps=2"]), device="cpu", data_root=tmp + "/p")
+    assert plain["hashes"][-1][1] != res["hashes"][-1][1]
