@@ -278,7 +278,18 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         spike.load_state_dict(side["spike_protocol"])
         rewarm_anchor = meta.rewarm_anchor_tokens if descriptor_checkpoint is not None else state_meta.rewarm_anchor_tokens
     if until_step is None:
-        until_step = step + max(cfg.train.ckpt_every_steps, 1)
+        # default span: one checkpoint interval of the recipe (steps, or tokens when the recipe clocks checkpoints by tokens)
+        if cfg.train.ckpt_every_steps == 0 and cfg.train.ckpt_every_tokens > 0:
+            from ..train.batch_schedule import iter_step_plans
+
+            every, c, until_step = cfg.train.ckpt_every_tokens, consumed, step
+            for plan in iter_step_plans(consumed, 0, cfg.train, start_step=step):
+                until_step += 1
+                c += plan.tokens_this_step
+                if c // every > plan.consumed_tokens // every or c >= cfg.train.total_tokens:
+                    break
+        else:
+            until_step = step + max(cfg.train.ckpt_every_steps, 1)
     if until_step <= step:
         raise AuditError("--until-step %d is not beyond the starting step %d" % (until_step, step))
 

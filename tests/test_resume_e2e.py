@@ -257,3 +257,18 @@ def test_hash_content_switches_and_gain_controls_replay(tmp_path, extra):
     assert audit_replay(from_init=True, descriptor_checkpoint=ck, data_root=tmp, until_step=3)["match"] is True
     plain = train(tiny_cfg(tmp + "/p", ["train.ckpt_every_steps=2"]), device="cpu", data_root=tmp + "/p")
     assert plain["hashes"][-1][1] != res["hashes"][-1][1]
+
+
+def test_token_clocked_checkpoints_and_latest(tmp_path):
+    """train.ckpt_every_tokens (with ckpt_every_steps = 0): a checkpoint whenever the consumed-token count crosses a multiple,
+    plus the final one; ``latest`` finds the newest complete one and ignores a half-written directory"""
+    tmp = str(tmp_path)
+    res = train(tiny_cfg(tmp, LONG + ["train.ckpt_every_steps=0", "train.ckpt_every_tokens=512"]), device="cpu", data_root=tmp)
+    ckdir = Path(res["run_dir"]) / "checkpoints"
+    assert sorted(p.name for p in ckdir.glob("step_*")) == ["step_000000002", "step_000000004", "step_000000005"]
+    ck = Checkpointer(res["run_dir"])
+    assert ck.complete_steps() == [2, 4, 5] and Path(ck.latest()).name == "step_000000005"
+    (ckdir / "step_000000005" / "_COMPLETE").unlink()              # a writer that died before finishing
+    assert Path(ck.latest()).name == "step_000000004"
+    r = audit_replay(str(ckdir / "step_000000002"), data_root=tmp)  # default span: to the next checkpoint of the cadence
+    assert r["step"] == 4 and r["match"] is True
