@@ -103,6 +103,14 @@ def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
     rc, weights_only = _run(hash_main, [ck, "--weights-only"], capsys)
     assert weights_only.strip() != out.strip()
     assert hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000003") != hash_checkpoint(ck)
+    rc, out = _run(inspect_main, [ck, "--full-config"], capsys)
+    assert rc == 0 and "bytes, --full-config" not in out and "vocab_size" in out
+    from open_transformers_b200.cli.dcp_safetensors import main as st_main
+
+    rc, out = _run(st_main, ["pack", ck, str(tmp_path / "one.safetensors")], capsys)
+    assert rc == 0 and json.loads(out)["tensors"] > 0
+    rc, out = _run(st_main, ["unpack", str(tmp_path / "one.safetensors"), str(tmp_path / "un" / "checkpoints" / "step_000000002")], capsys)
+    assert rc == 0 and hash_checkpoint(json.loads(out)["dir"]) == hash_checkpoint(ck)
 
 
 def test_train_command_creates_synthetic_data_resumes_and_refuses_to_overwrite(tmp_path, capsys):
