@@ -15,7 +15,8 @@ Two timed regions of K steps each, both on the device with CUDA events, max over
   * `e2e`:   every micro-batch is copied from pinned host memory inside the timed region and the
              step's loss is read back to the host every step, through the public
              `TrainEngine` API.
-`--impl reference` reports why the reference cannot run on this image.
+`--impl reference` times the unmodified reference training loop (`baseline/_ref`) over a stock-torch stand-in of
+its closed kernel library, same config, steps and warm-up (`baseline/reference_arm.py`).
 """
 from __future__ import annotations
 
@@ -71,11 +72,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm():
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "pip install of the reference source tree fails offline (build backend hatchling absent) and its model modules import "
-                      "the closed-source `repop` kernel library plus hydra-core/omegaconf, none of which exist on this image"}))
-    return 0
+def reference_arm(args) -> int:
+    """The unmodified reference training loop over a stock-torch stand-in of its closed kernel library
+    (`baseline/reference_arm.py`); imports nothing of this package."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("reference_arm", os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "reference_arm.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.run(args.gpus, args.steps, args.warmup, tiny=os.environ.get("OTB_REFERENCE_ARM_TINY") == "1")
 
 
 def main() -> int:
@@ -91,7 +96,7 @@ def main() -> int:
     ap.add_argument("--tp-fused", action="store_true", help="with --tp: peer-memory all-gather->GEMM / chained GEMM kernels (run.tp_fused)")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
 
     import torch
     import torch.distributed as dist

@@ -8,15 +8,50 @@ import sys
 import time
 from pathlib import Path
 
+import pytest
+
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_reference_arm_prints_one_json_line_and_exits_zero():
+def _reference_arm(env_extra, timeout=600):
+    env = dict(os.environ, **env_extra)
+    env.pop("RANK", None)
+    env.pop("WORLD_SIZE", None)
     r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
-                       capture_output=True, text=True, timeout=120)
-    assert r.returncode == 0
-    line = json.loads(r.stdout.strip())
+                       capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, r.stdout
+    return json.loads(lines[0])
+
+
+def test_reference_arm_says_why_when_the_reference_copy_is_absent(tmp_path):
+    line = _reference_arm({"OTB_REFERENCE_DIR": str(tmp_path / "nothing_here")}, timeout=120)
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_reference_arm_refuses_the_full_size_step_without_a_gpu():
+    if not (ROOT / "baseline" / "_ref" / "pretrain").is_dir():
+        pytest.skip("no copy of the reference under baseline/_ref")
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is visible")
+    line = _reference_arm({}, timeout=300)
+    assert line["impl"] == "reference" and "no CUDA device" in line["unavailable"]
+
+
+def test_reference_arm_times_the_unmodified_reference_loop_on_a_tiny_model():
+    """The whole arm on CPU: the reference's own train() from baseline/_ref over the stock-torch stand-in, a two-layer
+    model, three warm-up and two timed steps; the line carries the bench contract's keys and names no library of ours."""
+    if not (ROOT / "baseline" / "_ref" / "pretrain").is_dir():
+        pytest.skip("no copy of the reference under baseline/_ref")
+    line = _reference_arm({"OTB_REFERENCE_ARM_TINY": "1", "CUDA_VISIBLE_DEVICES": ""})
+    assert line["impl"] == "reference" and "unavailable" not in line
+    assert line["steps"] == 2 and line["warmup"] == 3 and line["value"] > 0 and line["unit"] == "tokens/s"
+    assert line["e2e"]["value"] == line["value"] and line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0
+    assert line["reference_step_records"]["n"] == 2 and len(line["final_hash"]) == 64
+    assert "native_libs" not in line
 
 
 def test_clock_sampler_reads_clocks_and_throttle_reasons(tmp_path, monkeypatch):
