@@ -107,6 +107,11 @@ def run(gpus: int, steps: int, warmup: int, overrides: list[str] | None = None, 
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("WANDB_MODE", "disabled")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if "RANK" not in os.environ and not tiny:
+        # the reference is always started by torchrun (scripts/launch_single_node.sh), also on one GPU: its device mesh
+        # needs a process group. A bare `python bench.py --impl reference` gets the environment of a one-rank launch.
+        os.environ.update({"RANK": "0", "WORLD_SIZE": "1", "LOCAL_RANK": "0"})
+        os.environ.setdefault("MASTER_PORT", str(29600 + os.getpid() % 2000))
     for p in (str(SHIMS), str(REF)):
         if p not in sys.path:
             sys.path.insert(0, p)

@@ -165,7 +165,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     from ..train import state_hash as SH
     from ..train.checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
     from ..train.engine import TrainEngine
-    from ..train.spike_protocol import SpikeProtocol
+    from ..train.spike_protocol import Halt, SpikeProtocol
     from ..train.qk_gain_control import clamp_qk_gains, zero_q_gain_grads
     from .cpu_threads import configure_cpu_threads
 
@@ -307,9 +307,15 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             break
         accum = plan.microbatches // V
         lr = sched(consumed, tr.total_tokens) * rewarm_factor(consumed, rewarm_anchor, cfg.schedule.rewarm_tokens)
+        engine.global_step = step
         engine.zero_grads()
         ces = []
-        for v, k, windows in batches:      # replica-major virtual-rank order, micro-batches ascending
+        if engine.fold:
+            # the loader yields micro-batches in global order (owner m mod V), which interleaves the virtual ranks; the
+            # folded mode has one work buffer, so it runs virtual rank by virtual rank, each rank's micro-batches ascending
+            batches = sorted(batches, key=lambda b: (b[0], b[1]))
+        halted = None
+        for v, k, windows in batches:
             batch = collate(windows)
             if sh_cfg.include_batch:
                 hashers[v].update(batch)
@@ -318,19 +324,24 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             if empty_cache_per_mb:
                 torch.cuda.empty_cache()
             if engine.fold and k == accum - 1:
-                engine.fold_virtual_rank(v)  # batches arrive virtual rank by virtual rank, micro-batches ascending
+                engine.fold_virtual_rank(v)  # all of v's micro-batches are in the work buffer
         memlog("step %d: after forward/backward" % (step + 1), device)
         grad_norm = engine.reduce_gradients()
         total = 0.0
         for _, _, c in ces:
             total += c
         loss_mean = total / max(len(ces), 1)
+        v0 = [c for v, _, c in sorted(ces, key=lambda t: (t[0], t[1])) if v == 0]
+        v0_sum = 0.0
+        for c in v0:
+            v0_sum += c
+        spike_loss = v0_sum / max(len(v0), 1)  # virtual rank 0's mean loss, as in the training loop
         zero_q_gain_grads(engine.named_grads(), step, tr.qk_freeze_q_gains_until_step)  # mirrors train/loop.py
-        if spike.should_skip(grad_norm, loss_mean, step):
+        if spike.should_skip(grad_norm, spike_loss, step):
             try:
                 spike.record_skip(step)
-            except Exception:
-                pass
+            except Halt as h:
+                halted = str(h)  # the step's hash is still recorded below, then the replay ends (as the run did)
             engine.skip_step()
         else:
             engine.optimizer_step(lr, engine.clip_coefficient(grad_norm, tr.grad_clip))
@@ -353,6 +364,13 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         if phases:
             log.info("step %d phases %s", step, json.dumps({k: round(v, 3) for k, v in phases.items()}))
         log.info("replayed step %d loss %.6f grad_norm %.6f", step, loss_mean, grad_norm)
+        if halted is not None:
+            if last_hash is None or not (hash_due or ckpt_due or step == until_step):
+                bd = SH.combine_batch_digests([hashers[v].local_digest() for v in range(V)]) if sh_cfg.include_batch else None
+                last_hash = engine.sharded_state_hash(chained, bd, include_grads=sh_cfg.include_grads, tensor_digest=sh_cfg.tensor_digest)
+            result["halted"] = halted
+            log.error("the spike protocol halted the run at step %d: %s", step, halted)
+            break
     result["seconds_per_step"] = (time.time() - t_start) / max(len(loss_rows), 1)
     if torch.cuda.is_available() and device.startswith("cuda"):
         result["peak_memory_bytes"] = int(torch.cuda.max_memory_allocated())

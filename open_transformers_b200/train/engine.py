@@ -230,6 +230,7 @@ class TrainEngine:
             g.zero_()
         self._stale = [False] * len(self.grads)
         self.opt_step = 0
+        self.global_step = None  # set by the loop / the replay: QAT gates follow the run's step, not the optimizer's
 
         # ---- chunk tables on the device, ownership
         dev = self.device
@@ -506,7 +507,7 @@ class TrainEngine:
                 self._tp_state.ws.barrier()
         qat = self.cfg.model.qat
         if qat.enabled and qat.enable_at_step > 0:  # bf16 warm start: a pure function of (step, config)
-            set_qat_active(self.model, self.opt_step >= qat.enable_at_step)
+            set_qat_active(self.model, self._run_step() >= qat.enable_at_step)
         self.model.train()
         self._tick(None)
         z_coeff = self.cfg.model.z_loss.coeff if self.cfg.model.z_loss.enabled else 0.0
@@ -782,6 +783,11 @@ class TrainEngine:
         h = np.float32(max_norm) / np.float32(np.float32(grad_norm) + np.float32(1e-6))
         return float(min(h, np.float32(1.0)))
 
+    def _run_step(self) -> int:
+        """Index of the step being computed: the run's step counter when the caller maintains `global_step` (it keeps
+        counting through skipped steps and through a resume that resets the optimizer), else the optimizer's own."""
+        return self.opt_step if self.global_step is None else int(self.global_step)
+
     def optimizer_step(self, lr: float, clip: float) -> None:
         """Step 4 on the owned segments; pushes the new weights to every rank."""
         self._wait_pending_hash()
@@ -811,12 +817,15 @@ class TrainEngine:
         self._tick("opt")
         self._barrier()  # peers' stores into this rank's weights are complete before the next forward
         K.weight_epoch = (K.weight_epoch or 0) + 1
+        self._refresh_scales_if_due(self.opt_step if self.global_step is None else int(self.global_step) + 1)
+
+    def _refresh_scales_if_due(self, steps_done: int) -> None:
+        """After the update (or the skipped update), before the state hash: every rank derives the same LSQ step sizes
+        from its (identical) compute weights (reference src/pretrain/train/loop.py:1069-1084; it runs on skipped steps too)."""
         refresh = self.cfg.model.qat.scale_refresh_every_n_steps
-        if self.cfg.model.qat.enabled and refresh > 0 and self.opt_step % refresh == 0:
-            # after the update, before the state hash: every rank derives the same step sizes from its
-            # (identical) compute weights (reference src/pretrain/train/loop.py:1069-1084)
+        if self.cfg.model.qat.enabled and refresh > 0 and steps_done % refresh == 0:
             refresh_lsq_weight_scales(self.model)
-            K.weight_epoch += 1
+            K.weight_epoch = (K.weight_epoch or 0) + 1
 
     def _muon_step(self, lr: float, clip: float) -> None:
         """Muon on the hidden matrices: momentum (kept in the first-moment buffer; the second stays zero), Nesterov
@@ -840,6 +849,8 @@ class TrainEngine:
 
     def skip_step(self) -> None:
         self._barrier()
+        if self.global_step is not None:
+            self._refresh_scales_if_due(int(self.global_step) + 1)
 
     # --------------------------------------------------------------------------------- hash
     def _hash_fields(self, include_grads: bool):

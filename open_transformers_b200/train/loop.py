@@ -121,7 +121,15 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
         stream_state = GlobalStreamState.from_json(side["global_stream"]) if side["global_stream"] else None
         spike.load_state_dict(side["spike_protocol"])
         hashers = {v: SH.RunningBatchHasher(side["batch_chains"][v]) for v in hosted}
-        rewarm_anchor = consumed if cfg.schedule.rewarm_on_resume else meta0.rewarm_anchor_tokens
+        # LR re-warm anchor (reference src/pretrain/train/loop.py:565-586): a resume that resets the optimizer ramps from the
+        # resume point; a moments-kept resume with rewarm_on_resume continues a recorded ramp, or starts one here; else none
+        if train_cfg.resume_reset_optimizer:
+            rewarm_anchor = consumed
+        elif cfg.schedule.rewarm_on_resume and cfg.schedule.rewarm_tokens > 0:
+            prev = meta0.rewarm_anchor_tokens
+            rewarm_anchor = prev if (prev is not None and prev >= 0) else consumed
+        else:
+            rewarm_anchor = None
     else:
         check_linear_anneal_resume(cfg, None)
 
@@ -203,8 +211,9 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                 raise RuntimeError("step %d has %d micro-batches, not a multiple of the %d virtual ranks" % (step, M, V))
             accum = M // V
             lr = sched(consumed, train_cfg.total_tokens) * rewarm_factor(consumed, rewarm_anchor, cfg.schedule.rewarm_tokens)
+            engine.global_step = step
             engine.zero_grads()
-            ces, zs = [], []
+            ces, zs, owners = [], [], []
             for v, k, windows in batches:
                 batch = collate(windows, pin=engine.is_cuda)
                 if sh_cfg.include_batch:
@@ -214,6 +223,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                 ce, z = engine.forward_backward(hosted.index(v), ids, labels, accum)
                 ces.append(ce.detach())
                 zs.append(z.detach())
+                owners.append(v)
             finish_pending_hash()  # the previous step's digests ran under this step's forward/backward
             grad_norm = engine.reduce_gradients()
             local_ce = [float(c) for c in ces]
@@ -221,8 +231,12 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             ce_sum, n_mb = deterministic_scalar_sum(local_ce if lead else [], world)
             z_sum, _ = deterministic_scalar_sum([float(z) for z in zs] if lead else [], world)
             loss_mean = ce_sum / max(n_mb, 1)
+            # the spike gate looks at virtual rank 0's mean loss, on every rank, as the replay does (reference
+            # src/pretrain/train/loop.py:977-992, src/pretrain/cli/audit_replay.py:2548-2551)
+            v0_sum, v0_n = deterministic_scalar_sum([c for c, v in zip(local_ce, owners) if v == 0] if lead else [], world)
+            spike_loss = v0_sum / max(v0_n, 1)
             zero_q_gain_grads(engine.named_grads(), step, train_cfg.qk_freeze_q_gains_until_step)
-            skipped = spike.should_skip(grad_norm, loss_mean, step)
+            skipped = spike.should_skip(grad_norm, spike_loss, step)
             clip = engine.clip_coefficient(grad_norm, train_cfg.grad_clip)
             if skipped:
                 spike.record_skip(step)

@@ -19,7 +19,7 @@ def clamp_qk_gains(model, max_gain: float) -> int:
     n = 0
     for which in ("q", "k"):
         for _, p in _gains(model, which):
-            p.clamp_(max=max_gain)
+            p.clamp_(min=-max_gain, max=max_gain)  # symmetric, as the reference's clamp_(-cap, cap)
             n += 1
     # the compute-dtype copies that the forward pass reads (installed by the training engine) follow on every rank
     for mod in model.modules():
@@ -27,7 +27,7 @@ def clamp_qk_gains(model, max_gain: float) -> int:
         if cw is not None and type(mod).__name__ == "RMSNorm" and any(mod is getattr(parent, a, None)
                                                                        for parent in model.modules() for a in ("q_norm", "k_norm")):
             if cw.data_ptr() != mod.weight.data_ptr():
-                cw.clamp_(max=max_gain)
+                cw.clamp_(min=-max_gain, max=max_gain)
     return n
 
 

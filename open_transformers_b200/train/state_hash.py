@@ -174,9 +174,9 @@ def _prev_bytes(prev: bytes | str | None) -> bytes:
         return ZERO_DIGEST
     if isinstance(prev, str):
         prev = bytes.fromhex(prev)
-    if len(prev) != DIGEST_SIZE:
-        raise ValueError("previous digest must be %d bytes, got %d" % (DIGEST_SIZE, len(prev)))
-    return bytes(prev)
+    prev = bytes(prev)
+    # a shorter digest is zero-padded, a longer one truncated (reference src/pretrain/train/state_hash.py:116-127)
+    return prev + b"\0" * (DIGEST_SIZE - len(prev)) if len(prev) < DIGEST_SIZE else prev[:DIGEST_SIZE]
 
 
 def feed_tensor(h, tag: str, t: torch.Tensor, tensor_digest: str = "raw", precomputed: bytes | None = None) -> None:
@@ -278,14 +278,22 @@ def combine_shard_state(local_digests: Sequence[bytes], num_ranks: int) -> bytes
     return h.digest()
 
 
-def finalize_state_hash(shard_state: bytes, param_groups: Sequence[Mapping], prev: bytes | str | None,
+def finalize_state_hash(shard_state: bytes, param_groups: Sequence[Mapping] | None, prev: bytes | str | None,
                         batch_digest: bytes | None) -> str:
+    """v3 stream: tag, prev, shard_state, then `param_groups` only when there is an optimizer and `batch_digest` only
+    when one is given (reference src/pretrain/train/state_hash.py:492-528)."""
+    if len(shard_state) != DIGEST_SIZE:
+        raise ValueError("shard_state must be %d bytes, got %d" % (DIGEST_SIZE, len(shard_state)))
     h = _new()
     h.update(V3_TAG)
     h.update(b"prev\0" + _prev_bytes(prev))
     h.update(b"shard_state\0" + shard_state)
-    h.update(b"param_groups\0" + param_groups_json(param_groups))
-    h.update(b"batch_digest\0" + (batch_digest if batch_digest is not None else ZERO_DIGEST))
+    if param_groups is not None:
+        h.update(b"param_groups\0" + param_groups_json(param_groups))
+    if batch_digest is not None:
+        if len(batch_digest) != DIGEST_SIZE:
+            raise ValueError("batch_digest must be %d bytes, got %d" % (DIGEST_SIZE, len(batch_digest)))
+        h.update(b"batch_digest\0" + batch_digest)
     return h.hexdigest()
 
 

@@ -191,6 +191,21 @@ def test_replay_with_folded_gradients_and_verified_spill(trained, tmp_path):
     eng.close()
 
 
+def test_folded_replay_with_gradient_accumulation_matches_the_plain_replay(tmp_path):
+    """Two micro-batches per virtual rank: the loader hands them out interleaved (v0k0, v1k0, v0k1, v1k1); the folded
+    replay has one work buffer and must run rank by rank. Its digests equal the run's and the plain replay's."""
+    tmp = str(tmp_path)
+    cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=1", "train.global_batch_tokens.warmup=512", "train.global_batch_tokens.main=512",
+                         "train.global_batch_tokens.late=512", "train.total_tokens=1024"])
+    mb_tokens = cfg.train.micro_batch_size * cfg.train.seq_len * cfg.run.virtual_dp_size
+    assert 512 // mb_tokens >= 2, "the recipe must accumulate at least two micro-batches per virtual rank"
+    res = train(cfg, device="cpu", data_root=tmp)
+    ck = res["run_dir"] + "/checkpoints/step_000000001"
+    plain = audit_replay(ck, data_root=tmp, until_step=2)
+    folded = audit_replay(ck, data_root=tmp, until_step=2, offload_grads=True)
+    assert plain["match"] is True and folded["match"] is True and plain["state_hash"] == folded["state_hash"] == res["hashes"][-1][1]
+
+
 def test_replay_with_offloaded_moments_and_master(trained, tmp_path):
     """--offload-optimizer / --offload-master keep the moments and the fp32 master weights in files; the digests are
     those of the plain replay, from a checkpoint and from the initial state, and the files hold the final state."""

@@ -54,6 +54,10 @@ def test_qk_gain_clamp_and_frozen_query_gains():
     assert clamp_qk_gains(m, 0.0) == 0 and float(m.q_norm.weight[0]) == 3.0
     assert clamp_qk_gains(m, 2.0) == 2
     assert float(m.q_norm.weight.max()) == 2.0 and float(m.k_norm.weight.max()) == 0.5
+    with torch.no_grad():
+        m.k_norm.weight[3] = -7.0  # the clamp is symmetric: a gain drifting below -cap is bounded too
+    clamp_qk_gains(m, 2.0)
+    assert float(m.k_norm.weight.min()) == -2.0
     grads = {"attn.q_norm.weight": torch.ones(32), "attn.k_norm.weight": torch.ones(32), "attn.wq.weight": torch.ones(4, 4)}
     assert zero_q_gain_grads(grads, step=3, freeze_until_step=5) == 1
     assert float(grads["attn.q_norm.weight"].sum()) == 0.0 and float(grads["attn.k_norm.weight"].sum()) == 32.0

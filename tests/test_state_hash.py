@@ -52,8 +52,35 @@ def test_chaining_and_prev_validation():
     h1 = SH.compute_state_hash(params)
     assert SH.compute_state_hash(params, prev=h1) != h1
     assert SH.compute_state_hash(params, prev=h1) == SH.compute_state_hash(params, prev=bytes.fromhex(h1))
+    # a previous digest of the wrong length is zero-padded or truncated to 32 bytes, as the reference does
+    assert SH.compute_state_hash(params, prev=b"short") == SH.compute_state_hash(params, prev=b"short" + b"\0" * 27)
+    assert SH.compute_state_hash(params, prev=bytes.fromhex(h1) + b"tail") == SH.compute_state_hash(params, prev=h1)
+
+
+def test_final_v3_stream_byte_for_byte():
+    """The v3 stream against a hand-built one: `param_groups` only with an optimizer, `batch_digest` only when given."""
+    import hashlib
+    import json
+
+    shard_state, prev, bd = b"\7" * 32, b"\3" * 32, b"\5" * 32
+    groups = [{"lr": 0.5, "betas": (0.9, 0.95), "weight_decay": 0.1, "params": [0, 1]}]
+
+    def stream(with_groups, with_batch, with_prev):
+        h = hashlib.blake2b(digest_size=32)
+        h.update(b"pretrain.state_hash.v3\n")
+        h.update(b"prev\0" + (prev if with_prev else b"\0" * 32))
+        h.update(b"shard_state\0" + shard_state)
+        if with_groups:
+            h.update(b"param_groups\0" + json.dumps([{"lr": 0.5, "betas": [0.9, 0.95], "weight_decay": 0.1}], sort_keys=True, default=str).encode())
+        if with_batch:
+            h.update(b"batch_digest\0" + bd)
+        return h.hexdigest()
+
+    assert SH.finalize_state_hash(shard_state, groups, prev, bd) == stream(True, True, True)
+    assert SH.finalize_state_hash(shard_state, groups, None, None) == stream(True, False, False)
+    assert SH.finalize_state_hash(shard_state, None, prev.hex(), None) == stream(False, False, True)
     with pytest.raises(ValueError):
-        SH.compute_state_hash(params, prev=b"short")
+        SH.finalize_state_hash(shard_state, groups, None, b"short")
 
 
 def test_sharded_combine_matches_single_process_reconstruction():
