@@ -151,7 +151,7 @@ def main() -> int:
                 else:
                     a, b = host[(step, v, k)]
                     ids, labels = a.to(device, non_blocking=True), b.to(device, non_blocking=True)
-                ce, z = eng.forward_backward(vi, ids, labels, accum)
+                ce, z = eng.forward_backward(vi, ids, labels, accum, last=(vi == len(hosted) - 1 and k == accum - 1))
                 last_ce = ce
         if not args.no_hash:
             flush_hash()  # the previous step's digests ran under this step's forward/backward; fold them in while it drains

@@ -315,11 +315,12 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             # folded mode has one work buffer, so it runs virtual rank by virtual rank, each rank's micro-batches ascending
             batches = sorted(batches, key=lambda b: (b[0], b[1]))
         halted = None
-        for v, k, windows in batches:
+        batches = list(batches)
+        for j, (v, k, windows) in enumerate(batches):
             batch = collate(windows)
             if sh_cfg.include_batch:
                 hashers[v].update(batch)
-            ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum)
+            ce, z = engine.forward_backward(v, batch["input_ids"].to(dev), batch["labels"].to(dev), accum, last=j == len(batches) - 1)
             ces.append((v, k, float(ce.detach())))
             if empty_cache_per_mb:
                 torch.cuda.empty_cache()

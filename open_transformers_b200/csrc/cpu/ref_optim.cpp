@@ -53,6 +53,30 @@ int otb_cpu_grad_reduce(const void* const* srcs, int S, int R, const long* chunk
   }
   return 0;
 }
+// The same fold over the chunks listed in `chunk_ids` (one bucket of the reduction that runs under the backward pass).
+int otb_cpu_grad_reduce_ids(const void* const* srcs, int S, int R, const long* chunk_start, const int* chunk_len,
+                            const int* chunk_ids, int nids, float* out, float* chunk_sos_out) {
+  const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
+#pragma omp parallel for schedule(static)
+  for (int k = 0; k < nids; ++k) {
+    const int c = chunk_ids[k];
+    const long base = chunk_start[c];
+    const int len = chunk_len[c];
+    float rep[16];
+    for (int i = 0; i < len; ++i) {
+      for (int r = 0; r < R; ++r) {
+        float in = ((const float*)srcs[r * S])[base + i];
+        for (int s = 1; s < S; ++s) in = in + ((const float*)srcs[r * S + s])[base + i];
+        rep[r] = in * inv_s;
+      }
+      for (int st = 1; st < R; st *= 2)
+        for (int q = 0; q + st < R; q += 2 * st) rep[q] = rep[q] + rep[q + st];
+      out[base + i] = rep[0] * inv_r;
+    }
+    chunk_sos_out[c] = chunk_sos(out + base, len);
+  }
+  return 0;
+}
 int otb_cpu_chunk_sos(const float* x, const long* chunk_start, const int* chunk_len, int nchunks, float* chunk_sos_out) {
 #pragma omp parallel for schedule(static)
   for (int c = 0; c < nchunks; ++c) chunk_sos_out[c] = chunk_sos(x + chunk_start[c], chunk_len[c]);

@@ -56,10 +56,13 @@ __device__ __forceinline__ float block_tree_sum_256(float v, float* sh) {
 // start 16-byte aligned). One CTA per chunk.
 __global__ void __launch_bounds__(256)
 grad_reduce_kernel(ReduceSrc src, int S, int R, float inv_s, float inv_r, const long* __restrict__ chunk_start,
-                   const int* __restrict__ chunk_len, float* __restrict__ out, float* __restrict__ chunk_sos) {
+                   const int* __restrict__ chunk_len, const int* __restrict__ chunk_ids, float* __restrict__ out,
+                   float* __restrict__ chunk_sos) {
   __shared__ float sh[32];
-  const long base = chunk_start[blockIdx.x];
-  const int len = chunk_len[blockIdx.x];
+  // a launch covers either the first gridDim.x chunks of the table or, with `chunk_ids`, the listed ones (one bucket)
+  const int c = chunk_ids ? chunk_ids[blockIdx.x] : (int)blockIdx.x;
+  const long base = chunk_start[c];
+  const int len = chunk_len[c];
   float acc = 0.0f;
   for (int j = threadIdx.x * 8; j < len; j += 2048) {
     float o[8];
@@ -102,7 +105,45 @@ grad_reduce_kernel(ReduceSrc src, int S, int R, float inv_s, float inv_r, const 
     }
   }
   const float s = block_tree_sum_256(acc, sh);
-  if (threadIdx.x == 0) chunk_sos[blockIdx.x] = s;
+  if (threadIdx.x == 0) chunk_sos[c] = s;
+}
+
+// Readiness flags of the overlapped reduction. Every GPU owns an array of `buckets x P` words in peer-mapped memory;
+// word [b * P + r] takes the step's epoch when rank r's gradients of bucket b are final. A signal is one release store
+// per destination at system scope; a wait is a bounded acquire poll (no trap, no endless loop: when the budget runs
+// out the kernel records which word it gave up on in `status` and returns, and the host raises after its next sync).
+struct FlagDst {
+  uint32_t* p[MAX_DST];
+};
+__global__ void flag_signal_kernel(FlagDst dst, int ndst, int idx, uint32_t val) {
+  const int d = threadIdx.x;
+  if (d < ndst) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.p[d] + idx), "r"(val) : "memory");
+  }
+}
+__global__ void flag_wait_kernel(const uint32_t* flags, int first, int count, uint32_t val, unsigned long long budget_ns,
+                                 uint32_t* status, uint32_t code) {
+  const int t = threadIdx.x;
+  if (t >= count) return;
+  const uint32_t* f = flags + first + t;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t i = 0;; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v == val) return;
+    if ((i & 15u) == 15u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > budget_ns) break;
+    }
+    __nanosleep(200);
+  }
+  if (status) {
+    atomicExch(status, code);
+    atomicExch(status + 1, (uint32_t)(first + t));
+  }
 }
 
 // Squared-norm partials only (same chunk order), for tensors that are not reduced by this kernel.
@@ -260,7 +301,38 @@ extern "C" int otb_grad_reduce(const void* const* srcs, int S, int R, const long
   for (int i = 0; i < S * R; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
   const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
   grad_reduce_kernel<<<nchunks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, inv_s, inv_r, chunk_start,
-                                                                                  chunk_len, out, chunk_sos);
+                                                                                  chunk_len, nullptr, out, chunk_sos);
+  return (int)cudaGetLastError();
+}
+// The same reduction over the chunks listed in `chunk_ids` (indices into the chunk table; `chunk_sos` is indexed by
+// them as well): one bucket of the reduction that runs under the backward pass.
+extern "C" int otb_grad_reduce_ids(const void* const* srcs, int S, int R, const long* chunk_start, const int* chunk_len,
+                                   const int* chunk_ids, int nids, float* out, float* chunk_sos, void* stream) {
+  if (S * R > MAX_SRC || R > 16 || S < 1 || R < 1 || !chunk_ids) return -2;
+  if (nids <= 0) return 0;
+  ReduceSrc rs;
+  for (int i = 0; i < S * R; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
+  const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
+  grad_reduce_kernel<<<nids, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, inv_s, inv_r, chunk_start, chunk_len,
+                                                                               chunk_ids, out, chunk_sos);
+  return (int)cudaGetLastError();
+}
+// Writes `val` into word `idx` of every destination flag array (this GPU's and the peers'), after everything queued
+// before it on `stream`.
+extern "C" int otb_flag_signal(void* const* dsts, int ndst, int idx, unsigned val, void* stream) {
+  if (ndst < 1 || ndst > MAX_DST || idx < 0) return -2;
+  FlagDst fd{};
+  for (int i = 0; i < ndst; ++i) fd.p[i] = reinterpret_cast<uint32_t*>(dsts[i]);
+  flag_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(fd, ndst, idx, val);
+  return (int)cudaGetLastError();
+}
+// Holds `stream` until words [first, first + count) of this GPU's flag array equal `val`, for at most `budget_ns`; a
+// wait that runs out writes `code` to status[0] and the word's index to status[1] and lets the stream go on.
+extern "C" int otb_flag_wait(const void* flags, int first, int count, unsigned val, unsigned long long budget_ns,
+                             uint32_t* status, unsigned code, void* stream) {
+  if (count < 1 || count > 32 || first < 0) return -2;
+  flag_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint32_t*>(flags), first, count,
+                                                                         val, budget_ns, status, code);
   return (int)cudaGetLastError();
 }
 extern "C" int otb_chunk_sos(const float* x, const long* chunk_start, const int* chunk_len, int nchunks, float* chunk_sos,

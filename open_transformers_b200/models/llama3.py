@@ -54,6 +54,9 @@ class Llama3(nn.Module):
         self.norm_out = NORM.get(cfg.modules.norm)(cfg.d_model, eps=cfg.rms_norm_eps)
         self.activation_checkpoint = False
         self.ac_every_other_block = False
+        # set by the training engine for the last micro-batch of a step: called from the backward pass with a block's
+        # index once that block (and everything after it) has produced its weight gradients; -1 = the vocabulary head
+        self.bucket_notify = None
 
     @property
     def lm_head(self) -> nn.Module:
@@ -70,13 +73,19 @@ class Llama3(nn.Module):
         x = self.embedding.encode(input_ids, self.compute_dtype)
         if self.emb_norm is not None:
             x = self.emb_norm(x)
+        notify = self.bucket_notify if (torch.is_grad_enabled() and st is None) else None
         for i, blk in enumerate(self.blocks):
+            if notify is not None:
+                x = A.bucket_mark(x, notify, i)
             if self.activation_checkpoint and self.training and (not self.ac_every_other_block or i % 2 == 0):
                 from torch.utils.checkpoint import checkpoint
                 x = checkpoint(blk, x, cos, sin, use_reentrant=False, preserve_rng_state=False)
             else:
                 x = blk(x, cos, sin)
-        return self.norm_out(x)
+        x = self.norm_out(x)
+        if notify is not None:
+            x = A.bucket_mark(x, notify, -1)
+        return x
 
     def forward(self, input_ids: torch.Tensor) -> ModelOutput:
         return ModelOutput(self.embedding.project(self.forward_hidden(input_ids)), None)

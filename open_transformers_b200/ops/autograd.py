@@ -77,6 +77,26 @@ def wgrad_join() -> None:
         torch.cuda.current_stream().wait_event(ev)
 
 
+class BucketMarkFn(Function):
+    """Identity in the forward pass. In the backward pass it tells `notify(bucket)` that the gradient with respect to
+    this point of the residual stream is complete, i.e. that every layer AFTER this point has run its backward and
+    written its weight gradients; the engine starts that bucket's gradient reduction under the rest of the backward."""
+
+    @staticmethod
+    def forward(ctx, x, notify, bucket):
+        ctx.notify, ctx.bucket = notify, bucket
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ctx.notify(ctx.bucket)
+        return dy, None, None
+
+
+def bucket_mark(x, notify, bucket):
+    return BucketMarkFn.apply(x, notify, bucket)
+
+
 class LinearFn(Function):
     """y = x W^T (+ residual). ``master`` is the fp32 parameter autograd knows about, ``w`` the
     compute-dtype weight actually multiplied (the same tensor in fp32 runs)."""

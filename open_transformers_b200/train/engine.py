@@ -283,6 +283,7 @@ class TrainEngine:
                                 torch.from_numpy(lay.chunk_group[keep]).to(dev), int(len(keep)))
         self.chunk_sos = torch.zeros(max(self.n_chunks, 1), dtype=torch.float32, device=dev)
         self.seg_sos = torch.zeros(max(self.n_segs, 1), dtype=torch.float32, device=dev)
+        self._setup_overlap()
 
         # ---- initialise (CPU-sampled Philox, byte-copied) and move the model onto the flat buffers
         if init:
@@ -299,6 +300,106 @@ class TrainEngine:
         for mod in self.model.modules():
             for bname, b in list(mod.named_buffers(recurse=False)):
                 mod._buffers[bname] = b.to(self.device)
+
+    # ------------------------------------------------------- gradient reduction under the backward pass
+    def _setup_overlap(self) -> None:
+        """Bucketed reduction that runs under the backward pass of the step's last micro-batch on this process.
+
+        The reference starts its reduce-scatter from inside the last micro-batch's backward, one FSDP module at a time
+        (src/pretrain/train/loop.py:872-873, 904; src/pretrain/parallel/deterministic_reduce.py:504-523). Here a bucket is
+        the vocabulary head, one transformer block (the final norm goes with the last block), or the embedding. When the
+        backward pass has finished a bucket (`BucketMarkFn`), this process
+          1. tells every peer so: one release store of the step's epoch into word [bucket, rank] of each GPU's flag array,
+          2. queues, on a side stream, a bounded wait for the same word of every rank followed by the reduction kernel
+             over the chunks of that bucket which this process owns.
+        The peers' gradients of block L thus cross NVLink while blocks < L are still in their backward pass. The kernel, the
+        chunk table and therefore every sum are those of the one-shot reduction: only the launch granularity changes.
+        OTB_REDUCE_OVERLAP = auto (GPUs: on) | 1 (also on the CPU, where it runs synchronously: tests) | 0."""
+        self._ov = None
+        mode = os.environ.get("OTB_REDUCE_OVERLAP", "auto")
+        eligible = (self.tp == 1 and not self.fold and not self.nccl_mode and not self.collective and not self.stream_head
+                    and not self.muon_params and (self.peer or self.world == 1))
+        if not eligible or mode == "0" or (mode == "auto" and not self.is_cuda):
+            return
+        lay, L = self.layout, self.cfg.model.n_layers
+
+        def bucket_of(name: str) -> int:  # in the order in which the backward pass completes them
+            if name.startswith("embedding.output."):
+                return 0
+            if name.startswith("norm_out."):
+                return 1
+            if name.startswith("blocks."):
+                return 1 + (L - 1 - int(name.split(".")[1]))
+            return L + 1  # token embedding and the norm on its output: the end of the backward pass
+
+        ids: list[list[int]] = [[] for _ in range(L + 2)]
+        for sg in lay.segments[self.seg_lo:self.seg_hi]:
+            ids[bucket_of(lay.names[sg.param])].extend(range(sg.first_chunk, sg.first_chunk + sg.n_chunks))
+        per = self.V // self.dp_groups
+        srcs = []
+        for v in range(self.V):
+            r, slot = v // per, v % per
+            srcs.append(self.buf_grads[slot].ptrs[r] if self.peer else self.grads[slot].data_ptr())
+        ov = {"ids": [torch.tensor(x, dtype=torch.int32, device=self.device) for x in ids], "n": [len(x) for x in ids],
+              "srcs": _ptr_array(srcs), "epoch": 0, "active": False, "launched": set(), "unwritten": None,
+              "budget_ns": int(float(os.environ.get("OTB_PEER_WAIT_MS", "30000")) * 1e6)}
+        if self.is_cuda:
+            ov["reduce_stream"] = torch.cuda.Stream(device=self.device)
+            ov["signal_stream"] = torch.cuda.Stream(device=self.device)
+        if self.peer:
+            ov["flags"] = PeerBuffer(4 * (L + 2) * self.world, self.device, self.rank, self.world, self.group)
+            ov["bar"] = PeerBuffer(4 * 8, self.device, self.rank, self.world, self.group)
+            ov["bar_seq"] = 0
+        self._ov = ov
+
+    def _block_done(self, block: int) -> None:
+        """Called from the backward pass (models/llama3.py): block `block` and everything after it are done; -1 = the head."""
+        L = self.cfg.model.n_layers
+        self._launch_bucket(0 if block < 0 else 1 + (L - 1 - block))
+
+    def _launch_bucket(self, b: int) -> None:
+        ov = self._ov
+        if b in ov["launched"]:
+            return
+        ov["launched"].add(b)
+        S, R = self.dp_shard, self.dp_replicate
+        if not self.is_cuda:
+            if ov["n"][b]:
+                check(self.lib.otb_cpu_grad_reduce_ids(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
+                                                       I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos)), "grad_reduce_ids")
+            return
+        wgrad_join()
+        done = torch.cuda.Event()
+        done.record()  # everything the backward pass has queued for this bucket
+        red = ov["reduce_stream"]
+        if self.peer:
+            sig = ov["signal_stream"]
+            sig.wait_event(done)
+            check(self.lib.otb_flag_signal(_ptr_array(ov["flags"].ptrs), I(self.world), I(b * self.world + self.rank),
+                                           ctypes.c_uint(ov["epoch"]), ctypes.c_void_p(sig.cuda_stream)), "flag_signal")
+        red.wait_event(done)
+        pending = getattr(self, "_hash_done", None)
+        if pending is not None:
+            red.wait_event(pending)  # the previous step's digests still read the reduced gradient
+        rs = ctypes.c_void_p(red.cuda_stream)
+        if self.peer:
+            check(self.lib.otb_flag_wait(ctypes.c_void_p(ov["flags"].ptrs[self.rank]), I(b * self.world), I(self.world),
+                                         ctypes.c_uint(ov["epoch"]), ctypes.c_ulonglong(ov["budget_ns"]), P(K._status(self.device)),
+                                         ctypes.c_uint(4), rs), "flag_wait")
+        if ov["n"][b]:
+            check(self.lib.otb_grad_reduce_ids(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
+                                               I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos), rs), "grad_reduce_ids")
+
+    def _stream_barrier(self) -> None:
+        """All processes have reached this point of their streams (flag exchange over peer memory on the current stream;
+        bounded wait, no host synchronisation). Falls back to the host barrier where there is no peer memory."""
+        ov = self._ov
+        if ov is None or not self.peer:
+            self._barrier()
+            return
+        ov["bar_seq"] += 1
+        check(self.lib.otb_peer_barrier(_ptr_array(ov["bar"].ptrs), I(self.rank), I(self.world), ctypes.c_uint(ov["bar_seq"]),
+                                        P(K._status(self.device)), stream_ptr()), "peer_barrier")
 
     # ------------------------------------------------------------------------------ phase timing
     def _tick(self, phase: str | None):
@@ -437,15 +538,18 @@ class TrainEngine:
             slot.buf = None if gbuf is None else gbuf[o0:o0 + rows * cols].view(rows, cols)
             slot.fresh, slot.written = fresh, False
 
-    def _zero_unwritten_slots(self) -> None:
+    def _zero_unwritten_slots(self) -> set:
         """After the first backward pass into a stale buffer: parameters nobody wrote get an explicit zero."""
         covered = set()
         for slot, _o0, _rows, _cols, members in self._fused:
             if slot.written:
                 covered.update(members)
+        unwritten = set()
         for i, slot in enumerate(self.slots):
             if not slot.written and i not in covered and slot.buf is not None:
                 slot.buf.zero_()
+                unwritten.add(i)
+        return unwritten
 
     def named_master(self):
         return [(n, self.layout.view(self.master, i)) for i, n in enumerate(self.names)]
@@ -492,11 +596,13 @@ class TrainEngine:
                   "push_cast")
 
     # ---------------------------------------------------------------------------- one step
-    def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int):
-        """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``)."""
+    def forward_backward(self, vslot: int, input_ids: torch.Tensor, labels: torch.Tensor, accum: int, last: bool = False):
+        """One micro-batch of hosted virtual rank ``vslot`` (index into ``self.hosted``). ``last``: this is the step's
+        final micro-batch on this process, so finished buckets of gradients may enter the reduction during its backward."""
         if self.fold:
             vslot = 0  # every virtual rank is processed in the one work buffer, then folded away
         fresh = self._stale[vslot]
+        overlap = last and self._ov is not None and self._begin_overlap(vslot, fresh)
         self._bind_slots(self.grads[vslot], fresh)
         set_tp(self._tp_state)
         if self._tp_state is not None:  # this rank's token rows of the labels
@@ -521,16 +627,45 @@ class TrainEngine:
             self._tick("fwd")
             hidden.backward(dh)
         else:
-            out = self.model(input_ids)
-            ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
-            loss = (ce + z) * (1.0 / accum)
-            self._tick("fwd")
-            loss.backward()
+            self.model.bucket_notify = self._block_done if overlap else None
+            try:
+                out = self.model(input_ids)
+                ce, z = fused_ce_z_loss(out.logits, labels, z_coeff, 1.0 / accum)
+                loss = (ce + z) * (1.0 / accum)
+                self._tick("fwd")
+                loss.backward()
+            finally:
+                self.model.bucket_notify = None
         self._tick("bwd")
         if fresh:
-            self._zero_unwritten_slots()
+            unwritten = self._zero_unwritten_slots()
             self._stale[vslot] = False
+            if self._ov is not None:
+                if overlap and not unwritten <= (self._ov["unwritten"] or set()):
+                    raise RuntimeError("parameters %s received no gradient in this micro-batch but did before: their buckets "
+                                       "entered the reduction with stale values" % sorted(unwritten - (self._ov["unwritten"] or set())))
+                self._ov["unwritten"] = unwritten
+        if overlap:
+            for b in range(self.cfg.model.n_layers + 2):  # the embedding, and any bucket no mark reported
+                self._launch_bucket(b)
         return ce, z
+
+    def _begin_overlap(self, vslot: int, fresh: bool) -> bool:
+        """Prepare the overlapped reduction for this (last) micro-batch; False = reduce after the backward pass as usual."""
+        ov = self._ov
+        if fresh and ov["unwritten"] is None:
+            return False  # which parameters never receive a gradient is learnt from the first backward pass
+        for j, stale in enumerate(self._stale):
+            if stale and j != vslot:  # a hosted virtual rank without micro-batches contributes zeros
+                self.grads[j].zero_()
+                self._stale[j] = False
+        if fresh:
+            for i in ov["unwritten"]:  # nobody will write these: they hold last step's values until zeroed
+                self.layout.view(self.grads[vslot], i).zero_()
+        ov["epoch"] += 1
+        ov["launched"] = set()
+        ov["active"] = True
+        return True
 
     def fold_virtual_rank(self, v: int) -> None:
         """Folded-gradient mode: virtual rank ``v`` has run all its micro-batches of this step; add its gradient (the
@@ -598,6 +733,16 @@ class TrainEngine:
         self._stale = [False] * len(self.grads)
         if self.is_cuda:
             wgrad_join()  # weight-gradient GEMMs run on a second stream during the backward pass
+        if self._ov is not None and self._ov["active"]:
+            # every bucket entered the reduction during the last backward pass; the main stream goes on after the last one
+            self._ov["active"] = False
+            if self.is_cuda:
+                ev = torch.cuda.Event()
+                ev.record(self._ov["reduce_stream"])
+                torch.cuda.current_stream().wait_event(ev)
+            if self.peer:
+                self._share_chunk_sos()
+            return self._finish_norm()
         if self.tp > 1:
             # assemble each virtual rank's gradient from the slices its tensor-parallel ranks wrote: at most one rank holds
             # a non-zero bit pattern per element, so the integer sum of the bit patterns is that pattern, exactly
@@ -631,7 +776,7 @@ class TrainEngine:
                                                    P(self.grad_red), P(self.chunk_sos)), "grad_reduce")
             self._keep = None
         else:
-            self._barrier()  # every rank's backward is complete before anyone pulls
+            self._stream_barrier()  # every rank's backward is complete before anyone pulls
             srcs = []
             if self.fold:
                 # the shard fold and the 1/S scaling are done; what is left is the pair tree over the R replica partials
@@ -655,6 +800,9 @@ class TrainEngine:
                 self._keep = None
             if self.peer:
                 self._share_chunk_sos()
+        return self._finish_norm()
+
+    def _finish_norm(self) -> float:
         if self.is_cuda:
             check(self.lib.otb_seg_pair_tree(P(self.chunk_sos), P(self.seg_first), I(self.n_segs), P(self.seg_sos), stream_ptr()), "seg_tree")
         else:
@@ -815,7 +963,7 @@ class TrainEngine:
         if self.collective:
             self._share_updated_weights()
         self._tick("opt")
-        self._barrier()  # peers' stores into this rank's weights are complete before the next forward
+        self._stream_barrier()  # peers' stores into this rank's weights are complete before the next forward
         K.weight_epoch = (K.weight_epoch or 0) + 1
         self._refresh_scales_if_due(self.opt_step if self.global_step is None else int(self.global_step) + 1)
 
@@ -848,7 +996,7 @@ class TrainEngine:
                     lay.view(self.compute, i).copy_(p)
 
     def skip_step(self) -> None:
-        self._barrier()
+        self._stream_barrier()  # nobody overwrites a gradient buffer that a peer may still be reading
         if self.global_step is not None:
             self._refresh_scales_if_due(int(self.global_step) + 1)
 
@@ -999,7 +1147,8 @@ class TrainEngine:
         if self._tp_state is not None and self._tp_state.ws is not None:
             self._tp_state.ws.close()
             self._tp_state.ws = None
-        for b in [self.buf_master, self.buf_compute] + self.buf_grads:
+        extra = [self._ov[k] for k in ("flags", "bar") if self._ov is not None and k in self._ov]
+        for b in [self.buf_master, self.buf_compute] + self.buf_grads + extra:
             b.close()
         self._off_files.clear()
         for tmp in self._off_tmp:

@@ -214,13 +214,14 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             engine.global_step = step
             engine.zero_grads()
             ces, zs, owners = [], [], []
-            for v, k, windows in batches:
+            batches = list(batches)
+            for j, (v, k, windows) in enumerate(batches):
                 batch = collate(windows, pin=engine.is_cuda)
                 if sh_cfg.include_batch:
                     hashers[v].update(batch)
                 ids = batch["input_ids"].to(dev, non_blocking=True)
                 labels = batch["labels"].to(dev, non_blocking=True)
-                ce, z = engine.forward_backward(hosted.index(v), ids, labels, accum)
+                ce, z = engine.forward_backward(hosted.index(v), ids, labels, accum, last=j == len(batches) - 1)
                 ces.append(ce.detach())
                 zs.append(z.detach())
                 owners.append(v)

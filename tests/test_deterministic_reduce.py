@@ -83,3 +83,51 @@ def test_every_aligned_power_of_two_range_is_a_subtree():
         for lo in range(0, 16, size):
             sub = pair_tree([str(i) for i in range(lo, lo + size)], lambda a, b: "(%s+%s)" % (a, b))
             assert sub in whole
+
+
+def test_reduction_under_the_backward_pass_gives_the_one_shot_bytes(tmp_path, monkeypatch):
+    """The bucketed reduction (head, blocks last to first, embedding; started from marks in the backward pass of the
+    step's last micro-batch) writes the same reduced gradient, chunk partials, norm and state hash as the reduction that
+    runs once after the backward pass. On the CPU the buckets run synchronously inside the hooks, which exercises the
+    bucket plan (every owned chunk in exactly one bucket), the stale-buffer rules and the call order."""
+    from helpers import tiny_cfg
+    from open_transformers_b200.train.engine import TrainEngine
+
+    cfg = tiny_cfg(str(tmp_path), ["model.n_layers=3"])
+    g = torch.Generator().manual_seed(11)
+    data = [[(torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g))
+             for _ in range(4)] for _ in range(3)]
+
+    def run(mode: str, accum: int):
+        monkeypatch.setenv("OTB_REDUCE_OVERLAP", mode)
+        eng = TrainEngine(cfg, "cpu")
+        assert (eng._ov is not None) == (mode == "1")
+        if eng._ov is not None:
+            plan = sorted(int(c) for ids in eng._ov["ids"] for c in ids.tolist())
+            assert plan == list(range(eng.chunk_lo, eng.chunk_hi))  # every owned chunk in exactly one bucket
+        out, prev = [], None
+        for step in range(3):
+            eng.zero_grads()
+            n = 0
+            for v in range(eng.V):
+                for k in range(accum):
+                    ids, lab = data[step][(v * accum + k) % 4]
+                    n += 1
+                    eng.forward_backward(v, ids, lab, accum, last=n == eng.V * accum)
+            norm = eng.reduce_gradients()
+            red, sos = eng.grad_red.clone(), eng.chunk_sos.clone()
+            eng.optimizer_step(1e-3, eng.clip_coefficient(norm, 1.0))
+            prev = eng.sharded_state_hash(prev, None)
+            out.append((norm, red, sos, prev))
+        launched = None if eng._ov is None else eng._ov["epoch"]
+        eng.close()
+        return out, launched
+
+    for accum in (1, 2):
+        plain, _ = run("0", accum)
+        over, epochs = run("1", accum)
+        # which parameters never get a gradient is learnt from the first backward pass into a stale buffer (virtual rank
+        # 0's, here), so already the first step's last micro-batch reduces under its backward pass
+        assert epochs == 3
+        for (n0, r0, s0, h0), (n1, r1, s1, h1) in zip(plain, over):
+            assert n0 == n1 and torch.equal(r0, r1) and torch.equal(s0, s1) and h0 == h1

@@ -39,4 +39,5 @@ def test_hashes_do_not_depend_on_the_gpu_count(tmp_path, shard):
             break
         many = _run(n, tmp_path / ("g%d.json" % n), shard)
         assert many["status"] == 0
+        assert many["overlapped_steps"] == 3  # every step's reduction ran bucket by bucket under the last backward pass
         assert many["hashes"] == one["hashes"], (n, many, one)
