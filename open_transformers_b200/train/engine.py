@@ -342,7 +342,9 @@ class TrainEngine:
             srcs.append(self.buf_grads[slot].ptrs[r] if self.peer else self.grads[slot].data_ptr())
         ov = {"ids": [torch.tensor(x, dtype=torch.int32, device=self.device) for x in ids], "n": [len(x) for x in ids],
               "srcs": _ptr_array(srcs), "epoch": 0, "active": False, "launched": set(), "unwritten": None,
-              "budget_ns": int(float(os.environ.get("OTB_PEER_WAIT_MS", "30000")) * 1e6)}
+              "budget_ns": int(float(os.environ.get("OTB_PEER_WAIT_MS", "30000")) * 1e6),
+              # OTB_REDUCE_TIMELINE=1: CUDA events per bucket (ready / reduction start / reduction end), see overlap_timeline()
+              "timeline": [] if os.environ.get("OTB_REDUCE_TIMELINE") == "1" else None}
         if self.is_cuda:
             ov["reduce_stream"] = torch.cuda.Stream(device=self.device)
             ov["signal_stream"] = torch.cuda.Stream(device=self.device)
@@ -369,7 +371,8 @@ class TrainEngine:
                                                        I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos)), "grad_reduce_ids")
             return
         wgrad_join()
-        done = torch.cuda.Event()
+        timed = ov["timeline"] is not None
+        done = torch.cuda.Event(enable_timing=timed)
         done.record()  # everything the backward pass has queued for this bucket
         red = ov["reduce_stream"]
         if self.peer:
@@ -386,9 +389,35 @@ class TrainEngine:
             check(self.lib.otb_flag_wait(ctypes.c_void_p(ov["flags"].ptrs[self.rank]), I(b * self.world), I(self.world),
                                          ctypes.c_uint(ov["epoch"]), ctypes.c_ulonglong(ov["budget_ns"]), P(K._status(self.device)),
                                          ctypes.c_uint(4), rs), "flag_wait")
+        if timed:
+            t0 = torch.cuda.Event(enable_timing=True)
+            t0.record(red)
         if ov["n"][b]:
             check(self.lib.otb_grad_reduce_ids(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
                                                I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos), rs), "grad_reduce_ids")
+        if timed:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record(red)
+            ov["timeline"].append((ov["epoch"], b, done, t0, t1))
+
+    def overlap_timeline(self) -> list[dict]:
+        """With OTB_REDUCE_TIMELINE=1: for every bucket of the last overlapped step, when the backward pass finished it,
+        when its reduction began (all ranks had signalled) and ended, in ms after the first bucket became ready, plus
+        `backward_end_ms`, the moment the backward pass itself was done. One device synchronisation."""
+        ov = self._ov
+        if ov is None or not ov.get("timeline"):
+            return []
+        torch.cuda.synchronize()
+        rows = [r for r in ov["timeline"] if r[0] == ov["epoch"]]
+        base = rows[0][2]
+        end = getattr(self, "_bwd_end_event", None)
+        out = [{"bucket": b, "chunks": ov["n"][b], "ready_ms": base.elapsed_time(d), "reduce_start_ms": base.elapsed_time(t0),
+                "reduce_end_ms": base.elapsed_time(t1)} for _, b, d, t0, t1 in rows]
+        if end is not None:
+            for r in out:
+                r["backward_end_ms"] = base.elapsed_time(end)
+        ov["timeline"].clear()
+        return out
 
     def _stream_barrier(self) -> None:
         """All processes have reached this point of their streams (flag exchange over peer memory on the current stream;
@@ -646,6 +675,9 @@ class TrainEngine:
                                        "entered the reduction with stale values" % sorted(unwritten - (self._ov["unwritten"] or set())))
                 self._ov["unwritten"] = unwritten
         if overlap:
+            if self._ov["timeline"] is not None:
+                self._bwd_end_event = torch.cuda.Event(enable_timing=True)
+                self._bwd_end_event.record()
             for b in range(self.cfg.model.n_layers + 2):  # the embedding, and any bucket no mark reported
                 self._launch_bucket(b)
         return ce, z
