@@ -76,6 +76,10 @@ struct TpArgs {
   int rank, P, tiles_per_shard, gemm_ctas;
 };
 
+// How long a kernel of this file waits for a peer's flag before it gives up, sets its status word and returns
+// (nanoseconds of %globaltimer; otb_set_peer_wait_ns changes it for the current device).
+__device__ unsigned long long g_peer_wait_ns = 2000000000ull;
+
 // Bounded wait for a flag written by a peer GPU (release at system scope on their side).
 __device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t seq, volatile uint32_t* abort_flag) {
   unsigned long long t0;
@@ -88,7 +92,7 @@ __device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t se
     if ((i & 63u) == 63u) {
       unsigned long long t1;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-      if (t1 - t0 > 2000000000ull) break;
+      if (t1 - t0 > g_peer_wait_ns) break;
     }
     __nanosleep(100);
   }
@@ -709,6 +713,14 @@ __global__ void peer_barrier_tab_kernel(PtrTable8 slots, int rank, int P, uint32
 }
 inline int tp_chain_bn(int N) { return N >= 256 ? 256 : 128; }
 }  // namespace
+
+// Budget of every bounded peer wait of the tensor-parallel kernels and of otb_peer_barrier on the current device
+// (default 2 s). A wait that runs out makes its kernel write its status word (1 all-gather->GEMM, 2 chained GEMM /
+// otb_tp_finish, 3 otb_peer_barrier) and return normally.
+extern "C" int otb_set_peer_wait_ns(unsigned long long ns) {
+  if (ns == 0) return -2;
+  return (int)cudaMemcpyToSymbol(g_peer_wait_ns, &ns, sizeof(ns));
+}
 
 // Cross-GPU barrier on the stream: slots[p] is rank p's array of P words (peer pointers); seq must grow by one per call.
 extern "C" int otb_peer_barrier(void* const* slots, int rank, int P, unsigned seq, uint32_t* status, void* stream) {

@@ -1,7 +1,9 @@
-"""Failure detection, all on the host with CPU (gloo) ranks: a rank that leaves between steps is noticed by the
-heartbeat before the survivor's next collective; a rank that never joins ends the rendezvous with an error after the
-configured timeout; SIGTERM produces an off-cadence checkpoint whose hash replays; run-id disagreement and a missing
-per-rank file are loud. No GPU is involved and nothing here makes a device fault, trap or hang."""
+"""Failure detection. On the host with CPU (gloo) ranks: a rank that leaves between steps is noticed by the heartbeat
+before the survivor's next collective; a rank that never joins ends the rendezvous with an error after the configured
+timeout; SIGTERM produces an off-cadence checkpoint whose hash replays; run-id disagreement and a missing per-rank file
+are loud. On one GPU (marked `gpu`): the bounded in-kernel waits on a peer's flag are given a few milliseconds and a flag
+that nothing sets; each kernel must write its status word and return, leaving the context usable. Nothing here makes a
+device fault, trap or hang."""
 import json
 import os
 import subprocess
@@ -217,3 +219,75 @@ def test_rendezvous_through_a_tcp_store_or_a_file_store(tmp_path, how):
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(2)]
     outs = [p.communicate(timeout=120)[0].decode() for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-3000:]
+
+
+# ------------------------------------------------------------------ bounded device-side waits (one GPU, no peer involved)
+def _cuda():
+    import ctypes
+
+    import torch
+
+    from open_transformers_b200.ops.native import cuda_lib
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return ctypes, torch, cuda_lib()
+
+
+@pytest.mark.gpu
+def test_a_flag_wait_that_runs_out_reports_the_word_and_returns():
+    """The wait that holds a bucket's gradient reduction until every rank has signalled it: five milliseconds, a word
+    nothing writes. Status word 0 takes the caller's code, word 1 the index of the flag, and the stream goes on."""
+    ctypes, torch, lib = _cuda()
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    flags[4] = 7                                     # rank 0 of bucket 2 (two ranks) has signalled epoch 7, rank 1 never does
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    rc = lib.otb_flag_wait(ctypes.c_void_p(flags.data_ptr()), ctypes.c_int(4), ctypes.c_int(2), ctypes.c_uint(7),
+                           ctypes.c_ulonglong(5_000_000), ctypes.c_void_p(status.data_ptr()), ctypes.c_uint(4),
+                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    after = torch.ones(8, device="cuda") * 3         # queued behind the wait on the same stream
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert status[:2].tolist() == [4, 5] and float(after.sum()) == 24.0
+    # the same wait with both words set returns at once and leaves the status alone
+    flags[5] = 7
+    status.zero_()
+    lib.otb_flag_wait(ctypes.c_void_p(flags.data_ptr()), ctypes.c_int(4), ctypes.c_int(2), ctypes.c_uint(7), ctypes.c_ulonglong(5_000_000),
+                      ctypes.c_void_p(status.data_ptr()), ctypes.c_uint(4), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.gpu
+def test_a_peer_barrier_whose_peer_never_arrives_gives_status_3_and_a_late_row_block_gives_status_2():
+    """`otb_peer_barrier` as rank 0 of 2 with a second slot array that no second rank exists to write, and
+    `otb_tp_finish` on a result buffer whose arrival flags stay clear; both with the wait budget set to 5 ms."""
+    ctypes, torch, lib = _cuda()
+    lib.otb_set_peer_wait_ns.argtypes = [ctypes.c_ulonglong]
+    assert lib.otb_set_peer_wait_ns(5_000_000) == 0
+    try:
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        slots = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+        arr = (ctypes.c_void_p * 2)(slots[0].data_ptr(), slots[1].data_ptr())
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        assert lib.otb_peer_barrier(arr, ctypes.c_int(0), ctypes.c_int(2), ctypes.c_uint(1), ctypes.c_void_p(status.data_ptr()), stream) == 0
+        torch.cuda.synchronize()
+        assert int(status[0]) == 3
+        assert int(slots[0][0]) == 1 and int(slots[1][0]) == 1 and int(slots[0][1]) == 0   # it announced itself; nobody answered
+
+        M = N = 128
+        acc = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+        tile_flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+        y = torch.full((M, N), 5.0, dtype=torch.bfloat16, device="cuda")
+        status.zero_()
+        rc = lib.otb_tp_finish(ctypes.c_void_p(acc.data_ptr()), ctypes.c_void_p(tile_flags.data_ptr()), ctypes.c_uint(1), ctypes.c_void_p(0),
+                               ctypes.c_void_p(y.data_ptr()), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(0), ctypes.c_int(1),
+                               ctypes.c_long(N), ctypes.c_long(N), ctypes.c_long(N), ctypes.c_void_p(status.data_ptr()), stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status[0]) == 2 and bool((y == 5.0).all())   # no row block was delivered, none was written
+    finally:
+        assert lib.otb_set_peer_wait_ns(2_000_000_000) == 0
+    assert float((torch.ones(4, device="cuda") + 1).sum()) == 8.0

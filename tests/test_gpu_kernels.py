@@ -252,3 +252,40 @@ def test_tree_digest_matches_host():
     for n in (0, 5, 1024, 1025, 300_000, 5_000_000):
         t = torch.randn(n, generator=g)
         assert SH.tree_digest_tensor(t) == SH.tree_digest_tensor(t.to(DEV)), n
+
+
+@pytest.mark.parametrize("S,R", [(4, 1), (2, 2), (8, 1), (2, 3)])
+def test_grad_reduce_gpu_equals_cpu_fold_in_any_launch_order(S, R):
+    """The fused reduction (ascending shard fold, replica pair tree, squared-norm partials) against the CPU fold, bit for
+    bit; and the same chunks launched in reversed and in shuffled order (the bucketed launches of the overlapped path):
+    every chunk is owned by one block, so the order of the blocks must not reach the bytes."""
+    import ctypes
+
+    import numpy as np
+
+    from open_transformers_b200.ops.native import I, P, cpu_lib, cuda_lib, stream_ptr
+    from open_transformers_b200.train.engine import _ptr_array
+
+    g = torch.Generator().manual_seed(S * 10 + R)
+    n = 5 * 8192 + 1000
+    starts = np.arange(0, n, 8192, dtype=np.int64)
+    lens = np.minimum(8192, n - starts).astype(np.int32)
+    srcs_cpu = [torch.randn(n, generator=g) * 1e-3 for _ in range(S * R)]
+    out_cpu, sos_cpu = torch.zeros(n), torch.zeros(len(starts))
+    cs, cl = torch.from_numpy(starts), torch.from_numpy(lens)
+    assert cpu_lib().otb_cpu_grad_reduce(_ptr_array([t.data_ptr() for t in srcs_cpu]), I(S), I(R), P(cs), P(cl), I(len(starts)), P(out_cpu), P(sos_cpu)) == 0
+    srcs = [t.to(DEV) for t in srcs_cpu]
+    ptrs = _ptr_array([t.data_ptr() for t in srcs])
+    csd, cld = cs.to(DEV), cl.to(DEV)
+    lib = cuda_lib()
+    out, sos = torch.zeros(n, device=DEV), torch.zeros(len(starts), device=DEV)
+    assert lib.otb_grad_reduce(ptrs, I(S), I(R), P(csd), P(cld), I(len(starts)), P(out), P(sos), stream_ptr()) == 0
+    _eq(out_cpu, out, "reduced gradient")
+    _eq(sos_cpu, sos, "chunk partials")
+    for order in (list(range(len(starts)))[::-1], [3, 0, 5, 1, 4, 2]):
+        ids = torch.tensor(order, dtype=torch.int32, device=DEV)
+        out2, sos2 = torch.full((n,), 9.0, device=DEV), torch.full((len(starts),), 9.0, device=DEV)
+        assert lib.otb_grad_reduce_ids(ptrs, I(S), I(R), P(csd), P(cld), P(ids), I(len(order)), P(out2), P(sos2), stream_ptr()) == 0
+        _eq(out_cpu, out2, "reduced gradient, launch order %s" % order)
+        _eq(sos_cpu, sos2, "chunk partials, launch order %s" % order)
+    del ctypes
