@@ -14,7 +14,7 @@ def hash_checkpoint(ckpt_dir: str, include_optimizer: bool = True) -> str:
     import torch
 
     from ..train import state_hash as SH
-    from ..train.checkpoint import validate_dcp_metadata
+    from ..train.checkpoint import optimizer_state_names, validate_dcp_metadata
 
     d = Path(ckpt_dir) / "dcp"
     validate_dcp_metadata(d)
@@ -29,10 +29,11 @@ def hash_checkpoint(ckpt_dir: str, include_optimizer: bool = True) -> str:
     params = {k[len("model."):]: v for k, v in template.items() if k.startswith("model.")}
     opt = {}
     if include_optimizer:
+        by_index = optimizer_state_names(ckpt_dir)  # torch-style payload: optim.state.<index>; older ones are keyed by name
         for k, v in template.items():
             if k.startswith("optim.state."):
                 name, field = k[len("optim.state."):].rsplit(".", 1)
-                opt.setdefault(name, {})[field] = v
+                opt.setdefault(by_index.get(name, name), {})[field] = v
     return SH.compute_state_hash(list(params.items()), opt or None, None)
 
 

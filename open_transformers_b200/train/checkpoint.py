@@ -2,8 +2,10 @@
 
 Layout of ``<run>/checkpoints/step_%09d/`` (reference src/pretrain/train/checkpoint.py:271-326, 743-782)::
 
-    dcp/                       torch.distributed.checkpoint of {"model": {name: fp32 tensor}, "optim": {"state": {name:
-                               {"step", "exp_avg", "exp_avg_sq"}}, "param_groups": [...]}}
+    dcp/                       torch.distributed.checkpoint of {"model": {name: fp32 tensor}, "optim": {"state": {index:
+                               {"step", "exp_avg", "exp_avg_sq"}}, "param_groups": [{..., "params": [indices]}]}} - the payload
+                               of `model.state_dict()` / `optimizer.state_dict()` (parameters numbered group by group, in
+                               `named_parameters()` order inside a group), as the reference saves it
     meta.json                  CheckpointMeta
     state_hash.txt             hash of the state at this step (hex)
     global_stream.json         position of the canonical data stream (same on every rank)
@@ -12,9 +14,13 @@ Layout of ``<run>/checkpoints/step_%09d/`` (reference src/pretrain/train/checkpo
     batch_hasher.rank_<v>.bin  32-byte running batch digest per virtual rank
     _COMPLETE                  written last; a directory without it is ignored
 
-Rank 0 writes every file (after the engine gathered the full state), so a lossy shared filesystem sees
-one writer. Reading never unpickles untrusted code: the DCP ``.metadata`` pickle goes through an
-allow-listing unpickler first and ``.pt`` files are loaded with ``weights_only=True``.
+Every process writes the rows of the tensors it owns into ``dcp/`` (a distributed DCP save over a dedicated gloo
+group: one data file per process, metadata committed by rank 0; reference src/pretrain/train/checkpoint.py:589-627),
+from a snapshot in pinned host memory taken when ``save`` is called, so the writing can run on a background thread
+while training goes on. Rank 0 writes every small file (reference :724-741) and, last, ``_COMPLETE``. Reading never
+unpickles untrusted code: the DCP ``.metadata`` pickle goes through an allow-listing unpickler first and ``.pt``
+files are loaded with ``weights_only=True``. Checkpoints whose optimizer state is keyed by parameter name (written
+by earlier versions of this package) still load.
 """
 from __future__ import annotations
 
@@ -24,6 +30,7 @@ import json
 import pickle
 import re
 import shutil
+import threading
 import time
 from pathlib import Path
 from typing import Any
@@ -61,6 +68,7 @@ class CheckpointMeta:
     windows_emitted: int = 0
     physical_world_size: int = 1
     mixed_precision: bool = True
+    optimizer_param_names: list = dataclasses.field(default_factory=list)   # parameter name of optim.state.<index>, by index
 
     def to_json(self) -> str:
         return json.dumps(dataclasses.asdict(self), indent=1, sort_keys=True)
@@ -115,24 +123,100 @@ def validate_dcp_metadata(dcp_dir: str | Path) -> None:
 
 
 # ------------------------------------------------------------------------------------------ writer / reader
+class OwnedRows:
+    """One tensor of the checkpoint as THIS process holds it: the global shape and dtype, and the row ranges it owns as
+    (first row, CPU tensor of those rows). The planner below turns every piece into one DCP chunk."""
+
+    def __init__(self, shape, dtype, pieces):
+        self.shape, self.dtype, self.pieces = tuple(shape), dtype, list(pieces)
+
+
+def _save_planner():
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint.metadata import ChunkStorageMetadata, MetadataIndex, TensorProperties
+    from torch.distributed.checkpoint.planner import SavePlan, TensorWriteData, WriteItem, WriteItemType
+    from torch.distributed.checkpoint.planner_helpers import _create_write_items
+
+    class OwnedRowsPlanner(dcp.DefaultSavePlanner):
+        """Sharded tensors arrive as `OwnedRows`: each owned row range becomes a SHARD write item at its offset in the
+        global tensor, so the chunks of all processes tile the tensor and any reader can re-shard them. Everything that
+        is the same on every process (step counters, param_groups) is written by the coordinator alone."""
+
+        def create_local_plan(self):
+            items = []
+            for fqn, obj in self.state_dict.items():
+                if isinstance(obj, OwnedRows):
+                    rest = [0] * (len(obj.shape) - 1)
+                    for row_lo, t in obj.pieces:
+                        offs = torch.Size([row_lo] + rest) if obj.shape else torch.Size([])
+                        props = TensorProperties(dtype=obj.dtype)
+                        items.append(WriteItem(index=MetadataIndex(fqn, offs), type=WriteItemType.SHARD,
+                                               tensor_data=TensorWriteData(chunk=ChunkStorageMetadata(offsets=offs, sizes=t.shape),
+                                                                           properties=props, size=torch.Size(obj.shape))))
+                elif self.is_coordinator:
+                    items += _create_write_items(fqn, obj)
+            plan = SavePlan(items)
+            if self.flatten_state_dict:
+                plan = dataclasses.replace(plan, planner_data=self.mappings)
+            self.plan = plan
+            return plan
+
+        def lookup_object(self, index):
+            obj = self.state_dict[index.fqn]
+            if isinstance(obj, OwnedRows):
+                for row_lo, t in obj.pieces:
+                    if not obj.shape or row_lo == index.offset[0]:
+                        return t
+                raise KeyError("no piece of %s at %s" % (index.fqn, tuple(index.offset)))
+            return super().lookup_object(index)
+
+    return OwnedRowsPlanner()
+
+
+def optimizer_param_indices(param_groups, names, members) -> dict[str, int]:
+    """Parameter name -> index in `optimizer.state_dict()`: parameters are numbered group by group, inside a group in
+    `named_parameters()` order (what torch.optim.Optimizer.state_dict does with the groups of optim/adamw.py)."""
+    out, nxt = {}, 0
+    for gi in range(len(param_groups)):
+        for n, m in zip(names, members):
+            if m == gi:
+                out[n] = nxt
+                nxt += 1
+    return out
+
+
 class Checkpointer:
     def __init__(self, run_dir: str | Path, rank: int = 0, world: int = 1, group=None):
         self.root = Path(run_dir) / "checkpoints"
         self.rank, self.world, self.group = rank, world, group
+        self._writer: threading.Thread | None = None
+        self._writer_error: list = []
+        self._pinned: dict = {}
+        self._save_group = None
+        if world > 1:
+            import torch.distributed as dist
+
+            if dist.is_available() and dist.is_initialized():
+                # DCP's planning collectives and the commit barrier run on their own gloo group, possibly from a background
+                # thread, and never interleave with the training collectives (reference src/pretrain/train/checkpoint.py:259-269)
+                self._save_group = dist.new_group(backend="gloo")
 
     def step_dir(self, step: int) -> Path:
         return self.root / ("step_%09d" % step)
 
     # -- save -------------------------------------------------------------------------------------------
     def save(self, step: int, engine, meta: CheckpointMeta, state_hash: str | None, stream_state: dict | None,
-             spike_state: dict | None, batch_chains: dict[int, bytes], rng_states: dict[int, dict] | None = None) -> Path:
+             spike_state: dict | None, batch_chains: dict[int, bytes], rng_states: dict[int, dict] | None = None,
+             wait: bool = True) -> Path:
         """``batch_chains`` / ``rng_states`` map VIRTUAL rank -> payload for the ranks this process hosts; they are
-        gathered to rank 0, which writes everything."""
+        gathered to rank 0, which writes the small files. The tensors are snapshotted here (device -> pinned host memory)
+        and written by every owner; with ``wait=False`` the writing, the commit barrier and ``_COMPLETE`` happen on a
+        background thread and ``wait()`` (or the next ``save``) joins it."""
         import torch.distributed as dist
 
+        self.wait()
         t0 = time.time()
         d = self.step_dir(step)
-        engine.gather_full_state()
         chains, rngs = dict(batch_chains), dict(rng_states or {})
         if self.world > 1:
             objs: list = [None] * self.world
@@ -145,7 +229,6 @@ class Checkpointer:
             d.mkdir(parents=True)
             if state_hash is not None:
                 (d / "state_hash.txt").write_text(state_hash + "\n")
-            self._write_tensors(d / "dcp", engine)
             for v in range(meta.dp_world_size):
                 if v not in chains:
                     raise FileNotFoundError("no batch-hasher chain for virtual rank %d" % v)
@@ -155,24 +238,101 @@ class Checkpointer:
             if stream_state is not None:
                 (d / "global_stream.json").write_text(json.dumps(stream_state))
             (d / "spike_protocol.json").write_text(json.dumps(spike_state or {}))
+            index = optimizer_param_indices(engine.param_groups, engine.layout.names, engine.layout.groups)
+            meta = dataclasses.replace(meta, optimizer_param_names=sorted(index, key=index.get))
             (d / "meta.json").write_text(meta.to_json())
-            (d / COMPLETE).write_text("%.3f\n" % (time.time() - t0))
+            (d / "dcp").mkdir(parents=True, exist_ok=True)
         if self.world > 1:
-            dist.barrier(group=self.group)
+            dist.barrier(group=self._save_group)  # the directory exists before anyone writes into it
+        state = self._snapshot(engine)
+        self.last_snapshot_s = time.time() - t0
+
+        def write():
+            try:
+                self._write_tensors(d / "dcp", state)
+                if self.world > 1:
+                    dist.barrier(group=self._save_group)
+                if self.rank == 0:
+                    (d / COMPLETE).write_text("%.3f\n" % (time.time() - t0))
+            except BaseException as e:  # surfaces in wait()
+                self._writer_error.append(e)
+
+        if wait:
+            write()
+            self.wait()
+        else:
+            self._writer = threading.Thread(target=write, name="checkpoint-writer", daemon=True)
+            self._writer.start()
         return d
 
-    @staticmethod
-    def _state_dict(engine) -> dict:
-        model = {n: t.detach().to("cpu").clone() for n, t in engine.named_master()}
-        optim_state = {n: {"step": torch.tensor(int(st["step"]), dtype=torch.int64), "exp_avg": st["exp_avg"].detach().to("cpu").clone(),
-                           "exp_avg_sq": st["exp_avg_sq"].detach().to("cpu").clone()} for n, st in engine.optimizer_state().items()}
-        return {"model": model, "optim": {"state": optim_state, "param_groups": [dict(g) for g in engine.param_groups]}}
+    def wait(self) -> None:
+        """Block until a background save has been committed; raises what the writer raised."""
+        if self._writer is not None:
+            self._writer.join()
+            self._writer = None
+        if self._writer_error:
+            raise self._writer_error.pop()
 
-    def _write_tensors(self, dcp_dir: Path, engine) -> None:
+    def _stage(self, key: str, count: int, dtype, device_is_cuda: bool) -> torch.Tensor:
+        buf = self._pinned.get(key)
+        if buf is None or buf.numel() < count or buf.dtype != dtype:
+            buf = torch.empty(max(count, 1), dtype=dtype, pin_memory=device_is_cuda)
+            self._pinned[key] = buf
+        return buf
+
+    def _snapshot(self, engine) -> dict:
+        """This process's rows of master weights and moments, copied to (pinned) host memory, in the reference's layout."""
+        lay = engine.layout
+        rows = engine.owned_row_ranges()
+        index = optimizer_param_indices(engine.param_groups, lay.names, lay.groups)
+        is_cuda = engine.is_cuda
+        total = sum((hi - lo) * (lay.numels[i] // max(lay.shapes[i][0] if lay.shapes[i] else 1, 1)) for i, rr in enumerate(rows) for lo, hi in rr)
+        kinds = {"weight": engine.master, "exp_avg": engine.m1, "exp_avg_sq": engine.m2}
+        stage = {k: self._stage(k, total, torch.float32, is_cuda) for k in kinds}
+        pieces = {k: [[] for _ in lay.names] for k in kinds}
+        off = 0
+        for i, rr in enumerate(rows):
+            shape = lay.shapes[i]
+            dim0 = shape[0] if shape else 1
+            row = lay.numels[i] // max(dim0, 1)
+            for lo, hi in rr:
+                n = (hi - lo) * row
+                a = lay.offsets[i] + lo * row
+                for k, flat in kinds.items():
+                    dst = stage[k][off:off + n]
+                    dst.copy_(flat[a:a + n], non_blocking=is_cuda)
+                    pieces[k][i].append((lo, dst.view((hi - lo,) + tuple(shape[1:])) if shape else dst.view(())))
+                off += n
+        if is_cuda:
+            torch.cuda.current_stream().synchronize()
+        model = {n: OwnedRows(lay.shapes[i], torch.float32, pieces["weight"][i]) for i, n in enumerate(lay.names)}
+        state = {index[n]: {"step": torch.tensor(int(engine.opt_step), dtype=torch.int64),
+                            "exp_avg": OwnedRows(lay.shapes[i], torch.float32, pieces["exp_avg"][i]),
+                            "exp_avg_sq": OwnedRows(lay.shapes[i], torch.float32, pieces["exp_avg_sq"][i])} for i, n in enumerate(lay.names)}
+        groups = []
+        for gi, g in enumerate(engine.param_groups):
+            groups.append(dict(g, params=[index[n] for n, m in zip(lay.names, lay.groups) if m == gi]))
+        return {"model": model, "optim": {"state": state, "param_groups": groups}}
+
+    def _write_tensors(self, dcp_dir: Path, state: dict) -> None:
         import torch.distributed.checkpoint as dcp
 
-        dcp_dir.mkdir(parents=True, exist_ok=True)
-        dcp.save(self._state_dict(engine), storage_writer=dcp.FileSystemWriter(str(dcp_dir), thread_count=1), no_dist=True)
+        dcp.save(state, storage_writer=dcp.FileSystemWriter(str(dcp_dir), thread_count=4, sync_files=False), planner=_save_planner(),
+                 process_group=self._save_group, no_dist=self.world == 1)
+
+    @staticmethod
+    def _template(engine, keyed_by_name: bool, load_optimizer: bool) -> dict:
+        lay = engine.layout
+        model = {n: torch.empty(lay.shapes[i], dtype=torch.float32) for i, n in enumerate(lay.names)}
+        if not load_optimizer:
+            return {"model": model}
+        index = optimizer_param_indices(engine.param_groups, lay.names, lay.groups)
+        key = (lambda n: n) if keyed_by_name else (lambda n: index[n])
+        st = {key(n): {"step": torch.zeros((), dtype=torch.int64), "exp_avg": torch.empty(lay.shapes[i], dtype=torch.float32),
+                       "exp_avg_sq": torch.empty(lay.shapes[i], dtype=torch.float32)} for i, n in enumerate(lay.names)}
+        groups = [dict(g) if keyed_by_name else dict(g, params=[index[n] for n, m in zip(lay.names, lay.groups) if m == gi])
+                  for gi, g in enumerate(engine.param_groups)]
+        return {"model": model, "optim": {"state": st, "param_groups": groups}}
 
     # -- load -------------------------------------------------------------------------------------------
     @staticmethod
@@ -188,20 +348,22 @@ class Checkpointer:
             raise FileNotFoundError("%s has no %s marker (incomplete checkpoint)" % (d, COMPLETE))
         meta = self.read_meta(d)
         validate_dcp_metadata(d / "dcp")
-        template = self._state_dict(engine)
-        if not load_optimizer:
-            template = {"model": template["model"]}
+        reader = dcp.FileSystemReader(str(d / "dcp"))
+        keyed_by_name = not any(k.startswith("optim.state.0.") for k in reader.read_metadata().state_dict_metadata)
+        template = self._template(engine, keyed_by_name, load_optimizer)
         dcp.load(template, storage_reader=dcp.FileSystemReader(str(d / "dcp")), no_dist=True)
         lay = engine.layout
+        index = optimizer_param_indices(engine.param_groups, lay.names, lay.groups)
+        key = (lambda n: n) if keyed_by_name else (lambda n: index[n])
         with torch.no_grad():
             for i, n in enumerate(engine.names):
                 lay.view(engine.master, i).copy_(template["model"][n])
                 if load_optimizer:
-                    st = template["optim"]["state"][n]
+                    st = template["optim"]["state"][key(n)]
                     lay.view(engine.m1, i).copy_(st["exp_avg"])
                     lay.view(engine.m2, i).copy_(st["exp_avg_sq"])
         if load_optimizer:
-            steps = {int(template["optim"]["state"][n]["step"]) for n in engine.names}
+            steps = {int(template["optim"]["state"][key(n)]["step"]) for n in engine.names}
             if len(steps) != 1:
                 raise ValueError("parameters disagree on the optimizer step: %s" % sorted(steps))
             engine.opt_step = steps.pop()
@@ -251,6 +413,16 @@ class Checkpointer:
                     shutil.rmtree(self.step_dir(s))
                     gone.append(self.step_dir(s))
         return gone
+
+
+def optimizer_state_names(ckpt_dir: str | Path) -> dict[str, str]:
+    """`optim.state.<key>` -> parameter name for a checkpoint directory: the index list recorded in meta.json for the
+    torch-style payload; empty for checkpoints whose optimizer state is keyed by name already."""
+    p = Path(ckpt_dir) / "meta.json"
+    if not p.is_file():
+        return {}
+    names = json.loads(p.read_text()).get("optimizer_param_names") or []
+    return {str(i): n for i, n in enumerate(names)}
 
 
 def resolved_config_json(cfg) -> str:

@@ -1161,6 +1161,29 @@ class TrainEngine:
         return SH.compute_state_hash(self.named_master(), self.optimizer_state(), self.param_groups, prev=prev,
                                      include_grads=include_grads, grads=grads, batch_digest=batch_digest)
 
+    def owned_row_ranges(self) -> list[list[tuple[int, int]]]:
+        """Per parameter, the row ranges [lo, hi) whose master weights and moments THIS process keeps current (adjacent
+        virtual shards merged). With sharded ownership: the rows of its segments; otherwise every process holds the whole
+        state and rank 0 stands for all of them."""
+        lay = self.layout
+        out: list[list[tuple[int, int]]] = [[] for _ in lay.names]
+        if self.sharded:
+            segs = lay.segments[self.seg_lo:self.seg_hi]
+        else:
+            segs = lay.segments if self.rank == 0 else []
+        for sg in sorted(segs, key=lambda g: (g.param, g.shard)):
+            shape = lay.shapes[sg.param]
+            dim0 = shape[0] if shape else 1
+            row = lay.numels[sg.param] // max(dim0, 1)
+            lo = (sg.start - lay.offsets[sg.param]) // row
+            hi = lo + sg.length // row
+            rr = out[sg.param]
+            if rr and rr[-1][1] == lo:
+                rr[-1] = (rr[-1][0], hi)
+            else:
+                rr.append((lo, hi))
+        return out
+
     def gather_full_state(self) -> None:
         """Make master / moments / reduced gradient complete on every rank (checkpoint, init hash)."""
         if not self.sharded:

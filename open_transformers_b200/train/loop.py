@@ -260,7 +260,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                        (train_cfg.ckpt_every_steps == 0 and train_cfg.ckpt_every_tokens > 0 and
                         consumed // train_cfg.ckpt_every_tokens > (consumed - plan.tokens_this_step) // train_cfg.ckpt_every_tokens)
             step_hash, t_hash = None, 0.0
-            if sh_cfg.every_n_steps > 0 and (hash_due or ckpt_due or exit_due or final_step):
+            if hash_due or ckpt_due or exit_due or final_step:  # a checkpoint is always stamped with its step's hash
                 t0 = time.perf_counter()
                 bd = global_batch_digest() if sh_cfg.include_batch else None
                 pending_hash.append((step, consumed, engine.begin_state_hash(include_grads=sh_cfg.include_grads), bd, hash_due))
@@ -272,8 +272,10 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             t_ckpt = 0.0
             if ckpt_due or exit_due or final_step:
                 t0 = time.perf_counter()
+                # a cadence checkpoint on GPUs is written in the background from a pinned-host snapshot; the last one of a run
+                # (and any on CPU ranks) is committed before going on
                 ckpt.save(step, engine, make_meta(), step_hash, loader.state().to_json(), spike.state_dict(),
-                          {v: h.local_digest() for v, h in hashers.items()})
+                          {v: h.local_digest() for v, h in hashers.items()}, wait=exit_due or final_step or not engine.is_cuda)
                 t_ckpt = (time.perf_counter() - t0) * 1e3
             wall_ms = (time.perf_counter() - t_step) * 1e3
             result["losses"].append(loss_mean)
@@ -305,9 +307,12 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             heartbeat.report_failure("%s: %s" % (type(e).__name__, e))  # the others leave at their next check
         raise
     finally:
-        if heartbeat is not None:
-            heartbeat.close()
-        metrics.close()
-        engine.close()
+        try:
+            ckpt.wait()  # a checkpoint still being written in the background is committed (or its error raised) before leaving
+        finally:
+            if heartbeat is not None:
+                heartbeat.close()
+            metrics.close()
+            engine.close()
     result.update({"step": step, "consumed_tokens": consumed, "chained_hash": chained})
     return result

@@ -3,6 +3,7 @@
 step, document dump to Parquet, checkpoint inspection and fingerprint.
 (reference: src/pretrain/cli/prepare_data.py:300-378, cli/dump_documents.py, cli/inspect_checkpoint.py, cli/hash_ckpt.py)"""
 import json
+from pathlib import Path
 
 import pytest
 
@@ -112,6 +113,51 @@ def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
     rc, out = _run(st_main, ["unpack", str(tmp_path / "one.safetensors"), str(tmp_path / "un" / "checkpoints" / "step_000000002")], capsys)
     assert rc == 0 and hash_checkpoint(json.loads(out)["dir"]) == hash_checkpoint(ck)
 
+    # the reference's command names and switches: to-safetensors / from-safetensors, --verify, --keys, --top-level-key
+    import pytest
+    import torch
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    from open_transformers_b200.cli import dcp_safetensors as DS
+
+    full = tmp_path / "full.safetensors"
+    rc, out = _run(st_main, ["to-safetensors", ck, str(full), "--verify"], capsys)
+    info = json.loads(out)
+    assert rc == 0 and info["verified"] and info["top_level_keys"] == ["model", "optim"] and "meta.json" in info["sidecar_files"]
+    with safe_open(str(full), framework="pt") as f:
+        header = f.metadata()
+        names = set(f.keys())
+    assert header["pretrain.format"] == "dcp-safetensors/1" and "pretrain.skeleton" in header and "pretrain.sidecar" in header
+    assert "optim.state.0.exp_avg" in names and any(n.startswith("__sidecar__.rng.") for n in names)
+    back = tmp_path / "back" / "checkpoints" / "step_000000002"
+    rc, out = _run(st_main, ["from-safetensors", str(full), str(back), "--verify"], capsys)
+    assert rc == 0 and json.loads(out)["verified"] and (back / "_COMPLETE").exists() and (back / "dcp" / ".metadata").exists()
+    for name in ("meta.json", "state_hash.txt", "global_stream.json", "spike_protocol.json", "batch_hasher.rank_1.bin"):
+        assert (back / name).read_bytes() == (Path(ck) / name).read_bytes(), name
+    assert DS.same_state(DS.read_dcp(back / "dcp"), DS.read_dcp(Path(ck) / "dcp"))
+    assert st_main(["from-safetensors", str(full), str(back)]) == 2    # a DCP writer adds files: a non-empty target is refused
+    # weights only: no sidecar travels, the way back is a bare DCP directory
+    rc, out = _run(st_main, ["to-safetensors", ck, str(tmp_path / "w.safetensors"), "--keys", "model"], capsys)
+    assert rc == 0 and json.loads(out)["sidecar_files"] is None and json.loads(out)["top_level_keys"] == ["model"]
+    rc, out = _run(st_main, ["from-safetensors", str(tmp_path / "w.safetensors"), str(tmp_path / "bare"), "--verify"], capsys)
+    assert rc == 0 and (tmp_path / "bare" / ".metadata").exists() and not (tmp_path / "bare" / "_COMPLETE").exists()
+    assert st_main(["to-safetensors", ck, str(tmp_path / "x.safetensors"), "--keys", "nothing_like_this"]) == 2
+    # a foreign file (no skeleton) nested under --top-level-key; NaN payloads compare equal bit for bit
+    foreign = {"a.weight": torch.tensor([1.0, float("nan"), -0.0]), "b.weight": torch.arange(6, dtype=torch.int32).view(2, 3)}
+    save_file(foreign, str(tmp_path / "foreign.safetensors"))
+    rc, out = _run(st_main, ["from-safetensors", str(tmp_path / "foreign.safetensors"), str(tmp_path / "fdcp"), "--top-level-key", "model", "--verify"], capsys)
+    assert rc == 0 and DS.same_state(DS.read_dcp(tmp_path / "fdcp"), {"model": foreign})
+    assert not DS.same_bits(torch.tensor([0.0]), torch.tensor([-0.0])) and DS.same_bits(torch.tensor([float("nan")]), torch.tensor([float("nan")]))
+    # names in a sidecar become paths: anything outside the allow-list is refused before a byte is written
+    with safe_open(str(full), framework="pt") as f:
+        tensors = {k: f.get_tensor(k) for k in f.keys()}
+    evil = dict(header)
+    evil["pretrain.sidecar"] = header["pretrain.sidecar"].replace("meta.json", "../../escape.json")
+    save_file(tensors, str(tmp_path / "evil.safetensors"), metadata=evil)
+    assert st_main(["from-safetensors", str(tmp_path / "evil.safetensors"), str(tmp_path / "evil_out")]) == 2
+    assert not (tmp_path / "escape.json").exists() and not (tmp_path / "evil_out" / "meta.json").exists()
+
 
 def test_train_command_creates_synthetic_data_resumes_and_refuses_to_overwrite(tmp_path, capsys):
     """the console entry of training, as a subprocess user would call it: first run with --synthetic-data and --max-steps,
@@ -161,15 +207,24 @@ def test_safetensors_interchange_refuses_foreign_files_and_path_like_sidecar_nam
     back = unpack(str(tmp_path / "ok.safetensors"), str(tmp_path / "back" / "checkpoints" / "step_000000002"))
     assert back["tensors"] == info["tensors"] and (tmp_path / "back" / "checkpoints" / "step_000000002" / "_COMPLETE").exists()
     t = {"model.w": torch.zeros(2)}
-    save_file(t, str(tmp_path / "foreign.safetensors"), metadata={"pretrain.format": "something/9"})
+    skeleton = json.dumps({"t": "dict", "items": [["model", {"t": "dict", "items": [["w", {"t": "tensor", "key": "model.w"}]]}]]})
+    save_file(t, str(tmp_path / "foreign.safetensors"), metadata={"pretrain.format": "something/9", "pretrain.skeleton": skeleton})
     with pytest.raises(ValueError):
         unpack(str(tmp_path / "foreign.safetensors"), str(tmp_path / "o1"))
+
+    def sidecar(name):
+        files = {"t": "dict", "items": [[name, {"t": "v", "v": "hi"}]]}
+        return json.dumps({"t": "dict", "items": [["files", files], ["rng", {"t": "dict", "items": []}], ["grads", {"t": "v", "v": None}]]})
+
     for bad in ("../escape.txt", "/tmp/abs.txt", "sub/meta.json", "meta.json.bak", "rng.rank_x.pt"):
-        save_file(t, str(tmp_path / "evil.safetensors"), metadata={"pretrain.format": FORMAT, "pretrain.skeleton": "{}",
-                                                                    "pretrain.sidecar": json.dumps({bad: "aGk="})})
+        save_file(t, str(tmp_path / "evil.safetensors"), metadata={"pretrain.format": FORMAT, "pretrain.skeleton": skeleton,
+                                                                    "pretrain.sidecar": sidecar(bad)})
         with pytest.raises(ValueError):
             unpack(str(tmp_path / "evil.safetensors"), str(tmp_path / "o2"))
         assert not (tmp_path / "o2").exists() and not (tmp_path / "escape.txt").exists()
+    save_file(t, str(tmp_path / "fine.safetensors"), metadata={"pretrain.format": FORMAT, "pretrain.skeleton": skeleton, "pretrain.sidecar": sidecar("meta.json")})
+    unpack(str(tmp_path / "fine.safetensors"), str(tmp_path / "o3"))
+    assert (tmp_path / "o3" / "meta.json").read_text() == "hi"
     with pytest.raises(FileNotFoundError):
         pack(str(tmp_path / "nowhere"), str(tmp_path / "x.safetensors"))
 

@@ -153,12 +153,15 @@ def test_off_cadence_final_checkpoint_hash_equals_log_and_replay_and_does_not_ad
 @pytest.mark.distributed
 def test_sharded_ownership_by_messages_through_the_train_loop_and_a_checkpoint(tmp_path):
     """two processes with sharded ownership over point-to-point messages (the transport of GPUs on several machines): hashes
-    of the single-process run, a checkpoint whose state was completed by broadcasts, and a single-process resume from it"""
+    of the single-process run, a checkpoint into which each process wrote the rows it owns (data files of both processes,
+    no gathering to rank 0), and a single-process resume from it"""
     tmp = str(tmp_path)
     over = LONG + ["++train.state_hash.tensor_digest=tree"]
     whole = train(tiny_cfg(tmp, over + ["run.run_id=one"]), device="cpu", data_root=tmp)
     two = _ranks(2, tmp, over + ["run.run_id=msg"], None, 2, str(tmp_path / "msg.json"), OTB_GRAD_TRANSPORT="collective")
     assert two == whole["hashes"][:2]
+    files = sorted(p.name for p in Path("%s/runs/msg/checkpoints/step_000000002/dcp" % tmp).iterdir())
+    assert ".metadata" in files and any(f.startswith("__0_") for f in files) and any(f.startswith("__1_") for f in files), files
     rest = train(tiny_cfg(tmp, over + ["run.run_id=msg"]), resume_from="%s/runs/msg/checkpoints/step_000000002" % tmp, device="cpu", data_root=tmp)
     assert rest["hashes"] == whole["hashes"][2:]
 
@@ -272,3 +275,42 @@ def test_token_clocked_checkpoints_and_latest(tmp_path):
     assert Path(ck.latest()).name == "step_000000004"
     r = audit_replay(str(ckdir / "step_000000002"), data_root=tmp)  # default span: to the next checkpoint of the cadence
     assert r["step"] == 4 and r["match"] is True
+
+
+def test_the_tensor_payload_is_what_a_torch_optimizer_and_module_would_save(runs):
+    """dcp/ holds {"model": state_dict, "optim": optimizer.state_dict()} in torch's own packing: optimizer state under
+    integer parameter indices (numbered group by group) and a `params` index list in every param_group. A plain module
+    with the same parameter names and a torch.optim.Optimizer over the same [decay, no_decay] groups provide the template;
+    DCP fills it and the values are the engine's."""
+    import torch
+    import torch.distributed.checkpoint as dcp
+
+    from open_transformers_b200.train.checkpoint import Checkpointer
+    from open_transformers_b200.train.engine import TrainEngine
+
+    tmp, whole, first = runs
+    ck = whole["run_dir"] + "/checkpoints/step_000000004"
+    cfg = tiny_cfg(tmp, LONG)
+    eng = TrainEngine(cfg, "cpu")
+    Checkpointer(whole["run_dir"]).load(ck, eng)
+    lay = eng.layout
+    params = {n: torch.nn.Parameter(torch.zeros(lay.shapes[i])) for i, n in enumerate(lay.names)}
+    groups = [{"params": [params[n] for n, m in zip(lay.names, lay.groups) if m == gi], "weight_decay": g["weight_decay"]}
+              for gi, g in enumerate(eng.param_groups)]
+    class Shell(torch.optim.Optimizer):               # the reference's optimizer shell: these defaults, state per parameter
+        def __init__(self, groups):
+            super().__init__(groups, dict(lr=1.0, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, amsgrad=False))
+
+    opt = Shell(groups)
+    for p in params.values():                         # primed state, as prime_optimizer_state leaves it
+        opt.state[p] = {"step": torch.zeros((), dtype=torch.int64), "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+    template = {"model": {n: p.data for n, p in params.items()}, "optim": opt.state_dict()}
+    dcp.load(template, storage_reader=dcp.FileSystemReader(ck + "/dcp"), no_dist=True)
+    opt.load_state_dict(template["optim"])
+    for i, n in enumerate(lay.names):
+        st = opt.state[params[n]]
+        assert torch.equal(params[n].data, lay.view(eng.master, i)), n
+        assert torch.equal(st["exp_avg"], lay.view(eng.m1, i)) and torch.equal(st["exp_avg_sq"], lay.view(eng.m2, i)), n
+        assert int(st["step"]) == eng.opt_step == 4
+    assert [g["lr"] for g in opt.param_groups] == [g["lr"] for g in eng.param_groups]
+    eng.close()
