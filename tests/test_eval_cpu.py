@@ -153,3 +153,96 @@ def test_eval_command_scripts_and_core_aggregate(ckpt, tmp_path, capsys):
     r = subprocess.run([sys.executable, str(ROOT / "scripts" / "prompt_checkpoint.py"), "--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--prompt", "the quick",
                         "--max-new-tokens", "3", "--temperature", "0"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.startswith("the quick"), r.stderr[-2000:]
+
+
+def test_olmes_suites_through_a_stand_in_for_oe_eval(ckpt, tmp_path, monkeypatch):
+    """`run_olmes` against stand-ins for the two packages it drives (neither is installed here): suite names expand to
+    leaf configs tagged with their alias, every leaf travels as one JSON argument, the library's model loader is swapped
+    for ours during the run and put back after, and metrics-all.jsonl is distilled into summary.json."""
+    import json
+    import sys
+    import types
+
+    from open_transformers_b200.eval import olmes_runner as R
+
+    suites = {"core_9mcqa::olmes": {"tasks": ["arc_easy::olmes", "pair"]}, "pair": {"tasks": ["boolq:mc::olmes", "boolq:rc::olmes"]},
+              "mmlu::olmes": {"tasks": ["mmlu_x:mc::olmes"]}}
+    configs = {n: {"task_name": n.split(":")[0], "num_shots": 5} for n in ("arc_easy::olmes", "boolq:mc::olmes", "boolq:rc::olmes",
+                                                                            "mmlu_x:mc::olmes", "gsm8k::olmes")}
+    leaves = R.expand_olmes_tasks(["core_9mcqa::olmes", "gsm8k::olmes"], suites, configs)
+    assert [c["metadata"]["alias"] for c in leaves] == ["arc_easy::olmes", "boolq:mc::olmes", "boolq:rc::olmes", "gsm8k::olmes"]
+    assert "metadata" not in configs["arc_easy::olmes"]                       # the tables themselves are not edited
+    with pytest.raises(ValueError):
+        R.expand_olmes_tasks(["no_such_task"], suites, configs)
+    with pytest.raises(ValueError):
+        R.expand_olmes_tasks(["loop"], {"loop": {"tasks": ["loop"]}}, configs)
+
+    seen = {}
+
+    class FakeHFLM:
+        max_gen_toks = 4
+
+        def __init__(self, pretrained=None, tokenizer=None, backend=None, batch_size=1, max_length=0):
+            self.model, self.tokenizer, self.batch_size, self.max_length = pretrained, tokenizer, batch_size, max_length
+
+        def _model_call(self, ids):
+            return self.model(ids).logits
+
+        def tok_decode(self, ids):
+            return " ".join(map(str, ids))
+
+        eot_token_id = 0
+
+    import argparse
+
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--task", nargs="+")
+    for flag in ("--model", "--model-type", "--output-dir", "--batch-size", "--max-length"):
+        parser.add_argument(flag)
+
+    def fake_run_eval(args):
+        lm = oe_run.load_model({})
+        seen["lm"], seen["args"] = lm, args
+        ids = torch.randint(1, 200, (2, 5))
+        out = lm._model_generate(ids, torch.ones_like(ids), stop=None, max_length=8)
+        seen["generated"] = out["sequences"].shape, len(out["scores"])
+        rows = [{"task_name": "core_9mcqa", "task_idx": None, "task_config": {"metadata": {"alias": "core_9mcqa::olmes"}}, "metrics": {"primary_score": 0.5}},
+                {"task_name": "mmlu", "task_idx": None, "task_config": {"metadata": {"alias": "mmlu::olmes"}}, "metrics": {"primary_score": 0.3}},
+                {"task_name": "boolq", "task_idx": 1, "task_config": {"metadata": {"alias": "boolq:mc::olmes"}}, "metrics": {"primary_score": 0.6}},
+                {"task_name": "gsm8k", "task_idx": 3, "task_config": {"metadata": {"alias": "gsm8k::olmes"}}, "metrics": {"primary_score": 0.1}},
+                {"task_name": "broken", "task_idx": 4, "metrics": {}}]
+        (Path(args["output_dir"]) / "metrics-all.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+
+    oe_run = types.ModuleType("oe_eval.run_eval")
+    oe_run._parser, oe_run.run_eval, oe_run.load_model = parser, fake_run_eval, "the stock loader"
+    mods = {"oe_eval": types.ModuleType("oe_eval"), "oe_eval.run_eval": oe_run, "oe_eval.configs": types.ModuleType("oe_eval.configs"),
+            "oe_eval.configs.task_suites": types.ModuleType("oe_eval.configs.task_suites"),
+            "oe_eval.configs.tasks": types.ModuleType("oe_eval.configs.tasks"), "oe_eval.models": types.ModuleType("oe_eval.models"),
+            "oe_eval.models.eleuther_huggingface": types.ModuleType("oe_eval.models.eleuther_huggingface"),
+            "lm_eval": types.ModuleType("lm_eval"), "lm_eval.models": types.ModuleType("lm_eval.models"),
+            "lm_eval.models.huggingface": types.ModuleType("lm_eval.models.huggingface")}
+    mods["oe_eval"].run_eval = oe_run
+    mods["oe_eval.configs.task_suites"].TASK_SUITE_CONFIGS = suites
+    mods["oe_eval.configs.tasks"].TASK_CONFIGS = configs
+    mods["lm_eval.models.huggingface"].HFLM = FakeHFLM
+    mods["oe_eval.models.eleuther_huggingface"].HFLM_Verbose = type("HFLM_Verbose", (FakeHFLM,), {})
+    for name, mod in mods.items():
+        monkeypatch.setitem(sys.modules, name, mod)
+    monkeypatch.setattr(R, "build_hf_tokenizer", lambda path: type("Tok", (), {"pad_token_id": 3, "__len__": lambda self: 256})())
+
+    model, _cfg, _eng = load_model_from_checkpoint(ckpt[0], "cpu")
+    summary = R.run_olmes(model, ckpt[1], tmp_path / "olmes", tasks=["core_9mcqa::olmes", "mmlu::olmes"], extended=False, batch_size=2,
+                          max_length=64, limit=7, device="cpu", model_label="m")
+    assert oe_run.load_model == "the stock loader"                            # put back after the run
+    sent = [json.loads(t) for t in seen["args"]["task"]]
+    assert [t["metadata"]["alias"] for t in sent] == ["arc_easy::olmes", "boolq:mc::olmes", "boolq:rc::olmes", "mmlu_x:mc::olmes"]
+    assert all(t["limit"] == 7 for t in sent) and seen["args"]["batch_size"] == "2" and seen["args"]["model_type"] == "hf"
+    assert seen["generated"][0][0] == 2 and 1 <= seen["generated"][1] <= 3 and seen["generated"][0][1] == 5 + seen["generated"][1]
+    assert summary["olmes_macro"] == pytest.approx((9 * 0.5 + 0.3) / 10) and summary["num_leaf_tasks"] == 1
+    assert summary["extended_tasks"] == {"gsm8k::olmes": 0.1} and summary["aggregates"]["mmlu::olmes"] == 0.3
+    assert json.loads((tmp_path / "olmes" / "summary.json").read_text()) == summary
+
+
+def test_olmes_cli_says_what_is_missing_without_oe_eval(ckpt, capsys):
+    assert olmes_main(["--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--out-dir", "/tmp/never_written"]) == 2
+    assert "oe_eval" in capsys.readouterr().err
