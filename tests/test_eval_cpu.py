@@ -149,7 +149,7 @@ def test_eval_command_scripts_and_core_aggregate(ckpt, tmp_path, capsys):
     assert (tmp_path / "c.png").exists() or r.stdout.count("\n") >= 3          # a figure, or the CSV dump where matplotlib is absent
     r = subprocess.run([sys.executable, str(ROOT / "scripts" / "collect_system_info.py")], capture_output=True, text=True, timeout=300)
     info = json.loads(r.stdout)
-    assert r.returncode == 0 and info["cpus"] >= 1 and "torch" in info and isinstance(info["env"], dict)
+    assert r.returncode == 0 and info["cpu"]["logical_cpus"] >= 1 and "version" in info["torch"] and isinstance(info["env"], dict)
     r = subprocess.run([sys.executable, str(ROOT / "scripts" / "prompt_checkpoint.py"), "--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--prompt", "the quick",
                         "--max-new-tokens", "3", "--temperature", "0"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.startswith("the quick"), r.stderr[-2000:]
@@ -246,3 +246,66 @@ def test_olmes_suites_through_a_stand_in_for_oe_eval(ckpt, tmp_path, monkeypatch
 def test_olmes_cli_says_what_is_missing_without_oe_eval(ckpt, capsys):
     assert olmes_main(["--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--out-dir", "/tmp/never_written"]) == 2
     assert "oe_eval" in capsys.readouterr().err
+
+
+def test_system_snapshot_sections_fake_gpu_inventory_and_redaction(tmp_path, monkeypatch):
+    """Every section is there, a broken probe costs only its own section, the GPU inventory comes from nvidia-smi's query
+    output (a stand-in executable here, which only answers reads), and variables that look like secrets are redacted."""
+    import importlib.util
+    import stat
+
+    spec = importlib.util.spec_from_file_location("collect_system_info", ROOT / "scripts" / "collect_system_info.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    fake = tmp_path / "nvidia-smi"
+    row = "0, NVIDIA B200, GPU-abc, 580.159, 97.00, 183359, 12, 1965, 1965, 3996, 3996, 180.5, 1000.00, 41, Enabled, Default, Enabled, Disabled, 5, 16"
+    fake.write_text("#!/bin/sh\ncase \"$*\" in *query-gpu*) echo '%s'; echo '%s' | sed 's/^0/1/';; *topo*) echo 'GPU0 GPU1 NV18';; *) echo links;; esac\n" % (row, row))
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + ":" + __import__("os").environ["PATH"])
+    monkeypatch.setenv("WANDB_API_KEY", "do-not-print")
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    monkeypatch.setenv("UNRELATED_SETTING", "x")
+    monkeypatch.setitem(mod.PROBES, "memory", lambda: 1 / 0)
+    info = mod.collect([ROOT])
+    for section in ("host", "kubernetes", "cpu", "memory", "disk", "network", "gpu", "nvidia_driver", "cuda", "python", "torch", "kernels", "git", "env", "pip_freeze"):
+        assert section in info, section
+    assert info["memory"] == {"error": "ZeroDivisionError: division by zero"} and info["cpu"]["logical_cpus"] >= 1
+    assert info["gpu"]["count"] == 2 and info["gpu"]["devices"][1]["name"] == "NVIDIA B200" and info["gpu"]["devices"][0]["clocks.max.sm"] == "1965"
+    assert "NV18" in info["gpu"]["topology"]
+    assert info["env"]["WANDB_API_KEY"] == "<redacted>" and info["env"]["NCCL_NVLS_ENABLE"] == "0" and "UNRELATED_SETTING" not in info["env"]
+    assert set(info["kernels"]["native_source_digests"]) >= {"otb_cpu"} and str(ROOT) in info["git"]
+    assert "2 x NVIDIA B200 driver=580.159" in mod.summary_line(info)
+    out = tmp_path / "deep" / "pod-0.json"
+    assert mod.main(["--output", str(out)]) == 0 and json.loads(out.read_text())["schema_version"] == 1
+
+
+def test_prompt_session_commands_change_the_sampler_and_reject_nonsense(ckpt):
+    import importlib.util
+    import io
+
+    spec = importlib.util.spec_from_file_location("prompt_checkpoint", ROOT / "scripts" / "prompt_checkpoint.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["prompt_checkpoint"] = mod                                     # dataclasses look their module up by name
+    spec.loader.exec_module(mod)
+    out = io.StringIO()
+    sess = mod.Session(mod.Settings(), out)
+    assert not sess.command("once upon a time")
+    for line in (":temp 0", ":topk 5", ":topp 0.5", ":tokens 3", ":seed 7", ":show"):
+        assert sess.command(line)
+    assert (sess.s.temperature, sess.s.top_k, sess.s.top_p, sess.s.max_new_tokens, sess.s.seed) == (0.0, 5, 0.5, 3, 7)
+    for line in (":temp hot", ":topp 1.5", ":tokens 0", ":tokens", ":frobnicate 1"):
+        assert sess.command(line)
+    assert (sess.s.temperature, sess.s.top_p, sess.s.max_new_tokens) == (0.0, 0.5, 3)          # nothing changed
+    text = out.getvalue()
+    assert "not a number: hot" in text and "top_p out of range" in text and ":tokens needs a value" in text and "unknown command :frobnicate" in text
+    assert "temperature=0 top_k=5 top_p=0.5 max_new_tokens=3 seed=7" in text
+    with pytest.raises(SystemExit):
+        sess.command(":quit")
+    model, cfg, _ = load_model_from_checkpoint(ckpt[0], "cpu")
+    tok = Tokenizer(ckpt[1])
+    out.seek(0)
+    out.truncate()
+    a = sess.complete(model, tok, "the quick", "cpu", cfg.train.seq_len)
+    assert a.startswith("the quick") and out.getvalue().rstrip("\n") == a            # what was streamed is what was returned
+    sess.command(":seed 7")
+    assert sess.complete(model, tok, "the quick", "cpu", cfg.train.seq_len, stream=False) == a   # greedy: the same text again
