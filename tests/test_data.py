@@ -128,3 +128,87 @@ def test_corpus_fan_out_shards_every_document_once_in_file_order(tmp_path):
         r = IndexedDatasetReader(str(tmp_path / "out" / sh.prefix))
         seen += [tok.decode(r.document(i).tolist()) for i in range(sh.num_documents)]
     assert seen == docs
+
+
+def test_corpus_pulls_resume_where_they_stopped_and_the_build_stages_are_idempotent(tmp_path):
+    """scripts/build_corpus.py with stand-ins for the network: a pull that dies between two resume notes is cut back to the
+    last note and continues from the recorded row of the raw stream (a filter that drops three rows in four makes the two
+    counts differ), quotas split a target over several configurations, file lists are visited round-robin without their
+    evaluation splits, blob fetches keep their order, and `build` skips what is already there."""
+    import json
+    import sys
+    from pathlib import Path
+
+    from open_transformers_b200.data.manifest import SourceManifest
+    from open_transformers_b200.data.tokenizer import train_tokenizer
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "scripts"))
+    import build_corpus as bc
+
+    calls = []
+
+    def rows(skip):
+        calls.append(skip)
+        for i in range(skip, 100_000):
+            yield {"text": "row %d" % i, "int_score": 3 if i % 4 == 0 else 1}
+
+    keep = lambda r: r["text"] if r["int_score"] >= 3 else None  # noqa: E731
+    out = tmp_path / "raw" / "fineweb.jsonl"
+
+    class Died(Exception):
+        pass
+
+    def dying(skip):
+        for r in rows(skip):
+            if r["text"] == "row 1000":       # the 251st kept row: past the note written at 200 documents
+                raise Died()
+            yield r
+
+    with pytest.raises(Died):
+        bc.pull(out, 500, [(bc.Stream("fw", dying, keep), None)], chunk=100)
+    assert len(out.read_text().splitlines()) == 250 and json.loads((tmp_path / "raw" / "fineweb.jsonl.scanned").read_text())["taken"] == {"fw": 200}
+    with open(out, "a") as f:
+        f.write('{"text": "torn li')                                         # and a torn last line on top
+    have, scanned = bc.pull(out, 500, [(bc.Stream("fw", rows, keep), None)], chunk=100)
+    texts = [json.loads(l)["text"] for l in out.read_text().splitlines()]
+    assert have == 500 and texts == ["row %d" % (4 * i) for i in range(500)]  # nothing lost, nothing twice
+    assert calls[-1] == 797 and scanned == {"fw": 1997}                       # resumed at the raw row after the 200th kept one
+    assert bc.pull(out, 500, [(bc.Stream("fw", rows, keep), None)], chunk=100)[0] == 500 and len(out.read_text().splitlines()) == 500
+    (tmp_path / "raw" / "fineweb.jsonl.scanned").write_text(json.dumps({"taken": {"fw": 900}, "scanned": {"fw": 1}}))
+    with pytest.raises(RuntimeError):
+        bc.pull(out, 1000, [(bc.Stream("fw", rows, keep), None)], chunk=100)
+
+    shares = bc.split_by_weight(1001, {"a": 0.5, "b": 0.3, "c": 0.2})
+    assert shares == {"a": 500, "b": 300, "c": 201}
+    mixed = tmp_path / "raw" / "proof.jsonl"
+    streams = [(bc.Stream(k, (lambda k: lambda skip: ({"text": "%s %d" % (k, i)} for i in range(skip, 10_000)))(k), bc.text_of), q) for k, q in shares.items()]
+    assert bc.pull(mixed, 1001, streams, chunk=100)[0] == 1001
+    kinds = [json.loads(l)["text"].split()[0] for l in mixed.read_text().splitlines()]
+    assert kinds == ["a"] * 500 + ["b"] * 300 + ["c"] * 201
+
+    order = [p for _, p in bc.round_robin_files({"math": ["m1", "m2", "m3"], "code": ["c1"], "web": ["w1", "w2"]})]
+    assert order == ["c1", "m1", "w1", "m2", "w2", "m3"]
+    assert bc.is_eval_split("/data/math/test/part-0.jsonl") and bc.is_eval_split("/x/heldout-1.jsonl") and not bc.is_eval_split("/data/math/train/part-0.jsonl")
+    import time as _t
+
+    fetched = list(bc.ordered_fetch(range(40), lambda i: (_t.sleep(0.001 * (i % 5)), None if i % 7 == 0 else i * i)[1], workers=8, window=16))
+    assert [i for i, _ in fetched] == list(range(40)) and fetched[7] == (7, None) and fetched[6] == (6, 36)
+    stack = bc.source_streams("stack", 10, fetch_blob=lambda r: "code of " + r["blob_id"], workers=4)
+    assert len(stack) == 1 and stack[0][1] is None
+
+    docs = ["document number %d says hello" % i for i in range(300)]
+    tok = train_tokenizer(iter(docs), tmp_path / "tok.json", vocab_size=300, min_frequency=1)
+    pulled = []
+
+    def fake_pull(raw, n, source):
+        pulled.append(source)
+        Path(raw).parent.mkdir(parents=True, exist_ok=True)
+        Path(raw).write_text("".join(json.dumps({"text": d}) + "\n" for d in docs[:n]))
+        return n, {}
+
+    done = bc.build({"dclm": 120, "proof": 0, "fineweb": 80}, tmp_path / "r", tmp_path / "s", tok, workers=2, only=["dclm", "fineweb"], pull_fn=fake_pull, log=lambda m: None)
+    assert pulled == ["dclm", "fineweb"] and set(done) == {"dclm", "fineweb"}
+    assert SourceManifest.load(done["dclm"]).total_documents == 120 and (tmp_path / "r" / "dclm.jsonl.shuffled").is_file()
+    assert sorted(json.loads(l)["text"] for l in (tmp_path / "r" / "dclm.jsonl").read_text().splitlines()) == sorted(docs[:120])
+    again = bc.build({"dclm": 120, "fineweb": 80}, tmp_path / "r", tmp_path / "s", tok, workers=2, pull_fn=fake_pull, log=lambda m: None)
+    assert again == done and pulled == ["dclm", "fineweb"]                   # manifests exist: nothing pulled or sharded again
