@@ -77,3 +77,28 @@ def test_overlapped_state_hash_equals_the_synchronous_one():
         pending = eng.begin_state_hash(tensor_digest="tree")
     got.append(eng.finish_state_hash(pending, prev, None))
     assert got == sync
+
+
+def test_offloaded_moments_leave_the_gpu_between_steps_and_change_no_bit(tmp_path):
+    """--offload-optimizer on a GPU: the two moment buffers are written to their files after the step's hash and read back for
+    the next optimizer step; they are absent during forward and backward and no digest changes."""
+    cfg = load_config("open1b_b200", ["model.n_layers=2", "model.vocab_size=4096", "train.seq_len=256", "data.seq_len=256",
+                                      "run.virtual_dp_size=2", "run.dp_shard_size=2"])
+    want = [h for _, _, h in _run(cfg, "cuda", steps=3, T=256, vocab=4096, td="tree")]
+    eng = TrainEngine(cfg, "cuda", offload_optimizer=True, optimizer_offload_dir=str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prev, got = None, []
+    for _ in range(3):
+        eng.zero_grads()
+        for v in range(2):
+            ids = torch.randint(0, 4096, (2, 256), generator=g).to("cuda")
+            lab = torch.randint(0, 4096, (2, 256), generator=g).to("cuda")
+            eng.forward_backward(v, ids, lab, 1)
+        assert got == [] or eng._m1 is None  # absent during forward and backward
+        norm = eng.reduce_gradients()
+        eng.optimizer_step(3e-4, eng.clip_coefficient(norm, 1.0))
+        prev = eng.sharded_state_hash(prev, None, tensor_digest="tree")
+        got.append(prev)
+        eng.release_state()
+    assert got == want
+    eng.close()

@@ -289,3 +289,13 @@ def test_grad_reduce_gpu_equals_cpu_fold_in_any_launch_order(S, R):
         _eq(out_cpu, out2, "reduced gradient, launch order %s" % order)
         _eq(sos_cpu, sos2, "chunk partials, launch order %s" % order)
     del ctypes
+
+
+def test_gpu_hadamard_int8_product_bitwise_vs_cpu():
+    """rotation (IEEE adds), row statistics, quantiser and the tcgen05 kind::i8 GEMM give the CPU twin's bits"""
+    g = torch.Generator().manual_seed(8)
+    a, b = torch.randn(256, 384, generator=g), torch.randn(136, 384, generator=g).bfloat16()
+    a[5, 100] = 90.0
+    cpu, gpu = _both(lambda a_, b_: K.ste_matmul_hadamard(a_, b_), a, b)
+    assert torch.equal(cpu, gpu.cpu()), "%d elements differ" % int((cpu != gpu.cpu()).sum())
+    assert K.kernel_status("cuda") == 0

@@ -41,3 +41,23 @@ def test_hashes_do_not_depend_on_the_gpu_count(tmp_path, shard):
         assert many["status"] == 0
         assert many["overlapped_steps"] == 3  # every step's reduction ran bucket by bucket under the last backward pass
         assert many["hashes"] == one["hashes"], (n, many, one)
+
+
+def test_message_transport_between_two_gpus_reproduces_the_single_gpu_hashes(tmp_path):
+    """OTB_GRAD_TRANSPORT=collective on GPUs of one machine (NCCL point-to-point in place of peer loads): the transport of
+    runs that span machines, checked against the single-GPU bytes"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    worker = str(Path(__file__).resolve().parent / "multi_gpu_worker.py")
+
+    def run(n, out, **extra):
+        env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_SHARD="4", NCCL_NVLS_ENABLE="0", **extra)
+        cmd = [sys.executable, worker] if n == 1 else [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % n,
+                                                       "--master-addr", "127.0.0.1", "--master-port", str(free_port()), worker]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        return json.load(open(out))
+
+    one = run(1, tmp_path / "g1.json")
+    two = run(2, tmp_path / "g2.json", OTB_GRAD_TRANSPORT="collective")
+    assert one["status"] == 0 and two["status"] == 0 and two["hashes"] == one["hashes"]

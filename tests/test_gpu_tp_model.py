@@ -1,5 +1,6 @@
-"""Tensor-parallel MODEL step on GPUs: a group of 2 GPUs (NCCL all-gathers around the tcgen05 kernels) must write the
-hashes, losses and gradient norms of the single-GPU run of the same bf16 model."""
+"""Tensor-parallel MODEL step on GPUs: a group of 2 GPUs must write the hashes, losses and gradient norms of the single-GPU
+run of the same bf16 model, with NCCL all-gathers around the tcgen05 kernels and with the fused peer-memory kernels
+(`run.tp_fused`); two groups of two on four GPUs likewise."""
 import json
 import os
 import subprocess
@@ -33,4 +34,23 @@ def test_tensor_parallel_pair_of_gpus_reproduces_the_single_gpu_bytes(tmp_path):
         pytest.skip("needs at least 2 GPUs")
     one = _run(1, 1, tmp_path / "g1.json")
     two = _run(2, 2, tmp_path / "g2.json")
+    assert two == one, (two, one)
+
+
+def test_two_tensor_parallel_groups_on_four_gpus_reproduce_the_single_gpu_hashes(tmp_path):
+    """TP = 2 x DP = 2: each group hosts one virtual rank; gradient buffers cross by NCCL all-gather"""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs at least 4 GPUs")
+    one = _run(1, 1, tmp_path / "g1.json")
+    four = _run(4, 2, tmp_path / "g4.json")
+    assert [h for _, _, h in four] == [h for _, _, h in one]
+    assert [n for n, _, _ in four] == [n for n, _, _ in one]
+
+
+def test_fused_peer_memory_kernels_carry_the_tensor_parallel_model_step(tmp_path):
+    """run.tp_fused: all-gather -> GEMM and chained GEMM -> ordered reduction inside the model step; same bytes as one GPU"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    one = _run(1, 1, tmp_path / "g1.json")
+    two = _run(2, 2, tmp_path / "g2.json", "run.tp_fused=true")
     assert two == one, (two, one)

@@ -4,8 +4,8 @@ Some users of the native library cannot ask CUDA for memory while they run (a ho
 library without PyTorch's allocator; a serving loop that reserved all device memory at start-up), so
 ``otb_rmsnorm_bwd_noalloc`` keeps its work buffer inside the library. This test checks that it returns the
 same bits as the regular entry point, twice in a row (the second call sees the first call's leftovers in the
-shared buffer), and that it refuses problems larger than the buffer. It is collected last so that a failure
-here cannot hide any other test in a stop-at-first-failure run."""
+shared buffer), and that it refuses problems larger than the buffer. The file name makes pytest collect it after
+every other test file."""
 import ctypes
 
 import pytest
