@@ -212,6 +212,9 @@ def main() -> int:
     if rank == 0:
         tps = tokens_per_step * Kst / (ms_dev / 1e3)
         tps_e2e = tokens_per_step * Kst / (ms_e2e / 1e3)
+        from open_transformers_b200.obs.metrics import hardware_flops_per_token
+
+        hw_flops = hardware_flops_per_token(cfg.model, T)
         flops_per_token = 72 * cfg.model.n_layers * cfg.model.d_model ** 2 + 12 * cfg.model.n_layers * T * cfg.model.d_model + 6 * vocab * cfg.model.d_model
         line = {
             "metric": "OPEN-1B training tokens/s (bit-identical step hash across GPU counts)", "value": tps, "unit": "tokens/s",
@@ -227,7 +230,9 @@ def main() -> int:
             "e2e": {"value": tps_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / Kst,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4 + 4 * eng.n_segs},
             "gpu_launches": launches,
+            # the reference's formula (every layer as dense T x T attention) and what the kernels execute (causal, 512-key windows)
             "model_tflops_per_gpu": flops_per_token * tps / world / 1e12,
+            "hardware_flops_per_token": hw_flops, "hardware_tflops_per_gpu": hw_flops * tps / world / 1e12,
             "final_loss": loss, "final_hash": state["prev"], "kernel_status": status,
             "native_libs": native.loaded_libraries(),
         }

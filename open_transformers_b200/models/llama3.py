@@ -54,6 +54,11 @@ class Llama3(nn.Module):
         self.norm_out = NORM.get(cfg.modules.norm)(cfg.d_model, eps=cfg.rms_norm_eps)
         self.activation_checkpoint = False
         self.ac_every_other_block = False
+        # CPU runs with activation checkpointing: keep each block's attention results for the recomputation
+        # (PRETRAIN_CPU_ATTENTION_CHECKPOINT_CACHE=1, or the reference's REPOP_CPU_ATTENTION_CHECKPOINT_CACHE=1)
+        import os
+
+        self.cpu_attention_cache = "1" in (os.environ.get("PRETRAIN_CPU_ATTENTION_CHECKPOINT_CACHE"), os.environ.get("REPOP_CPU_ATTENTION_CHECKPOINT_CACHE"))
         # set by the training engine for the last micro-batch of a step: called from the backward pass with a block's
         # index once that block (and everything after it) has produced its weight gradients; -1 = the vocabulary head
         self.bucket_notify = None
@@ -79,7 +84,11 @@ class Llama3(nn.Module):
                 x = A.bucket_mark(x, notify, i)
             if self.activation_checkpoint and self.training and (not self.ac_every_other_block or i % 2 == 0):
                 from torch.utils.checkpoint import checkpoint
-                x = checkpoint(blk, x, cos, sin, use_reentrant=False, preserve_rng_state=False)
+
+                extra = {}
+                if self.cpu_attention_cache and not x.is_cuda:
+                    extra["context_fn"] = A.cpu_attention_checkpoint_contexts
+                x = checkpoint(blk, x, cos, sin, use_reentrant=False, preserve_rng_state=False, **extra)
             else:
                 x = blk(x, cos, sin)
         x = self.norm_out(x)

@@ -451,6 +451,49 @@ def swiglu(gate_up):
     return SwiGLUFn.apply(gate_up)
 
 
+# Activation checkpointing recomputes a block's forward pass inside the backward pass. On a CPU the attention forward is
+# by far the most expensive part of that recomputation and its results (output and log-sum-exp rows) are small next to
+# the activations the checkpoint drops, so a replay on a CPU may keep them: `cpu_attention_checkpoint_contexts` is a
+# `context_fn` for torch.utils.checkpoint - the first context records the attention results of the original forward pass,
+# the second hands them out, in call order, to the recomputation. Bit-neutral: the recomputation would produce the same
+# values (reference: repop's cpu_attention_checkpoint_contexts, src/pretrain/parallel/parallelize_llama3_repop.py:118-124).
+_attn_cache: dict = {"mode": None, "store": None, "hits": 0}
+
+
+class _AttnCacheCtx:
+    def __init__(self, mode, store):
+        self.mode, self.store, self.prev = mode, store, None
+
+    def __enter__(self):
+        self.prev = (_attn_cache["mode"], _attn_cache["store"])
+        _attn_cache["mode"], _attn_cache["store"] = self.mode, self.store
+        if self.mode == "replay":
+            self.store["next"] = 0
+        return self
+
+    def __exit__(self, *exc):
+        _attn_cache["mode"], _attn_cache["store"] = self.prev
+        return False
+
+
+def cpu_attention_checkpoint_contexts():
+    store = {"results": [], "next": 0}
+    return _AttnCacheCtx("record", store), _AttnCacheCtx("replay", store)
+
+
+def _attn_fwd_cached(qk, q2, B, T, H, Hkv, D, window, int8_pv):
+    mode, store = _attn_cache["mode"], _attn_cache["store"]
+    if mode == "replay" and not qk.is_cuda and store["next"] < len(store["results"]):
+        out = store["results"][store["next"]]
+        store["next"] += 1
+        _attn_cache["hits"] += 1
+        return out
+    out = K.attn_fwd(qk, q2, B, T, H, Hkv, D, window, int8_pv)
+    if mode == "record" and not qk.is_cuda:
+        store["results"].append(out)
+    return out
+
+
 class AttentionFn(Function):
     """(gain-free QK-norm) -> RoPE -> causal / sliding-window flash attention on a packed qkv
     activation [B, T, (H + 2 Hkv) D]; returns [B, T, H D]."""
@@ -461,7 +504,7 @@ class AttentionFn(Function):
         q2 = qkv.reshape(B * T, -1)
         qk, rstd = K.qknorm_rope_fwd(q2, cos, sin, H + Hkv, D, T, qk_norm, eps)
         # int8 P V: quantised forward, straight-through (float shadow) backward through the ordinary kernels
-        O, lse = K.attn_fwd(qk, q2, B, T, H, Hkv, D, window, int8_pv)
+        O, lse = _attn_fwd_cached(qk, q2, B, T, H, Hkv, D, window, int8_pv)
         ctx.save_for_backward(q2, qk, rstd, O, lse, cos, sin)
         ctx.cfg = (B, T, H, Hkv, D, window, qk_norm)
         return O.view(B, T, H * D)

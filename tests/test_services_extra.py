@@ -286,3 +286,19 @@ def test_standalone_adamw_and_clip_helpers_give_the_engine_bits():
             assert torch.equal(p.detach(), after[n]), (step, n)
             assert torch.equal(opt.state[p]["exp_avg"], state[n]["exp_avg"]) and torch.equal(opt.state[p]["exp_avg_sq"], state[n]["exp_avg_sq"]), n
     eng.close()
+
+
+def test_hardware_flops_count_the_causal_mask_the_window_and_grouped_projections():
+    """8.54 GFLOP per token for the OPEN-1B shape (the reference's dense formula says 11.24): 6 per matrix weight, and per
+    layer 12 d per visible (query, key) pair - (T + 1) / 2 keys under the causal mask, about 480 under the 512-key window."""
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.obs.metrics import hardware_flops_per_token, transformer_flops_per_token
+
+    m = load_config("open1b_b200", []).model
+    hw = hardware_flops_per_token(m, 4096)
+    weights = 24 * (2048 * 2048 * 2 + 2048 * 512 * 2 + 3 * 2048 * 5632) + 128256 * 2048
+    window_keys = (512 * 513 / 2 + (4096 - 512) * 512) / 4096
+    assert hw == pytest.approx(6 * weights + 12 * 2048 * (5 * 2048.5 + 19 * window_keys))
+    assert 8.5e9 < hw < 8.6e9 < transformer_flops_per_token(24, 2048, 4096, 128256)
+    m2 = m.model_copy(update={"swa_window": 0})
+    assert hardware_flops_per_token(m2, 4096) == pytest.approx(6 * weights + 12 * 2048 * 24 * 2048.5)

@@ -277,6 +277,49 @@ def test_activation_checkpointing_changes_no_bit(bf16, monkeypatch):
     assert plain[2] == 2 * per_pass and every[2] == 2 * (per_pass + 6) and other[2] == 2 * (per_pass + 4)   # blocks 0 and 2 of 3 recomputed
 
 
+def test_cpu_attention_results_survive_the_recomputation_when_asked(monkeypatch):
+    """PRETRAIN_CPU_ATTENTION_CHECKPOINT_CACHE=1: under activation checkpointing on a CPU the recomputed block forward takes
+    each attention result from the original forward pass instead of running the kernel again; same hash, fewer calls."""
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.ops import autograd as A
+    from open_transformers_b200.ops import functional as K
+    from open_transformers_b200.train.engine import TrainEngine
+
+    def run(cache):
+        if cache:
+            monkeypatch.setenv("PRETRAIN_CPU_ATTENTION_CHECKPOINT_CACHE", "1")
+        else:
+            monkeypatch.delenv("PRETRAIN_CPU_ATTENTION_CHECKPOINT_CACHE", raising=False)
+        cfg = load_config("tiny_cpu", ["model.n_layers=3", "run.activation_checkpoint=true"])
+        eng = TrainEngine(cfg, "cpu")
+        g = torch.Generator().manual_seed(0)
+        calls = {"n": 0}
+        orig = K.attn_fwd
+
+        def counted(*a, **k):
+            calls["n"] += 1
+            return orig(*a, **k)
+
+        monkeypatch.setattr(K, "attn_fwd", counted)
+        hits0 = A._attn_cache["hits"]
+        eng.zero_grads()
+        for v in range(eng.V):
+            ids = torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g)
+            eng.forward_backward(v, ids, torch.randint(0, cfg.model.vocab_size, (2, 64), generator=g), 1)
+        norm = eng.reduce_gradients()
+        eng.optimizer_step(1e-3, 1.0)
+        h = eng.sharded_state_hash(None, None)
+        monkeypatch.setattr(K, "attn_fwd", orig)
+        eng.close()
+        return h, norm, calls["n"], A._attn_cache["hits"] - hits0
+
+    plain, cached = run(False), run(True)
+    assert plain[:2] == cached[:2]
+    assert plain[2] == 2 * 2 * 3 and plain[3] == 0            # two virtual ranks x (forward + recomputation) x three blocks
+    assert cached[2] == 2 * 3 and cached[3] == 2 * 3          # the recomputation took all six results from the first pass
+    assert A._attn_cache["mode"] is None
+
+
 @pytest.mark.parametrize("bf16", [False, True])
 def test_training_step_hash_is_the_same_on_the_plain_and_the_lane_parallel_gemm_twins(bf16):
     from open_transformers_b200.config import load_config
