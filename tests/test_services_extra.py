@@ -302,3 +302,50 @@ def test_hardware_flops_count_the_causal_mask_the_window_and_grouped_projections
     assert 8.5e9 < hw < 8.6e9 < transformer_flops_per_token(24, 2048, 4096, 128256)
     m2 = m.model_copy(update={"swa_window": 0})
     assert hardware_flops_per_token(m2, 4096) == pytest.approx(6 * weights + 12 * 2048 * 24 * 2048.5)
+
+
+def test_compiled_distribution_hook_translates_a_module_and_keeps_its_behaviour(tmp_path):
+    """setup.py's PRETRAIN_PYTHON_NATIVE path on one module: Cython translates `optim/schedules.py`, the C file is built
+    with -ffp-contract=off, the extension imports in place of the source and computes the same learning rates; package
+    markers stay source, and the recorded commit comes from PRETRAIN_BUILD_COMMIT when it is set."""
+    import importlib.util
+    import os
+    import shutil
+    import subprocess
+    import sys
+    import sysconfig
+    from pathlib import Path
+
+    pytest.importorskip("Cython")
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("otb_setup", root / "setup.py")
+    hook = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(hook)
+    mods = hook.compiled_modules()
+    assert len(mods) > 40 and not any(p.name in ("__init__.py", "__main__.py", "build_native.py") for p in mods)
+    os.environ["PRETRAIN_BUILD_COMMIT"] = "abc123"
+    try:
+        assert hook.build_commit() == "abc123"
+    finally:
+        del os.environ["PRETRAIN_BUILD_COMMIT"]
+    work = tmp_path / "w"
+    (work / "pkg").mkdir(parents=True)
+    shutil.copy(root / "open_transformers_b200" / "optim" / "schedules.py", work / "pkg" / "schedules.py")
+    (work / "pkg" / "__init__.py").write_text("")
+    exts = hook.cython_extensions([work / "pkg" / "schedules.py"], root=work, build_dir=str(work / "c"))
+    assert exts[0].name == "pkg.schedules" and "-ffp-contract=off" in exts[0].extra_compile_args
+    c_file = Path(exts[0].sources[0])
+    so = work / "pkg" / ("schedules" + sysconfig.get_config_var("EXT_SUFFIX"))
+    cc = sysconfig.get_config_var("CC").split()[0]
+    r = subprocess.run([cc, "-shared", "-fPIC", *exts[0].extra_compile_args, "-I", sysconfig.get_paths()["include"], str(c_file), "-o", str(so)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    (work / "pkg" / "schedules.py").unlink()                                   # only the extension is left
+    code = ("import sys; sys.path.insert(0, %r); sys.path.insert(0, %r); import pkg.schedules as c; "
+            "from open_transformers_b200.optim import schedules as s; "
+            "from open_transformers_b200.config import load_config; cfg = load_config('tiny_cpu', []); "
+            "a = c.build_schedule(cfg.schedule, cfg.train, cfg.optim); b = s.build_schedule(cfg.schedule, cfg.train, cfg.optim); "
+            "assert c.__file__.endswith('.so'); assert [a(t, 768) for t in range(0, 768, 64)] == [b(t, 768) for t in range(0, 768, 64)]; print('same')"
+            % (str(work), str(root)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "same" in r.stdout, r.stderr[-2000:]
