@@ -7,8 +7,9 @@ Reported per message size: time (CUDA events, max over ranks), algorithmic bus b
     busbw = (bytes pulled from peers per rank) / time
 against the measured NVLink peer-copy figure (770 GB/s per direction), and the same reduction done with NCCL
 (all_to_all_single of the bucket + local ascending adds = the reference's DeterministicReduceScatter,
-src/pretrain/parallel/deterministic_reduce.py:77-117). For sizes up to --verify-mb the result is compared bit for
-bit with the CPU twin applied to the gathered buckets.
+src/pretrain/parallel/deterministic_reduce.py:77-117). For sizes up to --verify-mb (default: all of them) every rank
+compares its slice of the result, and its squared-norm partials, bit for bit with the CPU twin applied to the same slice of
+all S x R buckets (regenerated from their seeds).
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
       benchmarks/reduce_bench.py --shard 4 --replicate 2 --sizes-mb 1,16,256,1024
@@ -45,7 +46,7 @@ def main():
     ap.add_argument("--replicate", type=int, default=1)
     ap.add_argument("--sizes-mb", default="1,4,16,64,256,1024")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--verify-mb", type=float, default=16)
+    ap.add_argument("--verify-mb", type=float, default=1024, help="check the result bit for bit against the CPU fold up to this bucket size")
     a = ap.parse_args()
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -117,29 +118,29 @@ def main():
                "frac_of_nvlink_peer_copy": remote_bytes / ms / 1e6 / NVLINK_PEER_GBS if world > 1 else None,
                "local_read_GBs": 4.0 * (n / world) * V / ms / 1e6, "nccl_a2a_ms": ms_nccl}
         if mb <= a.verify_mb:
+            # every rank checks ITS slice of the result against the CPU fold of the same slice of all V buckets; the buckets
+            # are seed-generated, so a rank regenerates each of them on its own GPU (one at a time) instead of gathering them
             fused()
             torch.cuda.synchronize()
-            full = [torch.empty(n, dtype=torch.float32, device=dev) for _ in range(world * per)]
-            if world > 1:
-                for slot, b in enumerate(bufs):
-                    parts = [torch.empty(n, dtype=torch.float32, device=dev) for _ in range(world)]
-                    dist.all_gather(parts, b.typed(torch.float32))
-                    for r in range(world):
-                        full[r * per + slot] = parts[r]
-            else:
-                full = [b.typed(torch.float32) for b in bufs]
-            host = [t.cpu() for t in full]
-            ref = torch.zeros(n, dtype=torch.float32)
-            rsos = torch.zeros(n_chunks, dtype=torch.float32)
-            hcs = torch.arange(n_chunks, dtype=torch.int64) * CHUNK
-            hcl = torch.full((n_chunks,), CHUNK, dtype=torch.int32)
-            check(cpu_lib().otb_cpu_grad_reduce(ptr_array([t.data_ptr() for t in host]), I(S), I(R), P(hcs), P(hcl), I(n_chunks), P(ref), P(rsos)), "cpu")
             lo, hi = rank * own * CHUNK, (rank + 1) * own * CHUNK
-            ok = torch.equal(out[lo:hi].cpu(), ref[lo:hi]) and torch.equal(sos.cpu(), rsos[rank * own:(rank + 1) * own])
+            host = []
+            for v in range(V):
+                g = torch.Generator(device=dev).manual_seed(1234 + v)
+                full = torch.randn(n, device=dev, generator=g) * 1e-3
+                host.append(full[lo:hi].cpu())
+                del full
+            m = hi - lo
+            ref = torch.zeros(m, dtype=torch.float32)
+            rsos = torch.zeros(own, dtype=torch.float32)
+            hcs = torch.arange(own, dtype=torch.int64) * CHUNK
+            hcl = torch.full((own,), CHUNK, dtype=torch.int32)
+            check(cpu_lib().otb_cpu_grad_reduce(ptr_array([t.data_ptr() for t in host]), I(S), I(R), P(hcs), P(hcl), I(own), P(ref), P(rsos)), "cpu")
+            ok = torch.equal(out[lo:hi].cpu(), ref) and torch.equal(sos.cpu(), rsos)
             t = torch.tensor([1 if ok else 0], device=dev)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
             row["bit_equal_to_cpu_fold"] = bool(t.item())
+            del host, ref
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)

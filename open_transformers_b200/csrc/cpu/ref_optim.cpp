@@ -121,6 +121,38 @@ int otb_cpu_adamw_push(const float* hyper, const long* chunk_start, const int* c
   }
   return 0;
 }
+// The same update dividing by the running element-wise maximum of the second moment (amsgrad).
+int otb_cpu_adamw_push_amsgrad(const float* hyper, const long* chunk_start, const int* chunk_len, const int* chunk_group,
+                       int nchunks, float* master, float* grad, float* m1, float* m2, float* vmax, const void* const* dsts, int ndst,
+                       int dst_bf16) {
+  const float clip = hyper[0], beta1 = hyper[3], beta2 = hyper[4], omb1 = hyper[5], omb2 = hyper[6], eps = hyper[7],
+              step_size = hyper[8], sqrt_bc2 = hyper[9];
+#pragma omp parallel for schedule(static)
+  for (int c = 0; c < nchunks; ++c) {
+    const long base = chunk_start[c];
+    const float keep = hyper[1 + chunk_group[c]];
+    for (int j = 0; j < chunk_len[c]; ++j) {
+      const long i = base + j;
+      const float g = grad[i] * clip;
+      grad[i] = g;
+      float p = master[i] * keep;
+      const float m = det_fmaf(m1[i], beta1, g * omb1);
+      const float v = det_fmaf(m2[i], beta2, (g * g) * omb2);
+      m1[i] = m;
+      m2[i] = v;
+      const float vd = fmaxf(vmax[i], v);  // running maximum of the second moment (IEEE maxNum on both sides)
+      vmax[i] = vd;
+      const float denom = det_sqrtf(vd) / sqrt_bc2 + eps;
+      p = det_fmaf(-step_size, m / denom, p);
+      master[i] = p;
+      for (int d = 0; d < ndst; ++d) {
+        if (dst_bf16) ((uint16_t*)dsts[d])[i] = det_f2bf(p);
+        else if ((float*)dsts[d] != master) ((float*)dsts[d])[i] = p;
+      }
+    }
+  }
+  return 0;
+}
 int otb_cpu_push_cast(const long* chunk_start, const int* chunk_len, int nchunks, const float* master,
                       const void* const* dsts, int ndst, int dst_bf16) {
 #pragma omp parallel for schedule(static)

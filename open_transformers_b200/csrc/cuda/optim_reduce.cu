@@ -183,11 +183,13 @@ struct AdamArgs {
   float beta1, beta2, one_m_b1, one_m_b2, eps, step_size, sqrt_bc2;
 };
 
-template <bool DST_BF16>
+// AMSGRAD: `vmax` keeps the running element-wise maximum of the second moment and the update divides by it
+// (max_exp_avg_sq of torch.optim.AdamW(amsgrad=True); reference src/pretrain/optim/adamw_repop.py:105-118).
+template <bool DST_BF16, bool AMSGRAD = false>
 __global__ void __launch_bounds__(256)
 adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* __restrict__ chunk_len,
                   const int* __restrict__ chunk_group, float* __restrict__ master, float* __restrict__ grad,
-                  float* __restrict__ m1, float* __restrict__ m2, PushDst dst, int ndst) {
+                  float* __restrict__ m1, float* __restrict__ m2, PushDst dst, int ndst, float* __restrict__ vmax = nullptr) {
   const long base = chunk_start[blockIdx.x];
   const int len = chunk_len[blockIdx.x];
   const float keep = a.lr_wd_keep[chunk_group[blockIdx.x]];
@@ -204,6 +206,11 @@ adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* _
       *reinterpret_cast<float4*>(mv + 4) = *reinterpret_cast<const float4*>(m1 + i0 + 4);
       *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(m2 + i0);
       *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(m2 + i0 + 4);
+      float xv[8];
+      if (AMSGRAD) {
+        *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(vmax + i0);
+        *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(vmax + i0 + 4);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float g = __fmul_rn(gv[e], a.clip);
@@ -213,7 +220,12 @@ adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* _
         const float v = __fmaf_rn(vv[e], a.beta2, __fmul_rn(__fmul_rn(g, g), a.one_m_b2));
         mv[e] = m;
         vv[e] = v;
-        const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.sqrt_bc2), a.eps);
+        float vd = v;
+        if (AMSGRAD) {
+          vd = fmaxf(xv[e], v);
+          xv[e] = vd;
+        }
+        const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(vd), a.sqrt_bc2), a.eps);
         p = __fmaf_rn(-a.step_size, __fdiv_rn(m, denom), p);
         pv[e] = p;
         pn[e] = p;
@@ -226,6 +238,10 @@ adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* _
       *reinterpret_cast<float4*>(m1 + i0 + 4) = *reinterpret_cast<float4*>(mv + 4);
       *reinterpret_cast<float4*>(m2 + i0) = *reinterpret_cast<float4*>(vv);
       *reinterpret_cast<float4*>(m2 + i0 + 4) = *reinterpret_cast<float4*>(vv + 4);
+      if (AMSGRAD) {
+        *reinterpret_cast<float4*>(vmax + i0) = *reinterpret_cast<float4*>(xv);
+        *reinterpret_cast<float4*>(vmax + i0 + 4) = *reinterpret_cast<float4*>(xv + 4);
+      }
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -238,7 +254,12 @@ adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* _
           const float v = __fmaf_rn(m2[i], a.beta2, __fmul_rn(__fmul_rn(g, g), a.one_m_b2));
           m1[i] = m;
           m2[i] = v;
-          const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), a.sqrt_bc2), a.eps);
+          float vd = v;
+          if (AMSGRAD) {
+            vd = fmaxf(vmax[i], v);
+            vmax[i] = vd;
+          }
+          const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(vd), a.sqrt_bc2), a.eps);
           p = __fmaf_rn(-a.step_size, __fdiv_rn(m, denom), p);
           master[i] = p;
           pn[e] = p;
@@ -362,6 +383,22 @@ extern "C" int otb_adamw_push(const float* hyper, const long* chunk_start, const
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dst_bf16) adamw_push_kernel<true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst);
   else adamw_push_kernel<false><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst);
+  return (int)cudaGetLastError();
+}
+// The same update with the running maximum of the second moment (`vmax`, fp32, same layout as m2).
+extern "C" int otb_adamw_push_amsgrad(const float* hyper, const long* chunk_start, const int* chunk_len, const int* chunk_group,
+                                      int nchunks, float* master, float* grad, float* m1, float* m2, float* vmax,
+                                      const void* const* dsts, int ndst, int dst_bf16, void* stream) {
+  if (ndst > MAX_DST || !vmax) return -2;
+  if (nchunks <= 0) return 0;
+  AdamArgs a;
+  a.clip = hyper[0]; a.lr_wd_keep[0] = hyper[1]; a.lr_wd_keep[1] = hyper[2]; a.beta1 = hyper[3]; a.beta2 = hyper[4];
+  a.one_m_b1 = hyper[5]; a.one_m_b2 = hyper[6]; a.eps = hyper[7]; a.step_size = hyper[8]; a.sqrt_bc2 = hyper[9];
+  PushDst pd;
+  for (int i = 0; i < ndst; ++i) pd.p[i] = const_cast<void*>(dsts[i]);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dst_bf16) adamw_push_kernel<true, true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, vmax);
+  else adamw_push_kernel<false, true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, vmax);
   return (int)cudaGetLastError();
 }
 extern "C" int otb_push_cast(const long* chunk_start, const int* chunk_len, int nchunks, const float* master,

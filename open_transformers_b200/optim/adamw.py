@@ -21,8 +21,11 @@ def _ptrs(ps):
 
 
 class DeterministicAdamW(torch.optim.Optimizer):
-    def __init__(self, params, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1):
-        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+    """``amsgrad=True`` keeps ``max_exp_avg_sq`` per parameter and divides by its square root (the kernel's optional
+    running maximum of the second moment; reference src/pretrain/optim/adamw_repop.py:62-118)."""
+
+    def __init__(self, params, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=False):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=bool(amsgrad)))
 
     @torch.no_grad()
     def step(self, closure=None, clip: float = 1.0):
@@ -37,6 +40,8 @@ class DeterministicAdamW(torch.optim.Optimizer):
                     st["step"] = torch.zeros((), dtype=torch.int64)
                     st["exp_avg"] = torch.zeros_like(p)
                     st["exp_avg_sq"] = torch.zeros_like(p)
+                if group.get("amsgrad") and "max_exp_avg_sq" not in st:
+                    st["max_exp_avg_sq"] = torch.zeros_like(p)
                 st["step"] += 1
                 hyper = (ctypes.c_float * 10)()
                 cpu_lib().otb_cpu_adamw_hyper(ctypes.c_double(group["lr"]), ctypes.c_double(group["betas"][0]), ctypes.c_double(group["betas"][1]),
@@ -48,11 +53,20 @@ class DeterministicAdamW(torch.optim.Optimizer):
                 cs, cl = torch.from_numpy(starts).to(p.device), torch.from_numpy(lens).to(p.device)
                 cg = torch.zeros(len(starts), dtype=torch.int32, device=p.device)
                 g = p.grad.contiguous()
-                args = (hyper, P(cs), P(cl), P(cg), I(len(starts)), P(p), P(g), P(st["exp_avg"]), P(st["exp_avg_sq"]), _ptrs([p.data_ptr()]), I(1), I(0))
-                if p.is_cuda:
-                    check(cuda_lib().otb_adamw_push(*args, stream_ptr()), "adamw")
+                head = (hyper, P(cs), P(cl), P(cg), I(len(starts)), P(p), P(g), P(st["exp_avg"]), P(st["exp_avg_sq"]))
+                tail = (_ptrs([p.data_ptr()]), I(1), I(0))
+                if group.get("amsgrad"):
+                    args = head + (P(st["max_exp_avg_sq"]),) + tail
+                    if p.is_cuda:
+                        check(cuda_lib().otb_adamw_push_amsgrad(*args, stream_ptr()), "adamw_amsgrad")
+                    else:
+                        check(cpu_lib().otb_cpu_adamw_push_amsgrad(*args), "adamw_amsgrad")
                 else:
-                    check(cpu_lib().otb_cpu_adamw_push(*args), "adamw")
+                    args = head + tail
+                    if p.is_cuda:
+                        check(cuda_lib().otb_adamw_push(*args, stream_ptr()), "adamw")
+                    else:
+                        check(cpu_lib().otb_cpu_adamw_push(*args), "adamw")
         return loss
 
 

@@ -299,3 +299,22 @@ def test_gpu_hadamard_int8_product_bitwise_vs_cpu():
     cpu, gpu = _both(lambda a_, b_: K.ste_matmul_hadamard(a_, b_), a, b)
     assert torch.equal(cpu, gpu.cpu()), "%d elements differ" % int((cpu != gpu.cpu()).sum())
     assert K.kernel_status("cuda") == 0
+
+
+def test_adamw_amsgrad_gpu_equals_cpu_bitwise():
+    """the AdamW kernel with the running maximum of the second moment: three steps on the GPU and on the CPU twin, bit for bit"""
+    from open_transformers_b200.optim.adamw import DeterministicAdamW
+
+    g = torch.Generator().manual_seed(9)
+    w0 = torch.randn(5, 8192 + 40, generator=g)
+    grads = [torch.randn(5, 8192 + 40, generator=g) * s for s in (1.0, 0.1, 3.0)]
+    out = {}
+    for dev in ("cpu", DEV):
+        p = torch.nn.Parameter(w0.clone().to(dev))
+        opt = DeterministicAdamW([p], lr=3e-3, weight_decay=0.1, amsgrad=True)
+        for gr in grads:
+            p.grad = gr.clone().to(dev)
+            opt.step()
+        out[dev] = (p.detach().cpu(), opt.state[p]["exp_avg_sq"].cpu(), opt.state[p]["max_exp_avg_sq"].cpu())
+    for a, b, what in zip(out["cpu"], out[DEV], ("parameter", "second moment", "its running maximum")):
+        _eq(a, b, what)

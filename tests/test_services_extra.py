@@ -349,3 +349,26 @@ def test_compiled_distribution_hook_translates_a_module_and_keeps_its_behaviour(
             % (str(work), str(root)))
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "same" in r.stdout, r.stderr[-2000:]
+
+
+def test_amsgrad_variant_of_the_adamw_kernel_follows_torch():
+    """the kernel's optional running maximum of the second moment against torch.optim.AdamW(amsgrad=True): a gradient that
+    shrinks after the first steps keeps dividing by the early, larger second moment"""
+    from open_transformers_b200.optim.adamw import DeterministicAdamW
+
+    g = torch.Generator().manual_seed(5)
+    w0 = torch.randn(3, 10_000, generator=g)
+    grads = [torch.randn(3, 10_000, generator=g) * s for s in (1.0, 2.0, 0.1, 0.05, 0.5)]
+    ours, ref = torch.nn.Parameter(w0.clone()), torch.nn.Parameter(w0.clone())
+    a = DeterministicAdamW([ours], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=True)
+    b = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=True)
+    plain = torch.nn.Parameter(w0.clone())
+    c = DeterministicAdamW([plain], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for gr in grads:
+        for p, o in ((ours, a), (ref, b), (plain, c)):
+            p.grad = gr.clone()
+            o.step()
+    assert torch.allclose(ours, ref, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(a.state[ours]["max_exp_avg_sq"], b.state[ref]["max_exp_avg_sq"], rtol=1e-6, atol=1e-12)
+    assert bool((a.state[ours]["max_exp_avg_sq"] >= a.state[ours]["exp_avg_sq"]).all()) and not torch.equal(ours, plain)
+    assert "max_exp_avg_sq" not in c.state[plain]
