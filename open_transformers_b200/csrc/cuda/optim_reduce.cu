@@ -55,7 +55,7 @@ __device__ __forceinline__ float block_tree_sum_256(float v, float* sh) {
 // chunk table: chunk c covers flat elements [chunk_start[c], chunk_start[c] + chunk_len[c]) (len <= 8192,
 // start 16-byte aligned). One CTA per chunk.
 __global__ void __launch_bounds__(256)
-grad_reduce_kernel(ReduceSrc src, int S, int R, float inv_s, float inv_r, const long* __restrict__ chunk_start,
+grad_reduce_kernel(ReduceSrc src, int S, int R, int TPN, float inv_s, float inv_r, const long* __restrict__ chunk_start,
                    const int* __restrict__ chunk_len, const int* __restrict__ chunk_ids, float* __restrict__ out,
                    float* __restrict__ chunk_sos) {
   __shared__ float sh[32];
@@ -71,7 +71,7 @@ grad_reduce_kernel(ReduceSrc src, int S, int R, float inv_s, float inv_r, const 
     for (int r = 0; r < R; ++r) {
       float in[8];
       for (int s = 0; s < S; ++s) {
-        const float* p = src.p[r * S + s] + base + j;
+        const float* p = src.p[(r * S + s) * TPN] + base + j;
         float v[8];
         if (vec) {
           const float4 a = *reinterpret_cast<const float4*>(p);
@@ -80,6 +80,23 @@ grad_reduce_kernel(ReduceSrc src, int S, int R, float inv_s, float inv_r, const 
         } else {
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[e] = (j + e < len) ? p[e] : 0.0f;
+        }
+        // Tensor-parallel group of TPN processes: each wrote only its own slices of this virtual rank's gradient and
+        // left +0.0 elsewhere, so at most one of the TPN buffers holds a non-zero bit pattern per element and the
+        // integer sum of the patterns is that pattern, exactly (no floating-point addition, no order).
+        for (int t = 1; t < TPN; ++t) {
+          const float* pt = src.p[(r * S + s) * TPN + t] + base + j;
+          if (vec) {
+            const uint4 a = *reinterpret_cast<const uint4*>(pt);
+            const uint4 b = *reinterpret_cast<const uint4*>(pt + 4);
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(__float_as_uint(v[e]) + w[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (j + e < len) v[e] = __uint_as_float(__float_as_uint(v[e]) + __float_as_uint(pt[e]));
+          }
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) in[e] = (s == 0) ? v[e] : __fadd_rn(in[e], v[e]);
@@ -321,7 +338,7 @@ extern "C" int otb_grad_reduce(const void* const* srcs, int S, int R, const long
   ReduceSrc rs;
   for (int i = 0; i < S * R; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
   const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
-  grad_reduce_kernel<<<nchunks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, inv_s, inv_r, chunk_start,
+  grad_reduce_kernel<<<nchunks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, 1, inv_s, inv_r, chunk_start,
                                                                                   chunk_len, nullptr, out, chunk_sos);
   return (int)cudaGetLastError();
 }
@@ -334,8 +351,22 @@ extern "C" int otb_grad_reduce_ids(const void* const* srcs, int S, int R, const 
   ReduceSrc rs;
   for (int i = 0; i < S * R; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
   const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
-  grad_reduce_kernel<<<nids, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, inv_s, inv_r, chunk_start, chunk_len,
+  grad_reduce_kernel<<<nids, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, 1, inv_s, inv_r, chunk_start, chunk_len,
                                                                                chunk_ids, out, chunk_sos);
+  return (int)cudaGetLastError();
+}
+// Tensor-parallel groups: srcs holds S*R*tp pointers, [virtual rank][tensor-parallel rank]; the tp partial buffers of a
+// virtual rank (disjoint slices, zeros elsewhere) are assembled by integer addition of their bit patterns, then the
+// same shard fold and replica tree run. `chunk_ids` may be null (the first `n` chunks of the table).
+extern "C" int otb_grad_reduce_tp(const void* const* srcs, int S, int R, int tp, const long* chunk_start, const int* chunk_len,
+                                  const int* chunk_ids, int n, float* out, float* chunk_sos, void* stream) {
+  if (tp < 1 || S * R * tp > MAX_SRC || R > 16 || S < 1 || R < 1) return -2;
+  if (n <= 0) return 0;
+  ReduceSrc rs;
+  for (int i = 0; i < S * R * tp; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
+  const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
+  grad_reduce_kernel<<<n, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, tp, inv_s, inv_r, chunk_start, chunk_len, chunk_ids,
+                                                                            out, chunk_sos);
   return (int)cudaGetLastError();
 }
 // Writes `val` into word `idx` of every destination flag array (this GPU's and the peers'), after everything queued

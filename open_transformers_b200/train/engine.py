@@ -137,8 +137,10 @@ class TrainEngine:
         self.layout = FlatLayout.build([(n, tuple(p.shape)) for n, p in named], self.dp_shard, member)
         lay = self.layout
         n = lay.total
-        # with a tensor-parallel group every process ends up with the whole gradient of its virtual ranks, so each
-        # reduces and updates everything itself (no peer-sharded ownership)
+        # Tensor-parallel groups on GPUs of one machine keep the sharded ownership too: every process of the run owns a run of
+        # segments, and the reduction kernel assembles each virtual rank's gradient from the disjoint slices its tensor-
+        # parallel ranks wrote (integer sum of bit patterns) while it pulls them. Elsewhere (CPU ranks, several machines) a
+        # tensor-parallel run assembles by an integer all-reduce and every process reduces and updates everything itself.
         # How the gradient buffers of the other processes are reached (OTB_GRAD_TRANSPORT = auto | peer | collective | gather):
         #   peer       - sharded ownership, plain loads from the other GPUs' buffers (CUDA IPC over NVLink; one machine);
         #   collective - sharded ownership, every process SENDS each owner its segments (point-to-point messages of the
@@ -150,7 +152,7 @@ class TrainEngine:
         transport = os.environ.get("OTB_GRAD_TRANSPORT", "auto")
         if transport not in ("auto", "peer", "collective", "gather"):
             raise ValueError("OTB_GRAD_TRANSPORT=%s (auto, peer, collective or gather)" % transport)
-        can_shard = world > 1 and not self.nccl_mode and self.tp == 1
+        can_shard = world > 1 and not self.nccl_mode and (self.tp == 1 or (self.is_cuda and transport in ("auto", "peer")))
         if transport == "auto":
             transport = "gather"
             if can_shard and self.is_cuda:
@@ -159,7 +161,7 @@ class TrainEngine:
                 hosts: list = [None] * world
                 dist.all_gather_object(hosts, socket.gethostname(), group=group)
                 transport = "peer" if len(set(hosts)) == 1 else "collective"
-        if not can_shard:
+        if not can_shard or (self.tp > 1 and transport != "peer"):
             transport = "gather"
         if transport == "peer" and not self.is_cuda:
             raise ValueError("OTB_GRAD_TRANSPORT=peer needs GPUs (peer loads over NVLink)")
@@ -775,7 +777,7 @@ class TrainEngine:
             if self.peer:
                 self._share_chunk_sos()
             return self._finish_norm()
-        if self.tp > 1:
+        if self.tp > 1 and not self.peer:
             # assemble each virtual rank's gradient from the slices its tensor-parallel ranks wrote: at most one rank holds
             # a non-zero bit pattern per element, so the integer sum of the bit patterns is that pattern, exactly
             for g in self.grads:
@@ -817,13 +819,18 @@ class TrainEngine:
                 self._keep = parts
                 srcs, S = [p.data_ptr() for p in parts], 1
                 self._partials = {}
+            tpn = self.tp if self.peer else 1
             for v in range(self.V if not self.fold else 0):
                 r, slot = v // per, v % per
-                srcs.append(self.buf_grads[slot].ptrs[r] if self.peer else self.grads[slot].data_ptr())
+                for t in range(tpn):  # the tensor-parallel ranks of group r hold disjoint slices of virtual rank v's gradient
+                    srcs.append(self.buf_grads[slot].ptrs[r * tpn + t] if self.peer else self.grads[slot].data_ptr())
             lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
             cs, cl = self.chunk_start[lo:], self.chunk_len[lo:]
             sos = self.chunk_sos[lo:]
-            if self.is_cuda:
+            if self.is_cuda and tpn > 1:
+                check(self.lib.otb_grad_reduce_tp(_ptr_array(srcs), I(S), I(R), I(tpn), P(cs), P(cl), P(None), I(cnt), P(self.grad_red), P(sos),
+                                                  stream_ptr()), "grad_reduce_tp")
+            elif self.is_cuda:
                 check(self.lib.otb_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos), stream_ptr()),
                       "grad_reduce")
             else:
