@@ -39,8 +39,10 @@ def test_hashes_do_not_depend_on_the_gpu_count(tmp_path, shard):
             break
         many = _run(n, tmp_path / ("g%d.json" % n), shard)
         assert many["status"] == 0
-        assert many["overlapped_steps"] == 3  # every step's reduction ran bucket by bucket under the last backward pass
         assert many["hashes"] == one["hashes"], (n, many, one)
+        # the reduction ran bucket by bucket under the last backward pass: in every step, or in every step after the first
+        # where a process hosts one virtual rank (its first backward pass tells which parameters never get a gradient)
+        assert many["overlapped_steps"] in (2, 3)
 
 
 def test_message_transport_between_two_gpus_reproduces_the_single_gpu_hashes(tmp_path):
