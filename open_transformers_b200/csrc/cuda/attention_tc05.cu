@@ -41,6 +41,10 @@ using namespace tc05;
 
 namespace {
 
+// Launch-order permutation for the race tests: block x works as block (x + g_attn_rotation) mod gridDim.x. A block owns
+// its query tile (or key block) and sums in a fixed order, so any rotation must give the same bytes (0 in production).
+__device__ int g_attn_rotation = 0;
+
 constexpr int BQ = 128;   // query rows per tile
 constexpr int BKV = 128;  // keys per block
 constexpr int NSPLIT = 4;                 // threads per row
@@ -168,7 +172,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (T + BQ - 1) / BQ;
-  const int qt = nq - 1 - blockIdx.x;  // heavy tiles first
+  const int qt = nq - 1 - (int)((blockIdx.x + g_attn_rotation) % gridDim.x);  // heavy tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int g = h / (H / Hkv);
   const int q0 = qt * BQ;
@@ -419,7 +423,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (T + BQ - 1) / BQ;
-  const int pr = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy pairs first
+  const int pr = (int)gridDim.x - 1 - (int)((blockIdx.x + g_attn_rotation) % gridDim.x);  // heavy pairs first
   const int h = blockIdx.y, b = blockIdx.z;
   const int g = h / (H / Hkv);
   const int tile0 = 2 * pr;
@@ -730,7 +734,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (T + BQ - 1) / BQ;
-  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int kb = (int)((blockIdx.x + g_attn_rotation) % gridDim.x), g = blockIdx.y, b = blockIdx.z;
   const int G = H / Hkv;
   const int k0 = kb * BKV;
   int qlast = nq - 1;
@@ -937,7 +941,7 @@ attn_bwd_q2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (T + BQ - 1) / BQ;
-  const int pr = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int pr = (int)gridDim.x - 1 - (int)((blockIdx.x + g_attn_rotation) % gridDim.x);
   const int h = blockIdx.y, b = blockIdx.z;
   const int g = h / (H / Hkv);
   const int tile0 = 2 * pr;
@@ -1165,7 +1169,7 @@ attn_bwd_kv2_kernel(const __grid_constant__ CUtensorMap tmQK, const __grid_const
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int kb = (int)((blockIdx.x + g_attn_rotation) % gridDim.x), g = blockIdx.y, b = blockIdx.z;
   const int G = H / Hkv;
   const int k0 = kb * BKV;
   const int nu = T / HK;  // query steps in the sequence
@@ -1419,6 +1423,10 @@ int set_smem(K kern, int bytes) {
 
 // qk: [B*T, ldqk] bf16 holding H query heads then Hkv key heads (width D each); qkv: [B*T, ldqkv] bf16 whose
 // value heads start at column (H + Hkv) * D; O: [B*T, ldo]; lse: [B, H, T] fp32. D in {64, 128}.
+extern "C" int otb_set_attn_rotation(int rotation) {
+  if (rotation < 0) return -2;
+  return (int)cudaMemcpyToSymbol(g_attn_rotation, &rotation, sizeof(rotation));
+}
 extern "C" int otb_attn_fwd(const void* qk, long ldqk, const void* qkv, long ldqkv, void* O, long ldo, float* lse, int B,
                             int T, int H, int Hkv, int D, int window, float scale, uint32_t* status, void* stream) {
   if ((D != 64 && D != 128) || H % Hkv || (ldqk & 7) || (ldqkv & 7) || (ldo & 7)) return -2;

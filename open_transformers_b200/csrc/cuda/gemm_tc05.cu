@@ -76,6 +76,11 @@ struct TpArgs {
   int rank, P, tiles_per_shard, gemm_ctas;
 };
 
+// Launch-order permutation for the race tests: CTA b works as CTA (b + g_cta_rotation) mod (number of GEMM CTAs). Every
+// output tile is owned by one CTA and summed in ascending k whatever CTA that is, so any rotation must give the same bytes
+// (otb_set_cta_rotation; 0 in production).
+__device__ int g_cta_rotation = 0;
+
 // How long a kernel of this file waits for a peer's flag before it gives up, sets its status word and returns
 // (nanoseconds of %globaltimer; otb_set_peer_wait_ns changes it for the current device).
 __device__ unsigned long long g_peer_wait_ns = 2000000000ull;
@@ -157,6 +162,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
   constexpr int BK = I8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per k-block
+  const int cta = ((int)blockIdx.x + g_cta_rotation) % nctas;  // which persistent worker this CTA is
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -221,7 +227,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += nctas) {
+      for (int t = cta; t < num_tiles && ok; t += nctas) {
         int tm, tn;
         tile_coord(t, tm, tn);
         if constexpr (TP == 1) {
@@ -259,7 +265,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = I8 ? make_idesc(BM, BN, 0, 0, 2, 1) : make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
+      for (int t = cta; t < num_tiles && ok; t += nctas, ++lt) {
         const uint32_t buf = lt & 1;
         const uint32_t bph = (lt >> 1) & 1;
         if (chain_in) {  // the loading warps waited for the buffer to be free and filled it with the incoming partial sum
@@ -295,7 +301,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int q = warp & 3;
         uint32_t lt = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
+        for (int t = cta; t < num_tiles && ok; t += nctas, ++lt) {
           int tm, tn;
           tile_coord(t, tm, tn);
           const uint32_t buf = lt & 1;
@@ -337,7 +343,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
     uint32_t lt = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += nctas, ++lt) {
+    for (int t = cta; t < num_tiles && ok; t += nctas, ++lt) {
       int tm, tn;
       tile_coord(t, tm, tn);
       const CUtensorMap* tmc = &tmC;
@@ -717,6 +723,10 @@ inline int tp_chain_bn(int N) { return N >= 256 ? 256 : 128; }
 // Budget of every bounded peer wait of the tensor-parallel kernels and of otb_peer_barrier on the current device
 // (default 2 s). A wait that runs out makes its kernel write its status word (1 all-gather->GEMM, 2 chained GEMM /
 // otb_tp_finish, 3 otb_peer_barrier) and return normally.
+extern "C" int otb_set_cta_rotation(int rotation) {
+  if (rotation < 0) return -2;
+  return (int)cudaMemcpyToSymbol(g_cta_rotation, &rotation, sizeof(rotation));
+}
 extern "C" int otb_set_peer_wait_ns(unsigned long long ns) {
   if (ns == 0) return -2;
   return (int)cudaMemcpyToSymbol(g_peer_wait_ns, &ns, sizeof(ns));

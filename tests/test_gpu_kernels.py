@@ -318,3 +318,44 @@ def test_adamw_amsgrad_gpu_equals_cpu_bitwise():
         out[dev] = (p.detach().cpu(), opt.state[p]["exp_avg_sq"].cpu(), opt.state[p]["max_exp_avg_sq"].cpu())
     for a, b, what in zip(out["cpu"], out[DEV], ("parameter", "second moment", "its running maximum")):
         _eq(a, b, what)
+
+
+def test_gemm_and_attention_bytes_do_not_depend_on_the_launch_order():
+    """Permuted launch order: with the test-only rotation each CTA takes over another CTA's share of the tiles (GEMM: the
+    persistent workers; attention: the query tiles / key blocks of the grid's x axis). Every output element is owned by one
+    CTA and summed in a fixed order, so the bytes must not move; a difference would be a race or an order that follows the
+    schedule."""
+    from open_transformers_b200.ops.native import cuda_lib
+
+    lib = cuda_lib()
+    g = torch.Generator().manual_seed(21)
+    M, N, K_ = 1500, 1100, 712                      # 12 x 5..9 tiles: several tiles per persistent worker and a ragged edge
+    A = torch.randn(M, K_, generator=g).bfloat16().to(DEV)
+    Bm = torch.randn(N, K_, generator=g).bfloat16().to(DEV)
+    At = A.t().contiguous()
+    B_, T, H, Hkv, D = 2, 640, 4, 2, 128
+    qk = torch.randn(B_ * T, (H + Hkv) * D, generator=g).bfloat16().to(DEV)
+    qkv = torch.randn(B_ * T, (H + 2 * Hkv) * D, generator=g).bfloat16().to(DEV)
+    dO = (0.5 * torch.randn(B_ * T, H * D, generator=g)).bfloat16().to(DEV)
+
+    def everything():
+        acc = torch.full((M, N), 0.5, device=DEV)
+        K.gemm(A, Bm, out=acc, epi=K.EPI_ACC_F32)
+        outs = [K.gemm(A, Bm), K.gemm(A, Bm, epi=K.EPI_STORE_F32), K.gemm(At, Bm, a_mn=True), acc]
+        for window in (0, 192):
+            O, lse = K.attn_fwd(qk, qkv, B_, T, H, Hkv, D, window)
+            dqk, dqkv = torch.zeros_like(qk), torch.zeros_like(qkv)
+            K.attn_bwd(qk, qkv, O, dO, lse, dqk, dqkv, B_, T, H, Hkv, D, window)
+            outs += [O, lse, dqk, dqkv]
+        torch.cuda.synchronize()
+        return [o.clone() for o in outs]
+
+    base = everything()
+    try:
+        for rot in (1, 5, 37):
+            assert lib.otb_set_cta_rotation(rot) == 0 and lib.otb_set_attn_rotation(rot) == 0
+            for i, (a, b) in enumerate(zip(base, everything())):
+                assert torch.equal(a, b), "output %d moved under rotation %d" % (i, rot)
+    finally:
+        assert lib.otb_set_cta_rotation(0) == 0 and lib.otb_set_attn_rotation(0) == 0
+    assert K.kernel_status(DEV) == 0
