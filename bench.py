@@ -12,9 +12,10 @@ redistribution and the chained state hash (tree digests on the device). Random-i
 
 Two timed regions of K steps each, both on the device with CUDA events, max over ranks:
   * `value`: inputs already resident on the device;
-  * `e2e`:   every micro-batch is copied from pinned host memory inside the timed region and the
-             step's loss is read back to the host every step, through the public
-             `TrainEngine` API.
+  * `e2e`:   the calls `train()` makes: micro-batches come from the canonical data stream over synthetic shards
+             (`build_global_loader`), are collated into pinned host memory, chained into the per-virtual-rank batch
+             digests and copied to the device inside the timed region; the step's loss is read back to the host and
+             the batch digest goes into the state hash every step.
 `--impl reference` times the unmodified reference training loop (`baseline/_ref`) over a stock-torch stand-in of
 its closed kernel library, same config, steps and warm-up (`baseline/reference_arm.py`).
 """
@@ -137,22 +138,53 @@ def main() -> int:
         seq = torch.randint(0, vocab, (mb, T + 1), generator=g, dtype=torch.int64)
         return seq[:, :-1].contiguous().pin_memory(), seq[:, 1:].contiguous().pin_memory()
 
-    host = {(s, v, k): host_batch(s, v, k) for s in range(total_steps) for v in hosted for k in range(accum)}
+    host = {(s, v, k): host_batch(s, v, k) for s in range(args.steps + args.warmup) for v in hosted for k in range(accum)}
     h2d_bytes = sum(a.numel() * 8 + b.numel() * 8 for (s, v, k), (a, b) in host.items() if s == 0)
-    state = {"prev": None, "consumed": 0, "step": 0, "loss": None}
+    state = {"prev": None, "consumed": 0, "step": 0, "loss": None, "pending": None, "pending_bd": None}
+
+    # the end-to-end region reads the canonical stream: seed-generated shards, written once by rank 0
+    import tempfile
+
+    from open_transformers_b200.data.loader import build_global_loader, collate
+    from open_transformers_b200.data.synthetic import ensure_synthetic_sources
+    from open_transformers_b200.train import state_hash as SH
+
+    data_root = os.path.join(tempfile.gettempdir(), "otb_bench_data_%s_%d" % (os.environ.get("MASTER_PORT", "single"), os.getppid() if world > 1 else os.getpid()))
+    if rank == 0:
+        ensure_synthetic_sources(cfg, data_root, (args.steps + args.warmup + 2) * tokens_per_step)
+    if world > 1:
+        dist.barrier()
+    stream = iter(build_global_loader(cfg, hosted, V, data_root=data_root))
+    hashers = {v: SH.RunningBatchHasher() for v in hosted}
+
+    def batch_digest():
+        chains = {v: h.local_digest() for v, h in hashers.items()}
+        if world > 1:
+            objs = [None] * world
+            dist.all_gather_object(objs, chains)
+            chains = {k: d for part in objs for k, d in part.items()}
+        return SH.combine_batch_digests([chains[v] for v in range(V)])
 
     def one_step(step: int, resident):
         eng.zero_grads()
         last_ce = None
-        for vi, v in enumerate(hosted):
-            for k in range(accum):
-                if resident is not None:
+        bd = None
+        if resident is not None:
+            for vi, v in enumerate(hosted):
+                for k in range(accum):
                     ids, labels = resident[(step, v, k)]
-                else:
-                    a, b = host[(step, v, k)]
-                    ids, labels = a.to(device, non_blocking=True), b.to(device, non_blocking=True)
-                ce, z = eng.forward_backward(vi, ids, labels, accum, last=(vi == len(hosted) - 1 and k == accum - 1))
+                    ce, z = eng.forward_backward(vi, ids, labels, accum, last=(vi == len(hosted) - 1 and k == accum - 1))
+                    last_ce = ce
+        else:
+            plan, batches = next(stream)
+            batches = list(batches)
+            for j, (v, k, windows) in enumerate(batches):
+                batch = collate(windows, pin=True)
+                hashers[v].update(batch)
+                ids, labels = batch["input_ids"].to(device, non_blocking=True), batch["labels"].to(device, non_blocking=True)
+                ce, z = eng.forward_backward(hosted.index(v), ids, labels, accum, last=j == len(batches) - 1)
                 last_ce = ce
+            bd = batch_digest()
         if not args.no_hash:
             flush_hash()  # the previous step's digests ran under this step's forward/backward; fold them in while it drains
         norm = eng.reduce_gradients()
@@ -162,11 +194,12 @@ def main() -> int:
         if not args.no_hash:
             # the digests of this step's state run on a side stream under the next step's forward/backward
             state["pending"] = eng.begin_state_hash(include_grads=cfg.train.state_hash.include_grads)
+            state["pending_bd"] = bd
         return last_ce, norm
 
     def flush_hash():
         if state.get("pending") is not None:
-            state["prev"] = eng.finish_state_hash(state["pending"], state["prev"], None)
+            state["prev"] = eng.finish_state_hash(state["pending"], state["prev"], state["pending_bd"])
             state["pending"] = None
 
     def timed(first_step: int, n: int, resident_mode: bool):
@@ -204,12 +237,15 @@ def main() -> int:
     ms_dev, _ = timed(W, Kst, True)
     launches = native.launch_count - launches0
     clocks = sampler.stop()
-    timed(W + Kst, W, False)                # warm-up of the end-to-end path
-    ms_e2e, loss = timed(2 * W + Kst, Kst, False)
+    timed(0, W, False)                      # warm-up of the end-to-end path (the stream supplies its own batches)
+    ms_e2e, loss = timed(0, Kst, False)
     status = kernel_status(device)
     if world > 1:
         dist.barrier()
     if rank == 0:
+        import shutil
+
+        shutil.rmtree(data_root, ignore_errors=True)
         tps = tokens_per_step * Kst / (ms_dev / 1e3)
         tps_e2e = tokens_per_step * Kst / (ms_e2e / 1e3)
         from open_transformers_b200.obs.metrics import hardware_flops_per_token
@@ -225,6 +261,7 @@ def main() -> int:
                        "global_batch_tokens": tokens_per_step, "parallelism": "virtual dp8 (shard 8) on %d GPU(s)%s" % (world, ", tensor-parallel groups of %d" % args.tp if args.tp > 1 else ""),
                        "l2": "inputs larger than L2 (3.2 GB of bf16 weights + 6.4 GB fp32 gradients per micro-batch)",
                        "state_hash": "none" if args.no_hash else "every step, tree digests on device",
+                       "e2e_path": "GlobalStream loader over synthetic shards -> pinned collate -> batch digests -> H2D, loss D2H per step",
                        "overrides": args.override},
             "clocks": clocks,
             "e2e": {"value": tps_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / Kst,

@@ -36,7 +36,10 @@ def main(argv: list[str] | None = None) -> int:
 
     res = train(cfg, a.resume_from, device=a.device, data_root=a.data_root, max_steps=a.max_steps)
     shutdown_distributed()  # after a clean run only: a barrier, then the process group is destroyed (a failed rank's peers may be gone)
-    print(json.dumps({k: v for k, v in res.items() if k != "losses"}, default=str))
+    import os
+
+    if int(os.environ.get("RANK", "0")) == 0:  # one line per run: lines of several ranks would run together on a shared pipe
+        print(json.dumps({k: v for k, v in res.items() if k != "losses"}, default=str), flush=True)
     return 0
 
 

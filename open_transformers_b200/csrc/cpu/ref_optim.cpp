@@ -77,6 +77,31 @@ int otb_cpu_grad_reduce_ids(const void* const* srcs, int S, int R, const long* c
   }
   return 0;
 }
+// Sharded state: the reduced gradient goes to `out + chunk_out_start[c]` (a packed buffer of the owned segments).
+int otb_cpu_grad_reduce_ex(const void* const* srcs, int S, int R, const long* chunk_start, const int* chunk_len,
+                           const int* chunk_ids, int nids, const long* chunk_out_start, float* out, float* chunk_sos_out) {
+  const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
+#pragma omp parallel for schedule(static)
+  for (int k = 0; k < nids; ++k) {
+    const int c = chunk_ids ? chunk_ids[k] : k;
+    const long base = chunk_start[c];
+    const int len = chunk_len[c];
+    const long obase = chunk_out_start ? chunk_out_start[c] : base;
+    float rep[16];
+    for (int i = 0; i < len; ++i) {
+      for (int r = 0; r < R; ++r) {
+        float in = ((const float*)srcs[r * S])[base + i];
+        for (int s = 1; s < S; ++s) in = in + ((const float*)srcs[r * S + s])[base + i];
+        rep[r] = in * inv_s;
+      }
+      for (int st = 1; st < R; st *= 2)
+        for (int q = 0; q + st < R; q += 2 * st) rep[q] = rep[q] + rep[q + st];
+      out[obase + i] = rep[0] * inv_r;
+    }
+    chunk_sos_out[c] = chunk_sos(out + obase, len);
+  }
+  return 0;
+}
 int otb_cpu_chunk_sos(const float* x, const long* chunk_start, const int* chunk_len, int nchunks, float* chunk_sos_out) {
 #pragma omp parallel for schedule(static)
   for (int c = 0; c < nchunks; ++c) chunk_sos_out[c] = chunk_sos(x + chunk_start[c], chunk_len[c]);
@@ -110,6 +135,37 @@ int otb_cpu_adamw_push(const float* hyper, const long* chunk_start, const int* c
       const float v = det_fmaf(m2[i], beta2, (g * g) * omb2);
       m1[i] = m;
       m2[i] = v;
+      const float denom = det_sqrtf(v) / sqrt_bc2 + eps;
+      p = det_fmaf(-step_size, m / denom, p);
+      master[i] = p;
+      for (int d = 0; d < ndst; ++d) {
+        if (dst_bf16) ((uint16_t*)dsts[d])[i] = det_f2bf(p);
+        else if ((float*)dsts[d] != master) ((float*)dsts[d])[i] = p;
+      }
+    }
+  }
+  return 0;
+}
+// Sharded state: gradient and moments are addressed by `chunk_state_start`, master weights and destinations by `chunk_start`.
+int otb_cpu_adamw_push_ex(const float* hyper, const long* chunk_start, const long* chunk_state_start, const int* chunk_len, const int* chunk_group,
+                       int nchunks, float* master, float* grad, float* m1, float* m2, const void* const* dsts, int ndst,
+                       int dst_bf16) {
+  const float clip = hyper[0], beta1 = hyper[3], beta2 = hyper[4], omb1 = hyper[5], omb2 = hyper[6], eps = hyper[7],
+              step_size = hyper[8], sqrt_bc2 = hyper[9];
+#pragma omp parallel for schedule(static)
+  for (int c = 0; c < nchunks; ++c) {
+    const long base = chunk_start[c];
+    const float keep = hyper[1 + chunk_group[c]];
+    for (int j = 0; j < chunk_len[c]; ++j) {
+      const long i = base + j;
+      const long si = (chunk_state_start ? chunk_state_start[c] : base) + j;  // gradient and moments: packed buffers
+      const float g = grad[si] * clip;
+      grad[si] = g;
+      float p = master[i] * keep;
+      const float m = det_fmaf(m1[si], beta1, g * omb1);
+      const float v = det_fmaf(m2[si], beta2, (g * g) * omb2);
+      m1[si] = m;
+      m2[si] = v;
       const float denom = det_sqrtf(v) / sqrt_bc2 + eps;
       p = det_fmaf(-step_size, m / denom, p);
       master[i] = p;

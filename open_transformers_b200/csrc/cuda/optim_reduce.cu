@@ -57,7 +57,7 @@ __device__ __forceinline__ float block_tree_sum_256(float v, float* sh) {
 __global__ void __launch_bounds__(256)
 grad_reduce_kernel(ReduceSrc src, int S, int R, int TPN, float inv_s, float inv_r, const long* __restrict__ chunk_start,
                    const int* __restrict__ chunk_len, const int* __restrict__ chunk_ids, float* __restrict__ out,
-                   float* __restrict__ chunk_sos) {
+                   float* __restrict__ chunk_sos, const long* __restrict__ chunk_out_start = nullptr) {
   __shared__ float sh[32];
   // a launch covers either the first gridDim.x chunks of the table or, with `chunk_ids`, the listed ones (one bucket)
   const int c = chunk_ids ? chunk_ids[blockIdx.x] : (int)blockIdx.x;
@@ -113,7 +113,8 @@ grad_reduce_kernel(ReduceSrc src, int S, int R, int TPN, float inv_s, float inv_
       o[e] = __fmul_rn(rep[0][e], inv_r);
       if (j + e < len) acc = __fmaf_rn(o[e], o[e], acc);
     }
-    float* q = out + base + j;
+    // the reduced gradient may live in a packed buffer that holds this process's segments only (sharded state)
+    float* q = out + (chunk_out_start ? chunk_out_start[c] : base) + j;
     if (vec) {
       *reinterpret_cast<float4*>(q) = make_float4(o[0], o[1], o[2], o[3]);
       *reinterpret_cast<float4*>(q + 4) = make_float4(o[4], o[5], o[6], o[7]);
@@ -206,9 +207,17 @@ template <bool DST_BF16, bool AMSGRAD = false>
 __global__ void __launch_bounds__(256)
 adamw_push_kernel(AdamArgs a, const long* __restrict__ chunk_start, const int* __restrict__ chunk_len,
                   const int* __restrict__ chunk_group, float* __restrict__ master, float* __restrict__ grad,
-                  float* __restrict__ m1, float* __restrict__ m2, PushDst dst, int ndst, float* __restrict__ vmax = nullptr) {
+                  float* __restrict__ m1, float* __restrict__ m2, PushDst dst, int ndst, float* __restrict__ vmax = nullptr,
+                  const long* __restrict__ chunk_state_start = nullptr) {
   const long base = chunk_start[blockIdx.x];
   const int len = chunk_len[blockIdx.x];
+  // sharded state: gradient and moments sit in packed buffers of this process's segments (their own offsets), the master
+  // weights and the destinations keep the full layout
+  const long sdelta = chunk_state_start ? chunk_state_start[blockIdx.x] - base : 0;
+  grad += sdelta;
+  m1 += sdelta;
+  m2 += sdelta;
+  if (AMSGRAD) vmax += sdelta;
   const float keep = a.lr_wd_keep[chunk_group[blockIdx.x]];
   for (int j = threadIdx.x * 8; j < len; j += 2048) {
     float pn[8];
@@ -430,6 +439,35 @@ extern "C" int otb_adamw_push_amsgrad(const float* hyper, const long* chunk_star
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dst_bf16) adamw_push_kernel<true, true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, vmax);
   else adamw_push_kernel<false, true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, vmax);
+  return (int)cudaGetLastError();
+}
+// Sharded state: the reduced gradient goes to `out + chunk_out_start[c]` (a packed buffer of the owned segments).
+// `tp` >= 1 partial buffers per virtual rank; `chunk_ids` may be null.
+extern "C" int otb_grad_reduce_ex(const void* const* srcs, int S, int R, int tp, const long* chunk_start, const int* chunk_len,
+                                  const int* chunk_ids, int n, const long* chunk_out_start, float* out, float* chunk_sos, void* stream) {
+  if (tp < 1 || S * R * tp > MAX_SRC || R > 16 || S < 1 || R < 1) return -2;
+  if (n <= 0) return 0;
+  ReduceSrc rs;
+  for (int i = 0; i < S * R * tp; ++i) rs.p[i] = reinterpret_cast<const float*>(srcs[i]);
+  const float inv_s = 1.0f / (float)S, inv_r = 1.0f / (float)R;
+  grad_reduce_kernel<<<n, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rs, S, R, tp, inv_s, inv_r, chunk_start, chunk_len, chunk_ids,
+                                                                            out, chunk_sos, chunk_out_start);
+  return (int)cudaGetLastError();
+}
+// Sharded state: gradient and moments are addressed by `chunk_state_start`, master weights and destinations by `chunk_start`.
+extern "C" int otb_adamw_push_ex(const float* hyper, const long* chunk_start, const long* chunk_state_start, const int* chunk_len,
+                                 const int* chunk_group, int nchunks, float* master, float* grad, float* m1, float* m2,
+                                 const void* const* dsts, int ndst, int dst_bf16, void* stream) {
+  if (ndst > MAX_DST) return -2;
+  if (nchunks <= 0) return 0;
+  AdamArgs a;
+  a.clip = hyper[0]; a.lr_wd_keep[0] = hyper[1]; a.lr_wd_keep[1] = hyper[2]; a.beta1 = hyper[3]; a.beta2 = hyper[4];
+  a.one_m_b1 = hyper[5]; a.one_m_b2 = hyper[6]; a.eps = hyper[7]; a.step_size = hyper[8]; a.sqrt_bc2 = hyper[9];
+  PushDst pd;
+  for (int i = 0; i < ndst; ++i) pd.p[i] = const_cast<void*>(dsts[i]);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dst_bf16) adamw_push_kernel<true><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, nullptr, chunk_state_start);
+  else adamw_push_kernel<false><<<nchunks, 256, 0, s>>>(a, chunk_start, chunk_len, chunk_group, master, grad, m1, m2, pd, ndst, nullptr, chunk_state_start);
   return (int)cudaGetLastError();
 }
 extern "C" int otb_push_cast(const long* chunk_start, const int* chunk_len, int nchunks, const float* master,
