@@ -337,7 +337,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         for c in v0:
             v0_sum += c
         spike_loss = v0_sum / max(len(v0), 1)  # virtual rank 0's mean loss, as in the training loop
-        zero_q_gain_grads(engine.named_grads(), step, tr.qk_freeze_q_gains_until_step)  # mirrors train/loop.py
+        engine.zero_q_gain_grads(step, tr.qk_freeze_q_gains_until_step)  # mirrors train/loop.py
         if spike.should_skip(grad_norm, spike_loss, step):
             try:
                 spike.record_skip(step)

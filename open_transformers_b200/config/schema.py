@@ -261,6 +261,9 @@ class RunConfig(_Strict):
     tp_size: int = 1
     tp_fused: bool = False  # tensor-parallel traffic through the peer-memory GEMM kernels instead of library all-gathers (GPUs)
     heartbeat_timeout_s: float = 0.0  # > 0: host-side failure detection between the processes (parallel/heartbeat.py)
+    # With sharded ownership: allocate the AdamW moments and the reduced gradient for the OWNED segments only (12 of the 16
+    # state bytes per parameter shrink with the process count; the fp32 master weights stay whole). OTB_STATE_SHARDING=1 too.
+    state_sharding: bool = False
 
     @model_validator(mode="after")
     def _check(self):

@@ -283,24 +283,21 @@ class Checkpointer:
     def _snapshot(self, engine) -> dict:
         """This process's rows of master weights and moments, copied to (pinned) host memory, in the reference's layout."""
         lay = engine.layout
-        rows = engine.owned_row_ranges()
+        owned = engine.owned_pieces()
         index = optimizer_param_indices(engine.param_groups, lay.names, lay.groups)
         is_cuda = engine.is_cuda
-        total = sum((hi - lo) * (lay.numels[i] // max(lay.shapes[i][0] if lay.shapes[i] else 1, 1)) for i, rr in enumerate(rows) for lo, hi in rr)
-        kinds = {"weight": engine.master, "exp_avg": engine.m1, "exp_avg_sq": engine.m2}
+        total = sum(t["weight"].numel() for pp in owned for _lo, _hi, t in pp)
+        kinds = ("weight", "exp_avg", "exp_avg_sq")
         stage = {k: self._stage(k, total, torch.float32, is_cuda) for k in kinds}
         pieces = {k: [[] for _ in lay.names] for k in kinds}
         off = 0
-        for i, rr in enumerate(rows):
+        for i, pp in enumerate(owned):
             shape = lay.shapes[i]
-            dim0 = shape[0] if shape else 1
-            row = lay.numels[i] // max(dim0, 1)
-            for lo, hi in rr:
-                n = (hi - lo) * row
-                a = lay.offsets[i] + lo * row
-                for k, flat in kinds.items():
+            for lo, hi, tensors in pp:
+                n = tensors["weight"].numel()
+                for k in kinds:
                     dst = stage[k][off:off + n]
-                    dst.copy_(flat[a:a + n], non_blocking=is_cuda)
+                    dst.copy_(tensors[k], non_blocking=is_cuda)
                     pieces[k][i].append((lo, dst.view((hi - lo,) + tuple(shape[1:])) if shape else dst.view(())))
                 off += n
         if is_cuda:
@@ -355,13 +352,9 @@ class Checkpointer:
         lay = engine.layout
         index = optimizer_param_indices(engine.param_groups, lay.names, lay.groups)
         key = (lambda n: n) if keyed_by_name else (lambda n: index[n])
-        with torch.no_grad():
-            for i, n in enumerate(engine.names):
-                lay.view(engine.master, i).copy_(template["model"][n])
-                if load_optimizer:
-                    st = template["optim"]["state"][key(n)]
-                    lay.view(engine.m1, i).copy_(st["exp_avg"])
-                    lay.view(engine.m2, i).copy_(st["exp_avg_sq"])
+        for i, n in enumerate(engine.names):
+            st = template["optim"]["state"][key(n)] if load_optimizer else None
+            engine.load_parameter_state(i, template["model"][n], st["exp_avg"] if st else None, st["exp_avg_sq"] if st else None)
         if load_optimizer:
             steps = {int(template["optim"]["state"][key(n)]["step"]) for n in engine.names}
             if len(steps) != 1:

@@ -202,16 +202,7 @@ class TrainEngine:
             self.compute = self.buf_compute.typed(torch.bfloat16)
         else:
             self.buf_compute, self.compute = self.buf_master, self.master
-        if self._off_opt:
-            for key in ("exp_avg", "exp_avg_sq"):
-                self._mapped_file(key, optimizer_offload_dir, n, np.float32)
-        if self._off_opt and not self.is_cuda:
-            self._m1 = torch.from_numpy(self._off_files["exp_avg"])
-            self._m2 = torch.from_numpy(self._off_files["exp_avg_sq"])
-        else:
-            self._m1 = torch.zeros(n, dtype=torch.float32, device=self.device)
-            self._m2 = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.grad_red = torch.zeros(n, dtype=torch.float32, device=self.device)
+        # (the moments and the reduced gradient are allocated below, once the ownership is known)
         # Folded gradients (single-process replay with little memory): instead of one gradient buffer per hosted virtual
         # rank there is ONE work buffer plus one partial per replica; ``fold_virtual_rank`` adds a finished virtual rank
         # into its replica's partial in ascending shard order - the same left fold, element by element, that the reduction
@@ -250,10 +241,11 @@ class TrainEngine:
         self.chunk_lo = int(lay.seg_first[self.seg_lo])
         self.chunk_hi = int(lay.seg_first[self.seg_hi])
         self.peer = peer
-        if self.collective:
-            # packed layout of every owner's segments (each starting at a multiple of 64 elements) and, for this process,
-            # the chunk table of its own segments inside its packed buffer
-            self._pack_off, self._pack_len = [], []
+        # Packed layout of every owner's segments (each starting at a multiple of 64 elements): what travels in the
+        # point-to-point transport, and where the moments and the reduced gradient live when the state is sharded
+        self._packed_state = bool(self.sharded and (run.state_sharding or os.environ.get("OTB_STATE_SHARDING") == "1"))
+        self._pack_off, self._pack_len, self._owner_ranges = [], [], ranges
+        if self.sharded:
             for slo, shi in ranges:
                 offs, off = [], 0
                 for sg in lay.segments[slo:shi]:
@@ -261,12 +253,31 @@ class TrainEngine:
                     off += -(-sg.length // 64) * 64
                 self._pack_off.append(offs)
                 self._pack_len.append(max(off, 64))
+        n_state = self._pack_len[rank] if self._packed_state else n
+        self.chunk_state_start = None
+        if self._packed_state:
+            st = np.full(len(lay.chunk_start), -1, dtype=np.int64)
+            for sg, off in zip(lay.segments[self.seg_lo:self.seg_hi], self._pack_off[rank]):
+                for c in range(sg.first_chunk, sg.first_chunk + sg.n_chunks):
+                    st[c] = off + int(lay.chunk_start[c]) - sg.start
+            self.chunk_state_start = torch.from_numpy(st).to(dev)
+        if self._off_opt:
+            for key in ("exp_avg", "exp_avg_sq"):
+                self._mapped_file(key, optimizer_offload_dir, n, np.float32)
+        if self._off_opt and not self.is_cuda:
+            self._m1 = torch.from_numpy(self._off_files["exp_avg"])
+            self._m2 = torch.from_numpy(self._off_files["exp_avg_sq"])
+        else:
+            self._m1 = torch.zeros(n_state, dtype=torch.float32, device=self.device)
+            self._m2 = torch.zeros(n_state, dtype=torch.float32, device=self.device)
+        self.grad_red = torch.zeros(n_state, dtype=torch.float32, device=self.device)
+        if self.collective:
+            # the chunk table of this process's own segments inside its packed buffer
             mine = []
             for sg, off in zip(lay.segments[self.seg_lo:self.seg_hi], self._pack_off[rank]):
                 for c in range(sg.first_chunk, sg.first_chunk + sg.n_chunks):
                     mine.append(off + int(lay.chunk_start[c]) - sg.start)
             self._packed_chunk_start = torch.from_numpy(np.asarray(mine, dtype=np.int64)).to(dev)
-            self._owner_ranges = ranges
         # ``optim.name: muon_hybrid`` (experimental, outside the audited path): Muon on the 2-D block weights, the AdamW
         # kernel on everything else through a chunk table without those parameters
         # (reference src/pretrain/optim/muon.py:24-164, gated by config in src/pretrain/optim/registry.py:13-27)
@@ -369,8 +380,8 @@ class TrainEngine:
         S, R = self.dp_shard, self.dp_replicate
         if not self.is_cuda:
             if ov["n"][b]:
-                check(self.lib.otb_cpu_grad_reduce_ids(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
-                                                       I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos)), "grad_reduce_ids")
+                check(self.lib.otb_cpu_grad_reduce_ex(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
+                                                      I(ov["n"][b]), P(self.chunk_state_start), P(self.grad_red), P(self.chunk_sos)), "grad_reduce_ids")
             return
         wgrad_join()
         timed = ov["timeline"] is not None
@@ -395,8 +406,8 @@ class TrainEngine:
             t0 = torch.cuda.Event(enable_timing=True)
             t0.record(red)
         if ov["n"][b]:
-            check(self.lib.otb_grad_reduce_ids(ov["srcs"], I(S), I(R), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
-                                               I(ov["n"][b]), P(self.grad_red), P(self.chunk_sos), rs), "grad_reduce_ids")
+            check(self.lib.otb_grad_reduce_ex(ov["srcs"], I(S), I(R), I(1), P(self.chunk_start), P(self.chunk_len), P(ov["ids"][b]),
+                                              I(ov["n"][b]), P(self.chunk_state_start), P(self.grad_red), P(self.chunk_sos), rs), "grad_reduce_ids")
         if timed:
             t1 = torch.cuda.Event(enable_timing=True)
             t1.record(red)
@@ -588,7 +599,8 @@ class TrainEngine:
     def resident_bytes(self) -> dict:
         """Bytes of training state this process holds, by kind (activations and collective staging excluded)."""
         n = self.layout.total
-        out = {"master": 4 * n, "moments": 0 if (self._off_opt and self._m1 is None) else 8 * n, "reduced_gradient": 4 * n,
+        ns = self._pack_len[self.rank] if self._packed_state else n  # moments and reduced gradient: owned segments only when sharded
+        out = {"master": 4 * n, "moments": 0 if (self._off_opt and self._m1 is None) else 8 * ns, "reduced_gradient": 4 * ns,
                "gradient_buffers": 4 * n * len(self.grads), "compute_weights": 2 * n if self.mixed else 0}
         out["total"] = sum(out.values())
         return out
@@ -599,13 +611,101 @@ class TrainEngine:
         src = self.compute if self.sharded else self.master
         return [(n, self.layout.view(src, i)) for i, n in enumerate(self.names)]
 
-    def optimizer_state(self):
+    def _segment_view(self, flat: torch.Tensor, si: int, packed: bool = True) -> torch.Tensor:
+        """The elements of segment ``si`` inside ``flat``: a state buffer (moments, reduced gradient; ``packed``) holds only
+        the owned segments when the state is sharded, the master weights always keep the full layout."""
+        seg = self.layout.segments[si]
+        if packed and self._packed_state:
+            if not (self.seg_lo <= si < self.seg_hi):
+                raise IndexError("segment %d is not owned by this process" % si)
+            off = self._pack_off[self.rank][si - self.seg_lo]
+            return flat[off:off + seg.length]
+        return flat[seg.start:seg.start + seg.length]
+
+    def _full_state(self, flat: torch.Tensor) -> torch.Tensor:
+        """A full-layout copy of a state buffer. With sharded state every process contributes the segments it owns
+        (collective: every process must call it); otherwise the buffer itself."""
+        if not self._packed_state:
+            return flat
         lay = self.layout
-        return {n: {"step": self.opt_step, "exp_avg": lay.view(self.m1, i), "exp_avg_sq": lay.view(self.m2, i)}
-                for i, n in enumerate(self.names)}
+        full = torch.zeros(lay.total, dtype=flat.dtype, device=flat.device)
+        for si in range(self.seg_lo, self.seg_hi):
+            seg = lay.segments[si]
+            full[seg.start:seg.start + seg.length].copy_(self._segment_view(flat, si))
+        for r, (slo, shi) in enumerate(self._owner_ranges):
+            for si in range(slo, shi):
+                seg = lay.segments[si]
+                dist.broadcast(full[seg.start:seg.start + seg.length], src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                               group=self.group)
+        return full
+
+    def optimizer_state(self):
+        """{name: {"step", "exp_avg", "exp_avg_sq"}} as whole tensors (with sharded state: gathered copies, a collective)."""
+        lay = self.layout
+        m1, m2 = self._full_state(self.m1), self._full_state(self.m2)
+        return {n: {"step": self.opt_step, "exp_avg": lay.view(m1, i), "exp_avg_sq": lay.view(m2, i)} for i, n in enumerate(self.names)}
 
     def named_grads(self):
-        return {n: self.layout.view(self.grad_red, i) for i, n in enumerate(self.names)}
+        """{name: reduced gradient} as whole tensors (with sharded state: gathered copies, a collective)."""
+        red = self._full_state(self.grad_red)
+        return {n: self.layout.view(red, i) for i, n in enumerate(self.names)}
+
+    def zero_q_gain_grads(self, step: int, freeze_until_step: int) -> int:
+        """Freeze the query gains of the QK norm for the first steps: their reduced gradient is zeroed before the update
+        (train/qk_gain_control.py; works on whole or sharded state)."""
+        if freeze_until_step <= 0 or step >= freeze_until_step:
+            return 0
+        n = 0
+        for si in (range(self.seg_lo, self.seg_hi) if self.sharded else range(self.n_segs)):
+            if self.names[self.layout.segments[si].param].endswith("q_norm.weight"):
+                self._segment_view(self.grad_red, si).zero_()
+                n += 1
+        return n
+
+    def owned_pieces(self) -> list[list[tuple[int, int, dict]]]:
+        """Per parameter, the row ranges this process keeps current, each with views of the master weights and the moments
+        of those rows: [(row_lo, row_hi, {"weight", "exp_avg", "exp_avg_sq"})]. Adjacent shards are one piece unless the
+        state is packed (where each segment has its own place)."""
+        lay = self.layout
+        out: list[list] = [[] for _ in lay.names]
+        if self._packed_state:
+            for si in range(self.seg_lo, self.seg_hi):
+                seg = lay.segments[si]
+                shape = lay.shapes[seg.param]
+                row = lay.numels[seg.param] // max(shape[0] if shape else 1, 1)
+                lo = (seg.start - lay.offsets[seg.param]) // row
+                out[seg.param].append((lo, lo + seg.length // row, {"weight": self._segment_view(self.master, si, packed=False),
+                                                                    "exp_avg": self._segment_view(self.m1, si), "exp_avg_sq": self._segment_view(self.m2, si)}))
+            for pieces in out:
+                pieces.sort(key=lambda t: t[0])
+            return out
+        for i, rr in enumerate(self.owned_row_ranges()):
+            shape = lay.shapes[i]
+            row = lay.numels[i] // max(shape[0] if shape else 1, 1)
+            for lo, hi in rr:
+                a, b = lay.offsets[i] + lo * row, lay.offsets[i] + hi * row
+                out[i].append((lo, hi, {"weight": self.master[a:b], "exp_avg": self.m1[a:b], "exp_avg_sq": self.m2[a:b]}))
+        return out
+
+    def load_parameter_state(self, i: int, weight: torch.Tensor, exp_avg: torch.Tensor | None, exp_avg_sq: torch.Tensor | None) -> None:
+        """Install parameter ``i``'s loaded tensors (whole, on any device): the master weights everywhere, the moments where
+        this process keeps them."""
+        lay = self.layout
+        with torch.no_grad():
+            lay.view(self.master, i).copy_(weight)
+            if exp_avg is None:
+                return
+            if not self._packed_state:
+                lay.view(self.m1, i).copy_(exp_avg)
+                lay.view(self.m2, i).copy_(exp_avg_sq)
+                return
+            for si in range(self.seg_lo, self.seg_hi):
+                seg = lay.segments[si]
+                if seg.param != i:
+                    continue
+                a = seg.start - lay.offsets[i]
+                self._segment_view(self.m1, si).copy_(exp_avg.reshape(-1)[a:a + seg.length])
+                self._segment_view(self.m2, si).copy_(exp_avg_sq.reshape(-1)[a:a + seg.length])
 
     def _barrier(self) -> None:
         if self.world > 1:
@@ -827,14 +927,13 @@ class TrainEngine:
             lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
             cs, cl = self.chunk_start[lo:], self.chunk_len[lo:]
             sos = self.chunk_sos[lo:]
-            if self.is_cuda and tpn > 1:
-                check(self.lib.otb_grad_reduce_tp(_ptr_array(srcs), I(S), I(R), I(tpn), P(cs), P(cl), P(None), I(cnt), P(self.grad_red), P(sos),
-                                                  stream_ptr()), "grad_reduce_tp")
-            elif self.is_cuda:
-                check(self.lib.otb_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos), stream_ptr()),
-                      "grad_reduce")
+            sst = self.chunk_state_start[lo:] if self.chunk_state_start is not None else None  # packed reduced gradient
+            if self.is_cuda:
+                check(self.lib.otb_grad_reduce_ex(_ptr_array(srcs), I(S), I(R), I(tpn), P(cs), P(cl), P(None), I(cnt), P(sst), P(self.grad_red), P(sos),
+                                                  stream_ptr()), "grad_reduce")
             else:
-                check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), I(cnt), P(self.grad_red), P(sos)), "grad_reduce")
+                check(self.lib.otb_cpu_grad_reduce_ex(_ptr_array(srcs), I(S), I(R), P(cs), P(cl), P(None), I(cnt), P(sst), P(self.grad_red), P(sos)),
+                      "grad_reduce")
             if self.fold:
                 self._keep = None
             if self.peer:
@@ -909,7 +1008,8 @@ class TrainEngine:
             for p_, t in enumerate(recvs):
                 got[p_ * per + j] = t
         srcs = [got[v].data_ptr() for v in range(self.V)]
-        red = torch.empty(mine, dtype=torch.float32, device=self.device)
+        # a packed reduced gradient has exactly the layout of the packed messages
+        red = self.grad_red if self._packed_state else torch.empty(mine, dtype=torch.float32, device=self.device)
         lo, cnt = self.chunk_lo, self.chunk_hi - self.chunk_lo
         cl, sos = self.chunk_len[lo:], self.chunk_sos[lo:]
         if self.is_cuda:
@@ -917,7 +1017,8 @@ class TrainEngine:
                   "grad_reduce")
         else:
             check(self.lib.otb_cpu_grad_reduce(_ptr_array(srcs), I(S), I(R), P(self._packed_chunk_start), P(cl), I(cnt), P(red), P(sos)), "grad_reduce")
-        self._unpack(red, self.rank, self.grad_red)
+        if not self._packed_state:
+            self._unpack(red, self.rank, self.grad_red)
         self._share_chunk_sos()
 
     def _share_chunk_sos(self) -> None:
@@ -993,12 +1094,15 @@ class TrainEngine:
             self._muon_step(float(lr), float(clip))
         dst_buf = self.buf_compute
         dsts = dst_buf.ptrs if self.peer else [self.compute.data_ptr()]
+        sst = None
+        if self.chunk_state_start is not None and not self.muon_params:
+            sst = self.chunk_state_start[lo:]  # gradient and moments sit in the packed buffers of the owned segments
         if self.is_cuda:
-            check(self.lib.otb_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
-                                          _ptr_array(dsts), I(len(dsts)), I(self.mixed), stream_ptr()), "adamw_push")
+            check(self.lib.otb_adamw_push_ex(hyper, P(cs), P(sst), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                             _ptr_array(dsts), I(len(dsts)), I(self.mixed), stream_ptr()), "adamw_push")
         else:
-            check(self.lib.otb_cpu_adamw_push(hyper, P(cs), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
-                                              _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
+            check(self.lib.otb_cpu_adamw_push_ex(hyper, P(cs), P(sst), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                                 _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
         if self.collective:
             self._share_updated_weights()
         self._tick("opt")
@@ -1068,7 +1172,7 @@ class TrainEngine:
             seg = lay.segments[si]
             for tag, flat in fields:
                 keys.append((seg.param, seg.shard, tag))
-                views.append(flat[seg.start:seg.start + seg.length])
+                views.append(self._segment_view(flat, si, packed=tag != "weight"))
         handle["keys"] = keys
         if self.is_cuda and views:
             plans = self.__dict__.setdefault("_hash_plans", {})
@@ -1198,7 +1302,7 @@ class TrainEngine:
         self._wait_pending_hash()
         lay = self.layout
         ranges = lay.owner_ranges(self.world)
-        for flat in (self.master, self.m1, self.m2, self.grad_red):
+        for flat in ((self.master,) if self._packed_state else (self.master, self.m1, self.m2, self.grad_red)):
             for r, (slo, shi) in enumerate(ranges):
                 for si in range(slo, shi):
                     seg = lay.segments[si]

@@ -236,7 +236,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             # src/pretrain/train/loop.py:977-992, src/pretrain/cli/audit_replay.py:2548-2551)
             v0_sum, v0_n = deterministic_scalar_sum([c for c, v in zip(local_ce, owners) if v == 0] if lead else [], world)
             spike_loss = v0_sum / max(v0_n, 1)
-            zero_q_gain_grads(engine.named_grads(), step, train_cfg.qk_freeze_q_gains_until_step)
+            engine.zero_q_gain_grads(step, train_cfg.qk_freeze_q_gains_until_step)
             skipped = spike.should_skip(grad_norm, spike_loss, step)
             clip = engine.clip_coefficient(grad_norm, train_cfg.grad_clip)
             if skipped:

@@ -151,15 +151,22 @@ def test_off_cadence_final_checkpoint_hash_equals_log_and_replay_and_does_not_ad
 
 
 @pytest.mark.distributed
-def test_sharded_ownership_by_messages_through_the_train_loop_and_a_checkpoint(tmp_path):
+@pytest.mark.parametrize("packed", [False, True])
+def test_sharded_ownership_by_messages_through_the_train_loop_and_a_checkpoint(tmp_path, packed):
     """two processes with sharded ownership over point-to-point messages (the transport of GPUs on several machines): hashes
     of the single-process run, a checkpoint into which each process wrote the rows it owns (data files of both processes,
-    no gathering to rank 0), and a single-process resume from it"""
+    no gathering to rank 0), and a single-process resume from it. ``packed``: run.state_sharding, where each process holds
+    the moments of its own segments only - the checkpoint is the same, and two such processes resume from it too"""
     tmp = str(tmp_path)
     over = LONG + ["++train.state_hash.tensor_digest=tree"]
     whole = train(tiny_cfg(tmp, over + ["run.run_id=one"]), device="cpu", data_root=tmp)
-    two = _ranks(2, tmp, over + ["run.run_id=msg"], None, 2, str(tmp_path / "msg.json"), OTB_GRAD_TRANSPORT="collective")
+    shard = ["run.state_sharding=true"] if packed else []
+    two = _ranks(2, tmp, over + shard + ["run.run_id=msg"], None, 2, str(tmp_path / "msg.json"), OTB_GRAD_TRANSPORT="collective")
     assert two == whole["hashes"][:2]
+    if packed:
+        again = _ranks(2, tmp, over + shard + ["run.run_id=msg2"], "%s/runs/msg/checkpoints/step_000000002" % tmp, None, str(tmp_path / "msg2.json"),
+                       OTB_GRAD_TRANSPORT="collective")
+        assert again == whole["hashes"][2:]
     files = sorted(p.name for p in Path("%s/runs/msg/checkpoints/step_000000002/dcp" % tmp).iterdir())
     assert ".metadata" in files and any(f.startswith("__0_") for f in files) and any(f.startswith("__1_") for f in files), files
     rest = train(tiny_cfg(tmp, over + ["run.run_id=msg"]), resume_from="%s/runs/msg/checkpoints/step_000000002" % tmp, device="cpu", data_root=tmp)

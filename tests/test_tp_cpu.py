@@ -126,3 +126,26 @@ def test_sharded_ownership_over_point_to_point_messages(tmp_path, world, bf16):
     got = _run(world, 1, bf16, tmp_path / "sharded.json", OTB_GRAD_TRANSPORT="collective", **env)
     assert [h for _, _, h in got] == [h for _, _, h in base]
     assert [n for n, _, _ in got] == [n for n, _, _ in base]
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_optimizer_state_keeps_only_owned_segments_and_writes_the_same_hashes(tmp_path, world):
+    """run.state_sharding / OTB_STATE_SHARDING=1: the AdamW moments and the reduced gradient are allocated for the segments a
+    process owns only (about 1/N of the full layout each); reductions, updates, digests, gathered state and resident-byte
+    accounting agree with the single-process run"""
+    import torch
+
+    env = dict(OTB_TEST_V="4", OTB_TEST_TD="tree")
+    base = _run(1, 1, True, tmp_path / "base.json", OTB_TEST_STATE_OUT=str(tmp_path / "base.pt"), **env)
+    got = _run(world, 1, True, tmp_path / "packed.json", OTB_GRAD_TRANSPORT="collective", OTB_STATE_SHARDING="1",
+               OTB_TEST_STATE_OUT=str(tmp_path / "packed.pt"), **env)
+    assert [(n, h) for n, _, h in got] == [(n, h) for n, _, h in base]
+    a, b = torch.load(tmp_path / "base.pt"), torch.load(tmp_path / "packed.pt")
+    for kind in ("m1", "m2", "grad"):
+        for name, t in a[kind].items():
+            assert torch.equal(t, b[kind][name]), (kind, name)
+    full, part = a["resident"], b["resident"]
+    assert part["master"] == full["master"]
+    for key in ("moments", "reduced_gradient"):
+        assert part[key] < full[key] * (1.0 / world + 0.2), (key, part[key], full[key])

@@ -73,6 +73,9 @@ def main():
         eng._tp_state.ws = HostWorkspace(eng.tp_rank, eng.tp, eng._tp_group)
     if os.environ.get("OTB_GRAD_TRANSPORT") == "collective" and world > 1:
         assert eng.collective and eng.sharded and not eng.peer and 0 < eng.seg_hi - eng.seg_lo < eng.n_segs
+    packed = os.environ.get("OTB_STATE_SHARDING") == "1" and world > 1
+    if packed:
+        assert eng._packed_state and eng.m1.numel() == eng.grad_red.numel() < eng.layout.total
     prev, out = None, []
     for step in range(3):
         eng.zero_grads()
@@ -95,6 +98,12 @@ def main():
     if os.environ.get("OTB_TEST_HOST_WS") == "1" and tp > 1:
         kinds = {c for c in eng._tp_state.ws.calls}
         assert kinds == {("ag", "col"), ("ag", "row_bwd"), ("chain", "row")}, kinds
+    if os.environ.get("OTB_TEST_STATE_OUT"):
+        # whole-tensor views of the optimizer state and the reduced gradient (gathered from their owners when sharded)
+        st, gr = eng.optimizer_state(), eng.named_grads()
+        if rank == 0:
+            torch.save({"m1": {n: s["exp_avg"].clone() for n, s in st.items()}, "m2": {n: s["exp_avg_sq"].clone() for n, s in st.items()},
+                        "grad": {n: g.clone() for n, g in gr.items()}, "resident": eng.resident_bytes()}, os.environ["OTB_TEST_STATE_OUT"])
     if rank == 0:
         json.dump(out, open(os.environ["OTB_TEST_OUT"], "w"))
     if world > 1:
