@@ -91,7 +91,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="open1b_b200")
-    ap.add_argument("--override", action="append", default=[], help="config override (debugging; makes the number invalid)")
+    ap.add_argument("--override", action="extend", nargs="+", default=[], help="config override (debugging; makes the number invalid)")
     ap.add_argument("--no-hash", action="store_true", help="debugging: skip the per-step state hash (makes the number invalid)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (run.tp_size); the GPUs form one group")
     ap.add_argument("--tp-fused", action="store_true", help="with --tp: peer-memory all-gather->GEMM / chained GEMM kernels (run.tp_fused)")
@@ -161,7 +161,7 @@ def main() -> int:
         chains = {v: h.local_digest() for v, h in hashers.items()}
         if world > 1:
             objs = [None] * world
-            dist.all_gather_object(objs, chains)
+            dist.all_gather_object(objs, chains, group=eng.host_group)  # host bytes over gloo: no wait on the device's queue
             chains = {k: d for part in objs for k, d in part.items()}
         return SH.combine_batch_digests([chains[v] for v in range(V)])
 

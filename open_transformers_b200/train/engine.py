@@ -98,6 +98,13 @@ class TrainEngine:
         self.dp_replicate, self.dp_shard, self.V, self.tp = dims.dp_replicate, dims.dp_shard, dims.virtual_dp, dims.tp
         self.dp_groups, self.dp_rank, self.tp_rank = dims.dp_processes, rank // dims.tp, dims.tp_rank(rank)
         self.hosted = dims.hosted_virtual_ranks(rank)
+        # Small host-side exchanges (digests, batch chains, logged scalars) go over a gloo group of their own: a library
+        # collective on device tensors would first wait for everything queued on the stream - the whole backward pass - and
+        # stall the host that should be queueing the next kernels. CPU ranks already talk gloo.
+        self.host_group = group
+        if world > 1 and group is None and dist.get_backend() != "gloo":
+            self.host_group = dist.new_group(backend="gloo")
+        self._host_gloo = world > 1 and dist.get_backend(self.host_group) == "gloo"
         self._tp_state = None
         if self.tp > 1:
             from ..ops.autograd import TpState
@@ -1220,9 +1227,13 @@ class TrainEngine:
                 mine = torch.zeros(width, dtype=torch.uint8)
                 raw = b"".join(digs)
                 mine[: len(raw)] = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
-                mine = mine.to(self.device)
-                parts = [torch.empty_like(mine) for _ in range(self.world)]
-                dist.all_gather(parts, mine, group=self.group)
+                if self._host_gloo:  # the digests are host bytes already: no reason to touch the device or its streams
+                    parts = [torch.empty_like(mine) for _ in range(self.world)]
+                    dist.all_gather(parts, mine, group=self.host_group)
+                else:
+                    mine = mine.to(self.device)
+                    parts = [torch.empty_like(mine) for _ in range(self.world)]
+                    dist.all_gather(parts, mine, group=self.group)
                 allraw = torch.stack(parts).cpu().numpy().tobytes()
                 seg_digests = {}
                 for r, keys in enumerate(keys_by_rank):

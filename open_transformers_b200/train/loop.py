@@ -47,25 +47,38 @@ def _on_sigterm(signum, frame):
     _sigterm["flag"] = True
 
 
-def _emergency_exit_requested(world: int, device: torch.device) -> bool:
-    """Every rank learns whether ANY rank received SIGTERM, so that all of them checkpoint at the same step."""
+def _emergency_exit_requested(world: int, device: torch.device, group=None) -> bool:
+    """Every rank learns whether ANY rank received SIGTERM, so that all of them checkpoint at the same step. ``group``: a
+    host-side (gloo) group, where there is one, so that the question does not wait for the device's queue."""
     if world == 1:
         return _sigterm["flag"]
-    t = torch.tensor([1 if _sigterm["flag"] else 0], dtype=torch.int32, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    host = group is not None and dist.get_backend(group) == "gloo"
+    t = torch.tensor([1 if _sigterm["flag"] else 0], dtype=torch.int32, device="cpu" if host else device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group if host else None)
     return bool(t.item())
 
 
-def deterministic_scalar_sum(values: list[float], world: int) -> tuple[float, int]:
-    """Sum of python floats contributed by all ranks, folded in fp64 in rank order (telemetry and spike input)."""
+def deterministic_scalar_sums(lists: dict[str, list[float]], world: int, group=None) -> dict[str, tuple[float, int]]:
+    """Per key: sum and count of the python floats contributed by all ranks, folded in fp64 in rank order (telemetry and
+    spike input). One exchange for all keys."""
+    parts = [{k: [float(x) for x in v] for k, v in lists.items()}]
     if world > 1:
-        objs: list = [None] * world
-        dist.all_gather_object(objs, [float(v) for v in values])
-        values = [v for part in objs for v in part]
-    total = 0.0
-    for v in values:
-        total += float(v)
-    return total, len(values)
+        parts = [None] * world
+        dist.all_gather_object(parts, {k: [float(x) for x in v] for k, v in lists.items()}, group=group)
+    out = {}
+    for key in lists:
+        total, n = 0.0, 0
+        for part in parts:
+            for v in part[key]:
+                total += float(v)
+                n += 1
+        out[key] = (total, n)
+    return out
+
+
+def deterministic_scalar_sum(values: list[float], world: int, group=None) -> tuple[float, int]:
+    """Sum of python floats contributed by all ranks, folded in fp64 in rank order."""
+    return deterministic_scalar_sums({"x": values}, world, group)["x"]
 
 
 def _assert_same_on_all_ranks(payload: str, what: str, world: int) -> None:
@@ -170,7 +183,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
         chains = {v: h.local_digest() for v, h in hashers.items()}
         if world > 1:
             objs: list = [None] * world
-            dist.all_gather_object(objs, chains)
+            dist.all_gather_object(objs, chains, group=engine.host_group)
             chains = {k: v for d in objs for k, v in d.items()}
         return SH.combine_batch_digests([chains[v] for v in range(V)])
 
@@ -229,12 +242,12 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             grad_norm = engine.reduce_gradients()
             local_ce = [float(c) for c in ces]
             lead = engine.tp_rank == 0  # the ranks of a tensor-parallel group hold the same values: one of them reports
-            ce_sum, n_mb = deterministic_scalar_sum(local_ce if lead else [], world)
-            z_sum, _ = deterministic_scalar_sum([float(z) for z in zs] if lead else [], world)
-            loss_mean = ce_sum / max(n_mb, 1)
-            # the spike gate looks at virtual rank 0's mean loss, on every rank, as the replay does (reference
+            # the spike gate looks at virtual rank 0's mean loss ("v0"), on every rank, as the replay does (reference
             # src/pretrain/train/loop.py:977-992, src/pretrain/cli/audit_replay.py:2548-2551)
-            v0_sum, v0_n = deterministic_scalar_sum([c for c, v in zip(local_ce, owners) if v == 0] if lead else [], world)
+            sums = deterministic_scalar_sums({"ce": local_ce if lead else [], "z": [float(z) for z in zs] if lead else [],
+                                              "v0": [c for c, v in zip(local_ce, owners) if v == 0] if lead else []}, world, engine.host_group)
+            (ce_sum, n_mb), (z_sum, _), (v0_sum, v0_n) = sums["ce"], sums["z"], sums["v0"]
+            loss_mean = ce_sum / max(n_mb, 1)
             spike_loss = v0_sum / max(v0_n, 1)
             engine.zero_q_gain_grads(step, train_cfg.qk_freeze_q_gains_until_step)
             skipped = spike.should_skip(grad_norm, spike_loss, step)
@@ -253,7 +266,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             consumed += plan.tokens_this_step
             step += 1
 
-            exit_due = _emergency_exit_requested(world, dev)
+            exit_due = _emergency_exit_requested(world, dev, engine.host_group)
             final_step = consumed >= train_cfg.total_tokens or (max_steps is not None and step >= max_steps)
             hash_due = sh_cfg.every_n_steps > 0 and step % sh_cfg.every_n_steps == 0
             ckpt_due = (train_cfg.ckpt_every_steps > 0 and step % train_cfg.ckpt_every_steps == 0) or \

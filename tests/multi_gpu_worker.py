@@ -39,7 +39,8 @@ def main():
         out.append([norm, prev])
     status = kernel_status(dev)
     if rank == 0:
-        json.dump({"hashes": out, "status": status, "overlapped_steps": 0 if eng._ov is None else eng._ov["epoch"]}, open(os.environ["OTB_TEST_OUT"], "w"))
+        json.dump({"hashes": out, "status": status, "overlapped_steps": 0 if eng._ov is None else eng._ov["epoch"], "resident": eng.resident_bytes(),
+                   "packed_state": bool(eng._packed_state)}, open(os.environ["OTB_TEST_OUT"], "w"))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -159,7 +159,7 @@ def test_sigterm_checkpoint_is_off_cadence_and_replays(tmp_path, monkeypatch):
     cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=0", "run.run_id=term"])
     calls = {"n": 0}
 
-    def fake(world, device):
+    def fake(world, device, group=None):
         calls["n"] += 1
         return calls["n"] == 2          # "SIGTERM arrived" during the second step
 

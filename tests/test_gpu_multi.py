@@ -15,8 +15,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.distributed]
 WORKER = str(Path(__file__).resolve().parent / "multi_gpu_worker.py")
 
 
-def _run(n, out, shard=4):
-    env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_SHARD=str(shard), NCCL_NVLS_ENABLE="0")
+def _run(n, out, shard=4, **extra):
+    env = dict(os.environ, OTB_TEST_OUT=str(out), OTB_TEST_SHARD=str(shard), NCCL_NVLS_ENABLE="0", **extra)
     if n == 1:
         cmd = [sys.executable, WORKER]
     else:
@@ -63,3 +63,16 @@ def test_message_transport_between_two_gpus_reproduces_the_single_gpu_hashes(tmp
     one = run(1, tmp_path / "g1.json")
     two = run(2, tmp_path / "g2.json", OTB_GRAD_TRANSPORT="collective")
     assert one["status"] == 0 and two["status"] == 0 and two["hashes"] == one["hashes"]
+
+
+def test_sharded_optimizer_state_over_peer_memory_reproduces_the_single_gpu_hashes(tmp_path):
+    """OTB_STATE_SHARDING=1: each GPU allocates the moments and the reduced gradient of its own segments only; the reduction
+    (bucket by bucket under the backward pass) and the AdamW kernel write through the packed offsets, and the bytes are those
+    of one GPU that holds everything"""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    one = _run(1, tmp_path / "g1.json")
+    two = _run(2, tmp_path / "g2.json", OTB_STATE_SHARDING="1")
+    assert one["status"] == 0 and two["status"] == 0 and two["packed_state"] and not one["packed_state"]
+    assert two["hashes"] == one["hashes"]
+    assert two["resident"]["moments"] < 0.6 * one["resident"]["moments"] and two["resident"]["reduced_gradient"] < 0.6 * one["resident"]["reduced_gradient"]
