@@ -234,7 +234,9 @@ def main() -> int:
     sampler = ClockSampler(local_rank)
     launches0 = native.launch_count
     sampler.start()
+    eng.phase_report()                      # (phase timers, when PRETRAIN_CUDA_EVENT_TIMING=1: start from zero)
     ms_dev, _ = timed(W, Kst, True)
+    phases = {k: v / Kst for k, v in eng.phase_report().items()}
     launches = native.launch_count - launches0
     clocks = sampler.stop()
     timed(0, W, False)                      # warm-up of the end-to-end path (the stream supplies its own batches)
@@ -273,6 +275,8 @@ def main() -> int:
             "final_loss": loss, "final_hash": state["prev"], "kernel_status": status,
             "native_libs": native.loaded_libraries(),
         }
+        if phases:  # diagnostic run with phase timers: device time per step inside forward / backward / reduction+norm / update
+            line["phases_ms_per_step"] = phases
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
