@@ -35,42 +35,76 @@ BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput figure
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region is timed."""
+    """SM clock, power and clock-event reasons of one GPU, sampled every 200 ms while a region is timed. Reads NVML in this
+    process (the library behind nvidia-smi; a read costs microseconds and starts no process next to the timed kernels);
+    without the Python binding it falls back to ONE long-running ``nvidia-smi -lms 200`` for the region."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+    def __init__(self, index: int, uuid: str | None = None):
+        self.index, self.uuid, self.rows, self._stop, self._t, self._proc = index, uuid, [], threading.Event(), None, None
+        self._nvml = self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid) if uuid else pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n, h = self._nvml, self._handle
+        bits = n.nvmlDeviceGetCurrentClocksEventReasons(h)
+        masks = (n.nvmlClocksEventReasonHwSlowdown, n.nvmlClocksEventReasonHwThermalSlowdown, n.nvmlClocksEventReasonSwThermalSlowdown,
+                 n.nvmlClocksEventReasonSwPowerCap)
+        return [str(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)), str(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)),
+                "%.1f" % (n.nvmlDeviceGetPowerUsage(h) / 1e3)] + ["Active" if bits & m else "Not Active" for m in masks]
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
+                self.rows.append(self._sample_nvml())
             except Exception:
                 pass
             self._stop.wait(0.2)
 
     def start(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        if self._nvml is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+            return
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", "-i", self.uuid or str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
 
     def stop(self) -> dict:
         self._stop.set()
         if self._t:
             self._t.join(timeout=6)
+        if self._proc is not None:
+            self._proc.terminate()  # the one process this sampler started
+            try:
+                out, _ = self._proc.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+                out, _ = self._proc.communicate()
+            self.rows += [[c.strip() for c in line.split(",")] for line in out.splitlines() if line.strip()]
         sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        watts = [float(r[2]) for r in self.rows if len(r) > 2 and r[2].replace(".", "").isdigit()]
         reasons = set()
         for r in self.rows:
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+            for name, val in zip(self.REASONS, r[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w": statistics.median(watts) if watts else None, "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 def reference_arm(args) -> int:
@@ -231,7 +265,7 @@ def main() -> int:
 
     W, Kst = args.warmup, args.steps
     timed(0, W, True)                       # warm-up (untimed)
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, "GPU-%s" % torch.cuda.get_device_properties(device).uuid)
     launches0 = native.launch_count
     sampler.start()
     eng.phase_report()                      # (phase timers, when PRETRAIN_CUDA_EVENT_TIMING=1: start from zero)

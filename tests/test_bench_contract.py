@@ -55,10 +55,13 @@ def test_reference_arm_times_the_unmodified_reference_loop_on_a_tiny_model():
 
 
 def test_clock_sampler_reads_clocks_and_throttle_reasons(tmp_path, monkeypatch):
+    """without the NVML binding: ONE nvidia-smi process that loops for the length of the region (here a stand-in script)"""
     fake = tmp_path / "nvidia-smi"
-    fake.write_text("#!/bin/sh\necho '1410, 1965, 987.5, Not Active, Not Active, Not Active, Active'\n")
+    line = "1410, 1965, 987.5, Not Active, Not Active, Not Active, Active"
+    fake.write_text("#!/bin/sh\nwhile true; do echo '%s'; sleep 0.1; done\n" % line)
     fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
     monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    monkeypatch.setitem(sys.modules, "pynvml", None)            # importing it fails: the fallback is taken
     sys.path.insert(0, str(ROOT))
     import bench
 
@@ -67,11 +70,35 @@ def test_clock_sampler_reads_clocks_and_throttle_reasons(tmp_path, monkeypatch):
     time.sleep(0.7)
     out = s.stop()
     assert out["sm_mhz"] == 1410.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"] and out["samples"] >= 2
-    fake.write_text("#!/bin/sh\necho '600, 1965, 300, Active, Not Active, Active, Not Active'\n")
+    assert out["source"] == "nvidia-smi" and out["power_w"] == 987.5
+    fake.write_text("#!/bin/sh\nwhile true; do echo '600, 1965, 300, Active, Not Active, Active, Not Active'; sleep 0.1; done\n")
     s = bench.ClockSampler(0)
     s.start()
     time.sleep(0.5)
     assert s.stop()["reasons"] == ["hw_slowdown", "sw_thermal_slowdown"]
+
+
+def test_clock_sampler_reads_nvml_in_process(monkeypatch):
+    """with the NVML binding: reads in this process by the GPU's UUID, reasons decoded from the event-reason bits"""
+    import types
+
+    seen = {}
+    nv = types.SimpleNamespace(
+        NVML_CLOCK_SM=1, nvmlClocksEventReasonHwSlowdown=0x8, nvmlClocksEventReasonHwThermalSlowdown=0x40,
+        nvmlClocksEventReasonSwThermalSlowdown=0x20, nvmlClocksEventReasonSwPowerCap=0x4,
+        nvmlInit=lambda: None, nvmlDeviceGetHandleByUUID=lambda u: seen.setdefault("uuid", u) and "h",
+        nvmlDeviceGetHandleByIndex=lambda i: "h", nvmlDeviceGetClockInfo=lambda h, k: 1530, nvmlDeviceGetMaxClockInfo=lambda h, k: 1965,
+        nvmlDeviceGetPowerUsage=lambda h: 998000, nvmlDeviceGetCurrentClocksEventReasons=lambda h: 0x4 | 0x1)
+    monkeypatch.setitem(sys.modules, "pynvml", nv)
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    s = bench.ClockSampler(3, "GPU-1234")
+    s.start()
+    time.sleep(0.5)
+    out = s.stop()
+    assert seen["uuid"] == "GPU-1234" and out["source"] == "nvml" and out["samples"] >= 2
+    assert out["sm_mhz"] == 1530.0 and out["sm_max_mhz"] == 1965.0 and out["power_w"] == 998.0 and out["reasons"] == ["sw_power_cap"]
 
 
 def test_defaults_are_one_gpu_and_at_least_three_warm_up_steps():
