@@ -264,6 +264,9 @@ class RunConfig(_Strict):
     # With sharded ownership: allocate the AdamW moments and the reduced gradient for the OWNED segments only (12 of the 16
     # state bytes per parameter shrink with the process count; the fp32 master weights stay whole). OTB_STATE_SHARDING=1 too.
     state_sharding: bool = False
+    # "gather": the bf16 rows of the projection weights stay with their owner after the update and the first forward GEMM
+    # pulls the others' rows over peer memory itself (parallel/param_gather.py); "replicate": the AdamW kernel pushes them
+    param_sharding: Literal["replicate", "gather"] = "replicate"
 
     @model_validator(mode="after")
     def _check(self):

@@ -74,7 +74,28 @@ struct TpArgs {
   long ag_block_u4;            // 16-byte units per 128-row block
   uint32_t seq;                // value a flag takes when its data of THIS call has landed
   int rank, P, tiles_per_shard, gemm_ctas;
+  // TP 3 (parameter gather): B [N,K] is a weight whose rows are spread over the P processes. Every process keeps a
+  // full-size buffer of the same layout in which only its own rows are current; the rows of the others are pulled
+  // from their buffers (plain peer loads) into the local one by four extra warps of the GEMM's own CTAs.
+  const uint4* pg_src[8];      // row 0 of this weight in every process's buffer ([rank] is the local buffer)
+  uint4* pg_dst;               // row 0 of this weight in the local buffer (what tmB reads)
+  uint32_t* pg_flags;          // local: one word per 128-row block of B; takes `seq` once the block is complete here
+  int pg_seg_begin[4];         // B is up to 3 row-concatenated parameters: first row of each, then N
+  int pg_rows_per_owner[3];    // rows of parameter j per process (process p holds rows [p*rpo, (p+1)*rpo) of it)
+  int pg_nseg, pg_rot;         // number of parameters; 128-row block the tile order starts from (own rows first)
+  int pg_row_u4, pg_ld_u4;     // 16-byte units per row that are copied / between rows
 };
+
+constexpr int PG_ROWS = 128;   // rows of B per parameter-gather flag
+
+// Which process holds row `row` of a gathered weight.
+__device__ __forceinline__ int pg_owner(const TpArgs& tp, int row) {
+  int j = 0;
+  if (tp.pg_nseg > 1 && row >= tp.pg_seg_begin[1]) j = 1;
+  if (tp.pg_nseg > 2 && row >= tp.pg_seg_begin[2]) j = 2;
+  const int o = (row - tp.pg_seg_begin[j]) / tp.pg_rows_per_owner[j];
+  return o < tp.P ? o : tp.P - 1;
+}
 
 // Launch-order permutation for the race tests: CTA b works as CTA (b + g_cta_rotation) mod (number of GEMM CTAs). Every
 // output tile is owned by one CTA and summed in ascending k whatever CTA that is, so any rotation must give the same bytes
@@ -121,7 +142,7 @@ struct SmemLayout {
 };
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool I8, int TP, typename TPA>
-__global__ void __launch_bounds__(TP == 2 ? NUM_THREADS + 128 : NUM_THREADS, 1)
+__global__ void __launch_bounds__(TP >= 2 ? NUM_THREADS + 128 : NUM_THREADS, 1)
 gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv,
                  const __nv_bfloat16* __restrict__ R, int M, int N, int K, long ldc, long ldr, int group_m,
@@ -218,6 +239,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tm = first_m + r % gsz;
     tn = r / gsz;
     if constexpr (TP == 1) tm = (tm + tp.rank * tp.tiles_per_shard) % tiles_m;  // own rows first, then the peers' in ring order
+    if constexpr (TP == 3) tn = (tn + tp.pg_rot / (BN / PG_ROWS)) % tiles_n;      // weight rows of this process first
   };
 
   if (warp == 0) {
@@ -236,6 +258,17 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!wait_peer_flag(tp.flags_in + owner * tp.tiles_per_shard + tm % tp.tiles_per_shard, tp.seq, abort_flag)) { ok = false; break; }
             asm volatile("fence.proxy.async;" ::: "memory");  // the peer's generic stores, then our TMA (async proxy) reads
           }
+        }
+        if constexpr (TP == 3) {
+          // the rows of this B tile must be complete in the local buffer: one flag per 128-row block, written by the
+          // copier warps of whichever CTA pulled the block
+          for (int b = 0; b < BN / PG_ROWS && ok; ++b) {
+            const int blk = tn * (BN / PG_ROWS) + b;
+            if (blk * PG_ROWS >= N) break;
+            if (!wait_peer_flag(tp.pg_flags + blk, tp.seq, abort_flag)) ok = false;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // the copiers' generic stores, then our TMA (async proxy) reads
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -292,6 +325,42 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs have read it
         }
         if (ok) mma_commit(&tfull_bar[buf]);  // accumulator complete
+      }
+    }
+  } else if (TP == 3 && warp >= 6) {
+    // ------------------------------------------ parameter gather: pull the other processes' rows of B into the local buffer
+    if constexpr (TP == 3) {
+      const int ct = threadIdx.x - 6 * 32;                  // 0..127 among the copier threads of this CTA
+      const int nblk = (N + PG_ROWS - 1) / PG_ROWS;
+      for (int j = cta; j < nblk; j += nctas) {
+        const int blk = (j + tp.pg_rot) % nblk;
+        const int row0 = blk * PG_ROWS;
+        const int nrows = min(PG_ROWS, N - row0);
+        const int total = nrows * tp.pg_row_u4;
+        for (int i0 = ct; i0 < total; i0 += 16 * 128) {
+          uint4 v[16];                                      // 16 independent 16-byte peer loads in flight per thread
+          long off[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int i = i0 + u * 128;
+            off[u] = -1;
+            if (i < total) {
+              const int r = i / tp.pg_row_u4;
+              const int row = row0 + r;
+              const int own = pg_owner(tp, row);
+              if (own != tp.rank) {
+                off[u] = (long)row * tp.pg_ld_u4 + (i - r * tp.pg_row_u4);
+                v[u] = tp.pg_src[own][off[u]];
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u)
+            if (off[u] >= 0) tp.pg_dst[off[u]] = v[u];
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // the four copier warps only
+        if (ct == 0) release_peer_flag(tp.pg_flags + blk, tp.seq);
       }
     }
   } else if (TP == 2 && warp >= 6) {
@@ -546,7 +615,7 @@ int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& t
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  kern<<<grid, TP == 2 ? NUM_THREADS + 128 : NUM_THREADS, L::TOTAL, stream>>>(
+  kern<<<grid, TP >= 2 ? NUM_THREADS + 128 : NUM_THREADS, L::TOTAL, stream>>>(
       ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr, 8, nullptr, nullptr, status, tp);
   return (int)cudaGetLastError();
 }
@@ -792,6 +861,75 @@ extern "C" int otb_tp_ag_gemm(void* const* a_full, void* const* ag_flags, int ra
   if (b_mn) { if (bf16_out) { OTB_AG(128, 6, true, EPI_BF16) } OTB_AG(128, 6, true, EPI_F32) }
   if (bf16_out) { OTB_AG(128, 6, false, EPI_BF16) } OTB_AG(128, 6, false, EPI_F32)
 #undef OTB_AG
+}
+
+// Parameter all-gather fused into the consuming GEMM:  C[M,N] = A[M,K] * B[N,K]^T (+ R), where B is a weight (or up to
+// three row-concatenated weights, e.g. wq|wk|wv) whose rows are spread over P processes.
+//   b_bufs[p]: row 0 of B inside process p's weight buffer (peer pointers; all buffers have the same layout, leading
+//   dimension ldb). In b_bufs[rank], the local buffer, only the rows this process owns need to be current: the call pulls
+//   every other row from its owner (plain peer loads issued by four extra warps of the GEMM's CTAs, 128-row blocks in ring
+//   order starting at this process's own rows), marks the block in `flags` (local, ceil(N/128) words) with `seq`, and the
+//   TMA producer of a tile waits for the blocks of its B rows only. Afterwards the local buffer holds all of B, so later
+//   GEMMs of the same step (other micro-batches, the backward pass) are plain GEMMs on b_bufs[rank].
+//   seg_begin[0..nseg-1] / rows_per_owner[0..nseg-1]: first row of each concatenated weight and how many of its rows
+//   each process holds (process p: rows [p*rpo, (p+1)*rpo), the last one to the end). seq: unique per (weight, update),
+//   never 0 after the flags were zeroed. The owners' rows must be final before the launch (the barrier after the
+//   optimizer step) and stay so until every process has pulled (the next optimizer step is behind the next reduction).
+//   epi: 0 bf16, 1 fp32, 3 bf16 + residual. Same bits as otb_gemm_bf16 on a complete B. Never allocates.
+extern "C" int otb_pg_gemm(const void* A, void* const* b_bufs, void* flags, int rank, int P, unsigned seq, void* C, const void* R,
+                           int M, int N, int K, long lda, long ldb, long ldc, long ldr, const int* seg_begin,
+                           const int* rows_per_owner, int nseg, int epi, uint32_t* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (P < 1 || P > 8 || rank < 0 || rank >= P || nseg < 1 || nseg > 3 || seq == 0) return -2;
+  if (epi != EPI_BF16 && epi != EPI_F32 && epi != EPI_BF16_RES) return -3;
+  const void* B = b_bufs[rank];
+  if ((lda & 7) || (ldb & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(C) & 15)) return -2;
+  for (int p = 0; p < P; ++p)
+    if (!b_bufs[p] || (reinterpret_cast<uintptr_t>(b_bufs[p]) & 15)) return -2;
+  for (int j = 0; j < nseg; ++j)
+    if (rows_per_owner[j] < 1 || seg_begin[j] < 0 || seg_begin[j] >= N || (j && seg_begin[j] <= seg_begin[j - 1])) return -2;
+  if (seg_begin[0] != 0) return -2;
+  const bool bf16_out = epi != EPI_F32;
+  if ((bf16_out && (ldc & 7)) || (!bf16_out && (ldc & 3)) || (epi == EPI_BF16_RES && (!R || (ldr & 7)))) return -2;
+  const int sms = otb_sm_count();
+  const int BN = N >= 256 ? 256 : 128;
+  const long tiles = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sms ? (int)tiles : sms;
+  constexpr int BK = BK_BYTES / 2;
+  CUtensorMap ta, tb, tc;
+  CUresult r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  r = bf16_out ? encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32, 2)
+               : encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, 4);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  TpArgs tp{};
+  tp.rank = rank; tp.P = P; tp.seq = seq; tp.gemm_ctas = grid;
+  for (int p = 0; p < P; ++p) tp.pg_src[p] = reinterpret_cast<const uint4*>(b_bufs[p]);
+  tp.pg_dst = reinterpret_cast<uint4*>(b_bufs[rank]);
+  tp.pg_flags = reinterpret_cast<uint32_t*>(flags);
+  tp.pg_nseg = nseg;
+  for (int j = 0; j < nseg; ++j) { tp.pg_seg_begin[j] = seg_begin[j]; tp.pg_rows_per_owner[j] = rows_per_owner[j]; }
+  tp.pg_seg_begin[nseg] = N;
+  tp.pg_row_u4 = K / 8;
+  tp.pg_ld_u4 = (int)(ldb / 8);
+  // start the tile order at the first block of this process's rows of the first weight (a multiple of BN / 128 blocks)
+  const int nblk = (N + PG_ROWS - 1) / PG_ROWS;
+  int rot = (int)(((long)rank * rows_per_owner[0]) / PG_ROWS);
+  rot -= rot % (BN / PG_ROWS);
+  tp.pg_rot = rot < nblk ? rot : 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define OTB_PG(BN_, ST_, EPI_) return launch_tp<BN_, ST_, false, EPI_, 3>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, grid, tp, s);
+  if (BN == 256) {
+    if (epi == EPI_BF16) { OTB_PG(256, 4, EPI_BF16) }
+    if (epi == EPI_F32) { OTB_PG(256, 4, EPI_F32) }
+    OTB_PG(256, 4, EPI_BF16_RES)
+  }
+  if (epi == EPI_BF16) { OTB_PG(128, 6, EPI_BF16) }
+  if (epi == EPI_F32) { OTB_PG(128, 6, EPI_F32) }
+  OTB_PG(128, 6, EPI_BF16_RES)
+#undef OTB_PG
 }
 
 extern "C" int otb_tp_chain_bn(int N) { return tp_chain_bn(N); }

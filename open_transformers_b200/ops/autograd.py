@@ -25,12 +25,15 @@ class GradSlot:
     read half of the accumulate, and sets ``written``. Whoever owns the slots zeroes those still unwritten after the
     backward pass (parameters that received no gradient)."""
 
-    __slots__ = ("buf", "fresh", "written")
+    __slots__ = ("buf", "fresh", "written", "gather")
 
     def __init__(self, buf: torch.Tensor | None = None):
         self.buf = buf
         self.fresh = False
         self.written = False
+        # parallel/param_gather.py::GatheredWeight when the weight's rows are pulled from their owners by the first
+        # forward GEMM after an update (``run.param_sharding: gather``), else None
+        self.gather = None
 
     def take(self) -> bool:
         """True if the caller must overwrite (store); later callers accumulate."""
@@ -106,7 +109,11 @@ class LinearFn(Function):
         x2 = _flat2d(x)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        if residual is not None:
+        pull = slot.gather if slot is not None else None
+        if pull is not None and pull.pending():
+            # first use of this weight since its owners updated it: the GEMM gathers the missing rows itself
+            y = pull.gemm(x2, _flat2d(residual) if residual is not None else None)
+        elif residual is not None:
             y = K.gemm(x2, w, epi=K.EPI_RESIDUAL, residual=_flat2d(residual))
         else:
             y = K.gemm(x2, w)

@@ -315,11 +315,104 @@ class TrainEngine:
         self.names = lay.names
         self.slots = [GradSlot() for _ in named]
         self._install_views()
+        self._setup_param_gather()
         self.refresh_compute_weights()
         # buffers (RoPE tables) follow the device
         for mod in self.model.modules():
             for bname, b in list(mod.named_buffers(recurse=False)):
                 mod._buffers[bname] = b.to(self.device)
+
+    # ------------------------------------------------------- parameter all-gather inside the consuming GEMM
+    def _setup_param_gather(self) -> None:
+        """``run.param_sharding: gather`` (or OTB_PARAM_SHARDING=gather): the AdamW kernel keeps the new bf16 rows of the
+        projection weights on the owner, and the first forward GEMM after an update pulls the other owners' rows itself
+        (parallel/param_gather.py; kernel otb_pg_gemm). Embedding, norm gains and any weight whose rows are not split
+        evenly over the processes are still pushed to every GPU by the AdamW kernel."""
+        self._pg = None
+        mode = os.environ.get("OTB_PARAM_SHARDING") or self.cfg.run.param_sharding
+        if mode != "gather" or self.world == 1:  # one process owns every row: nothing to gather (the replay of such a run)
+            return
+        if not (self.is_cuda and self.peer and self.sharded and self.mixed and self.tp == 1) or self.cfg.model.qat.enabled or self.muon_params:
+            raise ValueError("run.param_sharding=gather needs GPUs of one machine with sharded ownership over peer memory, bf16 compute "
+                             "weights, AdamW, no tensor parallelism and no quantisation-aware training")
+        from ..models.modules.core import Linear
+        from ..parallel.param_gather import ROWS_PER_FLAG, GatheredWeight, uniform_rows_per_owner
+
+        lay = self.layout
+        modules = dict(self.model.named_modules())
+        idx = {n: i for i, n in enumerate(lay.names)}
+
+        def rows_per_owner(i: int) -> int | None:
+            shape = lay.shapes[i]
+            row = lay.numels[i] // shape[0]
+            ranges = []
+            for slo, shi in self._owner_ranges:
+                segs = sorted((sg for sg in lay.segments[slo:shi] if sg.param == i), key=lambda g: g.start)
+                if not segs:
+                    ranges.append((0, 0))
+                    continue
+                if any(a.start + a.length != b.start for a, b in zip(segs, segs[1:])):
+                    return None
+                lo = (segs[0].start - lay.offsets[i]) // row
+                ranges.append((lo, lo + sum(g.length for g in segs) // row))
+            return uniform_rows_per_owner(ranges, shape[0])
+
+        groups = []   # (slot, parameter indices, element offset of row 0, rows, cols)
+        fused = set()
+        for slot, o0, rows, cols, members in self._fused:
+            groups.append((slot, tuple(members), o0, rows, cols))
+            fused.update(members)
+        for name, i in idx.items():
+            mod_name, _, attr = name.rpartition(".")
+            mod = modules[mod_name]
+            if i in fused or attr != "weight" or type(mod) is not Linear or len(lay.shapes[i]) != 2:
+                continue
+            groups.append((self.slots[i], (i,), lay.offsets[i], lay.shapes[i][0], lay.shapes[i][1]))
+        weights, pulled, blocks = [], set(), 0
+        plans = []
+        for slot, members, o0, rows, cols in groups:
+            rpo = [rows_per_owner(i) for i in members]
+            if any(r is None for r in rpo) or cols % 8 or (2 * o0) % 16:
+                continue
+            begins, at = [], 0
+            for i in members:
+                begins.append(at)
+                at += lay.shapes[i][0]
+            plans.append((slot, members, o0, rows, cols, begins, rpo, blocks))
+            blocks += -(-rows // ROWS_PER_FLAG)
+        self._pg_flags = torch.zeros(max(blocks, 1), dtype=torch.int32, device=self.device)
+        for slot, members, o0, rows, cols, begins, rpo, b0 in plans:
+            local = self.compute[o0:o0 + rows * cols].view(rows, cols)
+            gw = GatheredWeight(local, [p + 2 * o0 for p in self.buf_compute.ptrs], self.rank, begins, rpo,
+                                self._pg_flags[b0:b0 + -(-rows // ROWS_PER_FLAG)])
+            slot.gather = gw
+            weights.append(gw)
+            pulled.update(members)
+        # the owned chunks, split into those of pulled weights (stored locally by the AdamW kernel) and the rest (pushed)
+        own = np.arange(self.chunk_lo, self.chunk_hi, dtype=np.int64)
+        chunk_param = np.zeros(len(lay.chunk_start), dtype=np.int64)
+        for sg in lay.segments:
+            chunk_param[sg.first_chunk:sg.first_chunk + sg.n_chunks] = sg.param
+        is_pull = np.isin(chunk_param[own], np.fromiter(pulled, dtype=np.int64, count=len(pulled)))
+        tables = {}
+        for key, ids in (("pull", own[is_pull]), ("push", own[~is_pull])):
+            t = torch.from_numpy(ids).to(self.device)
+            tables[key] = (self.chunk_start[t].contiguous(), self.chunk_len[t].contiguous(), self.chunk_group[t].contiguous(),
+                           None if self.chunk_state_start is None else self.chunk_state_start[t].contiguous(), int(len(ids)))
+        self._pg = {"weights": weights, "tables": tables, "epoch": 0, "pulled_params": sorted(pulled)}
+
+    def complete_compute_weights(self) -> None:
+        """Gather mode: make every GPU's bf16 weights whole NOW (each owner pushes the rows it kept back), for readers
+        that are not a forward GEMM - weight statistics, an evaluation outside the step. Every process calls it."""
+        if self._pg is None or not any(g.pending() for g in self._pg["weights"]):
+            return
+        cs, cl, _cg, _sst, cnt = self._pg["tables"]["pull"]
+        if cnt:
+            check(self.lib.otb_push_cast(P(cs), P(cl), I(cnt), P(self.master), _ptr_array(self.buf_compute.ptrs), I(len(self.buf_compute.ptrs)),
+                                         I(1), stream_ptr()), "push_cast")
+        self._stream_barrier()
+        for g in self._pg["weights"]:
+            g.mark_complete()
 
     # ------------------------------------------------------- gradient reduction under the backward pass
     def _setup_overlap(self) -> None:
@@ -723,6 +816,9 @@ class TrainEngine:
     def refresh_compute_weights(self) -> None:
         """compute weights <- master (all segments, local only); used at start-up and after a load."""
         K.weight_epoch = (K.weight_epoch or 0) + 1
+        if getattr(self, "_pg", None) is not None:  # every process holds the whole master here: nothing left to pull
+            for g in self._pg["weights"]:
+                g.mark_complete()
         if not self.mixed:
             return
         arr = _ptr_array([self.compute.data_ptr()])
@@ -1104,12 +1200,23 @@ class TrainEngine:
         sst = None
         if self.chunk_state_start is not None and not self.muon_params:
             sst = self.chunk_state_start[lo:]  # gradient and moments sit in the packed buffers of the owned segments
-        if self.is_cuda:
-            check(self.lib.otb_adamw_push_ex(hyper, P(cs), P(sst), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
-                                             _ptr_array(dsts), I(len(dsts)), I(self.mixed), stream_ptr()), "adamw_push")
-        else:
-            check(self.lib.otb_cpu_adamw_push_ex(hyper, P(cs), P(sst), P(cl), P(cg), I(cnt), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
-                                                 _ptr_array(dsts), I(len(dsts)), I(self.mixed)), "adamw_push")
+        launches = [(cs, sst, cl, cg, cnt, dsts)]
+        if self._pg is not None:
+            # gather mode: the rows of the projection weights stay on their owner (the consuming GEMM pulls them), the
+            # rest (embedding, gains) goes to every GPU as before
+            own = [self.compute.data_ptr()]
+            launches = [(t[0], t[3], t[1], t[2], t[4], d) for t, d in ((self._pg["tables"]["pull"], own), (self._pg["tables"]["push"], dsts))]
+        for cs_, sst_, cl_, cg_, cnt_, dsts_ in launches:
+            if self.is_cuda:
+                check(self.lib.otb_adamw_push_ex(hyper, P(cs_), P(sst_), P(cl_), P(cg_), I(cnt_), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                                 _ptr_array(dsts_), I(len(dsts_)), I(self.mixed), stream_ptr()), "adamw_push")
+            else:
+                check(self.lib.otb_cpu_adamw_push_ex(hyper, P(cs_), P(sst_), P(cl_), P(cg_), I(cnt_), P(self.master), P(self.grad_red), P(self.m1), P(self.m2),
+                                                     _ptr_array(dsts_), I(len(dsts_)), I(self.mixed)), "adamw_push")
+        if self._pg is not None:
+            self._pg["epoch"] += 1
+            for g in self._pg["weights"]:
+                g.epoch = self._pg["epoch"]
         if self.collective:
             self._share_updated_weights()
         self._tick("opt")

@@ -293,6 +293,9 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             wall_ms = (time.perf_counter() - t_step) * 1e3
             result["losses"].append(loss_mean)
             phases = engine.phase_report()  # empty unless PRETRAIN_CUDA_EVENT_TIMING=1
+            gl = train_cfg.grad_norm_log
+            if gl.every_n_steps > 0 and step % gl.every_n_steps == 0 and gl.weight_stats_every_n_steps > 0 and step % gl.weight_stats_every_n_steps == 0:
+                engine.complete_compute_weights()  # the statistics read whole weights (a collective in gather mode, else nothing)
             if rank == 0:
                 tps = plan.tokens_this_step / (wall_ms / 1e3)
                 metrics.log({**phases, "step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_sum / max(n_mb, 1), "lr": lr,

@@ -40,7 +40,8 @@ def main():
     status = kernel_status(dev)
     if rank == 0:
         json.dump({"hashes": out, "status": status, "overlapped_steps": 0 if eng._ov is None else eng._ov["epoch"], "resident": eng.resident_bytes(),
-                   "packed_state": bool(eng._packed_state)}, open(os.environ["OTB_TEST_OUT"], "w"))
+                   "packed_state": bool(eng._packed_state),
+                   "gather_calls": 0 if eng._pg is None else sum(g.calls for g in eng._pg["weights"])}, open(os.environ["OTB_TEST_OUT"], "w"))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

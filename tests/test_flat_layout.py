@@ -56,3 +56,13 @@ def test_shard_rows_is_the_ceil_split_with_empty_tails():
     assert [shard_rows(10, 4, s) for s in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 10)]
     assert [shard_rows(3, 8, s) for s in range(8)] == [(0, 1), (1, 2), (2, 3)] + [(3, 3)] * 5
     assert [shard_rows(1, 2, s) for s in range(2)] == [(0, 1), (1, 1)]
+
+
+def test_rows_per_owner_must_describe_the_distribution():
+    from open_transformers_b200.parallel.param_gather import uniform_rows_per_owner
+
+    assert uniform_rows_per_owner([(0, 256), (256, 512), (512, 768), (768, 1024)], 1024) == 256
+    assert uniform_rows_per_owner([(0, 26), (26, 52), (52, 78), (78, 100)], 100) == 26          # the last owner takes the rest
+    assert uniform_rows_per_owner([(0, 50), (50, 100), (0, 0), (0, 0)], 100) == 50              # fewer rows than owners
+    assert uniform_rows_per_owner([(0, 30), (30, 50), (50, 100)], 100) is None
+    assert uniform_rows_per_owner([(10, 60), (60, 100)], 100) is None
