@@ -372,3 +372,39 @@ def test_amsgrad_variant_of_the_adamw_kernel_follows_torch():
     assert torch.allclose(a.state[ours]["max_exp_avg_sq"], b.state[ref]["max_exp_avg_sq"], rtol=1e-6, atol=1e-12)
     assert bool((a.state[ours]["max_exp_avg_sq"] >= a.state[ours]["exp_avg_sq"]).all()) and not torch.equal(ours, plain)
     assert "max_exp_avg_sq" not in c.state[plain]
+
+
+def test_linear_forward_hands_the_first_use_after_an_update_to_the_gathering_gemm():
+    """the hook of ``run.param_sharding: gather`` in the linear layer's forward: while the weight's descriptor reports rows
+    still to pull, the forward goes through it (once); afterwards, and in the backward pass, the plain GEMM runs"""
+    import torch
+
+    from open_transformers_b200.ops import autograd as A
+    from open_transformers_b200.ops import functional as K
+
+    class FakeGather:
+        def __init__(self, w):
+            self.w, self.todo, self.calls = w, True, []
+
+        def pending(self):
+            return self.todo
+
+        def gemm(self, x, residual=None):
+            self.calls.append(residual is not None)
+            self.todo = False
+            return K.gemm(x, self.w, epi=K.EPI_RESIDUAL, residual=residual) if residual is not None else K.gemm(x, self.w)
+
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(48, 32, generator=g).requires_grad_()
+    x = torch.randn(2, 8, 32, generator=g).requires_grad_()
+    res = torch.randn(2, 8, 48, generator=g)
+    slot = A.GradSlot(torch.zeros(48, 32))
+    slot.fresh = True
+    plain = A.linear(x, w, None, None, res)
+    slot.gather = FakeGather(w.detach())
+    first = A.linear(x, w, w.detach(), slot, res)
+    second = A.linear(x, w, w.detach(), slot, res)
+    assert slot.gather.calls == [True] and torch.equal(first, plain) and torch.equal(second, plain)
+    first.sum().backward()
+    assert torch.equal(slot.buf, torch.einsum("btn,btk->nk", torch.ones_like(res), x.detach())) or torch.allclose(
+        slot.buf, torch.einsum("btn,btk->nk", torch.ones_like(res), x.detach()), atol=1e-5)
