@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from open_transformers_b200.ops import functional as K
 from open_transformers_b200.parallel.flat import PeerBuffer
-from open_transformers_b200.parallel.param_gather import GatheredWeight
+from open_transformers_b200.parallel.param_gather import GatheredWeight, flag_words
 
 NVLINK_PEER_GBS = 770.0
 SHAPES = [("qkv", [2048, 512, 512], 2048), ("attn_out", [2048], 2048), ("gate_up", [11264], 2048), ("down", [2048], 5632),
@@ -85,7 +85,7 @@ def main():
             for b in bufs:
                 b.copy_(W)
         local_w.copy_(W)
-        flags = torch.zeros(-(-N // 128), dtype=torch.int32, device=dev)
+        flags = torch.zeros(flag_words(N), dtype=torch.int32, device=dev)
         gw = GatheredWeight(local_w, ptrs, me, seg_begin, rpo, flags)
         state = {"i": 0}
 
@@ -108,13 +108,16 @@ def main():
                 dist.all_gather_into_tensor(full, shard)
             K.gemm(xs[state["i"] % 3], full[:N])
 
-        t_plain, t_fused = timed(plain, a.iters, world), timed(fused, a.iters, world)
+        # fused first, plain before and after it: a difference between the two plain figures is clock drift under the power cap
+        t_plain0 = timed(plain, a.iters, world)
+        t_fused = timed(fused, a.iters, world)
+        t_plain = timed(plain, a.iters, world)
         t_lib = timed(library, a.iters, world) if world > 1 else None
         ok = bool(torch.equal(gw.gemm(xs[0]).view(torch.int16), K.gemm(xs[0], W).view(torch.int16)))
         flops = 2.0 * M * N * Kd
         pulled = 2.0 * N * Kd * (P - 1) / P
         roof_ms = max(flops / (a.gemm_tflops * 1e12), pulled / (NVLINK_PEER_GBS * 1e9)) * 1e3
-        rows.append({"shape": name, "M": M, "N": N, "K": Kd, "owners": P, "plain_ms": t_plain, "fused_ms": t_fused, "allgather_gemm_ms": t_lib,
+        rows.append({"shape": name, "M": M, "N": N, "K": Kd, "owners": P, "plain_ms": t_plain, "plain_before_ms": t_plain0, "fused_ms": t_fused, "allgather_gemm_ms": t_lib,
                      "pulled_mb": pulled / 1e6, "roofline_ms": roof_ms, "fused_of_roofline": roof_ms / t_fused, "same_bits": ok})
         del gw, local_w, W, xs, full, shard
         if world > 1:

@@ -79,14 +79,15 @@ struct TpArgs {
   // from their buffers (plain peer loads) into the local one by four extra warps of the GEMM's own CTAs.
   const uint4* pg_src[8];      // row 0 of this weight in every process's buffer ([rank] is the local buffer)
   uint4* pg_dst;               // row 0 of this weight in the local buffer (what tmB reads)
-  uint32_t* pg_flags;          // local: one word per 128-row block of B; takes `seq` once the block is complete here
+  uint32_t* pg_flags;          // local counters: word [tn] counts the copy units of B tile tn (BN rows) that have landed,
+                               // word [tiles_n] all units of the weight; they only grow: after call number `seq` of this
+                               // weight a complete tile reads seq x (its units)
   int pg_seg_begin[4];         // B is up to 3 row-concatenated parameters: first row of each, then N
   int pg_rows_per_owner[3];    // rows of parameter j per process (process p holds rows [p*rpo, (p+1)*rpo) of it)
-  int pg_nseg, pg_rot;         // number of parameters; 128-row block the tile order starts from (own rows first)
+  int pg_nseg, pg_rot;         // number of parameters; B tile the tile order starts from (this process's rows first)
+  int pg_unit_rows;            // rows per copy unit (divides 128): small weights are cut finer so that every CTA copies
   int pg_row_u4, pg_ld_u4;     // 16-byte units per row that are copied / between rows
 };
-
-constexpr int PG_ROWS = 128;   // rows of B per parameter-gather flag
 
 // Which process holds row `row` of a gathered weight.
 __device__ __forceinline__ int pg_owner(const TpArgs& tp, int row) {
@@ -105,6 +106,29 @@ __device__ int g_cta_rotation = 0;
 // How long a kernel of this file waits for a peer's flag before it gives up, sets its status word and returns
 // (nanoseconds of %globaltimer; otb_set_peer_wait_ns changes it for the current device).
 __device__ unsigned long long g_peer_wait_ns = 2000000000ull;
+
+// Counter words of the parameter gather: relaxed/acquire at GPU scope (copiers and consumers are CTAs of one launch).
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_count(const uint32_t* word, uint32_t target, volatile uint32_t* abort_flag) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t i = 0;; ++i) {
+    if (ld_acquire_gpu(word) == target) return true;
+    if (*abort_flag) return false;
+    if ((i & 63u) == 63u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > g_peer_wait_ns) break;
+    }
+    __nanosleep(100);
+  }
+  *abort_flag = 1;
+  return false;
+}
 
 // Bounded wait for a flag written by a peer GPU (release at system scope on their side).
 __device__ __forceinline__ bool wait_peer_flag(const uint32_t* flag, uint32_t seq, volatile uint32_t* abort_flag) {
@@ -239,7 +263,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tm = first_m + r % gsz;
     tn = r / gsz;
     if constexpr (TP == 1) tm = (tm + tp.rank * tp.tiles_per_shard) % tiles_m;  // own rows first, then the peers' in ring order
-    if constexpr (TP == 3) tn = (tn + tp.pg_rot / (BN / PG_ROWS)) % tiles_n;      // weight rows of this process first
+    if constexpr (TP == 3) tn = (tn + tp.pg_rot) % tiles_n;                        // weight rows of this process first
   };
 
   if (warp == 0) {
@@ -249,6 +273,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
+      [[maybe_unused]] bool pg_all = false;
       for (int t = cta; t < num_tiles && ok; t += nctas) {
         int tm, tn;
         tile_coord(t, tm, tn);
@@ -260,15 +285,19 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         if constexpr (TP == 3) {
-          // the rows of this B tile must be complete in the local buffer: one flag per 128-row block, written by the
-          // copier warps of whichever CTA pulled the block
-          for (int b = 0; b < BN / PG_ROWS && ok; ++b) {
-            const int blk = tn * (BN / PG_ROWS) + b;
-            if (blk * PG_ROWS >= N) break;
-            if (!wait_peer_flag(tp.pg_flags + blk, tp.seq, abort_flag)) ok = false;
+          // the rows of this B tile must be complete in the local buffer. Until the whole weight has arrived that is one
+          // look at the weight's counter and, if it is not there yet, a wait for the tile's own counter; afterwards nothing.
+          if (!pg_all) {
+            const int units_row = (N + tp.pg_unit_rows - 1) / tp.pg_unit_rows;
+            if (ld_acquire_gpu(tp.pg_flags + tiles_n) == tp.seq * (uint32_t)units_row) {
+              pg_all = true;
+            } else {
+              const int rows_here = min(BN, N - tn * BN);
+              const uint32_t units_here = (uint32_t)((rows_here + tp.pg_unit_rows - 1) / tp.pg_unit_rows);
+              if (!wait_count(tp.pg_flags + tn, tp.seq * units_here, abort_flag)) { ok = false; break; }
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");  // the copiers' generic stores, then our TMA (async proxy) reads
           }
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");  // the copiers' generic stores, then our TMA (async proxy) reads
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -331,36 +360,52 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------ parameter gather: pull the other processes' rows of B into the local buffer
     if constexpr (TP == 3) {
       const int ct = threadIdx.x - 6 * 32;                  // 0..127 among the copier threads of this CTA
-      const int nblk = (N + PG_ROWS - 1) / PG_ROWS;
-      for (int j = cta; j < nblk; j += nctas) {
-        const int blk = (j + tp.pg_rot) % nblk;
-        const int row0 = blk * PG_ROWS;
-        const int nrows = min(PG_ROWS, N - row0);
-        const int total = nrows * tp.pg_row_u4;
-        for (int i0 = ct; i0 < total; i0 += 16 * 128) {
-          uint4 v[16];                                      // 16 independent 16-byte peer loads in flight per thread
-          long off[16];
+      const int ur = tp.pg_unit_rows;
+      const int units = (N + ur - 1) / ur;
+      const int rot_units = tp.pg_rot * (BN / ur);
+      for (int j = cta; j < units; j += nctas) {
+        const int unit = (j + rot_units) % units;           // the order in which the tiles want them
+        const int row0 = unit * ur;
+        const int row1 = min(N, row0 + ur);
+        // walk the unit in runs of rows that have one owner; runs of this process's own rows cost nothing
+        for (int r = row0; r < row1;) {
+          int sj = 0;
+          if (tp.pg_nseg > 1 && r >= tp.pg_seg_begin[1]) sj = 1;
+          if (tp.pg_nseg > 2 && r >= tp.pg_seg_begin[2]) sj = 2;
+          const int sb = tp.pg_seg_begin[sj], se = tp.pg_seg_begin[sj + 1], rpo = tp.pg_rows_per_owner[sj];
+          int own = (r - sb) / rpo;
+          if (own > tp.P - 1) own = tp.P - 1;
+          int run_end = own == tp.P - 1 ? se : min(se, sb + (own + 1) * rpo);
+          run_end = min(run_end, row1);
+          if (own != tp.rank) {
+            const bool flat = tp.pg_ld_u4 == tp.pg_row_u4;   // rows adjacent in memory: the run is one span
+            const int spans = flat ? 1 : run_end - r;
+            const int span_u4 = flat ? (run_end - r) * tp.pg_row_u4 : tp.pg_row_u4;
+            for (int sp = 0; sp < spans; ++sp) {
+              const long base = (long)(r + sp) * tp.pg_ld_u4;
+              const uint4* __restrict__ src = tp.pg_src[own] + base;
+              uint4* __restrict__ dst = tp.pg_dst + base;
+              for (int i0 = ct; i0 < span_u4; i0 += 32 * 128) {
+                // 32 independent 16-byte peer loads in flight per thread (64 KB per CTA): a loaded link answers in
+                // microseconds, so the bytes in flight decide the rate
+                uint4 v[32];
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int i = i0 + u * 128;
-            off[u] = -1;
-            if (i < total) {
-              const int r = i / tp.pg_row_u4;
-              const int row = row0 + r;
-              const int own = pg_owner(tp, row);
-              if (own != tp.rank) {
-                off[u] = (long)row * tp.pg_ld_u4 + (i - r * tp.pg_row_u4);
-                v[u] = tp.pg_src[own][off[u]];
+                for (int u = 0; u < 32; ++u)
+                  if (i0 + u * 128 < span_u4) v[u] = src[i0 + u * 128];
+#pragma unroll
+                for (int u = 0; u < 32; ++u)
+                  if (i0 + u * 128 < span_u4) dst[i0 + u * 128] = v[u];
               }
             }
           }
-#pragma unroll
-          for (int u = 0; u < 16; ++u)
-            if (off[u] >= 0) tp.pg_dst[off[u]] = v[u];
+          r = run_end;
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");     // the four copier warps only
-        if (ct == 0) release_peer_flag(tp.pg_flags + blk, tp.seq);
+        if (ct == 0) {                                      // (fence, then relaxed adds: a release of the unit's rows)
+          atomicAdd(tp.pg_flags + row0 / BN, 1u);
+          atomicAdd(tp.pg_flags + tiles_n, 1u);
+        }
       }
     }
   } else if (TP == 2 && warp >= 6) {
@@ -606,7 +651,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 
 template <int BN, int STAGES, bool B_MN, int EPI, int TP>
 int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, const void* R, int M, int N, int K, long ldc,
-              long ldr, uint32_t* status, int grid, const TpArgs& tp, cudaStream_t stream) {
+              long ldr, uint32_t* status, int grid, const TpArgs& tp, cudaStream_t stream, int group_m = 8) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_tc05_kernel<BN, STAGES, false, B_MN, EPI, false, TP, TpArgs>;
   static bool attr_done = false;
@@ -616,7 +661,7 @@ int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& t
     attr_done = true;
   }
   kern<<<grid, TP >= 2 ? NUM_THREADS + 128 : NUM_THREADS, L::TOTAL, stream>>>(
-      ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr, 8, nullptr, nullptr, status, tp);
+      ta, tb, tc, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, ldr, group_m, nullptr, nullptr, status, tp);
   return (int)cudaGetLastError();
 }
 
@@ -868,14 +913,17 @@ extern "C" int otb_tp_ag_gemm(void* const* a_full, void* const* ag_flags, int ra
 //   b_bufs[p]: row 0 of B inside process p's weight buffer (peer pointers; all buffers have the same layout, leading
 //   dimension ldb). In b_bufs[rank], the local buffer, only the rows this process owns need to be current: the call pulls
 //   every other row from its owner (plain peer loads issued by four extra warps of the GEMM's CTAs, 128-row blocks in ring
-//   order starting at this process's own rows), marks the block in `flags` (local, ceil(N/128) words) with `seq`, and the
-//   TMA producer of a tile waits for the blocks of its B rows only. Afterwards the local buffer holds all of B, so later
-//   GEMMs of the same step (other micro-batches, the backward pass) are plain GEMMs on b_bufs[rank].
+//   order starting at this process's own rows) and counts every finished copy unit in `flags` (local, zeroed once:
+//   otb_pg_flag_words(N) words, one counter per B tile and one for the weight), and the TMA producer of a tile waits for
+//   the counter of its own B rows only. Afterwards the local buffer holds all of B, so later GEMMs of the same step (other
+//   micro-batches, the backward pass) are plain GEMMs on b_bufs[rank].
 //   seg_begin[0..nseg-1] / rows_per_owner[0..nseg-1]: first row of each concatenated weight and how many of its rows
-//   each process holds (process p: rows [p*rpo, (p+1)*rpo), the last one to the end). seq: unique per (weight, update),
-//   never 0 after the flags were zeroed. The owners' rows must be final before the launch (the barrier after the
+//   each process holds (process p: rows [p*rpo, (p+1)*rpo), the last one to the end). seq: how many calls this weight's
+//   `flags` have seen, this one included (1, 2, 3, ...): the counters only grow. The owners' rows must be final before the launch (the barrier after the
 //   optimizer step) and stay so until every process has pulled (the next optimizer step is behind the next reduction).
 //   epi: 0 bf16, 1 fp32, 3 bf16 + residual. Same bits as otb_gemm_bf16 on a complete B. Never allocates.
+extern "C" int otb_pg_flag_words(int N) { return (N + (N >= 256 ? 256 : 128) - 1) / (N >= 256 ? 256 : 128) + 1; }
+
 extern "C" int otb_pg_gemm(const void* A, void* const* b_bufs, void* flags, int rank, int P, unsigned seq, void* C, const void* R,
                            int M, int N, int K, long lda, long ldb, long ldc, long ldr, const int* seg_begin,
                            const int* rows_per_owner, int nseg, int epi, uint32_t* status, void* stream) {
@@ -914,13 +962,22 @@ extern "C" int otb_pg_gemm(const void* A, void* const* b_bufs, void* flags, int 
   tp.pg_seg_begin[nseg] = N;
   tp.pg_row_u4 = K / 8;
   tp.pg_ld_u4 = (int)(ldb / 8);
-  // start the tile order at the first block of this process's rows of the first weight (a multiple of BN / 128 blocks)
-  const int nblk = (N + PG_ROWS - 1) / PG_ROWS;
-  int rot = (int)(((long)rank * rows_per_owner[0]) / PG_ROWS);
-  rot -= rot % (BN / PG_ROWS);
-  tp.pg_rot = rot < nblk ? rot : 0;
+  // copy units: cut small weights finer, so that the copier warps of every CTA pull something (a unit is what one CTA's
+  // four copier warps fetch before they count it in); the cut depends on N only, so the counters of a weight advance by
+  // the same amounts in every call
+  tp.pg_unit_rows = N >= 16384 ? 128 : (N >= 8192 ? 64 : 16);
+  // start the tile order at the tile that holds the first of this process's rows of the first weight
+  const int tiles_n = (N + BN - 1) / BN;
+  const int rot = (int)(((long)rank * rows_per_owner[0]) / BN);
+  tp.pg_rot = rot < tiles_n ? rot : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-#define OTB_PG(BN_, ST_, EPI_) return launch_tp<BN_, ST_, false, EPI_, 3>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, grid, tp, s);
+  // Tile order: groups of row tiles whose A rows make about 16 MB (32 row tiles at K = 2048) sweep all column tiles. Wider
+  // than the plain GEMM's 8, so that a sweep stays on this process's own columns of B longer while the others arrive;
+  // much wider costs more in L2 misses on A than it hides (measured: 128 row tiles 3-9 % slower, 32 within 1 %).
+  int group_m = (int)((16L << 20) / ((long)K * 2 * BM));
+  if (group_m < 8) group_m = 8;
+  if (group_m > (M + BM - 1) / BM) group_m = (M + BM - 1) / BM;
+#define OTB_PG(BN_, ST_, EPI_) return launch_tp<BN_, ST_, false, EPI_, 3>(ta, tb, tc, C, R, M, N, K, ldc, ldr, status, grid, tp, s, group_m);
   if (BN == 256) {
     if (epi == EPI_BF16) { OTB_PG(256, 4, EPI_BF16) }
     if (epi == EPI_F32) { OTB_PG(256, 4, EPI_F32) }

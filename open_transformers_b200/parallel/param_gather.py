@@ -3,9 +3,9 @@
 With sharded ownership every process updates the rows of the weights it owns. In the default mode the AdamW kernel
 stores the new bf16 rows into every GPU's weight buffer straight away - an NVLink-bound tail after the optimizer step.
 In gather mode it stores them locally only, and the FIRST GEMM that multiplies by a weight after an update pulls the rows
-of the other owners itself: four extra warps in each CTA of ``otb_pg_gemm`` copy 128-row blocks from the owners' buffers
-(plain peer loads) into the local buffer, mark them, and the TMA producer of a tile waits for the blocks of its own B rows
-only - tiles over this process's rows start at once, the rest follow as their rows arrive. After that call the local
+of the other owners itself: four extra warps in each CTA of ``otb_pg_gemm`` copy runs of rows from the owners' buffers
+(plain peer loads) into the local buffer and count them in, and the TMA producer of a tile waits for the counter of its own
+B rows only - tiles over this process's rows start at once, the rest follow as their rows arrive. After that call the local
 buffer holds the whole weight, so the other micro-batches and the backward pass run the plain GEMM on it.
 
 This is what FSDP's parameter all-gather does before a layer's forward
@@ -22,8 +22,14 @@ import torch
 from ..ops import native
 from ..ops.native import I, L, P, check, cuda_lib, stream_ptr
 
-ROWS_PER_FLAG = 128
 EPI_BF16, EPI_F32, EPI_BF16_RES = 0, 1, 3
+
+
+def flag_words(rows: int) -> int:
+    """int32 words of counters a weight of ``rows`` rows needs (one per B tile of the GEMM plus one for the whole weight);
+    zeroed once, they only grow."""
+    tile = 256 if rows >= 256 else 128
+    return -(-rows // tile) + 1
 
 
 def uniform_rows_per_owner(row_ranges: list[tuple[int, int]], rows: int) -> int | None:
@@ -56,7 +62,7 @@ class GatheredWeight:
                  flags: torch.Tensor):
         assert local.dim() == 2 and local.is_contiguous() and local.dtype == torch.bfloat16
         assert 1 <= len(seg_begin) == len(rows_per_owner) <= 3 and seg_begin[0] == 0
-        assert flags.dtype == torch.int32 and flags.numel() >= -(-local.shape[0] // ROWS_PER_FLAG)
+        assert flags.dtype == torch.int32 and flags.numel() >= flag_words(local.shape[0])
         self.local, self.rank, self.P = local, rank, len(peer_ptrs)
         self.flags = flags
         self._ptrs = (ctypes.c_void_p * self.P)(*peer_ptrs)
@@ -84,8 +90,7 @@ class GatheredWeight:
         out = torch.empty((M, N), dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
         if residual is not None:
             assert residual.dtype == torch.bfloat16 and tuple(residual.shape) == (M, N)
-        # the flag value of this pull: unique per update of this weight and never zero (the flags start at zero)
-        seq = (self.epoch % 0x7FFFFFFE) + 1
+        seq = self.calls + 1    # the counters of this weight have seen `calls` pulls so far
         check(cuda_lib().otb_pg_gemm(P(x), self._ptrs, P(self.flags), I(self.rank), I(self.P), ctypes.c_uint(seq), P(out), P(residual),
                                      I(M), I(N), I(K), L(_ld(x)), L(_ld(self.local)), L(_ld(out)), L(_ld(residual) if residual is not None else 0),
                                      self._seg, self._rpo, I(self._nseg), I(epi), P(_status(x.device)), stream_ptr()),

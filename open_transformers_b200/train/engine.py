@@ -336,7 +336,7 @@ class TrainEngine:
             raise ValueError("run.param_sharding=gather needs GPUs of one machine with sharded ownership over peer memory, bf16 compute "
                              "weights, AdamW, no tensor parallelism and no quantisation-aware training")
         from ..models.modules.core import Linear
-        from ..parallel.param_gather import ROWS_PER_FLAG, GatheredWeight, uniform_rows_per_owner
+        from ..parallel.param_gather import GatheredWeight, flag_words, uniform_rows_per_owner
 
         lay = self.layout
         modules = dict(self.model.named_modules())
@@ -379,12 +379,12 @@ class TrainEngine:
                 begins.append(at)
                 at += lay.shapes[i][0]
             plans.append((slot, members, o0, rows, cols, begins, rpo, blocks))
-            blocks += -(-rows // ROWS_PER_FLAG)
+            blocks += flag_words(rows)
         self._pg_flags = torch.zeros(max(blocks, 1), dtype=torch.int32, device=self.device)
         for slot, members, o0, rows, cols, begins, rpo, b0 in plans:
             local = self.compute[o0:o0 + rows * cols].view(rows, cols)
             gw = GatheredWeight(local, [p + 2 * o0 for p in self.buf_compute.ptrs], self.rank, begins, rpo,
-                                self._pg_flags[b0:b0 + -(-rows // ROWS_PER_FLAG)])
+                                self._pg_flags[b0:b0 + flag_words(rows)])
             slot.gather = gw
             weights.append(gw)
             pulled.update(members)

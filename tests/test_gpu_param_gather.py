@@ -39,7 +39,7 @@ def _buffers(W, P, seg_begin, rpo):
                                             (8, 256, [200], 64)])                # fewer rows than owners x 128, ragged edge
 def test_gathering_gemm_equals_the_plain_gemm_and_completes_the_local_buffer(P, M, seg_rows, K_):
     from open_transformers_b200.ops import functional as K
-    from open_transformers_b200.parallel.param_gather import GatheredWeight
+    from open_transformers_b200.parallel.param_gather import GatheredWeight, flag_words
 
     g = torch.Generator().manual_seed(5)
     N = sum(seg_rows)
@@ -53,7 +53,8 @@ def test_gathering_gemm_equals_the_plain_gemm_and_completes_the_local_buffer(P, 
     want_f32 = K.gemm(x, W, epi=K.EPI_STORE_F32)
     for rank in sorted({0, P // 2, P - 1}):
         bufs = _buffers(W, P, seg_begin, rpo)
-        flags = torch.zeros(-(-N // 128), dtype=torch.int32, device=DEV)
+        flags = torch.zeros(flag_words(N), dtype=torch.int32, device=DEV)
+        unit = 128 if N >= 16384 else (64 if N >= 8192 else 16)   # rows per copy unit, as the kernel cuts them
         gw = GatheredWeight(bufs[rank], [b.data_ptr() for b in bufs], rank, seg_begin, rpo, flags)
         gw.epoch = 1
         assert gw.pending()
@@ -62,7 +63,7 @@ def test_gathering_gemm_equals_the_plain_gemm_and_completes_the_local_buffer(P, 
         assert K.kernel_status(torch.device(DEV)) == 0
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), rank
         assert torch.equal(bufs[rank].view(torch.int16), W.view(torch.int16)), "the local buffer must hold the whole weight afterwards"
-        assert not gw.pending() and int(flags.min()) == int(flags.max()) == 2
+        assert not gw.pending() and int(flags[-1]) == -(-N // unit) and int(flags[:-1].sum()) == -(-N // unit)
         for p in range(P):                                          # nobody else's buffer was written
             if p != rank:
                 assert torch.isnan(bufs[p].float()).any() or P == 1
@@ -75,6 +76,7 @@ def test_gathering_gemm_equals_the_plain_gemm_and_completes_the_local_buffer(P, 
         assert torch.equal(gw.gemm(x, res).view(torch.int16), want_res.view(torch.int16))
         gw.epoch = 3
         assert torch.equal(gw.gemm(x, out_fp32=True), want_f32)
+        assert int(flags[-1]) == 3 * -(-N // unit)                 # the counters only grow: three pulls so far
         assert K.kernel_status(torch.device(DEV)) == 0
 
 
