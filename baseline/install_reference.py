@@ -1,10 +1,12 @@
 """Puts the unmodified reference under `baseline/_ref` (git-ignored) for `bench.py --impl reference`.
 
-    python baseline/install_reference.py [/path/to/reference]
+    python baseline/install_reference.py /path/to/reference [/path/to/wheelhouse]
 
-First tries the offline pip install; the reference's build backend (hatchling) is not on this image, so that
-fails, and because the package is pure Python a plain copy of `src/pretrain` and `configs` is the install.
+(the source tree may also be named by OTB_REFERENCE_SRC). First tries an offline pip install; where the reference's build
+backend (hatchling) is not installed that fails, and because the package is pure Python a plain copy of `src/pretrain`
+and `configs` is the install.
 """
+import os
 import shutil
 import subprocess
 import sys
@@ -14,13 +16,18 @@ HERE = Path(__file__).resolve().parent
 
 
 def main() -> int:
-    src = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("OTB_REFERENCE_SRC", "")
+    if not where:
+        print(__doc__)
+        return 2
+    src = Path(where)
     dst = HERE / "_ref"
     if not (src / "src" / "pretrain").is_dir():
         print("no reference source tree at %s" % src)
         return 1
-    pip = subprocess.run([sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps", "--find-links",
-                          "/opt/wheelhouse", "--target", str(dst), str(src)], capture_output=True, text=True)
+    wheels = sys.argv[2] if len(sys.argv) > 2 else os.environ.get("PIP_FIND_LINKS", "")
+    pip = subprocess.run([sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation", "--no-deps"] +
+                         (["--find-links", wheels] if wheels else []) + ["--target", str(dst), str(src)], capture_output=True, text=True)
     if pip.returncode == 0 and (dst / "pretrain").is_dir():
         print("pip install succeeded")
     else:

@@ -84,7 +84,7 @@ class _Clocks:
 def install_hint() -> str | None:
     """None when the reference copy and the stand-ins are in place, else the reason they are not."""
     if not (REF / "pretrain" / "train" / "loop.py").is_file() or not (REF / "configs" / "train").is_dir():
-        return "baseline/_ref holds no copy of the reference (run `python baseline/install_reference.py` where /root/reference exists)"
+        return "baseline/_ref holds no copy of the reference (run `python baseline/install_reference.py <reference checkout>`)"
     if not (SHIMS / "repop" / "__init__.py").is_file():
         return "baseline/shims/repop is missing"
     return None
