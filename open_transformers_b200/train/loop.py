@@ -187,7 +187,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             chains = {k: v for d in objs for k, v in d.items()}
         return SH.combine_batch_digests([chains[v] for v in range(V)])
 
-    result = {"run_dir": str(run_dir), "hashes": [], "losses": []}
+    result = {"run_dir": str(run_dir), "hashes": [], "losses": [], "device": str(dev)}
     zero_norm_streak: dict[str, int] = {}
     heartbeat = None
     if world > 1 and cfg.run.heartbeat_timeout_s > 0:
