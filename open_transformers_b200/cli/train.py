@@ -40,14 +40,6 @@ def main(argv: list[str] | None = None) -> int:
 
     if int(os.environ.get("RANK", "0")) == 0:  # one line per run: lines of several ranks would run together on a shared pipe
         print(json.dumps({k: v for k, v in res.items() if k != "losses"}, default=str), flush=True)
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and str(res.get("device", "")).startswith("cuda") and os.environ.get("OTB_PLAIN_EXIT") != "1":
-        # Everything of the run is committed (checkpoint, logs, the barrier above). Interpreter finalisation of a process that
-        # holds tens of GB of peer-mapped device memory and several communicators took most of a minute on some ranks of an
-        # 8-GPU run; leave without it.
-        logging.shutdown()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
     return 0
 
 

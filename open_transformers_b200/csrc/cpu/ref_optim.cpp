@@ -6,6 +6,10 @@
 
 #include <vector>
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 #include "det_math.h"
 #include "det_reduce.h"
 
@@ -28,6 +32,20 @@ inline float chunk_sos(const float* x, int len) {
 }  // namespace
 
 extern "C" {
+
+// Thread count of the OpenMP loops of this library (every twin gives the same bytes at any count). Launchers that start
+// one process per GPU set OMP_NUM_THREADS=1 for all of them; the start-up work that runs on the host (the Philox
+// initialisation of every weight) may ask for more for its own duration. Returns the previous count.
+int otb_cpu_set_threads(int n) {
+#ifdef _OPENMP
+  const int before = omp_get_max_threads();
+  if (n > 0) omp_set_num_threads(n);
+  return before;
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 int otb_cpu_chunk_size() { return CHUNK; }
 

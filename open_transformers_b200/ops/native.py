@@ -48,6 +48,32 @@ def cuda_lib() -> ctypes.CDLL:
     return _load("otb_cuda", "build_cuda")
 
 
+class host_threads:
+    """``with host_threads(n):`` the OpenMP loops of the CPU twins use ``n`` threads inside the block (``n=None``: this
+    process's share of the machine, cores // processes of this node). For host-side start-up work of GPU runs: launchers
+    that start one process per GPU pin OMP_NUM_THREADS to 1, which makes the Philox initialisation of a billion weights
+    take minutes. The bytes do not depend on the thread count."""
+
+    def __init__(self, n: int | None = None):
+        if n is None:
+            local = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
+            try:
+                cores = len(os.sched_getaffinity(0))
+            except (AttributeError, OSError):
+                cores = os.cpu_count() or 1
+            n = max(1, cores // local)
+        self.n, self.before = int(n), None
+
+    def __enter__(self):
+        self.before = int(cpu_lib().otb_cpu_set_threads(ctypes.c_int(self.n)))
+        return self
+
+    def __exit__(self, *exc):
+        if self.before:
+            cpu_lib().otb_cpu_set_threads(ctypes.c_int(self.before))
+        return False
+
+
 def loaded_libraries() -> list[str]:
     return sorted(_libs)
 

@@ -307,7 +307,15 @@ class TrainEngine:
 
         # ---- initialise (CPU-sampled Philox, byte-copied) and move the model onto the flat buffers
         if init:
-            init_weights(model, cfg.run.seed if seed is None else seed)
+            if self.is_cuda:
+                # the sampling runs on the host whatever the device: give it this process's share of the cores even where
+                # the launcher pinned OMP_NUM_THREADS to 1 (same bytes at any thread count)
+                from ..ops.native import host_threads
+
+                with host_threads():
+                    init_weights(model, cfg.run.seed if seed is None else seed)
+            else:
+                init_weights(model, cfg.run.seed if seed is None else seed)
         with torch.no_grad():
             for i, (name, p) in enumerate(named):
                 lay.view(self.master, i).copy_(p.detach().to(torch.float32))

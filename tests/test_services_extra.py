@@ -408,3 +408,22 @@ def test_linear_forward_hands_the_first_use_after_an_update_to_the_gathering_gem
     first.sum().backward()
     assert torch.equal(slot.buf, torch.einsum("btn,btk->nk", torch.ones_like(res), x.detach())) or torch.allclose(
         slot.buf, torch.einsum("btn,btk->nk", torch.ones_like(res), x.detach()), atol=1e-5)
+
+
+def test_host_threads_block_changes_the_thread_count_and_not_the_bytes():
+    """start-up work on the host of a GPU run may use this process's share of the cores although the launcher pinned
+    OMP_NUM_THREADS to 1: the count is restored afterwards and the Philox samples do not depend on it"""
+    import torch
+
+    from open_transformers_b200.ops import functional as K
+    from open_transformers_b200.ops.native import cpu_lib, host_threads
+
+    before = int(cpu_lib().otb_cpu_set_threads(0))
+    a, b = torch.empty(300_001), torch.empty(300_001)
+    with host_threads(1):
+        K.trunc_normal_(a, 0.02, 7, 11)
+    with host_threads(3) as ht:
+        assert ht.n == 3 and int(cpu_lib().otb_cpu_set_threads(0)) == 3
+        K.trunc_normal_(b, 0.02, 7, 11)
+    assert torch.equal(a, b) and int(cpu_lib().otb_cpu_set_threads(0)) == before
+    assert host_threads().n >= 1
