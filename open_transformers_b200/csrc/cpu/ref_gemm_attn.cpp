@@ -208,7 +208,7 @@ namespace {
 // latency of the fused multiply-add. A lane never sees another lane's values, so the bits are those of the plain loop. The
 // function is cloned for CPUs with hardware FMA (x86-64-v3); elsewhere fmaf stays the library's correctly rounded routine.
 #if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
-#define OTB_FMA_CLONES __attribute__((target_clones("arch=x86-64-v3", "default")))
+#define OTB_FMA_CLONES __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default")))
 #else
 #define OTB_FMA_CLONES
 #endif
@@ -352,17 +352,21 @@ OTB_FMA_CLONES void tc_rows_x16(const Dec* a, const int32_t* bm, const int32_t* 
         half[j] += prod < 0 ? -t : t;
       }
     }
+    // normalise the 16 sums (branch-free, so that the loop vectorises: 64-bit adds, leading-zero count, shifts)
+#pragma omp simd
     for (int j = 0; j < FB_N; ++j) {
       const int64_t sum = (int64_t)lo[j] + (int64_t)hi[j];
-      if (sum == 0) { am[j] = 0; ae[j] = 0; al[j] = NO_LEAD; continue; }
-      int64_t mag = sum < 0 ? -sum : sum;
-      int32_t oe = E[j] - 25;
-      const int L = tcmodel::bitlen(mag);
-      if (L > 24) { mag >>= (L - 24); oe += L - 24; }
-      am[j] = (int32_t)(sum < 0 ? -mag : mag);
-      ae[j] = oe;
-      al[j] = oe + tcmodel::bitlen(mag) - 1;
-      if (al[j] > 120 || al[j] < -120) redo[j] = 1;
+      const int64_t mag0 = sum < 0 ? -sum : sum;
+      const int32_t L = 64 - (int32_t)__builtin_clzll((uint64_t)mag0 | 1u);   // bit length (1 for a zero sum, masked below)
+      const int32_t drop = L > 24 ? L - 24 : 0;                              // truncate toward zero to 24 bits
+      const int32_t mag = (int32_t)(mag0 >> drop);
+      const int32_t oe = E[j] - 25 + drop;
+      const int32_t lead = oe + (L > 24 ? 24 : L) - 1;
+      const bool nz = sum != 0;
+      am[j] = nz ? (sum < 0 ? -mag : mag) : 0;
+      ae[j] = nz ? oe : 0;
+      al[j] = nz ? lead : NO_LEAD;
+      redo[j] |= (uint8_t)(nz && (lead > 120 || lead < -120));
     }
   }
   for (int j = 0; j < FB_N; ++j) {
