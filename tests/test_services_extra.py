@@ -427,3 +427,42 @@ def test_host_threads_block_changes_the_thread_count_and_not_the_bytes():
         K.trunc_normal_(b, 0.02, 7, 11)
     assert torch.equal(a, b) and int(cpu_lib().otb_cpu_set_threads(0)) == before
     assert host_threads().n >= 1
+
+
+def test_gather_mode_plan_splits_the_owned_chunks_and_describes_every_projection(monkeypatch):
+    """the planning half of ``run.param_sharding: gather`` on a CPU stand-in for two GPUs: every projection weight (the fused
+    QKV operand as three row-concatenated weights) gets a descriptor whose rows-per-owner match the ownership, and the
+    owned chunks split exactly into those the AdamW kernel keeps local (pulled weights) and those it pushes (the rest)"""
+    import torch
+
+    from open_transformers_b200.config import load_config
+    from open_transformers_b200.train.engine import TrainEngine
+
+    cfg = load_config("tiny_cpu", ["model.n_layers=2", "model.d_model=128", "model.n_heads=2", "model.n_kv_heads=2", "model.ffn_intermediate=256",
+                                   "model.vocab_size=256", "train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64",
+                                   "run.virtual_dp_size=4", "run.dp_shard_size=4", "run.dp_replicate_size=1", "run.mixed_precision=true"])
+    eng = TrainEngine(cfg, "cpu", 0, 1)
+    assert eng._pg is None                                               # one process: nothing to gather
+    lay = eng.layout
+    # dress the engine up as rank 0 of two GPU processes with peer memory
+    eng.world, eng.is_cuda, eng.peer, eng.sharded = 2, True, True, True
+    eng._owner_ranges = lay.owner_ranges(2)
+    eng.seg_lo, eng.seg_hi = eng._owner_ranges[0]
+    eng.chunk_lo, eng.chunk_hi = int(lay.seg_first[eng.seg_lo]), int(lay.seg_first[eng.seg_hi])
+    eng.buf_compute.ptrs = [eng.compute.data_ptr(), eng.compute.data_ptr()]
+    monkeypatch.setenv("OTB_PARAM_SHARDING", "gather")
+    eng._setup_param_gather()
+    pg = eng._pg
+    names = {lay.names[i] for i in pg["pulled_params"]}
+    assert {n for n in lay.names if n.endswith((".wq.weight", ".wk.weight", ".wv.weight", ".wo.weight", ".w_gate_up.weight", ".w_down.weight"))} <= names
+    assert "embedding.output.weight" in names and not any("tok_embeddings" in n or "norm" in n for n in names)
+    fused = [g for g in pg["weights"] if g._nseg == 3]
+    assert len(fused) == cfg.model.n_layers and all(list(g._seg) == [0, 128, 256] and list(g._rpo) == [64, 64, 64] for g in fused)
+    assert all(not g.pending() for g in pg["weights"])                   # start-up: every process holds the whole weights
+    pull, push = pg["tables"]["pull"], pg["tables"]["push"]
+    owned = sum(s.length for s in lay.segments[eng.seg_lo:eng.seg_hi])
+    assert int(pull[1].sum()) + int(push[1].sum()) == owned and pull[4] + push[4] == eng.chunk_hi - eng.chunk_lo
+    starts = torch.cat([pull[0], push[0]])
+    assert starts.unique().numel() == starts.numel()                     # no chunk in both tables
+    pulled_elems = sum(s.length for s in lay.segments[eng.seg_lo:eng.seg_hi] if s.param in set(pg["pulled_params"]))
+    assert int(pull[1].sum()) == pulled_elems
