@@ -384,6 +384,50 @@ OTB_FMA_CLONES void tc_rows_x16(const float* av, const int32_t* alead, const flo
   }
 }
 
+// One query row of one (query block, key block) pair of the block-wise forward pass: mask, running maximum, probabilities
+// (rounded to bf16 for the P V product), the four partial row sums and the rescaling of the output accumulator. A function
+// of its own so that it is cloned for hardware FMA like the GEMM micro-kernels (fmaf is a library call otherwise).
+OTB_FMA_CLONES void attn_fwd_softmax_row(float* s, float* p, int qi, int k0, int T, int window, float c_log2, float* m_run, float* lp,
+                                         float* oacc, int D, bool later_block) {
+  if (qi >= T) { for (int e = 0; e < 128; ++e) p[e] = 0.0f; return; }
+  float mx = -INFINITY;
+  for (int e = 0; e < 128; ++e) {
+    const int kj = k0 + e;
+    if (masked_pair(qi, kj, window) || kj >= T) { s[e] = -INFINITY; continue; }
+    mx = fmaxf(mx, s[e]);
+  }
+  const float m_new = fmaxf(*m_run, mx * c_log2);
+  const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+  const float alpha = det_exp2_attn(*m_run + (-m_safe));
+  for (int part = 0; part < 4; ++part) {
+    float ls[2] = {0.0f, 0.0f};
+    for (int e = part * 32; e < part * 32 + 32; ++e) {
+      const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
+      ls[e & 1] = ls[e & 1] + pe;
+      p[e] = rbf(pe);
+    }
+    lp[part] = det_fmaf(lp[part], alpha, ls[0] + ls[1]);
+  }
+  for (int d = 0; d < D; ++d) oacc[d] = later_block ? oacc[d] * alpha : 0.0f;
+  *m_run = m_new;
+}
+
+// One query row of one block pair of the block-wise backward pass: P and dS (both rounded to bf16) and their transposes.
+OTB_FMA_CLONES void attn_bwd_probs_row(const float* s, const float* dp, float* P, float* dS, float* PT, float* dST, int qi, int k0, int T,
+                                       int window, bool row_ok, float l2, float dl, float c_log2, float scale) {
+  for (int e = 0; e < 128; ++e) {
+    const int kj = k0 + e;
+    float p = 0.0f, ds = 0.0f;
+    if (row_ok && kj < T && !masked_pair(qi, kj, window)) {
+      const float pe = det_exp2_attn(det_fmaf(s[e], c_log2, -l2));
+      p = rbf(pe);
+      ds = rbf((pe * (dp[e] + (-dl))) * scale);
+    }
+    P[e] = p; dS[e] = ds;
+    PT[e * 128] = p; dST[e * 128] = ds;
+  }
+}
+
 // acc[m * ldacc + n] <- tcmodel::dot(a_m, b_n, K, acc[m * ldacc + n]): an [M][K] and an [N][K] panel of bf16-representable
 // floats, every chain continuing from the value already in acc (pass zeros to start one).
 void tc_block(const float* a, const float* b, int M, int N, int K, float* acc, long ldacc) {
@@ -391,14 +435,23 @@ void tc_block(const float* a, const float* b, int M, int N, int K, float* acc, l
   std::vector<int32_t> alead((size_t)M * K), bl((size_t)nb * K * FB_N, NO_LEAD);
   std::vector<float> bv((size_t)nb * K * FB_N, 0.0f);
   bool wild = false;
-  for (size_t i = 0; i < (size_t)M * K; ++i) alead[i] = lead_of(a[i], &wild);
-  for (int n = 0; n < N; ++n)
+#pragma omp parallel for schedule(static) reduction(|| : wild)
+  for (int m = 0; m < M; ++m) {
+    bool w = false;
+    for (int k = 0; k < K; ++k) alead[(size_t)m * K + k] = lead_of(a[(size_t)m * K + k], &w);
+    wild = wild || w;
+  }
+#pragma omp parallel for schedule(static) reduction(|| : wild)
+  for (int n = 0; n < N; ++n) {
+    bool w = false;
     for (int k = 0; k < K; ++k) {
       const float v = b[(size_t)n * K + k];
       const size_t at = ((size_t)(n / FB_N) * K + k) * FB_N + (n % FB_N);
       bv[at] = v;
-      bl[at] = lead_of(v, &wild);
+      bl[at] = lead_of(v, &w);
     }
+    wild = wild || w;
+  }
 #pragma omp parallel for collapse(2) schedule(static)
   for (int m = 0; m < M; ++m) {
     for (int bn = 0; bn < nb; ++bn) {
@@ -426,6 +479,7 @@ int attn_bwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, c
   std::vector<float> Qb(128 * D), dOb(128 * D), Kb(128 * D), Vb(128 * D), QbT(128 * D), dObT(128 * D), KbT(128 * D);
   std::vector<float> S(128 * 128), dP(128 * 128), P(128 * 128), dS(128 * 128), PT(128 * 128), dST(128 * 128), dQ(128 * D);
   auto load = [&](const void* src, long ld, int b, int r0, long col0, float* rows, float* rowsT) {
+#pragma omp parallel for schedule(static)
     for (int r = 0; r < 128; ++r)
       for (int d = 0; d < D; ++d) {
         const int t = r0 + r;
@@ -455,18 +509,9 @@ int attn_bwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, c
 #pragma omp parallel for schedule(static)
             for (int r = 0; r < 128; ++r) {
               const int qi = q0 + r;
-              for (int e = 0; e < 128; ++e) {
-                const int kj = j * 128 + e;
-                float p = 0.0f, ds = 0.0f;
-                if (qi < T && kj < T && !masked_pair(qi, kj, window)) {
-                  const float l2 = lse[((long)b * H + h) * T + qi], dl = delta[((long)b * H + h) * T + qi];
-                  const float pe = det_exp2_attn(det_fmaf(S[r * 128 + e], c_log2, -l2));
-                  p = rbf(pe);
-                  ds = rbf((pe * (dP[r * 128 + e] + (-dl))) * scale);
-                }
-                P[r * 128 + e] = p; dS[r * 128 + e] = ds;
-                PT[e * 128 + r] = p; dST[e * 128 + r] = ds;
-              }
+              const bool row_ok = qi < T;
+              attn_bwd_probs_row(&S[r * 128], &dP[r * 128], &P[r * 128], &dS[r * 128], &PT[r], &dST[r], qi, j * 128, T, window, row_ok,
+                                 row_ok ? lse[((long)b * H + h) * T + qi] : 0.0f, row_ok ? delta[((long)b * H + h) * T + qi] : 0.0f, c_log2, scale);
             }
             tc_block(PT.data(), dObT.data(), 128, D, 128, dVacc.data() + (size_t)j * 128 * D, D);
             tc_block(dST.data(), QbT.data(), 128, D, 128, dKacc.data() + (size_t)j * 128 * D, D);
@@ -505,6 +550,7 @@ int attn_fwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, v
           for (int i = 0; i < 4; ++i) lp[r * 4 + i] = 0.0f;
         }
         for (int j = jmin; j <= qb; ++j) {
+#pragma omp parallel for schedule(static)
           for (int e = 0; e < 128; ++e)
             for (int d = 0; d < D; ++d) {
               const int kj = j * 128 + e;
@@ -514,32 +560,8 @@ int attn_fwd_tc_blocks(const void* qk, long ldqk, const void* qkv, long ldqkv, v
           for (auto& v : S) v = 0.0f;
           tc_block(Qb.data(), Kb.data(), 128, 128, D, S.data(), 128);
 #pragma omp parallel for schedule(static)
-          for (int r = 0; r < 128; ++r) {
-            const int qi = q0 + r;
-            float* s = &S[r * 128];
-            float* p = &P[r * 128];
-            if (qi >= T) { for (int e = 0; e < 128; ++e) p[e] = 0.0f; continue; }
-            float mx = -INFINITY;
-            for (int e = 0; e < 128; ++e) {
-              const int kj = j * 128 + e;
-              if (masked_pair(qi, kj, window) || kj >= T) { s[e] = -INFINITY; continue; }
-              mx = fmaxf(mx, s[e]);
-            }
-            const float m_new = fmaxf(m_run[r], mx * c_log2);
-            const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
-            const float alpha = det_exp2_attn(m_run[r] + (-m_safe));
-            for (int part = 0; part < 4; ++part) {
-              float ls[2] = {0.0f, 0.0f};
-              for (int e = part * 32; e < part * 32 + 32; ++e) {
-                const float pe = (s[e] == -INFINITY) ? 0.0f : det_exp2_attn(det_fmaf(s[e], c_log2, -m_safe));
-                ls[e & 1] = ls[e & 1] + pe;
-                p[e] = rbf(pe);
-              }
-              lp[r * 4 + part] = det_fmaf(lp[r * 4 + part], alpha, ls[0] + ls[1]);
-            }
-            for (int d = 0; d < D; ++d) Oacc[r * D + d] = j > jmin ? Oacc[r * D + d] * alpha : 0.0f;
-            m_run[r] = m_new;
-          }
+          for (int r = 0; r < 128; ++r)
+            attn_fwd_softmax_row(&S[r * 128], &P[r * 128], q0 + r, j * 128, T, window, c_log2, &m_run[r], &lp[r * 4], &Oacc[r * D], D, j > jmin);
           tc_block(P.data(), VbT.data(), 128, D, 128, Oacc.data(), D);
         }
         for (int r = 0; r < 128 && q0 + r < T; ++r) {
