@@ -166,7 +166,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     from ..train.checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
     from ..train.engine import TrainEngine
     from ..train.spike_protocol import Halt, SpikeProtocol
-    from ..train.qk_gain_control import clamp_qk_gains, zero_q_gain_grads
+    from ..train.qk_gain_control import clamp_qk_gains
     from .cpu_threads import configure_cpu_threads
 
     expected = resolve_expect_hash(expect_hash)

@@ -36,7 +36,7 @@ from . import state_hash as SH
 from .checkpoint import CheckpointMeta, Checkpointer, resolved_config_json
 from .engine import TrainEngine
 from .midtrain import check_linear_anneal_resume
-from .qk_gain_control import clamp_qk_gains, zero_q_gain_grads
+from .qk_gain_control import clamp_qk_gains
 from .spike_protocol import Halt, SpikeProtocol
 
 log = logging.getLogger("pretrain.train")
