@@ -243,8 +243,8 @@ void gemm_f32_chains(const float* a, const float* b, void* C, const void* R, int
   }
   const int mb = (M + FB_M - 1) / FB_M;
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int bm = 0; bm < mb; ++bm) {
-    for (int bn = 0; bn < nb; ++bn) {
+  for (int bn = 0; bn < nb; ++bn) {      // (panel outer, row blocks inner: the panel stays cached)
+    for (int bm = 0; bm < mb; ++bm) {
       float acc[FB_M * FB_N];
       const float* rows[FB_M];
       for (int i = 0; i < FB_M; ++i) {
@@ -457,9 +457,11 @@ void tc_block(const float* a, const float* b, int M, int N, int K, float* acc, l
     }
     wild = wild || w;
   }
+  // panel by panel, all rows of A per panel: a decoded panel of B (K x 16 values and exponents) stays in the second-level
+  // cache while the rows stream past it; the other order re-reads every panel from memory for every row
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int m = 0; m < M; ++m) {
-    for (int bn = 0; bn < nb; ++bn) {
+  for (int bn = 0; bn < nb; ++bn) {
+    for (int m = 0; m < M; ++m) {
       float in[FB_N], out[FB_N];
       uint8_t redo[FB_N];
       for (int j = 0; j < FB_N; ++j) in[j] = bn * FB_N + j < N ? acc[(long)m * ldacc + bn * FB_N + j] : 0.0f;
@@ -604,9 +606,11 @@ void gemm_tc_fast(const float* a, const float* b, void* C, const void* R, int M,
       bl[at] = lead_of(v, &w);
       wild = wild || w;
     }
+  // panel by panel, all rows of A per panel: a decoded panel of B (K x 16 values and exponents) stays in the second-level
+  // cache while the rows stream past it; the other order re-reads every panel from memory for every row
 #pragma omp parallel for collapse(2) schedule(static)
-  for (int m = 0; m < M; ++m) {
-    for (int bn = 0; bn < nb; ++bn) {
+  for (int bn = 0; bn < nb; ++bn) {
+    for (int m = 0; m < M; ++m) {
       float out[FB_N];
       uint8_t redo[FB_N];
       if (!wild) tc_rows_x16(a + (size_t)m * K, alead.data() + (size_t)m * K, bv.data() + (size_t)bn * K * FB_N, bl.data() + (size_t)bn * K * FB_N, K, out, redo);
