@@ -84,9 +84,11 @@ WORKER = str(Path(__file__).resolve().parent / "multi_gpu_worker.py")
 
 
 @pytest.mark.distributed
-def test_gather_mode_on_two_gpus_reproduces_the_replicated_hashes(tmp_path):
+@pytest.mark.parametrize("sharded_state", [False, True])
+def test_gather_mode_on_two_gpus_reproduces_the_replicated_hashes(tmp_path, sharded_state):
     """run.param_sharding=gather: the AdamW kernel keeps the projection weights' new rows on their owner and the first
-    forward GEMM of the next step pulls them over peer memory; hashes are those of the default mode and of one GPU"""
+    forward GEMM of the next step pulls them over peer memory; hashes are those of the default mode and of one GPU.
+    ``sharded_state``: together with moments and reduced gradient allocated for the owned segments only"""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least 2 GPUs")
 
@@ -99,7 +101,8 @@ def test_gather_mode_on_two_gpus_reproduces_the_replicated_hashes(tmp_path):
         return json.load(open(out))
 
     one = run(1, tmp_path / "g1.json")
-    two = run(2, tmp_path / "g2.json", OTB_PARAM_SHARDING="gather")
-    assert one["status"] == 0 and two["status"] == 0
+    extra = {"OTB_STATE_SHARDING": "1"} if sharded_state else {}
+    two = run(2, tmp_path / "g2.json", OTB_PARAM_SHARDING="gather", **extra)
+    assert one["status"] == 0 and two["status"] == 0 and two["packed_state"] == sharded_state
     assert two["hashes"] == one["hashes"]
     assert two["gather_calls"] > 0 and one["gather_calls"] == 0
