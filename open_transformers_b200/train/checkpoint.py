@@ -280,6 +280,16 @@ class Checkpointer:
             self._pinned[key] = buf
         return buf
 
+    def prepare(self, engine) -> None:
+        """Allocate (page-lock) the host staging buffers of this process's rows now, so that the first checkpoint of a run
+        does not pay for it on the training thread (page-locking runs at 1-2 GB/s: 11 s for the 19 GB of one GPU holding
+        everything, 2.5 s per process on eight)."""
+        if not engine.is_cuda:
+            return
+        total = sum(t["weight"].numel() for pp in engine.owned_pieces() for _lo, _hi, t in pp)
+        for k in ("weight", "exp_avg", "exp_avg_sq"):
+            self._stage(k, total, torch.float32, True)
+
     def _snapshot(self, engine) -> dict:
         """This process's rows of master weights and moments, copied to (pinned) host memory, in the reference's layout."""
         lay = engine.layout

@@ -110,6 +110,8 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
         raise RuntimeError("%s already holds checkpoints; pass --resume-from or choose a new run_id (cold-start overwrite guard)" % run_dir)
 
     engine = TrainEngine(cfg, dev, rank, world)
+    if cfg.train.ckpt_every_steps > 0 or cfg.train.ckpt_every_tokens > 0:
+        ckpt.prepare(engine)  # page-lock the staging buffers before the first step, not inside the first checkpoint
     V, hosted = engine.V, engine.hosted
     if rank == 0:
         rb = engine.resident_bytes()
