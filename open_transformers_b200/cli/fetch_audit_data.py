@@ -1,21 +1,39 @@
-"""``pretrain-fetch-audit-data --checkpoint DIR --mirror gs://... | DIR --dest DIR [--until-step N]``:
-download (and verify) only the shards an audit interval reads; see data/fetch_interval.py."""
+"""``pretrain-fetch-audit-data``: download (and verify) only the shards an audit interval reads.
+
+    pretrain-fetch-audit-data --checkpoint DIR --gcs-root gs://bucket/shards [--dest ./data/audit_data] [--config-name NAME]
+                              [--until-step N] [--no-verify]
+
+``--gcs-root`` (also ``--mirror``) names the mirror of the dataset's shard directory: a ``gs://`` URL or a local directory
+with the same layout. The interval runs from the checkpoint's step to ``--until-step`` (default: one checkpoint interval).
+Prints what was fetched and the replay command for it. (flags: reference src/pretrain/cli/fetch_audit_data.py:29-62;
+mechanics: data/fetch_interval.py)
+"""
 from __future__ import annotations
 
 import argparse
+import json
+import logging
 import sys
 
 
 def main(argv=None) -> int:
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s :: %(message)s")
     ap = argparse.ArgumentParser(prog="pretrain-fetch-audit-data")
-    ap.add_argument("--checkpoint", required=True)
-    ap.add_argument("--mirror", "--gcs-root", dest="mirror", required=True)
-    ap.add_argument("--dest", required=True)
-    ap.add_argument("--until-step", type=int)
+    ap.add_argument("--checkpoint", required=True, help="auditable checkpoint directory to start from")
+    ap.add_argument("--gcs-root", "--mirror", dest="mirror", required=True, help="gs:// root (or a local directory) holding one <source>/ per source")
+    ap.add_argument("--dest", default="./data/audit_data", help="local destination root (default: ./data/audit_data)")
+    ap.add_argument("--config-name", default=None, help="train config name (default: the configuration in the checkpoint's meta.json)")
+    ap.add_argument("--until-step", type=int, default=None, help="fetch through this optimizer step (default: one checkpoint interval)")
+    ap.add_argument("--no-verify", action="store_true", help="skip the blake2b verification of downloaded .idx / .bin files")
     a = ap.parse_args(argv)
-    from ..data.fetch_interval import fetch_audit_interval
+    from ..data.fetch_interval import fetch_audit_interval, read_checkpoint_descriptor
 
-    print(fetch_audit_interval(a.checkpoint, a.mirror, a.dest, until_step=a.until_step))
+    data_root = fetch_audit_interval(a.checkpoint, a.mirror, a.dest, until_step=a.until_step, config_name=a.config_name, verify=not a.no_verify)
+    meta = read_checkpoint_descriptor(a.checkpoint)["meta"]
+    print(json.dumps({"data_root": data_root, "checkpoint": a.checkpoint, "from_step": meta["step"], "until_step": a.until_step,
+                      "verified": not a.no_verify}, indent=2))
+    print("\nAudit this interval with:\n  pretrain-audit-replay \\\n      --checkpoint %s \\\n      --data-root %s \\\n"
+          "      --expect-hash <next-checkpoint>/state_hash.txt" % (a.checkpoint, data_root))
     return 0
 
 

@@ -94,9 +94,15 @@ def enumerate_touched_shards(cfg, data_root: str | Path, stream_state, consumed_
     return touched
 
 
-def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path, until_step: int | None = None, cfg=None) -> str:
-    """Materialise under ``dest`` everything a replay of [checkpoint.step, until_step) needs; returns ``dest``."""
-    from ..config import parse_config_resolved
+def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path, until_step: int | None = None, cfg=None, *,
+                         config_name: str | None = None, verify: bool = True) -> str:
+    """Materialise under ``dest`` everything a replay of [checkpoint.step, until_step) needs; returns ``dest``.
+    ``config_name``: a train config to use instead of the one recorded in the checkpoint; ``verify=False`` skips the
+    blake2b comparison of downloaded files with their manifest (reference src/pretrain/cli/fetch_audit_data.py:49-60)."""
+    from ..config import load_config, parse_config_resolved
+
+    if cfg is None and config_name:
+        cfg = load_config(config_name)
 
     if isinstance(mirror, str):
         mirror = GcsMirror(mirror) if mirror.startswith("gs://") else DirMirror(mirror)
@@ -114,7 +120,7 @@ def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path, until
         man = SourceManifest.load(dest / rel / "manifest.yaml")
         for s in man.shards:
             mirror.download(str(rel / (s.prefix + ".idx")), dest / rel / (s.prefix + ".idx"))
-            if s.idx_blake2b and blake2b_file(dest / rel / (s.prefix + ".idx")) != s.idx_blake2b:
+            if verify and s.idx_blake2b and blake2b_file(dest / rel / (s.prefix + ".idx")) != s.idx_blake2b:
                 raise FetchIntegrityError("%s.idx does not match its manifest digest" % s.prefix)
     # 2. which payloads are needed
     touched = enumerate_touched_shards(cfg, dest, desc["stream"], meta["consumed_tokens"], meta["step"], n_steps, meta["dp_world_size"])
@@ -129,7 +135,7 @@ def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path, until
             target = dest / rel / (s.prefix + ".bin")
             if sid in touched.get(man.name, set()):
                 mirror.download(str(rel / (s.prefix + ".bin")), target)
-                if s.bin_blake2b and blake2b_file(target) != s.bin_blake2b:
+                if verify and s.bin_blake2b and blake2b_file(target) != s.bin_blake2b:
                     target.unlink()
                     raise FetchIntegrityError("%s.bin does not match its manifest digest" % s.prefix)
             elif not target.exists():

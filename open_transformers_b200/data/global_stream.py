@@ -142,8 +142,9 @@ class ShardedWindowView:
     world of ``world_size``). Iterating yields ``(plan, [(rank, accum_index, windows[mb, seq_len+1]), ...])``."""
 
     def __init__(self, manifests, manifest_dirs, weights, seq_len, seed, train, ranks, world_size, eos_id=0,
-                 state: GlobalStreamState | None = None, consumed_tokens: int = 0, start_step: int = 0):
-        self._core = _Core(manifests, manifest_dirs, weights, seq_len, seed, eos_id, state, index_only=False)
+                 state: GlobalStreamState | None = None, consumed_tokens: int = 0, start_step: int = 0, index_only: bool = False):
+        self._core = _Core(manifests, manifest_dirs, weights, seq_len, seed, eos_id, state, index_only=index_only)
+        self.has_carry_over = bool(state and state.carry_over)  # tokens queued by an earlier step: they name no document
         self.train, self.world_size = train, world_size
         self.ranks = [ranks] if isinstance(ranks, int) else list(ranks)
         self._consumed_tokens, self._step = consumed_tokens, start_step
@@ -168,6 +169,31 @@ class ShardedWindowView:
             self._consumed_tokens += plan.tokens_this_step
             self._step += 1
             yield plan, out
+
+    def stream_position(self) -> dict:
+        """Where the stream stands, in the terms a checkpoint's ``global_stream.json`` records (payload-free: also for
+        index-only walks, whose carry-over tokens cannot be materialised)."""
+        c = self._core
+        return {"consumed_documents_per_source": {w.name: w.consumed for w in c.walkers},
+                "epoch_per_source": {w.name: w.epoch for w in c.walkers}, "windows_emitted": c.windows_emitted}
+
+    def walk_step_spans(self, until_step: int):
+        """Per optimizer step below ``until_step``: ``(plan, spans)`` with one span ``(global_window, source, shard, document,
+        first token, end token)`` per document piece of the step's windows, in stream order, without reading token payloads
+        (reference src/pretrain/data/global_stream.py, ``walk_step_spans``; used by the step -> document map)."""
+        mb, n = self.train.micro_batch_size, self._core.seq_len + 1
+        for plan in iter_step_plans(self._consumed_tokens, self._core.windows_emitted, self.train, start_step=self._step):
+            if plan.step >= until_step:
+                return
+            spans = []
+            for _ in range(plan.microbatches * mb):
+                gw = self._core.windows_emitted
+                for p in self._core.cut(n):
+                    if p[0] == "doc":
+                        spans.append((gw, self._core.walkers[p[1]].name, p[2], p[3], p[4], p[4] + p[5]))
+            self._consumed_tokens += plan.tokens_this_step
+            self._step += 1
+            yield plan, spans
 
     def walk_doc_refs(self, n_steps: int):
         """(step, microbatch, slot, source, shard, local, start, length) for every document piece of the next

@@ -42,10 +42,13 @@ def resolve_sources(data_cfg, data_root: str | None = None):
 
 
 def build_global_loader(cfg, ranks, world_size: int, state: GlobalStreamState | None = None, consumed_tokens: int = 0,
-                        start_step: int = 0, data_root: str | None = None) -> ShardedWindowView:
+                        start_step: int = 0, data_root: str | None = None, index_only: bool = False, seed: int | None = None) -> ShardedWindowView:
+    """``index_only``: a view that walks document lengths only (manifest + .idx, no .bin): for the step -> document map and
+    the shard fetcher. ``seed``: the run's recorded seed where it is not the configuration's."""
     manifests, dirs, weights = resolve_sources(cfg.data, data_root)
-    return ShardedWindowView(manifests, dirs, weights, cfg.data.seq_len, cfg.run.seed, cfg.train, ranks, world_size,
-                             eos_id=cfg.data.document_separator_id, state=state, consumed_tokens=consumed_tokens, start_step=start_step)
+    return ShardedWindowView(manifests, dirs, weights, cfg.data.seq_len, cfg.run.seed if seed is None else seed, cfg.train, ranks, world_size,
+                             eos_id=cfg.data.document_separator_id, state=state, consumed_tokens=consumed_tokens, start_step=start_step,
+                             index_only=index_only)
 
 
 def build_global_stream(cfg, state: GlobalStreamState | None = None, data_root: str | None = None) -> GlobalStream:

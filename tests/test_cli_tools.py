@@ -3,6 +3,7 @@
 step, document dump to Parquet, checkpoint inspection and fingerprint.
 (reference: src/pretrain/cli/prepare_data.py:300-378, cli/dump_documents.py, cli/inspect_checkpoint.py, cli/hash_ckpt.py)"""
 import json
+import shutil
 from pathlib import Path
 
 import pytest
@@ -261,15 +262,46 @@ def test_doc_map_and_fetch_commands_and_a_replay_on_fetched_data(tmp_path, capsy
     ck = res["run_dir"] + "/checkpoints/step_000000002"
     over = ["train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64", "train.micro_batch_size=2",
             "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=256", "train.global_batch_tokens.late=256"]
-    rc, out = _run(map_main, ["--config-name", "tiny_cpu", "--data-root", tmp, "--steps", "2", "--output", str(tmp_path / "m0.parquet"), *over], capsys)
-    rows0 = pq.read_table(tmp_path / "m0.parquet").to_pylist()
-    assert rc == 0 and json.loads(out)["rows"] == len(rows0) > 0 and {r["step"] for r in rows0} == {0, 1}
-    rc, out = _run(map_main, ["--checkpoint", ck, "--data-root", tmp, "--steps", "1", "--output", str(tmp_path / "m2.parquet")], capsys)
-    rows2 = pq.read_table(tmp_path / "m2.parquet").to_pylist()
-    assert rc == 0 and {r["step"] for r in rows2} == {2} and sum(r["length"] for r in rows2) <= 4 * 65
+    # from step 0 to the checkpoint's step: chunk files, a manifest, and the position check against global_stream.json
+    rc, out = _run(map_main, ["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "m0"), "--chunk-steps", "1"], capsys)
+    man = json.loads((tmp_path / "m0" / "step_docs_manifest.json").read_text())
+    rows0 = [r for f in man["files"] for r in pq.read_table(f).to_pylist()]
+    assert rc == 0 and man["rows"] == len(rows0) > 0 and {r["step"] for r in rows0} == {0, 1} and man["validation"]["match"] is True
+    assert [Path(f).name for f in man["files"]] == ["step_docs-000000-000000.parquet", "step_docs-000001-000001.parquet"]
+    # a wrong topology override changes only the rank column; a walk that stops early is not compared
+    rc, out = _run(map_main, ["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "m1"), "--until-step", "1", "--dp-world-size", "1"], capsys)
+    man1 = json.loads((tmp_path / "m1" / "step_docs_manifest.json").read_text())
+    assert rc == 0 and "validation" not in man1 and {r["dp_rank"] for f in man1["files"] for r in pq.read_table(f).to_pylist()} == {0}
+    # from the checkpoint's own position: needs --until-step past it (this checkpoint carries no tokens over, or the tool
+    # says why it cannot attribute them)
+    with pytest.raises(SystemExit):
+        map_main(["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "mx"), "--from-checkpoint-state"])
+    with pytest.raises(SystemExit):
+        map_main(["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "mx"), "--from-checkpoint-state", "--until-step", "2"])
+    carry = json.loads((Path(ck) / "global_stream.json").read_text())["carry_over"]
+    if carry:
+        with pytest.raises(SystemExit):
+            map_main(["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "m2"), "--from-checkpoint-state", "--until-step", "3"])
+    else:
+        rc, out = _run(map_main, ["--checkpoint", ck, "--data-root", tmp, "--out-dir", str(tmp_path / "m2"), "--from-checkpoint-state", "--until-step", "3"], capsys)
+        rows2 = [r for f in json.loads((tmp_path / "m2" / "step_docs_manifest.json").read_text())["files"] for r in pq.read_table(f).to_pylist()]
+        assert rc == 0 and {r["step"] for r in rows2} == {2}
+    # a stream position that differs from the checkpoint's record exits 2
+    doctored = tmp_path / "doctored"
+    shutil.copytree(ck, doctored)
+    gs = json.loads((doctored / "global_stream.json").read_text())
+    gs["windows_emitted"] += 1
+    (doctored / "global_stream.json").write_text(json.dumps(gs))
+    rc, out = _run(map_main, ["--checkpoint", str(doctored), "--data-root", tmp, "--out-dir", str(tmp_path / "m3")], capsys)
+    assert rc == 2 and json.loads((tmp_path / "m3" / "step_docs_manifest.json").read_text())["validation"]["match"] is False
     dest = tmp_path / "fetched"
-    rc, out = _run(fetch_main, ["--checkpoint", ck, "--mirror", tmp, "--dest", str(dest), "--until-step", "3"], capsys)
-    assert rc == 0 and out.strip() == str(dest) and list(dest.rglob("manifest.yaml"))
+    rc, out = _run(fetch_main, ["--checkpoint", ck, "--gcs-root", tmp, "--dest", str(dest), "--until-step", "3"], capsys)
+    report = json.loads(out[:out.index("\nAudit this interval")])
+    assert rc == 0 and report["data_root"] == str(dest) and report["verified"] and report["from_step"] == 2 and list(dest.rglob("manifest.yaml"))
+    assert "--data-root %s" % dest in out
+    rc, out = _run(fetch_main, ["--checkpoint", ck, "--mirror", tmp, "--dest", str(tmp_path / "unverified"), "--until-step", "3", "--no-verify",
+                                "--config-name", "tiny_cpu"], capsys)
+    assert rc == 0 and json.loads(out[:out.index("\nAudit this interval")])["verified"] is False
     assert audit_main(["--checkpoint", ck, "--data-root", str(dest), "--until-step", "3"]) == 0
     assert "MATCH=True" in capsys.readouterr().out
     # the replay fetching for itself: --gcs-root names the mirror, --fetch-dest where to put the interval's data

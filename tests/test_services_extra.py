@@ -110,9 +110,10 @@ def test_cpu_threads_parsing():
 
 # ------------------------------------------------------------------------- doc map and interval fetcher
 def test_doc_map_covers_every_window_slot_and_fetch_interval_brings_only_touched_shards(tmp_path):
+    import pandas as pd
     import pyarrow.parquet as pq
 
-    from open_transformers_b200.data.doc_map import COLUMNS, write_doc_map
+    from open_transformers_b200.data.doc_map import COLUMNS, compare_position, write_doc_map
     from open_transformers_b200.data.fetch_interval import DirMirror, fetch_audit_interval
     from open_transformers_b200.data.loader import build_global_loader
     from open_transformers_b200.train.loop import train
@@ -120,20 +121,31 @@ def test_doc_map_covers_every_window_slot_and_fetch_interval_brings_only_touched
     tmp = str(tmp_path)
     cfg = tiny_cfg(tmp, ["train.ckpt_every_steps=1"])
     V = cfg.run.virtual_dp_size or 2
-    loader = build_global_loader(cfg, list(range(V)), V, data_root=tmp)
-    out = tmp_path / "doc_map.parquet"
-    n = write_doc_map(loader, 2, V, out)
-    tab = pq.read_table(str(out)).to_pandas()
-    assert list(tab.columns) == COLUMNS and len(tab) == n > 0
+    view = build_global_loader(cfg, [], 1, data_root=tmp, index_only=True)
+    out = tmp_path / "doc_map"
+    summary = write_doc_map(view, out, until_step=2, micro_batch_size=cfg.train.micro_batch_size, dp_world_size=V, chunk_steps=1)
+    assert [Path(f).name for f in summary["files"]] == ["step_docs-000000-000000.parquet", "step_docs-000001-000001.parquet"]
+    tab = pd.concat([pq.read_table(f).to_pandas() for f in summary["files"]])
+    assert tuple(tab.columns) == COLUMNS and len(tab) == summary["rows"] > 0 and summary["steps_walked"] == 2
     per_step = cfg.train.global_batch_tokens.warmup // cfg.train.seq_len
-    assert set(tab["step"]) == {0, 1}
-    # every window slot of every micro-batch is covered by document pieces that add up to seq_len + 1 tokens or less
+    assert set(tab["step"]) == {0, 1} and summary["windows"] == 2 * per_step
+    # every window slot of every micro-batch is covered by document pieces that add up to seq_len + 1 tokens or less; the
+    # pieces of a window are numbered from 0, and the global window index follows (step, micro-batch, slot)
+    tab["length"] = tab["tok_end"] - tab["tok_start"]
     grp = tab.groupby(["step", "microbatch", "slot"])["length"].sum()
     assert len(grp) == 2 * per_step and int(grp.max()) <= cfg.train.seq_len + 1 and int(grp.min()) > 0
-    assert set(tab["dp_rank"]) <= set(range(V))
+    assert set(tab["dp_rank"]) <= set(range(V)) and tab.groupby("global_window")["frag_idx"].min().eq(0).all()
+    mb = cfg.train.micro_batch_size
+    assert ((tab["global_window"] - tab["step"] * per_step) == tab["microbatch"] * mb + tab["slot"]).all()
+    assert sum(summary["rows_per_source"].values()) == summary["rows"]
+    # the position a walk ends at is what a training run records after the same steps
+    assert summary["position"]["windows_emitted"] == 2 * per_step
 
     res = train(cfg, device="cpu", data_root=tmp, max_steps=2)
     ck = Path(res["run_dir"]) / "checkpoints" / "step_000000001"
+    recorded = json.loads((Path(res["run_dir"]) / "checkpoints" / "step_000000002" / "global_stream.json").read_text())
+    assert compare_position(summary["position"], recorded) == []
+    assert compare_position(dict(summary["position"], windows_emitted=1), recorded) == ["windows_emitted: walk=1 ckpt=%d" % (2 * per_step)]
     dest = tmp_path / "fetched"
     fetch_audit_interval(ck, DirMirror(tmp), dest, until_step=2)
     from open_transformers_b200.cli.audit_replay import audit_replay
