@@ -26,7 +26,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="pretrain-eval-olmes")
     ap.add_argument("--checkpoint", required=True)
     ap.add_argument("--tokenizer", required=True)
-    ap.add_argument("--config-name", default=None, help="accepted for compatibility; the checkpoint's own configuration is used")
+    ap.add_argument("--config-name", default=None, help="train config name (default: the configuration recorded in the checkpoint)")
+    ap.add_argument("--override", nargs="*", default=[], help="config overrides (with --config-name)")
     ap.add_argument("--out-dir", help="oe_eval output directory (metrics-all.jsonl, predictions, summary.json)")
     ap.add_argument("--task", nargs="*", default=None, help="olmes task / suite names (default: %s)" % " ".join(OLMES_DEFAULT_SUITES))
     ap.add_argument("--extended", action="store_true", help="also the generative extension tasks (hours at 1 B parameters)")
@@ -48,7 +49,7 @@ def main(argv=None) -> int:
         print("pretrain-eval-olmes: the OLMES suites need the oe_eval and lm_eval packages, which are not installed; "
               "use --task-file with local JSONL tasks", file=sys.stderr)
         return 2
-    model, _cfg, _eng = load_model_from_checkpoint(a.checkpoint, a.device)
+    model, _cfg, _eng = load_model_from_checkpoint(a.checkpoint, a.device, config_name=a.config_name, overrides=a.override)
     meta = Checkpointer.read_meta(a.checkpoint)
     if not a.task_file:
         out = R.run_olmes(model, a.tokenizer, a.out_dir, tasks=a.task, extended=a.extended, batch_size=a.batch_size, max_length=a.max_length,

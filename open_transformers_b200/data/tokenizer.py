@@ -66,3 +66,7 @@ class Tokenizer:
 
     def decode(self, ids) -> str:
         return self._tok.decode(list(int(i) for i in ids), skip_special_tokens=False)
+
+    def decode_batch(self, batch, skip_special_tokens: bool = False) -> list[str]:
+        """Several id sequences at once (special tokens kept by default, so the text stays faithful to the stored ids)."""
+        return self._tok.decode_batch([[int(i) for i in ids] for ids in batch], skip_special_tokens=skip_special_tokens)

@@ -73,12 +73,23 @@ def test_tokenizer_shards_manifests_and_dumps(corpus, capsys):
     rc, out = _run(prep, ["inspect", str(root / "src_a" / man.shards[0].prefix), "--tokenizer", tok_path, "--docs", "2"], capsys)
     assert rc == 0 and "alpha" in out or "beta" in out
 
-    rc, out = _run(dump_main, ["--source-dir", str(root / "src_a"), "--tokenizer", tok_path, "--out-dir", str(root / "dump"), "--workers", "1"], capsys)
-    assert rc == 0 and json.loads(out)["documents"] == 120
+    # the documents table: one file per shard under <out>/<source>/, keyed like the step -> document map; a second run skips
+    rc, out = _run(dump_main, ["--data-root", str(root), "--tokenizer", tok_path, "--out-dir", str(root / "dump"), "--workers", "1", "--batch-docs", "50"], capsys)
     import pyarrow.parquet as pq
 
-    table = pq.read_table(root / "dump" / (man.shards[0].prefix + ".parquet")).to_pylist()
-    assert table[0]["text"] == json.loads(open(paths[0]).readline())["text"] and table[0]["length"] == first.document_length(0)
+    files = sorted((root / "dump").rglob("*.parquet"))
+    assert rc == 0 and files and not list((root / "dump").rglob("*.part"))
+    first_file = root / "dump" / man.name / ("00000_%s.parquet" % Path(man.shards[0].prefix).name)
+    table = pq.read_table(first_file).to_pylist()
+    assert list(table[0]) == ["source", "shard_id", "local_doc", "n_tokens", "text"]
+    assert table[0]["text"] == json.loads(open(paths[0]).readline())["text"] and table[0]["n_tokens"] == first.document_length(0)
+    assert table[0]["source"] == man.name and table[0]["shard_id"] == 0 and [r["local_doc"] for r in table] == list(range(len(table)))
+    assert sum(len(pq.read_table(f)) for f in files if f.parent.name == man.name) == 120
+    stamp = first_file.stat().st_mtime_ns
+    rc, _ = _run(dump_main, ["--data-root", str(root), "--tokenizer", tok_path, "--out-dir", str(root / "dump"), "--workers", "1", "--sources", man.name,
+                             "--limit-shards", "1"], capsys)
+    assert rc == 0 and first_file.stat().st_mtime_ns == stamp
+    assert dump_main(["--data-root", str(root / "nothing_here"), "--tokenizer", tok_path, "--out-dir", str(root / "dump2"), "--workers", "1"]) == 1
 
 
 def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):

@@ -134,16 +134,46 @@ def test_eval_command_scripts_and_core_aggregate(ckpt, tmp_path, capsys):
     acc = {"arc_easy": 0.40, "piqa": 0.60, "lambada_openai": 0.10, "not_a_core_task": 0.99}
     (tmp_path / "acc.json").write_text(json.dumps(acc))
     capsys.readouterr()
-    assert eval_main(["--checkpoint", ckpt[0], "--shard-prefix", str(tmp_path / "heldout"), "--max-tokens", "300", "--batch-windows", "2",
-                      "--task-accuracies", str(tmp_path / "acc.json")]) == 0
-    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
-    assert out["tokens"] == 300 and 50 < out["perplexity"] < 5000
+    assert eval_main(["--checkpoint", ckpt[0], "--held-out", str(tmp_path / "heldout"), "--max-tokens", "300", "--batch-windows", "2", "--no-dclm",
+                      "--out-dir", str(tmp_path / "ev"), "--task-accuracies", str(tmp_path / "acc.json")]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out == json.loads((tmp_path / "ev" / "summary.json").read_text())
+    assert out["held_out_tokens"] == 300 and 50 < out["held_out_ppl"] < 5000 and "dclm_core_macro" not in out
     want = {"arc_easy": (0.40 - 0.25) / 0.75, "piqa": (0.60 - 0.5) / 0.5, "lambada_openai": 0.10}
     assert out["dclm_core"]["per_task"] == pytest.approx(want) and out["dclm_core"]["core"] == pytest.approx(sum(want.values()) / 3)
     assert "not_a_core_task" not in out["dclm_core"]["per_task"] and len(out["dclm_core"]["missing"]) == len(DCLM_CORE_TASKS) - 3
     assert centred(1.0, 0.25) == 1.0 and centred(0.25, 0.25) == 0.0 and dclm_core_score({})["core"] == 0.0
+    # the DCLM-CORE slice: without the harness an empty result file and the reason; with a scorer handed in, the categories,
+    # the single-task category, a failing task, and the file scripts/plot_evals.py reads
+    from open_transformers_b200.eval.dclm_core import primary_metric, run_dclm_core
+
+    with pytest.raises(SystemExit):
+        eval_main(["--checkpoint", ckpt[0]])                                   # the task run needs a tokenizer
+    assert eval_main(["--checkpoint", ckpt[0], "--tokenizer", ckpt[1], "--out-dir", str(tmp_path / "ev2")]) == 0
+    out2 = json.loads(capsys.readouterr().out)
+    empty = json.loads(next((tmp_path / "ev2").glob("step_*.json")).read_text())
+    if "dclm_core_error" in out2:                                              # lm-eval is not installed here
+        assert empty["categories"] == {} and empty["error"] == out2["dclm_core_error"] and out2["dclm_core_macro"] is None
+    scores = {"hellaswag": {"acc_norm,none": 0.30, "acc,none": 0.28}, "piqa": {"acc,none": 0.60}, "mmlu": {"acc,none": 0.27}, "boolq": {"exact_match,none": 0.5}}
+    shots = {}
+
+    def scorer(task, num_fewshot):
+        shots[task] = num_fewshot
+        return scores[task]                                                   # winogrande and openbookqa raise KeyError: recorded as errors
+
     run_dir = Path(ckpt[2])
-    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "plot_evals.py"), str(run_dir / "logs" / "metrics.jsonl"), "--out", str(tmp_path / "c.png")],
+    for step, bump in ((10, 0.0), (20, 0.05)):
+        scores["piqa"] = {"acc,none": 0.60 + bump}
+        res = run_dclm_core(None, None, run_dir / "evals" / ("step_%d" % step), step, evaluate=scorer)
+    assert shots["mmlu"] == 5 and shots["piqa"] == 0 and "error" in res["tasks"]["winogrande"] and res["tasks"]["hellaswag"]["primary"] == 0.30
+    assert res["categories"] == pytest.approx({"commonsense": (0.30 + 0.65) / 2, "world_knowledge": 0.27, "reading": 0.5})
+    assert res["macro_average"] == pytest.approx(sum(res["categories"].values()) / 3) and res["category_tasks"]["world_knowledge"] == ["mmlu"]
+    assert (run_dir / "evals" / "step_20" / "step_000000020.json").exists() and primary_metric({"note": "x", "f1": 0.4}) == 0.4 and primary_metric({}) == 0.0
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "plot_evals.py"), str(run_dir), str(run_dir), "--stitch", "-o", str(tmp_path / "e.png")],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert (tmp_path / "e.png").exists() or ("mmlu" in r.stdout.splitlines()[0] and r.stdout.count("\n") >= 3)
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "plot_training_curves.py"), str(run_dir / "logs" / "metrics.jsonl"), "--out", str(tmp_path / "c.png")],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
     assert (tmp_path / "c.png").exists() or r.stdout.count("\n") >= 3          # a figure, or the CSV dump where matplotlib is absent
