@@ -358,3 +358,76 @@ def test_launcher_script_runs_two_cpu_ranks_with_overrides_after_options(tmp_pat
 
     one = train(load_config("tiny_cpu", ["run.output_dir=%s/one" % tmp, "run.run_id=one", *over]), device="cpu", data_root=tmp)
     assert [tuple(h) for h in got] == [tuple(h) for h in one["hashes"]] and len(got) >= 1
+
+
+def test_prepare_data_takes_the_reference_flag_forms(corpus, tmp_path, capsys):
+    """--input-dir / --glob / --format inputs, fan-out sharding by byte range (--worker-id / --num-workers) joined by
+    merge-manifests --output-dir, --shard-tag, inspect --shard --n, token-stats --tokenizer --sample, the configuration-free
+    synthetic sources and replay-step --rank / --world-size / --seed / --override"""
+    from open_transformers_b200.cli.prepare_data import main as prep
+    from open_transformers_b200.data.indexed_dataset import IndexedDatasetReader
+    from open_transformers_b200.data.manifest import SourceManifest
+
+    root, paths = corpus
+    tok_path = str(tmp_path / "tok.json")
+    rc, out = _run(prep, ["train-tokenizer", "--input-dir", str(root), "--glob", "part*.jsonl", "--format", "jsonl", "--text-field", "text",
+                          "--output", tok_path, "--vocab-size", "320", "--min-frequency", "1"], capsys)
+    assert rc == 0 and Path(tok_path).exists()
+    with pytest.raises(SystemExit):
+        prep(["train-tokenizer", "--input-dir", str(root), "--glob", "*.nothing", "--output", tok_path])
+
+    # one worker, then three workers over byte ranges of the same files: the same documents, in worker order
+    one = tmp_path / "one"
+    rc, out = _run(prep, ["shard", "--input-dir", str(root), "--glob", "part*.jsonl", "--format", "jsonl", "--tokenizer", tok_path, "--output-dir", str(one),
+                          "--source-name", "src"], capsys)
+    whole = SourceManifest.load(one / "manifest.yaml")
+    assert rc == 0 and whole.total_documents == 120 and sorted(whole.raw_jsonl_blake2b) == ["part0.jsonl", "part1.jsonl"]
+    fan = tmp_path / "fan"
+    for k in range(3):
+        rc, out = _run(prep, ["shard", "--input-dir", str(root), "--glob", "part*.jsonl", "--format", "jsonl", "--tokenizer", tok_path, "--output-dir", str(fan),
+                              "--source-name", "src", "--worker-id", str(k), "--num-workers", "3"], capsys)
+        assert rc == 0 and json.loads(out)["manifest"] == "manifest.w%02d.yaml" % k and list(fan.glob("src_w%02d_00000.bin" % k))
+    with pytest.raises(SystemExit):
+        prep(["merge-manifests", "--output-dir", str(fan), "--expected-workers", "4"])
+    rc, out = _run(prep, ["merge-manifests", "--output-dir", str(fan), "--expected-workers", "3", "--remove-worker-manifests"], capsys)
+    merged = SourceManifest.load(fan / "manifest.yaml")
+    assert rc == 0 and merged.total_documents == 120 and merged.total_tokens == whole.total_tokens and not list(fan.glob("manifest.w*.yaml"))
+    assert [s.prefix for s in merged.shards] == ["src_w00_00000", "src_w01_00000", "src_w02_00000"] and merged.raw_jsonl_blake2b == whole.raw_jsonl_blake2b
+
+    def lengths(directory, man):
+        return sorted(IndexedDatasetReader(directory / s.prefix).document_length(i) for s in man.shards for i in range(s.num_documents))
+
+    assert lengths(fan, merged) == lengths(one, whole)
+    with pytest.raises(SystemExit):
+        prep(["shard", "--input-dir", str(root), "--glob", "part*.jsonl", "--tokenizer", tok_path, "--output-dir", str(fan), "--source-name", "src",
+              "--num-workers", "2", "--shard-tag", "x"])
+    rc, out = _run(prep, ["shard", str(paths[0]), "--tokenizer", tok_path, "--out-dir", str(tmp_path / "tagged"), "--name", "src", "--shard-tag", "w07"], capsys)
+    assert rc == 0 and (tmp_path / "tagged" / "manifest.w07.yaml").exists() and (tmp_path / "tagged" / "src_w07_00000.bin").exists()
+
+    rc, out = _run(prep, ["inspect", "--shard", str(one / whole.shards[0].prefix), "--tokenizer", tok_path, "--n", "2"], capsys)
+    assert rc == 0 and len(json.loads(out)["samples"]) == 2
+    sample = tmp_path / "sample.txt"
+    sample.write_text("alpha beta gamma 12 345 " * 20, encoding="utf-8")
+    rc, out = _run(prep, ["token-stats", "--tokenizer", tok_path, "--sample", str(sample)], capsys)
+    assert rc == 0 and 1.0 < json.loads(out)["bytes_per_token"] < 10.0
+
+    syn = tmp_path / "syn"
+    rc, out = _run(prep, ["synthetic", "--output-dir", str(syn), "--docs-a", "40", "--docs-b", "20", "--min-doc-len", "8", "--max-doc-len", "32",
+                          "--vocab-size", "500", "--seed", "3"], capsys)
+    a, b = SourceManifest.load(syn / "synth_a" / "manifest.yaml"), SourceManifest.load(syn / "synth_b" / "manifest.yaml")
+    assert rc == 0 and a.total_documents == 40 and b.total_documents == 20 and a.tokenizer_hash == "synthetic-no-tokenizer"
+    r = IndexedDatasetReader(syn / "synth_a" / "synth_a_00000")
+    docs = [r.document(i) for i in range(40)]
+    assert all(8 <= len(d) <= 32 and 1 <= int(d.min()) and int(d.max()) < 500 for d in docs) and a.total_tokens == sum(len(d) for d in docs)
+
+    data = str(tmp_path / "cfgdata")
+    over = ["train.seq_len=64", "data.seq_len=64", "model.max_seq_len_pretrain=64", "train.micro_batch_size=2",
+            "train.global_batch_tokens.warmup=256", "train.global_batch_tokens.main=256", "train.global_batch_tokens.late=256"]
+    assert _run(prep, ["synthetic", "--config-name", "tiny_cpu", "--data-root", data, "--tokens", "4000", *over], capsys)[0] == 0
+    rc, out = _run(prep, ["replay-step", "--config-name", "tiny_cpu", "--data-root", data, "--step", "1", "--override", *over], capsys)
+    everyone = [json.loads(l) for l in out.splitlines()]
+    rc, out = _run(prep, ["replay-step", "--config-name", "tiny_cpu", "--data-root", data, "--step", "1", "--rank", "1", "--world-size", "2", "--override", *over], capsys)
+    rank1 = [json.loads(l) for l in out.splitlines()]
+    assert rc == 0 and rank1 and {r["dp_rank"] for r in rank1} == {1} and rank1 == [r for r in everyone if r["dp_rank"] == 1]
+    rc, out = _run(prep, ["replay-step", "--config-name", "tiny_cpu", "--data-root", data, "--step", "1", "--seed", "5", "--override", *over], capsys)
+    assert rc == 0 and [json.loads(l)["tokens"] for l in out.splitlines()] != [r["tokens"] for r in everyone]
