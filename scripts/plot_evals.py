@@ -97,7 +97,7 @@ def main(argv=None) -> int:
     ap.add_argument("runs", nargs="+")
     ap.add_argument("--labels", nargs="*")
     ap.add_argument("--stitch", action="store_true", help="the directories are consecutive segments of one resumed run")
-    ap.add_argument("-o", "--out", default="evals.png")
+    ap.add_argument("-o", "--output", "--out", dest="out", default="evals.png")
     a = ap.parse_args(argv)
     loaded = [load_run(Path(r)) for r in a.runs]
     members = [m for _p, m in loaded]

@@ -32,7 +32,8 @@ def main(argv=None) -> int:
     ap.add_argument("runs", nargs="+")
     ap.add_argument("--labels", nargs="*")
     ap.add_argument("--stitch", action="store_true", help="treat all directories as segments of one run")
-    ap.add_argument("-o", "--out", default="evals_olmes.png")
+    ap.add_argument("-o", "--output", "--out", dest="out", default="evals_olmes.png")
+    ap.add_argument("--best-only", action="store_true", help="only the headline score per task (no dashed raw-accuracy trace)")
     a = ap.parse_args(argv)
     runs = [(Path(r), load_run(Path(r))) for r in a.runs]
     if a.stitch:
@@ -56,7 +57,8 @@ def main(argv=None) -> int:
                 print("%s,%d,macro,%.6f" % (label, step, pts[step]["macro"]))
                 for t, v in pts[step]["tasks"].items():
                     print("%s,%d,%s,%.6f" % (label, step, t, v["accuracy"]))
-                    print("%s,%d,%s_raw,%.6f" % (label, step, t, v["accuracy_raw"]))
+                    if not a.best_only:
+                        print("%s,%d,%s_raw,%.6f" % (label, step, t, v["accuracy_raw"]))
         return 0
     n = 1 + len(tasks)
     cols = min(3, n)
@@ -69,7 +71,8 @@ def main(argv=None) -> int:
         for ax, t in zip(flat[1:], tasks):
             have = [s for s in steps if t in pts[s]["tasks"]]
             line, = ax.plot(have, [pts[s]["tasks"][t]["accuracy"] for s in have], marker="o", label=label)
-            ax.plot(have, [pts[s]["tasks"][t]["accuracy_raw"] for s in have], linestyle="--", color=line.get_color())
+            if not a.best_only:
+                ax.plot(have, [pts[s]["tasks"][t]["accuracy_raw"] for s in have], linestyle="--", color=line.get_color())
     flat[0].set_title("macro average")
     for ax, t in zip(flat[1:], tasks):
         ax.set_title(t)

@@ -147,6 +147,9 @@ def main(argv=None) -> int:
     ap.add_argument("--config-name", default=None, help="accepted for compatibility: the checkpoint's own configuration is used")
     ap.add_argument("--override", nargs="*", default=[])
     ap.add_argument("--device", default=None, help="cuda or cpu (default: cuda when there is one)")
+    ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16",
+                    help="accepted for compatibility: the forward pass runs in the precision the checkpoint's run trained in (its kernels "
+                         "are bit-defined per precision family; there is no autocast to switch)")
     ap.add_argument("--prompt", help="continue this text once and exit")
     ap.add_argument("--max-new-tokens", type=int, default=200)
     ap.add_argument("--temperature", type=float, default=0.8)
