@@ -75,8 +75,9 @@ def _shard_worker(args):
     return str(Path(out_dir) / "manifest.yaml"), man.total_documents, man.total_tokens
 
 
-def shard_source(src, tokenizer_path, out_dir, name, workers=8, shard_bytes=1 << 30, field="text"):
-    """Parallel sharding of one JSONL file; returns the merged manifest (also written to <out_dir>/manifest.yaml)."""
+def shard_source(src, tokenizer_path, out_dir, name, workers=8, shard_bytes=1 << 30, field="text", prefix_tag="", manifest_name="manifest.yaml"):
+    """Parallel sharding of one JSONL file; returns the merged manifest (also written to <out_dir>/<manifest_name>).
+    ``prefix_tag`` (e.g. ``_w03``: one machine of a fan-out) keeps this call's shard directories apart from its siblings'."""
     import multiprocessing as mp
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -85,9 +86,10 @@ def shard_source(src, tokenizer_path, out_dir, name, workers=8, shard_bytes=1 <<
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
     jobs = []
+    sub = prefix_tag.strip("_") + "/" if prefix_tag else ""
     for seg in segment_plan(src, workers):
         a, b = (int(x) for x in seg["segment"].split(":"))
-        jobs.append((str(src), a, b, str(tokenizer_path), str(out / ("w%03d" % seg["worker"])), name, shard_bytes, field))
+        jobs.append((str(src), a, b, str(tokenizer_path), str(out / (sub + "w%03d" % seg["worker"])), name, shard_bytes, field))
     with mp.get_context("spawn").Pool(min(workers, os.cpu_count() or 1)) as pool:
         results = pool.map(_shard_worker, jobs)
     shards, first = [], None
@@ -95,10 +97,10 @@ def shard_source(src, tokenizer_path, out_dir, name, workers=8, shard_bytes=1 <<
         man = SourceManifest.load(mpath)
         first = first or man
         for sh in man.shards:  # worker order, then shard order: the merged manifest lists documents in file order
-            shards.append(ShardInfo("w%03d/%s" % (k, sh.prefix), sh.num_documents, sh.token_count, sh.bin_blake2b, sh.idx_blake2b))
+            shards.append(ShardInfo("%sw%03d/%s" % (sub, k, sh.prefix), sh.num_documents, sh.token_count, sh.bin_blake2b, sh.idx_blake2b))
     merged = SourceManifest(name=name, tokenizer_hash=first.tokenizer_hash, dtype=first.dtype, shards=shards,
                             raw_jsonl_blake2b={Path(src).name: blake2b_file(str(src))})
-    merged.save(out / "manifest.yaml")
+    merged.save(out / manifest_name)
     return merged
 
 
@@ -283,8 +285,9 @@ def swh_fetcher():
     return fetch
 
 
-def source_streams(source, target, fetch_blob=None, list_files=None, workers=64):
-    """[(Stream, quota)] of one named source. `fetch_blob` / `list_files` stand in for the network in tests."""
+def source_streams(source, target, fetch_blob=None, list_files=None, workers=64, worker_id=0, num_workers=1):
+    """[(Stream, quota)] of one named source. `fetch_blob` / `list_files` stand in for the network in tests. ``num_workers`` > 1
+    (the Stack): this process takes every ``num_workers``-th metadata row starting at ``worker_id``."""
     if source == "dclm":
         return [(Stream("dclm", hub_rows("mlfoundations/dclm-baseline-1.0"), text_of), None)]
     if source == "fineweb":
@@ -317,7 +320,7 @@ def source_streams(source, target, fetch_blob=None, list_files=None, workers=64)
         meta = hub_rows("bigcode/the-stack-v2-dedup")
 
         def rows(skip):
-            permissive = (r for r in meta(skip))
+            permissive = (r for i, r in enumerate(meta(skip)) if num_workers <= 1 or (skip + i) % num_workers == worker_id)
             for row, content in ordered_fetch(permissive, lambda r: fetch(r) if (r.get("detected_licenses") and set(map(str.lower, r["detected_licenses"])) <= PERMISSIVE) else None, workers):
                 yield {"text": content}
         return [(Stream("stack", rows, text_of), None)]
@@ -325,23 +328,46 @@ def source_streams(source, target, fetch_blob=None, list_files=None, workers=64)
 
 
 PULL_SOURCES = ("dclm", "fineweb", "stack", "proof", "dolma3_dolmino_mix")
+# the names the data recipes use for these sources (configs/data/*.yaml: manifest name and shard directory)
+CORPUS_NAME = {"dclm": "dclm_baseline", "fineweb": "fineweb_edu", "stack": "stack_v2_permissive", "proof": "proof_pile_2",
+               "dolma3_dolmino_mix": "dolma3_dolmino_mix"}
+SHORT_NAME = {v: k for k, v in CORPUS_NAME.items()}
+MIDTRAIN_SOURCES = ("dolma3_dolmino_mix",)   # built only when named with --only
 
 
-def build(counts, raw_dir, shard_dir, tokenizer, suffix="_proxy", shuffle_seed=0, workers=8, delete_raw=False, only=None, pull_fn=None, log=print):
+def build(counts, raw_dir, shard_dir, tokenizer, suffix="_proxy", shuffle_seed=0, workers=8, delete_raw=False, only=None, pull_fn=None, log=print,
+          concurrency=None, worker_id=0, num_workers=1):
     """pull -> shuffle -> shard per source; every stage is idempotent (manifest present: source done; `.shuffled` note: shuffle
-    done). Returns {source: manifest path}."""
+    done). Files carry the recipes' source names (``dclm`` -> ``<shard_dir>/dclm_baseline<suffix>``, manifest name
+    ``dclm_baseline``). ``concurrency``: {source: parallel fetches}. ``num_workers`` > 1 (the Stack only): this process is worker
+    ``worker_id`` of a fan-out over several machines - it pulls its slice into ``<name>_w<K>.jsonl`` and writes ``<name>_w<K>_*``
+    shards with ``manifest.w<K>.yaml``; ``pretrain-prepare-data merge-manifests --output-dir`` joins them afterwards.
+    Returns {source: manifest path}."""
     raw_dir, shard_dir = Path(raw_dir), Path(shard_dir)
+    only = [SHORT_NAME.get(x, x) for x in only] if only else None
+    concurrency = concurrency or {}
+    fan_out = num_workers > 1
+    if fan_out and only != ["stack"]:
+        raise ValueError("--num-workers > 1 is only supported with --only stack_v2_permissive")
     done = {}
     for source, n in counts.items():
-        if (only and source not in only) or n <= 0:
+        if (only and source not in only) or n <= 0 or (source in MIDTRAIN_SOURCES and not (only and source in only)):
             continue
-        out_dir = shard_dir / (source + suffix)
-        if (out_dir / "manifest.yaml").is_file():
-            log("[%s] manifest exists, skipping" % source)
-            done[source] = str(out_dir / "manifest.yaml")
+        name = CORPUS_NAME.get(source, source)
+        out_dir = shard_dir / (name + suffix)
+        tag = "_w%02d" % worker_id if fan_out else ""
+        manifest = out_dir / ("manifest.w%02d.yaml" % worker_id if fan_out else "manifest.yaml")
+        if manifest.is_file():
+            log("[%s] %s exists, skipping" % (source, manifest.name))
+            done[source] = str(manifest)
             continue
-        raw = raw_dir / (source + ".jsonl")
-        have, _ = (pull_fn or (lambda o, t, s: pull(o, t, source_streams(s, t), log=log)))(raw, n, source)
+        raw = raw_dir / (name + tag + ".jsonl")
+        if pull_fn is not None:
+            have, _ = pull_fn(raw, n, source)
+        else:
+            share = -(-n // num_workers) if fan_out else n
+            streams = source_streams(source, share, workers=concurrency.get(source, 64), worker_id=worker_id, num_workers=num_workers)
+            have, _ = pull(raw, share, streams, log=log)
         log("[%s] %d documents in %s" % (source, have, raw))
         mark = _note(raw, "shuffled")
         if not mark.is_file():
@@ -349,8 +375,8 @@ def build(counts, raw_dir, shard_dir, tokenizer, suffix="_proxy", shuffle_seed=0
             lines = shuffle_jsonl(raw, tmp, seed=shuffle_seed)
             os.replace(tmp, raw)
             mark.write_text(json.dumps({"seed": shuffle_seed, "buckets": 64, "lines": lines}))
-        shard_source(raw, tokenizer, out_dir, source, workers=workers)
-        done[source] = str(out_dir / "manifest.yaml")
+        shard_source(raw, tokenizer, out_dir, name, workers=workers, prefix_tag=tag, manifest_name=manifest.name)
+        done[source] = str(manifest)
         if delete_raw:
             for p in (raw, mark, _note(raw, "scanned"), _note(raw, "revision")):
                 if p.exists():
@@ -374,8 +400,18 @@ def main():
         b.add_argument("--docs-" + src.split("_")[0], type=int, dest="docs_" + src)
     b.add_argument("--tokenizer", default="data/tokenizer.json"); b.add_argument("--raw-dir", default="data/raw"); b.add_argument("--shard-dir", default="data/shards")
     b.add_argument("--shard-suffix", default="_proxy"); b.add_argument("--delete-raw", action="store_true"); b.add_argument("--shuffle-seed", type=int, default=0)
-    b.add_argument("--only", nargs="+", choices=sorted(PULL_SOURCES)); b.add_argument("--workers", type=int, default=8)
-    a = ap.parse_args()
+    b.add_argument("--only", nargs="+", choices=sorted(set(PULL_SOURCES) | set(CORPUS_NAME.values())),
+                   help="restrict to these sources (default: the four pretraining sources; dolma3_dolmino_mix runs only when named here)")
+    b.add_argument("--workers", type=int, default=8, help="tokenizer processes of the shard step")
+    b.add_argument("--stack-concurrency", type=int, default=64, help="parallel blob fetches for the Stack")
+    b.add_argument("--dolma3-concurrency", type=int, default=24, help="parallel file fetches for dolma3_dolmino_mix")
+    b.add_argument("--dolma3-shard-workers", type=int, default=8, help="tokenizer processes for dolma3_dolmino_mix's shard step")
+    b.add_argument("--worker-id", type=int, default=0, help="zero-based index of this machine in a Stack fan-out")
+    b.add_argument("--num-workers", type=int, default=1, help="machines of the Stack fan-out (1: no slicing); needs --only stack_v2_permissive")
+    argv = sys.argv[1:]
+    if argv and argv[0].startswith("--"):   # `build_corpus.py --preset ...`: the orchestration is the default command
+        argv = ["build"] + argv
+    a = ap.parse_args(argv)
     if a.cmd == "shuffle":
         print(json.dumps({"lines": shuffle_jsonl(a.src, a.dst, a.seed, a.buckets)}))
     elif a.cmd == "plan":
@@ -399,8 +435,15 @@ def main():
         if not counts:
             ap.error("build needs --preset or at least one --docs-<source>")
         try:
-            print(json.dumps(build(counts, a.raw_dir, a.shard_dir, a.tokenizer, a.shard_suffix, a.shuffle_seed, a.workers, a.delete_raw, a.only,
-                                   log=lambda m: print(m, file=sys.stderr))))
+            if a.num_workers > 1 and not 0 <= a.worker_id < a.num_workers:
+                ap.error("--worker-id=%d out of range for --num-workers=%d" % (a.worker_id, a.num_workers))
+            only = [SHORT_NAME.get(x, x) for x in a.only] if a.only else None
+            workers = a.dolma3_shard_workers if only == ["dolma3_dolmino_mix"] else a.workers
+            print(json.dumps(build(counts, a.raw_dir, a.shard_dir, a.tokenizer, a.shard_suffix, a.shuffle_seed, workers, a.delete_raw, only,
+                                   log=lambda m: print(m, file=sys.stderr), concurrency={"stack": a.stack_concurrency, "dolma3_dolmino_mix": a.dolma3_concurrency},
+                                   worker_id=a.worker_id, num_workers=a.num_workers)))
+        except ValueError as e:
+            ap.error(str(e))
         except ImportError as e:
             print("build: %s is not installed (the pullers need `datasets`, `huggingface_hub`, and `boto3` for the Stack)" % e.name, file=sys.stderr)
             return 2

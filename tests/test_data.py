@@ -208,7 +208,24 @@ def test_corpus_pulls_resume_where_they_stopped_and_the_build_stages_are_idempot
 
     done = bc.build({"dclm": 120, "proof": 0, "fineweb": 80}, tmp_path / "r", tmp_path / "s", tok, workers=2, only=["dclm", "fineweb"], pull_fn=fake_pull, log=lambda m: None)
     assert pulled == ["dclm", "fineweb"] and set(done) == {"dclm", "fineweb"}
-    assert SourceManifest.load(done["dclm"]).total_documents == 120 and (tmp_path / "r" / "dclm.jsonl.shuffled").is_file()
-    assert sorted(json.loads(l)["text"] for l in (tmp_path / "r" / "dclm.jsonl").read_text().splitlines()) == sorted(docs[:120])
+    man = SourceManifest.load(done["dclm"])
+    assert man.total_documents == 120 and man.name == "dclm_baseline" and (tmp_path / "r" / "dclm_baseline.jsonl.shuffled").is_file()
+    assert done["dclm"] == str(tmp_path / "s" / "dclm_baseline_proxy" / "manifest.yaml")       # the directory the data recipes name
+    assert sorted(json.loads(l)["text"] for l in (tmp_path / "r" / "dclm_baseline.jsonl").read_text().splitlines()) == sorted(docs[:120])
     again = bc.build({"dclm": 120, "fineweb": 80}, tmp_path / "r", tmp_path / "s", tok, workers=2, pull_fn=fake_pull, log=lambda m: None)
     assert again == done and pulled == ["dclm", "fineweb"]                   # manifests exist: nothing pulled or sharded again
+    # the recipes' long names select sources too; a midtraining source is built only when named; a Stack fan-out worker writes
+    # tagged files that merge-manifests joins
+    assert bc.build({"dclm": 5, "dolma3_dolmino_mix": 5}, tmp_path / "r2", tmp_path / "s2", tok, workers=1, only=["dclm_baseline"], pull_fn=fake_pull,
+                    log=lambda m: None).keys() == {"dclm"}
+    assert "dolma3_dolmino_mix" not in bc.build({"dolma3_dolmino_mix": 5}, tmp_path / "r2", tmp_path / "s2", tok, workers=1, pull_fn=fake_pull, log=lambda m: None)
+    with pytest.raises(ValueError):
+        bc.build({"dclm": 5}, tmp_path / "r3", tmp_path / "s3", tok, workers=1, only=["dclm"], pull_fn=fake_pull, log=lambda m: None, num_workers=2)
+    for k in range(2):
+        part = bc.build({"stack": 40}, tmp_path / "r3", tmp_path / "s3", tok, suffix="", workers=1, only=["stack_v2_permissive"], pull_fn=fake_pull,
+                        log=lambda m: None, worker_id=k, num_workers=2)
+        assert part["stack"].endswith("stack_v2_permissive/manifest.w%02d.yaml" % k) and (tmp_path / "r3" / ("stack_v2_permissive_w%02d.jsonl" % k)).is_file()
+    from open_transformers_b200.data.prepare import merge_worker_manifests
+
+    merged = merge_worker_manifests(tmp_path / "s3" / "stack_v2_permissive", expected_workers=2)
+    assert merged.total_documents == 80 and merged.name == "stack_v2_permissive" and all(s.prefix.startswith(("w00/", "w01/")) for s in merged.shards)
