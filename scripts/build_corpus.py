@@ -409,7 +409,7 @@ def main():
     b.add_argument("--worker-id", type=int, default=0, help="zero-based index of this machine in a Stack fan-out")
     b.add_argument("--num-workers", type=int, default=1, help="machines of the Stack fan-out (1: no slicing); needs --only stack_v2_permissive")
     argv = sys.argv[1:]
-    if argv and argv[0].startswith("--"):   # `build_corpus.py --preset ...`: the orchestration is the default command
+    if argv and argv[0].startswith("--") and argv[0] != "--help":   # `build_corpus.py --preset ...`: the orchestration is the default command
         argv = ["build"] + argv
     a = ap.parse_args(argv)
     if a.cmd == "shuffle":
