@@ -14,6 +14,7 @@ Run directory ``<output_dir>/<run_id>/``: ``checkpoints/``, ``checkpoints/state_
 from __future__ import annotations
 
 import json
+import math
 import logging
 import os
 import signal
@@ -268,6 +269,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
             consumed += plan.tokens_this_step
             step += 1
 
+            compute_ms = (time.perf_counter() - t_step) * 1e3  # forward, backward, reduction, clip, update: before hash and checkpoint
             exit_due = _emergency_exit_requested(world, dev, engine.host_group)
             final_step = consumed >= train_cfg.total_tokens or (max_steps is not None and step >= max_steps)
             hash_due = sh_cfg.every_n_steps > 0 and step % sh_cfg.every_n_steps == 0
@@ -300,11 +302,16 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                 engine.complete_compute_weights()  # the statistics read whole weights (a collective in gather mode, else nothing)
             if rank == 0:
                 tps = plan.tokens_this_step / (wall_ms / 1e3)
-                metrics.log({**phases, "step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_sum / max(n_mb, 1), "lr": lr,
+                z_mean = z_sum / max(n_mb, 1)
+                mine_ce = sum(local_ce) / max(len(local_ce), 1)              # this process's micro-batches (the reference's rank-local keys)
+                mine_z = sum(float(z) for z in zs) / max(len(zs), 1)
+                metrics.log({**phases, "step": step, "consumed_tokens": consumed, "loss": loss_mean, "z_loss": z_mean, "lr": lr,
+                             "accum_steps": accum, "loss_ce": mine_ce, "loss_zloss": mine_z, "perplexity": math.exp(min(mine_ce, 700.0)),
+                             "loss_ce_global": loss_mean, "loss_zloss_global": z_mean, "perplexity_global": math.exp(min(loss_mean, 700.0)),
                              "grad_norm_pre_clip": grad_norm, "clip_coef": clip, "skipped": skipped,
                              "skipped_steps_total": spike.state.skipped_steps, "tokens_per_sec": tps, "tokens_per_sec_per_gpu": tps / world,
-                             "mfu": mfu(tps / world, flops_tok), "step_wall_time_ms": wall_ms, "hash_time_ms": t_hash,
-                             "ckpt_save_time_ms": t_ckpt, "state_hash": step_hash, "microbatches": M}, step=step)
+                             "mfu": mfu(tps / world, flops_tok), "step_compute_time_ms": compute_ms, "step_wall_time_ms": wall_ms,
+                             "hash_time_ms": t_hash, "ckpt_save_time_ms": t_ckpt, "state_hash": step_hash, "microbatches": M}, step=step)
                 gl = train_cfg.grad_norm_log
                 if gl.every_n_steps > 0 and step % gl.every_n_steps == 0:
                     from ..obs import grad_norm_log as GN

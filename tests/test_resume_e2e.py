@@ -185,6 +185,11 @@ def test_replay_loss_log_equals_the_training_metrics_bit_for_bit(runs, tmp_path)
     assert [m["step"] for m in mine] == [1, 2, 3, 4]
     assert [m["loss"] for m in mine] == [t["loss"] for t in theirs]
     assert [m["grad_norm"] for m in mine] == [t["grad_norm_pre_clip"] for t in theirs]
+    # metrics.jsonl carries the reference's keys (src/pretrain/train/loop.py, metrics.log) beside this package's own
+    wanted = {"consumed_tokens", "lr", "accum_steps", "grad_norm_pre_clip", "loss_ce", "loss_zloss", "perplexity", "loss_ce_global", "loss_zloss_global",
+              "perplexity_global", "tokens_per_sec", "tokens_per_sec_per_gpu", "mfu", "step_compute_time_ms", "step_wall_time_ms", "hash_time_ms",
+              "ckpt_save_time_ms", "skipped_steps_total"}
+    assert wanted <= set(theirs[0]) and theirs[0]["loss_ce_global"] == theirs[0]["loss"] and theirs[0]["step_compute_time_ms"] <= theirs[0]["step_wall_time_ms"]
 
 
 def test_skipped_steps_are_replayed_as_skips_and_a_halt_ends_the_run(tmp_path):
