@@ -64,6 +64,9 @@ class CheckpointMeta:
     torch_version: str = ""
     numpy_version: str = ""
     kernel_env: dict = dataclasses.field(default_factory=dict)
+    # REPOP_* variables of the writing process: the reference's meta.json field of that name (its kernel library's switches);
+    # this package's own switches are `kernel_env`
+    repop_env: dict = dataclasses.field(default_factory=dict)
     native_source_digests: dict = dataclasses.field(default_factory=dict)   # sha256 of each native library's sources + flags
     windows_emitted: int = 0
     physical_world_size: int = 1

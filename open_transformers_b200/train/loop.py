@@ -179,6 +179,7 @@ def train(cfg: RootConfig, resume_from: str | None = None, *, device: str | None
                               dp_replicate=engine.dp_replicate, dp_shard=engine.dp_shard, tensor_digest=sh_cfg.tensor_digest,
                               rewarm_anchor_tokens=rewarm_anchor, seed=cfg.run.seed, torch_version=torch.__version__,
                               numpy_version=np.__version__, kernel_env={k: v for k, v in os.environ.items() if k.startswith("OTB_")},
+                              repop_env={k: v for k, v in os.environ.items() if k.startswith("REPOP_")},
                               windows_emitted=loader.state().windows_emitted, physical_world_size=world,
                               mixed_precision=cfg.run.mixed_precision)
 
