@@ -381,6 +381,9 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
                    "match": (last_hash == expected) if expected else None})
     if loss_log:
         Path(loss_log).write_text("\n".join(json.dumps(r) for r in loss_rows) + "\n")
+    diff_against = os.environ.get("PRETRAIN_AUDIT_DIFF_CKPT") or os.environ.get("REPOP_AUDIT_DIFF_CKPT")
+    if diff_against:
+        result["diff"] = diff_against_checkpoint(engine, diff_against)
     if save_checkpoint_dir:
         ck = Checkpointer(save_checkpoint_dir)
         m = CheckpointMeta(consumed_tokens=consumed, step=step, config_resolved=resolved_config_json(cfg), chained_hash=chained,
@@ -394,6 +397,39 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         result["saved_checkpoint"] = str(d)
     engine.close()
     return result
+
+
+def diff_against_checkpoint(engine, checkpoint: str, top: int = 15) -> dict:
+    """Where a replay and a checkpoint part ways, tensor by tensor (a diagnostic for a hash mismatch; it changes nothing of
+    the replay): the largest absolute difference of every master weight and of both moments between the replayed state and
+    the checkpoint named by PRETRAIN_AUDIT_DIFF_CKPT (the reference's REPOP_AUDIT_DIFF_CKPT is read too,
+    src/pretrain/cli/audit_replay.py:2725-2760). Returns {"tensors", "differing", "top": [[max |delta|, kind, name], ...]}."""
+    import torch
+
+    from ..train.checkpoint import optimizer_state_names
+    from .dcp_safetensors import read_dcp
+
+    state = read_dcp(Path(checkpoint) / "dcp")
+    names = optimizer_state_names(checkpoint)          # optimizer-state key (an index as a string) -> parameter name
+    rows = []
+    mine = dict(engine.named_master())
+    for name, theirs in (state.get("model") or {}).items():
+        if name in mine:
+            rows.append((float((mine[name].detach().float().cpu() - theirs.float()).abs().max()), "param", name))
+    moments = engine.optimizer_state()
+    for key, st in ((state.get("optim") or {}).get("state") or {}).items():
+        name = names.get(str(key), str(key))
+        if name not in moments:
+            continue
+        for kind in ("exp_avg", "exp_avg_sq"):
+            if kind in st and torch.is_tensor(st[kind]):
+                rows.append((float((moments[name][kind].detach().float().cpu() - st[kind].float()).abs().max()), "optim." + kind, name))
+    rows.sort(key=lambda r: -r[0])
+    differing = sum(1 for r in rows if r[0] > 0)
+    log.info("DIFF against %s: %d of %d tensors differ; largest differences:", checkpoint, differing, len(rows))
+    for d, kind, name in rows[:top]:
+        log.info("  max|delta|=%.6e  %s  %s", d, kind, name)
+    return {"against": str(checkpoint), "tensors": len(rows), "differing": differing, "top": [[d, kind, name] for d, kind, name in rows[:top]]}
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -185,6 +185,17 @@ def test_replay_loss_log_equals_the_training_metrics_bit_for_bit(runs, tmp_path)
     assert [m["step"] for m in mine] == [1, 2, 3, 4]
     assert [m["loss"] for m in mine] == [t["loss"] for t in theirs]
     assert [m["grad_norm"] for m in mine] == [t["grad_norm_pre_clip"] for t in theirs]
+    # the tensor-level diagnostic: against the checkpoint of the replayed step nothing differs, against an earlier one everything does
+    import os
+
+    ck4, ck2 = whole["run_dir"] + "/checkpoints/step_000000004", whole["run_dir"] + "/checkpoints/step_000000002"
+    for env_name, against, want_zero in (("PRETRAIN_AUDIT_DIFF_CKPT", ck4, True), ("REPOP_AUDIT_DIFF_CKPT", ck2, False)):
+        os.environ[env_name] = against
+        try:
+            d = audit_replay(from_init=True, descriptor_checkpoint=ck4, data_root=tmp, until_step=4)["diff"]
+        finally:
+            del os.environ[env_name]
+        assert d["tensors"] > 0 and (d["differing"] == 0) == want_zero and len(d["top"]) <= 15 and d["top"][0][1] in ("param", "optim.exp_avg", "optim.exp_avg_sq")
     # metrics.jsonl carries the reference's keys (src/pretrain/train/loop.py, metrics.log) beside this package's own
     wanted = {"consumed_tokens", "lr", "accum_steps", "grad_norm_pre_clip", "loss_ce", "loss_zloss", "perplexity", "loss_ce_global", "loss_zloss_global",
               "perplexity_global", "tokens_per_sec", "tokens_per_sec_per_gpu", "mfu", "step_compute_time_ms", "step_wall_time_ms", "hash_time_ms",
