@@ -26,6 +26,9 @@ from pathlib import Path
 
 log = logging.getLogger("pretrain.audit")
 MAX_AUDIT_WORLD = 64
+# The replica fold of the reduction kernels is the pair tree with strides 1, 2, 4, ... (parallel/deterministic_reduce.py);
+# checkpoints written before the tag was renamed carry its first name.
+REPLICATE_REDUCE_ALGOS = {"stride_pair_tree", "binary_blocks_tree"}
 _HEX64 = re.compile(r"^[0-9a-fA-F]{64}$")
 # kernel-selecting environment a checkpoint may ask the replay to re-apply; anything else is refused
 ALLOWED_KERNEL_ENV = {"OTB_EXECUTION_MODE", "OTB_ATTN_BLOCK", "OTB_TENSOR_DIGEST"}
@@ -209,6 +212,9 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
             raise AuditError("recorded topology (world %d = replicate %d x shard %d) is out of bounds" % (V, R, S))
         if meta.clip_algo != "global" or meta.grad_norm_algo != "deterministic_per_tensor_sos_v1":
             raise AuditError("unsupported clip / norm algorithm in checkpoint metadata")
+        if meta.replicate_reduce_algo not in REPLICATE_REDUCE_ALGOS:
+            raise AuditError("this replay knows the replica orders %s; the checkpoint was trained with replicate_reduce_algo=%r"
+                             % (sorted(REPLICATE_REDUCE_ALGOS), meta.replicate_reduce_algo))
         cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = V, S, R
     elif cfg.run.virtual_dp_size == 0:
         raise AuditError("--from-init with --config-name needs run.virtual_dp_size (the topology to emulate)")

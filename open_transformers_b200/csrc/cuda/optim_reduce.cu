@@ -6,7 +6,7 @@
 //  grad_reduce  (pull reduce-scatter + replica tree + squared-norm partials)
 //     For every element this GPU owns:
 //        inner_r = (((g[r,0] + g[r,1]) + ...) + g[r,S-1]) * (1/S)       ascending shard rank
-//        outer   = pair_tree(inner_0 .. inner_{R-1})   * (1/R)          binary blocks over replicas
+//        outer   = pair_tree(inner_0 .. inner_{R-1})   * (1/R)          strides 1, 2, 4, ... over replicas
 //     g[r,s] is virtual rank (r*S+s)'s fp32 gradient buffer, local or a peer's. The same pass
 //     writes `outer` and folds it into the squared-norm partial of its 8192-element chunk
 //     (thread t takes elements j*2048 + t*8 .. +7, fma chain, block_tree_sum).

@@ -52,3 +52,18 @@ def sliding_window_nll(model, tokens: torch.Tensor, seq_len: int, stride: int | 
 def perplexity(model, tokens: torch.Tensor, seq_len: int, stride: int | None = None, batch_windows: int = 1) -> float:
     nll, n = sliding_window_nll(model, tokens, seq_len, stride, batch_windows=batch_windows)
     return math.exp(nll / max(n, 1))
+
+
+def compute_perplexity(model, held_out_prefix, seq_len: int, device=None, micro_batch_size: int = 1, max_tokens: int | None = None) -> float:
+    """Perplexity of a held-out ``.bin/.idx`` shard: its documents joined in order, scored in windows of ``seq_len``
+    (``micro_batch_size`` windows per forward pass). (entry point of the reference's src/pretrain/eval/perplexity.py:22)"""
+    import numpy as np
+
+    from ..data.indexed_dataset import IndexedDatasetReader
+
+    r = IndexedDatasetReader(held_out_prefix)
+    toks = np.concatenate([np.asarray(r.document(i), dtype=np.int64) for i in range(len(r))])
+    if max_tokens:
+        toks = toks[:max_tokens]
+    return perplexity(model, torch.from_numpy(toks), seq_len, None, micro_batch_size)
+

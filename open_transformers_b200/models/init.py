@@ -36,3 +36,8 @@ def init_weights(model: nn.Module, seed: int, std: float | None = None) -> None:
         for m in model.modules():
             if isinstance(m, QuantLinear) and m.method == "lsq":
                 m.weight_scale.copy_(m.lsq_optimal_scale(m.weight.detach().float()))
+
+
+def init_weights_seeded(model: nn.Module, seed: int) -> None:
+    """``init_weights`` with the model's configured spread: same seed, same bytes, on every device."""
+    init_weights(model, seed)

@@ -191,6 +191,16 @@ class RoPE(nn.Module):
         return self.rope_cos[:seq_len], self.rope_sin[:seq_len]
 
 
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """The rotation written out on tensors: ``x`` [..., T, H, head_dim], tables [T, head_dim/2]; element pairs
+    (2j, 2j+1) of every head turn by the angle of position t and frequency j. The training path applies the same rotation
+    inside the fused QK-norm / RoPE kernel; this form serves tests and tools.
+    (reference src/pretrain/model/modules/rope.py:103-125)"""
+    even, odd = x[..., 0::2], x[..., 1::2]
+    c, s = cos.unsqueeze(-2), sin.unsqueeze(-2)
+    return torch.stack([even * c - odd * s, even * s + odd * c], -1).flatten(-2)
+
+
 @ROPE.register("rope_yarn")
 class RoPEYarn(RoPE):
     """NTK-by-parts (YaRN) frequency interpolation for long-context annealing: low-frequency

@@ -62,3 +62,10 @@ def compute_z_loss(logits: torch.Tensor, cfg_or_coeff) -> torch.Tensor:
     if coeff == 0.0:
         return torch.zeros((), dtype=torch.float32, device=logits.device)
     return _ZLossFn.apply(logits, coeff)
+
+
+def compute_z_loss_inert(logits: torch.Tensor, cfg_or_coeff) -> torch.Tensor:
+    """The value of the z-loss without its gradient: the regime of runs made before the term had a backward pass, kept so
+    that such a run's logged loss can be recomputed. (reference src/pretrain/model/z_loss.py:132-146)"""
+    with torch.no_grad():
+        return compute_z_loss(logits.detach(), cfg_or_coeff)

@@ -9,6 +9,10 @@ from pathlib import Path
 B200_BF16_DENSE_PEAK = 2.25e15  # nominal dense bf16 FLOP/s of one B200
 
 
+def tokens_per_sec(tokens: int, elapsed_s: float) -> float:
+    return tokens / max(elapsed_s, 1e-9)
+
+
 def transformer_flops_per_token(n_layers: int, d_model: int, seq_len: int, vocab_size: int) -> float:
     """Forward + backward FLOPs per token: 72 L d^2 (dense blocks) + 12 L s d (attention) + 6 V d (head)
     (reference src/pretrain/obs/metrics.py:23-47)."""

@@ -46,20 +46,34 @@ class LRSchedule:
         return self.peak + (self.end - self.peak) * t
 
 
+def _warmup_tokens(sched, train) -> int:
+    return sched.warmup_steps * train.global_batch_tokens.warmup
+
+
+def cosine_schedule(sched, train, optim) -> LRSchedule:
+    return LRSchedule("cosine", optim.peak_lr, optim.peak_lr * sched.min_lr_frac, _warmup_tokens(sched, train), train.total_tokens)
+
+
+def wsd_schedule(sched, train, optim) -> LRSchedule:
+    return LRSchedule("wsd", optim.peak_lr, optim.peak_lr * sched.wsd_decay_to_frac, _warmup_tokens(sched, train), train.total_tokens,
+                      decay_start_frac=sched.wsd_decay_start_frac)
+
+
+def linear_anneal_schedule(sched, train, optim) -> LRSchedule:
+    if train.total_tokens <= sched.anneal_start_tokens:
+        raise ValueError("linear_anneal: train.total_tokens (%d) is absolute (pre-training + mid-training) and must exceed "
+                         "schedule.anneal_start_tokens (%d)" % (train.total_tokens, sched.anneal_start_tokens))
+    return LRSchedule("linear_anneal", optim.peak_lr, optim.peak_lr * sched.min_lr_frac, _warmup_tokens(sched, train), train.total_tokens,
+                      anneal_start_tokens=sched.anneal_start_tokens)
+
+
+SCHEDULES = {"cosine": cosine_schedule, "wsd": wsd_schedule, "linear_anneal": linear_anneal_schedule}
+
+
 def build_schedule(sched, train, optim) -> LRSchedule:
-    warm = sched.warmup_steps * train.global_batch_tokens.warmup
-    peak = optim.peak_lr
-    if sched.name == "cosine":
-        return LRSchedule("cosine", peak, peak * sched.min_lr_frac, warm, train.total_tokens)
-    if sched.name == "wsd":
-        return LRSchedule("wsd", peak, peak * sched.wsd_decay_to_frac, warm, train.total_tokens, decay_start_frac=sched.wsd_decay_start_frac)
-    if sched.name == "linear_anneal":
-        if train.total_tokens <= sched.anneal_start_tokens:
-            raise ValueError("linear_anneal: train.total_tokens (%d) is absolute (pre-training + mid-training) and must exceed "
-                             "schedule.anneal_start_tokens (%d)" % (train.total_tokens, sched.anneal_start_tokens))
-        return LRSchedule("linear_anneal", peak, peak * sched.min_lr_frac, warm, train.total_tokens,
-                          anneal_start_tokens=sched.anneal_start_tokens)
-    raise ValueError("unknown schedule %r" % sched.name)
+    if sched.name not in SCHEDULES:
+        raise ValueError("unknown schedule %r" % sched.name)
+    return SCHEDULES[sched.name](sched, train, optim)
 
 
 def rewarm_factor(consumed_tokens: int, anchor_tokens: int | None, rewarm_tokens: int) -> float:

@@ -37,6 +37,12 @@ def grad_accum_steps(consumed_tokens: int, train, dp_world_size: int) -> int:
     return max(1, -(-current_global_batch_tokens(consumed_tokens, train) // per))
 
 
+def tokens_per_optimizer_step(consumed_tokens: int, train, *, dp_world_size: int) -> int:
+    """Tokens one optimizer step consumes under the legacy per-rank accumulation rule (the canonical stream uses
+    ``canonical_tokens_per_step``)."""
+    return grad_accum_steps(consumed_tokens, train, dp_world_size) * train.micro_batch_size * train.seq_len * max(dp_world_size, 1)
+
+
 def owner_rank(microbatch: int, *, world_size: int) -> int:
     return microbatch % max(world_size, 1)
 

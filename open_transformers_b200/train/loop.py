@@ -91,6 +91,14 @@ def _assert_same_on_all_ranks(payload: str, what: str, world: int) -> None:
         raise RuntimeError("%s differs between ranks: %s" % (what, sorted(set(objs))))
 
 
+def cross_entropy_loss(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Mean cross-entropy of full-vocabulary logits in the canonical summation order (no z-loss, no gradient side effects).
+    The step itself uses the fused CE + z-loss; this is the plain form. (reference src/pretrain/train/loop.py:155-169)"""
+    from ..models.fused_loss import cross_entropy
+
+    return cross_entropy(logits, labels)
+
+
 def _append_jsonl(path: Path, row: dict) -> None:
     path.parent.mkdir(parents=True, exist_ok=True)
     with open(path, "a", encoding="utf-8") as f:

@@ -115,6 +115,12 @@ def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
     assert rc == 0 and out.strip() == hash_checkpoint(ck) and len(out.strip()) == 64
     rc, weights_only = _run(hash_main, [ck, "--weights-only"], capsys)
     assert weights_only.strip() != out.strip()
+    # --config-name checks the checkpoint against that recipe's model: the run's own shape passes, the stock one does not
+    shape = ["model.n_layers=1", "model.d_model=128", "model.n_heads=2", "model.n_kv_heads=2", "model.ffn_intermediate=256", "model.vocab_size=256"]
+    rc, again = _run(hash_main, [ck, "--config-name", "tiny_cpu", "--override", *shape], capsys)
+    assert rc == 0 and again.strip() == out.strip()
+    with pytest.raises(ValueError, match="does not match configuration tiny_cpu"):
+        hash_main([ck, "--config-name", "tiny_cpu"])
     assert hash_checkpoint(res["run_dir"] + "/checkpoints/step_000000003") != hash_checkpoint(ck)
     rc, out = _run(inspect_main, [ck, "--full-config"], capsys)
     assert rc == 0 and "bytes, --full-config" not in out and "vocab_size" in out
@@ -126,7 +132,6 @@ def test_synthetic_sources_step_windows_and_checkpoint_tools(tmp_path, capsys):
     assert rc == 0 and hash_checkpoint(json.loads(out)["dir"]) == hash_checkpoint(ck)
 
     # the reference's command names and switches: to-safetensors / from-safetensors, --verify, --keys, --top-level-key
-    import pytest
     import torch
     from safetensors import safe_open
     from safetensors.torch import save_file

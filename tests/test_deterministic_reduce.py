@@ -131,3 +131,51 @@ def test_reduction_under_the_backward_pass_gives_the_one_shot_bytes(tmp_path, mo
         assert epochs == 3
         for (n0, r0, s0, h0), (n1, r1, s1, h1) in zip(plain, over):
             assert n0 == n1 and torch.equal(r0, r1) and torch.equal(s0, s1) and h0 == h1
+
+
+# ---- the whole-tensor statement of the same orders (parallel/deterministic_reduce.py)
+
+def test_whole_tensor_fold_equals_the_kernel_twin_bit_for_bit():
+    from open_transformers_b200.parallel import deterministic_reduce as DR
+
+    for S, R in [(1, 1), (3, 2), (2, 3), (1, 5), (2, 6), (1, 7), (4, 8), (1, 9), (1, 11), (2, 13)]:
+        rng = np.random.default_rng(77 * S + R)
+        n = CHUNK + 37
+        grads = [(rng.standard_normal(n) * 10.0 ** rng.integers(-3, 3)).astype(np.float32) for _ in range(S * R)]
+        got, _ = native_reduce(grads, S, R, n)
+        want = DR.fold_virtual_ranks([torch.from_numpy(g) for g in grads], S, R).numpy()
+        assert got.tobytes() == want.tobytes(), (S, R)
+
+
+def test_pair_tree_and_binary_blocks_agree_up_to_two_blocks_and_not_beyond():
+    from open_transformers_b200.parallel import deterministic_reduce as DR
+
+    class Sym:
+        def __init__(self, s):
+            self.s = s
+
+        def __add__(self, o):
+            return Sym("(%s+%s)" % (self.s, o.s))
+
+    assert DR.binary_blocks(6) == [4, 2] and DR.binary_blocks(7) == [4, 2, 1] and DR.binary_blocks(8) == [8] and DR.binary_blocks(1) == [1]
+    for n in range(1, 17):
+        a = DR.tree_reduce_sum([Sym(str(i)) for i in range(n)]).s
+        b = DR.binary_blocks_sum([Sym(str(i)) for i in range(n)]).s
+        assert a == pair_tree([str(i) for i in range(n)], lambda x, y: "(%s+%s)" % (x, y))
+        assert (a == b) == (bin(n).count("1") <= 2), (n, a, b)
+    assert DR.binary_blocks_sum([Sym(str(i)) for i in range(7)]).s == "((((0+1)+(2+3))+(4+5))+6)"
+    with pytest.raises(ValueError):
+        DR.tree_reduce_sum([])
+
+
+def test_shard0_helpers():
+    from open_transformers_b200.parallel import deterministic_reduce as DR
+
+    t = torch.arange(10 * 3, dtype=torch.float32).view(10, 3)
+    assert DR.shard0_full_chunk_size(10, 4) == 3 and DR.shard0_full_chunk_size(8, 4) == 2 and DR.shard0_full_chunk_size(3, 1) == 3
+    parts = [DR.shard0_logical_chunk(t, r, 4) for r in range(4)]
+    assert [p.shape[0] for p in parts] == [3, 3, 3, 1] and torch.equal(torch.cat(parts), t)
+    padded = [DR.shard0_chunk(t, r, 4) for r in range(4)]
+    assert all(p.shape == (3, 3) for p in padded) and torch.equal(padded[3][0], t[9]) and float(padded[3][1:].abs().sum()) == 0.0
+    # more shards than rows: the trailing shards are empty / all padding
+    assert DR.shard0_logical_chunk(t[:2], 3, 4).shape[0] == 0 and DR.shard0_chunk(t[:2], 3, 4).shape == (1, 3)

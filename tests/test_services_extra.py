@@ -478,3 +478,82 @@ def test_gather_mode_plan_splits_the_owned_chunks_and_describes_every_projection
     assert starts.unique().numel() == starts.numel()                     # no chunk in both tables
     pulled_elems = sum(s.length for s in lay.segments[eng.seg_lo:eng.seg_hi] if s.param in set(pg["pulled_params"]))
     assert int(pull[1].sum()) == pulled_elems
+
+
+def test_small_helpers_under_the_reference_names(tmp_path):
+    """tokens_per_sec, tokens_per_optimizer_step, rank / world_size / is_main_process outside a process group, and
+    compute_perplexity over a held-out shard."""
+    import math
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    from open_transformers_b200.data.indexed_dataset import IndexedDatasetWriter
+    from open_transformers_b200.eval.perplexity import compute_perplexity
+    from open_transformers_b200.obs.metrics import tokens_per_sec
+    from open_transformers_b200.parallel import env
+    from open_transformers_b200.train.batch_schedule import grad_accum_steps, tokens_per_optimizer_step
+
+    assert tokens_per_sec(1000, 0.5) == 2000.0 and tokens_per_sec(1, 0.0) > 9e8
+    assert env.rank() == 0 and env.world_size() == 1 and env.is_main_process()
+    from open_transformers_b200.config.schema import GlobalBatchTokens, TrainConfig
+
+    train = TrainConfig(micro_batch_size=2, seq_len=16, global_batch_tokens=GlobalBatchTokens(warmup=200, main=512, late=1024),
+                        warmup_to_main_at_tokens=1000, main_to_late_at_tokens=5000)
+    assert grad_accum_steps(0, train, 2) == 4          # ceil(200 / (2 * 16 * 2))
+    assert tokens_per_optimizer_step(0, train, dp_world_size=2) == 4 * 2 * 16 * 2
+    assert tokens_per_optimizer_step(2000, train, dp_world_size=2) == 512 and tokens_per_optimizer_step(9000, train, dp_world_size=4) == 1024
+
+    class Uniform(torch.nn.Module):
+        def __init__(self, vocab):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.zeros(1))
+            self.vocab = vocab
+
+        def forward(self, ids):
+            return SimpleNamespace(logits=torch.zeros(ids.shape + (self.vocab,), dtype=torch.float32) + self.w)
+
+    with IndexedDatasetWriter(tmp_path / "held") as w:
+        rng = np.random.default_rng(0)
+        for n in (9, 17, 5):
+            w.add_document(rng.integers(0, 64, n))
+    ppl = compute_perplexity(Uniform(64), tmp_path / "held", seq_len=8, micro_batch_size=2)
+    assert math.isclose(ppl, 64.0, rel_tol=1e-5)
+
+
+def test_tensor_level_helpers_rope_zloss_norm():
+    """apply_rope equals the fused QK-norm / RoPE kernel with the norm switched off; the inert z-loss has the value and no
+    gradient; the total-norm helpers agree with the clip module; seeded init repeats."""
+    from types import SimpleNamespace
+
+    from open_transformers_b200.models.init import init_weights_seeded
+    from open_transformers_b200.models.modules.core import apply_rope
+    from open_transformers_b200.models.z_loss import compute_z_loss, compute_z_loss_inert
+    from open_transformers_b200.ops import functional as K
+    from open_transformers_b200.parallel import deterministic_reduce as DR
+    from open_transformers_b200.train.global_clip import deterministic_global_norm
+    from open_transformers_b200.train.loop import cross_entropy_loss
+
+    g = torch.Generator().manual_seed(4)
+    B, T, H, D = 2, 24, 3, 16
+    x = torch.randn(B, T, H * D, generator=g)
+    cos, sin = K.rope_tables(T, D, 10000.0, "cpu")
+    fused = K.qknorm_rope_fwd(x.reshape(B * T, H * D).clone(), cos, sin, H, D, T, False, 1e-5)[0]
+    assert torch.allclose(apply_rope(x.view(B, T, H, D), cos, sin).reshape(B, T, H * D), fused.reshape(B, T, H * D), atol=1e-6)
+
+    logits = torch.randn(6, 32, generator=g, requires_grad=True)
+    cfg = SimpleNamespace(enabled=True, coeff=1e-3)
+    inert = compute_z_loss_inert(logits, cfg)
+    assert not inert.requires_grad and torch.equal(inert, compute_z_loss(logits, cfg).detach())
+    labels = torch.randint(0, 32, (6,), generator=g)
+    assert torch.allclose(cross_entropy_loss(logits.detach(), labels), torch.nn.functional.cross_entropy(logits.detach(), labels), atol=1e-6)
+
+    grads = [("a", torch.randn(33, 8, generator=g)), ("b", torch.randn(16, generator=g))]
+    norm, per = deterministic_global_norm(grads, 2)
+    assert DR.deterministic_total_norm(grads, 2) == norm == DR.audit_total_norm(grads, 2)
+    assert DR.grad_sum_of_squares(grads, 2).tobytes() == per.tobytes()
+    assert abs(norm - float(torch.cat([t.flatten() for _, t in grads]).norm())) < 1e-4
+
+    m1, m2 = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
+    init_weights_seeded(m1, 5), init_weights_seeded(m2, 5)
+    assert torch.equal(m1.weight, m2.weight) and float(m1.bias.detach().abs().sum()) == 0.0
