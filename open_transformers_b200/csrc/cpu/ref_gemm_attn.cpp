@@ -207,7 +207,9 @@ namespace {
 // columns of a row sit in SIMD lanes (B is repacked K-major in 16-column panels, tails zero-filled) and the 4 rows hide the
 // latency of the fused multiply-add. A lane never sees another lane's values, so the bits are those of the plain loop. The
 // function is cloned for CPUs with hardware FMA (x86-64-v3); elsewhere fmaf stays the library's correctly rounded routine.
-#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#if defined(OTB_FMA_CLONES)
+// set by the build (for instance empty, to test the baseline clone on a machine that would pick a wider one)
+#elif defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
 #define OTB_FMA_CLONES __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default")))
 #else
 #define OTB_FMA_CLONES
