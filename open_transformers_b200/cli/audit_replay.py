@@ -26,9 +26,8 @@ from pathlib import Path
 
 log = logging.getLogger("pretrain.audit")
 MAX_AUDIT_WORLD = 64
-# The replica fold of the reduction kernels is the pair tree with strides 1, 2, 4, ... (parallel/deterministic_reduce.py);
-# checkpoints written before the tag was renamed carry its first name.
-REPLICATE_REDUCE_ALGOS = {"stride_pair_tree", "binary_blocks_tree"}
+# The replica fold the reduction kernels implement (parallel/deterministic_reduce.py::tree_reduce_sum).
+REPLICATE_REDUCE_ALGOS = {"binary_blocks_tree"}
 _HEX64 = re.compile(r"^[0-9a-fA-F]{64}$")
 # kernel-selecting environment a checkpoint may ask the replay to re-apply; anything else is refused
 ALLOWED_KERNEL_ENV = {"OTB_EXECUTION_MODE", "OTB_ATTN_BLOCK", "OTB_TENSOR_DIGEST"}
@@ -64,6 +63,43 @@ def apply_kernel_env(env: dict) -> dict:
             os.environ[k] = str(v)
             applied[k] = str(v)
     return applied
+
+
+def check_device(device: str) -> None:
+    """Refuse a device this process cannot use, before anything is built: ``cuda`` / ``cuda:N`` without a visible GPU (or
+    with fewer than N+1), a GPU request on a checkout whose CUDA library was never built, anything that is neither ``cpu``
+    nor ``cuda``. (reference src/pretrain/cli/audit_replay.py device guard and audit-kit provenance check)"""
+    import torch
+
+    if device == "cpu":
+        return
+    kind, _, index = device.partition(":")
+    if kind != "cuda" or (index and not index.isdigit()):
+        raise AuditError("--device %s: this build replays on cpu or cuda[:N]" % device)
+    if not torch.cuda.is_available():
+        raise AuditError("--device %s requested but no CUDA device is visible" % device)
+    if index and int(index) >= torch.cuda.device_count():
+        raise AuditError("--device %s requested but only %d CUDA device(s) are visible" % (device, torch.cuda.device_count()))
+    from .. import build_native
+
+    if not (build_native.EXT / "libotb_cuda.so").is_file():
+        try:
+            build_native._nvcc()   # a missing library is built on first use, which needs the compiler
+        except RuntimeError:
+            raise AuditError("--device %s: this installation has no CUDA kernels (%s is missing and there is no nvcc to build it)"
+                             % (device, build_native.EXT / "libotb_cuda.so")) from None
+
+
+def check_meta_bounds(meta, state_meta=None) -> None:
+    """``meta.json`` is untrusted input and the replay's memory and time grow with the recorded world size: implausible
+    integers are refused before the model is built. (reference tests/test_audit_meta_bounds.py)"""
+    V, S, R = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
+    if not all(isinstance(x, int) for x in (V, S, R)) or S < 1 or R < 1 or not (1 <= V <= MAX_AUDIT_WORLD) or S * R != V:
+        raise AuditError("recorded topology (world %s = replicate %s x shard %s) is out of bounds (1..%d, factors >= 1, product = world)"
+                         % (V, R, S, MAX_AUDIT_WORLD))
+    for m in (meta, state_meta):
+        if m is not None and (m.step < 0 or m.consumed_tokens < 0):
+            raise AuditError("recorded position (step %s, consumed tokens %s) is negative" % (m.step, m.consumed_tokens))
 
 
 def mismatch_message(got: str, want: str) -> str:
@@ -175,8 +211,7 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     expected = resolve_expect_hash(expect_hash)
     if device == "cpu":
         configure_cpu_threads(cpu_threads or "auto")
-    if device.startswith("cuda") and not torch.cuda.is_available():
-        raise AuditError("--device cuda requested but no CUDA device is visible")
+    check_device(device)
     if not from_init and checkpoint is None:
         raise AuditError("either --checkpoint or --from-init (with --config-name or --descriptor-checkpoint) is required")
 
@@ -207,9 +242,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     if cfg.run.parallel == "ddp":
         raise AuditError("run.parallel=ddp is not auditable (library all-reduce, reduction order not pinned)")
     if meta is not None:
+        check_meta_bounds(meta, state_meta)
         V, S, R = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
-        if not (1 <= V <= MAX_AUDIT_WORLD) or S * R != V:
-            raise AuditError("recorded topology (world %d = replicate %d x shard %d) is out of bounds" % (V, R, S))
         if meta.clip_algo != "global" or meta.grad_norm_algo != "deterministic_per_tensor_sos_v1":
             raise AuditError("unsupported clip / norm algorithm in checkpoint metadata")
         if meta.replicate_reduce_algo not in REPLICATE_REDUCE_ALGOS:
@@ -218,6 +252,9 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = V, S, R
     elif cfg.run.virtual_dp_size == 0:
         raise AuditError("--from-init with --config-name needs run.virtual_dp_size (the topology to emulate)")
+
+    if until_step is not None and state_meta is not None and until_step <= state_meta.step:
+        raise AuditError("--until-step %d is not beyond the starting step %d" % (until_step, state_meta.step))  # before anything is built
 
     cfg.run.tp_size = 1  # a tensor-parallel run is replayed unsplit: the split never changes a bit
     # --offload-grads: one work buffer plus one partial per replica instead of one gradient buffer per virtual rank

@@ -63,8 +63,9 @@ int otb_cpu_grad_reduce(const void* const* srcs, int S, int R, const long* chunk
         for (int s = 1; s < S; ++s) in = in + ((const float*)srcs[r * S + s])[base + i];
         rep[r] = in * inv_s;
       }
-      for (int st = 1; st < R; st *= 2)
-        for (int k = 0; k + st < R; k += 2 * st) rep[k] = rep[k] + rep[k + st];
+#define OTB_REP_ADD(a, b) rep[a] = rep[a] + rep[b]
+      DET_BLOCKS_FOLD(R, OTB_REP_ADD);  // binary blocks over the replicas
+#undef OTB_REP_ADD
       out[base + i] = rep[0] * inv_r;
     }
     chunk_sos_out[c] = chunk_sos(out + base, len);
@@ -87,8 +88,9 @@ int otb_cpu_grad_reduce_ids(const void* const* srcs, int S, int R, const long* c
         for (int s = 1; s < S; ++s) in = in + ((const float*)srcs[r * S + s])[base + i];
         rep[r] = in * inv_s;
       }
-      for (int st = 1; st < R; st *= 2)
-        for (int q = 0; q + st < R; q += 2 * st) rep[q] = rep[q] + rep[q + st];
+#define OTB_REP_ADD(a, b) rep[a] = rep[a] + rep[b]
+      DET_BLOCKS_FOLD(R, OTB_REP_ADD);  // binary blocks over the replicas
+#undef OTB_REP_ADD
       out[base + i] = rep[0] * inv_r;
     }
     chunk_sos_out[c] = chunk_sos(out + base, len);
@@ -112,8 +114,9 @@ int otb_cpu_grad_reduce_ex(const void* const* srcs, int S, int R, const long* ch
         for (int s = 1; s < S; ++s) in = in + ((const float*)srcs[r * S + s])[base + i];
         rep[r] = in * inv_s;
       }
-      for (int st = 1; st < R; st *= 2)
-        for (int q = 0; q + st < R; q += 2 * st) rep[q] = rep[q] + rep[q + st];
+#define OTB_REP_ADD(a, b) rep[a] = rep[a] + rep[b]
+      DET_BLOCKS_FOLD(R, OTB_REP_ADD);  // binary blocks over the replicas
+#undef OTB_REP_ADD
       out[obase + i] = rep[0] * inv_r;
     }
     chunk_sos_out[c] = chunk_sos(out + obase, len);

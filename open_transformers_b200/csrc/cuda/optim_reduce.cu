@@ -6,7 +6,7 @@
 //  grad_reduce  (pull reduce-scatter + replica tree + squared-norm partials)
 //     For every element this GPU owns:
 //        inner_r = (((g[r,0] + g[r,1]) + ...) + g[r,S-1]) * (1/S)       ascending shard rank
-//        outer   = pair_tree(inner_0 .. inner_{R-1})   * (1/R)          strides 1, 2, 4, ... over replicas
+//        outer   = blocks_fold(inner_0 .. inner_{R-1})   * (1/R)          binary blocks over replicas (det_reduce.h)
 //     g[r,s] is virtual rank (r*S+s)'s fp32 gradient buffer, local or a peer's. The same pass
 //     writes `outer` and folds it into the squared-norm partial of its 8192-element chunk
 //     (thread t takes elements j*2048 + t*8 .. +7, fma chain, block_tree_sum).
@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "det_math.h"
+#include "det_reduce.h"
 
 namespace {
 
@@ -104,10 +105,12 @@ grad_reduce_kernel(ReduceSrc src, int S, int R, int TPN, float inv_s, float inv_
 #pragma unroll
       for (int e = 0; e < 8; ++e) rep[r][e] = __fmul_rn(in[e], inv_s);
     }
-    for (int st = 1; st < R; st *= 2)
-      for (int i = 0; i + st < R; i += 2 * st)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) rep[i][e] = __fadd_rn(rep[i][e], rep[i + st][e]);
+    // binary blocks over the replicas (det_reduce.h): balanced trees inside the power-of-two blocks of R, block sums added
+    // left to right
+#define OTB_REP_ADD(a, b)                                                            \
+  _Pragma("unroll") for (int e = 0; e < 8; ++e) rep[a][e] = __fadd_rn(rep[a][e], rep[b][e])
+    DET_BLOCKS_FOLD(R, OTB_REP_ADD);
+#undef OTB_REP_ADD
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       o[e] = __fmul_rn(rep[0][e], inv_r);

@@ -6,22 +6,22 @@ re-derive a reduced gradient without the engine. With V = dp_replicate x dp_shar
 ``r * dp_shard + s`` being shard ``s`` of replica ``r``:
 
     inside a replica      g_r = ((g_{r,0} + g_{r,1}) + g_{r,2}) + ...        ascending shard order, then x 1/dp_shard
-    across the replicas   the pair tree: strides 1, 2, 4, ...; at stride s, value k takes value k + s on its right for
-                          every k that is a multiple of 2s with k + s in range; then x 1/dp_replicate
+    across the replicas   binary blocks: the replicas are cut into power-of-two blocks, one per set bit of the count,
+                          largest first (6 = 4 + 2, 7 = 4 + 2 + 1); a block is summed as a balanced tree of adjacent pairs,
+                          lower index on the left; the block sums are added left to right; then x 1/dp_replicate
 
 fp32 addition is commutative but not associative, so this grouping is what every process count and the single-device replay
-repeat. For a power-of-two count the tree is the balanced one, ((g0+g1)+(g2+g3))+...; 6 folds as ((g0+g1)+(g2+g3))+(g4+g5).
-The reference cuts the replicas into power-of-two blocks and adds the block sums left to right
-(src/pretrain/parallel/deterministic_reduce.py:140-185); the two groupings are the same for 1-6, 8-10, 12 and 16 replicas
-and differ from 7 on where three or more blocks exist (7: ours adds g6 to (g4+g5) first, the blocks add (g4+g5) to the
-first four first). ``binary_blocks`` / ``binary_blocks_sum`` state that order for comparison; the engine never uses it.
-(shard fold: reference src/pretrain/parallel/deterministic_reduce.py:77-117; ``Shard(0)`` row split :584-621)
+repeat. For a power-of-two count the tree is the balanced one, ((g0+g1)+(g2+g3))+...; 6 folds as ((g0+g1)+(g2+g3))+(g4+g5),
+7 as (((g0+g1)+(g2+g3))+(g4+g5))+g6. ``pair_tree_sum`` is the other fixed tree of this package (strides 1, 2, 4, ...; used
+over token slabs, K slabs and chunk partials, where counts are powers of two or the tail is short); the two agree while
+the count has at most two set bits.
+(reference src/pretrain/parallel/deterministic_reduce.py:77-117 shard fold, :140-185 binary blocks, :584-621 ``Shard(0)``)
 """
 from __future__ import annotations
 
 import torch
 
-REPLICATE_REDUCE_ALGO = "stride_pair_tree"                   # tag written into checkpoint metadata
+REPLICATE_REDUCE_ALGO = "binary_blocks_tree"                  # tag written into checkpoint metadata
 GRAD_NORM_ALGO = "deterministic_per_tensor_sos_v1"
 
 
@@ -36,21 +36,7 @@ def binary_blocks(n: int) -> list[int]:
 
 
 def tree_reduce_sum(parts: list[torch.Tensor]) -> torch.Tensor:
-    """Sum of ``parts`` in the pair-tree order of the reduction kernels (module docstring). One part is returned as it is."""
-    if not parts:
-        raise ValueError("nothing to sum")
-    v = list(parts)
-    stride = 1
-    while stride < len(v):
-        for k in range(0, len(v) - stride, 2 * stride):
-            v[k] = v[k] + v[k + stride]
-        stride *= 2
-    return v[0]
-
-
-def binary_blocks_sum(parts: list[torch.Tensor]) -> torch.Tensor:
-    """Sum of ``parts`` in the binary-blocks order: balanced adjacent-pair tree inside each power-of-two block, block sums
-    added left to right. Equal to ``tree_reduce_sum`` whenever ``len(parts)`` has at most two set bits."""
+    """Sum of ``parts`` in the binary-blocks order of the replica fold (module docstring). One part is returned as it is."""
     if not parts:
         raise ValueError("nothing to sum")
     total, at = None, 0
@@ -61,6 +47,21 @@ def binary_blocks_sum(parts: list[torch.Tensor]) -> torch.Tensor:
             level = [level[i] + level[i + 1] for i in range(0, len(level), 2)]
         total = level[0] if total is None else total + level[0]
     return total
+
+
+def pair_tree_sum(parts: list[torch.Tensor]) -> torch.Tensor:
+    """Sum of ``parts`` by the stride tree: at stride s = 1, 2, 4, ... value k takes value k + s on its right for every k
+    that is a multiple of 2s with k + s in range. Equal to ``tree_reduce_sum`` whenever ``len(parts)`` has at most two
+    set bits."""
+    if not parts:
+        raise ValueError("nothing to sum")
+    v = list(parts)
+    stride = 1
+    while stride < len(v):
+        for k in range(0, len(v) - stride, 2 * stride):
+            v[k] = v[k] + v[k + stride]
+        stride *= 2
+    return v[0]
 
 
 def fold_virtual_ranks(grads: list[torch.Tensor], dp_shard: int, dp_replicate: int = 1) -> torch.Tensor:

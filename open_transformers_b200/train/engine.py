@@ -15,8 +15,8 @@ One optimizer step
   1. for each hosted virtual rank, for each of its micro-batches: forward + backward; weight
      gradients accumulate in fp32 straight into that rank's flat buffer (GEMM beta=1 epilogue);
   2. `grad_reduce`: every process reduces the segments it owns by reading all V buffers (its own
-     and, over NVLink peer loads, the other GPUs') in ascending shard order, x 1/S, pair tree
-     (strides 1, 2, 4, ...) over replicas, x 1/R, and emits per-chunk squared-norm partials in the same pass;
+     and, over NVLink peer loads, the other GPUs') in ascending shard order, x 1/S, binary-blocks
+     tree over replicas, x 1/R, and emits per-chunk squared-norm partials in the same pass;
   3. the partials are combined per (parameter, shard) by the pair tree, folded ascending shard then
      ascending parameter in fp32 on the host, sqrt, clip coefficient
      h = min(max_norm / (norm + 1e-6), 1)   (reference src/pretrain/train/global_clip.py:47-55);
@@ -1027,7 +1027,7 @@ class TrainEngine:
             self._stream_barrier()  # every rank's backward is complete before anyone pulls
             srcs = []
             if self.fold:
-                # the shard fold and the 1/S scaling are done; what is left is the pair tree over the R replica partials
+                # the shard fold and the 1/S scaling are done; what is left is the binary-blocks fold over the R replica partials
                 parts = [self._partials[r] for r in range(R)]
                 parts = [self._unspill(p) if isinstance(p, str) else p for p in parts]
                 self._keep = parts

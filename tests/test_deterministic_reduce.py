@@ -1,6 +1,6 @@
 """The deterministic gradient reduction against a plain restatement of its rule, bit for bit: per replica the shard
-gradients are added in ascending shard order and scaled by 1/S; the replica values are combined by the lower-index-left
-pair tree (strides 1, 2, 4, ...) and scaled by 1/R. Replica counts 1..9 (powers of two and not), element counts that end
+gradients are added in ascending shard order and scaled by 1/S; the replica values are combined by the binary-blocks
+tree (power-of-two blocks, largest first, balanced pair tree inside, block sums left to right) and scaled by 1/R. Replica counts 1..9 (powers of two and not), element counts that end
 inside a chunk, and the association itself checked symbolically.
 (reference test strategy: tests/distributed/test_deterministic_reduce.py:56-185, tests/test_binary_blocks_tree.py:56-70)"""
 import ctypes
@@ -25,6 +25,20 @@ def pair_tree(values, add):
     return v[0]
 
 
+def blocks_tree(values, add):
+    v, total, at = list(values), None, 0
+    bit = 1 << (len(v).bit_length() - 1)
+    while bit:
+        if len(v) & bit:
+            level = v[at:at + bit]
+            at += bit
+            while len(level) > 1:
+                level = [add(level[i], level[i + 1]) for i in range(0, len(level), 2)]
+            total = level[0] if total is None else add(total, level[0])
+        bit >>= 1
+    return total
+
+
 def spec(grads, S, R):
     f = np.float32
     reps = []
@@ -33,7 +47,7 @@ def spec(grads, S, R):
         for s in range(1, S):
             acc = (acc + grads[r * S + s]).astype(f)
         reps.append((acc * f(1.0 / S)).astype(f))
-    return (pair_tree(reps, lambda a, b: (a + b).astype(f)) * f(1.0 / R)).astype(f)
+    return (blocks_tree(reps, lambda a, b: (a + b).astype(f)) * f(1.0 / R)).astype(f)
 
 
 def native_reduce(grads, S, R, n):
@@ -48,7 +62,8 @@ def native_reduce(grads, S, R, n):
 
 
 @pytest.mark.parametrize("n", [1, 7, 257, 4097, 2 * CHUNK + 5])
-@pytest.mark.parametrize("S,R", [(1, 1), (2, 1), (4, 1), (1, 2), (3, 2), (2, 3), (1, 5), (2, 6), (1, 7), (4, 8), (1, 9)])
+@pytest.mark.parametrize("S,R", [(1, 1), (2, 1), (4, 1), (1, 2), (3, 2), (2, 3), (1, 5), (2, 6), (1, 7), (4, 8), (1, 9), (1, 11), (2, 13), (1, 15),
+                                 (1, 16)])
 def test_reduction_equals_the_stated_rule_bit_for_bit(S, R, n):
     rng = np.random.default_rng(1000 * S + 10 * R + n)
     grads = [(rng.standard_normal(n) * 10.0 ** rng.integers(-3, 3)).astype(np.float32) for _ in range(S * R)]
@@ -148,6 +163,7 @@ def test_whole_tensor_fold_equals_the_kernel_twin_bit_for_bit():
 
 
 def test_pair_tree_and_binary_blocks_agree_up_to_two_blocks_and_not_beyond():
+    # the reference pins the same strings for its tree_reduce_sum (tests/test_binary_blocks_tree.py:56-70)
     from open_transformers_b200.parallel import deterministic_reduce as DR
 
     class Sym:
@@ -159,11 +175,13 @@ def test_pair_tree_and_binary_blocks_agree_up_to_two_blocks_and_not_beyond():
 
     assert DR.binary_blocks(6) == [4, 2] and DR.binary_blocks(7) == [4, 2, 1] and DR.binary_blocks(8) == [8] and DR.binary_blocks(1) == [1]
     for n in range(1, 17):
-        a = DR.tree_reduce_sum([Sym(str(i)) for i in range(n)]).s
-        b = DR.binary_blocks_sum([Sym(str(i)) for i in range(n)]).s
+        a = DR.pair_tree_sum([Sym(str(i)) for i in range(n)]).s
+        b = DR.tree_reduce_sum([Sym(str(i)) for i in range(n)]).s
         assert a == pair_tree([str(i) for i in range(n)], lambda x, y: "(%s+%s)" % (x, y))
+        assert b == blocks_tree([str(i) for i in range(n)], lambda x, y: "(%s+%s)" % (x, y))
         assert (a == b) == (bin(n).count("1") <= 2), (n, a, b)
-    assert DR.binary_blocks_sum([Sym(str(i)) for i in range(7)]).s == "((((0+1)+(2+3))+(4+5))+6)"
+    assert DR.tree_reduce_sum([Sym(str(i)) for i in range(6)]).s == "(((0+1)+(2+3))+(4+5))"
+    assert DR.tree_reduce_sum([Sym(str(i)) for i in range(7)]).s == "((((0+1)+(2+3))+(4+5))+6)"
     with pytest.raises(ValueError):
         DR.tree_reduce_sum([])
 

@@ -254,7 +254,7 @@ def test_tree_digest_matches_host():
         assert SH.tree_digest_tensor(t) == SH.tree_digest_tensor(t.to(DEV)), n
 
 
-@pytest.mark.parametrize("S,R", [(4, 1), (2, 2), (8, 1), (2, 3)])
+@pytest.mark.parametrize("S,R", [(4, 1), (2, 2), (8, 1), (2, 3), (1, 7)])
 def test_grad_reduce_gpu_equals_cpu_fold_in_any_launch_order(S, R):
     """The fused reduction (ascending shard fold, replica pair tree, squared-norm partials) against the CPU fold, bit for
     bit; and the same chunks launched in reversed and in shuffled order (the bucketed launches of the overlapped path):
