@@ -26,8 +26,11 @@ from pathlib import Path
 
 log = logging.getLogger("pretrain.audit")
 MAX_AUDIT_WORLD = 64
-# The replica fold the reduction kernels implement (parallel/deterministic_reduce.py::tree_reduce_sum).
-REPLICATE_REDUCE_ALGOS = {"binary_blocks_tree"}
+# The replica fold the reduction kernels implement (parallel/deterministic_reduce.py::tree_reduce_sum), under the tag the
+# reference writes for the same combination tree. "binary_blocks_tree" is what earlier versions of this package wrote while
+# their kernels used the stride tree, which is the same grouping only while the replica count has at most two set bits.
+REPLICATE_REDUCE_ALGOS = {"recursive_doubling"}
+LEGACY_REPLICATE_REDUCE_ALGO = "binary_blocks_tree"
 _HEX64 = re.compile(r"^[0-9a-fA-F]{64}$")
 # kernel-selecting environment a checkpoint may ask the replay to re-apply; anything else is refused
 ALLOWED_KERNEL_ENV = {"OTB_EXECUTION_MODE", "OTB_ATTN_BLOCK", "OTB_TENSOR_DIGEST"}
@@ -246,7 +249,8 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         V, S, R = meta.dp_world_size, meta.dp_shard, meta.dp_replicate
         if meta.clip_algo != "global" or meta.grad_norm_algo != "deterministic_per_tensor_sos_v1":
             raise AuditError("unsupported clip / norm algorithm in checkpoint metadata")
-        if meta.replicate_reduce_algo not in REPLICATE_REDUCE_ALGOS:
+        legacy_ok = meta.replicate_reduce_algo == LEGACY_REPLICATE_REDUCE_ALGO and bin(max(meta.dp_replicate, 0)).count("1") <= 2
+        if meta.replicate_reduce_algo not in REPLICATE_REDUCE_ALGOS and not legacy_ok:
             raise AuditError("this replay knows the replica orders %s; the checkpoint was trained with replicate_reduce_algo=%r"
                              % (sorted(REPLICATE_REDUCE_ALGOS), meta.replicate_reduce_algo))
         cfg.run.virtual_dp_size, cfg.run.dp_shard_size, cfg.run.dp_replicate_size = V, S, R

@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import torch
 
-REPLICATE_REDUCE_ALGO = "binary_blocks_tree"                  # tag written into checkpoint metadata
+REPLICATE_REDUCE_ALGO = "recursive_doubling"                   # tag written into checkpoint metadata
 GRAD_NORM_ALGO = "deterministic_per_tensor_sos_v1"
 
 

@@ -55,7 +55,7 @@ class CheckpointMeta:
     dp_world_size: int = 1             # VIRTUAL data-parallel world size
     dp_replicate: int = 1
     dp_shard: int = 1
-    replicate_reduce_algo: str = "binary_blocks_tree"   # parallel/deterministic_reduce.py::REPLICATE_REDUCE_ALGO
+    replicate_reduce_algo: str = "recursive_doubling"   # parallel/deterministic_reduce.py::REPLICATE_REDUCE_ALGO
     grad_norm_algo: str = "deterministic_per_tensor_sos_v1"
     clip_algo: str = "global"
     tensor_digest: str = "raw"

@@ -37,6 +37,7 @@ def meta_only_checkpoint(tmp_path, **over):
     (dict(step=-1), "negative"),
     (dict(consumed_tokens=-5), "negative"),
     (dict(replicate_reduce_algo="ascending_allgather"), "replica orders"),
+    (dict(replicate_reduce_algo="binary_blocks_tree", dp_world_size=7, dp_replicate=7, dp_shard=1), "replica orders"),   # the earlier stride tree differs at 7
     (dict(clip_algo="per_tensor"), "clip / norm"),
 ])
 def test_implausible_metadata_is_refused_before_anything_is_built(tmp_path, over, what):
@@ -46,10 +47,12 @@ def test_implausible_metadata_is_refused_before_anything_is_built(tmp_path, over
 
 
 def test_plausible_metadata_passes_the_gate_and_fails_later_on_the_missing_payload(tmp_path):
-    ck = meta_only_checkpoint(tmp_path, dp_world_size=8, dp_replicate=2, dp_shard=4)
-    with pytest.raises(Exception) as e:
-        AR.audit_replay(ck, device="cpu", until_step=11)
-    assert not isinstance(e.value, AR.AuditError)
+    for i, over in enumerate([dict(dp_world_size=8, dp_replicate=2, dp_shard=4), dict(replicate_reduce_algo="recursive_doubling"),
+                              dict(replicate_reduce_algo="binary_blocks_tree", dp_world_size=6, dp_replicate=6, dp_shard=1)]):
+        ck = meta_only_checkpoint(tmp_path / str(i), **over)
+        with pytest.raises(Exception) as e:
+            AR.audit_replay(ck, device="cpu", until_step=11)
+        assert not isinstance(e.value, AR.AuditError), over
 
 
 @pytest.mark.parametrize("until_step", [10, 9, 0, -3])
