@@ -104,9 +104,10 @@ def test_handoff_and_safetensors_relay(trained, tmp_path):
     r = audit_replay(un["dir"], data_root=tmp, until_step=3, save_checkpoint_dir=str(tmp_path / "handoff"), expect_hash=res["hashes"][-1][1])
     assert r["match"] is True
     prev = dict(res["hashes"])[2]
-    v = verify_handoff(r["saved_checkpoint"], prev_hash=prev)
-    assert v["match"] is True
-    assert verify_handoff(r["saved_checkpoint"], prev_hash="1" * 64)["match"] is False
+    want = dict(res["hashes"])[3]
+    v = verify_handoff(r["saved_checkpoint"], expect_hash=want, prev_hash=prev)
+    assert v["verified"] is True and v["reconstructed_hash"] == want
+    assert verify_handoff(r["saved_checkpoint"], expect_hash=want, prev_hash="1" * 64)["verified"] is False
 
 
 WORKER = textwrap.dedent("""
