@@ -326,17 +326,9 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
         rewarm_anchor = meta.rewarm_anchor_tokens if descriptor_checkpoint is not None else state_meta.rewarm_anchor_tokens
     if until_step is None:
         # default span: one checkpoint interval of the recipe (steps, or tokens when the recipe clocks checkpoints by tokens)
-        if cfg.train.ckpt_every_steps == 0 and cfg.train.ckpt_every_tokens > 0:
-            from ..train.batch_schedule import iter_step_plans
+        from ..train.batch_schedule import default_interval_end
 
-            every, c, until_step = cfg.train.ckpt_every_tokens, consumed, step
-            for plan in iter_step_plans(consumed, 0, cfg.train, start_step=step):
-                until_step += 1
-                c += plan.tokens_this_step
-                if c // every > plan.consumed_tokens // every or c >= cfg.train.total_tokens:
-                    break
-        else:
-            until_step = step + max(cfg.train.ckpt_every_steps, 1)
+        until_step = default_interval_end(step, consumed, cfg.train)
     if until_step <= step:
         raise AuditError("--until-step %d is not beyond the starting step %d" % (until_step, step))
 
@@ -518,7 +510,8 @@ def main(argv: list[str] | None = None) -> int:
         from ..data.fetch_interval import fetch_audit_interval
 
         if a.checkpoint and a.gcs_root:
-            a.data_root = fetch_audit_interval(a.checkpoint, a.gcs_root, a.fetch_dest or "audit_data", until_step=a.until_step)
+            a.data_root = fetch_audit_interval(a.checkpoint, a.gcs_root, a.fetch_dest or "audit_data", until_step=a.until_step,
+                                               config_name=a.config_name, from_init=a.from_init).data_root
     try:
         res = audit_replay(a.checkpoint, config_name=a.config_name, overrides=a.overrides, data_root=a.data_root, device=a.device,
                            cpu_threads=a.cpu_threads, from_init=a.from_init, descriptor_checkpoint=a.descriptor_checkpoint,

@@ -25,15 +25,21 @@ def main(argv=None) -> int:
     ap.add_argument("--config-name", default=None, help="train config name (default: the configuration in the checkpoint's meta.json)")
     ap.add_argument("--until-step", type=int, default=None, help="fetch through this optimizer step (default: one checkpoint interval)")
     ap.add_argument("--no-verify", action="store_true", help="skip the blake2b verification of downloaded .idx / .bin files")
+    ap.add_argument("--from-init", action="store_true", help="fetch for `pretrain-audit-replay --from-init`: walk from the stream's origin "
+                                                             "to --until-step (default: the checkpoint's step)")
     a = ap.parse_args(argv)
-    from ..data.fetch_interval import fetch_audit_interval, read_checkpoint_descriptor
+    import dataclasses
 
-    data_root = fetch_audit_interval(a.checkpoint, a.mirror, a.dest, until_step=a.until_step, config_name=a.config_name, verify=not a.no_verify)
-    meta = read_checkpoint_descriptor(a.checkpoint)["meta"]
-    print(json.dumps({"data_root": data_root, "checkpoint": a.checkpoint, "from_step": meta["step"], "until_step": a.until_step,
-                      "verified": not a.no_verify}, indent=2))
-    print("\nAudit this interval with:\n  pretrain-audit-replay \\\n      --checkpoint %s \\\n      --data-root %s \\\n"
-          "      --expect-hash <next-checkpoint>/state_hash.txt" % (a.checkpoint, data_root))
+    from ..data.fetch_interval import fetch_audit_interval
+
+    r = fetch_audit_interval(a.checkpoint, a.mirror, a.dest, until_step=a.until_step, config_name=a.config_name, from_init=a.from_init,
+                             verify=not a.no_verify)
+    out = dataclasses.asdict(r)
+    out.update(checkpoint=a.checkpoint, from_step=r.start_step)
+    print(json.dumps(out, indent=2))
+    print("\nAudit this interval with:\n  pretrain-audit-replay \\\n      --checkpoint %s \\\n      --data-root %s \\\n%s"
+          "      --until-step %d \\\n      --expect-hash <target-checkpoint>/state_hash.txt"
+          % (a.checkpoint, r.data_root, "      --from-init \\\n" if a.from_init else "", r.until_step))
     return 0
 
 

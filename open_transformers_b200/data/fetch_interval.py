@@ -9,11 +9,17 @@ google-cloud-storage when it is installed (anonymous client as fallback), ``DirM
 (tests, air-gapped boxes) (reference src/pretrain/data/fetch_interval.py:60-534)."""
 from __future__ import annotations
 
+import dataclasses
 import json
+import logging
 import shutil
 from pathlib import Path
 
+import numpy as np
+
 from .manifest import SourceManifest, blake2b_file
+
+log = logging.getLogger("pretrain.fetch_interval")
 
 
 class DirMirror:
@@ -94,51 +100,140 @@ def enumerate_touched_shards(cfg, data_root: str | Path, stream_state, consumed_
     return touched
 
 
-def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path, until_step: int | None = None, cfg=None, *,
-                         config_name: str | None = None, verify: bool = True) -> str:
-    """Materialise under ``dest`` everything a replay of [checkpoint.step, until_step) needs; returns ``dest``.
-    ``config_name``: a train config to use instead of the one recorded in the checkpoint; ``verify=False`` skips the
-    blake2b comparison of downloaded files with their manifest (reference src/pretrain/cli/fetch_audit_data.py:49-60)."""
-    from ..config import load_config, parse_config_resolved
+@dataclasses.dataclass
+class FetchResult:
+    dest: str
+    data_root: str                       # what the replay takes as --data-root
+    start_step: int
+    start_consumed_tokens: int
+    until_step: int
+    from_init: bool
+    touched_shards: dict                 # {source name: sorted shard ids}
+    bytes_fetched: int                   # payload bytes that landed on disk in this call (0 for shards already present and verified)
+    stubs_created: int
+    verified: bool
 
-    if cfg is None and config_name:
-        cfg = load_config(config_name)
+
+def _fetch_indices(mirror, rel: Path, dest: Path, verify: bool) -> SourceManifest:
+    """A source's manifest and every shard's ``.idx`` (a fraction of a percent of the corpus): what the length walk needs.
+    Index files already present are kept when they match the manifest's digest."""
+    if not mirror.exists(str(rel / "manifest.yaml")):
+        raise FileNotFoundError("mirror lacks %s" % (rel / "manifest.yaml"))
+    mirror.download(str(rel / "manifest.yaml"), dest / rel / "manifest.yaml")
+    man = SourceManifest.load(dest / rel / "manifest.yaml")
+    for s in man.shards:
+        idx = dest / rel / (s.prefix + ".idx")
+        if not idx.exists() or (verify and s.idx_blake2b and blake2b_file(idx) != s.idx_blake2b):
+            mirror.download(str(rel / (s.prefix + ".idx")), idx)
+        if verify and s.idx_blake2b and blake2b_file(idx) != s.idx_blake2b:
+            raise FetchIntegrityError("%s does not match its manifest digest: the mirror is corrupt or stale for this shard" % idx)
+    return man
+
+
+def _fetch_payloads(mirror, rel: Path, dest: Path, man: SourceManifest, shard_ids, verify: bool) -> int:
+    """The whole ``.bin`` of every touched shard, checked against the manifest's blake2b - a stronger statement than a
+    replay (the bytes ARE the cluster's). A file already there is kept if it verifies; a sparse stub left by an earlier,
+    shorter fetch fails the digest and is replaced. Returns the bytes downloaded."""
+    fetched = 0
+    for sid in sorted(shard_ids):
+        s = man.shards[sid]
+        target = dest / rel / (s.prefix + ".bin")
+        if target.exists():
+            size_ok = target.stat().st_size == s.token_count * np.dtype(man.dtype).itemsize
+            if size_ok and (not verify or not s.bin_blake2b or blake2b_file(target) == s.bin_blake2b) and not _is_sparse_stub(target):
+                continue
+            target.unlink()
+        mirror.download(str(rel / (s.prefix + ".bin")), target)
+        fetched += target.stat().st_size
+        if verify and s.bin_blake2b and blake2b_file(target) != s.bin_blake2b:
+            target.unlink()
+            raise FetchIntegrityError("%s.bin does not match its manifest digest: the mirror is corrupt or stale for this shard" % s.prefix)
+    return fetched
+
+
+def _is_sparse_stub(path: Path) -> bool:
+    """A placeholder written by ``_stub_untouched``: a file with bytes but no blocks. (Only consulted when verification is
+    off or the manifest has no digest; with a digest the zeros fail the comparison anyway.)"""
+    st = path.stat()
+    return st.st_size > 0 and getattr(st, "st_blocks", 1) == 0
+
+
+def _stub_untouched(dest: Path, rel: Path, man: SourceManifest, touched: set) -> int:
+    """The loader opens a reader for EVERY shard of every source, and a payload reader wants its ``.bin`` to exist. Shards the
+    interval never reads get a sparse file of the right size (no disk blocks); were the walk ever to read one, the zeros
+    would surface as a hash mismatch, not as silent corruption."""
+    item, made = np.dtype(man.dtype).itemsize, 0
+    for sid, s in enumerate(man.shards):
+        target = dest / rel / (s.prefix + ".bin")
+        if sid in touched or target.exists():
+            continue
+        with open(target, "wb") as f:
+            f.truncate(s.token_count * item)
+        made += 1
+    return made
+
+
+def fetch_audit_interval(checkpoint: str | Path, mirror, dest: str | Path = "./data/audit_data", until_step: int | None = None, cfg=None, *,
+                         config_name: str | None = None, from_init: bool = False, verify: bool = True) -> FetchResult:
+    """Materialise under ``dest`` everything a replay of the interval that starts at ``checkpoint`` needs.
+
+    The interval ends at ``until_step``, by default one checkpoint interval after the start (``ckpt_every_steps``, or the
+    first step across the next multiple of ``ckpt_every_tokens``). ``from_init=True`` matches ``audit_replay --from-init``:
+    the walk starts at the ORIGIN of the canonical stream (step 0, fresh state) and runs to ``until_step`` (default: the
+    checkpoint's own step); the checkpoint then only supplies configuration, seed and topology. ``config_name``: a train
+    configuration to use instead of the recorded one; ``verify=False`` skips the blake2b comparisons. A second call with
+    a longer interval keeps verified files and replaces the stubs that became touched. Writes ``fetch_manifest.json``.
+    (reference src/pretrain/data/fetch_interval.py:393-534)"""
+    from ..config import load_config, parse_config_resolved
+    from ..train.batch_schedule import default_interval_end
 
     if isinstance(mirror, str):
         mirror = GcsMirror(mirror) if mirror.startswith("gs://") else DirMirror(mirror)
     desc = read_checkpoint_descriptor(checkpoint)
     meta = desc["meta"]
-    cfg = cfg or parse_config_resolved(meta["config_resolved"])
+    if cfg is None:
+        cfg = load_run_config(meta, config_name)
     dest = Path(dest)
-    n_steps = (until_step - meta["step"]) if until_step else max(cfg.train.ckpt_every_steps, 1)
+    if from_init:
+        stream, start_step, start_consumed = None, 0, 0
+        until_step = int(meta["step"]) if until_step is None else until_step
+    else:
+        stream, start_step, start_consumed = desc["stream"], int(meta["step"]), int(meta["consumed_tokens"])
+        if until_step is None:
+            until_step = default_interval_end(start_step, start_consumed, cfg.train)
+    if until_step <= start_step:
+        raise ValueError("until_step %d is not beyond the starting step %d" % (until_step, start_step))
+    log.info("fetch interval: step %d (%d tokens) -> step %d, seed %s%s", start_step, start_consumed, until_step, meta.get("seed"),
+             " (from the stream's origin)" if from_init else "")
     # 1. manifests and indexes of every source (small)
+    manifests = {}
     for src in cfg.data.sources:
-        rel = Path(src.path)
-        if not mirror.exists(str(rel / "manifest.yaml")):
-            raise FileNotFoundError("mirror lacks %s" % (rel / "manifest.yaml"))
-        mirror.download(str(rel / "manifest.yaml"), dest / rel / "manifest.yaml")
-        man = SourceManifest.load(dest / rel / "manifest.yaml")
-        for s in man.shards:
-            mirror.download(str(rel / (s.prefix + ".idx")), dest / rel / (s.prefix + ".idx"))
-            if verify and s.idx_blake2b and blake2b_file(dest / rel / (s.prefix + ".idx")) != s.idx_blake2b:
-                raise FetchIntegrityError("%s.idx does not match its manifest digest" % s.prefix)
-    # 2. which payloads are needed
-    touched = enumerate_touched_shards(cfg, dest, desc["stream"], meta["consumed_tokens"], meta["step"], n_steps, meta["dp_world_size"])
-    # 3. payloads: fetched + verified, or sparse stubs
+        manifests[src.path] = _fetch_indices(mirror, Path(src.path), dest, verify)
+    # 2. which payloads the interval reads: the same window cursor the replay drives, over document lengths only
+    touched = enumerate_touched_shards(cfg, dest, stream, start_consumed, start_step, until_step - start_step, int(meta.get("dp_world_size") or 1))
+    log.info("interval touches %d shard(s) of %d source(s): %s", sum(len(v) for v in touched.values()), len(touched),
+             {k: len(v) for k, v in touched.items()})
+    # 3. payloads, then sparse stand-ins for everything else
+    fetched = stubs = 0
     for src in cfg.data.sources:
-        rel = Path(src.path)
-        man = SourceManifest.load(dest / rel / "manifest.yaml")
-        import numpy as np
+        man = manifests[src.path]
+        ids = touched.get(man.name, set())
+        fetched += _fetch_payloads(mirror, Path(src.path), dest, man, ids, verify)
+        stubs += _stub_untouched(dest, Path(src.path), man, ids)
+    log.info("downloaded %.2f GB of shard payloads, %d sparse placeholder(s) for untouched shards", fetched / 1e9, stubs)
+    result = FetchResult(dest=str(dest), data_root=str(dest), start_step=start_step, start_consumed_tokens=start_consumed, until_step=until_step,
+                         from_init=from_init, touched_shards={k: sorted(v) for k, v in touched.items()}, bytes_fetched=fetched,
+                         stubs_created=stubs, verified=verify)
+    (dest / "fetch_manifest.json").write_text(json.dumps(dataclasses.asdict(result), indent=2) + "\n")
+    return result
 
-        item = np.dtype(man.dtype).itemsize
-        for sid, s in enumerate(man.shards):
-            target = dest / rel / (s.prefix + ".bin")
-            if sid in touched.get(man.name, set()):
-                mirror.download(str(rel / (s.prefix + ".bin")), target)
-                if verify and s.bin_blake2b and blake2b_file(target) != s.bin_blake2b:
-                    target.unlink()
-                    raise FetchIntegrityError("%s.bin does not match its manifest digest" % s.prefix)
-            elif not target.exists():
-                with open(target, "wb") as f:
-                    f.truncate(s.token_count * item)   # sparse stub: right size, no blocks
-    return str(dest)
+
+def load_run_config(meta: dict, config_name: str | None = None):
+    """The run's configuration: a named one when given, else the one embedded in the checkpoint's metadata."""
+    from ..config import load_config, parse_config_resolved
+
+    if config_name:
+        return load_config(config_name)
+    if not meta.get("config_resolved"):
+        raise ValueError("the checkpoint embeds no configuration; pass config_name")
+    return parse_config_resolved(meta["config_resolved"])

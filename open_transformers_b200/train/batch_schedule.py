@@ -84,6 +84,21 @@ def iter_step_plans(consumed_tokens: int, windows_emitted: int, train, *, start_
         step += 1
 
 
+def default_interval_end(step: int, consumed_tokens: int, train) -> int:
+    """The step at which the checkpoint interval that starts at (``step``, ``consumed_tokens``) ends: ``ckpt_every_steps``
+    further on, or - when the recipe clocks checkpoints by tokens - the first step that crosses the next multiple of
+    ``ckpt_every_tokens`` (or exhausts ``total_tokens``). The replay's default target and the span whose data is fetched."""
+    if train.ckpt_every_steps == 0 and train.ckpt_every_tokens > 0:
+        every, c, end = train.ckpt_every_tokens, consumed_tokens, step
+        for plan in iter_step_plans(consumed_tokens, 0, train, start_step=step):
+            end += 1
+            c += plan.tokens_this_step
+            if c // every > plan.consumed_tokens // every or c >= train.total_tokens:
+                break
+        return end
+    return step + max(train.ckpt_every_steps, 1)
+
+
 def windows_consumed_before(consumed_tokens: int, train) -> int:
     """Windows emitted by a run from token 0 up to ``consumed_tokens`` (must land on a step boundary)."""
     c = w = 0
