@@ -14,14 +14,19 @@ from torch import nn
 from ..ops.functional import trunc_normal_
 
 
-def init_weights(model: nn.Module, seed: int, std: float | None = None) -> None:
+def init_weights(model: nn.Module, seed: int | None, std: float | None = None) -> None:
+    """``seed=None`` is the legacy path of single-process experiments: matrices come from torch's global generator (which
+    ``parallel.env.set_seed`` offsets by rank, so ranks would differ) instead of the Philox stream; nothing that is hashed
+    or replayed uses it. (reference src/pretrain/model/init.py:47-84)"""
     cfg = getattr(model, "cfg", None)
     if std is None:
         std = cfg.init.std if cfg is not None else 0.02
     offset = 0
     with torch.no_grad():
         for name, p in model.named_parameters():
-            if p.dim() >= 2:
+            if p.dim() >= 2 and seed is None:
+                nn.init.trunc_normal_(p, std=std, a=-2 * std, b=2 * std)
+            elif p.dim() >= 2:
                 buf = torch.empty(p.shape, dtype=torch.float32)
                 trunc_normal_(buf, std, seed, offset)
                 offset += p.numel()

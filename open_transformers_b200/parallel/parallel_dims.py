@@ -45,3 +45,39 @@ class ParallelDims:
 
     def tp_rank(self, rank: int) -> int:
         return rank % self.tp
+
+    # ---- the reference's vocabulary (src/pretrain/parallel/parallel_dims.py:141-194), over the virtual topology
+    @property
+    def dp_replicate_enabled(self) -> bool:
+        return self.dp_replicate > 1
+
+    @property
+    def dp_shard_enabled(self) -> bool:
+        return self.dp_shard > 1
+
+    @property
+    def fsdp_enabled(self) -> bool:
+        return self.dp_shard_enabled
+
+    @property
+    def dp_enabled(self) -> bool:
+        return self.dp_replicate_enabled or self.dp_shard_enabled
+
+    @property
+    def dp_world_size(self) -> int:
+        """Ranks that consume distinct tokens: the VIRTUAL data-parallel size (a tensor-parallel group shares its batch)."""
+        return self.virtual_dp
+
+    def dp_rank(self, global_rank: int = 0) -> int:
+        """The data-parallel process index of a physical rank (its first hosted virtual rank divided by the ranks per process)."""
+        return global_rank // self.tp
+
+    def make_dp_gloo_group(self):
+        """A gloo group over all processes for host-side metadata (32-byte digests, scalars), or None outside a process
+        group / with one process. NCCL collectives on device tensors wait for the whole stream; these do not."""
+        import torch.distributed as dist
+
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() <= 1:
+            return None
+        return dist.new_group(ranks=list(range(dist.get_world_size())), backend="gloo")
+

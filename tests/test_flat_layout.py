@@ -66,3 +66,17 @@ def test_rows_per_owner_must_describe_the_distribution():
     assert uniform_rows_per_owner([(0, 50), (50, 100), (0, 0), (0, 0)], 100) == 50              # fewer rows than owners
     assert uniform_rows_per_owner([(0, 30), (30, 50), (50, 100)], 100) is None
     assert uniform_rows_per_owner([(10, 60), (60, 100)], 100) is None
+
+
+def test_parallel_dims_vocabulary_over_the_virtual_topology():
+    from open_transformers_b200.parallel.parallel_dims import ParallelDims
+
+    d = ParallelDims(2, 4, 8)
+    assert d.dp_world_size == 8 and d.dp_replicate_enabled and d.dp_shard_enabled and d.fsdp_enabled and d.dp_enabled
+    assert [d.dp_rank(r) for r in range(8)] == list(range(8)) and d.coords(5) == (1, 1) and d.make_dp_gloo_group() is None
+    one = ParallelDims(1, 1, 1)
+    assert not one.dp_enabled and one.dp_world_size == 1
+    tp = ParallelDims(1, -1, 8, tp=4)                       # two tensor-parallel groups of four share two batches
+    assert tp.dp_world_size == 2 and tp.dp_shard == 2 and [tp.dp_rank(r) for r in (0, 3, 4, 7)] == [0, 0, 1, 1]
+    virt = ParallelDims(2, 4, 2, virtual_dp=8)              # eight virtual ranks on two processes
+    assert virt.dp_world_size == 8 and virt.hosted_virtual_ranks(1) == [4, 5, 6, 7]

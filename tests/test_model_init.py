@@ -100,3 +100,20 @@ def test_yarn_rope_keeps_high_frequencies_and_stretches_low_ones():
         ce, _ = eng.forward_backward(v, ids, ids, 1)
     assert torch.isfinite(ce) and eng.reduce_gradients() > 0
     eng.close()
+
+
+def test_unseeded_init_uses_the_global_generator_and_keeps_the_rules_for_vectors():
+    import torch
+
+    from open_transformers_b200.models.init import init_weights
+
+    torch.manual_seed(3)
+    a = torch.nn.Linear(16, 16)
+    init_weights(a, None, std=0.02)
+    torch.manual_seed(3)
+    b = torch.nn.Linear(16, 16)
+    init_weights(b, None, std=0.02)
+    assert torch.equal(a.weight, b.weight) and float(a.weight.abs().max()) <= 0.04 + 1e-9 and float(a.bias.detach().abs().sum()) == 0.0
+    c = torch.nn.Linear(16, 16)
+    init_weights(c, 3, std=0.02)
+    assert not torch.equal(a.weight, c.weight)
