@@ -16,6 +16,7 @@ MAGIC = b"MMIDIDX\0"
 VERSION = 1
 DTYPE_CODES = {1: np.uint8, 2: np.int8, 3: np.int16, 4: np.int32, 5: np.int64, 6: np.float32, 7: np.float64, 8: np.uint16, 9: np.uint32}
 _CODE_OF = {np.dtype(v): k for k, v in DTYPE_CODES.items()}
+CODE_BY_DTYPE = _CODE_OF
 _HEAD = struct.Struct("<8sQBqq")
 
 
@@ -93,12 +94,16 @@ class IndexedDatasetWriter:
         return self._offsets[-1]
 
     def finalize(self) -> None:
+        if self._bin.closed:
+            return
         self._bin.close()
         off = np.asarray(self._offsets, dtype="<i8")
         with open(str(self.prefix) + ".idx", "wb") as f:
             f.write(_HEAD.pack(MAGIC, VERSION, _CODE_OF[self.dtype], self.num_documents, self.token_count))
             f.write(off.tobytes())
             f.write((off * self.dtype.itemsize).astype("<i8").tobytes())
+
+    close = finalize
 
     def __enter__(self):
         return self
