@@ -1,17 +1,20 @@
-"""``pretrain-dump-documents``: the ``documents`` table of a corpus - every document of every shard detokenised to Parquet.
+"""``pretrain-dump-documents``: a prepared corpus turned back into text, one Parquet file per shard.
 
     pretrain-dump-documents --data-root data/shards --tokenizer tokenizer.json --out-dir DIR [--sources NAME ...]
                             [--workers N] [--batch-docs 2048] [--limit-shards N]
 
-One file per shard, ``<out>/<source>/<shard id, 5 digits>_<prefix>.parquet``, rows ``source, shard_id, local_doc, n_tokens,
-text`` - ``(source, shard_id, local_doc)`` is the document key of the step -> document map (``pretrain-dump-doc-map``). A file
-that exists is skipped, so an interrupted run resumes; a file is renamed into place only when complete. Special tokens stay
-in the text (a scraped document may contain the end-of-text marker literally; the text must match the stored ids).
-(flags, file layout and columns: reference src/pretrain/cli/dump_documents.py:33-161)
+Layout: ``<out>/<source>/<five-digit shard id>_<shard prefix>.parquet`` with the columns ``source, shard_id, local_doc,
+n_tokens, text``. The first three are the document key that ``pretrain-dump-doc-map`` writes, so "which text did step 812
+read" is a join of the two tables. Decoding keeps special tokens: web text now and then contains the end-of-text marker as
+literal characters, the tokenizer stored it as the special id, and the text has to correspond to the ``n_tokens`` ids on
+disk. Work is split by shard over a process pool; a shard whose file exists is left alone (the job can be re-run after an
+interruption), and a file appears under its final name only once it is whole.
+(flag set, file naming and columns: reference src/pretrain/cli/dump_documents.py:33-107)
 """
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import logging
 import multiprocessing as mp
 import sys
@@ -20,112 +23,144 @@ from pathlib import Path
 
 log = logging.getLogger("pretrain.dump_documents")
 COLUMNS = ("source", "shard_id", "local_doc", "n_tokens", "text")
-_tokenizer = None
+SKIPPED = -1
+_decoder = None   # per-process tokenizer, set by the pool initializer
 
 
-def _worker_init(tokenizer_path: str) -> None:
-    global _tokenizer
+@dataclasses.dataclass(frozen=True)
+class ShardJob:
+    source: str
+    shard_id: int
+    prefix: str          # <dir>/<name> of the .bin / .idx pair
+    target: str          # Parquet file to produce
+    batch_docs: int
+
+
+def _load_decoder(tokenizer_path: str) -> None:
+    global _decoder
     from ..data.tokenizer import Tokenizer
 
-    _tokenizer = Tokenizer(tokenizer_path)
+    _decoder = Tokenizer(tokenizer_path)
 
 
-def dump_shard(task) -> tuple[str, int, int, float]:
-    """One shard -> one Parquet file. Returns (source, shard id, documents written or -1 when the file existed, seconds)."""
+def _schema():
     import pyarrow as pa
-    import pyarrow.parquet as pq
+
+    kinds = {"source": pa.string(), "shard_id": pa.int32(), "local_doc": pa.int32(), "n_tokens": pa.int32(), "text": pa.large_string()}
+    return pa.schema([(c, kinds[c]) for c in COLUMNS])
+
+
+def _row_groups(job: ShardJob, schema):
+    """Tables of at most ``batch_docs`` documents, in document order."""
+    import pyarrow as pa
 
     from ..data.indexed_dataset import IndexedDatasetReader
 
-    source, shard_id, prefix, out_path, batch_docs = task
-    out = Path(out_path)
-    if out.exists():
-        return source, shard_id, -1, 0.0
-    t0 = time.time()
-    reader = IndexedDatasetReader(prefix)
-    sch = pa.schema([("source", pa.string()), ("shard_id", pa.int32()), ("local_doc", pa.int32()), ("n_tokens", pa.int32()), ("text", pa.large_string())])
-    out.parent.mkdir(parents=True, exist_ok=True)
-    part = out.with_suffix(".parquet.part")
-    n = reader.num_documents
-    with pq.ParquetWriter(part, sch, compression="zstd") as writer:
-        for lo in range(0, n, batch_docs):
-            hi = min(n, lo + batch_docs)
-            ids = [reader.document(i).tolist() for i in range(lo, hi)]
-            writer.write_table(pa.table({"source": pa.array([source] * (hi - lo), pa.string()), "shard_id": pa.array([shard_id] * (hi - lo), pa.int32()),
-                                         "local_doc": pa.array(range(lo, hi), pa.int32()), "n_tokens": pa.array([len(x) for x in ids], pa.int32()),
-                                         "text": pa.array(_tokenizer.decode_batch(ids, skip_special_tokens=False), pa.large_string())}, schema=sch))
-    part.replace(out)
-    return source, shard_id, n, time.time() - t0
+    shard = IndexedDatasetReader(job.prefix)
+    for first in range(0, len(shard), job.batch_docs):
+        docs = range(first, min(len(shard), first + job.batch_docs))
+        ids = [shard.document(d).tolist() for d in docs]
+        cols = {"source": [job.source] * len(ids), "shard_id": [job.shard_id] * len(ids), "local_doc": list(docs),
+                "n_tokens": [len(t) for t in ids], "text": _decoder.decode_batch(ids, skip_special_tokens=False)}
+        yield pa.table({c: pa.array(cols[c], schema.field(c).type) for c in COLUMNS}, schema=schema)
 
 
-def build_tasks(data_root: Path, out_dir: Path, sources, batch_docs: int, limit):
-    """One task per shard of every ``<source>/manifest.yaml`` under ``data_root``. Output names carry the shard id (prefixes
-    in different directories may share a base name); two shards that would land on one file are refused, because the
-    skip-existing rule would silently drop one of them."""
+def dump_shard(job) -> tuple[str, int, int, float]:
+    """Write one shard's file; ``(source, shard id, documents written, seconds)``, with ``SKIPPED`` documents when the file
+    was already there. Accepts a ``ShardJob`` or its fields as a tuple."""
+    import pyarrow.parquet as pq
+
+    job = job if isinstance(job, ShardJob) else ShardJob(*job)
+    final = Path(job.target)
+    if final.exists():
+        return job.source, job.shard_id, SKIPPED, 0.0
+    began, written = time.time(), 0
+    final.parent.mkdir(parents=True, exist_ok=True)
+    unfinished = final.with_suffix(".parquet.part")
+    schema = _schema()
+    with pq.ParquetWriter(unfinished, schema, compression="zstd") as sink:
+        for table in _row_groups(job, schema):
+            sink.write_table(table)
+            written += table.num_rows
+    unfinished.replace(final)
+    return job.source, job.shard_id, written, time.time() - began
+
+
+def build_tasks(data_root: Path, out_dir: Path, sources, batch_docs: int, limit) -> list[ShardJob]:
+    """Every shard of every ``<source>/manifest.yaml`` below ``data_root`` (restricted to ``sources`` and to the first
+    ``limit`` shards of each, when given). The shard id is part of the file name because prefixes that live in different
+    directories can share their last component; if two shards still map to one file - two manifests carrying one source
+    name - that is an error, since "skip what exists" would quietly lose one of them."""
     from ..data.manifest import SourceManifest
 
-    tasks, taken = [], {}
-    for mpath in sorted(data_root.glob("*/manifest.yaml")):
-        man = SourceManifest.load(mpath)
-        if sources and man.name not in sources:
+    jobs, owner_of = [], {}
+    for manifest_file in sorted(data_root.glob("*/manifest.yaml")):
+        manifest = SourceManifest.load(manifest_file)
+        if sources and manifest.name not in sources:
             continue
-        for sid, shard in enumerate(man.shards):
-            if limit is not None and sid >= limit:
-                break
-            stem = Path(shard.prefix)
-            prefix = stem if stem.is_absolute() else mpath.parent / stem
-            out = out_dir / man.name / ("%05d_%s.parquet" % (sid, stem.name))
-            if str(out) in taken:
-                raise ValueError("duplicate output %s for shards %s and %s" % (out, taken[str(out)], prefix))
-            taken[str(out)] = str(prefix)
-            tasks.append((man.name, sid, str(prefix), str(out), batch_docs))
-    return tasks
+        shards = manifest.shards if limit is None else manifest.shards[:limit]
+        for shard_id, shard in enumerate(shards):
+            rel = Path(shard.prefix)
+            prefix = str(rel if rel.is_absolute() else manifest_file.parent / rel)
+            target = str(out_dir / manifest.name / ("%05d_%s.parquet" % (shard_id, rel.name)))
+            if target in owner_of:
+                raise ValueError("duplicate output %s: both %s and %s would be written there" % (target, owner_of[target], prefix))
+            owner_of[target] = prefix
+            jobs.append(ShardJob(manifest.name, shard_id, prefix, target, batch_docs))
+    return jobs
+
+
+class _Tally:
+    def __init__(self, total: int):
+        self.total, self.written, self.skipped, self.docs, self.began = total, 0, 0, 0, time.time()
+
+    def add(self, outcome) -> None:
+        source, shard_id, n, seconds = outcome
+        if n == SKIPPED:
+            self.skipped += 1
+            return
+        self.written += 1
+        self.docs += n
+        if self.written % 10 == 0 or seconds > 300:
+            log.info("%d of %d shards done (%d already present), %d documents; %s shard %d took %.0fs; %.0fs so far", self.written + self.skipped,
+                     self.total, self.skipped, self.docs, source, shard_id, seconds, time.time() - self.began)
 
 
 def run(a) -> int:
-    tasks = build_tasks(Path(a.data_root), Path(a.out_dir), a.sources, a.batch_docs, a.limit_shards)
-    if not tasks:
+    jobs = build_tasks(Path(a.data_root), Path(a.out_dir), a.sources, a.batch_docs, a.limit_shards)
+    if not jobs:
         log.error("no shards found under %s", a.data_root)
         return 1
-    log.info("%d shards, %d workers, out=%s", len(tasks), a.workers, a.out_dir)
-    t0 = time.time()
-    written = skipped = docs = 0
-
-    def account(result):
-        nonlocal written, skipped, docs
-        source, sid, n, dt = result
-        if n < 0:
-            skipped += 1
-            return
-        written += 1
-        docs += n
-        if written % 10 == 0 or dt > 300:
-            log.info("%d/%d shards (%d skipped), %d docs, last %s/%d %.0fs, elapsed %.0fs", written + skipped, len(tasks), skipped, docs, source, sid,
-                     dt, time.time() - t0)
-
-    if a.workers > 1 and len(tasks) > 1:
-        with mp.get_context("spawn").Pool(min(a.workers, len(tasks)), initializer=_worker_init, initargs=(a.tokenizer,)) as pool:
-            for result in pool.imap_unordered(dump_shard, tasks):
-                account(result)
+    procs = max(1, min(a.workers, len(jobs)))
+    log.info("%d shards to decode with %d process(es) into %s", len(jobs), procs, a.out_dir)
+    tally = _Tally(len(jobs))
+    if procs == 1:
+        _load_decoder(a.tokenizer)
+        for job in jobs:
+            tally.add(dump_shard(job))
     else:
-        _worker_init(a.tokenizer)
-        for task in tasks:
-            account(dump_shard(task))
-    log.info("finished: %d written, %d skipped, %d docs, %.0fs", written, skipped, docs, time.time() - t0)
+        with mp.get_context("spawn").Pool(procs, initializer=_load_decoder, initargs=(a.tokenizer,)) as pool:
+            for outcome in pool.imap_unordered(dump_shard, jobs):
+                tally.add(outcome)
+    log.info("finished: %d written, %d skipped, %d docs, %.0fs", tally.written, tally.skipped, tally.docs, time.time() - tally.began)
     return 0
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="pretrain-dump-documents", description="Detokenise the shards of a prepared corpus into Parquet.")
+    ap.add_argument("--data-root", required=True, help="parent directory of the sources (each with its manifest.yaml and shards)")
+    ap.add_argument("--tokenizer", required=True, help="the tokenizer.json that produced the shards")
+    ap.add_argument("--out-dir", required=True, help="root of the output tree: <out>/<source>/<shard id>_<prefix>.parquet")
+    ap.add_argument("--sources", nargs="*", default=None, help="only these source names")
+    ap.add_argument("--workers", type=int, default=max(1, mp.cpu_count() - 2), help="decoder processes")
+    ap.add_argument("--batch-docs", type=int, default=2048, help="documents per decode call and per Parquet row group")
+    ap.add_argument("--limit-shards", type=int, default=None, help="stop after this many shards of each source (for trying things out)")
+    return ap
 
 
 def main(argv=None) -> int:
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s :: %(message)s")
-    ap = argparse.ArgumentParser(prog="pretrain-dump-documents")
-    ap.add_argument("--data-root", required=True, help="directory holding <source>/manifest.yaml and the shards")
-    ap.add_argument("--tokenizer", required=True, help="tokenizer.json the shards were prepared with")
-    ap.add_argument("--out-dir", required=True, help="output root; files land at <out>/<source>/<shard id>_<prefix>.parquet")
-    ap.add_argument("--sources", nargs="*", default=None, help="subset of source names (default: all)")
-    ap.add_argument("--workers", type=int, default=max(1, mp.cpu_count() - 2))
-    ap.add_argument("--batch-docs", type=int, default=2048, help="documents decoded per batch / row group")
-    ap.add_argument("--limit-shards", type=int, default=None, help="debugging: only the first N shards per source")
-    return run(ap.parse_args(argv))
+    return run(build_parser().parse_args(argv))
 
 
 if __name__ == "__main__":

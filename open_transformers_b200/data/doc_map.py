@@ -51,49 +51,63 @@ def iter_doc_map(view, *, until_step: int, micro_batch_size: int, dp_world_size:
         yield plan, step_rows(plan, spans, micro_batch_size=micro_batch_size, dp_world_size=dp_world_size)
 
 
-def _write_chunk(cols: dict[str, list], out_dir: Path, first: int, last: int) -> str:
-    import pyarrow as pa
-    import pyarrow.parquet as pq
+class ChunkedParquet:
+    """Rows gathered step by step and written as ``step_docs-<first>-<last>.parquet`` every ``chunk_steps`` steps. A chunk gets
+    its name only when it is whole (written beside it as ``.part`` first), so a reader of the directory never sees half a file."""
 
-    sch = schema()
-    table = pa.table({name: pa.array(cols[name], type=sch.field(name).type) for name in COLUMNS})
-    path = out_dir / ("step_docs-%06d-%06d.parquet" % (first, last))
-    part = path.with_suffix(".parquet.part")       # a reader never sees a half-written chunk
-    pq.write_table(table, part, compression="zstd")
-    part.replace(path)
-    return str(path)
+    def __init__(self, out_dir: Path, chunk_steps: int):
+        self.dir, self.every = out_dir, max(1, chunk_steps)
+        self.dir.mkdir(parents=True, exist_ok=True)
+        self.files: list[str] = []
+        self._cols: dict[str, list] = {c: [] for c in COLUMNS}
+        self._span: list[int] = []            # [first step, last step] of what is pending
+
+    def add(self, step: int, cols: dict[str, list]) -> bool:
+        """Take one step's rows; True when that completed a chunk."""
+        self._span = [self._span[0] if self._span else step, step]
+        for c in COLUMNS:
+            self._cols[c] += cols[c]
+        if (step + 1) % self.every:
+            return False
+        self.flush()
+        return True
+
+    def flush(self) -> None:
+        if not self._span or not self._cols["step"]:
+            self._span = []
+            return
+        import pyarrow as pa
+        import pyarrow.parquet as pq
+
+        sch = schema()
+        final = self.dir / ("step_docs-%06d-%06d.parquet" % tuple(self._span))
+        part = final.with_suffix(".parquet.part")
+        pq.write_table(pa.table({c: pa.array(self._cols[c], type=sch.field(c).type) for c in COLUMNS}), part, compression="zstd")
+        part.replace(final)
+        self.files.append(str(final))
+        self._cols, self._span = {c: [] for c in COLUMNS}, []
 
 
 def write_doc_map(view, out_dir: str | Path, *, until_step: int, micro_batch_size: int, dp_world_size: int, chunk_steps: int = 1000,
                   progress=None) -> dict:
-    """Walk the view's steps below ``until_step`` into Parquet chunks under ``out_dir``. Returns the summary that goes into
-    the manifest: steps, windows, rows (total and per source), files, and the stream position at the end of the walk."""
-    out = Path(out_dir)
-    out.mkdir(parents=True, exist_ok=True)
-    pending: dict[str, list] = {c: [] for c in COLUMNS}
-    files, per_source = [], {}
-    rows = windows = steps = 0
-    first = last = None
+    """Map every step of the view below ``until_step`` into ``out_dir``. The returned summary is the body of the manifest:
+    how many steps / windows / rows (rows also per source), the files, and where the stream stood when the walk ended -
+    the value a checkpoint of that step records in ``global_stream.json``. ``progress(next_step, rows_so_far)`` is called
+    after each completed chunk."""
+    sink = ChunkedParquet(Path(out_dir), chunk_steps)
+    count = {"steps": 0, "windows": 0, "rows": 0}
+    by_source: dict[str, int] = {}
     for plan, cols in iter_doc_map(view, until_step=until_step, micro_batch_size=micro_batch_size, dp_world_size=dp_world_size):
-        first = plan.step if first is None else first
-        last = plan.step
-        steps += 1
-        rows += len(cols["step"])
-        windows += plan.microbatches * micro_batch_size
+        count["steps"] += 1
+        count["windows"] += plan.microbatches * micro_batch_size
+        count["rows"] += len(cols["step"])
         for name in cols["source"]:
-            per_source[name] = per_source.get(name, 0) + 1
-        for c in COLUMNS:
-            pending[c].extend(cols[c])
-        if (plan.step + 1) % chunk_steps == 0:
-            files.append(_write_chunk(pending, out, first, last))
-            pending = {c: [] for c in COLUMNS}
-            first = None
-            if progress is not None:
-                progress(plan.step + 1, rows)
-    if first is not None and pending["step"]:
-        files.append(_write_chunk(pending, out, first, last))
-    return {"until_step": until_step, "steps_walked": steps, "windows": windows, "rows": rows, "rows_per_source": per_source, "files": files,
-            "position": view.stream_position()}
+            by_source[name] = by_source.get(name, 0) + 1
+        if sink.add(plan.step, cols) and progress is not None:
+            progress(plan.step + 1, count["rows"])
+    sink.flush()
+    return {"until_step": until_step, "steps_walked": count["steps"], "windows": count["windows"], "rows": count["rows"],
+            "rows_per_source": by_source, "files": sink.files, "position": view.stream_position()}
 
 
 def compare_position(position: dict, global_stream_json: dict) -> list[str]:

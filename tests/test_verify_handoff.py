@@ -65,7 +65,7 @@ def test_commitments_are_literal_digests_and_the_bad_flag_is_named(handoff, tmp_
     f.write_text(hashes[3])
     for flag, kw in (("--expect-hash", dict(expect_hash=str(f), prev_hash=hashes[2])), ("--prev-hash", dict(expect_hash=hashes[3], prev_hash=str(f))),
                      ("--expect-hash", dict(expect_hash=hashes[3][:16], prev_hash=hashes[2])), ("--prev-hash", dict(expect_hash=hashes[3], prev_hash=""))):
-        with pytest.raises(HandoffError, match=flag + " must be a full literal hex digest"):
+        with pytest.raises(HandoffError, match=flag + " takes the 64 hex digits of a published hash"):
             verify_handoff(ck, **kw)
 
 
@@ -105,10 +105,10 @@ def test_batch_chains_every_rank_is_needed_and_boundaries_cannot_move(handoff, t
     assert len(whole) == 32 and whole != (d / "batch_hasher.rank_0.bin").read_bytes()      # rank 0 alone does not stand for the run
     assert read_batch_digest(d, 1) == (d / "batch_hasher.rank_0.bin").read_bytes()           # one rank: its chain, as the run combined it
     (d / "batch_hasher.rank_1.bin").write_bytes((d / "batch_hasher.rank_1.bin").read_bytes()[:16])
-    with pytest.raises(HandoffError, match="holds 16 bytes"):
+    with pytest.raises(HandoffError, match="holds 16 bytes, a chain is 32"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2])
     (d / "batch_hasher.rank_1.bin").unlink()
-    with pytest.raises(HandoffError, match=r"batch_hasher.rank_1.bin is missing.*dp_world_size=2"):
+    with pytest.raises(HandoffError, match=r"batch_hasher.rank_1.bin is missing; with dp_world_size=2"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2])
 
 
@@ -127,31 +127,31 @@ def test_gradient_files_that_do_not_account_for_the_model_are_refused(handoff, t
             verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2])
 
     side.unlink()
-    refused("is missing.*never read as 'every gradient was None'")
+    refused("is missing.*not the same as a model whose gradients were all None")
     for md in ({"format": "something-else", "format_version": "1", "none_grad_names": "[]"}, {"format": "pretrain-audit-gradients", "format_version": "2", "none_grad_names": "[]"}):
         save_file(tensors, str(side), metadata=md)
-        refused("unsupported gradient file format")
+        refused("format tag")
     save_file(tensors, str(side), metadata={"format": "pretrain-audit-gradients", "format_version": "1"})
-    refused("invalid gradient file: KeyError")
+    refused(r"does not parse as a gradient file \(KeyError")
     for bad in ('{"a": 1}', "[1, 2]", "not json"):
         save_file(tensors, str(side), metadata=dict(ok, none_grad_names=bad))
-        refused("none_grad_names must be a list of strings|invalid gradient file")
+        refused("none_grad_names is not a list of names|does not parse as a gradient file")
     side.write_bytes(b"\x00" * 64)
-    refused("invalid gradient file")
+    refused("does not parse as a gradient file")
     save_file(tensors, str(side), metadata=dict(ok, none_grad_names=json.dumps([name])))
-    refused("both as a tensor and as a parameter without gradient")
+    refused("has a tensor AND is listed as having no gradient")
     save_file(tensors, str(side), metadata=dict(ok, none_grad_names=json.dumps(["x.y", "x.y"])))
-    refused("lists a name twice")
+    refused("a name appears twice in none_grad_names")
     save_file(dict(tensors, **{"not.a.parameter": torch.zeros(2)}), str(side), metadata=ok)
-    refused("parameters this model does not have")
+    refused("names parameters the model does not have: not.a.parameter")
     fewer = dict(tensors)
     fewer.pop(name)
     save_file(fewer, str(side), metadata=ok)
-    refused("accounts for no gradient at all for")
+    refused("says nothing about %s" % name.replace(".", r"\."))
     save_file(dict(fewer, **{name: tensors[name].reshape(-1)[:-1].clone()}), str(side), metadata=ok)    # another model's shape
-    refused("gradient of %s is torch.float32" % name.replace(".", r"\."))
+    refused("%s comes as torch.float32" % name.replace(".", r"\."))
     save_file(dict(fewer, **{name: tensors[name].to(torch.bfloat16)}), str(side), metadata=ok)
-    refused("is torch.bfloat16")
+    refused("comes as torch.bfloat16")
     # an explicit zero gradient is not an absent one: naming the parameter in none_grad_names instead is accepted by the
     # reader but hashes as this engine hashes a zero gradient, so only a tensor that really was zero would still verify
     save_file(fewer, str(side), metadata=dict(ok, none_grad_names=json.dumps([name])))
@@ -169,41 +169,41 @@ def test_incomplete_self_contradicting_and_off_cadence_artifacts_are_refused(han
     kw = dict(expect_hash=hashes[3], prev_hash=hashes[2])
     d = _copy(ck, tmp_path / "c" / "checkpoints" / "step_000000003")
     (d / "_COMPLETE").unlink()
-    with pytest.raises(HandoffError, match="no _COMPLETE marker"):
+    with pytest.raises(HandoffError, match="has no _COMPLETE marker"):
         verify_handoff(str(d), **kw)
     d = _copy(ck, tmp_path / "n" / "checkpoints" / "step_000000003")
     (d / "meta.json").unlink()
-    with pytest.raises(HandoffError, match="meta.json is missing"):
+    with pytest.raises(HandoffError, match="meta.json is missing, so neither topology nor hash cadence"):
         verify_handoff(str(d), **kw)
     (d / "meta.json").write_text("[1, 2")
-    with pytest.raises(HandoffError, match="not readable JSON"):
+    with pytest.raises(HandoffError, match="is not readable JSON"):
         verify_handoff(str(d), **kw)
     (d / "meta.json").write_text("[1, 2]")
-    with pytest.raises(HandoffError, match="must hold a JSON object"):
+    with pytest.raises(HandoffError, match="expected a JSON object"):
         verify_handoff(str(d), **kw)
     for step in (None, 0, -3, "3", 3.0, True):
         d2 = _copy(ck, tmp_path / ("st%r" % (step,)).replace(".", "_") / "checkpoints" / "step_000000003")
         _edit_meta(d2, step=step)
-        with pytest.raises(HandoffError, match="step must be a positive integer"):
+        with pytest.raises(HandoffError, match="step has to be a positive integer"):
             verify_handoff(str(d2), **kw)
     # the artifact's own claim disagrees with the published value: refused before anything is loaded
     d = _copy(ck, tmp_path / "claim" / "checkpoints" / "step_000000003")
-    with pytest.raises(HandoffError, match="claims another state than the run published for step 3"):
+    with pytest.raises(HandoffError, match="the directory and the published log disagree about step 3"):
         verify_handoff(str(d), expect_hash="5" * 64, prev_hash=hashes[2])
     # state_hash.txt that is not the running chain (an off-cadence side link, or a doctored file)
     (d / "state_hash.txt").write_text("7" * 64 + "\n")
-    with pytest.raises(HandoffError, match="disagrees with the running chain"):
+    with pytest.raises(HandoffError, match="is not the running chain recorded in meta.json"):
         verify_handoff(str(d), **kw)
     # a cadence the step is not on, and a run that never hashed
     d = _copy(ck, tmp_path / "cad" / "checkpoints" / "step_000000003")
     cfg = json.loads(json.loads((d / "meta.json").read_text())["config_resolved"])
     cfg["train"]["state_hash"]["every_n_steps"] = 2
     _edit_meta(d, config_resolved=json.dumps(cfg))
-    with pytest.raises(HandoffError, match="off the run's hash cadence"):
+    with pytest.raises(HandoffError, match="lies between hashed steps"):
         verify_handoff(str(d), **kw)
     cfg["train"]["state_hash"]["every_n_steps"] = 0
     _edit_meta(d, config_resolved=json.dumps(cfg))
-    with pytest.raises(HandoffError, match="did not hash its state"):
+    with pytest.raises(HandoffError, match="never hashed its state"):
         verify_handoff(str(d), **kw)
 
 
@@ -213,7 +213,7 @@ def test_an_implausible_topology_is_refused(handoff, tmp_path, bad):
     tmp, res, ck, hashes = handoff
     d = _copy(ck, tmp_path / "checkpoints" / "step_000000003")
     _edit_meta(d, **bad)
-    with pytest.raises(HandoffError, match="implausible topology|topology is inconsistent"):
+    with pytest.raises(HandoffError, match="is implausible|does not multiply out"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2])
 
 
@@ -230,14 +230,14 @@ def test_cheap_refusals_do_not_apply_the_checkpoints_environment(handoff, tmp_pa
     d = _copy(ck, tmp_path / "checkpoints" / "step_000000003")
     _edit_meta(d, kernel_env={"OTB_GEMM_PLAIN_TEST_MARK": "1", "PRETRAIN_AUDIT_STREAM_HEAD": "1"}, dp_world_size=10 ** 6)
     before = dict(os.environ)
-    with pytest.raises(HandoffError, match="implausible topology"):
+    with pytest.raises(HandoffError, match="is implausible"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2])
     assert dict(os.environ) == before
     monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
     d = _copy(ck, tmp_path / "dev" / "checkpoints" / "step_000000003")
-    with pytest.raises(HandoffError, match="CUDA is unavailable"):
+    with pytest.raises(HandoffError, match="no CUDA device here"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2], device="cuda")
-    with pytest.raises(HandoffError, match="verifies on cpu or cuda"):
+    with pytest.raises(HandoffError, match="can be held on cpu or cuda"):
         verify_handoff(str(d), expect_hash=hashes[3], prev_hash=hashes[2], device="meta")
     # metadata that tries to redirect native code is refused as a hand-off error, not applied
     _edit_meta(d, kernel_env={"LD_PRELOAD": "/tmp/x.so"})
@@ -261,7 +261,7 @@ def test_command_line_round_trip_tampering_and_json_result(handoff, tmp_path, ca
     out.write_text(json.dumps({"verified": True}))
     assert verify_main(["--checkpoint", ck, "--expect-hash", "abc", "--prev-hash", hashes[2], "--json", str(out)]) == 1
     refusal = json.loads(out.read_text())
-    assert refusal["verified"] is False and "--expect-hash must be a full literal hex digest" in refusal["error"]
+    assert refusal["verified"] is False and "--expect-hash takes the 64 hex digits" in refusal["error"]
     capsys.readouterr()
     # an unexpected failure (here: the tensor payload is gone) is reported with its type, as JSON, not as a traceback exit
     d = _copy(ck, tmp_path / "broken" / "checkpoints" / "step_000000003")
