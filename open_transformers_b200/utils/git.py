@@ -56,9 +56,9 @@ def native_source_digests() -> dict:
 
 
 def run_provenance() -> dict:
-    from .. import __version__
+    from .. import __version__, build_info
     from ..ops import native
 
     return {"framework": "open_transformers_b200", "version": __version__, "git_sha": git_sha(), "dirty": bool(git_diff()),
-            "repo": repo_provenance("open_transformers_b200"),
+            "repo": repo_provenance("open_transformers_b200"), "backends": build_info()["backends"],
             "native_libs": native.loaded_libraries(), "native_source_digests": native_source_digests()}

@@ -557,3 +557,11 @@ def test_tensor_level_helpers_rope_zloss_norm():
     m1, m2 = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
     init_weights_seeded(m1, 5), init_weights_seeded(m2, 5)
     assert torch.equal(m1.weight, m2.weight) and float(m1.bias.detach().abs().sum()) == 0.0
+
+
+def test_build_info_names_backends_and_commit():
+    import open_transformers_b200 as pkg
+
+    info = pkg.build_info()
+    assert info["version"] == pkg.__version__ and "cpu" in info["backends"] and isinstance(info["native_source_digests"], dict)
+    assert info["commit"] and isinstance(info["python_native"], bool)
