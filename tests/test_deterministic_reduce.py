@@ -197,3 +197,41 @@ def test_shard0_helpers():
     assert all(p.shape == (3, 3) for p in padded) and torch.equal(padded[3][0], t[9]) and float(padded[3][1:].abs().sum()) == 0.0
     # more shards than rows: the trailing shards are empty / all padding
     assert DR.shard0_logical_chunk(t[:2], 3, 4).shape[0] == 0 and DR.shard0_chunk(t[:2], 3, 4).shape == (1, 3)
+
+
+# ---- telemetry scalars: one fp64 fold in rank order, the same on every rank (gloo ranks on the CPU)
+
+def _scalar_fold_worker(rank, world, init_file, out_dir):
+    import json
+    import os
+
+    import torch.distributed as dist
+
+    from open_transformers_b200.train.loop import deterministic_scalar_sum, deterministic_scalar_sums
+
+    dist.init_process_group("gloo", init_method="file://" + init_file, rank=rank, world_size=world)
+    try:
+        # values whose fp64 sum depends on the order: 1e16 + 1 - 1e16 is 0 or 1 depending on the grouping
+        mine = [[1e16, 0.25], [1.0], [-1e16, 3.0, 0.5]][rank]
+        total, n = deterministic_scalar_sum(mine, world)
+        both = deterministic_scalar_sums({"a": mine, "b": [float(rank)] * (rank + 1)}, world)
+        with open(os.path.join(out_dir, "rank%d.json" % rank), "w") as f:
+            json.dump({"total": total.hex(), "n": n, "a": both["a"][0].hex(), "b": list(both["b"])}, f)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_scalar_fold_is_the_rank_ordered_fp64_sum_on_every_rank(tmp_path):
+    import json
+
+    import torch.multiprocessing as mp
+
+    world = 3
+    mp.spawn(_scalar_fold_worker, args=(world, str(tmp_path / "init"), str(tmp_path)), nprocs=world, join=True)
+    want = 0.0
+    for v in [1e16, 0.25, 1.0, -1e16, 3.0, 0.5]:
+        want += v
+    rows = [json.loads((tmp_path / ("rank%d.json" % r)).read_text()) for r in range(world)]
+    assert all(r == rows[0] for r in rows)
+    assert rows[0]["total"] == want.hex() == rows[0]["a"] and rows[0]["n"] == 6 and rows[0]["b"] == [0.0 + 1.0 + 1.0 + 2.0 + 2.0 + 2.0, 6]
+    assert want != sum(sorted([1e16, 0.25, 1.0, -1e16, 3.0, 0.5]))       # another order gives another value: the order is what is pinned
