@@ -46,30 +46,16 @@ class ParallelDims:
     def tp_rank(self, rank: int) -> int:
         return rank % self.tp
 
-    # ---- the reference's vocabulary (src/pretrain/parallel/parallel_dims.py:141-194), over the virtual topology
-    @property
-    def dp_replicate_enabled(self) -> bool:
-        return self.dp_replicate > 1
-
-    @property
-    def dp_shard_enabled(self) -> bool:
-        return self.dp_shard > 1
-
-    @property
-    def fsdp_enabled(self) -> bool:
-        return self.dp_shard_enabled
-
-    @property
-    def dp_enabled(self) -> bool:
-        return self.dp_replicate_enabled or self.dp_shard_enabled
-
-    @property
-    def dp_world_size(self) -> int:
-        """Ranks that consume distinct tokens: the VIRTUAL data-parallel size (a tensor-parallel group shares its batch)."""
-        return self.virtual_dp
+    # ---- the reference's vocabulary (src/pretrain/parallel/parallel_dims.py:141-194), answered from the virtual topology
+    dp_replicate_enabled = property(lambda self: self.dp_replicate > 1)
+    dp_shard_enabled = property(lambda self: self.dp_shard > 1)
+    fsdp_enabled = dp_shard_enabled
+    dp_enabled = property(lambda self: self.virtual_dp > 1)
+    # ranks that consume distinct tokens: the VIRTUAL data-parallel size (a tensor-parallel group shares its batch)
+    dp_world_size = property(lambda self: self.virtual_dp)
 
     def dp_rank(self, global_rank: int = 0) -> int:
-        """The data-parallel process index of a physical rank (its first hosted virtual rank divided by the ranks per process)."""
+        """Index of a physical rank's data-parallel process (the ranks of one tensor-parallel group share it)."""
         return global_rank // self.tp
 
     def make_dp_gloo_group(self):
