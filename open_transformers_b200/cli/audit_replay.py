@@ -272,13 +272,19 @@ def audit_replay(checkpoint: str | None = None, *, config_name: str | None = Non
     plan = memory_plan(count_parameters(m), cfg.run.virtual_dp_size, max(1, cfg.run.dp_replicate_size), bool(cfg.run.mixed_precision), act,
                        _free_bytes(device), int(float(os.environ.get("PRETRAIN_AUDIT_MEM_RESERVE_GB", "4")) * 2 ** 30),
                        offload_grads, offload_optimizer)
-    for what in plan["auto"]:
-        log.warning("memory plan: %s AUTO-ENABLED - %.1f GiB free is less than the default plan needs; pass the flag to make it explicit",
-                    what, plan["free_bytes"] / 2 ** 30)
-    if not plan["fits"]:
-        log.warning("memory plan: about %.1f GiB needed, %.1f GiB free - the replay may run out of memory", plan["need_bytes"] / 2 ** 30,
-                    plan["free_bytes"] / 2 ** 30)
-    offload_grads, offload_optimizer = plan["offload_grads"], plan["offload_optimizer"]
+    init_only = from_init and until_step in (None, 0)
+    if init_only:
+        # an init audit never runs a step: gradient buffers and moments stay untouched zero pages, no activations exist, and
+        # moments kept in files would only make the full hash read them back. The plan is for replays that train.
+        offload_grads = True   # one work buffer instead of one per virtual rank; nothing is ever written to it
+    else:
+        for what in plan["auto"]:
+            log.warning("memory plan: %s AUTO-ENABLED - %.1f GiB free is less than the default plan needs; pass the flag to make it explicit",
+                        what, plan["free_bytes"] / 2 ** 30)
+        if not plan["fits"]:
+            log.warning("memory plan: about %.1f GiB needed, %.1f GiB free - the replay may run out of memory", plan["need_bytes"] / 2 ** 30,
+                        plan["free_bytes"] / 2 ** 30)
+        offload_grads, offload_optimizer = plan["offload_grads"], plan["offload_optimizer"]
     spill = None if (no_fold_spill or not offload_grads) else fold_spill_dir
     # --offload-optimizer / --offload-master: moments / fp32 master weights live in files between steps
     engine = TrainEngine(cfg, device, 0, 1, init=from_init or checkpoint is None, fold_gradients=offload_grads, fold_spill_dir=spill,

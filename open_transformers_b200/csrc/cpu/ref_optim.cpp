@@ -299,18 +299,23 @@ static inline float erfinv_central(float x) {  // |x| <= 0.96; Giles' single-pre
 // (seed, its index in the stream), never on how the work is split.
 void otb_cpu_trunc_normal(float* out, long n, float std, uint64_t seed, uint64_t offset) {
   const float span = 0.95449973610364158f;  // erf(2/sqrt(2)) = P(|z| <= 2)
+  // one Philox block yields the four words 4b .. 4b+3; walk whole blocks and drop the words outside [offset, offset + n)
+  const uint64_t first = offset, end = offset + (uint64_t)n;
+  const long b0 = (long)(first >> 2), b1 = (long)((end + 3) >> 2);
 #pragma omp parallel for schedule(static)
-  for (long i = 0; i < n; ++i) {
-    const uint64_t w = offset + (uint64_t)i;
+  for (long b = b0; b < b1; ++b) {
     uint32_t r[4];
-    philox4x32(w >> 2, seed, r);
-    const uint32_t bits = r[w & 3];
-    // uniform in (-1, 1), 24 bits, symmetric about 0
-    const float u = ((float)(bits >> 8) + 0.5f) * (1.0f / 8388608.0f) - 1.0f;
-    float z = 1.41421356237309505f * erfinv_central(u * span);
-    if (z > 2.0f) z = 2.0f;
-    if (z < -2.0f) z = -2.0f;
-    out[i] = z * std;
+    philox4x32((uint64_t)b, seed, r);
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t w = ((uint64_t)b << 2) + (uint64_t)j;
+      if (w < first || w >= end) continue;
+      // uniform in (-1, 1), 24 bits, symmetric about 0
+      const float u = ((float)(r[j] >> 8) + 0.5f) * (1.0f / 8388608.0f) - 1.0f;
+      float z = 1.41421356237309505f * erfinv_central(u * span);
+      if (z > 2.0f) z = 2.0f;
+      if (z < -2.0f) z = -2.0f;
+      out[w - first] = z * std;
+    }
   }
 }
 }  // extern "C"

@@ -27,10 +27,12 @@ def init_weights(model: nn.Module, seed: int | None, std: float | None = None) -
             if p.dim() >= 2 and seed is None:
                 nn.init.trunc_normal_(p, std=std, a=-2 * std, b=2 * std)
             elif p.dim() >= 2:
-                buf = torch.empty(p.shape, dtype=torch.float32)
+                direct = p.device.type == "cpu" and p.dtype == torch.float32 and p.is_contiguous()
+                buf = p.data if direct else torch.empty(p.shape, dtype=torch.float32)   # fp32 host parameters are filled in place
                 trunc_normal_(buf, std, seed, offset)
                 offset += p.numel()
-                p.copy_(buf.to(p.dtype))
+                if not direct:
+                    p.copy_(buf.to(p.dtype))
             elif name.endswith("norm.weight") or ".norm" in name or "norm_" in name or name.endswith("_norm.weight"):
                 p.fill_(1.0)
             else:

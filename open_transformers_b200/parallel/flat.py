@@ -109,6 +109,20 @@ class _CudaPtr:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+def lazy_zeros(n: int, dtype: torch.dtype, device) -> torch.Tensor:
+    """``torch.zeros`` for the large flat buffers. On the CPU the tensor sits on an anonymous memory mapping: pages exist
+    only once they are read or written, so a buffer that is never used (the gradient buffers of an init audit, which runs no
+    step) costs neither time nor resident memory, where ``torch.zeros`` writes every byte up front. The tensor keeps the
+    mapping alive. Device tensors, and small ones, are plain ``torch.zeros``."""
+    device = torch.device(device)
+    nbytes = n * dtype.itemsize
+    if device.type != "cpu" or nbytes < (1 << 24):
+        return torch.zeros(n, dtype=dtype, device=device)
+    import mmap
+
+    return torch.frombuffer(mmap.mmap(-1, nbytes), dtype=dtype, count=n)
+
+
 class PeerBuffer:
     """A flat device buffer every rank of ``group`` can address: ``ptrs[r]`` is rank r's buffer as
     seen from this process (CUDA IPC mapping for r != rank). On the CPU, or with a single rank, it is
@@ -123,7 +137,7 @@ class PeerBuffer:
         if storage is not None:  # caller-provided bytes (a file mapping): single rank only
             assert not self._ipc and storage.dtype == torch.uint8 and storage.numel() >= nbytes
         if not self._ipc:
-            self.bytes = storage[:nbytes] if storage is not None else torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            self.bytes = storage[:nbytes] if storage is not None else lazy_zeros(nbytes, torch.uint8, device)
             self.ptrs = [self.bytes.data_ptr()]
             return
         import torch.distributed as dist

@@ -43,7 +43,7 @@ from ..models.precision import PrecisionPolicy
 from ..ops import functional as K
 from ..ops.autograd import GradSlot, set_tp, wgrad_join
 from ..ops.native import F, I, P, check, cpu_lib, cuda_lib, stream_ptr
-from ..parallel.flat import FlatLayout, PeerBuffer
+from ..parallel.flat import FlatLayout, PeerBuffer, lazy_zeros
 from ..parallel.parallel_dims import ParallelDims
 from . import state_hash as SH
 
@@ -277,7 +277,7 @@ class TrainEngine:
         else:
             self._m1 = torch.zeros(n_state, dtype=torch.float32, device=self.device)
             self._m2 = torch.zeros(n_state, dtype=torch.float32, device=self.device)
-        self.grad_red = torch.zeros(n_state, dtype=torch.float32, device=self.device)
+        self.grad_red = lazy_zeros(n_state, torch.float32, self.device)
         if self.collective:
             # the chunk table of this process's own segments inside its packed buffer
             mine = []
@@ -315,10 +315,17 @@ class TrainEngine:
                 with host_threads():
                     init_weights(model, cfg.run.seed if seed is None else seed)
             else:
+                # on the host the parameters become views of the master buffer BEFORE they are sampled, so that the stream
+                # is written once, where it will live (no second copy of the model, no second pass over its pages)
+                for i, (name, p) in enumerate(named):
+                    if p.dtype == torch.float32:
+                        p.data = lay.view(self.master, i)
                 init_weights(model, cfg.run.seed if seed is None else seed)
         with torch.no_grad():
             for i, (name, p) in enumerate(named):
-                lay.view(self.master, i).copy_(p.detach().to(torch.float32))
+                dst = lay.view(self.master, i)
+                if p.data_ptr() != dst.data_ptr():
+                    dst.copy_(p.detach().to(torch.float32))
         self.model = model
         self.names = lay.names
         self.slots = [GradSlot() for _ in named]
@@ -1378,7 +1385,7 @@ class TrainEngine:
                         h.update(tag + head)
                         row = lay.numels[pi] // max(shape[0], 1)
                         st = lay.offsets[pi] + lo * row
-                        h.update(SH.tensor_bytes(flat[st:st + (hi - lo) * row]))
+                        SH.feed_raw(h, flat[st:st + (hi - lo) * row])
 
                 feed(b"weight", "weight", self.master)
                 h.update(step_bytes)

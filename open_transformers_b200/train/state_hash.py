@@ -52,6 +52,22 @@ def tensor_bytes(t: torch.Tensor) -> bytes:
     return t.view(torch.uint8).numpy().tobytes() if t.dim() > 0 else t.reshape(1).view(torch.uint8).numpy().tobytes()
 
 
+FEED_CHUNK = 1 << 26
+
+
+def feed_raw(h, t: torch.Tensor) -> None:
+    """``h.update`` over a tensor's raw little-endian bytes without building a ``bytes`` copy of it: the hash reads the
+    tensor's own memory (a host copy first, for a device tensor) in 64 MB pieces. The digest is that of
+    ``h.update(tensor_bytes(t))``; for the 19 GB of weights and moments of a 1.6 B-parameter model the copy was most of the time
+    and all of the extra memory of a full hash."""
+    t = t.detach().to("cpu").contiguous()
+    if t.numel() == 0:
+        return
+    flat = t.reshape(-1).view(torch.uint8).numpy()
+    for at in range(0, flat.size, FEED_CHUNK):
+        h.update(flat[at:at + FEED_CHUNK])
+
+
 def tree_digest_bytes(data: bytes | np.ndarray) -> bytes:
     """32-byte tree digest of a byte string (host implementation)."""
     from ..ops.native import cpu_lib
@@ -187,7 +203,7 @@ def feed_tensor(h, tag: str, t: torch.Tensor, tensor_digest: str = "raw", precom
         h.update(b"tree\0")
         h.update(precomputed if precomputed is not None else tree_digest_tensor(t))
     else:
-        h.update(tensor_bytes(t))
+        feed_raw(h, t)
 
 
 def param_groups_json(param_groups: Sequence[Mapping[str, Any]]) -> bytes:
@@ -321,7 +337,7 @@ class RunningBatchHasher:
         for k in sorted(batch):
             t = batch[k]
             h.update(k.encode() + b"\0" + str(t.dtype).encode() + b"\0" + str(tuple(t.shape)).encode() + b"\0")
-            h.update(tensor_bytes(t))
+            feed_raw(h, t)
         self._chain = h.digest()
 
     def local_digest(self) -> bytes:
