@@ -120,7 +120,10 @@ def lazy_zeros(n: int, dtype: torch.dtype, device) -> torch.Tensor:
         return torch.zeros(n, dtype=dtype, device=device)
     import mmap
 
-    return torch.frombuffer(mmap.mmap(-1, nbytes), dtype=dtype, count=n)
+    try:
+        return torch.frombuffer(mmap.mmap(-1, nbytes), dtype=dtype, count=n)
+    except (OSError, ValueError):   # no anonymous mapping of that size on this system: the ordinary allocation reports the error
+        return torch.zeros(n, dtype=dtype, device=device)
 
 
 class PeerBuffer:

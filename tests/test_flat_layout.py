@@ -80,3 +80,19 @@ def test_parallel_dims_vocabulary_over_the_virtual_topology():
     assert tp.dp_world_size == 2 and tp.dp_shard == 2 and [tp.dp_rank(r) for r in (0, 3, 4, 7)] == [0, 0, 1, 1]
     virt = ParallelDims(2, 4, 2, virtual_dp=8)              # eight virtual ranks on two processes
     assert virt.dp_world_size == 8 and virt.hosted_virtual_ranks(1) == [4, 5, 6, 7]
+
+
+def test_lazy_zeros_is_zero_writable_and_aligned():
+    import torch
+
+    from open_transformers_b200.parallel.flat import lazy_zeros
+
+    big = lazy_zeros(5_000_000, torch.float32, "cpu")          # above the threshold: an anonymous mapping
+    assert big.dtype == torch.float32 and big.numel() == 5_000_000 and float(big.abs().sum()) == 0.0 and big.data_ptr() % 4096 == 0
+    big[123] = 2.5
+    big[-1] = -1.0
+    assert float(big.sum()) == 1.5 and big.view(torch.uint8).numel() == 20_000_000
+    small = lazy_zeros(10, torch.int32, "cpu")
+    assert small.dtype == torch.int32 and int(small.sum()) == 0
+    half = lazy_zeros(10_000_000, torch.bfloat16, "cpu")
+    assert half.dtype == torch.bfloat16 and float(half.float().abs().sum()) == 0.0
