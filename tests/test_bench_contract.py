@@ -106,3 +106,18 @@ def test_defaults_are_one_gpu_and_at_least_three_warm_up_steps():
     assert r.returncode == 0 and "--gpus" in r.stdout and "--steps" in r.stdout and "--warmup" in r.stdout and "--impl" in r.stdout
     src = (ROOT / "bench.py").read_text()
     assert 'add_argument("--gpus", type=int, default=1)' in src and 'add_argument("--warmup", type=int, default=3)' in src
+
+
+def test_cpu_microbatch_benchmark_prints_engine_and_microbatch_lines():
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([sys.executable, str(root / "benchmarks" / "cpu_microbatch.py"), "--config-name", "tiny_cpu", "--cpu-threads", "2"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(line) for line in r.stdout.splitlines() if line.startswith("{")]
+    assert len(rows) == 2 and rows[0]["threads"] == 2 and "engine_s" in rows[0]
+    assert rows[1]["tokens"] > 0 and rows[1]["microbatch_fwd_bwd_s"] > 0 and rows[1]["loss_ce"] > 0 and rows[1]["peak_rss_gb"] > 0
